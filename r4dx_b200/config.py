@@ -1,0 +1,236 @@
+"""Model configuration for the Qwen-style hybrid family (Gated DeltaNet + gated full attention).
+
+Covers the dense hybrid (27B geometry), the tiny 4-layer test geometry and the hybrid MoE
+variant (routed experts + shared expert).  ``shard(world, rank)`` returns the rank-local view for
+tensor parallelism at world 1/2/4/8; unlike the reference, whose ``ModelConfig::Shard`` accepts
+world 2 only (reference: src/model/model_config.h:211-266), KV heads are replicated when the
+world exceeds the KV head count so that TP=8 works on 4 KV heads.
+"""
+from __future__ import annotations
+
+import dataclasses
+import json
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+
+@dataclass
+class ModelConfig:
+    arch: str = "qwen_hybrid"          # qwen_hybrid | qwen_hybrid_moe | llama
+    hidden_size: int = 0
+    num_hidden_layers: int = 0
+    layer_types: List[str] = field(default_factory=list)   # "linear_attention" | "full_attention"
+    num_attention_heads: int = 0
+    num_key_value_heads: int = 0
+    head_dim: int = 0
+    attn_output_gate: bool = True
+    intermediate_size: int = 0
+    partial_rotary_factor: float = 0.25
+    rope_theta: float = 1.0e7
+    mrope_interleaved: bool = True
+    mrope_section: List[int] = field(default_factory=list)
+    linear_num_key_heads: int = 0
+    linear_num_value_heads: int = 0
+    linear_key_head_dim: int = 0
+    linear_value_head_dim: int = 0
+    linear_conv_kernel_dim: int = 4
+    rms_norm_eps: float = 1e-6
+    vocab_size: int = 0
+    tie_word_embeddings: bool = False
+    mtp_num_hidden_layers: int = 0
+    max_position_embeddings: int = 262144
+    # MoE variant (0 experts = dense MLP in every layer)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    shared_expert_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    # tensor parallel view
+    tp_world: int = 1
+    tp_rank: int = 0
+    kv_replicas: int = 1               # >1 when tp_world > global KV heads
+
+    # ---- derived shapes (names follow reference src/model/model_config.h:76-96) ----
+    @property
+    def key_dim(self) -> int:
+        return self.linear_num_key_heads * self.linear_key_head_dim
+
+    @property
+    def value_dim(self) -> int:
+        return self.linear_num_value_heads * self.linear_value_head_dim
+
+    @property
+    def conv_dim(self) -> int:
+        return 2 * self.key_dim + self.value_dim
+
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor + 0.5)
+
+    @property
+    def gdn_gqa(self) -> int:
+        return self.linear_num_value_heads // max(1, self.linear_num_key_heads)
+
+    @property
+    def attn_gqa(self) -> int:
+        return self.num_attention_heads // max(1, self.num_key_value_heads)
+
+    @property
+    def q_dim(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    @property
+    def vocab_shard_size(self) -> int:
+        return self.vocab_size // self.tp_world
+
+    @property
+    def vocab_shard_begin(self) -> int:
+        return self.tp_rank * self.vocab_shard_size
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def is_attention_layer(self, i: int) -> bool:
+        return self.layer_types[i] == "full_attention"
+
+    def num_attention_layers(self) -> int:
+        return sum(1 for t in self.layer_types if t == "full_attention")
+
+    def validate(self) -> None:
+        if len(self.layer_types) != self.num_hidden_layers:
+            raise ValueError("layer_types length != num_hidden_layers")
+        if self.num_attention_heads % max(1, self.num_key_value_heads):
+            raise ValueError("attention heads not a multiple of KV heads")
+        if self.linear_num_value_heads % max(1, self.linear_num_key_heads):
+            raise ValueError("GDN value heads not a multiple of key heads")
+        if self.hidden_size % 128:
+            raise ValueError("hidden_size must be a multiple of 128 (trellis block)")
+
+    # ---- tensor-parallel shard view --------------------------------------------------------
+    def shard(self, world: int, rank: int) -> "ModelConfig":
+        """Rank-local view: head counts and intermediate sizes of this rank's slices.
+
+        vocab_size stays global; the lm_head width is ``vocab_shard_size``.  Contiguous head
+        blocks per rank keep the GQA grouping intact.  When ``world`` exceeds the KV head count
+        each KV head is replicated on ``world / kv_heads`` consecutive ranks.
+        """
+        if world not in (1, 2, 4, 8):
+            raise ValueError(f"tp world {world} not in (1, 2, 4, 8)")
+        if not 0 <= rank < world:
+            raise ValueError("rank out of range")
+        if self.tp_world != 1:
+            raise ValueError("shard() must be called on the global config")
+        if world == 1:
+            return dataclasses.replace(self)
+        c = dataclasses.replace(self, tp_world=world, tp_rank=rank)
+
+        def div(v: int, what: str) -> int:
+            if v % world:
+                raise ValueError(f"{what}={v} not divisible by tp world {world}")
+            return v // world
+
+        c.num_attention_heads = div(self.num_attention_heads, "num_attention_heads")
+        if self.num_key_value_heads >= world:
+            c.num_key_value_heads = div(self.num_key_value_heads, "num_key_value_heads")
+            c.kv_replicas = 1
+        else:
+            if world % self.num_key_value_heads:
+                raise ValueError("tp world not a multiple of KV heads")
+            c.num_key_value_heads = 1
+            c.kv_replicas = world // self.num_key_value_heads
+            if c.num_attention_heads * world // self.num_key_value_heads % c.kv_replicas:
+                raise ValueError("query heads do not split evenly over replicated KV heads")
+        c.linear_num_key_heads = div(self.linear_num_key_heads, "linear_num_key_heads")
+        c.linear_num_value_heads = div(self.linear_num_value_heads, "linear_num_value_heads")
+        c.intermediate_size = div(self.intermediate_size, "intermediate_size") if self.intermediate_size else 0
+        if c.intermediate_size % 128:
+            raise ValueError("per-rank intermediate_size must stay a multiple of 128")
+        if self.vocab_size % (world * 16):
+            raise ValueError("vocab shard must be a multiple of 16 rows")
+        if self.shared_expert_intermediate_size:
+            c.shared_expert_intermediate_size = div(self.shared_expert_intermediate_size, "shared expert")
+        return c
+
+    def kv_head_of_rank(self) -> int:
+        """Global index of the first KV head held by this rank."""
+        if self.kv_replicas > 1:
+            return self.tp_rank // self.kv_replicas
+        return self.tp_rank * self.num_key_value_heads
+
+    # ---- json ------------------------------------------------------------------------------
+    def to_json(self) -> str:
+        return json.dumps(dataclasses.asdict(self), sort_keys=True)
+
+    @staticmethod
+    def from_json(text: str) -> "ModelConfig":
+        d = json.loads(text)
+        if "text_config" in d:
+            d = d["text_config"]
+        known = {f.name for f in dataclasses.fields(ModelConfig)}
+        cfg = ModelConfig(**{k: v for k, v in d.items() if k in known})
+        if not cfg.layer_types and cfg.num_hidden_layers:
+            interval = int(d.get("full_attention_interval", 4))
+            cfg.layer_types = ["full_attention" if (i + 1) % interval == 0 else "linear_attention"
+                               for i in range(cfg.num_hidden_layers)]
+        cfg.validate()
+        return cfg
+
+
+def _pattern(n_layers: int, interval: int = 4) -> List[str]:
+    return ["full_attention" if (i + 1) % interval == 0 else "linear_attention" for i in range(n_layers)]
+
+
+def tiny_hybrid_config() -> ModelConfig:
+    """4-layer test geometry: layers 0-2 Gated DeltaNet, layer 3 gated full attention."""
+    return ModelConfig(
+        hidden_size=256, num_hidden_layers=4, layer_types=_pattern(4),
+        num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+        intermediate_size=512, partial_rotary_factor=0.25, rope_theta=1.0e7,
+        linear_num_key_heads=2, linear_num_value_heads=4,
+        linear_key_head_dim=64, linear_value_head_dim=64, linear_conv_kernel_dim=4,
+        rms_norm_eps=1e-6, vocab_size=4096, mtp_num_hidden_layers=1)
+
+
+def small_hybrid_config(layers: int = 4) -> ModelConfig:
+    """Same per-layer shapes as the 27B geometry's kernels need (head_dim 256 / 128) but narrow."""
+    return ModelConfig(
+        hidden_size=1024, num_hidden_layers=layers, layer_types=_pattern(layers),
+        num_attention_heads=8, num_key_value_heads=2, head_dim=256,
+        intermediate_size=2048, linear_num_key_heads=4, linear_num_value_heads=8,
+        linear_key_head_dim=128, linear_value_head_dim=128, vocab_size=8192, mtp_num_hidden_layers=1)
+
+
+def qwen_hybrid_27b_config(layers: int = 64) -> ModelConfig:
+    """Dense hybrid 27B geometry (reference: docs/architecture.md:85-142)."""
+    return ModelConfig(
+        hidden_size=5120, num_hidden_layers=layers, layer_types=_pattern(layers),
+        num_attention_heads=24, num_key_value_heads=4, head_dim=256,
+        intermediate_size=17408, linear_num_key_heads=16, linear_num_value_heads=48,
+        linear_key_head_dim=128, linear_value_head_dim=128, vocab_size=248320,
+        mtp_num_hidden_layers=1, mrope_section=[11, 11, 10])
+
+
+def qwen_hybrid_moe_config(layers: int = 48) -> ModelConfig:
+    """Hybrid MoE geometry: 512 routed experts, top-10, one shared expert."""
+    return ModelConfig(
+        arch="qwen_hybrid_moe", hidden_size=2048, num_hidden_layers=layers, layer_types=_pattern(layers),
+        num_attention_heads=16, num_key_value_heads=2, head_dim=256,
+        intermediate_size=0, linear_num_key_heads=16, linear_num_value_heads=32,
+        linear_key_head_dim=128, linear_value_head_dim=128, vocab_size=151936,
+        num_experts=512, num_experts_per_tok=10, moe_intermediate_size=512,
+        shared_expert_intermediate_size=512, mtp_num_hidden_layers=0)
+
+
+def tiny_moe_config() -> ModelConfig:
+    return ModelConfig(
+        arch="qwen_hybrid_moe", hidden_size=256, num_hidden_layers=4, layer_types=_pattern(4),
+        num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+        intermediate_size=0, linear_num_key_heads=2, linear_num_value_heads=4,
+        linear_key_head_dim=64, linear_value_head_dim=64, vocab_size=4096,
+        num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128,
+        shared_expert_intermediate_size=128, mtp_num_hidden_layers=0)

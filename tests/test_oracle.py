@@ -1,0 +1,75 @@
+"""CPU oracle self-consistency (tiny hybrid geometry)."""
+import torch
+
+from r4dx_b200.config import tiny_hybrid_config, tiny_moe_config
+from r4dx_b200.models.oracle import OracleModel, OracleState, init_weights
+from r4dx_b200.ops import reference as R
+
+
+def test_gdn_chunked_matches_recurrent():
+    g = torch.Generator().manual_seed(3)
+    T, Hk, H, K, V = 150, 2, 4, 64, 64
+    q = R.l2norm(torch.randn(T, Hk, K, generator=g))
+    k = R.l2norm(torch.randn(T, Hk, K, generator=g))
+    v = torch.randn(T, H, V, generator=g)
+    gate = -torch.rand(T, H, generator=g) * 0.5
+    beta = torch.rand(T, H, generator=g)
+    s0 = torch.randn(H, V, K, generator=g) * 0.1
+    o1, s1 = R.gdn_recurrent(q, k, v, gate, beta, s0)
+    o2, s2 = R.gdn_chunked(q, k, v, gate, beta, s0, chunk=64)
+    assert torch.allclose(o1, o2, atol=2e-4, rtol=1e-4)
+    assert torch.allclose(s1, s2, atol=2e-4, rtol=1e-4)
+
+
+def test_prefill_equals_stepwise():
+    cfg = tiny_hybrid_config()
+    w = init_weights(cfg, 0)
+    m = OracleModel(cfg, w)
+    ids = torch.randint(0, cfg.vocab_size, (24,), generator=torch.Generator().manual_seed(1))
+    full, _ = m.forward(ids)
+    st = OracleState()
+    rows = []
+    for s in (0, 7, 8, 20):
+        e = {0: 7, 7: 8, 8: 20, 20: 24}[s]
+        lg, st = m.forward(ids[s:e], st)
+        rows.append(lg)
+    step = torch.cat(rows)
+    assert torch.allclose(full, step, atol=1e-4, rtol=1e-4)
+
+
+def test_chunked_model_equals_recurrent_model():
+    cfg = tiny_hybrid_config()
+    w = init_weights(cfg, 0)
+    ids = torch.randint(0, cfg.vocab_size, (64,), generator=torch.Generator().manual_seed(1))
+    a, _ = OracleModel(cfg, w).forward(ids)
+    b, _ = OracleModel(cfg, w, chunked_gdn=True).forward(ids)
+    assert torch.allclose(a, b, atol=2e-4, rtol=1e-3)
+
+
+def test_greedy_16_tokens_deterministic():
+    cfg = tiny_hybrid_config()
+    w = init_weights(cfg, 0)
+    ids = torch.randint(0, cfg.vocab_size, (64,), generator=torch.Generator().manual_seed(1))
+    t1 = OracleModel(cfg, w).greedy(ids, 16)
+    t2 = OracleModel(cfg, w).greedy(ids, 16)
+    assert t1 == t2 and len(t1) == 16
+
+
+def test_moe_oracle_runs():
+    cfg = tiny_moe_config()
+    w = init_weights(cfg, 0)
+    ids = torch.randint(0, cfg.vocab_size, (6,), generator=torch.Generator().manual_seed(1))
+    lg, st = OracleModel(cfg, w).forward(ids)
+    assert lg.shape == (6, cfg.vocab_size) and torch.isfinite(lg).all()
+
+
+def test_shard_views():
+    from r4dx_b200.config import qwen_hybrid_27b_config
+    cfg = qwen_hybrid_27b_config()
+    for world in (1, 2, 4, 8):
+        for r in range(world):
+            s = cfg.shard(world, r)
+            assert s.num_attention_heads * world == 24
+            assert s.intermediate_size % 128 == 0
+    s8 = cfg.shard(8, 5)
+    assert s8.num_key_value_heads == 1 and s8.kv_replicas == 2 and s8.kv_head_of_rank() == 2
