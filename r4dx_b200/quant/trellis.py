@@ -1,0 +1,99 @@
+"""Trellis-coded weights: Python face of the C++ quantizer / decoder.
+
+Format and bit-exact decode definition: ``native/include/r4dxb_trellis.h``.
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from .. import native
+
+
+@dataclass
+class TrellisWeight:
+    """One quantized linear. ``words`` int32 [packed], ``suh`` fp16 [K], ``svh`` fp16 [N]."""
+    words: torch.Tensor
+    suh: torch.Tensor
+    svh: torch.Tensor
+    N: int
+    K: int
+    kb: int
+
+    def to(self, device) -> "TrellisWeight":
+        return TrellisWeight(self.words.to(device), self.suh.to(device), self.svh.to(device), self.N, self.K, self.kb)
+
+    @property
+    def nbytes(self) -> int:
+        return self.words.numel() * 4 + self.suh.numel() * 2 + self.svh.numel() * 2
+
+
+def _ptr(t: torch.Tensor) -> int:
+    return t.data_ptr()
+
+
+def packed_words(N: int, K: int, kb: int) -> int:
+    return (N // 16) * (K // 16) * 8 * kb
+
+
+def quantize(W: torch.Tensor, kb: int, seed: int = 0, threads: int | None = None) -> tuple[TrellisWeight, float]:
+    """Viterbi-quantizes W [N, K] (any float dtype, CPU). Returns (weight, relative squared error)."""
+    L = native.host()
+    W = W.detach().to(torch.float32).contiguous().cpu()
+    N, K = W.shape
+    if N % 128 or K % 128:
+        raise ValueError(f"trellis needs N and K multiples of 128, got {N}x{K}")
+    words = torch.empty(packed_words(N, K, kb), dtype=torch.int32)
+    suh = torch.empty(K, dtype=torch.float16)
+    svh = torch.empty(N, dtype=torch.float16)
+    threads = threads or min(32, os.cpu_count() or 1)
+    err = L.r4dxb_trellis_quantize(_ptr(W), N, K, kb, seed, threads, _ptr(words), _ptr(suh), _ptr(svh))
+    if err < 0:
+        raise ValueError("r4dxb_trellis_quantize rejected the arguments")
+    return TrellisWeight(words, suh, svh, N, K, kb), float(err)
+
+
+def random_weight(N: int, K: int, kb: int, seed: int = 0, sigma: float = 0.02, device="cpu") -> TrellisWeight:
+    """Synthetic weight: random code bits (values ~ N(0,1)), random signs, global scale sigma."""
+    g = torch.Generator().manual_seed(seed)
+    n_words = packed_words(N, K, kb)
+    if str(device).startswith("cuda"):
+        gg = torch.Generator(device=device).manual_seed(seed)
+        words = torch.randint(-2**31, 2**31 - 1, (n_words,), dtype=torch.int32, device=device, generator=gg)
+    else:
+        words = torch.empty(n_words, dtype=torch.int32)
+        native.host().r4dxb_trellis_random_fill(_ptr(words), n_words, seed)
+    suh = (torch.randint(0, 2, (K,), generator=g) * 2 - 1).to(torch.float16)
+    svh = ((torch.randint(0, 2, (N,), generator=g) * 2 - 1).float() * sigma).to(torch.float16)
+    return TrellisWeight(words.to(device), suh.to(device), svh.to(device), N, K, kb)
+
+
+def decode_codes(tw: TrellisWeight) -> torch.Tensor:
+    """Q [N, K] fp16: the raw code values before the Hadamard sandwich."""
+    L = native.host()
+    words = tw.words.cpu().contiguous()
+    q = torch.empty(tw.N, tw.K, dtype=torch.float16)
+    L.r4dxb_trellis_decode(_ptr(words), tw.N, tw.K, tw.kb, _ptr(q))
+    return q
+
+
+def reconstruct(tw: TrellisWeight, threads: int | None = None) -> torch.Tensor:
+    """Effective dense weight [N, K] fp32 = diag(svh) H_N Q H_K diag(suh)."""
+    L = native.host()
+    words, suh, svh = tw.words.cpu().contiguous(), tw.suh.cpu().contiguous(), tw.svh.cpu().contiguous()
+    W = torch.empty(tw.N, tw.K, dtype=torch.float32)
+    threads = threads or min(32, os.cpu_count() or 1)
+    L.r4dxb_trellis_reconstruct(_ptr(words), _ptr(suh), _ptr(svh), tw.N, tw.K, tw.kb, threads, _ptr(W))
+    return W
+
+
+def linear_reference(tw: TrellisWeight, x: torch.Tensor) -> torch.Tensor:
+    """y = svh * H_N(Q . H_K(suh * x)) in fp32 on the CPU (x: [T, K])."""
+    from ..ops.reference import fwht
+    q = decode_codes(tw).float()
+    xt = fwht(x.float().cpu() * tw.suh.float().cpu()[None, :])
+    y = xt @ q.T
+    return fwht(y) * tw.svh.float().cpu()[None, :]

