@@ -1,0 +1,228 @@
+#!/usr/bin/env python
+"""Headline benchmark: batch-1 greedy decode tok/s (and cold TTFT) of the Qwen-hybrid-27B geometry.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched by torch.distributed.run)
+    python bench.py --impl reference ...                     (the reference cannot be installed here)
+
+One step = one decoded token at batch 1 after an 8192-token prompt.  Weights are random-init in the
+container's quantized layouts (trellis ~4.5 bpw body, w4a16 head), KV cache fp8 e4m3 paged.
+Rank 0 prints one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+BASELINE_DECODE_TOK_S = 59.8     # reference README.md:69-70 (2x R9700, --tp 2)
+BASELINE_TTFT_S = {8192: 1.77, 32768: 7.78, 131072: 44.0}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prompt-len", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=64, help="debug only: fewer layers makes the result invalid")
+    ap.add_argument("--model", default="qwen-hybrid-27b", choices=["qwen-hybrid-27b", "small"])
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            f = [x.strip() for x in r.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        med = sm[len(sm) // 2] if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "reference is a HIP/RDNA4/Windows CMake project with no setup.py/pyproject.toml; "
+                          "pip install /root/reference fails: 'not installable'"}))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+    from r4dx_b200 import native
+    from r4dx_b200.config import qwen_hybrid_27b_config, small_hybrid_config
+    from r4dx_b200.models.hybrid import HybridModel
+    from r4dx_b200.ops import kernels as K
+    from r4dx_b200.quant.weights import synthetic_weight_set
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(f"--gpus {args.gpus} needs torch.distributed.run with {args.gpus} ranks", file=sys.stderr)
+            return 2
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    comm = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+        from r4dx_b200.parallel.tp_comm import make_comm
+        comm = make_comm(world, rank, dev)
+    native.cuda()
+
+    gcfg = qwen_hybrid_27b_config(args.layers) if args.model == "qwen-hybrid-27b" else small_hybrid_config(args.layers)
+    cfg = gcfg.shard(world, rank) if world > 1 else gcfg
+    total = args.prompt_len + args.warmup * 2 + args.steps * 2 + 64
+    w = synthetic_weight_set(cfg, device=dev, seed=0)
+    model = HybridModel(cfg, w, max_ctx=total, device=dev, comm=comm)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, gcfg.vocab_size, (args.prompt_len,), generator=g, dtype=torch.int32)
+
+    # ---- cold TTFT: prompt in, first token out ---------------------------------------------------
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    tok = model.prefill(prompt)
+    e1.record()
+    barrier()
+    ttft_ms = e0.elapsed_time(e1)
+
+    # ---- device-timed decode -----------------------------------------------------------------------
+    K.launch_count_reset()
+    model.enable_graphs((1,))
+    per_graph = K.launch_count() // 2          # warm-up pass + capture pass each went through the launchers
+    model.decode_begin(tok)
+    for _ in range(args.warmup):
+        model.decode_step_graph()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0.record()
+    for _ in range(args.steps):
+        model.decode_step_graph()
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else {}
+    t = torch.tensor([dev_ms, ttft_ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, ttft_ms = float(t[0]), float(t[1])
+
+    # ---- end to end through the public API: pinned H2D of the token, step, D2H of the result -----
+    e2e = None
+    if not args.no_e2e:
+        from r4dx_b200.runtime.engine import GreedySession
+        sess = GreedySession(model)
+        nxt = int(model.buf.next_ids[0].item())
+        for _ in range(args.warmup):
+            nxt = sess.step(nxt)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            nxt = sess.step(nxt)
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t[0])
+        e2e = {"value": args.steps / (e2e_ms / 1e3), "unit": "tok/s", "h2d_bytes_per_step": sess.h2d_bytes,
+               "d2h_bytes_per_step": sess.d2h_bytes, "ms_per_step": e2e_ms / args.steps}
+
+    if rank == 0:
+        value = args.steps / (dev_ms / 1e3)
+        stream_gb = model.streamed_bytes_per_token() / 1e9
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))
+        except Exception:
+            pass
+        hbm = peaks.get("hbm_gbs", 6650.0)
+        out = {
+            "metric": "batch-1 greedy decode tok/s, Qwen-hybrid-27B, 8192-token prompt",
+            "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": value / BASELINE_DECODE_TOK_S, "dtype": "bf16",
+            "data": "synthetic: random-init weights created in the quantized layouts (random trellis codes ~4.5 bpw, "
+                    "random w4a16 head), uniform random prompt ids",
+            "config": {"model": args.model if args.layers == 64 else f"{args.model}-{args.layers}layers(INVALID: debug)",
+                       "global_batch": 1, "seq_len": args.prompt_len, "parallelism": f"tp{world}",
+                       "kv_cache": "fp8 e4m3 paged, 16-token blocks", "weights": "trellis mixed 4/5-bit + w4a16 g64 head",
+                       "l2_policy": "inputs larger than L2: every step streams %.2f GB of weights per rank" % stream_gb},
+            "ttft_s": {str(args.prompt_len): ttft_ms / 1e3},
+            "ttft_vs_baseline": (BASELINE_TTFT_S[args.prompt_len] / (ttft_ms / 1e3)) if args.prompt_len in BASELINE_TTFT_S else None,
+            "weight_stream_gbs": stream_gb / (dev_ms / args.steps / 1e3),
+            "weight_stream_frac_of_measured_hbm": stream_gb / (dev_ms / args.steps / 1e3) / hbm,
+            "clocks": clocks, "gpu_launches": per_graph * args.steps, "kernels_per_step": per_graph,
+            "impl": "ours",
+        }
+        if e2e:
+            out["e2e"] = e2e
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,363 @@
+"""GPU model graph of the Qwen-style hybrid decoder (dense), single rank or one TP rank.
+
+PyTorch is the framework layer here: module wiring, state allocation (paged fp8 KV, GDN state,
+conv ring), workspaces and CUDA-graph capture.  Every op on the token path is a kernel of
+``libr4dxb_cuda.so``.  The forward follows the reference's chunk pipeline -- prologue (ids ->
+embedding), layer range, epilogue (final norm, LM head, argmax)
+(reference: src/model/model.cpp:1228-1935) -- but state handling is designed for replayable
+graphs: positions, the committed-row count and the token feedback all live in device memory.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import kernels as K
+from ..quant.trellis import TrellisWeight
+from ..quant.w4a16 import W4Weight
+
+BF = torch.bfloat16
+MAX_ROWS = 8          # rows per small-batch call (decode = 1, verify window <= 8)
+KV_BLOCK = 16
+CONV_RING = 16
+
+
+class Linear:
+    """One weight in whatever layout the container gave it; y = x W^T for T <= MAX_ROWS rows."""
+
+    def __init__(self, w, name: str = ""):
+        self.w = w
+        self.name = name
+        if isinstance(w, TrellisWeight):
+            self.N, self.K = w.N, w.K
+            self.ksplit = K.pick_ksplit(w.N, w.K)
+        elif isinstance(w, W4Weight):
+            self.N, self.K = w.N, w.K
+        else:
+            self.N, self.K = w.shape
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        w = self.w
+        if isinstance(w, TrellisWeight):
+            return K.trellis_gemv(w, x, residual=residual, out=out, ksplit=self.ksplit)
+        if isinstance(w, W4Weight):
+            if residual is not None:
+                raise NotImplementedError("w4a16 with a residual epilogue")
+            return K.w4a16_gemv(w, x, out_f32=(out.dtype == torch.float32), out=out)
+        raise NotImplementedError(f"layout of {self.name}")
+
+    @property
+    def nbytes(self) -> int:
+        w = self.w
+        return w.nbytes if hasattr(w, "nbytes") and not isinstance(w, torch.Tensor) else w.numel() * w.element_size()
+
+
+@dataclass
+class StepBuffers:
+    """Workspaces for one call of up to MAX_ROWS rows (allocated once; graph-safe)."""
+    ids: torch.Tensor
+    positions: torch.Tensor
+    n_replay: torch.Tensor
+    next_ids: torch.Tensor
+    next_vals: torch.Tensor
+    x: torch.Tensor
+    h: torch.Tensor
+    mixed: torch.Tensor
+    z: torch.Tensor
+    ab: torch.Tensor
+    core: torch.Tensor
+    qg: torch.Tensor
+    k: torch.Tensor
+    v: torch.Tensor
+    q: torch.Tensor
+    gate_up: torch.Tensor
+    act: torch.Tensor
+    logits: torch.Tensor
+    argmax_scratch: torch.Tensor
+    part_acc: torch.Tensor
+    part_ml: torch.Tensor
+
+
+class HybridModel:
+    def __init__(self, cfg: ModelConfig, weights: Dict[str, object], max_ctx: int = 8192 + 1024,
+                 device: str = "cuda", attn_splits: Optional[int] = None, comm=None):
+        cfg.validate() if cfg.tp_world == 1 else None
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.comm = comm                       # tensor-parallel communicator (None = single rank)
+        self.max_ctx = ((max_ctx + KV_BLOCK - 1) // KV_BLOCK) * KV_BLOCK
+        self.w = weights
+        self.lin: Dict[str, Linear] = {}
+        for name, t in weights.items():
+            if isinstance(t, (TrellisWeight, W4Weight)):
+                self.lin[name] = Linear(t, name)
+        # fused [a; b] gate projection per GDN layer
+        self.ab_w: Dict[int, torch.Tensor] = {}
+        for i in range(cfg.num_hidden_layers):
+            if not cfg.is_attention_layer(i):
+                p = f"text.layers.{i}.gdn."
+                self.ab_w[i] = torch.cat([weights[p + "in_proj_a"], weights[p + "in_proj_b"]], 0).contiguous()
+        self._alloc_state(attn_splits)
+        self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.pos = 0                           # host mirror of the next position
+        self.pending_rows = 0                  # rows of the last call not yet committed to the GDN base state
+
+    # ------------------------------------------------------------------------------------------
+    def _alloc_state(self, attn_splits: Optional[int]) -> None:
+        cfg, dev = self.cfg, self.device
+        H = cfg.hidden_size
+        Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
+        nblk = self.max_ctx // KV_BLOCK + 1       # one spare block: scratch positions for graph warm-up
+        self.block_table = torch.arange(nblk, dtype=torch.int32, device=dev)
+        self.kv: Dict[int, torch.Tensor] = {}
+        self.gdn_state: Dict[int, torch.Tensor] = {}
+        self.ring: Dict[int, torch.Tensor] = {}
+        self.log_u: Dict[int, torch.Tensor] = {}
+        self.log_k: Dict[int, torch.Tensor] = {}
+        self.log_eg: Dict[int, torch.Tensor] = {}
+        for i in range(cfg.num_hidden_layers):
+            if cfg.is_attention_layer(i):
+                self.kv[i] = torch.zeros(nblk, Hkv, 2, KV_BLOCK, D, dtype=torch.uint8, device=dev)
+            else:
+                self.gdn_state[i] = torch.zeros(Hv, Dg, Dg, dtype=torch.float32, device=dev)
+                self.ring[i] = torch.zeros(CONV_RING, cfg.conv_dim, dtype=BF, device=dev)
+                self.log_u[i] = torch.zeros(MAX_ROWS, Hv, Dg, dtype=torch.float32, device=dev)
+                self.log_k[i] = torch.zeros(MAX_ROWS, Hv, Dg, dtype=torch.float32, device=dev)
+                self.log_eg[i] = torch.zeros(MAX_ROWS, Hv, dtype=torch.float32, device=dev)
+        if attn_splits is None:
+            attn_splits = max(1, min(64, (148 + Hkv - 1) // max(1, Hkv)))
+        self.attn_splits = attn_splits
+        G = (Hq // max(1, Hkv)) * MAX_ROWS
+        R = MAX_ROWS
+        V = cfg.vocab_shard_size
+        e = lambda *s, dtype=BF: torch.zeros(*s, dtype=dtype, device=dev)
+        self.buf = StepBuffers(
+            ids=e(R, dtype=torch.int32), positions=e(R, dtype=torch.int32), n_replay=e(1, dtype=torch.int32),
+            next_ids=e(R, dtype=torch.int32), next_vals=e(R, dtype=torch.float32),
+            x=e(R, H), h=e(R, H), mixed=e(R, cfg.conv_dim), z=e(R, cfg.value_dim),
+            ab=e(R, 2 * Hv, dtype=torch.float32), core=e(R, max(cfg.value_dim, cfg.q_dim)),
+            qg=e(R, 2 * cfg.q_dim), k=e(R, cfg.kv_dim), v=e(R, cfg.kv_dim), q=e(R, cfg.q_dim),
+            gate_up=e(R, 2 * cfg.intermediate_size), act=e(R, cfg.intermediate_size),
+            logits=e(R, V, dtype=torch.float32), argmax_scratch=e(2 * R * 256, dtype=torch.float32),
+            part_acc=e(attn_splits * Hkv * G * D, dtype=torch.float32),
+            part_ml=e(attn_splits * Hkv * G * 2, dtype=torch.float32))
+
+    def state_bytes(self) -> int:
+        n = 0
+        for d in (self.kv, self.gdn_state, self.ring):
+            n += sum(t.numel() * t.element_size() for t in d.values())
+        return n
+
+    def weight_bytes(self) -> int:
+        n = 0
+        for t in self.w.values():
+            n += t.nbytes if not isinstance(t, torch.Tensor) else t.numel() * t.element_size()
+        return n
+
+    def streamed_bytes_per_token(self) -> int:
+        """Bytes every decoded token must read: all quantized linears + the LM head shard."""
+        return sum(l.nbytes for l in self.lin.values())
+
+    # ------------------------------------------------------------------------------------------
+    def reset(self) -> None:
+        for d in (self.kv, self.gdn_state, self.ring):
+            for t in d.values():
+                t.zero_()
+        self.buf.n_replay.zero_()
+        self.pos = 0
+        self.pending_rows = 0
+
+    # ---- layers ---------------------------------------------------------------------------------
+    def _gdn_layer(self, i: int, T: int) -> None:
+        cfg, b, w = self.cfg, self.buf, self.w
+        p = f"text.layers.{i}.gdn."
+        Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
+        h = b.h[:T]
+        self.lin[p + "in_proj_qkv"](h, out=b.mixed[:T])
+        self.lin[p + "in_proj_z"](h, out=b.z[:T])
+        K.bf16_gemv(self.ab_w[i], h, out=b.ab[:T])
+        K.gdn_decode(b.mixed, b.z, b.ab, w[p + "conv1d_weight"], w[p + "A_log"], w[p + "dt_bias"], w[p + "norm_weight"],
+                     self.ring[i], self.gdn_state[i], self.log_u[i], self.log_k[i], self.log_eg[i], b.positions,
+                     b.n_replay, b.core, T, Hv, Hk, Dg, cfg.rms_norm_eps)
+        core = b.core.view(-1)[:T * cfg.value_dim].view(T, cfg.value_dim)
+        self._row_parallel(self.lin[p + "out_proj"], core, T)
+
+    def _attn_layer(self, i: int, T: int) -> None:
+        cfg, b, w = self.cfg, self.buf, self.w
+        p = f"text.layers.{i}.attn."
+        Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        h = b.h[:T]
+        self.lin[p + "qg"](h, out=b.qg[:T])
+        self.lin[p + "k"](h, out=b.k[:T])
+        self.lin[p + "v"](h, out=b.v[:T])
+        K.attn_precore(b.qg, b.k, b.v, w[p + "q_norm"], w[p + "k_norm"], w[p + "k_descale"], w[p + "v_descale"],
+                       b.positions, self.block_table, b.q, self.kv[i], T, Hq, Hkv, D, cfg.rotary_dim,
+                       cfg.rope_theta, cfg.rms_norm_eps)
+        core = b.core.view(-1)[:T * cfg.q_dim].view(T, cfg.q_dim)
+        K.attn_decode(b.q, b.qg, self.kv[i], self.block_table, b.positions, w[p + "k_descale"], w[p + "v_descale"],
+                      b.part_acc, b.part_ml, core, T, Hq, Hkv, D, self.attn_splits, cfg.attn_output_gate)
+        self._row_parallel(self.lin[p + "o"], core, T)
+
+    def _mlp(self, i: int, T: int) -> None:
+        cfg, b = self.cfg, self.buf
+        p = f"text.layers.{i}.mlp."
+        self.lin[p + "gate_up"](b.h[:T], out=b.gate_up[:T])
+        K.silu_mul(b.gate_up[:T], out=b.act[:T])
+        self._row_parallel(self.lin[p + "down"], b.act[:T], T)
+
+    def _row_parallel(self, lin: Linear, x: torch.Tensor, T: int) -> None:
+        """Row-parallel linear whose result is added to the residual stream ``buf.x``."""
+        b = self.buf
+        if self.comm is None or self.comm.world == 1:
+            lin(x, out=b.x[:T], residual=b.x[:T])
+        else:
+            self.comm.row_parallel_linear(lin, x, b.x[:T])
+
+    # ---- forward --------------------------------------------------------------------------------
+    def forward_rows(self, T: int, want_logits: bool = True) -> None:
+        """Runs the T rows staged in ``buf.ids`` / ``buf.positions``; results in ``buf.logits`` / ``buf.next_ids``."""
+        cfg, b, w = self.cfg, self.buf, self.w
+        K.embed_gather(b.ids[:T], w["text.embed_tokens"], out=b.x[:T])
+        for i in range(cfg.num_hidden_layers):
+            p = f"text.layers.{i}."
+            K.rmsnorm(b.x[:T], w[p + "input_layernorm"], cfg.rms_norm_eps, out=b.h[:T])
+            if cfg.is_attention_layer(i):
+                self._attn_layer(i, T)
+            else:
+                self._gdn_layer(i, T)
+            K.rmsnorm(b.x[:T], w[p + "post_attention_layernorm"], cfg.rms_norm_eps, out=b.h[:T])
+            self._mlp(i, T)
+        if want_logits:
+            K.rmsnorm(b.x[:T], w["text.final_norm"], cfg.rms_norm_eps, out=b.h[:T])
+            self.lin["lm_head"](b.h[:T], out=b.logits[:T])
+            K.argmax_rows(b.logits[:T], cfg.vocab_shard_begin, b.next_ids[:T], b.next_vals[:T], b.argmax_scratch)
+            if self.comm is not None and self.comm.world > 1:
+                self.comm.merge_argmax(b.next_ids[:T], b.next_vals[:T])
+
+    def _stage(self, ids: torch.Tensor, pos0: int) -> int:
+        T = ids.numel()
+        b = self.buf
+        b.ids[:T].copy_(ids.to(device=self.device, dtype=torch.int32), non_blocking=True)
+        b.positions[:T].copy_(torch.arange(pos0, pos0 + T, dtype=torch.int32, device=self.device))
+        return T
+
+    def feed(self, ids: torch.Tensor, want_logits: bool = True, accepted: Optional[int] = None) -> None:
+        """Feeds up to MAX_ROWS rows at the current position and commits all of them (or ``accepted``)."""
+        T = self._stage(ids, self.pos)
+        if self.pos + T > self.max_ctx:
+            raise ValueError("context overflow")
+        self.buf.n_replay.fill_(self.pending_rows)
+        self.forward_rows(T, want_logits)
+        n = T if accepted is None else accepted
+        self.pending_rows = n
+        self.pos += n
+
+    def prefill(self, ids: torch.Tensor) -> int:
+        """Feeds a prompt through the small-batch path (MAX_ROWS rows per call); returns the greedy next token."""
+        ids = ids.to(torch.int32)
+        n = ids.numel()
+        s = 0
+        while s < n:
+            e = min(n, s + MAX_ROWS)
+            self.feed(ids[s:e], want_logits=(e == n))
+            s = e
+        last = (n - 1) % MAX_ROWS
+        return int(self.buf.next_ids[last].item())
+
+    def logits_rows(self, T: int) -> torch.Tensor:
+        return self.buf.logits[:T]
+
+    # ---- graph decode ---------------------------------------------------------------------------
+    def _capture(self, T: int) -> torch.cuda.CUDAGraph:
+        b = self.buf
+        # warm-up on a side stream (sets kernel attributes, loads modules) without touching live state
+        snap = self._snapshot()
+        # warm-up rows live in the spare KV block past max_ctx, so no real cache row is touched
+        b.positions.copy_(torch.arange(self.max_ctx, self.max_ctx + MAX_ROWS, dtype=torch.int32, device=self.device))
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._graph_body(T)
+        torch.cuda.current_stream().wait_stream(s)
+        self._restore(snap)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._graph_body(T)
+        self._restore(snap)
+        return g
+
+    def _graph_body(self, T: int) -> None:
+        b = self.buf
+        self.forward_rows(T, True)
+        # device-side bookkeeping so the graph can be replayed back to back
+        b.ids[:1].copy_(b.next_ids[T - 1:T])
+        b.positions.add_(T)
+        b.n_replay.fill_(T)
+
+    def _snapshot(self):
+        b = self.buf
+        snap = {"ids": b.ids.clone(), "pos": b.positions.clone(), "nr": b.n_replay.clone(), "x": b.x.clone()}
+        snap["kvrow"] = {}
+        snap["gdn"] = {i: t.clone() for i, t in self.gdn_state.items()}
+        snap["ring"] = {i: t.clone() for i, t in self.ring.items()}
+        snap["log"] = {i: (self.log_u[i].clone(), self.log_k[i].clone(), self.log_eg[i].clone()) for i in self.log_u}
+        return snap
+
+    def _restore(self, snap) -> None:
+        b = self.buf
+        b.ids.copy_(snap["ids"]); b.positions.copy_(snap["pos"]); b.n_replay.copy_(snap["nr"]); b.x.copy_(snap["x"])
+        for i, t in snap["gdn"].items():
+            self.gdn_state[i].copy_(t)
+        for i, t in snap["ring"].items():
+            self.ring[i].copy_(t)
+        for i, (u, k, eg) in snap["log"].items():
+            self.log_u[i].copy_(u); self.log_k[i].copy_(k); self.log_eg[i].copy_(eg)
+
+    def enable_graphs(self, rows=(1,)) -> None:
+        for T in rows:
+            if T not in self._graphs:
+                self._graphs[T] = self._capture(T)
+
+    def decode_begin(self, first_token: int) -> None:
+        """Stages the token / position / commit count for graph replays starting at the current position."""
+        b = self.buf
+        b.ids[:1].fill_(first_token)
+        b.positions.copy_(torch.arange(self.pos, self.pos + MAX_ROWS, dtype=torch.int32, device=self.device))
+        b.n_replay.fill_(self.pending_rows)
+
+    def decode_step_graph(self) -> None:
+        """One greedy step: consumes ``buf.ids[0]``, leaves the next token in ``buf.ids[0]`` / ``buf.next_ids[0]``."""
+        if self.pos + 1 > self.max_ctx:
+            raise ValueError("context overflow")
+        self._graphs[1].replay()
+        self.pos += 1
+        self.pending_rows = 1
+
+    def decode_step_greedy(self, token: int) -> int:
+        """Eager single step (no graph): feed one token, return the greedy next token."""
+        self.feed(torch.tensor([token], dtype=torch.int32))
+        return int(self.buf.next_ids[0].item())
+
+    def generate_greedy(self, prompt: torch.Tensor, n: int, use_graph: bool = True) -> List[int]:
+        tok = self.prefill(prompt)
+        out = [tok]
+        if n <= 1:
+            return out
+        if use_graph:
+            self.enable_graphs((1,))
+            self.decode_begin(tok)
+            toks = torch.empty(n - 1, dtype=torch.int32, device=self.device)
+            for j in range(n - 1):
+                self.decode_step_graph()
+                toks[j:j + 1].copy_(self.buf.next_ids[:1])
+            out += toks.tolist()
+        else:
+            for _ in range(n - 1):
+                tok = self.decode_step_greedy(tok)
+                out.append(tok)
+        return out

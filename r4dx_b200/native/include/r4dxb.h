@@ -1,0 +1,73 @@
+/* C ABI of libr4dxb_cuda.so: every entry point takes raw device pointers and a CUDA stream
+ * handle, launches on that stream and returns 0 or an error code (a cudaError_t value, or one
+ * of the R4DXB_* codes below).  Nothing on a launch path allocates or synchronises unless its
+ * comment says so, so the decode step can be captured in a CUDA graph. */
+#ifndef R4DXB_H_
+#define R4DXB_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define R4DXB_BAD_ARG 10001
+#define R4DXB_UNSUPPORTED 10002
+#define R4DXB_TOO_LARGE 10003
+
+unsigned long long r4dxb_launch_count(void);
+void r4dxb_launch_count_reset(void);
+
+/* ---- elementwise / norms ------------------------------------------------------------------ */
+int r4dxb_embed_gather_bf16(const int* ids, const void* table, void* out, int T, int H, int V, void* stream);
+/* mode bit0: weight is zero-centred (1 + w); bit1: no weight */
+int r4dxb_rmsnorm_bf16(const void* x, const void* w, void* out, int T, int H, float eps, int mode, void* stream);
+/* res += delta (rounded to bf16 in place), out = rmsnorm(res) */
+int r4dxb_add_rmsnorm_bf16(void* res, const void* delta, const void* w, void* out, int T, int H, float eps, int mode,
+                           void* stream);
+int r4dxb_layernorm_bf16(const void* x, const void* w, const void* b, void* out, int T, int H, float eps, void* stream);
+int r4dxb_silu_mul_bf16(const void* gate_up, void* out, int T, int I, void* stream);
+int r4dxb_residual_add_bf16(void* res, const void* delta, long long n, void* stream);
+int r4dxb_bias_act_bf16(void* x, const void* bias, int T, int H, int act, void* stream);
+
+/* ---- weight-streaming GEMMs for T <= 8 rows ------------------------------------------------- */
+/* y[T,N] (bf16) = svh * H(Q . H(suh * x)) (+ residual), trellis-coded Q, kb in {3,4,5}.
+ * ksplit in {1,2,4,8} CTAs share one 128-row block through a thread-block cluster. */
+int r4dxb_trellis_gemv(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                       const void* residual, int T, int N, int K, int kb, int ksplit, void* stream);
+/* logits[T,N] = x . dequant(wq)^T, asymmetric 4-bit groups of 32/64/128 along K; out_f32 selects
+ * fp32 or bf16 output */
+int r4dxb_w4a16_gemv(const void* wq, const void* wsz, const void* x, void* y, int T, int N, int K, int group,
+                     int out_f32, void* stream);
+/* y[T,N] (fp32) = x[T,K] (bf16) . W[N,K]^T (bf16): small dense projections (gates, router) */
+int r4dxb_bf16_gemv(const void* W, const void* x, float* y, int T, int N, int K, void* stream);
+
+/* ---- sampling ------------------------------------------------------------------------------- */
+/* row-wise argmax with ties to the lowest index; writes id + id_offset (int32) and the max (f32).
+ * scratch: 2 * T * 256 * 4 bytes */
+int r4dxb_argmax_rows(const void* logits, int is_f32, int T, int V, int id_offset, int* out_ids, float* out_vals,
+                      void* scratch, void* stream);
+
+/* ---- Gated DeltaNet ------------------------------------------------------------------------- */
+/* Fused decode / verify step (T <= 8 rows): conv1d ring + SiLU, L2 norm, gates, delta rule, gated
+ * RMSNorm.  The base state is only written when *n_replay > 0 (commit of the previous call's
+ * accepted rows); this call's rows go to the log.  D (= key = value head dim) in {64, 128}. */
+int r4dxb_gdn_decode(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
+                     const float* dt_bias, const void* norm_w, void* ring, float* state, float* log_u, float* log_k,
+                     float* log_eg, const int* positions, const int* n_replay, void* out, int T, int H, int Hk, int D,
+                     float eps, void* stream);
+
+/* ---- attention (fp8 e4m3 paged KV, 16-token blocks) ------------------------------------------ */
+int r4dxb_attn_precore(const void* qg, const void* k, const void* v, const void* q_norm, const void* k_norm,
+                       const float* k_descale, const float* v_descale, const int* positions, const int* block_table,
+                       void* q_out, void* cache, int T, int Hq, int Hkv, int D, int rotary_dim, float theta, float eps,
+                       void* stream);
+/* scratch: part_acc = splits*Hkv*G*D floats, part_ml = splits*Hkv*G*2 floats, G = Hq/Hkv*T */
+int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const int* block_table, const int* positions,
+                      const float* k_descale, const float* v_descale, float* part_acc, float* part_ml, void* out,
+                      int T, int Hq, int Hkv, int D, int splits, int gated, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* R4DXB_H_ */

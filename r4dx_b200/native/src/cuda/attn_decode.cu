@@ -1,0 +1,326 @@
+// Gated full attention for T <= 8 query rows (decode / speculative verify) over an fp8 e4m3
+// paged KV cache with 16-token blocks.
+//
+//   precore : per-head q|gate split, zero-centred RMSNorm on q and k, partial NeoX rope, fp8
+//             quantisation of k and v with a static per-head descale, paged cache write
+//             (reference fuses the same steps: src/kernels/src/r4dx_kernels.hip:647).
+//   decode  : split-KV flash decoding; one CTA per (split, kv head) walks its share of the
+//             sequence's blocks, all gqa*T query rows of the kv head at once, and writes an
+//             (m, l, acc) partial (reference: third_party/libr4d/r4d_attn_decode_h256_gqa6.hip:1-16).
+//   combine : merges the partials, applies o * sigmoid(gate), one bf16 rounding.
+//
+// Cache layout: [block][kv_head][2 (K, V)][16 tokens][D] fp8 -- a K tile and a V tile of one
+// block are each one contiguous 16*D byte run.  The sequence length is read from device memory
+// (positions[T-1] + 1) so that a captured CUDA graph can be replayed as the context grows.
+#include "common.cuh"
+
+namespace r4dxb {
+namespace {
+
+constexpr int kBlockTokens = 16;
+
+__device__ __forceinline__ uint8_t ToFp8(float v) {
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ __half2 Fp8x2ToHalf2(uint16_t v) {
+  __half2_raw r = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v), __NV_E4M3);
+  return *reinterpret_cast<__half2*>(&r);
+}
+
+struct PrecoreArgs {
+  const __nv_bfloat16* qg;     // [T, Hq, 2D]
+  const __nv_bfloat16* k;      // [T, Hkv, D]
+  const __nv_bfloat16* v;      // [T, Hkv, D]
+  const __nv_bfloat16* q_norm; // [D]
+  const __nv_bfloat16* k_norm; // [D]
+  const float* k_descale;      // [Hkv]
+  const float* v_descale;      // [Hkv]
+  const int* positions;        // [T]
+  const int* block_table;      // [max_blocks]
+  __nv_bfloat16* q_out;        // [T, Hq, D]
+  uint8_t* cache;
+  int T, Hq, Hkv, D, rotary_dim;
+  float theta, eps;
+};
+
+// grid (Hq + 2 Hkv, T), block D threads (one element each)
+__global__ void PrecoreKernel(PrecoreArgs a) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int t = blockIdx.y, hh = blockIdx.x, d = threadIdx.x, D = a.D;
+  const int pos = a.positions[t];
+  int kind, head;   // 0 = q, 1 = k, 2 = v
+  if (hh < a.Hq) { kind = 0; head = hh; }
+  else if (hh < a.Hq + a.Hkv) { kind = 1; head = hh - a.Hq; }
+  else { kind = 2; head = hh - a.Hq - a.Hkv; }
+  float x;
+  if (kind == 0) x = __bfloat162float(a.qg[(static_cast<size_t>(t) * a.Hq + head) * 2 * D + d]);
+  else if (kind == 1) x = __bfloat162float(a.k[(static_cast<size_t>(t) * a.Hkv + head) * D + d]);
+  else x = __bfloat162float(a.v[(static_cast<size_t>(t) * a.Hkv + head) * D + d]);
+  if (kind != 2) {
+    const float ss = BlockSum(x * x, red);
+    const float w = 1.0f + __bfloat162float((kind == 0 ? a.q_norm : a.k_norm)[d]);
+    x = x * rsqrtf(ss / D + a.eps) * w;
+    row[d] = x;
+    __syncthreads();
+    const int half = a.rotary_dim / 2;
+    if (d < a.rotary_dim) {
+      const int i = d < half ? d : d - half;
+      const double inv = exp2(-log2(static_cast<double>(a.theta)) * (2.0 * i / a.rotary_dim));
+      double s, c;
+      sincos(static_cast<double>(pos) * inv, &s, &c);
+      const float fs = static_cast<float>(s), fc = static_cast<float>(c);
+      x = d < half ? row[d] * fc - row[d + half] * fs : row[d] * fc + row[d - half] * fs;
+    }
+  }
+  if (kind == 0) {
+    a.q_out[(static_cast<size_t>(t) * a.Hq + head) * D + d] = __float2bfloat16(x);
+  } else {
+    const int blk = a.block_table[pos / kBlockTokens], tok = pos % kBlockTokens;
+    const float ds = (kind == 1 ? a.k_descale : a.v_descale)[head];
+    uint8_t* dst = a.cache + ((static_cast<size_t>(blk) * a.Hkv + head) * 2 + (kind - 1)) * kBlockTokens * D;
+    dst[tok * D + d] = ToFp8(x / ds);
+  }
+}
+
+struct DecodeArgs {
+  const __nv_bfloat16* q;      // [T, Hq, D] (normed + roped)
+  const uint8_t* cache;
+  const int* block_table;
+  const int* positions;        // [T]
+  const float* k_descale;
+  const float* v_descale;
+  float* part_acc;             // [splits, Hkv, G, D]
+  float* part_ml;              // [splits, Hkv, G, 2]
+  int T, Hq, Hkv, D, splits;
+};
+
+// grid (splits, Hkv), 256 threads.  G = gqa * T query rows, row g = t * gqa + j.
+template <int GMAX>
+__global__ void __launch_bounds__(256) DecodeKernel(DecodeArgs a) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  const int D = a.D, gqa = a.Hq / a.Hkv, G = gqa * a.T;
+  const int split = blockIdx.x, hkv = blockIdx.y, tid = threadIdx.x;
+  const int KS = D + 16;                          // padded K row stride (bytes) against bank conflicts
+  uint8_t* Kt = smem;                              // [16][KS]
+  uint8_t* Vt = Kt + kBlockTokens * KS;            // [16][D]
+  __half* qs = reinterpret_cast<__half*>(Vt + kBlockTokens * D);   // [GMAX][D]
+  float* P = reinterpret_cast<float*>(qs + GMAX * D);              // [GMAX][16]
+  float* mrow = P + GMAX * kBlockTokens;           // [GMAX]
+  float* lrow = mrow + GMAX;
+  float* arow = lrow + GMAX;                       // per-block rescale factor
+  int* qpos = reinterpret_cast<int*>(arow + GMAX); // [GMAX] position of each query row
+
+  const int seqlen = a.positions[a.T - 1] + 1;
+  const int nblocks = (seqlen + kBlockTokens - 1) / kBlockTokens;
+  const int per = (nblocks + a.splits - 1) / a.splits;
+  const int b0 = split * per, b1 = min(nblocks, b0 + per);
+
+  const float sm_scale = rsqrtf(static_cast<float>(D)) * a.k_descale[hkv] * 1.4426950408889634f;  // into log2 domain
+  for (int i = tid; i < GMAX * D; i += 256) {
+    const int g = i / D, d = i % D;
+    float v = 0.f;
+    if (g < G) {
+      const int t = g / gqa, j = g % gqa;
+      v = __bfloat162float(a.q[(static_cast<size_t>(t) * a.Hq + hkv * gqa + j) * D + d]) * sm_scale;
+    }
+    qs[i] = __float2half(v);
+  }
+  if (tid < GMAX) {
+    mrow[tid] = -INFINITY;
+    lrow[tid] = 0.f;
+    qpos[tid] = tid < G ? a.positions[tid / gqa] : -1;
+  }
+  float acc[GMAX];
+#pragma unroll
+  for (int g = 0; g < GMAX; ++g) acc[g] = 0.f;
+  __syncthreads();
+
+  for (int b = b0; b < b1; ++b) {
+    const int blk = a.block_table[b];
+    const uint8_t* src = a.cache + (static_cast<size_t>(blk) * a.Hkv + hkv) * 2 * kBlockTokens * D;
+    const int vec_per_tile = kBlockTokens * D / 16;
+    for (int i = tid; i < 2 * vec_per_tile; i += 256) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + i);
+      if (i < vec_per_tile) {
+        const int tok = (i * 16) / D, off = (i * 16) % D;
+        *reinterpret_cast<uint4*>(Kt + tok * KS + off) = v;
+      } else {
+        *reinterpret_cast<uint4*>(Vt + (i - vec_per_tile) * 16) = v;
+      }
+    }
+    __syncthreads();
+    // scores: one thread per (g, tok)
+    for (int i = tid; i < G * kBlockTokens; i += 256) {
+      const int g = i / kBlockTokens, tok = i % kBlockTokens;
+      const int kp = b * kBlockTokens + tok;
+      float s = -INFINITY;
+      if (kp <= qpos[g]) {
+        const uint2* kr = reinterpret_cast<const uint2*>(Kt + tok * KS);
+        const uint4* qr = reinterpret_cast<const uint4*>(qs + g * D);
+        float sum = 0.f;
+        for (int c = 0; c < D / 8; ++c) {
+          const uint2 kv = kr[c];
+          const uint4 qv = qr[c];
+          __half2 p = __hmul2(Fp8x2ToHalf2(kv.x & 0xFFFF), *reinterpret_cast<const __half2*>(&qv.x));
+          p = __hfma2(Fp8x2ToHalf2(kv.x >> 16), *reinterpret_cast<const __half2*>(&qv.y), p);
+          p = __hfma2(Fp8x2ToHalf2(kv.y & 0xFFFF), *reinterpret_cast<const __half2*>(&qv.z), p);
+          p = __hfma2(Fp8x2ToHalf2(kv.y >> 16), *reinterpret_cast<const __half2*>(&qv.w), p);
+          sum += __low2float(p) + __high2float(p);
+        }
+        s = sum;
+      }
+      P[i] = s;
+    }
+    __syncthreads();
+    // online softmax per query row (log2 domain)
+    if (tid < G) {
+      const int g = tid;
+      float mx = mrow[g];
+      for (int tok = 0; tok < kBlockTokens; ++tok) mx = fmaxf(mx, P[g * kBlockTokens + tok]);
+      const float alpha = (mx == -INFINITY) ? 1.f : exp2f(mrow[g] - mx);
+      float l = lrow[g] * alpha;
+      for (int tok = 0; tok < kBlockTokens; ++tok) {
+        const float s = P[g * kBlockTokens + tok];
+        const float p = (s == -INFINITY) ? 0.f : exp2f(s - mx);
+        P[g * kBlockTokens + tok] = p;
+        l += p;
+      }
+      mrow[g] = mx;
+      lrow[g] = l;
+      arow[g] = alpha;
+    }
+    __syncthreads();
+    // PV: thread owns one output dim for every query row
+    if (tid < D) {
+      float vcol[kBlockTokens];
+#pragma unroll
+      for (int tok = 0; tok < kBlockTokens; ++tok) {
+        const __half_raw hr = __nv_cvt_fp8_to_halfraw(Vt[tok * D + tid], __NV_E4M3);
+        vcol[tok] = __half2float(*reinterpret_cast<const __half*>(&hr));
+      }
+#pragma unroll
+      for (int g = 0; g < GMAX; ++g) {
+        if (g < G) {
+          float s = acc[g] * arow[g];
+#pragma unroll
+          for (int tok = 0; tok < kBlockTokens; ++tok) s = fmaf(P[g * kBlockTokens + tok], vcol[tok], s);
+          acc[g] = s;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  const float vds = a.v_descale[hkv];
+  const size_t base = (static_cast<size_t>(split) * a.Hkv + hkv) * G;
+  if (tid < D) {
+#pragma unroll
+    for (int g = 0; g < GMAX; ++g)
+      if (g < G) a.part_acc[(base + g) * D + tid] = acc[g] * vds;
+  }
+  if (tid < G) {
+    a.part_ml[(base + tid) * 2] = mrow[tid];
+    a.part_ml[(base + tid) * 2 + 1] = lrow[tid];
+  }
+}
+
+// grid (G, Hkv), D threads
+__global__ void CombineKernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                              const __nv_bfloat16* __restrict__ qg, __nv_bfloat16* __restrict__ out, int T, int Hq,
+                              int Hkv, int D, int splits, int gated) {
+  const int g = blockIdx.x, hkv = blockIdx.y, d = threadIdx.x;
+  const int gqa = Hq / Hkv, G = gqa * T;
+  float M = -INFINITY;
+  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[((static_cast<size_t>(s) * Hkv + hkv) * G + g) * 2]);
+  float num = 0.f, den = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const size_t r = (static_cast<size_t>(s) * Hkv + hkv) * G + g;
+    const float m = part_ml[r * 2];
+    if (m == -INFINITY) continue;
+    const float w = exp2f(m - M);
+    num += w * part_acc[r * D + d];
+    den += w * part_ml[r * 2 + 1];
+  }
+  float o = den > 0.f ? num / den : 0.f;
+  const int t = g / gqa, hq = hkv * gqa + g % gqa;
+  if (gated) {
+    const float gate = __bfloat162float(qg[(static_cast<size_t>(t) * Hq + hq) * 2 * D + D + d]);
+    o *= Sigmoid(gate);
+  }
+  out[(static_cast<size_t>(t) * Hq + hq) * D + d] = __float2bfloat16(o);
+}
+
+template <int GMAX>
+int LaunchDecode(const DecodeArgs& a, cudaStream_t s) {
+  const int D = a.D;
+  const size_t smem = kBlockTokens * (D + 16) + kBlockTokens * D + static_cast<size_t>(GMAX) * D * 2 +
+                      static_cast<size_t>(GMAX) * kBlockTokens * 4 + GMAX * 4 * 4;
+  auto kern = DecodeKernel<GMAX>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  kern<<<dim3(a.splits, a.Hkv), 256, smem, s>>>(a);
+  return FinishLaunch();
+}
+
+}  // namespace
+}  // namespace r4dxb
+
+using namespace r4dxb;
+
+extern "C" {
+
+int r4dxb_attn_precore(const void* qg, const void* k, const void* v, const void* q_norm, const void* k_norm,
+                       const float* k_descale, const float* v_descale, const int* positions, const int* block_table,
+                       void* q_out, void* cache, int T, int Hq, int Hkv, int D, int rotary_dim, float theta, float eps,
+                       void* stream) {
+  if (T < 1 || D > 1024 || D % 32 || rotary_dim > D || rotary_dim % 2) return R4DXB_BAD_ARG;
+  PrecoreArgs a;
+  a.qg = static_cast<const __nv_bfloat16*>(qg);
+  a.k = static_cast<const __nv_bfloat16*>(k);
+  a.v = static_cast<const __nv_bfloat16*>(v);
+  a.q_norm = static_cast<const __nv_bfloat16*>(q_norm);
+  a.k_norm = static_cast<const __nv_bfloat16*>(k_norm);
+  a.k_descale = k_descale;
+  a.v_descale = v_descale;
+  a.positions = positions;
+  a.block_table = block_table;
+  a.q_out = static_cast<__nv_bfloat16*>(q_out);
+  a.cache = static_cast<uint8_t*>(cache);
+  a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.rotary_dim = rotary_dim; a.theta = theta; a.eps = eps;
+  PrecoreKernel<<<dim3(Hq + 2 * Hkv, T), D, D * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
+  return FinishLaunch();
+}
+
+/* scratch: part_acc = splits*Hkv*G*D floats, part_ml = splits*Hkv*G*2 floats (G = Hq/Hkv*T) */
+int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const int* block_table, const int* positions,
+                      const float* k_descale, const float* v_descale, float* part_acc, float* part_ml, void* out,
+                      int T, int Hq, int Hkv, int D, int splits, int gated, void* stream) {
+  if (T < 1 || T > 8 || Hq % Hkv || D % 16 || D > 256 || splits < 1) return R4DXB_BAD_ARG;
+  const int G = Hq / Hkv * T;
+  DecodeArgs a;
+  a.q = static_cast<const __nv_bfloat16*>(q);
+  a.cache = static_cast<const uint8_t*>(cache);
+  a.block_table = block_table;
+  a.positions = positions;
+  a.k_descale = k_descale;
+  a.v_descale = v_descale;
+  a.part_acc = part_acc;
+  a.part_ml = part_ml;
+  a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.splits = splits;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int e;
+  if (G <= 8) e = LaunchDecode<8>(a, s);
+  else if (G <= 16) e = LaunchDecode<16>(a, s);
+  else if (G <= 32) e = LaunchDecode<32>(a, s);
+  else if (G <= 64) e = LaunchDecode<64>(a, s);
+  else return R4DXB_UNSUPPORTED;
+  if (e) return e;
+  CombineKernel<<<dim3(G, Hkv), D, 0, s>>>(part_acc, part_ml, static_cast<const __nv_bfloat16*>(qg),
+                                           static_cast<__nv_bfloat16*>(out), T, Hq, Hkv, D, splits, gated);
+  return FinishLaunch();
+}
+
+}  // extern "C"

@@ -1,0 +1,74 @@
+// Shared device/host helpers for the sm_100a kernel library.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "r4dxb.h"
+
+namespace r4dxb {
+
+// Every launcher bumps this host counter (one per kernel launch), so a caller can report how many
+// kernels of this library ran in a region (reference keeps the same kind of counter:
+// src/kernels/include/r4dx/kernels/kernels.h:666-680).
+extern unsigned long long g_launch_count;
+
+inline int FinishLaunch() {
+  ++g_launch_count;
+  return static_cast<int>(cudaGetLastError());
+}
+
+__device__ __forceinline__ float WarpSum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float WarpMax(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum; `red` needs 32 floats of shared memory. All threads get the result.
+__device__ __forceinline__ float BlockSum(float v, float* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = WarpSum(v);
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = (lane < nw) ? red[lane] : 0.0f;
+  r = WarpSum(r);
+  return r;
+}
+
+__device__ __forceinline__ float Bf16Bits(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
+__device__ __forceinline__ float BfLo(uint32_t p) { return __uint_as_float(p << 16); }
+__device__ __forceinline__ float BfHi(uint32_t p) { return __uint_as_float(p & 0xFFFF0000u); }
+__device__ __forceinline__ uint32_t PackBf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float Sigmoid(float x) { return 1.0f / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float Silu(float x) { return x / (1.0f + __expf(-x)); }
+
+// 128-point Sylvester FWHT held by one warp: lane l owns elements 4l .. 4l+3 (unnormalised).
+__device__ __forceinline__ void WarpFwht128(float (&v)[4]) {
+  const int lane = threadIdx.x & 31;
+  {
+    const float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];
+    v[0] = a + c; v[1] = b + d; v[2] = a - c; v[3] = b - d;
+  }
+#pragma unroll
+  for (int m = 1; m < 32; m <<= 1) {
+    const bool upper = lane & m;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float o = __shfl_xor_sync(0xffffffffu, v[i], m);
+      v[i] = upper ? (o - v[i]) : (v[i] + o);
+    }
+  }
+}
+
+}  // namespace r4dxb

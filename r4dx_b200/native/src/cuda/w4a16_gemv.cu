@@ -1,0 +1,228 @@
+// Weight-streaming GEMMs for T <= 8 rows over 4-bit grouped weights (LM / MTP / drafter heads)
+// and over small dense bf16 matrices (gate projections, MoE router), plus the row argmax.
+//
+// w4a16: w = scale * (q - zero); a nibble n becomes fp16 (0x6400 | n) = 1024 + n, the stored
+// fp16 -(1024 + zero) makes n - zero exact, eight products are summed in fp16x2 and the group
+// sum is scaled in fp32 (the reference uses the same exact-nibble trick on its WMMA path:
+// reference third_party/libr4d/r4d_gemm_w4a16_nt_m64.hip:1-67).  One warp streams one weight
+// row with 16-byte loads (32 weights per lane per load); rows are independent, so there is no
+// cross-CTA reduction.
+#include "common.cuh"
+
+namespace r4dxb {
+namespace {
+
+constexpr int kThreads = 256;
+
+template <int TMAX>
+__global__ void __launch_bounds__(kThreads)
+W4Gemv(const uint4* __restrict__ wq, const uint32_t* __restrict__ wsz, const __nv_bfloat16* __restrict__ x,
+       void* __restrict__ y, int T, int N, int K, int group, int out_f32, int rows_per_cta) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __half* xs = reinterpret_cast<__half*>(smem_raw);   // [TMAX][K], every 8 values stored as 0,4,1,5,2,6,3,7
+  for (int i = threadIdx.x; i < TMAX * K; i += kThreads) {
+    const int t = i / K, k = i % K;
+    const int j = k & 7;
+    const int slot = (j < 4) ? 2 * j : 2 * (j - 4) + 1;
+    xs[t * K + (k & ~7) + slot] = (t < T) ? __float2half(__bfloat162float(x[static_cast<size_t>(t) * K + k])) : __half(0);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int vec_per_row = K / 32;            // uint4 per row
+  const int groups = K / group;
+  const int row0 = blockIdx.x * rows_per_cta;
+  for (int r = warp; r < rows_per_cta; r += kThreads / 32) {
+    const int n = row0 + r;
+    if (n >= N) break;
+    float acc[TMAX];
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t) acc[t] = 0.f;
+    const uint4* rowp = wq + static_cast<size_t>(n) * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) {
+      const uint4 q = __ldg(rowp + v);
+      const int k0 = v * 32;
+      const uint32_t sz = __ldg(wsz + static_cast<size_t>(n) * groups + k0 / group);
+      const float scale = __half2float(__ushort_as_half(static_cast<unsigned short>(sz & 0xFFFF)));
+      const uint32_t nzb = (sz >> 16) | (sz & 0xFFFF0000u);
+      const __half2 nz = *reinterpret_cast<const __half2*>(&nzb);
+      const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+      float gsum[TMAX];
+#pragma unroll
+      for (int t = 0; t < TMAX; ++t) gsum[t] = 0.f;
+#pragma unroll
+      for (int wi = 0; wi < 4; ++wi) {
+        __half2 wv[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint32_t bits = ((qw[wi] >> (4 * i)) & 0x000F000Fu) | 0x64006400u;
+          wv[i] = __hadd2(*reinterpret_cast<const __half2*>(&bits), nz);   // (n_i - zero, n_{i+4} - zero), exact
+        }
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xs + t * K + k0 + wi * 8);
+          __half2 s = __hmul2(wv[0], *reinterpret_cast<const __half2*>(&xv.x));
+          s = __hfma2(wv[1], *reinterpret_cast<const __half2*>(&xv.y), s);
+          s = __hfma2(wv[2], *reinterpret_cast<const __half2*>(&xv.z), s);
+          s = __hfma2(wv[3], *reinterpret_cast<const __half2*>(&xv.w), s);
+          gsum[t] += __low2float(s) + __high2float(s);
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < TMAX; ++t) acc[t] = fmaf(gsum[t], scale, acc[t]);
+    }
+#pragma unroll
+    for (int t = 0; t < TMAX; ++t) {
+      const float s = WarpSum(acc[t]);
+      if (lane == 0 && t < T) {
+        if (out_f32) static_cast<float*>(y)[static_cast<size_t>(t) * N + n] = s;
+        else static_cast<__nv_bfloat16*>(y)[static_cast<size_t>(t) * N + n] = __float2bfloat16(s);
+      }
+    }
+  }
+}
+
+__global__ void Bf16Gemv(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x, float* __restrict__ y,
+                         int T, int N, int K) {
+  __shared__ float red[32];
+  const int n = blockIdx.x;
+  const __nv_bfloat16* w = W + static_cast<size_t>(n) * K;
+  for (int t = 0; t < T; ++t) {
+    float s = 0.f;
+    for (int k = threadIdx.x * 2; k < K; k += blockDim.x * 2) {
+      const uint32_t a = *reinterpret_cast<const uint32_t*>(w + k);
+      const uint32_t b = *reinterpret_cast<const uint32_t*>(x + static_cast<size_t>(t) * K + k);
+      s += BfLo(a) * BfLo(b) + BfHi(a) * BfHi(b);
+    }
+    s = BlockSum(s, red);
+    if (threadIdx.x == 0) y[static_cast<size_t>(t) * N + n] = s;
+  }
+}
+
+// ---- argmax ------------------------------------------------------------------------------------
+constexpr int kArgParts = 256;
+
+__device__ __forceinline__ void ArgBetter(float v, int i, float& bv, int& bi) {
+  if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+}
+
+template <bool kF32>
+__global__ void ArgmaxPartial(const void* __restrict__ logits, int V, float* __restrict__ pv, int* __restrict__ pi) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int t = blockIdx.y, part = blockIdx.x;
+  const int chunk = (V + kArgParts - 1) / kArgParts;
+  const int b = part * chunk, e = min(V, b + chunk);
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = b + threadIdx.x; i < e; i += blockDim.x) {
+    float v;
+    if (kF32) v = static_cast<const float*>(logits)[static_cast<size_t>(t) * V + i];
+    else v = __bfloat162float(static_cast<const __nv_bfloat16*>(logits)[static_cast<size_t>(t) * V + i]);
+    if (v != v) v = -INFINITY;   // a NaN never wins
+    ArgBetter(v, i, bv, bi);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    ArgBetter(ov, oi, bv, bi);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (warp == 0) {
+    const int nw = blockDim.x >> 5;
+    bv = lane < nw ? sv[lane] : -INFINITY;
+    bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      ArgBetter(ov, oi, bv, bi);
+    }
+    if (lane == 0) { pv[t * kArgParts + part] = bv; pi[t * kArgParts + part] = bi; }
+  }
+}
+
+__global__ void ArgmaxFinal(const float* __restrict__ pv, const int* __restrict__ pi, int id_offset,
+                            int* __restrict__ out_ids, float* __restrict__ out_vals) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
+  const int t = blockIdx.x;
+  float bv = pv[t * kArgParts + threadIdx.x];
+  int bi = pi[t * kArgParts + threadIdx.x];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    ArgBetter(ov, oi, bv, bi);
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kArgParts / 32; ++w) ArgBetter(sv[w], si[w], bv, bi);
+    out_ids[t] = bi + id_offset;
+    if (out_vals) out_vals[t] = bv;
+  }
+}
+
+template <int TMAX>
+int LaunchW4(const void* wq, const void* wsz, const void* x, void* y, int T, int N, int K, int group, int out_f32,
+             cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(TMAX) * K * 2;
+  if (smem > 200 * 1024) return R4DXB_TOO_LARGE;
+  auto kern = W4Gemv<TMAX>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  // enough CTAs to fill 148 SMs a few times over, but rows_per_cta >= 8 so that every warp has work
+  int rows_per_cta = (N + 148 * 8 - 1) / (148 * 8);
+  rows_per_cta = ((rows_per_cta + 7) / 8) * 8;
+  const int grid = (N + rows_per_cta - 1) / rows_per_cta;
+  kern<<<grid, kThreads, smem, stream>>>(static_cast<const uint4*>(wq), static_cast<const uint32_t*>(wsz),
+                                         static_cast<const __nv_bfloat16*>(x), y, T, N, K, group, out_f32, rows_per_cta);
+  return FinishLaunch();
+}
+
+}  // namespace
+}  // namespace r4dxb
+
+using namespace r4dxb;
+
+extern "C" {
+
+int r4dxb_w4a16_gemv(const void* wq, const void* wsz, const void* x, void* y, int T, int N, int K, int group,
+                     int out_f32, void* stream) {
+  if (T < 1 || T > 8 || K % 32 || (group != 32 && group != 64 && group != 128) || K % group) return R4DXB_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (T == 1) return LaunchW4<1>(wq, wsz, x, y, T, N, K, group, out_f32, s);
+  if (T == 2) return LaunchW4<2>(wq, wsz, x, y, T, N, K, group, out_f32, s);
+  if (T <= 4) return LaunchW4<4>(wq, wsz, x, y, T, N, K, group, out_f32, s);
+  return LaunchW4<8>(wq, wsz, x, y, T, N, K, group, out_f32, s);
+}
+
+int r4dxb_bf16_gemv(const void* W, const void* x, float* y, int T, int N, int K, void* stream) {
+  if (T < 1 || N < 1 || K % 2) return R4DXB_BAD_ARG;
+  Bf16Gemv<<<N, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(W),
+                                                             static_cast<const __nv_bfloat16*>(x), y, T, N, K);
+  return FinishLaunch();
+}
+
+int r4dxb_argmax_rows(const void* logits, int is_f32, int T, int V, int id_offset, int* out_ids, float* out_vals,
+                      void* scratch, void* stream) {
+  if (T < 1 || V < 1) return R4DXB_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* pv = static_cast<float*>(scratch);
+  int* pi = reinterpret_cast<int*>(pv + static_cast<size_t>(T) * kArgParts);
+  dim3 grid(kArgParts, T);
+  if (is_f32) ArgmaxPartial<true><<<grid, 256, 0, s>>>(logits, V, pv, pi);
+  else ArgmaxPartial<false><<<grid, 256, 0, s>>>(logits, V, pv, pi);
+  int e = FinishLaunch();
+  if (e) return e;
+  ArgmaxFinal<<<T, kArgParts, 0, s>>>(pv, pi, id_offset, out_ids, out_vals);
+  return FinishLaunch();
+}
+
+}  // extern "C"

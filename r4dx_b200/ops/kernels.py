@@ -1,0 +1,228 @@
+"""Python face of the sm_100a kernel library: tensor checks + ctypes calls on the current stream.
+
+Every function requires CUDA tensors and the in-tree ``libr4dxb_cuda.so``; there is no eager
+fallback (a missing library raises).  Reference numerics for each op live in ``ops/reference.py``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import native
+from ..native import c_f32, c_i64, c_int, c_ptr, register_cuda_sig
+from ..quant.trellis import TrellisWeight
+from ..quant.w4a16 import W4Weight
+
+_I = c_int
+_P = c_ptr
+_F = c_f32
+
+register_cuda_sig("r4dxb_launch_count", ctypes.c_ulonglong, [])
+register_cuda_sig("r4dxb_launch_count_reset", None, [])
+register_cuda_sig("r4dxb_embed_gather_bf16", _I, [_P, _P, _P, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_rmsnorm_bf16", _I, [_P, _P, _P, _I, _I, _F, _I, _P])
+register_cuda_sig("r4dxb_add_rmsnorm_bf16", _I, [_P, _P, _P, _P, _I, _I, _F, _I, _P])
+register_cuda_sig("r4dxb_layernorm_bf16", _I, [_P, _P, _P, _P, _I, _I, _F, _P])
+register_cuda_sig("r4dxb_silu_mul_bf16", _I, [_P, _P, _I, _I, _P])
+register_cuda_sig("r4dxb_residual_add_bf16", _I, [_P, _P, ctypes.c_longlong, _P])
+register_cuda_sig("r4dxb_bias_act_bf16", _I, [_P, _P, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_trellis_gemv", _I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_w4a16_gemv", _I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_bf16_gemv", _I, [_P, _P, _P, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_argmax_rows", _I, [_P, _I, _I, _I, _I, _P, _P, _P, _P])
+register_cuda_sig("r4dxb_gdn_decode", _I, [_P] * 15 + [_I, _I, _I, _I, _F, _P])
+register_cuda_sig("r4dxb_attn_precore", _I, [_P] * 11 + [_I, _I, _I, _I, _I, _F, _F, _P])
+register_cuda_sig("r4dxb_attn_decode", _I, [_P] * 10 + [_I, _I, _I, _I, _I, _I, _P])
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _lib():
+    return native.cuda()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, name: str) -> None:
+    if code != 0:
+        raise KernelError(f"{name} failed with code {code}")
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def _req(t: torch.Tensor, dtype, name: str) -> torch.Tensor:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    return t
+
+
+def launch_count() -> int:
+    return int(_lib().r4dxb_launch_count())
+
+
+def launch_count_reset() -> None:
+    _lib().r4dxb_launch_count_reset()
+
+
+BF = torch.bfloat16
+
+NORM_ZERO_CENTERED = 1
+NORM_NO_WEIGHT = 2
+
+
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _req(ids, torch.int32, "ids"); _req(table, BF, "table")
+    T, (V, H) = ids.numel(), table.shape
+    out = out if out is not None else torch.empty(T, H, dtype=BF, device=ids.device)
+    _check(_lib().r4dxb_embed_gather_bf16(_p(ids), _p(table), _p(out), T, H, V, _stream()), "embed_gather")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float = 1e-6, zero_centered: bool = True,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _req(x, BF, "x")
+    H = x.shape[-1]
+    T = x.numel() // H
+    out = out if out is not None else torch.empty_like(x)
+    mode = (NORM_ZERO_CENTERED if zero_centered else 0) | (NORM_NO_WEIGHT if w is None else 0)
+    _check(_lib().r4dxb_rmsnorm_bf16(_p(x), _p(w), _p(out), T, H, eps, mode, _stream()), "rmsnorm")
+    return out
+
+
+def add_rmsnorm(res: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: float = 1e-6,
+                zero_centered: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """res += delta in place (bf16); returns rmsnorm(res)."""
+    _req(res, BF, "res"); _req(delta, BF, "delta")
+    H = res.shape[-1]
+    T = res.numel() // H
+    out = out if out is not None else torch.empty_like(res)
+    mode = NORM_ZERO_CENTERED if zero_centered else 0
+    _check(_lib().r4dxb_add_rmsnorm_bf16(_p(res), _p(delta), _p(w), _p(out), T, H, eps, mode, _stream()), "add_rmsnorm")
+    return out
+
+
+def layernorm(x, w, b, eps: float = 1e-6):
+    _req(x, BF, "x")
+    H = x.shape[-1]
+    out = torch.empty_like(x)
+    _check(_lib().r4dxb_layernorm_bf16(_p(x), _p(w), _p(b), _p(out), x.numel() // H, H, eps, _stream()), "layernorm")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _req(gate_up, BF, "gate_up")
+    I = gate_up.shape[-1] // 2
+    T = gate_up.numel() // (2 * I)
+    out = out if out is not None else torch.empty(*gate_up.shape[:-1], I, dtype=BF, device=gate_up.device)
+    _check(_lib().r4dxb_silu_mul_bf16(_p(gate_up), _p(out), T, I, _stream()), "silu_mul")
+    return out
+
+
+def residual_add(res: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    _req(res, BF, "res"); _req(delta, BF, "delta")
+    _check(_lib().r4dxb_residual_add_bf16(_p(res), _p(delta), res.numel(), _stream()), "residual_add")
+    return res
+
+
+def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], act: int = 0) -> torch.Tensor:
+    _req(x, BF, "x")
+    H = x.shape[-1]
+    _check(_lib().r4dxb_bias_act_bf16(_p(x), _p(bias), x.numel() // H, H, act, _stream()), "bias_act")
+    return x
+
+
+def pick_ksplit(N: int, K: int, target_ctas: int = 296) -> int:
+    """Smallest cluster split (1/2/4/8) that gives at least ``target_ctas`` CTAs, subject to K/128 % split == 0."""
+    kblocks = K // 128
+    best = 1
+    for s in (1, 2, 4, 8):
+        if kblocks % s:
+            continue
+        best = s
+        if (N // 128) * s >= target_ctas:
+            break
+    return best
+
+
+def trellis_gemv(w: TrellisWeight, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None, ksplit: Optional[int] = None) -> torch.Tensor:
+    """y[T, N] = trellis linear of x[T, K] (T <= 8), optionally + residual (may alias out)."""
+    _req(x, BF, "x")
+    T = x.numel() // w.K
+    out = out if out is not None else torch.empty(T, w.N, dtype=BF, device=x.device)
+    ks = ksplit or pick_ksplit(w.N, w.K)
+    _check(_lib().r4dxb_trellis_gemv(_p(w.words), _p(w.suh), _p(w.svh), _p(x), _p(out), _p(residual), T, w.N, w.K,
+                                     w.kb, ks, _stream()), "trellis_gemv")
+    return out
+
+
+def w4a16_gemv(w: W4Weight, x: torch.Tensor, out_f32: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _req(x, BF, "x")
+    T = x.numel() // w.K
+    if out is None:
+        out = torch.empty(T, w.N, dtype=torch.float32 if out_f32 else BF, device=x.device)
+    _check(_lib().r4dxb_w4a16_gemv(_p(w.wq), _p(w.wsz), _p(x), _p(out), T, w.N, w.K, w.group, 1 if out_f32 else 0,
+                                   _stream()), "w4a16_gemv")
+    return out
+
+
+def bf16_gemv(W: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _req(W, BF, "W"); _req(x, BF, "x")
+    N, K = W.shape
+    T = x.numel() // K
+    out = out if out is not None else torch.empty(T, N, dtype=torch.float32, device=x.device)
+    _check(_lib().r4dxb_bf16_gemv(_p(W), _p(x), _p(out), T, N, K, _stream()), "bf16_gemv")
+    return out
+
+
+def argmax_rows(logits: torch.Tensor, id_offset: int = 0, out_ids: Optional[torch.Tensor] = None,
+                out_vals: Optional[torch.Tensor] = None, scratch: Optional[torch.Tensor] = None):
+    T, V = logits.shape
+    is_f32 = logits.dtype == torch.float32
+    if not is_f32:
+        _req(logits, BF, "logits")
+    dev = logits.device
+    out_ids = out_ids if out_ids is not None else torch.empty(T, dtype=torch.int32, device=dev)
+    out_vals = out_vals if out_vals is not None else torch.empty(T, dtype=torch.float32, device=dev)
+    scratch = scratch if scratch is not None else torch.empty(2 * T * 256, dtype=torch.float32, device=dev)
+    _check(_lib().r4dxb_argmax_rows(_p(logits), 1 if is_f32 else 0, T, V, id_offset, _p(out_ids), _p(out_vals),
+                                    _p(scratch), _stream()), "argmax_rows")
+    return out_ids, out_vals
+
+
+def gdn_decode(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, log_u, log_k, log_eg, positions,
+               n_replay, out, T: int, H: int, Hk: int, D: int, eps: float = 1e-6) -> torch.Tensor:
+    _check(_lib().r4dxb_gdn_decode(_p(mixed), _p(z), _p(ab), _p(conv_w), _p(A_log), _p(dt_bias), _p(norm_w), _p(ring),
+                                   _p(state), _p(log_u), _p(log_k), _p(log_eg), _p(positions), _p(n_replay), _p(out),
+                                   T, H, Hk, D, eps, _stream()), "gdn_decode")
+    return out
+
+
+def attn_precore(qg, k, v, q_norm, k_norm, k_descale, v_descale, positions, block_table, q_out, cache, T: int,
+                 Hq: int, Hkv: int, D: int, rotary_dim: int, theta: float, eps: float = 1e-6):
+    _check(_lib().r4dxb_attn_precore(_p(qg), _p(k), _p(v), _p(q_norm), _p(k_norm), _p(k_descale), _p(v_descale),
+                                     _p(positions), _p(block_table), _p(q_out), _p(cache), T, Hq, Hkv, D, rotary_dim,
+                                     theta, eps, _stream()), "attn_precore")
+    return q_out
+
+
+def attn_decode(q, qg, cache, block_table, positions, k_descale, v_descale, part_acc, part_ml, out, T: int, Hq: int,
+                Hkv: int, D: int, splits: int, gated: bool = True):
+    _check(_lib().r4dxb_attn_decode(_p(q), _p(qg), _p(cache), _p(block_table), _p(positions), _p(k_descale),
+                                    _p(v_descale), _p(part_acc), _p(part_ml), _p(out), T, Hq, Hkv, D, splits,
+                                    1 if gated else 0, _stream()), "attn_decode")
+    return out

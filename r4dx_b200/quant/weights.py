@@ -1,0 +1,188 @@
+"""Model weight sets: quantizing fp32 weights, synthetic quantized weights, container save/load.
+
+A weight set is a dict name -> TrellisWeight | W4Weight | torch.Tensor.  Body linears use the
+trellis layout (mixed 4/5 bit = ~4.5 bpw by default), the LM head w4a16 (group 64), gates /
+norms / conv stay bf16 or fp32 -- the same split the reference container uses
+(reference: docs/container-format.md:50-83, 599-605).
+"""
+from __future__ import annotations
+
+import json
+from typing import Callable, Dict, Iterable, Optional, Tuple
+
+import torch
+
+from ..config import ModelConfig
+from . import trellis, w4a16
+from .container import Container, write_container
+from .trellis import TrellisWeight
+from .w4a16 import W4Weight
+
+F32_NAMES = ("A_log", "dt_bias", "k_descale", "v_descale")
+
+
+def default_kb_rule(name: str) -> int:
+    """Mixed 4/5-bit plan (~4.5 bpw): 5 bits on even layers, 4 bits on odd layers."""
+    parts = name.split(".")
+    if "layers" in parts:
+        layer = int(parts[parts.index("layers") + 1])
+        return 5 if layer % 2 == 0 else 4
+    return 4
+
+
+def moe_kb_rule(name: str) -> int:
+    """Mixed 3/4-bit plan (~3.3 bpw) for the expert-heavy MoE variant: experts mostly 3 bits."""
+    if ".experts." in name:
+        parts = name.split(".")
+        e = int(parts[parts.index("experts") + 1])
+        return 4 if e % 3 == 0 else 3
+    return 4
+
+
+def is_quantized_linear(name: str) -> bool:
+    leaf = name.split(".")[-1]
+    return leaf in ("qg", "k", "v", "o", "in_proj_qkv", "in_proj_z", "out_proj", "gate_up", "down")
+
+
+def quantize_weight_set(cfg: ModelConfig, w: Dict[str, torch.Tensor], layout: str = "trellis",
+                        kb_rule: Callable[[str], int] = default_kb_rule, head_group: int = 64,
+                        seed: int = 0) -> Dict[str, object]:
+    """fp32 weights -> quantized set (CPU; Viterbi for trellis).  layout: trellis | w4a16 | bf16."""
+    out: Dict[str, object] = {}
+    for i, (name, t) in enumerate(w.items()):
+        leaf = name.split(".")[-1]
+        if name == "lm_head":
+            out[name] = w4a16.quantize(t, head_group) if layout != "bf16" else t.to(torch.bfloat16)
+        elif is_quantized_linear(name) and layout == "trellis" and t.shape[0] % 128 == 0 and t.shape[1] % 128 == 0:
+            out[name], _ = trellis.quantize(t, kb_rule(name), seed=seed * 100003 + i)
+        elif is_quantized_linear(name) and layout == "w4a16":
+            out[name] = w4a16.quantize(t, head_group)
+        elif leaf in F32_NAMES:
+            out[name] = t.float()
+        else:
+            out[name] = t.to(torch.bfloat16)
+    return out
+
+
+def dequantize_weight_set(q: Dict[str, object]) -> Dict[str, torch.Tensor]:
+    """Effective fp32 weights of a quantized set: what the CPU oracle must use to match the GPU."""
+    out = {}
+    for name, t in q.items():
+        if isinstance(t, TrellisWeight):
+            out[name] = trellis.reconstruct(t)
+        elif isinstance(t, W4Weight):
+            out[name] = w4a16.dequantize(t)
+        else:
+            out[name] = t.float().cpu()
+    return out
+
+
+def linear_shapes(cfg: ModelConfig, with_mtp: bool = False) -> Iterable[Tuple[str, int, int]]:
+    """(name, N, K) of every quantizable linear of the (rank-local) config."""
+    H = cfg.hidden_size
+    for i in range(cfg.num_hidden_layers):
+        p = f"text.layers.{i}."
+        if cfg.is_attention_layer(i):
+            yield p + "attn.qg", 2 * cfg.q_dim, H
+            yield p + "attn.k", cfg.kv_dim, H
+            yield p + "attn.v", cfg.kv_dim, H
+            yield p + "attn.o", H, cfg.q_dim
+        else:
+            yield p + "gdn.in_proj_qkv", cfg.conv_dim, H
+            yield p + "gdn.in_proj_z", cfg.value_dim, H
+            yield p + "gdn.out_proj", H, cfg.value_dim
+        if not cfg.is_moe:
+            yield p + "mlp.gate_up", 2 * cfg.intermediate_size, H
+            yield p + "mlp.down", H, cfg.intermediate_size
+
+
+def synthetic_weight_set(cfg: ModelConfig, device="cuda", seed: int = 0, sigma: float = 0.02,
+                         kb_rule: Callable[[str], int] = default_kb_rule, head_group: int = 64,
+                         with_mtp: bool = False) -> Dict[str, object]:
+    """Random-init weights created directly in the quantized domain (dense hybrid).
+
+    Body linears get random trellis code bits (decoded values ~ N(0,1)) with svh = +-sigma, the LM
+    head random nibbles; everything else is N(0, sigma).  ``cfg`` may be a TP shard view, in which
+    case only this rank's slices are created.
+    """
+    g = torch.Generator(device=device).manual_seed(seed)
+
+    def n(*shape, dtype=torch.bfloat16):
+        return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * sigma).to(dtype)
+
+    H = cfg.hidden_size
+    w: Dict[str, object] = {"text.embed_tokens": n(cfg.vocab_size, H)}
+    for i, (name, N, K) in enumerate(linear_shapes(cfg)):
+        w[name] = trellis.random_weight(N, K, kb_rule(name), seed=seed * 7919 + i, sigma=sigma, device=device)
+    for i in range(cfg.num_hidden_layers):
+        p = f"text.layers.{i}."
+        w[p + "input_layernorm"] = n(H)
+        w[p + "post_attention_layernorm"] = n(H)
+        if cfg.is_attention_layer(i):
+            w[p + "attn.q_norm"] = n(cfg.head_dim)
+            w[p + "attn.k_norm"] = n(cfg.head_dim)
+            w[p + "attn.k_descale"] = torch.full((cfg.num_key_value_heads,), 1.0 / 16, device=device)
+            w[p + "attn.v_descale"] = torch.full((cfg.num_key_value_heads,), 1.0 / 16, device=device)
+        else:
+            Hv = cfg.linear_num_value_heads
+            w[p + "gdn.in_proj_a"] = n(Hv, H)
+            w[p + "gdn.in_proj_b"] = n(Hv, H)
+            w[p + "gdn.conv1d_weight"] = n(cfg.conv_dim, cfg.linear_conv_kernel_dim)
+            w[p + "gdn.A_log"] = n(Hv, dtype=torch.float32)
+            w[p + "gdn.dt_bias"] = n(Hv, dtype=torch.float32)
+            w[p + "gdn.norm_weight"] = (1.0 + n(cfg.linear_value_head_dim).float()).to(torch.bfloat16)
+    w["text.final_norm"] = n(H)
+    w["lm_head"] = w4a16.random_weight(cfg.vocab_shard_size, H, head_group, seed=seed + 17, sigma=sigma, device=device)
+    return w
+
+
+# ---- container -------------------------------------------------------------------------------------
+def save_weight_set(path: str, cfg: ModelConfig, q: Dict[str, object], extra_meta: Optional[Dict[str, str]] = None) -> None:
+    tensors = []
+    quant = {}
+    for name, t in q.items():
+        if isinstance(t, TrellisWeight):
+            quant[name] = {"layout": "trellis", "kb": t.kb, "N": t.N, "K": t.K}
+            tensors += [(name + ".trellis.words", t.words), (name + ".trellis.suh", t.suh), (name + ".trellis.svh", t.svh)]
+        elif isinstance(t, W4Weight):
+            quant[name] = {"layout": "w4a16", "group": t.group, "N": t.N, "K": t.K}
+            tensors += [(name + ".w4a16.wq", t.wq), (name + ".w4a16.wsz", t.wsz)]
+        else:
+            tensors.append((name, t))
+    meta = {"model_config": cfg.to_json(), "quant": json.dumps(quant), "format": "r4dxb-1",
+            "arch": cfg.arch}
+    meta.update(extra_meta or {})
+    write_container(path, tensors, meta)
+
+
+def load_weight_set(path: str, device="cpu", names: Optional[Callable[[str], bool]] = None) -> Tuple[ModelConfig, Dict[str, object]]:
+    ct = Container(path)
+    cfg = ct.model_config()
+    quant = ct.quant_info()
+    out: Dict[str, object] = {}
+    on_cpu = str(device) == "cpu"
+
+    class _Get:
+        """Copies out of the read-only mapping (the mapping dies with the Container object)."""
+        @staticmethod
+        def tensor(n):
+            t = Container.tensor(ct, n)
+            return t.clone() if on_cpu else t.to(device)
+    ct_get = _Get()
+    for name, qi in quant.items():
+        if names and not names(name):
+            continue
+        if qi["layout"] == "trellis":
+            out[name] = TrellisWeight(ct_get.tensor(name + ".trellis.words"), ct_get.tensor(name + ".trellis.suh"),
+                                      ct_get.tensor(name + ".trellis.svh"), qi["N"], qi["K"], qi["kb"])
+        else:
+            out[name] = W4Weight(ct_get.tensor(name + ".w4a16.wq"), ct_get.tensor(name + ".w4a16.wsz"),
+                                 qi["N"], qi["K"], qi["group"])
+    for name in ct.names:
+        if ".trellis." in name or ".w4a16." in name:
+            continue
+        if names and not names(name):
+            continue
+        out[name] = ct_get.tensor(name)
+    ct.close()
+    return cfg, out

@@ -1,0 +1,228 @@
+"""CUDA kernels vs the plain PyTorch fp32 reference of the same op (needs a B200)."""
+import math
+
+import pytest
+import torch
+
+from r4dx_b200.ops import reference as R
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def K():
+    from r4dx_b200.ops import kernels
+    from r4dx_b200 import native
+    native.cuda()
+    return kernels
+
+
+def _bf(t):
+    return t.to(BF).cuda()
+
+
+def test_native_library_is_loaded(K):
+    from r4dx_b200 import native
+    assert native.cuda_loaded()
+
+
+def test_embed_rmsnorm_silu(K):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(100, 256, generator=g)
+    ids = torch.tensor([3, 99, 0, 250, -4], dtype=torch.int32)
+    out = K.embed_gather(ids.cuda(), _bf(table))
+    exp = table.to(BF)[ids.clamp(0, 99).long()]
+    assert torch.equal(out.cpu(), exp)
+
+    x = torch.randn(5, 5120, generator=g)
+    w = torch.randn(5120, generator=g) * 0.1
+    y = K.rmsnorm(_bf(x), _bf(w))
+    ref = R.rmsnorm_1pw(x.to(BF), w.to(BF))
+    assert torch.allclose(y.float().cpu(), ref, atol=2e-2, rtol=1e-2)
+    y2 = K.rmsnorm(_bf(x), _bf(w), zero_centered=False)
+    assert torch.allclose(y2.float().cpu(), R.rmsnorm_plain(x.to(BF), w.to(BF)), atol=2e-2, rtol=1e-2)
+
+    res = _bf(x.clone())
+    delta = _bf(torch.randn(5, 5120, generator=g))
+    res0 = res.clone()
+    y3 = K.add_rmsnorm(res, delta, _bf(w))
+    summed = (res0.float() + delta.float()).to(BF)
+    assert torch.equal(res, summed)
+    assert torch.allclose(y3.float().cpu(), R.rmsnorm_1pw(summed.cpu(), w.to(BF)), atol=2e-2, rtol=1e-2)
+
+    gu = torch.randn(3, 2 * 1024, generator=g)
+    act = K.silu_mul(_bf(gu))
+    assert torch.allclose(act.float().cpu(), R.silu_mul(gu.to(BF)), atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("kb", [3, 4, 5])
+@pytest.mark.parametrize("T,ksplit", [(1, 1), (1, 4), (3, 2), (8, 8)])
+def test_trellis_gemv(K, kb, T, ksplit):
+    from r4dx_b200.quant import trellis
+    N, Kd = 256, 1024
+    tw = trellis.random_weight(N, Kd, kb, seed=kb * 10 + T, sigma=0.02)
+    g = torch.Generator().manual_seed(T)
+    x = torch.randn(T, Kd, generator=g).to(BF)
+    res = torch.randn(T, N, generator=g).to(BF)
+    ref = trellis.linear_reference(tw, x.float())
+    y = K.trellis_gemv(tw.to("cuda"), x.cuda(), ksplit=ksplit)
+    scale = ref.abs().max().item()
+    assert (y.float().cpu() - ref).abs().max().item() < 0.02 * scale + 1e-3
+    y2 = K.trellis_gemv(tw.to("cuda"), x.cuda(), residual=res.cuda(), ksplit=ksplit)
+    assert (y2.float().cpu() - (ref + res.float())).abs().max().item() < 0.02 * (scale + 3) + 1e-3
+
+
+def test_trellis_gemv_one_hot_returns_decoded_rows(K):
+    """x = e_k after undoing the input transform picks out column k of H Q H exactly (up to bf16)."""
+    from r4dx_b200.quant import trellis
+    tw = trellis.random_weight(128, 128, 4, seed=3, sigma=1.0)
+    Wr = trellis.reconstruct(tw)
+    x = torch.zeros(2, 128)
+    x[0, 5] = 1.0
+    x[1, 77] = 2.0
+    y = K.trellis_gemv(tw.to("cuda"), _bf(x), ksplit=1).float().cpu()
+    assert torch.allclose(y[0], Wr[:, 5], atol=0.03, rtol=0.02)
+    assert torch.allclose(y[1], 2 * Wr[:, 77], atol=0.06, rtol=0.02)
+
+
+@pytest.mark.parametrize("T", [1, 2, 5, 8])
+def test_w4a16_gemv_and_argmax(K, T):
+    from r4dx_b200.quant import w4a16
+    g = torch.Generator().manual_seed(T)
+    W = torch.randn(1000, 512, generator=g) * 0.02
+    q = w4a16.quantize(W, 64)
+    Wd = w4a16.dequantize(q)
+    x = torch.randn(T, 512, generator=g).to(BF)
+    y = K.w4a16_gemv(q.to("cuda"), x.cuda())
+    ref = x.float() @ Wd.T
+    assert torch.allclose(y.cpu(), ref, atol=5e-3, rtol=1e-2)
+    ids, vals = K.argmax_rows(y, id_offset=7)
+    assert torch.equal(ids.cpu().long(), y.cpu().argmax(-1) + 7)
+
+
+def test_argmax_ties_take_lowest_id(K):
+    lg = torch.zeros(2, 5000, device="cuda")
+    lg[0, 4000] = 1.0
+    lg[0, 123] = 1.0
+    lg[1, 4999] = 2.0
+    ids, vals = K.argmax_rows(lg)
+    assert ids.tolist() == [123, 4999] and vals.tolist() == [1.0, 2.0]
+    ids, _ = K.argmax_rows(lg.to(BF))
+    assert ids.tolist() == [123, 4999]
+
+
+def test_bf16_gemv(K):
+    g = torch.Generator().manual_seed(0)
+    W = torch.randn(96, 1024, generator=g).to(BF)
+    x = torch.randn(4, 1024, generator=g).to(BF)
+    y = K.bf16_gemv(W.cuda(), x.cuda())
+    assert torch.allclose(y.cpu(), x.float() @ W.float().T, atol=1e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("D,Hv,Hk", [(128, 6, 2), (64, 4, 2)])
+def test_gdn_decode_matches_recurrence_with_rollback(K, D, Hv, Hk):
+    """Rows are fed in windows; only an accepted prefix of each window is committed."""
+    g = torch.Generator().manual_seed(D)
+    key_dim, conv_dim = Hk * D, 2 * Hk * D + Hv * D
+    n_tok = 40
+    mixed = (torch.randn(n_tok, conv_dim, generator=g) * 0.5).to(BF)
+    z = torch.randn(n_tok, Hv * D, generator=g).to(BF)
+    ab = torch.randn(n_tok, 2 * Hv, generator=g)
+    conv_w = (torch.randn(conv_dim, 4, generator=g) * 0.5).to(BF)
+    A_log = torch.randn(Hv, generator=g) * 0.3
+    dt_bias = torch.randn(Hv, generator=g) * 0.3
+    norm_w = (1 + 0.1 * torch.randn(D, generator=g)).to(BF)
+    # reference over the full accepted sequence
+    y, _ = R.causal_conv1d_silu(mixed.float(), conv_w.float(), None)
+    q = R.l2norm(y[:, :key_dim].view(n_tok, Hk, D))
+    k = R.l2norm(y[:, key_dim:2 * key_dim].view(n_tok, Hk, D))
+    v = y[:, 2 * key_dim:].view(n_tok, Hv, D)
+    gg, beta = R.gdn_gates(ab[:, :Hv], ab[:, Hv:], A_log, dt_bias)
+    o, S_ref = R.gdn_recurrent(q, k, v, gg, beta, None)
+    ref = R.gated_rmsnorm(o, z.float().view(n_tok, Hv, D), norm_w.float()).view(n_tok, Hv * D)
+
+    dev = "cuda"
+    ring = torch.zeros(16, conv_dim, dtype=BF, device=dev)
+    state = torch.zeros(Hv, D, D, device=dev)
+    log_u = torch.zeros(8, Hv, D, device=dev)
+    log_k = torch.zeros(8, Hv, D, device=dev)
+    log_eg = torch.zeros(8, Hv, device=dev)
+    n_replay = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = torch.zeros(8, Hv * D, dtype=BF, device=dev)
+    got = torch.zeros(n_tok, Hv * D)
+    pos = 0
+    gj = torch.Generator().manual_seed(1)
+    pending = 0
+    while pos < n_tok:
+        T = min(int(torch.randint(1, 9, (1,), generator=gj)), n_tok - pos)
+        acc = int(torch.randint(1, T + 1, (1,), generator=gj))
+        # rejected rows carry junk that must leave no trace
+        rows_m = mixed[pos:pos + T].clone()
+        rows_z = z[pos:pos + T].clone()
+        rows_ab = ab[pos:pos + T].clone()
+        if acc < T:
+            rows_m[acc:] = 3.0
+            rows_ab[acc:] = -1.0
+        positions = torch.arange(pos, pos + T, dtype=torch.int32, device=dev)
+        n_replay.fill_(pending)
+        K.gdn_decode(rows_m.cuda(), rows_z.cuda(), rows_ab.cuda(), conv_w.cuda(), A_log.cuda(), dt_bias.cuda(),
+                     norm_w.cuda(), ring, state, log_u, log_k, log_eg, positions, n_replay, out, T, Hv, Hk, D)
+        got[pos:pos + acc] = out[:acc].float().cpu()
+        pending = acc
+        pos += acc
+    assert torch.allclose(got, ref, atol=3e-2, rtol=3e-2)
+    # commit the tail and compare the state
+    n_replay.fill_(pending)
+    K.gdn_decode(mixed[:1].cuda(), z[:1].cuda(), ab[:1].cuda(), conv_w.cuda(), A_log.cuda(), dt_bias.cuda(),
+                 norm_w.cuda(), ring, state, log_u, log_k, log_eg, torch.zeros(1, dtype=torch.int32, device=dev),
+                 n_replay, out, 0, Hv, Hk, D)
+    assert torch.allclose(state.cpu(), S_ref, atol=2e-3, rtol=2e-2)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,T,ctx", [(256, 6, 1, 1, 100), (256, 12, 2, 4, 333), (64, 4, 2, 8, 40), (256, 24, 4, 1, 1500)])
+def test_attention_precore_and_decode(K, D, Hq, Hkv, T, ctx):
+    g = torch.Generator().manual_seed(ctx)
+    dev = "cuda"
+    rd = D // 4
+    theta = 1e7
+    nblk = (ctx + T + 15) // 16 + 1
+    cache = torch.zeros(nblk, Hkv, 2, 16, D, dtype=torch.uint8, device=dev)
+    # shuffled physical blocks exercise the block table
+    table = torch.randperm(nblk, generator=g).to(torch.int32).cuda()
+    qn = (torch.randn(D, generator=g) * 0.1).to(BF)
+    kn = (torch.randn(D, generator=g) * 0.1).to(BF)
+    kds = torch.full((Hkv,), 1 / 8.0)
+    vds = torch.full((Hkv,), 1 / 16.0)
+    total = ctx + T
+    qg_all = torch.randn(total, Hq, 2 * D, generator=g).to(BF)
+    k_all = torch.randn(total, Hkv, D, generator=g).to(BF)
+    v_all = torch.randn(total, Hkv, D, generator=g).to(BF)
+    q_out = torch.zeros(8, Hq, D, dtype=BF, device=dev)
+    # fill the context through the precore kernel, 8 rows per call
+    for s in range(0, ctx, 8):
+        e = min(ctx, s + 8)
+        pos = torch.arange(s, e, dtype=torch.int32, device=dev)
+        K.attn_precore(qg_all[s:e].cuda(), k_all[s:e].cuda(), v_all[s:e].cuda(), qn.cuda(), kn.cuda(), kds.cuda(),
+                       vds.cuda(), pos, table, q_out, cache, e - s, Hq, Hkv, D, rd, theta)
+    pos = torch.arange(ctx, ctx + T, dtype=torch.int32, device=dev)
+    qg_new = qg_all[ctx:].cuda().contiguous()
+    K.attn_precore(qg_new, k_all[ctx:].cuda(), v_all[ctx:].cuda(), qn.cuda(), kn.cuda(), kds.cuda(), vds.cuda(), pos,
+                   table, q_out, cache, T, Hq, Hkv, D, rd, theta)
+    splits = 5
+    G = Hq // Hkv * T
+    part_acc = torch.zeros(splits * Hkv * G * D, device=dev)
+    part_ml = torch.zeros(splits * Hkv * G * 2, device=dev)
+    out = torch.zeros(T, Hq * D, dtype=BF, device=dev)
+    K.attn_decode(q_out, qg_new, cache, table, pos, kds.cuda(), vds.cuda(), part_acc, part_ml, out, T, Hq, Hkv, D,
+                  splits, True)
+    # reference
+    allpos = torch.arange(total)
+    qf = R.rope_partial_neox(R.rmsnorm_1pw(qg_all[..., :D], qn), allpos, rd, theta)
+    kf = R.rope_partial_neox(R.rmsnorm_1pw(k_all, kn), allpos, rd, theta)
+    kq = R.fp8_e4m3_roundtrip(kf, 1 / 8.0)
+    vq = R.fp8_e4m3_roundtrip(v_all.float(), 1 / 16.0)
+    assert torch.allclose(q_out[:T].float().cpu(), qf[ctx:].to(BF).float(), atol=3e-2, rtol=2e-2)
+    o = R.causal_gqa_attention(qf[ctx:].to(BF), kq, vq, ctx)
+    o = o * torch.sigmoid(qg_all[ctx:, :, D:].float())
+    assert torch.allclose(out.float().cpu().view(T, Hq, D), o, atol=2e-2, rtol=3e-2)

@@ -1,0 +1,71 @@
+"""End-to-end GPU model vs the fp32 CPU oracle on the tiny hybrid geometry (needs a B200)."""
+import pytest
+import torch
+
+from r4dx_b200.config import tiny_hybrid_config
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    from r4dx_b200.models.oracle import OracleModel, init_weights
+    from r4dx_b200.quant.weights import dequantize_weight_set, quantize_weight_set
+    cfg = tiny_hybrid_config()
+    w = init_weights(cfg, 0)
+    q = quantize_weight_set(cfg, w)
+    dq = dequantize_weight_set(q)
+    oracle = OracleModel(cfg, dq, fp8_kv=True)
+    return cfg, q, oracle
+
+
+def _to_dev(q):
+    return {k: (v.to("cuda") if hasattr(v, "to") else v) for k, v in q.items()}
+
+
+def test_logits_and_greedy_tokens_match_oracle(tiny):
+    from r4dx_b200.models.hybrid import HybridModel
+    cfg, q, oracle = tiny
+    ids = torch.randint(0, cfg.vocab_size, (64,), generator=torch.Generator().manual_seed(1))
+    ref_logits, st = oracle.forward(ids)
+    m = HybridModel(cfg, _to_dev(q), max_ctx=256)
+    # feed 8 rows at a time and collect the logits of every row
+    rows = []
+    for s in range(0, 64, 8):
+        m.feed(ids[s:s + 8].to(torch.int32))
+        rows.append(m.logits_rows(8).float().cpu().clone())
+    got = torch.cat(rows)
+    scale = ref_logits.abs().max().item()
+    err = (got - ref_logits).abs().max().item()
+    assert err < 0.05 * scale, (err, scale)
+    agree = (got.argmax(-1) == ref_logits.argmax(-1)).float().mean().item()
+    assert agree > 0.9, agree
+
+
+def test_graph_decode_equals_eager_decode(tiny):
+    from r4dx_b200.models.hybrid import HybridModel
+    cfg, q, oracle = tiny
+    ids = torch.randint(0, cfg.vocab_size, (19,), generator=torch.Generator().manual_seed(2))
+    a = HybridModel(cfg, _to_dev(q), max_ctx=256)
+    t_eager = a.generate_greedy(ids, 16, use_graph=False)
+    b = HybridModel(cfg, _to_dev(q), max_ctx=256)
+    t_graph = b.generate_greedy(ids, 16, use_graph=True)
+    assert t_eager == t_graph
+    ref = oracle.greedy(ids, 16)
+    same = sum(int(x == y) for x, y in zip(t_eager, ref))
+    assert same >= 12, (t_eager, ref)     # bf16 activations may flip a near-tie late in the sequence
+
+
+def test_single_row_steps_equal_eight_row_chunks(tiny):
+    from r4dx_b200.models.hybrid import HybridModel
+    cfg, q, _ = tiny
+    ids = torch.randint(0, cfg.vocab_size, (24,), generator=torch.Generator().manual_seed(3)).to(torch.int32)
+    a = HybridModel(cfg, _to_dev(q), max_ctx=128)
+    for s in range(0, 24, 8):
+        a.feed(ids[s:s + 8])
+    la = a.logits_rows(8)[7].float().cpu()
+    b = HybridModel(cfg, _to_dev(q), max_ctx=128)
+    for s in range(24):
+        b.feed(ids[s:s + 1])
+    lb = b.logits_rows(1)[0].float().cpu()
+    assert torch.allclose(la, lb, atol=2e-2 * la.abs().max().item())
