@@ -1,0 +1,107 @@
+"""Microbenchmarks of the hot kernels at the 27B geometry's shapes.
+
+    python -m r4dx_b200.utils.bench_kernels [--only trellis_gemv] [--shape gate_up] [--rows 1] [--iters 20]
+
+Each kernel is timed with CUDA events after warm-up; a 256 MiB buffer is rewritten between timed
+launches so the weights never sit in L2.  Prints algorithmic bytes / time and the fraction of the
+measured copy bandwidth (MEASURED_PEAKS.json beside the repository root, else 6650 GB/s).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+SHAPES_27B = {            # name: (N, K)
+    "in_proj_qkv": (10240, 5120), "in_proj_z": (6144, 5120), "out_proj": (5120, 6144),
+    "qg": (12288, 5120), "kv": (1024, 5120), "o": (5120, 6144),
+    "gate_up": (34816, 5120), "down": (5120, 17408),
+}
+
+
+def _peak_gbs() -> float:
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(p))["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+def timed(fn, iters: int, flush: torch.Tensor) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    tot = 0.0
+    for _ in range(iters):
+        flush.add_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        tot += e0.elapsed_time(e1)
+    return tot / iters * 1e3      # us
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--shape", default="")
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--kb", type=int, default=0)
+    ap.add_argument("--ctx", type=int, default=8192)
+    a = ap.parse_args()
+    from r4dx_b200.ops import kernels as K
+    from r4dx_b200.quant import trellis, w4a16
+    peak = _peak_gbs()
+    dev = "cuda"
+    flush = torch.zeros(256 << 18, dtype=torch.float32, device=dev)
+    T = a.rows
+    BF = torch.bfloat16
+    if a.only in ("", "trellis_gemv"):
+        for name, (N, Kd) in SHAPES_27B.items():
+            if a.shape and a.shape != name:
+                continue
+            for kb in ((a.kb,) if a.kb else (4, 5)):
+                w = trellis.random_weight(N, Kd, kb, seed=1, device=dev)
+                x = torch.randn(T, Kd, device=dev).to(BF)
+                y = torch.empty(T, N, dtype=BF, device=dev)
+                ks = K.pick_ksplit(N, Kd)
+                us = timed(lambda: K.trellis_gemv(w, x, out=y, ksplit=ks), a.iters, flush)
+                gbs = w.nbytes / us / 1e3
+                print(f"trellis_gemv {name:12s} N={N:6d} K={Kd:6d} kb={kb} T={T} ksplit={ks}: {us:8.1f} us  "
+                      f"{gbs:7.0f} GB/s  {gbs / peak:5.2f} of measured HBM  {N * Kd / us / 1e6:6.2f} Tweights/s")
+    if a.only in ("", "w4a16"):
+        N, Kd = 248320, 5120
+        w = w4a16.random_weight(N, Kd, 64, device=dev)
+        x = torch.randn(T, Kd, device=dev).to(BF)
+        y = torch.empty(T, N, dtype=torch.float32, device=dev)
+        us = timed(lambda: K.w4a16_gemv(w, x, out=y), a.iters, flush)
+        gbs = w.nbytes / us / 1e3
+        print(f"w4a16_gemv lm_head N={N} K={Kd} T={T}: {us:8.1f} us  {gbs:7.0f} GB/s  {gbs / peak:5.2f} of measured HBM")
+    if a.only in ("", "attn"):
+        Hq, Hkv, D = 24, 4, 256
+        ctx = a.ctx
+        nblk = (ctx + T + 15) // 16 + 1
+        cache = torch.randint(0, 120, (nblk, Hkv, 2, 16, D), dtype=torch.uint8, device=dev)
+        table = torch.arange(nblk, dtype=torch.int32, device=dev)
+        pos = torch.arange(ctx, ctx + T, dtype=torch.int32, device=dev)
+        q = torch.randn(T, Hq, D, device=dev).to(BF)
+        qg = torch.randn(T, Hq, 2 * D, device=dev).to(BF)
+        ds = torch.full((Hkv,), 1 / 16.0, device=dev)
+        splits = 37
+        G = Hq // Hkv * T
+        pa = torch.zeros(splits * Hkv * G * D, device=dev)
+        pm = torch.zeros(splits * Hkv * G * 2, device=dev)
+        out = torch.zeros(T, Hq * D, dtype=BF, device=dev)
+        us = timed(lambda: K.attn_decode(q, qg, cache, table, pos, ds, ds, pa, pm, out, T, Hq, Hkv, D, splits, True),
+                   a.iters, flush)
+        nbytes = ctx * Hkv * 2 * D
+        print(f"attn_decode ctx={ctx} T={T}: {us:8.1f} us  {nbytes / us / 1e3:7.0f} GB/s  {nbytes / us / 1e3 / peak:5.2f} of measured HBM")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,47 @@
+"""Runs a few eager decode steps of a synthetic model for kernel profiling.
+
+    python -m r4dx_b200.utils.profile_step --layers 64 --ctx 8192 --steps 1
+
+The model is positioned at ``--ctx`` without a prefill (the KV cache holds zeros, which costs the
+same to read), one untimed step warms every kernel up, then ``--steps`` steps run between
+cudaProfilerStart/Stop so that a profiler started with ``--profile-from-start off`` captures
+exactly those launches.  Prints the device time of the profiled steps.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--steps", type=int, default=1)
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--model", default="27b", choices=["27b", "small"])
+    a = ap.parse_args()
+    from r4dx_b200.config import qwen_hybrid_27b_config, small_hybrid_config
+    from r4dx_b200.models.hybrid import HybridModel
+    from r4dx_b200.quant.weights import synthetic_weight_set
+    cfg = qwen_hybrid_27b_config(a.layers) if a.model == "27b" else small_hybrid_config(a.layers)
+    w = synthetic_weight_set(cfg, device="cuda", seed=0)
+    m = HybridModel(cfg, w, max_ctx=a.ctx + 64 + a.rows * (a.steps + 2))
+    m.pos = a.ctx
+    ids = torch.randint(0, cfg.vocab_size, (a.rows,), dtype=torch.int32)
+    m.feed(ids)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()
+    e0.record()
+    for _ in range(a.steps):
+        m.feed(ids)
+    e1.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(f"eager {a.steps} step(s) of {a.rows} row(s): {e0.elapsed_time(e1) / a.steps:.3f} ms/step")
+
+
+if __name__ == "__main__":
+    main()
