@@ -226,3 +226,64 @@ int r4dxb_argmax_rows(const void* logits, int is_f32, int T, int V, int id_offse
 }
 
 }  // extern "C"
+
+// ---- row argmax for callers that cannot allocate -------------------------------------------------
+// Declared in r4dxb_noalloc.h.  Same two kernels as r4dxb_argmax_rows, but the per-part
+// (value, index) partials live in a fixed array inside this library instead of a caller buffer.
+#include <mutex>
+
+#include "r4dxb_noalloc.h"
+
+namespace r4dxb {
+namespace {
+
+// [rows][256 parts] floats followed by [rows][256 parts] ints; every GPU that loads the library
+// carries one copy (128 KiB) until the process exits.
+static __device__ __align__(256) unsigned char g_argmax_static_scratch[R4DXB_ARGMAX_STATIC_MAX_ROWS * kArgParts * 8];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};   // device address of the array, per device ordinal
+std::mutex g_static_scratch_mutex;
+
+// In host code the array's name is only a handle; the address a kernel can use comes from
+// cudaGetSymbolAddress, looked up once per device while that device is current.
+int StaticScratchFor(int device, void** out) {
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[device] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_argmax_static_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_static_scratch_addr[device] = p;
+  }
+  *out = g_static_scratch_addr[device];
+  return 0;
+}
+
+}  // namespace
+}  // namespace r4dxb
+
+extern "C" int r4dxb_argmax_rows_static(const void* logits, int is_f32, int T, int V, int id_offset, int* out_ids,
+                                        float* out_vals, void* stream) {
+  using namespace r4dxb;
+  if (T < 1 || V < 1 || logits == nullptr || out_ids == nullptr) return R4DXB_BAD_ARG;
+  if (T > R4DXB_ARGMAX_STATIC_MAX_ROWS) return R4DXB_TOO_LARGE;
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (device < 0 || device >= kMaxDevices) return R4DXB_UNSUPPORTED;
+  void* scratch = nullptr;
+  const int rc = StaticScratchFor(device, &scratch);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* pv = static_cast<float*>(scratch);
+  int* pi = reinterpret_cast<int*>(pv + static_cast<size_t>(T) * kArgParts);
+  // Every (row, part) slot that ArgmaxFinal reads is written by ArgmaxPartial in this same call,
+  // so nothing left over from an earlier call is ever consumed and nothing needs clearing.
+  dim3 grid(kArgParts, T);
+  if (is_f32) ArgmaxPartial<true><<<grid, 256, 0, s>>>(logits, V, pv, pi);
+  else ArgmaxPartial<false><<<grid, 256, 0, s>>>(logits, V, pv, pi);
+  int err = FinishLaunch();
+  if (err) return err;
+  ArgmaxFinal<<<T, kArgParts, 0, s>>>(pv, pi, id_offset, out_ids, out_vals);
+  return FinishLaunch();
+}
