@@ -1,0 +1,333 @@
+// Trellis-decode GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), for T >= 16 rows.
+//
+//   Y[t, n] = bf16( svh[n] * H128( sum_k Q[n, k] * Xh[t, k] )[n] (+ residual[t, n]) )
+//
+// "Swap-AB": the decoded weight block is the UMMA A operand (M = 128 weight rows = the span of one
+// output Hadamard), the activations are the B operand (N = TN tokens), so the fp32 accumulator
+// sits in TMEM as [lane = weight row][column = token].  Weights are decoded exactly once per CTA
+// and reused by all TN tokens of the tile.
+//
+// Warp roles (192 threads):
+//   warps 0-3  decode: packed words (shared memory) -> fp16 codes -> A tile in the canonical
+//              K-major 128-byte-swizzled UMMA layout; later the epilogue (TMEM -> registers ->
+//              shared transpose -> FWHT128 over the weight rows -> svh, residual -> bf16 rows)
+//   warp 4     producer: TMA tile of Xh [TN x 64] (128B swizzle) + bulk copy of the slab's words
+//   warp 5     MMA issuer: one elected thread issues 4 x tcgen05.mma (K = 16) per 64-wide K slab
+//              and commits to the stage's "empty" barrier; it also owns the TMEM allocation.
+// A dense mode (KB == 0) takes A from a plain fp16 [N, K] matrix instead of decoding: that is the
+// bf16/fp16-layout linear and the bisecting aid for the tensor-core plumbing.
+//
+// The reference engine's counterparts are WMMA kernels whose decoded fragments are shared through
+// LDS (reference: third_party/libr4d/r4d_gemm_trellis_nt_m256.hip:1-60); nothing is shared with them.
+#include "sm100_ptx.cuh"
+#include "trellis_decode.cuh"
+
+namespace r4dxb {
+namespace {
+
+constexpr int kGemmThreads = 192;
+constexpr int kSlabK = 64;                 // K per pipeline stage = one 128-byte swizzle row of fp16
+constexpr int kATileBytes = 128 * kSlabK * 2;   // 16 KiB
+
+template <int KB, int TN, int STAGES>
+struct GemmSmem {
+  static constexpr int kWordsBytes = (KB == 0) ? 0 : 4 * 8 * 8 * KB * 4;   // 4 k-tiles x 8 n-tiles x 8KB words
+  static constexpr int kXTileBytes = TN * kSlabK * 2;
+  static constexpr int kStageBytes = kATileBytes + kXTileBytes + ((kWordsBytes + 1023) / 1024) * 1024;
+  static constexpr int kEpiStride = 132;                                     // floats per staged token row
+  static constexpr int kEpiBytes = 32 * kEpiStride * 4;
+  static constexpr int kTotal = STAGES * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+template <int KB, int TN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __restrict__ wsrc,
+                  const __half* __restrict__ svh, __nv_bfloat16* __restrict__ y,
+                  const __nv_bfloat16* __restrict__ residual, int T, int N, int K, int* __restrict__ status) {
+  using S = GemmSmem<KB, TN, STAGES>;
+  extern __shared__ unsigned char smem_dyn[];
+  // 1024-byte alignment: required by the swizzled UMMA / TMA tiles
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  unsigned char* stage_base = smem;
+  float* epi = reinterpret_cast<float*>(smem + STAGES * S::kStageBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes + S::kEpiBytes);
+  uint64_t* full = bars;                    // [STAGES] producer -> decode / MMA
+  uint64_t* aready = bars + STAGES;         // [STAGES] decode -> MMA
+  uint64_t* empty = bars + 2 * STAGES;      // [STAGES] MMA -> producer
+  uint64_t* accum = bars + 3 * STAGES;      // [1]      MMA -> epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nb = blockIdx.x;                 // 128-row weight block
+  const int t0 = blockIdx.y * TN;            // first token of the tile
+  const int slabs = K / kSlabK;
+  constexpr uint32_t kTmemCols = TN < 32 ? 32 : TN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::MbarInit(&full[s], 1);
+      ptx::MbarInit(&aready[s], 4);
+      ptx::MbarInit(&empty[s], 1);
+    }
+    ptx::MbarInit(accum, 1);
+    *abort_flag = 0;
+    ptx::MbarFenceInit();
+  }
+  if (warp == 5) {
+    ptx::TmemAlloc(tmem_slot, kTmemCols);
+    ptx::TmemRelinquish();
+  }
+  if (warp == 4 && lane == 0) ptx::PrefetchTensorMap(&tmap_x);
+  ptx::TcFenceBefore();
+  __syncthreads();
+  ptx::TcFenceAfter();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto a_tile = [&](int s) { return stage_base + s * S::kStageBytes; };
+  auto x_tile = [&](int s) { return stage_base + s * S::kStageBytes + kATileBytes; };
+  auto w_tile = [&](int s) { return stage_base + s * S::kStageBytes + kATileBytes + S::kXTileBytes; };
+
+  if (warp == 4) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      const size_t slab_words = 4 * 8 * 8 * (KB == 0 ? 1 : KB);
+      const uint32_t* wbase = static_cast<const uint32_t*>(wsrc) + static_cast<size_t>(nb) * (K / 16) * 8 * 8 * (KB == 0 ? 1 : KB);
+      for (int it = 0; it < slabs; ++it) {
+        const int s = it % STAGES, round = it / STAGES;
+        if (!ptx::MbarWait(&empty[s], (round & 1) ^ 1, abort_flag, 1)) break;
+        ptx::MbarArriveExpectTx(&full[s], S::kXTileBytes + S::kWordsBytes);
+        ptx::TmaLoad2D(x_tile(s), &tmap_x, &full[s], it * kSlabK, t0);
+        if (KB != 0) ptx::BulkLoad(w_tile(s), wbase + static_cast<size_t>(it) * slab_words, S::kWordsBytes, &full[s]);
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::UmmaInstrDescF16(128, TN, false);
+      bool ok = true;
+      for (int it = 0; it < slabs && ok; ++it) {
+        const int s = it % STAGES, round = it / STAGES;
+        ok = ptx::MbarWait(&full[s], round & 1, abort_flag, 2) && ptx::MbarWait(&aready[s], round & 1, abort_flag, 3);
+        if (!ok) break;
+        ptx::TcFenceAfter();
+        const uint32_t a_addr = ptx::SmemAddr(a_tile(s)), b_addr = ptx::SmemAddr(x_tile(s));
+#pragma unroll
+        for (int k = 0; k < kSlabK / 16; ++k) {
+          const uint64_t da = ptx::UmmaDescSw128(a_addr + k * 32), db = ptx::UmmaDescSw128(b_addr + k * 32);
+          ptx::UmmaF16(tmem_base, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        ptx::UmmaCommit(&empty[s]);           // frees the stage once these MMAs have read it
+      }
+      if (ok) ptx::UmmaCommit(accum);         // accumulator complete
+    }
+  } else {
+    // ---------------- decode warps 0-3 ----------------
+    // lane slot: row (lane % 16) of the 16-row n-tile, K half (lane / 16) -> conflict-free 16-byte stores
+    const int row_in_tile = lane & 15, khalf = lane >> 4;
+    TrellisLane<(KB == 0 ? 4 : KB)> tl;
+    tl.Init(2 * row_in_tile + khalf);
+    bool ok = true;
+    for (int it = 0; it < slabs && ok; ++it) {
+      const int s = it % STAGES, round = it / STAGES;
+      if (KB != 0) {
+        ok = ptx::MbarWait(&full[s], round & 1, abort_flag, 4);
+      } else {
+        // dense mode reads global memory directly, but the A tile must be free again
+        ok = ptx::MbarWait(&empty[s], (round & 1) ^ 1, abort_flag, 5);
+      }
+      if (!ok) break;
+      unsigned char* at = a_tile(s);
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const int j = warp * 2 + jj;                       // n-tile inside the 128-row block
+        const int r = j * 16 + row_in_tile;                // row inside the block
+#pragma unroll
+        for (int kt = 0; kt < 4; ++kt) {
+          uint4 packed;
+          if (KB != 0) {
+            constexpr int NW = 8 * (KB == 0 ? 4 : KB);
+            const uint32_t* tw = reinterpret_cast<const uint32_t*>(w_tile(s)) + (kt * 8 + j) * NW;
+            uint32_t hi, lo;
+            tl.Window(tw[tl.i0], tw[tl.i1], (KB == 4) ? 0u : tw[tl.i2], hi, lo);
+            __half2 w[4];
+            TrellisDecode8<(KB == 0 ? 4 : KB)>(hi, lo, w);
+            packed.x = *reinterpret_cast<uint32_t*>(&w[0]);
+            packed.y = *reinterpret_cast<uint32_t*>(&w[1]);
+            packed.z = *reinterpret_cast<uint32_t*>(&w[2]);
+            packed.w = *reinterpret_cast<uint32_t*>(&w[3]);
+          } else {
+            const __half* dense = static_cast<const __half*>(wsrc);
+            packed = __ldg(reinterpret_cast<const uint4*>(dense + (static_cast<size_t>(nb) * 128 + r) * K + it * kSlabK +
+                                                          kt * 16 + khalf * 8));
+          }
+          const int chunk = kt * 2 + khalf;                // 16-byte chunk inside the 128-byte row
+          *reinterpret_cast<uint4*>(at + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4)) = packed;
+        }
+      }
+      ptx::FenceProxyAsyncShared();          // generic-proxy stores -> visible to the tensor core (async proxy)
+      __syncwarp();
+      if (lane == 0) ptx::MbarArrive(&aready[s]);
+    }
+
+    // ---------------- epilogue (same four warps: warp w owns TMEM lanes 32w .. 32w+31) ----------------
+    if (ok) ok = ptx::MbarWait(accum, 0, abort_flag, 6);
+    ptx::TcFenceAfter();
+    const float inv_sqrt = 0.08838834764831845f;
+    for (int c0 = 0; c0 < TN; c0 += 32) {
+      constexpr int CW = TN < 32 ? 16 : 32;   // columns per TMEM load
+      if (ok) {
+        uint32_t v[32];
+        if constexpr (CW == 32) {
+          ptx::TmemLoad32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
+        } else {
+          uint32_t v16[16];
+          ptx::TmemLoad32x16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c0, v16);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = v16[i];
+        }
+        ptx::TmemLoadWait();
+#pragma unroll
+        for (int c = 0; c < CW; ++c) epi[c * S::kEpiStride + warp * 32 + lane] = __uint_as_float(v[c]);
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (ok) {
+        for (int c = warp; c < CW; c += 4) {
+          const int t = t0 + c0 + c;
+          if (t < T) {
+            const float4 p = *reinterpret_cast<const float4*>(epi + c * S::kEpiStride + lane * 4);
+            float f[4] = {p.x, p.y, p.z, p.w};
+            WarpFwht128(f);
+            const int n = nb * 128 + lane * 4;
+            const uint2 sv = *reinterpret_cast<const uint2*>(svh + n);
+            const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
+            float o0 = f[0] * inv_sqrt * __low2float(s01), o1 = f[1] * inv_sqrt * __high2float(s01);
+            float o2 = f[2] * inv_sqrt * __low2float(s23), o3 = f[3] * inv_sqrt * __high2float(s23);
+            if (residual != nullptr) {
+              const uint2 rv = *reinterpret_cast<const uint2*>(residual + static_cast<size_t>(t) * N + n);
+              o0 += BfLo(rv.x); o1 += BfHi(rv.x); o2 += BfLo(rv.y); o3 += BfHi(rv.y);
+            }
+            uint2 ov;
+            ov.x = PackBf16(o0, o1);
+            ov.y = PackBf16(o2, o3);
+            *reinterpret_cast<uint2*>(y + static_cast<size_t>(t) * N + n) = ov;
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
+  }
+
+  // ---------------- teardown ----------------
+  ptx::TcFenceBefore();
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // give copies that may still be in flight time to land before the shared memory goes away
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0) atomicExch(status, *abort_flag);
+  }
+  if (warp == 5) ptx::TmemDealloc(tmem_base, kTmemCols);
+}
+
+// ---- input transform: Xh = fp16(H128(suh * x)) -------------------------------------------------------
+// one warp per 128-block; producer variants fold the preceding elementwise op into the transform
+// (reference: src/kernels/src/trellis_transform.hip:84-486 fuses the same producers).
+//   mode 0: x = in[t, k]                      (in: [T, K])
+//   mode 1: x = silu(in[t, k]) * in[t, K + k] (in: [T, 2K] fused gate|up rows)
+__global__ void TrellisInputKernel(const __nv_bfloat16* __restrict__ in, const __half* __restrict__ suh,
+                                   __half* __restrict__ out, int T, int K, int mode) {
+  const int lane = threadIdx.x & 31;
+  const int blocks_per_row = K / 128;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= static_cast<long long>(T) * blocks_per_row) return;
+  const int t = static_cast<int>(item / blocks_per_row), b = static_cast<int>(item % blocks_per_row);
+  const int k = b * 128 + lane * 4;
+  float v[4];
+  if (mode == 0) {
+    const uint2 xv = *reinterpret_cast<const uint2*>(in + static_cast<size_t>(t) * K + k);
+    v[0] = BfLo(xv.x); v[1] = BfHi(xv.x); v[2] = BfLo(xv.y); v[3] = BfHi(xv.y);
+  } else {
+    const uint2 g = *reinterpret_cast<const uint2*>(in + static_cast<size_t>(t) * 2 * K + k);
+    const uint2 u = *reinterpret_cast<const uint2*>(in + static_cast<size_t>(t) * 2 * K + K + k);
+    // the product is rounded to bf16 exactly like the unfused silu_mul kernel rounds it
+    const uint32_t p01 = PackBf16(Silu(BfLo(g.x)) * BfLo(u.x), Silu(BfHi(g.x)) * BfHi(u.x));
+    const uint32_t p23 = PackBf16(Silu(BfLo(g.y)) * BfLo(u.y), Silu(BfHi(g.y)) * BfHi(u.y));
+    v[0] = BfLo(p01); v[1] = BfHi(p01); v[2] = BfLo(p23); v[3] = BfHi(p23);
+  }
+  const uint2 sv = *reinterpret_cast<const uint2*>(suh + k);
+  const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
+  v[0] *= __low2float(s01); v[1] *= __high2float(s01); v[2] *= __low2float(s23); v[3] *= __high2float(s23);
+  WarpFwht128(v);
+  const float inv_sqrt = 0.08838834764831845f;
+  __half2 o01 = __floats2half2_rn(v[0] * inv_sqrt, v[1] * inv_sqrt), o23 = __floats2half2_rn(v[2] * inv_sqrt, v[3] * inv_sqrt);
+  uint2 ov;
+  ov.x = *reinterpret_cast<uint32_t*>(&o01);
+  ov.y = *reinterpret_cast<uint32_t*>(&o23);
+  *reinterpret_cast<uint2*>(out + static_cast<size_t>(t) * K + k) = ov;
+}
+
+template <int KB, int TN, int STAGES>
+int LaunchGemm(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
+               int* status, cudaStream_t stream) {
+  using S = GemmSmem<KB, TN, STAGES>;
+  CUtensorMap tmap;
+  const int rc = MakeTensorMap2D16(&tmap, xh, static_cast<uint64_t>(T), static_cast<uint64_t>(K), TN, kSlabK, false);
+  if (rc) return rc;
+  auto kern = TrellisGemmKernel<KB, TN, STAGES>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  dim3 grid(N / 128, (T + TN - 1) / TN);
+  kern<<<grid, kGemmThreads, S::kTotal, stream>>>(tmap, wsrc, static_cast<const __half*>(svh),
+                                                  static_cast<__nv_bfloat16*>(y),
+                                                  static_cast<const __nv_bfloat16*>(residual), T, N, K, status);
+  return FinishLaunch();
+}
+
+template <int KB>
+int LaunchGemmTN(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
+                 int tn, int* status, cudaStream_t s) {
+  switch (tn) {
+    case 16: return LaunchGemm<KB, 16, 4>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 32: return LaunchGemm<KB, 32, 4>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 64: return LaunchGemm<KB, 64, 4>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 128: return LaunchGemm<KB, 128, 4>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 256: return LaunchGemm<KB, 256, 3>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    default: return R4DXB_BAD_ARG;
+  }
+}
+
+}  // namespace
+}  // namespace r4dxb
+
+using namespace r4dxb;
+
+extern "C" {
+
+int r4dxb_trellis_input(const void* in, const void* suh, void* out, int T, int K, int mode, void* stream) {
+  if (T < 1 || K % 128 || mode < 0 || mode > 1) return R4DXB_BAD_ARG;
+  const long long items = static_cast<long long>(T) * (K / 128);
+  const int warps_per_cta = 8;
+  TrellisInputKernel<<<static_cast<unsigned>((items + warps_per_cta - 1) / warps_per_cta), warps_per_cta * 32, 0,
+                       static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(in),
+                                                            static_cast<const __half*>(suh), static_cast<__half*>(out), T, K, mode);
+  return FinishLaunch();
+}
+
+/* y[T, N] (bf16) from xh[T, K] (fp16, already input-transformed).  kb = 0: `w` is a dense fp16 [N, K]
+ * matrix (svh still applies; pass ones and set hadamard-free weights accordingly); kb in {3,4,5}: packed
+ * trellis words.  tn = token tile (16/32/64/128/256).  status: device int, set non-zero if a bounded wait
+ * inside the kernel ran out. */
+int r4dxb_trellis_gemm(const void* w, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
+                       int kb, int tn, int* status, void* stream) {
+  if (T < 1 || N % 128 || K % 128) return R4DXB_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (kb) {
+    case 0: return LaunchGemmTN<0>(w, svh, xh, y, residual, T, N, K, tn, status, s);
+    case 3: return LaunchGemmTN<3>(w, svh, xh, y, residual, T, N, K, tn, status, s);
+    case 4: return LaunchGemmTN<4>(w, svh, xh, y, residual, T, N, K, tn, status, s);
+    case 5: return LaunchGemmTN<5>(w, svh, xh, y, residual, T, N, K, tn, status, s);
+    default: return R4DXB_BAD_ARG;
+  }
+}
+
+}  // extern "C"

@@ -226,3 +226,65 @@ def attn_decode(q, qg, cache, block_table, positions, k_descale, v_descale, part
                                     _p(v_descale), _p(part_acc), _p(part_ml), _p(out), T, Hq, Hkv, D, splits,
                                     1 if gated else 0, _stream()), "attn_decode")
     return out
+
+
+register_cuda_sig("r4dxb_trellis_input", _I, [_P, _P, _P, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_trellis_gemm", _I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P])
+
+_STATUS = {}
+
+
+def gemm_status(device) -> torch.Tensor:
+    """Device word that a tcgen05 kernel sets when one of its bounded waits runs out."""
+    key = torch.device(device).index or 0
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_gemm_status(device) -> None:
+    code = int(gemm_status(device).item())
+    if code:
+        gemm_status(device).zero_()
+        raise KernelError(f"tcgen05 GEMM gave up in a bounded wait (role code {code})")
+
+
+def trellis_input(x: torch.Tensor, suh: torch.Tensor, out: Optional[torch.Tensor] = None, fused_silu_mul: bool = False) -> torch.Tensor:
+    """fp16 H128(suh * x) rows; with ``fused_silu_mul`` x is silu(gate) * up of fused [T, 2K] rows."""
+    _req(x, BF, "x")
+    K_ = suh.numel()
+    T = x.numel() // (2 * K_ if fused_silu_mul else K_)
+    out = out if out is not None else torch.empty(T, K_, dtype=torch.float16, device=x.device)
+    _check(_lib().r4dxb_trellis_input(_p(x), _p(suh), _p(out), T, K_, 1 if fused_silu_mul else 0, _stream()), "trellis_input")
+    return out
+
+
+def pick_token_tile(T: int) -> int:
+    for tn in (16, 32, 64, 128):
+        if T <= tn:
+            return tn
+    return 256 if T >= 512 else 128
+
+
+def trellis_gemm(w: TrellisWeight, xh: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                 out: Optional[torch.Tensor] = None, tn: Optional[int] = None) -> torch.Tensor:
+    """y[T, N] from input-transformed xh[T, K] on the tcgen05 path."""
+    _req(xh, torch.float16, "xh")
+    T = xh.numel() // w.K
+    out = out if out is not None else torch.empty(T, w.N, dtype=BF, device=xh.device)
+    tn = tn or pick_token_tile(T)
+    _check(_lib().r4dxb_trellis_gemm(_p(w.words), _p(w.svh), _p(xh), _p(out), _p(residual), T, w.N, w.K, w.kb, tn,
+                                     _p(gemm_status(xh.device)), _stream()), "trellis_gemm")
+    return out
+
+
+def dense_gemm_hadamard(W: torch.Tensor, svh: torch.Tensor, xh: torch.Tensor, tn: Optional[int] = None) -> torch.Tensor:
+    """Same kernel with a dense fp16 A operand: y = svh * H128(xh W^T) over 128-row blocks of N."""
+    _req(W, torch.float16, "W"); _req(xh, torch.float16, "xh")
+    N, K_ = W.shape
+    T = xh.numel() // K_
+    out = torch.empty(T, N, dtype=BF, device=xh.device)
+    tn = tn or pick_token_tile(T)
+    _check(_lib().r4dxb_trellis_gemm(_p(W), _p(svh), _p(xh), _p(out), None, T, N, K_, 0, tn,
+                                     _p(gemm_status(xh.device)), _stream()), "dense_gemm")
+    return out
