@@ -50,6 +50,17 @@ class Linear:
             return K.w4a16_gemv(w, x, out_f32=(out.dtype == torch.float32), out=out)
         raise NotImplementedError(f"layout of {self.name}")
 
+    def chunk(self, x: torch.Tensor, xh_buf: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
+              fused_silu_mul: bool = False) -> torch.Tensor:
+        """Large-T path: input transform (optionally fused with SwiGLU) + tcgen05 GEMM."""
+        w = self.w
+        if not isinstance(w, TrellisWeight):
+            raise NotImplementedError(f"chunk path for layout of {self.name}")
+        T = out.shape[0]
+        xh = xh_buf.view(-1)[:T * w.K].view(T, w.K)
+        K.trellis_input(x, w.suh, out=xh, fused_silu_mul=fused_silu_mul)
+        return K.trellis_gemm(w, xh, residual=residual, out=out)
+
     @property
     def nbytes(self) -> int:
         w = self.w
@@ -257,7 +268,7 @@ class HybridModel:
         self.pending_rows = n
         self.pos += n
 
-    def prefill(self, ids: torch.Tensor) -> int:
+    def prefill_small(self, ids: torch.Tensor) -> int:
         """Feeds a prompt through the small-batch path (MAX_ROWS rows per call); returns the greedy next token."""
         ids = ids.to(torch.int32)
         n = ids.numel()
@@ -268,6 +279,128 @@ class HybridModel:
             s = e
         last = (n - 1) % MAX_ROWS
         return int(self.buf.next_ids[last].item())
+
+    # ---- chunked prefill (tcgen05 GEMMs, long-chunk GDN scan, tensor-core attention) ----------------
+    def _chunk_buffers(self, C: int) -> dict:
+        cb = getattr(self, "_cb", None)
+        if cb is not None and cb["C"] >= C:
+            return cb
+        cfg, dev = self.cfg, self.device
+        H = cfg.hidden_size
+        Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
+        kmax = max(H, cfg.value_dim, cfg.q_dim, cfg.intermediate_size)
+        e = lambda *s, dtype=BF: torch.empty(*s, dtype=dtype, device=dev)
+        f32 = torch.float32
+        cb = dict(C=C, ids=e(C, dtype=torch.int32), positions=e(C, dtype=torch.int32), x=e(C, H), h=e(C, H),
+                  xh=e(C * kmax, dtype=torch.float16), mixed=e(C, cfg.conv_dim), z=e(C, cfg.value_dim),
+                  ab=e(C, 2 * Hv, dtype=f32), core=e(C * max(cfg.value_dim, cfg.q_dim)), qg=e(C, 2 * cfg.q_dim),
+                  k=e(C, cfg.kv_dim), v=e(C, cfg.kv_dim), q=e(C, cfg.q_dim), gate_up=e(C, 2 * cfg.intermediate_size),
+                  gdn=dict(q=e(C, Hk, Dg, dtype=f32), k=e(C, Hk, Dg, dtype=f32), v=e(C, Hv, Dg, dtype=f32),
+                           o=e(C, Hv, Dg, dtype=f32), eg=e(C, Hv, dtype=f32), beta=e(C, Hv, dtype=f32)))
+        self._cb = cb
+        return cb
+
+    def commit_pending(self) -> None:
+        """Folds the rows still sitting in the GDN logs into the base states (needed before a chunk scan)."""
+        if self.pending_rows == 0:
+            return
+        cfg, b, w = self.cfg, self.buf, self.w
+        b.n_replay.fill_(self.pending_rows)
+        for i in self.gdn_state:
+            p = f"text.layers.{i}.gdn."
+            K.gdn_decode(b.mixed, b.z, b.ab, w[p + "conv1d_weight"], w[p + "A_log"], w[p + "dt_bias"], w[p + "norm_weight"],
+                         self.ring[i], self.gdn_state[i], self.log_u[i], self.log_k[i], self.log_eg[i], b.positions,
+                         b.n_replay, b.core, 0, cfg.linear_num_value_heads, cfg.linear_num_key_heads,
+                         cfg.linear_key_head_dim, cfg.rms_norm_eps)
+        self.pending_rows = 0
+        b.n_replay.zero_()
+
+    def forward_chunk(self, T: int, want_logits: bool) -> None:
+        """Runs T (> MAX_ROWS) rows staged in the chunk buffers at positions self.pos .. ; commits them."""
+        cfg, w, cb = self.cfg, self.w, self._cb
+        H = cfg.hidden_size
+        Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
+        x, h = cb["x"][:T], cb["h"][:T]
+        pos0 = self.pos
+        K.embed_gather(cb["ids"][:T], w["text.embed_tokens"], out=x)
+        for i in range(cfg.num_hidden_layers):
+            p = f"text.layers.{i}."
+            K.rmsnorm(x, w[p + "input_layernorm"], cfg.rms_norm_eps, out=h)
+            if cfg.is_attention_layer(i):
+                pa = p + "attn."
+                qg, kk, vv, q = cb["qg"][:T], cb["k"][:T], cb["v"][:T], cb["q"][:T]
+                self.lin[pa + "qg"].chunk(h, cb["xh"], qg)
+                self.lin[pa + "k"].chunk(h, cb["xh"], kk)
+                self.lin[pa + "v"].chunk(h, cb["xh"], vv)
+                K.attn_precore(qg, kk, vv, w[pa + "q_norm"], w[pa + "k_norm"], w[pa + "k_descale"], w[pa + "v_descale"],
+                               cb["positions"], self.block_table, q, self.kv[i], T, Hq, Hkv, D, cfg.rotary_dim,
+                               cfg.rope_theta, cfg.rms_norm_eps)
+                core = cb["core"][:T * cfg.q_dim].view(T, cfg.q_dim)
+                K.attn_prefill(q, qg, self.kv[i], self.block_table, w[pa + "k_descale"], w[pa + "v_descale"], core, T,
+                               Hq, Hkv, D, pos0, cfg.attn_output_gate)
+                self._row_parallel_chunk(self.lin[pa + "o"], core, x, cb)
+            else:
+                pg = p + "gdn."
+                mixed, z, ab = cb["mixed"][:T], cb["z"][:T], cb["ab"][:T]
+                self.lin[pg + "in_proj_qkv"].chunk(h, cb["xh"], mixed)
+                self.lin[pg + "in_proj_z"].chunk(h, cb["xh"], z)
+                K.bf16_gemv(self.ab_w[i], h, out=ab)
+                core = cb["core"][:T * cfg.value_dim].view(T, cfg.value_dim)
+                K.gdn_prefill(mixed, z, ab, w[pg + "conv1d_weight"], w[pg + "A_log"], w[pg + "dt_bias"],
+                              w[pg + "norm_weight"], self.ring[i], self.gdn_state[i], cb["gdn"], core, T, Hv, Hk, Dg,
+                              pos0, cfg.rms_norm_eps)
+                self._row_parallel_chunk(self.lin[pg + "out_proj"], core, x, cb)
+            K.rmsnorm(x, w[p + "post_attention_layernorm"], cfg.rms_norm_eps, out=h)
+            pm = p + "mlp."
+            gu = cb["gate_up"][:T]
+            self.lin[pm + "gate_up"].chunk(h, cb["xh"], gu)
+            self._row_parallel_chunk(self.lin[pm + "down"], gu, x, cb, fused_silu_mul=True)
+        if want_logits:
+            b = self.buf
+            K.rmsnorm(x[T - 1:T], w["text.final_norm"], cfg.rms_norm_eps, out=b.h[:1])
+            self.lin["lm_head"](b.h[:1], out=b.logits[:1])
+            K.argmax_rows(b.logits[:1], cfg.vocab_shard_begin, b.next_ids[:1], b.next_vals[:1], b.argmax_scratch)
+            if self.comm is not None and self.comm.world > 1:
+                self.comm.merge_argmax(b.next_ids[:1], b.next_vals[:1])
+        self.pos += T
+        self.pending_rows = 0
+
+    def _row_parallel_chunk(self, lin: Linear, inp: torch.Tensor, x: torch.Tensor, cb: dict,
+                            fused_silu_mul: bool = False) -> None:
+        if self.comm is None or self.comm.world == 1:
+            lin.chunk(inp, cb["xh"], x, residual=x, fused_silu_mul=fused_silu_mul)
+        else:
+            self.comm.row_parallel_chunk(lin, inp, x, cb, fused_silu_mul)
+
+    def prefill(self, ids: torch.Tensor, chunk: int = 2048) -> int:
+        """Cold or warm prefill of ``ids`` at the current position; returns the greedy next token."""
+        ids = ids.to(torch.int32)
+        n = ids.numel()
+        if n <= MAX_ROWS:
+            return self.prefill_small(ids)
+        if self.pos + n > self.max_ctx:
+            raise ValueError("context overflow")
+        self.commit_pending()
+        cb = self._chunk_buffers(min(chunk, n))
+        s = 0
+        last_small = False
+        while s < n:
+            e = min(n, s + cb["C"])
+            T = e - s
+            if T <= MAX_ROWS:
+                # short tail: the small-batch path logs its rows instead of committing them
+                self.feed(ids[s:e], want_logits=True)
+                last_small = True
+            else:
+                cb["ids"][:T].copy_(ids[s:e].to(self.device), non_blocking=True)
+                cb["positions"][:T].copy_(torch.arange(self.pos, self.pos + T, dtype=torch.int32, device=self.device))
+                self.forward_chunk(T, want_logits=(e == n))
+            s = e
+        K.check_gemm_status(self.device)
+        if last_small:
+            return int(self.buf.next_ids[(n - 1) % cb["C"]].item())
+        return int(self.buf.next_ids[0].item())
 
     def logits_rows(self, T: int) -> torch.Tensor:
         return self.buf.logits[:T]

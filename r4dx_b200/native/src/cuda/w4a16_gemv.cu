@@ -98,6 +98,43 @@ __global__ void Bf16Gemv(const __nv_bfloat16* __restrict__ W, const __nv_bfloat1
   }
 }
 
+// Many-row variant: one CTA stages 8 activation rows in shared memory and its warps sweep the
+// weight rows, so W is read once per 8 tokens instead of once per token.
+__global__ void __launch_bounds__(256) Bf16GemvTiled(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x,
+                                                     float* __restrict__ y, int T, int N, int K) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [8][K]
+  const int t0 = blockIdx.x * 8;
+  for (int i = threadIdx.x; i < 8 * (K / 8); i += 256) {
+    const int tt = i / (K / 8), c = (i % (K / 8)) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t0 + tt < T) v = *reinterpret_cast<const uint4*>(x + static_cast<size_t>(t0 + tt) * K + c);
+    *reinterpret_cast<uint4*>(xs + tt * K + c) = v;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int n = warp; n < N; n += 8) {
+    float acc[8];
+#pragma unroll
+    for (int tt = 0; tt < 8; ++tt) acc[tt] = 0.f;
+    const __nv_bfloat16* w = W + static_cast<size_t>(n) * K;
+    for (int k = lane * 8; k < K; k += 256) {
+      const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w + k));
+#pragma unroll
+      for (int tt = 0; tt < 8; ++tt) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(xs + tt * K + k);
+        acc[tt] += BfLo(wv.x) * BfLo(xv.x) + BfHi(wv.x) * BfHi(xv.x) + BfLo(wv.y) * BfLo(xv.y) + BfHi(wv.y) * BfHi(xv.y) +
+                   BfLo(wv.z) * BfLo(xv.z) + BfHi(wv.z) * BfHi(xv.z) + BfLo(wv.w) * BfLo(xv.w) + BfHi(wv.w) * BfHi(xv.w);
+      }
+    }
+#pragma unroll
+    for (int tt = 0; tt < 8; ++tt) {
+      const float s = WarpSum(acc[tt]);
+      if (lane == 0 && t0 + tt < T) y[static_cast<size_t>(t0 + tt) * N + n] = s;
+    }
+  }
+}
+
 // ---- argmax ------------------------------------------------------------------------------------
 constexpr int kArgParts = 256;
 
@@ -205,6 +242,14 @@ int r4dxb_w4a16_gemv(const void* wq, const void* wsz, const void* x, void* y, in
 
 int r4dxb_bf16_gemv(const void* W, const void* x, float* y, int T, int N, int K, void* stream) {
   if (T < 1 || N < 1 || K % 2) return R4DXB_BAD_ARG;
+  if (T > 8 && K % 8 == 0 && static_cast<size_t>(K) * 16 <= 200 * 1024) {
+    const int smem = K * 16;
+    cudaError_t e = cudaFuncSetAttribute(Bf16GemvTiled, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    Bf16GemvTiled<<<(T + 7) / 8, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(W), static_cast<const __nv_bfloat16*>(x), y, T, N, K);
+    return FinishLaunch();
+  }
   Bf16Gemv<<<N, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(W),
                                                              static_cast<const __nv_bfloat16*>(x), y, T, N, K);
   return FinishLaunch();

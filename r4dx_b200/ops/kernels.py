@@ -288,3 +288,24 @@ def dense_gemm_hadamard(W: torch.Tensor, svh: torch.Tensor, xh: torch.Tensor, tn
     _check(_lib().r4dxb_trellis_gemm(_p(W), _p(svh), _p(xh), _p(out), None, T, N, K_, 0, tn,
                                      _p(gemm_status(xh.device)), _stream()), "dense_gemm")
     return out
+
+
+register_cuda_sig("r4dxb_gdn_prefill", _I, [_P] * 16 + [_I, _I, _I, _I, _I, _F, _P])
+register_cuda_sig("r4dxb_attn_prefill", _I, [_P] * 7 + [_I, _I, _I, _I, _I, _I, _P])
+
+
+def gdn_prefill(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, scratch: dict, out, T: int, H: int, Hk: int,
+                D: int, pos0: int, eps: float = 1e-6):
+    """scratch: dict with fp32 tensors q, k [T,Hk,D]; v, o [T,H,D]; eg, beta [T,H]."""
+    _check(_lib().r4dxb_gdn_prefill(_p(mixed), _p(z), _p(ab), _p(conv_w), _p(A_log), _p(dt_bias), _p(norm_w), _p(ring),
+                                    _p(state), _p(scratch["q"]), _p(scratch["k"]), _p(scratch["v"]), _p(scratch["eg"]),
+                                    _p(scratch["beta"]), _p(scratch["o"]), _p(out), T, H, Hk, D, pos0, eps, _stream()),
+           "gdn_prefill")
+    return out
+
+
+def attn_prefill(q, qg, cache, block_table, k_descale, v_descale, out, T: int, Hq: int, Hkv: int, D: int, pos0: int,
+                 gated: bool = True):
+    _check(_lib().r4dxb_attn_prefill(_p(q), _p(qg), _p(cache), _p(block_table), _p(k_descale), _p(v_descale), _p(out),
+                                     T, Hq, Hkv, D, pos0, 1 if gated else 0, _stream()), "attn_prefill")
+    return out

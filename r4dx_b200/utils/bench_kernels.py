@@ -74,6 +74,26 @@ def main() -> None:
                 gbs = w.nbytes / us / 1e3
                 print(f"trellis_gemv {name:12s} N={N:6d} K={Kd:6d} kb={kb} T={T} ksplit={ks}: {us:8.1f} us  "
                       f"{gbs:7.0f} GB/s  {gbs / peak:5.2f} of measured HBM  {N * Kd / us / 1e6:6.2f} Tweights/s")
+    if a.only in ("trellis_gemm",):
+        Tg = max(a.rows, 16)
+        tf_peak = 1699.0
+        try:
+            tf_peak = float(json.load(open(os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")))["bf16_tflops"])
+        except Exception:
+            pass
+        for name, (N, Kd) in SHAPES_27B.items():
+            if a.shape and a.shape != name:
+                continue
+            for kb in ((a.kb,) if a.kb else (4,)):
+                w = trellis.random_weight(N, Kd, kb, seed=1, device=dev)
+                x = torch.randn(Tg, Kd, device=dev).to(BF)
+                xh = K.trellis_input(x, w.suh)
+                y = torch.empty(Tg, N, dtype=BF, device=dev)
+                us = timed(lambda: K.trellis_gemm(w, xh, out=y), a.iters, flush)
+                K.check_gemm_status(dev)
+                tf = 2.0 * N * Kd * Tg / us / 1e6
+                print(f"trellis_gemm {name:12s} N={N:6d} K={Kd:6d} kb={kb} T={Tg} tn={K.pick_token_tile(Tg)}: {us:9.1f} us  "
+                      f"{tf:7.1f} TFLOP/s  {tf / tf_peak:5.2f} of measured cuBLAS bf16")
     if a.only in ("", "w4a16"):
         N, Kd = 248320, 5120
         w = w4a16.random_weight(N, Kd, 64, device=dev)

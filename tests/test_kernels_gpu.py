@@ -226,3 +226,86 @@ def test_attention_precore_and_decode(K, D, Hq, Hkv, T, ctx):
     o = R.causal_gqa_attention(qf[ctx:].to(BF), kq, vq, ctx)
     o = o * torch.sigmoid(qg_all[ctx:, :, D:].float())
     assert torch.allclose(out.float().cpu().view(T, Hq, D), o, atol=2e-2, rtol=3e-2)
+
+
+def test_bf16_gemv_many_rows(K):
+    g = torch.Generator().manual_seed(5)
+    W = torch.randn(96, 1024, generator=g).to(BF)
+    x = torch.randn(37, 1024, generator=g).to(BF)
+    y = K.bf16_gemv(W.cuda(), x.cuda())
+    assert torch.allclose(y.cpu(), x.float() @ W.float().T, atol=1e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("D,Hv,Hk,T", [(128, 6, 2, 70), (64, 4, 2, 33)])
+def test_gdn_prefill_matches_recurrence_and_hands_over_to_decode(K, D, Hv, Hk, T):
+    g = torch.Generator().manual_seed(D + T)
+    key_dim, conv_dim = Hk * D, 2 * Hk * D + Hv * D
+    n_tok = T + 5
+    mixed = (torch.randn(n_tok, conv_dim, generator=g) * 0.5).to(BF)
+    z = torch.randn(n_tok, Hv * D, generator=g).to(BF)
+    ab = torch.randn(n_tok, 2 * Hv, generator=g)
+    conv_w = (torch.randn(conv_dim, 4, generator=g) * 0.5).to(BF)
+    A_log = torch.randn(Hv, generator=g) * 0.3
+    dt_bias = torch.randn(Hv, generator=g) * 0.3
+    norm_w = (1 + 0.1 * torch.randn(D, generator=g)).to(BF)
+    y, _ = R.causal_conv1d_silu(mixed.float(), conv_w.float(), None)
+    q = R.l2norm(y[:, :key_dim].view(n_tok, Hk, D))
+    k = R.l2norm(y[:, key_dim:2 * key_dim].view(n_tok, Hk, D))
+    v = y[:, 2 * key_dim:].view(n_tok, Hv, D)
+    gg, beta = R.gdn_gates(ab[:, :Hv], ab[:, Hv:], A_log, dt_bias)
+    o, S_ref = R.gdn_recurrent(q, k, v, gg, beta, None)
+    ref = R.gated_rmsnorm(o, z.float().view(n_tok, Hv, D), norm_w.float()).view(n_tok, Hv * D)
+    dev = "cuda"
+    f32 = torch.float32
+    ring = torch.zeros(16, conv_dim, dtype=BF, device=dev)
+    state = torch.zeros(Hv, D, D, device=dev)
+    # two prefill chunks (the second starts mid-ring), then decode rows
+    split = T // 2 + 3
+    out = torch.zeros(n_tok, Hv * D, dtype=BF, device=dev)
+    for s, e in ((0, split), (split, T)):
+        n = e - s
+        sc = dict(q=torch.empty(n, Hk, D, device=dev), k=torch.empty(n, Hk, D, device=dev), v=torch.empty(n, Hv, D, device=dev),
+                  o=torch.empty(n, Hv, D, device=dev), eg=torch.empty(n, Hv, device=dev), beta=torch.empty(n, Hv, device=dev))
+        K.gdn_prefill(mixed[s:e].cuda(), z[s:e].cuda(), ab[s:e].cuda(), conv_w.cuda(), A_log.cuda(), dt_bias.cuda(),
+                      norm_w.cuda(), ring, state, sc, out[s:e], n, Hv, Hk, D, s)
+    log_u = torch.zeros(8, Hv, D, device=dev); log_k = torch.zeros(8, Hv, D, device=dev); log_eg = torch.zeros(8, Hv, device=dev)
+    n_replay = torch.zeros(1, dtype=torch.int32, device=dev)
+    dec = torch.zeros(8, Hv * D, dtype=BF, device=dev)
+    K.gdn_decode(mixed[T:].cuda(), z[T:].cuda(), ab[T:].cuda(), conv_w.cuda(), A_log.cuda(), dt_bias.cuda(), norm_w.cuda(),
+                 ring, state, log_u, log_k, log_eg, torch.arange(T, n_tok, dtype=torch.int32, device=dev), n_replay, dec,
+                 5, Hv, Hk, D)
+    out[T:] = dec[:5]
+    assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("D,Hq,Hkv,T,ctx", [(256, 6, 1, 40, 0), (256, 12, 2, 70, 100), (64, 4, 2, 33, 17), (256, 3, 1, 20, 64)])
+def test_attention_prefill(K, D, Hq, Hkv, T, ctx):
+    g = torch.Generator().manual_seed(ctx + T)
+    dev = "cuda"
+    rd, theta = D // 4, 1e7
+    total = ctx + T
+    nblk = (total + 15) // 16 + 1
+    cache = torch.zeros(nblk, Hkv, 2, 16, D, dtype=torch.uint8, device=dev)
+    table = torch.randperm(nblk, generator=g).to(torch.int32).cuda()
+    qn = (torch.randn(D, generator=g) * 0.1).to(BF)
+    kn = (torch.randn(D, generator=g) * 0.1).to(BF)
+    kds = torch.full((Hkv,), 1 / 8.0)
+    vds = torch.full((Hkv,), 1 / 16.0)
+    qg_all = torch.randn(total, Hq, 2 * D, generator=g).to(BF)
+    k_all = torch.randn(total, Hkv, D, generator=g).to(BF)
+    v_all = torch.randn(total, Hkv, D, generator=g).to(BF)
+    q_out = torch.zeros(total, Hq, D, dtype=BF, device=dev)
+    pos = torch.arange(total, dtype=torch.int32, device=dev)
+    K.attn_precore(qg_all.cuda(), k_all.cuda(), v_all.cuda(), qn.cuda(), kn.cuda(), kds.cuda(), vds.cuda(), pos, table,
+                   q_out, cache, total, Hq, Hkv, D, rd, theta)
+    out = torch.zeros(T, Hq * D, dtype=BF, device=dev)
+    K.attn_prefill(q_out[ctx:].contiguous(), qg_all[ctx:].cuda().contiguous(), cache, table, kds.cuda(), vds.cuda(), out,
+                   T, Hq, Hkv, D, ctx, True)
+    allpos = torch.arange(total)
+    qf = R.rope_partial_neox(R.rmsnorm_1pw(qg_all[..., :D], qn), allpos, rd, theta)
+    kf = R.rope_partial_neox(R.rmsnorm_1pw(k_all, kn), allpos, rd, theta)
+    kq = R.fp8_e4m3_roundtrip(kf, 1 / 8.0)
+    vq = R.fp8_e4m3_roundtrip(v_all.float(), 1 / 16.0)
+    o = R.causal_gqa_attention(qf[ctx:].to(BF), kq, vq, ctx)
+    o = o * torch.sigmoid(qg_all[ctx:, :, D:].float())
+    assert torch.allclose(out.float().cpu().view(T, Hq, D), o, atol=2e-2, rtol=3e-2)
