@@ -220,7 +220,12 @@ def main():
             out["e2e"] = e2e
         print(json.dumps(out))
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing NCCL down: communicators referenced by captured graphs can stall the teardown
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     return 0
 
 

@@ -86,6 +86,16 @@ int r4dxb_gdn_prefill(const void* mixed, const void* z, const float* ab, const v
 int r4dxb_attn_prefill(const void* q, const void* qg, const void* cache, const int* block_table, const float* k_descale,
                        const float* v_descale, void* out, int T, int Hq, int Hkv, int D, int pos0, int gated, void* stream);
 
+/* ---- tensor parallel: collectives issued from inside the compute kernels ------------------------- */
+/* Row-parallel trellis linear (T <= 8) + all-reduce over NVLink peer memory + residual, one kernel.
+ * recv[p] / flags[p]: rank p's receive buffer ([2][world][8][N] fp32) and flag array ([N/128][world] u32),
+ * peer-mapped; block_seq ([N/128] u32) and status (int) are this rank's own.  Every wait is bounded by
+ * spin_limit polls; when one runs out *status becomes 100 + the rank that did not answer. */
+int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                                 const void* residual, int T, int N, int K, int kb, int ksplit, void* const* recv,
+                                 void* const* flags, void* block_seq, int* status, int world, int rank, int spin_limit,
+                                 void* stream);
+
 #ifdef __cplusplus
 }
 #endif

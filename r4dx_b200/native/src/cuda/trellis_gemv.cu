@@ -23,12 +23,37 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
+constexpr int kMaxWorld = 8;
 
-template <int KB, int TMAX>
+// Tensor-parallel epilogue: the all-reduce of a row-parallel linear, issued from the GEMV kernel.
+// Every rank's CTA for block nb pushes its fp32 partial (T x 128) into each peer's receive slot
+// with plain stores over NVLink, releases a per-(block, source) flag at system scope, waits
+// (bounded) for the other ranks' flags of the same block, sums the partials in rank order -- the
+// same order on every rank, so all ranks hold identical bits -- adds the residual and writes bf16.
+// Receive slots are double-buffered by the call parity of a per-block sequence counter that lives
+// in device memory (so a captured graph can be replayed).
+struct TpPush {
+  float* recv[kMaxWorld];          // recv[p]: rank p's receive buffer [2][world][8][N] (peer-mapped)
+  unsigned* flags[kMaxWorld];      // flags[p]: rank p's flags [N/128][world]
+  unsigned* block_seq;             // local [N/128] call counters
+  int* status;                     // local: set non-zero when a wait ran out
+  int world, rank, spin_limit;
+};
+
+__device__ __forceinline__ void StoreReleaseSys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned LoadAcquireSys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <int KB, int TMAX, bool kTp>
 __global__ void __launch_bounds__(kThreads)
 TrellisGemvKernel(const uint32_t* __restrict__ words, const __half* __restrict__ suh, const __half* __restrict__ svh,
                   const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
-                  const __nv_bfloat16* __restrict__ residual, int T, int N, int K, int kblocks_per_cta) {
+                  const __nv_bfloat16* __restrict__ residual, int T, int N, int K, int kblocks_per_cta, TpPush tp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   cg::cluster_group cluster = cg::this_cluster();
   const int ksplit = gridDim.x;
@@ -127,7 +152,11 @@ TrellisGemvKernel(const uint32_t* __restrict__ words, const __half* __restrict__
   }
   cluster.sync();   // every CTA's partial block is complete and visible cluster-wide
   if (krank == 0) {
-    for (int t = warp; t < T; t += kThreads / 32) {
+    const float inv_sqrt = 0.08838834764831845f;
+    float o[4] = {0.f, 0.f, 0.f, 0.f};
+    const int t = warp;              // warp t finishes row t (T <= 8 = warps per CTA)
+    const int n = nb * 128 + lane * 4;
+    if (t < T) {
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       for (int r = 0; r < ksplit; ++r) {       // fixed order: the result does not depend on timing
         const float* rp = cluster.map_shared_rank(part, r);
@@ -135,32 +164,73 @@ TrellisGemvKernel(const uint32_t* __restrict__ words, const __half* __restrict__
         v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
       }
       WarpFwht128(v);
-      const int n = nb * 128 + lane * 4;
       const uint2 sv = *reinterpret_cast<const uint2*>(svh + n);
       const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
-      const float inv_sqrt = 0.08838834764831845f;
-      float o0 = v[0] * inv_sqrt * __low2float(s01), o1 = v[1] * inv_sqrt * __high2float(s01);
-      float o2 = v[2] * inv_sqrt * __low2float(s23), o3 = v[3] * inv_sqrt * __high2float(s23);
+      o[0] = v[0] * inv_sqrt * __low2float(s01); o[1] = v[1] * inv_sqrt * __high2float(s01);
+      o[2] = v[2] * inv_sqrt * __low2float(s23); o[3] = v[3] * inv_sqrt * __high2float(s23);
+    }
+    if constexpr (kTp) {
+      __shared__ unsigned s_seq;
+      __shared__ int s_fail;
+      if (threadIdx.x == 0) { s_seq = tp.block_seq[nb] + 1; s_fail = 0; }
+      __syncthreads();
+      const unsigned seq = s_seq;
+      const size_t slot_elems = static_cast<size_t>(tp.world) * 8 * N;
+      const size_t my_off = (seq & 1) * slot_elems + (static_cast<size_t>(tp.rank) * 8 + t) * N + n;
+      if (t < T) {
+        for (int p = 0; p < tp.world; ++p)
+          if (p != tp.rank) *reinterpret_cast<float4*>(tp.recv[p] + my_off) = make_float4(o[0], o[1], o[2], o[3]);
+        __threadfence_system();
+      }
+      __syncthreads();
+      if (threadIdx.x < tp.world && threadIdx.x != tp.rank) {
+        StoreReleaseSys(tp.flags[threadIdx.x] + nb * tp.world + tp.rank, seq);
+        // wait for the same block from that rank
+        const unsigned* f = tp.flags[tp.rank] + nb * tp.world + threadIdx.x;
+        bool ok = false;
+        for (int i = 0; i < tp.spin_limit; ++i) {
+          if (static_cast<int>(LoadAcquireSys(f) - seq) >= 0) { ok = true; break; }
+          if (i > 64) __nanosleep(64);
+        }
+        if (!ok) { s_fail = 1; atomicExch(tp.status, 100 + static_cast<int>(threadIdx.x)); }
+      }
+      __syncthreads();
+      if (t < T && !s_fail) {
+        float a4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* mine = tp.recv[tp.rank] + (seq & 1) * slot_elems;
+        for (int r = 0; r < tp.world; ++r) {     // rank order, identical on every rank
+          if (r == tp.rank) {
+            a4[0] += o[0]; a4[1] += o[1]; a4[2] += o[2]; a4[3] += o[3];
+          } else {
+            const float4 p = __ldcg(reinterpret_cast<const float4*>(mine + (static_cast<size_t>(r) * 8 + t) * N + n));   // L2, never a stale L1 line
+            a4[0] += p.x; a4[1] += p.y; a4[2] += p.z; a4[3] += p.w;
+          }
+        }
+        o[0] = a4[0]; o[1] = a4[1]; o[2] = a4[2]; o[3] = a4[3];
+      }
+      if (threadIdx.x == 0) tp.block_seq[nb] = seq;
+    }
+    if (t < T) {
       if (residual != nullptr) {
         const uint2 rv = *reinterpret_cast<const uint2*>(residual + static_cast<size_t>(t) * N + n);
-        o0 += BfLo(rv.x); o1 += BfHi(rv.x); o2 += BfLo(rv.y); o3 += BfHi(rv.y);
+        o[0] += BfLo(rv.x); o[1] += BfHi(rv.x); o[2] += BfLo(rv.y); o[3] += BfHi(rv.y);
       }
       uint2 ov;
-      ov.x = PackBf16(o0, o1);
-      ov.y = PackBf16(o2, o3);
+      ov.x = PackBf16(o[0], o[1]);
+      ov.y = PackBf16(o[2], o[3]);
       *reinterpret_cast<uint2*>(y + static_cast<size_t>(t) * N + n) = ov;
     }
   }
   cluster.sync();   // peers keep their shared memory alive until rank 0 has read it
 }
 
-template <int KB, int TMAX>
+template <int KB, int TMAX, bool kTp>
 int Launch(const void* words, const void* suh, const void* svh, const void* x, void* y, const void* residual, int T,
-           int N, int K, int ksplit, cudaStream_t stream) {
+           int N, int K, int ksplit, cudaStream_t stream, const TpPush& tp) {
   const int kblocks = K / 128 / ksplit;
   const size_t smem = static_cast<size_t>(TMAX) * 128 * 4 + static_cast<size_t>(TMAX) * kblocks * 128 * 2;
   if (smem > 200 * 1024) return R4DXB_TOO_LARGE;
-  auto kern = TrellisGemvKernel<KB, TMAX>;
+  auto kern = TrellisGemvKernel<KB, TMAX, kTp>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -180,18 +250,18 @@ int Launch(const void* words, const void* suh, const void* svh, const void* x, v
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<const uint32_t*>(words), static_cast<const __half*>(suh),
                                      static_cast<const __half*>(svh), static_cast<const __nv_bfloat16*>(x),
                                      static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(residual), T, N, K,
-                                     kblocks);
+                                     kblocks, tp);
   ++g_launch_count;
   return static_cast<int>(e);
 }
 
-template <int KB>
+template <int KB, bool kTp>
 int LaunchT(const void* words, const void* suh, const void* svh, const void* x, void* y, const void* residual, int T,
-            int N, int K, int ksplit, cudaStream_t stream) {
-  if (T == 1) return Launch<KB, 1>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream);
-  if (T == 2) return Launch<KB, 2>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream);
-  if (T <= 4) return Launch<KB, 4>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream);
-  return Launch<KB, 8>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream);
+            int N, int K, int ksplit, cudaStream_t stream, const TpPush& tp) {
+  if (T == 1) return Launch<KB, 1, kTp>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream, tp);
+  if (T == 2) return Launch<KB, 2, kTp>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream, tp);
+  if (T <= 4) return Launch<KB, 4, kTp>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream, tp);
+  return Launch<KB, 8, kTp>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream, tp);
 }
 
 }  // namespace
@@ -205,10 +275,40 @@ extern "C" int r4dxb_trellis_gemv(const void* words, const void* suh, const void
   if ((K / 128) % ksplit) return R4DXB_BAD_ARG;
   if (((K / 128 / ksplit) * 8) % kUnroll) return R4DXB_BAD_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  TpPush none = {};
   switch (kb) {
-    case 3: return LaunchT<3>(words, suh, svh, x, y, residual, T, N, K, ksplit, s);
-    case 4: return LaunchT<4>(words, suh, svh, x, y, residual, T, N, K, ksplit, s);
-    case 5: return LaunchT<5>(words, suh, svh, x, y, residual, T, N, K, ksplit, s);
+    case 3: return LaunchT<3, false>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, none);
+    case 4: return LaunchT<4, false>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, none);
+    case 5: return LaunchT<5, false>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, none);
+    default: return R4DXB_BAD_ARG;
+  }
+}
+
+// Row-parallel linear + all-reduce in one kernel (see TpPush).  recv / flags: `world` peer-mapped
+// pointers (index = rank); block_seq, status: this rank's own memory.  spin_limit bounds every wait.
+extern "C" int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                                            const void* residual, int T, int N, int K, int kb, int ksplit,
+                                            void* const* recv, void* const* flags, void* block_seq, int* status,
+                                            int world, int rank, int spin_limit, void* stream) {
+  using namespace r4dxb;
+  if (T < 1 || T > 8 || N % 128 || K % 128 || world < 2 || world > kMaxWorld || rank < 0 || rank >= world) return R4DXB_BAD_ARG;
+  if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8) return R4DXB_BAD_ARG;
+  if ((K / 128) % ksplit) return R4DXB_BAD_ARG;
+  TpPush tp = {};
+  for (int p = 0; p < world; ++p) {
+    tp.recv[p] = static_cast<float*>(recv[p]);
+    tp.flags[p] = static_cast<unsigned*>(flags[p]);
+  }
+  tp.block_seq = static_cast<unsigned*>(block_seq);
+  tp.status = status;
+  tp.world = world;
+  tp.rank = rank;
+  tp.spin_limit = spin_limit;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (kb) {
+    case 3: return LaunchT<3, true>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, tp);
+    case 4: return LaunchT<4, true>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, tp);
+    case 5: return LaunchT<5, true>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, tp);
     default: return R4DXB_BAD_ARG;
   }
 }
