@@ -118,11 +118,12 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(dev))
-        from r4dx_b200.parallel.tp_comm import make_comm
-        comm = make_comm(world, rank, dev)
     native.cuda()
 
     gcfg = qwen_hybrid_27b_config(args.layers) if args.model == "qwen-hybrid-27b" else small_hybrid_config(args.layers)
+    if world > 1:
+        from r4dx_b200.parallel.tp_comm import make_comm
+        comm = make_comm(world, rank, dev, hidden=gcfg.hidden_size)
     cfg = gcfg.shard(world, rank) if world > 1 else gcfg
     total = args.prompt_len + args.warmup * 2 + args.steps * 2 + 64
     w = synthetic_weight_set(cfg, device=dev, seed=0)

@@ -40,10 +40,12 @@ class Linear:
         else:
             self.N, self.K = w.shape
 
-    def __call__(self, x: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                 prologue: int = 0, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6) -> torch.Tensor:
         w = self.w
         if isinstance(w, TrellisWeight):
-            return K.trellis_gemv(w, x, residual=residual, out=out, ksplit=self.ksplit)
+            return K.trellis_gemv(w, x, residual=residual, out=out, ksplit=self.ksplit, prologue=prologue,
+                                  norm_w=norm_w, eps=eps)
         if isinstance(w, W4Weight):
             if residual is not None:
                 raise NotImplementedError("w4a16 with a residual epilogue")
@@ -188,10 +190,10 @@ class HybridModel:
         cfg, b, w = self.cfg, self.buf, self.w
         p = f"text.layers.{i}.gdn."
         Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
-        h = b.h[:T]
-        self.lin[p + "in_proj_qkv"](h, out=b.mixed[:T])
-        self.lin[p + "in_proj_z"](h, out=b.z[:T])
-        K.bf16_gemv(self.ab_w[i], h, out=b.ab[:T])
+        x, nw, eps = b.x[:T], w[f"text.layers.{i}.input_layernorm"], cfg.rms_norm_eps
+        self.lin[p + "in_proj_qkv"](x, out=b.mixed[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+        self.lin[p + "in_proj_z"](x, out=b.z[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+        K.bf16_gemv_norm(self.ab_w[i], x, nw, eps, b.ab[:T])
         K.gdn_decode(b.mixed, b.z, b.ab, w[p + "conv1d_weight"], w[p + "A_log"], w[p + "dt_bias"], w[p + "norm_weight"],
                      self.ring[i], self.gdn_state[i], self.log_u[i], self.log_k[i], self.log_eg[i], b.positions,
                      b.n_replay, b.core, T, Hv, Hk, Dg, cfg.rms_norm_eps)
@@ -202,10 +204,10 @@ class HybridModel:
         cfg, b, w = self.cfg, self.buf, self.w
         p = f"text.layers.{i}.attn."
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-        h = b.h[:T]
-        self.lin[p + "qg"](h, out=b.qg[:T])
-        self.lin[p + "k"](h, out=b.k[:T])
-        self.lin[p + "v"](h, out=b.v[:T])
+        x, nw, eps = b.x[:T], w[f"text.layers.{i}.input_layernorm"], cfg.rms_norm_eps
+        self.lin[p + "qg"](x, out=b.qg[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+        self.lin[p + "k"](x, out=b.k[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+        self.lin[p + "v"](x, out=b.v[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
         K.attn_precore(b.qg, b.k, b.v, w[p + "q_norm"], w[p + "k_norm"], w[p + "k_descale"], w[p + "v_descale"],
                        b.positions, self.block_table, b.q, self.kv[i], T, Hq, Hkv, D, cfg.rotary_dim,
                        cfg.rope_theta, cfg.rms_norm_eps)
@@ -215,19 +217,19 @@ class HybridModel:
         self._row_parallel(self.lin[p + "o"], core, T)
 
     def _mlp(self, i: int, T: int) -> None:
-        cfg, b = self.cfg, self.buf
+        cfg, b, w = self.cfg, self.buf, self.w
         p = f"text.layers.{i}.mlp."
-        self.lin[p + "gate_up"](b.h[:T], out=b.gate_up[:T])
-        K.silu_mul(b.gate_up[:T], out=b.act[:T])
-        self._row_parallel(self.lin[p + "down"], b.act[:T], T)
+        self.lin[p + "gate_up"](b.x[:T], out=b.gate_up[:T], prologue=K.PRO_RMSNORM,
+                                norm_w=w[f"text.layers.{i}.post_attention_layernorm"], eps=cfg.rms_norm_eps)
+        self._row_parallel(self.lin[p + "down"], b.gate_up[:T], T, prologue=K.PRO_SILU_MUL)
 
-    def _row_parallel(self, lin: Linear, x: torch.Tensor, T: int) -> None:
+    def _row_parallel(self, lin: Linear, x: torch.Tensor, T: int, prologue: int = 0) -> None:
         """Row-parallel linear whose result is added to the residual stream ``buf.x``."""
         b = self.buf
         if self.comm is None or self.comm.world == 1:
-            lin(x, out=b.x[:T], residual=b.x[:T])
+            lin(x, out=b.x[:T], residual=b.x[:T], prologue=prologue)
         else:
-            self.comm.row_parallel_linear(lin, x, b.x[:T])
+            self.comm.row_parallel_linear(lin, x, b.x[:T], prologue)
 
     # ---- forward --------------------------------------------------------------------------------
     def forward_rows(self, T: int, want_logits: bool = True) -> None:
@@ -235,13 +237,11 @@ class HybridModel:
         cfg, b, w = self.cfg, self.buf, self.w
         K.embed_gather(b.ids[:T], w["text.embed_tokens"], out=b.x[:T])
         for i in range(cfg.num_hidden_layers):
-            p = f"text.layers.{i}."
-            K.rmsnorm(b.x[:T], w[p + "input_layernorm"], cfg.rms_norm_eps, out=b.h[:T])
+            # the two RMSNorms and the SwiGLU of a layer run inside the prologues of the linears
             if cfg.is_attention_layer(i):
                 self._attn_layer(i, T)
             else:
                 self._gdn_layer(i, T)
-            K.rmsnorm(b.x[:T], w[p + "post_attention_layernorm"], cfg.rms_norm_eps, out=b.h[:T])
             self._mlp(i, T)
         if want_logits:
             K.rmsnorm(b.x[:T], w["text.final_norm"], cfg.rms_norm_eps, out=b.h[:T])

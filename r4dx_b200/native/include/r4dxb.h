@@ -41,6 +41,9 @@ int r4dxb_w4a16_gemv(const void* wq, const void* wsz, const void* x, void* y, in
                      int out_f32, void* stream);
 /* y[T,N] (fp32) = x[T,K] (bf16) . W[N,K]^T (bf16): small dense projections (gates, router) */
 int r4dxb_bf16_gemv(const void* W, const void* x, float* y, int T, int N, int K, void* stream);
+/* same for T <= 8 rows of the residual stream with the zero-centred RMSNorm folded in */
+int r4dxb_bf16_gemv_norm(const void* W, const void* x, const void* norm_w, float eps, float* y, int T, int N, int K,
+                         void* stream);
 
 /* ---- sampling ------------------------------------------------------------------------------- */
 /* row-wise argmax with ties to the lowest index; writes id + id_offset (int32) and the max (f32).
@@ -86,14 +89,21 @@ int r4dxb_gdn_prefill(const void* mixed, const void* z, const float* ab, const v
 int r4dxb_attn_prefill(const void* q, const void* qg, const void* cache, const int* block_table, const float* k_descale,
                        const float* v_descale, void* out, int T, int Hq, int Hkv, int D, int pos0, int gated, void* stream);
 
+/* Same kernel with a fused activation producer: prologue 0 = x is the activation [T,K];
+ * 1 = x is the residual stream and the activation is RMSNorm(x) with zero-centred weight norm_w;
+ * 2 = x is fused [gate | up] rows [T,2K] and the activation is bf16(silu(gate) * up). */
+int r4dxb_trellis_gemv_ex(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                          const void* residual, const void* norm_w, float eps, int prologue, int T, int N, int K, int kb,
+                          int ksplit, void* stream);
+
 /* ---- tensor parallel: collectives issued from inside the compute kernels ------------------------- */
 /* Row-parallel trellis linear (T <= 8) + all-reduce over NVLink peer memory + residual, one kernel.
- * recv[p] / flags[p]: rank p's receive buffer ([2][world][8][N] fp32) and flag array ([N/128][world] u32),
- * peer-mapped; block_seq ([N/128] u32) and status (int) are this rank's own.  Every wait is bounded by
- * spin_limit polls; when one runs out *status becomes 100 + the rank that did not answer. */
+ * recv[p]: rank p's receive buffer, [2][world][8][N] (fp32 value, u32 sequence) pairs, zero-initialised and
+ * peer-mapped; block_seq ([N/128] u32, zeros) and status (int) are this rank's own.  Every wait is bounded
+ * by spin_limit polls; when one runs out *status becomes 100 + the rank that did not answer. */
 int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void* svh, const void* x, void* y,
-                                 const void* residual, int T, int N, int K, int kb, int ksplit, void* const* recv,
-                                 void* const* flags, void* block_seq, int* status, int world, int rank, int spin_limit,
+                                 const void* residual, int prologue, int T, int N, int K, int kb, int ksplit,
+                                 void* const* recv, void* block_seq, int* status, int world, int rank, int spin_limit,
                                  void* stream);
 
 #ifdef __cplusplus

@@ -1,19 +1,33 @@
 // Trellis-decode weight-streaming GEMM for T <= 8 activation rows (decode and speculative verify).
 //
-//   y[t, n] = bf16( svh[n] * H128( sum_k Q[n, k] * xh[t, k] )[n] ) (+ residual[t, n])
-//   xh = fp16( H128(suh (.) x) )
+//   y[t, n] = bf16( svh[n] * H128( sum_k Q[n, k] * xh[t, k] )[n] (+ residual[t, n]) )
+//   xh = fp16( H128(suh (.) act(x)) )
 //
-// One CTA owns a 128-row block of N (the span of one output Hadamard) and a K slice; `ksplit`
-// CTAs of one thread-block cluster share a row block and are reduced through distributed shared
-// memory in rank order (deterministic, no atomics, no global scratch).  Warp j of the CTA streams
-// n-tile j (16 rows): every lane decodes 8 consecutive K codes of one row per tile and multiplies
-// them with the staged activations.  The input Hadamard runs in the prologue from global x, the
-// output Hadamard + svh + residual in the epilogue, so a layer's linear is a single launch.
+// One CTA owns a 128-row block of N (the span of one output Hadamard) and a K slice; `ksplit` CTAs of
+// one thread-block cluster share a row block and are reduced through distributed shared memory in
+// rank order (deterministic, no atomics, no global scratch).
 //
-// The reference engine splits this over an input-transform kernel and a WMMA GEMM with a
-// ticket-based split-K finish (reference: third_party/libr4d/r4d_gemm_trellis_nt_m64.hip:30-90,216).
+// Weight stream: a producer warp moves the CTA's packed words global -> shared with bulk async
+// copies (one 128-K stage = 8 k-tiles x 8 n-tiles, a single contiguous run thanks to the
+// [N/128][K/16][8][words] order) through a ring of mbarrier-guarded stages, so the whole slice of a
+// small matrix is in flight at once and a large one keeps tens of KB per SM in flight without
+// spending registers.  Eight consumer warps (warp j = n-tile j) decode from shared memory: every
+// lane turns 8 consecutive K codes of one row into fp16 and multiplies them with the staged
+// activations.
+//
+// Prologue modes fold the producer of the activations into this kernel:
+//   0  x is the activation                       [T, K]
+//   1  x is the residual stream, act = RMSNorm   x * rsqrt(mean x^2 + eps) * (1 + w), rounded to bf16
+//   2  x is fused [gate | up] rows [T, 2K], act = bf16(silu(gate) * up)
+// so a decoder layer needs no separate norm / SwiGLU launches.
+//
+// The tensor-parallel variant finishes a row-parallel linear with the all-reduce inside the kernel
+// (see TpPush).  The reference engine uses an input-transform kernel + a WMMA GEMM with a ticket-based
+// split-K finish + a host-mailbox all-reduce kernel for the same job
+// (reference: third_party/libr4d/r4d_gemm_trellis_nt_m64.hip:30-90,216; src/kernels/src/r4dx_tp_kernels.hip:235-311).
 #include <cooperative_groups.h>
 
+#include "sm100_ptx.cuh"
 #include "trellis_decode.cuh"
 
 namespace cg = cooperative_groups;
@@ -21,66 +35,131 @@ namespace cg = cooperative_groups;
 namespace r4dxb {
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kUnroll = 4;
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxWorld = 8;
 
-// Tensor-parallel epilogue: the all-reduce of a row-parallel linear, issued from the GEMV kernel.
-// Every rank's CTA for block nb pushes its fp32 partial (T x 128) into each peer's receive slot
-// with plain stores over NVLink, releases a per-(block, source) flag at system scope, waits
-// (bounded) for the other ranks' flags of the same block, sums the partials in rank order -- the
-// same order on every rank, so all ranks hold identical bits -- adds the residual and writes bf16.
-// Receive slots are double-buffered by the call parity of a per-block sequence counter that lives
-// in device memory (so a captured graph can be replayed).
+// Tensor-parallel epilogue: all-reduce by one-shot push over NVLink peer memory.  Each value travels
+// as an 8-byte (fp32 value, sequence number) pair, so data and "ready" flag arrive in one store and
+// no fence or separate flag round is needed; the receiver polls the pairs it needs (bounded).  Every
+// rank sums the world's partials in rank order, so all ranks hold identical bits.  Receive slots are
+// double-buffered by the parity of a per-block call counter kept in device memory (a captured graph
+// can be replayed).
 struct TpPush {
-  float* recv[kMaxWorld];          // recv[p]: rank p's receive buffer [2][world][8][N] (peer-mapped)
-  unsigned* flags[kMaxWorld];      // flags[p]: rank p's flags [N/128][world]
+  float2* recv[kMaxWorld];         // recv[p]: rank p's buffer [2][world][8][N] of (value, seq) pairs, peer-mapped
   unsigned* block_seq;             // local [N/128] call counters
-  int* status;                     // local: set non-zero when a wait ran out
+  int* status;                     // local: set to 100 + rank when that rank did not answer in time
   int world, rank, spin_limit;
 };
 
-__device__ __forceinline__ void StoreReleaseSys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned LoadAcquireSys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
+struct GemvArgs {
+  const uint32_t* words;
+  const __half* suh;
+  const __half* svh;
+  const __nv_bfloat16* x;
+  __nv_bfloat16* y;
+  const __nv_bfloat16* residual;
+  const __nv_bfloat16* norm_w;     // prologue mode 1
+  float eps;
+  int T, N, K, kblocks_per_cta, stages;
+};
 
-template <int KB, int TMAX, bool kTp>
+template <int KB, int TMAX, int PRO, bool kTp>
 __global__ void __launch_bounds__(kThreads)
-TrellisGemvKernel(const uint32_t* __restrict__ words, const __half* __restrict__ suh, const __half* __restrict__ svh,
-                  const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
-                  const __nv_bfloat16* __restrict__ residual, int T, int N, int K, int kblocks_per_cta, TpPush tp) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+TrellisGemvKernel(GemvArgs a, TpPush tp) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   cg::cluster_group cluster = cg::this_cluster();
   const int ksplit = gridDim.x;
   const int krank = blockIdx.x;            // == rank inside the cluster
   const int nb = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int kslice = kblocks_per_cta * 128;
+  const int kslice = a.kblocks_per_cta * 128;
   const int k_begin = krank * kslice;
+  const int T = a.T, N = a.N, K = a.K;
+  constexpr int NW = 8 * KB;
+  constexpr int kStageBytes = 8 * 8 * NW * 4;     // 8 k-tiles x 8 n-tiles
 
-  float* part = reinterpret_cast<float*>(smem_raw);                       // [TMAX][128]
-  __half* xs = reinterpret_cast<__half*>(smem_raw + TMAX * 128 * 4);       // [TMAX][kslice]
+  float* part = reinterpret_cast<float*>(smem_raw);                                  // [ksplit][TMAX][128] (used on cluster rank 0)
+  float* rnorm = part + ksplit * TMAX * 128;                                          // [8] per-row rsqrt
+  uint64_t* full = reinterpret_cast<uint64_t*>(rnorm + 8);                            // [8]
+  uint64_t* empty = full + 8;                                                         // [8]
+  uint64_t* red_bar = empty + 8;                                                      // [1] split-K partials have landed
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(red_bar + 1);
+  __half* xs = reinterpret_cast<__half*>(smem_raw + ksplit * TMAX * 128 * 4 + 32 + 128 + 16);   // [TMAX][kslice]
+  unsigned char* wst = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(xs + static_cast<size_t>(TMAX) * kslice) + 127) & ~uintptr_t(127));   // [stages][kStageBytes]
 
-  // ---- prologue: xs = fp16(H128(suh * x)) for this CTA's K slice -------------------------------
-  {
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      ptx::MbarInit(&full[s], 1);
+      ptx::MbarInit(&empty[s], kConsumerWarps);
+    }
+    ptx::MbarInit(red_bar, ksplit * kConsumerWarps);
+    *abort_flag = 0;
+    ptx::MbarFenceInit();
+  }
+  __syncthreads();
+  // Cluster rendezvous, split in two: arrive now, wait only just before the first remote write, so
+  // the weight stream and the prologue overlap with it.  It guarantees that rank 0's reduction
+  // barrier is initialised before any peer CTA touches it.
+  if (ksplit > 1) asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer: stream this CTA's words through the stage ring ----------------
+    if (lane == 0) {
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(a.words) +
+                                 (static_cast<size_t>(nb) * (K / 128) + static_cast<size_t>(krank) * a.kblocks_per_cta) * kStageBytes;
+      for (int it = 0; it < a.kblocks_per_cta; ++it) {
+        const int s = it % a.stages, round = it / a.stages;
+        if (!ptx::MbarWait(&empty[s], (round & 1) ^ 1, abort_flag, 1)) break;
+        ptx::MbarArriveExpectTx(&full[s], kStageBytes);
+        ptx::BulkLoad(wst + static_cast<size_t>(s) * kStageBytes, src + static_cast<size_t>(it) * kStageBytes, kStageBytes, &full[s]);
+      }
+    }
+  } else {
+    // ---------------- prologue (consumer warps): xs = fp16(H128(suh * act(x))) for this K slice ----------------
+    if constexpr (PRO == 1) {
+      // RMSNorm statistics need the whole row, not just this CTA's slice: warp t reduces row t
+      if (warp < T) {
+        const __nv_bfloat16* row = a.x + static_cast<size_t>(warp) * K;
+        float ss = 0.f;
+        for (int k = lane * 8; k < K; k += 256) {
+          const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+          ss += BfLo(v.x) * BfLo(v.x) + BfHi(v.x) * BfHi(v.x) + BfLo(v.y) * BfLo(v.y) + BfHi(v.y) * BfHi(v.y) +
+                BfLo(v.z) * BfLo(v.z) + BfHi(v.z) * BfHi(v.z) + BfLo(v.w) * BfLo(v.w) + BfHi(v.w) * BfHi(v.w);
+        }
+        ss = WarpSum(ss);
+        if (lane == 0) rnorm[warp] = rsqrtf(ss / K + a.eps);
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+    }
     const float inv_sqrt = 0.08838834764831845f;   // 1 / sqrt(128)
-    for (int item = warp; item < kblocks_per_cta * TMAX; item += kThreads / 32) {
-      const int t = item / kblocks_per_cta, b = item % kblocks_per_cta;
+    for (int item = warp; item < a.kblocks_per_cta * TMAX; item += kConsumerWarps) {
+      const int t = item / a.kblocks_per_cta, b = item % a.kblocks_per_cta;
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       const int k = k_begin + b * 128 + lane * 4;
       if (t < T) {
-        const uint2 xv = *reinterpret_cast<const uint2*>(x + static_cast<size_t>(t) * K + k);
-        const uint2 sv = *reinterpret_cast<const uint2*>(suh + k);
+        if constexpr (PRO == 2) {
+          const uint2 g = *reinterpret_cast<const uint2*>(a.x + static_cast<size_t>(t) * 2 * K + k);
+          const uint2 u = *reinterpret_cast<const uint2*>(a.x + static_cast<size_t>(t) * 2 * K + K + k);
+          const uint32_t p01 = PackBf16(Silu(BfLo(g.x)) * BfLo(u.x), Silu(BfHi(g.x)) * BfHi(u.x));
+          const uint32_t p23 = PackBf16(Silu(BfLo(g.y)) * BfLo(u.y), Silu(BfHi(g.y)) * BfHi(u.y));
+          v[0] = BfLo(p01); v[1] = BfHi(p01); v[2] = BfLo(p23); v[3] = BfHi(p23);
+        } else {
+          const uint2 xv = *reinterpret_cast<const uint2*>(a.x + static_cast<size_t>(t) * K + k);
+          v[0] = BfLo(xv.x); v[1] = BfHi(xv.x); v[2] = BfLo(xv.y); v[3] = BfHi(xv.y);
+          if constexpr (PRO == 1) {
+            const uint2 wv = *reinterpret_cast<const uint2*>(a.norm_w + k);
+            const float r = rnorm[t];
+            // same rounding point as the standalone norm kernel: the normalised row is a bf16 tensor
+            const uint32_t p01 = PackBf16(v[0] * r * (1.f + BfLo(wv.x)), v[1] * r * (1.f + BfHi(wv.x)));
+            const uint32_t p23 = PackBf16(v[2] * r * (1.f + BfLo(wv.y)), v[3] * r * (1.f + BfHi(wv.y)));
+            v[0] = BfLo(p01); v[1] = BfHi(p01); v[2] = BfLo(p23); v[3] = BfHi(p23);
+          }
+        }
+        const uint2 sv = *reinterpret_cast<const uint2*>(a.suh + k);
         const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
-        v[0] = BfLo(xv.x) * __low2float(s01);
-        v[1] = BfHi(xv.x) * __high2float(s01);
-        v[2] = BfLo(xv.y) * __low2float(s23);
-        v[3] = BfHi(xv.y) * __high2float(s23);
+        v[0] *= __low2float(s01); v[1] *= __high2float(s01); v[2] *= __low2float(s23); v[3] *= __high2float(s23);
       }
       WarpFwht128(v);
       __half2 o01 = __floats2half2_rn(v[0] * inv_sqrt, v[1] * inv_sqrt);
@@ -90,153 +169,176 @@ TrellisGemvKernel(const uint32_t* __restrict__ words, const __half* __restrict__
       ov.y = *reinterpret_cast<uint32_t*>(&o23);
       *reinterpret_cast<uint2*>(xs + static_cast<size_t>(t) * kslice + b * 128 + lane * 4) = ov;
     }
-  }
-  __syncthreads();
+    asm volatile("bar.sync 1, 256;" ::: "memory");
 
-  // ---- main loop: warp = n-tile, lane = (row, k half) ------------------------------------------
-  constexpr int NW = 8 * KB;
-  TrellisLane<KB> tl;
-  tl.Init(lane);
-  const int tiles_k = K / 16;
-  const int kt_begin = k_begin / 16, kt_count = kslice / 16;
-  // tile (nb, tk, warp) starts at ((nb * tiles_k + tk) * 8 + warp) * NW
-  const uint32_t* wp = words + (static_cast<size_t>(nb) * tiles_k + kt_begin) * 8 * NW + warp * NW;
-  constexpr size_t kTileStride = 8 * NW;   // words between consecutive k-tiles of the same n-tile
-
-  float acc[TMAX];
+    // ---------------- main loop: warp = n-tile, lane = (row, k half) ----------------
+    TrellisLane<KB> tl;
+    tl.Init(lane);
+    float acc[TMAX];
 #pragma unroll
-  for (int t = 0; t < TMAX; ++t) acc[t] = 0.f;
-
-  uint32_t cur[kUnroll][3], nxt[kUnroll][3];
-  auto load = [&](uint32_t (&dst)[kUnroll][3], int kt) {
+    for (int t = 0; t < TMAX; ++t) acc[t] = 0.f;
+    const int khalf = (lane & 1) * 8;
+    bool ok = true;
+    for (int it = 0; it < a.kblocks_per_cta && ok; ++it) {
+      const int s = it % a.stages, round = it / a.stages;
+      ok = ptx::MbarWait(&full[s], round & 1, abort_flag, 2);
+      if (!ok) break;
+      const uint32_t* sw = reinterpret_cast<const uint32_t*>(wst + static_cast<size_t>(s) * kStageBytes) + warp * NW;
+      __half2 hacc[TMAX];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const uint32_t* p = wp + static_cast<size_t>(kt + u) * kTileStride;
-      dst[u][0] = __ldg(p + tl.i0);
-      dst[u][1] = __ldg(p + tl.i1);
-      if constexpr (KB != 4) dst[u][2] = __ldg(p + tl.i2); else dst[u][2] = 0;
+      for (int t = 0; t < TMAX; ++t) hacc[t] = __float2half2_rn(0.f);
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) {
+        const uint32_t* tw = sw + kt * 8 * NW;
+        uint32_t hi, lo;
+        tl.Window(tw[tl.i0], tw[tl.i1], (KB == 4) ? 0u : tw[tl.i2], hi, lo);
+        __half2 w[4];
+        TrellisDecode8<KB>(hi, lo, w);
+        const int kk = it * 128 + kt * 16 + khalf;
+#pragma unroll
+        for (int t = 0; t < TMAX; ++t) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xs + static_cast<size_t>(t) * kslice + kk);
+          __half2 h = __hfma2(w[0], *reinterpret_cast<const __half2*>(&xv.x), hacc[t]);
+          h = __hfma2(w[1], *reinterpret_cast<const __half2*>(&xv.y), h);
+          h = __hfma2(w[2], *reinterpret_cast<const __half2*>(&xv.z), h);
+          hacc[t] = __hfma2(w[3], *reinterpret_cast<const __half2*>(&xv.w), h);
+        }
+        if (kt == 3 || kt == 7) {       // fold the fp16 partials into fp32 every 32 products per half
+#pragma unroll
+          for (int t = 0; t < TMAX; ++t) {
+            acc[t] += __low2float(hacc[t]) + __high2float(hacc[t]);
+            hacc[t] = __float2half2_rn(0.f);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::MbarArrive(&empty[s]);
     }
-  };
-  load(cur, 0);
-  const int khalf = (lane & 1) * 8;
-  for (int kt = 0; kt < kt_count; kt += kUnroll) {
-    if (kt + kUnroll < kt_count) load(nxt, kt + kUnroll);
+    // hand the partial rows to cluster rank 0: distributed-shared-memory stores + one remote
+    // mbarrier arrival per warp; only rank 0 waits, the other CTAs are done
+    __syncwarp();
+    if (ksplit > 1) asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+    float* dst = ksplit > 1 ? cluster.map_shared_rank(part, 0) : part;
+    dst += krank * TMAX * 128;
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      uint32_t hi, lo;
-      tl.Window(cur[u][0], cur[u][1], cur[u][2], hi, lo);
-      __half2 w[4];
-      TrellisDecode8<KB>(hi, lo, w);
-      const int kk = (kt + u) * 16 + khalf;
-#pragma unroll
-      for (int t = 0; t < TMAX; ++t) {
-        const uint4 xv = *reinterpret_cast<const uint4*>(xs + static_cast<size_t>(t) * kslice + kk);
-        __half2 s = __hmul2(w[0], *reinterpret_cast<const __half2*>(&xv.x));
-        s = __hfma2(w[1], *reinterpret_cast<const __half2*>(&xv.y), s);
-        s = __hfma2(w[2], *reinterpret_cast<const __half2*>(&xv.z), s);
-        s = __hfma2(w[3], *reinterpret_cast<const __half2*>(&xv.w), s);
-        acc[t] += __low2float(s) + __high2float(s);
+    for (int t = 0; t < TMAX; ++t) {
+      acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], 1);
+      if ((lane & 1) == 0) dst[t * 128 + warp * 16 + (lane >> 1)] = acc[t];
+    }
+    __syncwarp();
+    if (lane == 0) {
+      uint32_t remote_bar;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(ptx::SmemAddr(red_bar)), "r"(0));
+      asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+    }
+  }
+  if (warp == kConsumerWarps) {
+    // lane 0 may still be feeding the ring while the other lanes are already here: reconverge first,
+    // and use the per-thread (non-.aligned) form of the barrier
+    __syncwarp();
+    if (ksplit > 1) asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+  }
+
+  // ---------------- epilogue (cluster rank 0) ----------------
+  if (krank == 0 && warp < kConsumerWarps) {
+    {
+      // wait (bounded) until every consumer warp of every CTA of the cluster has delivered its partial rows
+      bool landed = false;
+      for (int i = 0; i < ptx::kSpinLimit && !landed; ++i) {
+        uint32_t okw;
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+            : "=r"(okw) : "r"(ptx::SmemAddr(red_bar)), "r"(0) : "memory");
+        landed = okw != 0;
       }
     }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      cur[u][0] = nxt[u][0]; cur[u][1] = nxt[u][1]; cur[u][2] = nxt[u][2];
-    }
-  }
-
-  // ---- epilogue ---------------------------------------------------------------------------------
-#pragma unroll
-  for (int t = 0; t < TMAX; ++t) {
-    acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], 1);
-    if ((lane & 1) == 0) part[t * 128 + warp * 16 + (lane >> 1)] = acc[t];
-  }
-  cluster.sync();   // every CTA's partial block is complete and visible cluster-wide
-  if (krank == 0) {
     const float inv_sqrt = 0.08838834764831845f;
     float o[4] = {0.f, 0.f, 0.f, 0.f};
-    const int t = warp;              // warp t finishes row t (T <= 8 = warps per CTA)
+    const int t = warp;              // warp t finishes row t (T <= 8 = consumer warps)
     const int n = nb * 128 + lane * 4;
     if (t < T) {
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       for (int r = 0; r < ksplit; ++r) {       // fixed order: the result does not depend on timing
-        const float* rp = cluster.map_shared_rank(part, r);
-        const float4 p = *reinterpret_cast<const float4*>(rp + t * 128 + lane * 4);
+        const float4 p = *reinterpret_cast<const float4*>(part + (r * TMAX + t) * 128 + lane * 4);
         v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
       }
       WarpFwht128(v);
-      const uint2 sv = *reinterpret_cast<const uint2*>(svh + n);
+      const uint2 sv = *reinterpret_cast<const uint2*>(a.svh + n);
       const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
       o[0] = v[0] * inv_sqrt * __low2float(s01); o[1] = v[1] * inv_sqrt * __high2float(s01);
       o[2] = v[2] * inv_sqrt * __low2float(s23); o[3] = v[3] * inv_sqrt * __high2float(s23);
     }
     if constexpr (kTp) {
-      __shared__ unsigned s_seq;
-      __shared__ int s_fail;
-      if (threadIdx.x == 0) { s_seq = tp.block_seq[nb] + 1; s_fail = 0; }
-      __syncthreads();
-      const unsigned seq = s_seq;
-      const size_t slot_elems = static_cast<size_t>(tp.world) * 8 * N;
-      const size_t my_off = (seq & 1) * slot_elems + (static_cast<size_t>(tp.rank) * 8 + t) * N + n;
+      const unsigned seq = tp.block_seq[nb] + 1;     // written only by this CTA, after the barrier below
+      const size_t slot_pairs = static_cast<size_t>(tp.world) * 8 * N;
       if (t < T) {
-        for (int p = 0; p < tp.world; ++p)
-          if (p != tp.rank) *reinterpret_cast<float4*>(tp.recv[p] + my_off) = make_float4(o[0], o[1], o[2], o[3]);
-        __threadfence_system();
-      }
-      __syncthreads();
-      if (threadIdx.x < tp.world && threadIdx.x != tp.rank) {
-        StoreReleaseSys(tp.flags[threadIdx.x] + nb * tp.world + tp.rank, seq);
-        // wait for the same block from that rank
-        const unsigned* f = tp.flags[tp.rank] + nb * tp.world + threadIdx.x;
-        bool ok = false;
-        for (int i = 0; i < tp.spin_limit; ++i) {
-          if (static_cast<int>(LoadAcquireSys(f) - seq) >= 0) { ok = true; break; }
-          if (i > 64) __nanosleep(64);
+        const size_t my_off = (seq & 1) * slot_pairs + (static_cast<size_t>(tp.rank) * 8 + t) * N + n;
+        const float fs = __uint_as_float(seq);
+        for (int p = 0; p < tp.world; ++p) {
+          if (p == tp.rank) continue;
+          float4* dst = reinterpret_cast<float4*>(tp.recv[p] + my_off);
+          dst[0] = make_float4(o[0], fs, o[1], fs);
+          dst[1] = make_float4(o[2], fs, o[3], fs);
         }
-        if (!ok) { s_fail = 1; atomicExch(tp.status, 100 + static_cast<int>(threadIdx.x)); }
-      }
-      __syncthreads();
-      if (t < T && !s_fail) {
         float a4[4] = {0.f, 0.f, 0.f, 0.f};
-        const float* mine = tp.recv[tp.rank] + (seq & 1) * slot_elems;
+        const float2* mine = tp.recv[tp.rank] + (seq & 1) * slot_pairs;
+        bool fail = false;
         for (int r = 0; r < tp.world; ++r) {     // rank order, identical on every rank
           if (r == tp.rank) {
             a4[0] += o[0]; a4[1] += o[1]; a4[2] += o[2]; a4[3] += o[3];
-          } else {
-            const float4 p = __ldcg(reinterpret_cast<const float4*>(mine + (static_cast<size_t>(r) * 8 + t) * N + n));   // L2, never a stale L1 line
-            a4[0] += p.x; a4[1] += p.y; a4[2] += p.z; a4[3] += p.w;
+            continue;
           }
+          const float4* src = reinterpret_cast<const float4*>(mine + (static_cast<size_t>(r) * 8 + t) * N + n);
+          float4 p0, p1;
+          bool got = false;
+          for (int i = 0; i < tp.spin_limit; ++i) {
+            p0 = __ldcv(src);
+            p1 = __ldcv(src + 1);
+            if (__float_as_uint(p0.y) == seq && __float_as_uint(p0.w) == seq && __float_as_uint(p1.y) == seq &&
+                __float_as_uint(p1.w) == seq) { got = true; break; }
+            if (i > 256) __nanosleep(32);
+          }
+          if (!got) { fail = true; atomicExch(tp.status, 100 + r); break; }
+          a4[0] += p0.x; a4[1] += p0.z; a4[2] += p1.x; a4[3] += p1.z;
         }
-        o[0] = a4[0]; o[1] = a4[1]; o[2] = a4[2]; o[3] = a4[3];
+        if (!fail) { o[0] = a4[0]; o[1] = a4[1]; o[2] = a4[2]; o[3] = a4[3]; }
       }
+      asm volatile("bar.sync 2, 256;" ::: "memory");
       if (threadIdx.x == 0) tp.block_seq[nb] = seq;
     }
     if (t < T) {
-      if (residual != nullptr) {
-        const uint2 rv = *reinterpret_cast<const uint2*>(residual + static_cast<size_t>(t) * N + n);
+      if (a.residual != nullptr) {
+        const uint2 rv = *reinterpret_cast<const uint2*>(a.residual + static_cast<size_t>(t) * N + n);
         o[0] += BfLo(rv.x); o[1] += BfHi(rv.x); o[2] += BfLo(rv.y); o[3] += BfHi(rv.y);
       }
       uint2 ov;
       ov.x = PackBf16(o[0], o[1]);
       ov.y = PackBf16(o[2], o[3]);
-      *reinterpret_cast<uint2*>(y + static_cast<size_t>(t) * N + n) = ov;
+      *reinterpret_cast<uint2*>(a.y + static_cast<size_t>(t) * N + n) = ov;
     }
   }
-  cluster.sync();   // peers keep their shared memory alive until rank 0 has read it
 }
 
-template <int KB, int TMAX, bool kTp>
-int Launch(const void* words, const void* suh, const void* svh, const void* x, void* y, const void* residual, int T,
-           int N, int K, int ksplit, cudaStream_t stream, const TpPush& tp) {
-  const int kblocks = K / 128 / ksplit;
-  const size_t smem = static_cast<size_t>(TMAX) * 128 * 4 + static_cast<size_t>(TMAX) * kblocks * 128 * 2;
-  if (smem > 200 * 1024) return R4DXB_TOO_LARGE;
-  auto kern = TrellisGemvKernel<KB, TMAX, kTp>;
+size_t SmemBytes(int tmax, int kslice, int stages, int kb, int ksplit) {
+  return static_cast<size_t>(ksplit) * tmax * 128 * 4 + 32 + 128 + 16 + static_cast<size_t>(tmax) * kslice * 2 + 128 +
+         static_cast<size_t>(stages) * 8 * 8 * 8 * kb * 4;
+}
+
+template <int KB, int TMAX, int PRO, bool kTp>
+int Launch(GemvArgs a, int ksplit, cudaStream_t stream, const TpPush& tp) {
+  a.kblocks_per_cta = a.K / 128 / ksplit;
+  const int kslice = a.kblocks_per_cta * 128;
+  // ring depth: everything in flight for short slices, otherwise up to 6 stages (48-60 KiB)
+  a.stages = a.kblocks_per_cta < 6 ? a.kblocks_per_cta : 6;
+  const size_t smem = SmemBytes(TMAX, kslice, a.stages, KB, ksplit);
+  if (smem > 220 * 1024) return R4DXB_TOO_LARGE;
+  auto kern = TrellisGemvKernel<KB, TMAX, PRO, kTp>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(ksplit, N / 128, 1);
+  cfg.gridDim = dim3(ksplit, a.N / 128, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -247,68 +349,81 @@ int Launch(const void* words, const void* suh, const void* svh, const void* x, v
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<const uint32_t*>(words), static_cast<const __half*>(suh),
-                                     static_cast<const __half*>(svh), static_cast<const __nv_bfloat16*>(x),
-                                     static_cast<__nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(residual), T, N, K,
-                                     kblocks, tp);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, tp);
   ++g_launch_count;
   return static_cast<int>(e);
 }
 
-template <int KB, bool kTp>
-int LaunchT(const void* words, const void* suh, const void* svh, const void* x, void* y, const void* residual, int T,
-            int N, int K, int ksplit, cudaStream_t stream, const TpPush& tp) {
-  if (T == 1) return Launch<KB, 1, kTp>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream, tp);
-  if (T == 2) return Launch<KB, 2, kTp>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream, tp);
-  if (T <= 4) return Launch<KB, 4, kTp>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream, tp);
-  return Launch<KB, 8, kTp>(words, suh, svh, x, y, residual, T, N, K, ksplit, stream, tp);
+template <int KB, int PRO, bool kTp>
+int LaunchT(const GemvArgs& a, int ksplit, cudaStream_t stream, const TpPush& tp) {
+  if (a.T == 1) return Launch<KB, 1, PRO, kTp>(a, ksplit, stream, tp);
+  if (a.T == 2) return Launch<KB, 2, PRO, kTp>(a, ksplit, stream, tp);
+  if (a.T <= 4) return Launch<KB, 4, PRO, kTp>(a, ksplit, stream, tp);
+  return Launch<KB, 8, PRO, kTp>(a, ksplit, stream, tp);
+}
+
+template <bool kTp>
+int LaunchAll(const GemvArgs& a, int kb, int prologue, int ksplit, cudaStream_t s, const TpPush& tp) {
+#define R4DXB_CASE(KBV, PROV) \
+  if (kb == KBV && prologue == PROV) return LaunchT<KBV, PROV, kTp>(a, ksplit, s, tp);
+  R4DXB_CASE(3, 0) R4DXB_CASE(3, 1) R4DXB_CASE(3, 2)
+  R4DXB_CASE(4, 0) R4DXB_CASE(4, 1) R4DXB_CASE(4, 2)
+  R4DXB_CASE(5, 0) R4DXB_CASE(5, 1) R4DXB_CASE(5, 2)
+#undef R4DXB_CASE
+  return R4DXB_BAD_ARG;
+}
+
+int CheckArgs(int T, int N, int K, int ksplit) {
+  if (T < 1 || T > 8 || N % 128 || K % 128) return R4DXB_BAD_ARG;
+  if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8) return R4DXB_BAD_ARG;
+  if ((K / 128) % ksplit) return R4DXB_BAD_ARG;
+  return 0;
 }
 
 }  // namespace
 }  // namespace r4dxb
 
-extern "C" int r4dxb_trellis_gemv(const void* words, const void* suh, const void* svh, const void* x, void* y,
-                                  const void* residual, int T, int N, int K, int kb, int ksplit, void* stream) {
-  using namespace r4dxb;
-  if (T < 1 || T > 8 || N % 128 || K % 128) return R4DXB_BAD_ARG;
-  if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8) return R4DXB_BAD_ARG;
-  if ((K / 128) % ksplit) return R4DXB_BAD_ARG;
-  if (((K / 128 / ksplit) * 8) % kUnroll) return R4DXB_BAD_ARG;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+using namespace r4dxb;
+
+extern "C" {
+
+int r4dxb_trellis_gemv_ex(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                          const void* residual, const void* norm_w, float eps, int prologue, int T, int N, int K, int kb,
+                          int ksplit, void* stream) {
+  if (int rc = CheckArgs(T, N, K, ksplit)) return rc;
+  if (prologue == 1 && (norm_w == nullptr || K % 8)) return R4DXB_BAD_ARG;
+  GemvArgs a = {static_cast<const uint32_t*>(words), static_cast<const __half*>(suh), static_cast<const __half*>(svh),
+                static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y),
+                static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_w), eps, T, N, K, 0, 0};
   TpPush none = {};
-  switch (kb) {
-    case 3: return LaunchT<3, false>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, none);
-    case 4: return LaunchT<4, false>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, none);
-    case 5: return LaunchT<5, false>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, none);
-    default: return R4DXB_BAD_ARG;
-  }
+  return LaunchAll<false>(a, kb, prologue, ksplit, static_cast<cudaStream_t>(stream), none);
 }
 
-// Row-parallel linear + all-reduce in one kernel (see TpPush).  recv / flags: `world` peer-mapped
-// pointers (index = rank); block_seq, status: this rank's own memory.  spin_limit bounds every wait.
-extern "C" int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void* svh, const void* x, void* y,
-                                            const void* residual, int T, int N, int K, int kb, int ksplit,
-                                            void* const* recv, void* const* flags, void* block_seq, int* status,
-                                            int world, int rank, int spin_limit, void* stream) {
-  using namespace r4dxb;
-  if (T < 1 || T > 8 || N % 128 || K % 128 || world < 2 || world > kMaxWorld || rank < 0 || rank >= world) return R4DXB_BAD_ARG;
-  if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8) return R4DXB_BAD_ARG;
-  if ((K / 128) % ksplit) return R4DXB_BAD_ARG;
+int r4dxb_trellis_gemv(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                       const void* residual, int T, int N, int K, int kb, int ksplit, void* stream) {
+  return r4dxb_trellis_gemv_ex(words, suh, svh, x, y, residual, nullptr, 0.f, 0, T, N, K, kb, ksplit, stream);
+}
+
+// Row-parallel linear + all-reduce + residual in one kernel (see TpPush).  recv: `world` peer-mapped
+// pointers (index = rank), each [2][world][8][N] (value, seq) pairs, zero-initialised; block_seq
+// ([N/128] u32, zero-initialised) and status: this rank's own memory.  spin_limit bounds every wait.
+int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                                 const void* residual, int prologue, int T, int N, int K, int kb, int ksplit,
+                                 void* const* recv, void* block_seq, int* status, int world, int rank, int spin_limit,
+                                 void* stream) {
+  if (int rc = CheckArgs(T, N, K, ksplit)) return rc;
+  if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world || prologue == 1) return R4DXB_BAD_ARG;
+  GemvArgs a = {static_cast<const uint32_t*>(words), static_cast<const __half*>(suh), static_cast<const __half*>(svh),
+                static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y),
+                static_cast<const __nv_bfloat16*>(residual), nullptr, 0.f, T, N, K, 0, 0};
   TpPush tp = {};
-  for (int p = 0; p < world; ++p) {
-    tp.recv[p] = static_cast<float*>(recv[p]);
-    tp.flags[p] = static_cast<unsigned*>(flags[p]);
-  }
+  for (int p = 0; p < world; ++p) tp.recv[p] = static_cast<float2*>(recv[p]);
   tp.block_seq = static_cast<unsigned*>(block_seq);
   tp.status = status;
   tp.world = world;
   tp.rank = rank;
   tp.spin_limit = spin_limit;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  switch (kb) {
-    case 3: return LaunchT<3, true>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, tp);
-    case 4: return LaunchT<4, true>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, tp);
-    case 5: return LaunchT<5, true>(words, suh, svh, x, y, residual, T, N, K, ksplit, s, tp);
-    default: return R4DXB_BAD_ARG;
-  }
+  return LaunchAll<true>(a, kb, prologue, ksplit, static_cast<cudaStream_t>(stream), tp);
 }
+
+}  // extern "C"

@@ -98,6 +98,34 @@ __global__ void Bf16Gemv(const __nv_bfloat16* __restrict__ W, const __nv_bfloat1
   }
 }
 
+// Small-batch variant with the RMSNorm of the residual stream folded in:
+// y[t, n] = W[n, :] . bf16(x[t] * rsqrt(mean x[t]^2 + eps) * (1 + nw))
+__global__ void Bf16GemvNorm(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x,
+                             const __nv_bfloat16* __restrict__ nw, float eps, float* __restrict__ y, int T, int N, int K) {
+  __shared__ float red[32];
+  const int n = blockIdx.x;
+  const __nv_bfloat16* w = W + static_cast<size_t>(n) * K;
+  for (int t = 0; t < T; ++t) {
+    const __nv_bfloat16* xr = x + static_cast<size_t>(t) * K;
+    float ss = 0.f;
+    for (int k = threadIdx.x * 2; k < K; k += blockDim.x * 2) {
+      const uint32_t b = *reinterpret_cast<const uint32_t*>(xr + k);
+      ss += BfLo(b) * BfLo(b) + BfHi(b) * BfHi(b);
+    }
+    const float r = rsqrtf(BlockSum(ss, red) / K + eps);
+    float s = 0.f;
+    for (int k = threadIdx.x * 2; k < K; k += blockDim.x * 2) {
+      const uint32_t a = *reinterpret_cast<const uint32_t*>(w + k);
+      const uint32_t b = *reinterpret_cast<const uint32_t*>(xr + k);
+      const uint32_t g = *reinterpret_cast<const uint32_t*>(nw + k);
+      const uint32_t h = PackBf16(BfLo(b) * r * (1.f + BfLo(g)), BfHi(b) * r * (1.f + BfHi(g)));
+      s += BfLo(a) * BfLo(h) + BfHi(a) * BfHi(h);
+    }
+    s = BlockSum(s, red);
+    if (threadIdx.x == 0) y[static_cast<size_t>(t) * N + n] = s;
+  }
+}
+
 // Many-row variant: one CTA stages 8 activation rows in shared memory and its warps sweep the
 // weight rows, so W is read once per 8 tokens instead of once per token.
 __global__ void __launch_bounds__(256) Bf16GemvTiled(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x,
@@ -252,6 +280,15 @@ int r4dxb_bf16_gemv(const void* W, const void* x, float* y, int T, int N, int K,
   }
   Bf16Gemv<<<N, 128, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(W),
                                                              static_cast<const __nv_bfloat16*>(x), y, T, N, K);
+  return FinishLaunch();
+}
+
+int r4dxb_bf16_gemv_norm(const void* W, const void* x, const void* norm_w, float eps, float* y, int T, int N, int K,
+                         void* stream) {
+  if (T < 1 || T > 8 || N < 1 || K % 2) return R4DXB_BAD_ARG;
+  Bf16GemvNorm<<<N, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(W),
+                                                                 static_cast<const __nv_bfloat16*>(x),
+                                                                 static_cast<const __nv_bfloat16*>(norm_w), eps, y, T, N, K);
   return FinishLaunch();
 }
 

@@ -29,8 +29,10 @@ register_cuda_sig("r4dxb_silu_mul_bf16", _I, [_P, _P, _I, _I, _P])
 register_cuda_sig("r4dxb_residual_add_bf16", _I, [_P, _P, ctypes.c_longlong, _P])
 register_cuda_sig("r4dxb_bias_act_bf16", _I, [_P, _P, _I, _I, _I, _P])
 register_cuda_sig("r4dxb_trellis_gemv", _I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_trellis_gemv_ex", _I, [_P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P])
 register_cuda_sig("r4dxb_w4a16_gemv", _I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P])
 register_cuda_sig("r4dxb_bf16_gemv", _I, [_P, _P, _P, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_bf16_gemv_norm", _I, [_P, _P, _P, _F, _P, _I, _I, _I, _P])
 register_cuda_sig("r4dxb_argmax_rows", _I, [_P, _I, _I, _I, _I, _P, _P, _P, _P])
 register_cuda_sig("r4dxb_gdn_decode", _I, [_P] * 15 + [_I, _I, _I, _I, _F, _P])
 register_cuda_sig("r4dxb_attn_precore", _I, [_P] * 11 + [_I, _I, _I, _I, _I, _F, _F, _P])
@@ -158,15 +160,23 @@ def pick_ksplit(N: int, K: int, target_ctas: int = 296) -> int:
     return best
 
 
+PRO_NONE, PRO_RMSNORM, PRO_SILU_MUL = 0, 1, 2
+
+
 def trellis_gemv(w: TrellisWeight, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
-                 out: Optional[torch.Tensor] = None, ksplit: Optional[int] = None) -> torch.Tensor:
-    """y[T, N] = trellis linear of x[T, K] (T <= 8), optionally + residual (may alias out)."""
+                 out: Optional[torch.Tensor] = None, ksplit: Optional[int] = None, prologue: int = PRO_NONE,
+                 norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6) -> torch.Tensor:
+    """y[T, N] = trellis linear of act(x) (T <= 8), optionally + residual (may alias out).
+
+    prologue PRO_RMSNORM: x is the residual stream [T, K], act = zero-centred RMSNorm with ``norm_w``;
+    PRO_SILU_MUL: x is fused [gate | up] rows [T, 2K].
+    """
     _req(x, BF, "x")
-    T = x.numel() // w.K
+    T = x.numel() // (2 * w.K if prologue == PRO_SILU_MUL else w.K)
     out = out if out is not None else torch.empty(T, w.N, dtype=BF, device=x.device)
     ks = ksplit or pick_ksplit(w.N, w.K)
-    _check(_lib().r4dxb_trellis_gemv(_p(w.words), _p(w.suh), _p(w.svh), _p(x), _p(out), _p(residual), T, w.N, w.K,
-                                     w.kb, ks, _stream()), "trellis_gemv")
+    _check(_lib().r4dxb_trellis_gemv_ex(_p(w.words), _p(w.suh), _p(w.svh), _p(x), _p(out), _p(residual), _p(norm_w), eps,
+                                        prologue, T, w.N, w.K, w.kb, ks, _stream()), "trellis_gemv")
     return out
 
 
@@ -186,6 +196,15 @@ def bf16_gemv(W: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = No
     T = x.numel() // K
     out = out if out is not None else torch.empty(T, N, dtype=torch.float32, device=x.device)
     _check(_lib().r4dxb_bf16_gemv(_p(W), _p(x), _p(out), T, N, K, _stream()), "bf16_gemv")
+    return out
+
+
+def bf16_gemv_norm(W: torch.Tensor, x: torch.Tensor, norm_w: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out[T, N] = rmsnorm(x) W^T for T <= 8 rows of the residual stream (fp32 out)."""
+    _req(W, BF, "W"); _req(x, BF, "x")
+    N, K = W.shape
+    T = x.numel() // K
+    _check(_lib().r4dxb_bf16_gemv_norm(_p(W), _p(x), _p(norm_w), eps, _p(out), T, N, K, _stream()), "bf16_gemv_norm")
     return out
 
 

@@ -57,10 +57,10 @@ class NcclComm:
         return t
 
     # ---- row-parallel linears -----------------------------------------------------------------
-    def row_parallel_linear(self, lin, x: torch.Tensor, res: torch.Tensor) -> None:
-        """res += all_reduce(lin(x)) for T <= 8 rows."""
+    def row_parallel_linear(self, lin, x: torch.Tensor, res: torch.Tensor, prologue: int = 0) -> None:
+        """res += all_reduce(lin(act(x))) for T <= 8 rows."""
         tmp = self._scratch(res.shape, BF)
-        lin(x, out=tmp)
+        lin(x, out=tmp, prologue=prologue)
         dist.all_reduce(tmp, group=self.group)
         K.residual_add(res, tmp)
         self.stats.all_reduces += 1
@@ -105,11 +105,11 @@ class TpDivergenceError(RuntimeError):
     pass
 
 
-def make_comm(world: int, rank: int, device: str, mode: Optional[str] = None):
+def make_comm(world: int, rank: int, device: str, mode: Optional[str] = None, hidden: int = 5120):
     mode = mode or os.environ.get("R4DXB_TP_MODE", "fused")
     if world == 1:
         return None
     if mode == "fused":
         from .tp_fused import FusedComm
-        return FusedComm(world, rank, device)
+        return FusedComm(world, rank, device, n=hidden)
     return NcclComm(world, rank, device)

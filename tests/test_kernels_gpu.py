@@ -309,3 +309,36 @@ def test_attention_prefill(K, D, Hq, Hkv, T, ctx):
     o = R.causal_gqa_attention(qf[ctx:].to(BF), kq, vq, ctx)
     o = o * torch.sigmoid(qg_all[ctx:, :, D:].float())
     assert torch.allclose(out.float().cpu().view(T, Hq, D), o, atol=2e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("T", [1, 3, 8])
+def test_trellis_gemv_fused_prologues_equal_the_unfused_chain(K, T):
+    """RMSNorm / SwiGLU folded into the GEMV prologue give the same bits as the separate kernels."""
+    from r4dx_b200.quant import trellis
+    g = torch.Generator().manual_seed(T)
+    N, Kd = 256, 1024
+    tw = trellis.random_weight(N, Kd, 5, seed=T, sigma=0.02).to("cuda")
+    x = torch.randn(T, Kd, generator=g).to(BF).cuda()
+    nw = (torch.randn(Kd, generator=g) * 0.1).to(BF).cuda()
+    h = K.rmsnorm(x, nw)
+    ref = K.trellis_gemv(tw, h, ksplit=4)
+    got = K.trellis_gemv(tw, x, ksplit=4, prologue=K.PRO_RMSNORM, norm_w=nw)
+    assert torch.equal(ref, got)
+    gu = torch.randn(T, 2 * Kd, generator=g).to(BF).cuda()
+    ref2 = K.trellis_gemv(tw, K.silu_mul(gu), ksplit=2)
+    got2 = K.trellis_gemv(tw, gu, ksplit=2, prologue=K.PRO_SILU_MUL)
+    assert torch.equal(ref2, got2)
+    W = torch.randn(96, Kd, generator=g).to(BF).cuda()
+    out = torch.empty(T, 96, device="cuda")
+    K.bf16_gemv_norm(W, x, nw, 1e-6, out)
+    assert torch.allclose(out, K.bf16_gemv(W, h), atol=1e-3, rtol=1e-3)
+
+
+def test_trellis_gemv_long_k_uses_the_stage_ring(K):
+    """K large enough that the weight stages wrap around the ring several times."""
+    from r4dx_b200.quant import trellis
+    tw = trellis.random_weight(128, 4096, 4, seed=9, sigma=0.02)
+    x = torch.randn(2, 4096, generator=torch.Generator().manual_seed(1)).to(BF)
+    ref = trellis.linear_reference(tw, x.float())
+    y = K.trellis_gemv(tw.to("cuda"), x.cuda(), ksplit=1)
+    assert (y.float().cpu() - ref).abs().max().item() < 0.02 * ref.abs().max().item() + 1e-3

@@ -39,15 +39,13 @@ def test_fused_allreduce_wait_runs_out_and_reports(tmp_path):
     tw = trellis.random_weight(N, Kd, 4, seed=1).to(dev)
     x = torch.randn(1, Kd, device=dev).to(torch.bfloat16)
     y = torch.zeros(1, N, dtype=torch.bfloat16, device=dev)
-    # both "ranks" point at local buffers; nobody ever writes rank 1's flags
-    recv = torch.zeros(2 * world * 8 * N, device=dev)
-    flags = torch.zeros((N // 128) * world, dtype=torch.int32, device=dev)
+    # both "ranks" point at the same local buffer; nobody ever writes rank 1's (value, seq) pairs
+    recv = torch.zeros(2 * world * 8 * N * 2, device=dev)
     seq = torch.zeros(N // 128, dtype=torch.int32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     tab = (ctypes.c_void_p * world)(recv.data_ptr(), recv.data_ptr())
-    ftab = (ctypes.c_void_p * world)(flags.data_ptr(), flags.data_ptr())
     rc = L.r4dxb_trellis_gemv_allreduce(tw.words.data_ptr(), tw.suh.data_ptr(), tw.svh.data_ptr(), x.data_ptr(),
-                                        y.data_ptr(), None, 1, N, Kd, 4, 1, tab, ftab, seq.data_ptr(), status.data_ptr(),
+                                        y.data_ptr(), None, 0, 1, N, Kd, 4, 1, tab, seq.data_ptr(), status.data_ptr(),
                                         world, 0, 2000, torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     torch.cuda.synchronize()                      # returns: the wait was bounded

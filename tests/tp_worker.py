@@ -23,7 +23,7 @@ def main():
     from r4dx_b200.quant.weights import synthetic_weight_set
     gcfg = small_hybrid_config(layers=4)
     full = synthetic_weight_set(gcfg, device=dev, seed=3, sigma=0.05)
-    comm = make_comm(world, rank, dev)
+    comm = make_comm(world, rank, dev, hidden=gcfg.hidden_size)
     cfg = gcfg.shard(world, rank)
     model = HybridModel(cfg, shard_weight_set(gcfg, full, world, rank), max_ctx=512, device=dev, comm=comm)
     ids = torch.randint(0, gcfg.vocab_size, (90,), generator=torch.Generator().manual_seed(7), dtype=torch.int32)
