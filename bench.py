@@ -34,6 +34,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=64, help="debug only: fewer layers makes the result invalid")
     ap.add_argument("--model", default="qwen-hybrid-27b", choices=["qwen-hybrid-27b", "small"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true", help="A/B: disable programmatic dependent launch")
     return ap.parse_args()
 
 
@@ -119,6 +120,8 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(dev))
     native.cuda()
+    if args.no_pdl:
+        native.cuda().r4dxb_set_pdl(0)
 
     gcfg = qwen_hybrid_27b_config(args.layers) if args.model == "qwen-hybrid-27b" else small_hybrid_config(args.layers)
     if world > 1:

@@ -15,11 +15,9 @@
 // lane turns 8 consecutive K codes of one row into fp16 and multiplies them with the staged
 // activations.
 //
-// Small matrices are latency-bound, so two more things hide latency: (a) `wpt` warps share an
-// n-tile (each takes every wpt-th k-tile of a stage), shortening the serial decode chain per warp;
-// (b) programmatic dependent launch: the kernel lets its successor start early and itself waits
-// for its predecessor (griddepcontrol.wait) only before touching activations -- the weight stream,
-// which depends on no other kernel, is already in flight by then.
+// Programmatic dependent launch hides launch and prefetch latency: the kernel lets its successor
+// start early and itself waits for its predecessor (griddepcontrol.wait) only before touching
+// activations -- the weight stream, which depends on no other kernel, is already in flight by then.
 //
 // Prologue modes fold the producer of the activations into this kernel:
 //   0  x is the activation                       [T, K]
@@ -41,10 +39,10 @@ namespace cg = cooperative_groups;
 namespace r4dxb {
 namespace {
 
-constexpr int kTileWarps = 8;              // n-tiles per 128-row block
-constexpr int kMaxWpt = 3;                 // warps per n-tile
-constexpr int kMaxThreads = (kTileWarps * kMaxWpt + 1) * 32;
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxWorld = 8;
+bool g_use_pdl = true;
 
 // Tensor-parallel epilogue: all-reduce by one-shot push over NVLink peer memory.  Each value travels
 // as an 8-byte (fp32 value, sequence number) pair, so data and "ready" flag arrive in one store and
@@ -68,11 +66,11 @@ struct GemvArgs {
   const __nv_bfloat16* residual;
   const __nv_bfloat16* norm_w;     // prologue mode 1
   float eps;
-  int T, N, K, kblocks_per_cta, stages, wpt;
+  int T, N, K, kblocks_per_cta, stages;
 };
 
 template <int KB, int TMAX, int PRO, bool kTp>
-__global__ void __launch_bounds__(kMaxThreads)
+__global__ void __launch_bounds__(kThreads)
 TrellisGemvKernel(GemvArgs a, TpPush tp) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   cg::cluster_group cluster = cg::this_cluster();
@@ -80,23 +78,19 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
   const int krank = blockIdx.x;            // == rank inside the cluster
   const int nb = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int wpt = a.wpt;
-  const int kConsumerWarps = kTileWarps * wpt;       // the producer is warp index kConsumerWarps
-  const int jtile = warp & 7, ksub = warp >> 3;      // n-tile of this warp, and which k-tiles of a stage it takes
   const int kslice = a.kblocks_per_cta * 128;
   const int k_begin = krank * kslice;
   const int T = a.T, N = a.N, K = a.K;
   constexpr int NW = 8 * KB;
   constexpr int kStageBytes = 8 * 8 * NW * 4;     // 8 k-tiles x 8 n-tiles
 
-  const int nparts = ksplit * wpt;
-  float* part = reinterpret_cast<float*>(smem_raw);                                  // [ksplit * wpt][TMAX][128] (used on cluster rank 0)
-  float* rnorm = part + nparts * TMAX * 128;                                          // [8] per-row rsqrt
+  float* part = reinterpret_cast<float*>(smem_raw);                                  // [ksplit][TMAX][128] (used on cluster rank 0)
+  float* rnorm = part + ksplit * TMAX * 128;                                          // [8] per-row rsqrt
   uint64_t* full = reinterpret_cast<uint64_t*>(rnorm + 8);                            // [8]
   uint64_t* empty = full + 8;                                                         // [8]
   uint64_t* red_bar = empty + 8;                                                      // [1] split-K partials have landed
   volatile int* abort_flag = reinterpret_cast<volatile int*>(red_bar + 1);
-  __half* xs = reinterpret_cast<__half*>(smem_raw + nparts * TMAX * 128 * 4 + 32 + 128 + 16);   // [TMAX][kslice]
+  __half* xs = reinterpret_cast<__half*>(smem_raw + ksplit * TMAX * 128 * 4 + 32 + 128 + 16);   // [TMAX][kslice]
   unsigned char* wst = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(xs + static_cast<size_t>(TMAX) * kslice) + 127) & ~uintptr_t(127));   // [stages][kStageBytes]
 
@@ -133,7 +127,6 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
     // ---------------- prologue (consumer warps): xs = fp16(H128(suh * act(x))) for this K slice ----------------
     // everything before this point touched only weights; activations come from the previous kernel
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int cthreads = kConsumerWarps * 32;
     if constexpr (PRO == 1) {
       // RMSNorm statistics need the whole row, not just this CTA's slice: warp t reduces row t
       if (warp < T) {
@@ -147,7 +140,7 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
         ss = WarpSum(ss);
         if (lane == 0) rnorm[warp] = rsqrtf(ss / K + a.eps);
       }
-      asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");
     }
     const float inv_sqrt = 0.08838834764831845f;   // 1 / sqrt(128)
     for (int item = warp; item < a.kblocks_per_cta * TMAX; item += kConsumerWarps) {
@@ -185,7 +178,7 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
       ov.y = *reinterpret_cast<uint32_t*>(&o23);
       *reinterpret_cast<uint2*>(xs + static_cast<size_t>(t) * kslice + b * 128 + lane * 4) = ov;
     }
-    asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
+    asm volatile("bar.sync 1, 256;" ::: "memory");
 
     // ---------------- main loop: warp = n-tile, lane = (row, k half) ----------------
     TrellisLane<KB> tl;
@@ -199,11 +192,12 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
       const int s = it % a.stages, round = it / a.stages;
       ok = ptx::MbarWait(&full[s], round & 1, abort_flag, 2);
       if (!ok) break;
-      const uint32_t* sw = reinterpret_cast<const uint32_t*>(wst + static_cast<size_t>(s) * kStageBytes) + jtile * NW;
+      const uint32_t* sw = reinterpret_cast<const uint32_t*>(wst + static_cast<size_t>(s) * kStageBytes) + warp * NW;
       __half2 hacc[TMAX];
 #pragma unroll
       for (int t = 0; t < TMAX; ++t) hacc[t] = __float2half2_rn(0.f);
-      for (int kt = ksub; kt < 8; kt += wpt) {
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) {
         const uint32_t* tw = sw + kt * 8 * NW;
         uint32_t hi, lo;
         tl.Window(tw[tl.i0], tw[tl.i1], (KB == 4) ? 0u : tw[tl.i2], hi, lo);
@@ -218,10 +212,14 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
           h = __hfma2(w[2], *reinterpret_cast<const __half2*>(&xv.z), h);
           hacc[t] = __hfma2(w[3], *reinterpret_cast<const __half2*>(&xv.w), h);
         }
-      }
-      // fold the fp16 partials (at most 8 tiles = 32 products per half) into fp32 once per stage
+        if (kt == 3 || kt == 7) {       // fold the fp16 partials into fp32 every 32 products per half
 #pragma unroll
-      for (int t = 0; t < TMAX; ++t) acc[t] += __low2float(hacc[t]) + __high2float(hacc[t]);
+          for (int t = 0; t < TMAX; ++t) {
+            acc[t] += __low2float(hacc[t]) + __high2float(hacc[t]);
+            hacc[t] = __float2half2_rn(0.f);
+          }
+        }
+      }
       __syncwarp();
       if (lane == 0) ptx::MbarArrive(&empty[s]);
     }
@@ -230,11 +228,11 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
     __syncwarp();
     if (ksplit > 1) asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     float* dst = ksplit > 1 ? cluster.map_shared_rank(part, 0) : part;
-    dst += (krank * wpt + ksub) * TMAX * 128;
+    dst += krank * TMAX * 128;
 #pragma unroll
     for (int t = 0; t < TMAX; ++t) {
       acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], 1);
-      if ((lane & 1) == 0) dst[t * 128 + jtile * 16 + (lane >> 1)] = acc[t];
+      if ((lane & 1) == 0) dst[t * 128 + warp * 16 + (lane >> 1)] = acc[t];
     }
     __syncwarp();
     if (lane == 0) {
@@ -251,7 +249,7 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
   }
 
   // ---------------- epilogue (cluster rank 0) ----------------
-  if (krank == 0 && warp < kTileWarps) {
+  if (krank == 0 && warp < kConsumerWarps) {
     {
       // wait (bounded) until every consumer warp of every CTA of the cluster has delivered its partial rows
       bool landed = false;
@@ -269,7 +267,7 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
     const int n = nb * 128 + lane * 4;
     if (t < T) {
       float v[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int r = 0; r < nparts; ++r) {       // fixed order: the result does not depend on timing
+      for (int r = 0; r < ksplit; ++r) {       // fixed order: the result does not depend on timing
         const float4 p = *reinterpret_cast<const float4*>(part + (r * TMAX + t) * 128 + lane * 4);
         v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
       }
@@ -330,8 +328,8 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
   }
 }
 
-size_t SmemBytes(int tmax, int kslice, int stages, int kb, int nparts) {
-  return static_cast<size_t>(nparts) * tmax * 128 * 4 + 32 + 128 + 16 + static_cast<size_t>(tmax) * kslice * 2 + 128 +
+size_t SmemBytes(int tmax, int kslice, int stages, int kb, int ksplit) {
+  return static_cast<size_t>(ksplit) * tmax * 128 * 4 + 32 + 128 + 16 + static_cast<size_t>(tmax) * kslice * 2 + 128 +
          static_cast<size_t>(stages) * 8 * 8 * 8 * kb * 4;
 }
 
@@ -341,10 +339,7 @@ int Launch(GemvArgs a, int ksplit, cudaStream_t stream, const TpPush& tp) {
   const int kslice = a.kblocks_per_cta * 128;
   // ring depth: everything in flight for short slices, otherwise up to 6 stages (48-60 KiB)
   a.stages = a.kblocks_per_cta < 6 ? a.kblocks_per_cta : 6;
-  // few CTAs -> more warps per n-tile, so that every SM scheduler has work and each warp's serial chain is short
-  const int ctas = (a.N / 128) * ksplit;
-  a.wpt = ctas >= 592 ? 1 : (ctas >= 296 ? 2 : kMaxWpt);
-  const size_t smem = SmemBytes(TMAX, kslice, a.stages, KB, ksplit * a.wpt);
+  const size_t smem = SmemBytes(TMAX, kslice, a.stages, KB, ksplit);
   if (smem > 220 * 1024) return R4DXB_TOO_LARGE;
   auto kern = TrellisGemvKernel<KB, TMAX, PRO, kTp>;
   if (smem > 48 * 1024) {
@@ -353,7 +348,7 @@ int Launch(GemvArgs a, int ksplit, cudaStream_t stream, const TpPush& tp) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(ksplit, a.N / 128, 1);
-  cfg.blockDim = dim3((kTileWarps * a.wpt + 1) * 32, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -366,7 +361,7 @@ int Launch(GemvArgs a, int ksplit, cudaStream_t stream, const TpPush& tp) {
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 2;
+  cfg.numAttrs = g_use_pdl ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, tp);
   ++g_launch_count;
   return static_cast<int>(e);
@@ -405,6 +400,9 @@ using namespace r4dxb;
 
 extern "C" {
 
+/* A/B switch for programmatic dependent launch (default on). */
+void r4dxb_set_pdl(int on) { g_use_pdl = on != 0; }
+
 int r4dxb_trellis_gemv_ex(const void* words, const void* suh, const void* svh, const void* x, void* y,
                           const void* residual, const void* norm_w, float eps, int prologue, int T, int N, int K, int kb,
                           int ksplit, void* stream) {
@@ -412,7 +410,7 @@ int r4dxb_trellis_gemv_ex(const void* words, const void* suh, const void* svh, c
   if (prologue == 1 && (norm_w == nullptr || K % 8)) return R4DXB_BAD_ARG;
   GemvArgs a = {static_cast<const uint32_t*>(words), static_cast<const __half*>(suh), static_cast<const __half*>(svh),
                 static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y),
-                static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_w), eps, T, N, K, 0, 0, 1};
+                static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_w), eps, T, N, K, 0, 0};
   TpPush none = {};
   return LaunchAll<false>(a, kb, prologue, ksplit, static_cast<cudaStream_t>(stream), none);
 }
@@ -433,7 +431,7 @@ int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void*
   if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world || prologue == 1) return R4DXB_BAD_ARG;
   GemvArgs a = {static_cast<const uint32_t*>(words), static_cast<const __half*>(suh), static_cast<const __half*>(svh),
                 static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y),
-                static_cast<const __nv_bfloat16*>(residual), nullptr, 0.f, T, N, K, 0, 0, 1};
+                static_cast<const __nv_bfloat16*>(residual), nullptr, 0.f, T, N, K, 0, 0};
   TpPush tp = {};
   for (int p = 0; p < world; ++p) tp.recv[p] = static_cast<float2*>(recv[p]);
   tp.block_seq = static_cast<unsigned*>(block_seq);
