@@ -1,0 +1,94 @@
+"""Flag definitions shared by the CLI generator and the server (reference: src/cli/cli_args.h,
+src/server/server_args.h; flag names follow the reference's so scripts carry over)."""
+from __future__ import annotations
+
+import argparse
+import os
+
+
+def add_model_flags(ap: argparse.ArgumentParser) -> None:
+    g = ap.add_argument_group("model")
+    g.add_argument("--model", required=False, help="container file (.r4dxb) or 'synthetic:<tiny|small|27b>'")
+    g.add_argument("--layout", default="trellis", choices=["bf16", "w4a16", "trellis", "w8a16"])
+    g.add_argument("--tokenizer-dir", default=None)
+    g.add_argument("--max-ctx", type=int, default=8192)
+    g.add_argument("--layers", type=int, default=0, help="load only the first N layers (debug)")
+    g.add_argument("--prefill-chunk", type=int, default=int(os.environ.get("R4DXB_PREFILL_CHUNK", "2048")))
+    g.add_argument("--mtp", type=int, default=0, metavar="K", help="MTP speculative decoding with K drafts per round")
+    g.add_argument("--dflash", default=None, metavar="CONTAINER", help="block-diffusion drafter container")
+    g.add_argument("--dflash-k", type=int, default=7)
+    g.add_argument("--dflash-p-min", type=float, default=0.0)
+    g.add_argument("--dflash-n-min", type=int, default=0)
+    g.add_argument("--vision", default="off", choices=["off", "on"])
+    p = ap.add_argument_group("parallelism")
+    p.add_argument("--tp", type=int, default=1, choices=[1, 2, 4, 8])
+    p.add_argument("--tp-mode", default=os.environ.get("R4DXB_TP_MODE", "fused"), choices=["fused", "nccl", "noop"])
+    p.add_argument("--tp-ar-timeout-ms", type=int, default=500)
+    p.add_argument("--pp", type=int, default=1, choices=[1, 2])
+    p.add_argument("--pp-split", type=int, default=0)
+    p.add_argument("--pp-min-rows", type=int, default=512)
+    p.add_argument("--hybrid", action="store_true", help="pipeline-parallel prefill, then reshard to tensor-parallel decode")
+    p.add_argument("--tp-fault", default=os.environ.get("R4DXB_TP_FAULT", ""), help="host-side fault injection 'rank:n:kind'")
+
+
+def add_sampling_flags(ap: argparse.ArgumentParser, prefix: str = "") -> None:
+    g = ap.add_argument_group("sampling")
+    g.add_argument(f"--{prefix}temperature", type=float, default=0.0 if not prefix else 1.0)
+    g.add_argument(f"--{prefix}top-k", type=int, default=0)
+    g.add_argument(f"--{prefix}top-p", type=float, default=1.0)
+    g.add_argument(f"--{prefix}min-p", type=float, default=0.0)
+    g.add_argument(f"--{prefix}repetition-penalty", type=float, default=1.0)
+
+
+def cli_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser("r4dxb-cli", description="one-shot / chat text generation")
+    add_model_flags(ap)
+    add_sampling_flags(ap)
+    ap.add_argument("--prompt", default=None)
+    ap.add_argument("--prompt-file", default=None)
+    ap.add_argument("--system", default=None)
+    ap.add_argument("--chat", action="store_true")
+    ap.add_argument("--max-tokens", type=int, default=256)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--think", default="on", choices=["on", "off"])
+    ap.add_argument("--stats", action="store_true")
+    ap.add_argument("--profile", action="store_true", help="per-op device timing of one decode step")
+    ap.add_argument("--profile-prefill", action="store_true")
+    ap.add_argument("--dump-token-ids", action="store_true")
+    return ap
+
+
+def server_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser("r4dxb-server", description="OpenAI-compatible server")
+    add_model_flags(ap)
+    add_sampling_flags(ap, "default-")
+    ap.add_argument("--host", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=8080)
+    ap.add_argument("--max-queue", type=int, default=8)
+    ap.add_argument("--max-tokens-default", type=int, default=512)
+    ap.add_argument("--log-level", default="info", choices=["debug", "info", "warn", "error"])
+    ap.add_argument("--prompt-checkpoint", default="on", choices=["on", "off"])
+    ap.add_argument("--request-log", default=None)
+    ap.add_argument("--request-log-tokens", action="store_true")
+    ap.add_argument("--batch", type=int, default=0, help="concurrent decode slots")
+    ap.add_argument("--batch-ctx", type=int, default=32768)
+    return ap
+
+
+def convert_parser() -> argparse.ArgumentParser:
+    ap = argparse.ArgumentParser("r4dxb-convert", description="checkpoint -> quantized container")
+    ap.add_argument("--input", required=True, help="safetensors file/dir with config.json, or 'random:<tiny|small>'")
+    ap.add_argument("--output", required=True)
+    ap.add_argument("--layouts", default="trellis", help="comma list: trellis,w4a16,bf16")
+    ap.add_argument("--lm-head", default="w4a16", choices=["w4a16", "bf16"])
+    ap.add_argument("--lm-head-group", type=int, default=64)
+    ap.add_argument("--kb-plan", default="mix4.5", choices=["mix4.5", "mix3.3", "kb3", "kb4", "kb5"])
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--threads", type=int, default=0)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--mtp", action="store_true")
+    ap.add_argument("--keep-bf16", default="", help="comma list of tensor-name substrings kept in bf16")
+    ap.add_argument("--kv-calib", default=None, help="JSON file with per-layer k/v amax for fp8 descales")
+    ap.add_argument("--reuse-tensors-from", default=None, help="older container whose identical tensors are copied, guarded by sha256")
+    ap.add_argument("--selftest", action="store_true", help="re-open the output and verify every tensor's reconstruction error")
+    return ap

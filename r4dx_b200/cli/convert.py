@@ -1,0 +1,92 @@
+"""r4dxb-convert: fp32/bf16 checkpoint (safetensors + config.json) or a random init -> quantized container.
+
+Two-phase writer (plan, then stream), `.partial` + rename, optional re-open self test with a reconstruction
+error bound per tensor, optional reuse of unchanged tensors from an older container guarded by sha256
+(reference: src/convert/main.cpp:1-120)."""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import sys
+
+import torch
+
+from .args import convert_parser
+
+
+def _kb_rule(plan: str):
+    from ..quant.weights import default_kb_rule, moe_kb_rule
+    return {"mix4.5": default_kb_rule, "mix3.3": moe_kb_rule, "kb3": lambda n: 3, "kb4": lambda n: 4, "kb5": lambda n: 5}[plan]
+
+
+def load_source(spec: str, layers: int, mtp: bool, seed: int):
+    from ..config import ModelConfig, small_hybrid_config, tiny_hybrid_config
+    from ..models.oracle import init_weights
+    if spec.startswith("random:"):
+        cfg = {"tiny": tiny_hybrid_config, "small": small_hybrid_config}[spec.split(":", 1)[1]]()
+        if layers:
+            cfg.num_hidden_layers, cfg.layer_types = layers, cfg.layer_types[:layers]
+        return cfg, init_weights(cfg, seed, with_mtp=mtp)
+    from safetensors import safe_open
+    d = spec if os.path.isdir(spec) else os.path.dirname(spec)
+    cfg = ModelConfig.from_json(open(os.path.join(d, "config.json")).read())
+    files = [os.path.join(d, f) for f in sorted(os.listdir(d)) if f.endswith(".safetensors")] if os.path.isdir(spec) else [spec]
+    w = {}
+    for f in files:
+        with safe_open(f, "pt") as sf:
+            for k in sf.keys():
+                w[k] = sf.get_tensor(k)
+    return cfg, w
+
+
+def main(argv=None) -> int:
+    args = convert_parser().parse_args(argv)
+    from ..quant.container import Container
+    from ..quant.weights import dequantize_weight_set, load_weight_set, quantize_weight_set, save_weight_set
+    if args.threads:
+        torch.set_num_threads(args.threads)
+    cfg, w = load_source(args.input, args.layers, args.mtp, args.seed)
+    keep = [s for s in args.keep_bf16.split(",") if s]
+    layout = args.layouts.split(",")[0]
+    src = {k: v for k, v in w.items()}
+    q = quantize_weight_set(cfg, src, layout=layout, kb_rule=_kb_rule(args.kb_plan), head_group=args.lm_head_group, seed=args.seed)
+    for k in list(q):
+        if any(s in k for s in keep):
+            q[k] = w[k].to(torch.bfloat16)
+    if args.lm_head == "bf16":
+        q["lm_head"] = w["lm_head"].to(torch.bfloat16)
+    if args.kv_calib:
+        cal = json.load(open(args.kv_calib))
+        for name, amax in cal.items():
+            q[name] = torch.tensor(amax, dtype=torch.float32) / 448.0
+    reused = 0
+    if args.reuse_tensors_from and os.path.exists(args.reuse_tensors_from):
+        old = Container(args.reuse_tensors_from)
+        src_hash = json.loads(old.metadata.get("source_sha256", "{}"))
+        _, oldq = load_weight_set(args.reuse_tensors_from)
+        for k, v in w.items():
+            h = hashlib.sha256(v.detach().float().contiguous().numpy().tobytes()).hexdigest()
+            if src_hash.get(k) == h and k in oldq:
+                q[k] = oldq[k]
+                reused += 1
+    hashes = {k: hashlib.sha256(v.detach().float().contiguous().numpy().tobytes()).hexdigest() for k, v in w.items()}
+    save_weight_set(args.output, cfg, q, {"source_sha256": json.dumps(hashes), "converter": "r4dxb-convert 0.1",
+                                         "kb_plan": args.kb_plan})
+    print(f"wrote {args.output}: {len(q)} tensors, {reused} reused", file=sys.stderr)
+    if args.selftest:
+        _, back = load_weight_set(args.output)
+        dq = dequantize_weight_set(back)
+        worst = 0.0
+        for k, v in w.items():
+            if v.dim() == 2 and k in dq:
+                rel = float(((dq[k] - v.float()) ** 2).sum() / (v.float() ** 2).sum().clamp_min(1e-30))
+                worst = max(worst, rel)
+        print(f"selftest: worst relative squared error {worst:.4f}", file=sys.stderr)
+        if worst > 0.2:
+            return 1
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,93 @@
+"""r4dxb-cli: one-shot or interactive generation (reference: src/cli/main.cpp:128,557,969)."""
+from __future__ import annotations
+
+import sys
+import time
+
+from .args import cli_parser
+
+
+def run_turn(tm, tk, prompt_ids, args, rng, out=sys.stdout):
+    """Prefill + decode one answer; returns (token ids, stats dict)."""
+    from ..runtime.sampler import SampleParams
+    from ..runtime.tokenizer import StreamDecoder
+    params = SampleParams(args.temperature, args.top_k, args.top_p, args.min_p, args.seed, args.repetition_penalty)
+    t0 = time.perf_counter()
+    tok = tm.prefill(prompt_ids)
+    if not params.greedy:
+        tok = tm.sample_from_last(params, rng, prompt_ids)
+    t1 = time.perf_counter()
+    eos = set(getattr(tk, "eos_ids", []))
+    dec = StreamDecoder(tk)
+    ids, rounds = [], 0
+    pending = [tok]
+    while pending and len(ids) < args.max_tokens:
+        tok = pending.pop(0)
+        if tok in eos:
+            break
+        ids.append(tok)
+        out.write(dec.feed(tok)); out.flush()
+        if not pending:
+            rounds += 1
+            if args.mtp > 0 and params.greedy:
+                pending = tm.decode_step_spec_greedy(tok, args.mtp)
+            elif params.greedy:
+                pending = [tm.decode_step_greedy(tok)]
+            else:
+                pending = [tm.decode_step_sampled(tok, params, rng, list(prompt_ids) + ids)]
+    out.write(dec.flush() + "\n")
+    t2 = time.perf_counter()
+    stats = {"prompt_tokens": len(prompt_ids), "prefill_tok_s": len(prompt_ids) / max(t1 - t0, 1e-9),
+             "ttft_s": t1 - t0, "decode_tokens": len(ids), "decode_tok_s": max(len(ids) - 1, 0) / max(t2 - t1, 1e-9),
+             "tokens_per_round": len(ids) / max(rounds, 1)}
+    return ids, stats
+
+
+def main(argv=None) -> int:
+    args = cli_parser().parse_args(argv)
+    from ..runtime.sampler import Rng
+    from .loader import load_text_model
+    tm, tk, tpl = load_text_model(args)
+    rng = Rng(args.seed)
+    if args.profile or args.profile_prefill:
+        from ..utils.profiler import profile_decode_step, profile_prefill
+        ids = tk.encode(args.prompt or "hello")
+        print(profile_prefill(tm.m, ids) if args.profile_prefill else profile_decode_step(tm.m, ids))
+        return 0
+
+    def build(messages):
+        text = tpl.render(messages, add_generation_prompt=True, enable_thinking=(args.think == "on"))
+        return tk.encode(text)
+
+    messages = []
+    if args.system:
+        messages.append({"role": "system", "content": args.system})
+    if args.chat:
+        while True:
+            try:
+                line = input("> ")
+            except EOFError:
+                break
+            if not line.strip():
+                continue
+            messages.append({"role": "user", "content": line})
+            tm.reset()
+            ids, stats = run_turn(tm, tk, build(messages), args, rng)
+            messages.append({"role": "assistant", "content": tk.decode(ids)})
+            if args.stats:
+                print(f"[stats] {stats}", file=sys.stderr)
+        return 0
+    prompt = args.prompt if args.prompt is not None else (open(args.prompt_file).read() if args.prompt_file else "Hello")
+    messages.append({"role": "user", "content": prompt})
+    pids = build(messages)
+    if args.dump_token_ids:
+        print(pids, file=sys.stderr)
+    ids, stats = run_turn(tm, tk, pids, args, rng)
+    if args.stats:
+        print(f"[stats] prefill {stats['prefill_tok_s']:.1f} tok/s (TTFT {stats['ttft_s'] * 1e3:.1f} ms), decode "
+              f"{stats['decode_tok_s']:.1f} tok/s, {stats['tokens_per_round']:.2f} tokens/round, tp={tm.tp_world()}", file=sys.stderr)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

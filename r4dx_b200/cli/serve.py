@@ -1,0 +1,33 @@
+"""r4dxb-server entry point (reference: src/server/main.cpp)."""
+from __future__ import annotations
+
+import sys
+
+from .args import server_parser
+
+
+def main(argv=None) -> int:
+    args = server_parser().parse_args(argv)
+    from ..server.engine import Engine
+    from ..server.http_server import ApiServer
+    from ..server.request_log import RequestLog
+    from .loader import load_text_model
+    tm, tk, tpl = load_text_model(args)
+    eng = Engine(tm, tk, max_queue=args.max_queue, prompt_checkpoint=(args.prompt_checkpoint == "on"),
+                 request_log=RequestLog(args.request_log, args.request_log_tokens))
+    defaults = {"temperature": args.default_temperature, "top_k": args.default_top_k, "top_p": args.default_top_p,
+                "min_p": args.default_min_p, "repetition_penalty": args.default_repetition_penalty}
+    srv = ApiServer(eng, tk, tpl, tm.model_id, host=args.host, port=args.port, max_tokens_default=args.max_tokens_default,
+                    defaults=defaults, spec_k=args.mtp)
+    print(f"[r4dxb-server] {tm.model_id} on http://{args.host}:{srv.port} (tp={tm.tp_world()})", file=sys.stderr)
+    try:
+        srv.serve_forever()
+    except KeyboardInterrupt:
+        pass
+    finally:
+        eng.shutdown()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

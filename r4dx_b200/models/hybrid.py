@@ -405,6 +405,52 @@ class HybridModel:
     def logits_rows(self, T: int) -> torch.Tensor:
         return self.buf.logits[:T]
 
+    # ---- speculative window -----------------------------------------------------------------------
+    def verify_window(self, anchor: int, drafts: List[int]) -> List[int]:
+        """Feeds [anchor, d1..dm] (m <= MAX_ROWS - 1), accepts the longest prefix of drafts the target agrees
+        with (greedy, lossless) and commits exactly those rows.  Returns the emitted tokens: accepted drafts
+        plus one correction / bonus token (reference: src/model/model.cpp:2694-2975, 3344-3426)."""
+        m = len(drafts)
+        if m + 1 > MAX_ROWS:
+            raise ValueError("speculative window too long")
+        ids = torch.tensor([anchor] + list(drafts), dtype=torch.int32)
+        T = self._stage(ids, self.pos)
+        if self.pos + T > self.max_ctx:
+            raise ValueError("context overflow")
+        b = self.buf
+        b.n_replay.fill_(self.pending_rows)
+        self.forward_rows(T, True)
+        if not hasattr(self, "_spec_out"):
+            self._spec_out = torch.zeros(MAX_ROWS + 2, dtype=torch.int32, device=self.device)
+        K.spec_accept(b.next_ids, b.ids[1:], T, self._spec_out, None)
+        res = self._spec_out[:T + 1].tolist()        # one small read-back per round
+        n = res[0]
+        self.pending_rows = n
+        self.pos += n
+        return res[1:1 + n]
+
+    # ---- prompt checkpoint ---------------------------------------------------------------------------
+    def save_checkpoint(self) -> dict:
+        """Snapshot of the recurrent state (KV needs no copy: it is overwritten by position)
+        (reference: src/model/model.h:361-379)."""
+        self.commit_pending()
+        return {"pos": self.pos, "gdn": {i: t.clone() for i, t in self.gdn_state.items()},
+                "ring": {i: t.clone() for i, t in self.ring.items()}}
+
+    def restore_checkpoint(self, ck: dict) -> None:
+        for i, t in ck["gdn"].items():
+            self.gdn_state[i].copy_(t)
+        for i, t in ck["ring"].items():
+            self.ring[i].copy_(t)
+        self.pos = ck["pos"]
+        self.pending_rows = 0
+        self.buf.n_replay.zero_()
+
+    def decode_step_logits(self, token: int) -> torch.Tensor:
+        """Eager single step returning this rank's fp32 logits row (sampling path)."""
+        self.feed(torch.tensor([token], dtype=torch.int32))
+        return self.buf.logits[0]
+
     # ---- graph decode ---------------------------------------------------------------------------
     def _capture(self, T: int) -> torch.cuda.CUDAGraph:
         b = self.buf

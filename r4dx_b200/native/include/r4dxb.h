@@ -30,6 +30,10 @@ int r4dxb_silu_mul_bf16(const void* gate_up, void* out, int T, int I, void* stre
 int r4dxb_residual_add_bf16(void* res, const void* delta, long long n, void* stream);
 int r4dxb_bias_act_bf16(void* x, const void* bias, int T, int H, int act, void* stream);
 
+/* Speculative-window acceptance (greedy or sample-and-match: next_ids = the target's pick per row):
+ * out[0] = rows to commit, out[1..out[0]] = emitted tokens; n_replay (optional) receives out[0]. */
+int r4dxb_spec_accept(const int* next_ids, const int* draft, int T, int* out, int* n_replay, void* stream);
+
 /* ---- weight-streaming GEMMs for T <= 8 rows ------------------------------------------------- */
 /* y[T,N] (bf16) = svh * H(Q . H(suh * x)) (+ residual), trellis-coded Q, kb in {3,4,5}.
  * ksplit in {1,2,4,8} CTAs share one 128-row block through a thread-block cluster. */

@@ -113,6 +113,22 @@ __global__ void BiasActKernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16
   x[i] = __float2bfloat16(v);
 }
 
+// Lossless greedy verification of a speculative window: row i's argmax must equal draft i+1.
+// out[0] = rows to commit (accepted drafts + 1), out[1..] = emitted tokens (accepted drafts, then the
+// correction / bonus token).  (reference: src/model/model.cpp:3344-3426 does this walk on the host)
+__global__ void SpecAcceptKernel(const int* __restrict__ next_ids, const int* __restrict__ draft, int T,
+                                 int* __restrict__ out, int* __restrict__ n_replay) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int n = 1;
+  while (n < T && next_ids[n - 1] == draft[n - 1]) ++n;
+  for (int i = 0; i + 1 < n; ++i) out[1 + i] = draft[i];
+  out[n] = next_ids[n - 1];
+  out[0] = n;
+  if (n_replay) n_replay[0] = n;
+}
+
+// (Sample-and-match uses the same kernel: next_ids then holds the token drawn per row from the
+// target distribution, and a draft is accepted while the draw equals it.)
 }  // namespace
 }  // namespace r4dxb
 
@@ -168,6 +184,12 @@ int r4dxb_residual_add_bf16(void* res, const void* delta, long long n, void* str
   const size_t n2 = n / 2;
   ResidualAddKernel<<<static_cast<unsigned>((n2 + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(delta), n2);
+  return FinishLaunch();
+}
+
+int r4dxb_spec_accept(const int* next_ids, const int* draft, int T, int* out, int* n_replay, void* stream) {
+  if (T < 1 || T > 64) return R4DXB_BAD_ARG;
+  SpecAcceptKernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(next_ids, draft, T, out, n_replay);
   return FinishLaunch();
 }
 

@@ -328,3 +328,12 @@ def attn_prefill(q, qg, cache, block_table, k_descale, v_descale, out, T: int, H
     _check(_lib().r4dxb_attn_prefill(_p(q), _p(qg), _p(cache), _p(block_table), _p(k_descale), _p(v_descale), _p(out),
                                      T, Hq, Hkv, D, pos0, 1 if gated else 0, _stream()), "attn_prefill")
     return out
+
+
+register_cuda_sig("r4dxb_spec_accept", _I, [_P, _P, _I, _P, _P, _P])
+
+
+def spec_accept(next_ids: torch.Tensor, draft: torch.Tensor, T: int, out: torch.Tensor, n_replay: Optional[torch.Tensor]) -> torch.Tensor:
+    """out[0] = rows to commit, out[1..] = emitted tokens for a T-row speculative window."""
+    _check(_lib().r4dxb_spec_accept(_p(next_ids), _p(draft), T, _p(out), _p(n_replay), _stream()), "spec_accept")
+    return out

@@ -1,0 +1,29 @@
+"""Argument parsers and the converter round trip (CPU)."""
+import torch
+
+from r4dx_b200.cli.args import cli_parser, convert_parser, server_parser
+
+
+def test_parsers_accept_the_documented_flags():
+    a = cli_parser().parse_args(["--model", "m.r4dxb", "--prompt", "hi", "--max-tokens", "5", "--tp", "2", "--mtp", "3",
+                                 "--temperature", "0.7", "--top-k", "40", "--stats", "--think", "off", "--pp", "2", "--hybrid"])
+    assert a.tp == 2 and a.mtp == 3 and a.top_k == 40 and a.think == "off" and a.hybrid
+    s = server_parser().parse_args(["--model", "m", "--port", "9000", "--max-queue", "3", "--request-log", "x.jsonl",
+                                    "--default-temperature", "0.5", "--batch", "4", "--prompt-checkpoint", "off"])
+    assert s.port == 9000 and s.max_queue == 3 and s.default_temperature == 0.5 and s.batch == 4
+    c = convert_parser().parse_args(["--input", "random:tiny", "--output", "o", "--kb-plan", "kb4", "--selftest"])
+    assert c.kb_plan == "kb4" and c.selftest
+
+
+def test_convert_roundtrip_and_reuse(tmp_path):
+    from r4dx_b200.cli import convert
+    from r4dx_b200.quant.weights import load_weight_set
+    out = str(tmp_path / "tiny.r4dxb")
+    assert convert.main(["--input", "random:tiny", "--output", out, "--layers", "1", "--kb-plan", "kb4", "--selftest"]) == 0
+    cfg, q = load_weight_set(out)
+    assert cfg.num_hidden_layers == 1 and "lm_head" in q
+    out2 = str(tmp_path / "tiny2.r4dxb")
+    assert convert.main(["--input", "random:tiny", "--output", out2, "--layers", "1", "--kb-plan", "kb4",
+                         "--reuse-tensors-from", out]) == 0
+    _, q2 = load_weight_set(out2)
+    assert torch.equal(q2["text.layers.0.mlp.down"].words, q["text.layers.0.mlp.down"].words)

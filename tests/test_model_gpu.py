@@ -89,3 +89,44 @@ def test_chunked_prefill_matches_small_batch_prefill(tiny):
     tb = b.generate_greedy(torch.tensor([tok], dtype=torch.int32), 6, use_graph=False)
     assert int(la.argmax()) == tok
     assert sum(int(x == y) for x, y in zip(ta, tb)) >= 5
+
+
+def test_speculative_verify_is_lossless(tiny):
+    """Windows with correct, partly wrong and fully wrong drafts reproduce the plain greedy stream."""
+    from r4dx_b200.models.hybrid import HybridModel
+    cfg, q, _ = tiny
+    ids = torch.randint(0, cfg.vocab_size, (21,), generator=torch.Generator().manual_seed(5)).to(torch.int32)
+    plain = HybridModel(cfg, _to_dev(q), max_ctx=256)
+    ref = plain.generate_greedy(ids, 24, use_graph=False)
+    spec = HybridModel(cfg, _to_dev(q), max_ctx=256)
+    tok = spec.prefill(ids)
+    out = [tok]
+    g = torch.Generator().manual_seed(0)
+    rounds = 0
+    while len(out) < 24:
+        k = len(out)
+        # drafts: the true continuation with a wrong token injected at a random spot (or none)
+        truth = ref[k:k + 5]
+        drafts = list(truth)
+        bad = int(torch.randint(0, 7, (1,), generator=g))
+        if bad < len(drafts):
+            drafts[bad] = (drafts[bad] + 1) % cfg.vocab_size
+        emitted = spec.verify_window(out[-1], drafts)
+        assert 1 <= len(emitted) <= len(drafts) + 1
+        out += emitted
+        rounds += 1
+    assert out[:24] == ref[:24]
+    assert rounds < 23          # speculation did accept drafts
+
+
+def test_checkpoint_restore_replays_identically(tiny):
+    from r4dx_b200.models.hybrid import HybridModel
+    cfg, q, _ = tiny
+    ids = torch.randint(0, cfg.vocab_size, (30,), generator=torch.Generator().manual_seed(6)).to(torch.int32)
+    m = HybridModel(cfg, _to_dev(q), max_ctx=256)
+    tok = m.prefill(ids)
+    ck = m.save_checkpoint()
+    a = [m.decode_step_greedy(t) for t in [tok, 5, 9]]
+    m.restore_checkpoint(ck)
+    b = [m.decode_step_greedy(t) for t in [tok, 5, 9]]
+    assert a == b

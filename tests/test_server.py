@@ -1,0 +1,153 @@
+"""Serving layer on CPU fakes: engine, prefix reuse, recovery, OpenAI HTTP API, SSE, parsers, request log."""
+import json
+import threading
+import urllib.error
+import urllib.request
+
+import pytest
+
+from r4dx_b200.runtime.prefix_state import PrefixState
+from r4dx_b200.runtime.sampler import SampleParams
+from r4dx_b200.runtime.text_model import FakeTextModel
+from r4dx_b200.runtime.tokenizer import ByteTokenizer, ChatTemplate, StreamDecoder
+from r4dx_b200.server.engine import Engine, GenRequest, QueueFull
+from r4dx_b200.server.http_server import ApiServer
+from r4dx_b200.server.parsers import QwenToolCallParser, ReasoningSplitter
+from r4dx_b200.server.request_log import RequestLog
+
+
+def test_prefix_plan():
+    p = PrefixState()
+    assert p.plan([1, 2, 3]).action == "reset"
+    p.commit([1, 2, 3, 9, 9], checkpoint_len=3)
+    assert p.plan([1, 2, 3, 9, 9, 4]).action == "extend"
+    pl = p.plan([1, 2, 3, 7])
+    assert pl.action == "restore" and pl.feed_from == 3
+    assert p.plan([5, 5]).action == "reset"
+    assert p.plan([1, 2, 3]).action == "reset"       # nothing left to feed -> no fresh logits -> start over
+    p.invalidate()
+    assert p.plan([1, 2, 3, 9, 9, 4]).action == "reset"
+
+
+def test_tokenizer_stream_decoder_holds_partial_utf8():
+    tk = ByteTokenizer()
+    ids = tk.encode("héllo <|im_end|>")
+    assert tk.decode(ids) == "héllo "
+    d = StreamDecoder(tk)
+    pieces = [d.feed(i) for i in tk.encode("é")]
+    assert pieces == ["", "é"]
+    assert "<|im_start|>user" in ChatTemplate().render([{"role": "user", "content": "hi"}])
+
+
+def test_reasoning_splitter_and_tool_parser_incremental():
+    s = ReasoningSplitter()
+    c = r = ""
+    for piece in ["<th", "ink>let me ", "see</thi", "nk>\nans", "wer"]:
+        dc, dr = s.feed(piece)
+        c += dc; r += dr
+    dc, dr = s.flush()
+    assert (c + dc, r + dr) == ("answer", "let me see")
+    t = QwenToolCallParser()
+    out = ""
+    for piece in ['ok <tool_', 'call>{"name": "f", "argum', 'ents": {"x": 1}}</tool_call> done']:
+        out += t.feed(piece)
+    out += t.flush()
+    assert out == "ok  done" and t.calls[0]["function"]["name"] == "f"
+    assert json.loads(t.calls[0]["function"]["arguments"]) == {"x": 1}
+
+
+def _engine(**kw):
+    return Engine(FakeTextModel(vocab=300, **kw), ByteTokenizer(300), max_queue=2)
+
+
+def test_engine_generates_and_reuses_prefix(tmp_path):
+    log = str(tmp_path / "req.jsonl")
+    eng = Engine(FakeTextModel(vocab=300), ByteTokenizer(300), request_log=RequestLog(log))
+    tk = ByteTokenizer(300)
+    p1 = tk.encode("hello world")
+    r1 = eng.generate(GenRequest(p1, max_tokens=8, params=SampleParams(temperature=0)))
+    assert r1.error is None and 1 <= r1.completion_tokens <= 8 and r1.reused_tokens == 0
+    # same prompt + the answer + a new turn: extends the fed prefix
+    p2 = p1 + r1.token_ids + tk.encode(" more")
+    r2 = eng.generate(GenRequest(p2, max_tokens=4, params=SampleParams(temperature=0)))
+    assert r2.reused_tokens >= len(p1)
+    # a different continuation of the latest prompt: the model cannot rewind, the prompt checkpoint can
+    r3 = eng.generate(GenRequest(p2 + tk.encode("!!"), max_tokens=4, params=SampleParams(temperature=0)))
+    assert r3.reused_tokens == len(p2)
+    # determinism: greedy output is a pure function of the tokens
+    eng2 = Engine(FakeTextModel(vocab=300), ByteTokenizer(300))
+    assert eng2.generate(GenRequest(p1, max_tokens=8, params=SampleParams(temperature=0))).token_ids == r1.token_ids
+    lines = [json.loads(l) for l in open(log)]
+    assert len(lines) == 3 and "prompt_ids" not in lines[0] and lines[1]["prefix_cache_tokens"] >= len(p1)
+    eng.shutdown(); eng2.shutdown()
+
+
+def test_sampled_is_seed_deterministic():
+    eng = _engine()
+    tk = ByteTokenizer(300)
+    a = eng.generate(GenRequest(tk.encode("abc"), max_tokens=12, params=SampleParams(temperature=0.9, top_p=0.9, seed=7)))
+    b = eng.generate(GenRequest(tk.encode("abc"), max_tokens=12, params=SampleParams(temperature=0.9, top_p=0.9, seed=7)))
+    c = eng.generate(GenRequest(tk.encode("abc"), max_tokens=12, params=SampleParams(temperature=0.9, top_p=0.9, seed=8)))
+    assert a.token_ids == b.token_ids and a.token_ids != c.token_ids
+    eng.shutdown()
+
+
+def test_engine_recovers_after_a_model_fault():
+    eng = _engine(fail_at_call=2)
+    tk = ByteTokenizer(300)
+    bad = eng.generate(GenRequest(tk.encode("xyz"), max_tokens=8, params=SampleParams(temperature=0)))
+    assert bad.error and "injected" in bad.error
+    good = eng.generate(GenRequest(tk.encode("xyz"), max_tokens=4, params=SampleParams(temperature=0)))
+    assert good.error is None and good.reused_tokens == 0
+    eng.shutdown()
+
+
+def _post(port, path, body):
+    req = urllib.request.Request(f"http://127.0.0.1:{port}{path}", data=json.dumps(body).encode(),
+                                 headers={"Content-Type": "application/json"})
+    return urllib.request.urlopen(req, timeout=20)
+
+
+def test_http_api_roundtrip():
+    eng = _engine()
+    srv = ApiServer(eng, ByteTokenizer(300), ChatTemplate(), "fake-model", port=0)
+    srv.start()
+    try:
+        assert json.load(urllib.request.urlopen(f"http://127.0.0.1:{srv.port}/health"))["status"] == "ok"
+        assert json.load(urllib.request.urlopen(f"http://127.0.0.1:{srv.port}/v1/models"))["data"][0]["id"] == "fake-model"
+        r = json.load(_post(srv.port, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 6, "temperature": 0}))
+        assert r["object"] == "chat.completion" and r["choices"][0]["finish_reason"] in ("stop", "length")
+        assert r["usage"]["completion_tokens"] <= 6 and "timings" in r
+        c = json.load(_post(srv.port, "/v1/completions", {"prompt": "abc", "max_tokens": 3, "temperature": 0}))
+        assert c["object"] == "text_completion"
+        # streaming
+        resp = _post(srv.port, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 5, "temperature": 0, "stream": True})
+        events = [l.decode().strip() for l in resp if l.strip()]
+        assert events[-1] == "data: [DONE]"
+        last = json.loads(events[-2][6:])
+        assert last["choices"][0]["finish_reason"] in ("stop", "length") and "usage" in last
+        # validation errors
+        for body in ({"messages": []}, {"messages": [{"role": "user", "content": "x"}], "max_tokens": 0},
+                     {"messages": [{"role": "user", "content": "x"}], "temperature": "hot"}):
+            with pytest.raises(urllib.error.HTTPError) as e:
+                _post(srv.port, "/v1/chat/completions", body)
+            assert e.value.code == 400
+    finally:
+        srv.stop(); eng.shutdown()
+
+
+def test_queue_full_gives_429():
+    class Slow(FakeTextModel):
+        def decode_step(self, token):
+            import time
+            time.sleep(0.05)
+            return super().decode_step(token)
+    eng = Engine(Slow(vocab=300), ByteTokenizer(300), max_queue=1)
+    tk = ByteTokenizer(300)
+    jobs = [eng.submit(GenRequest(tk.encode("a"), max_tokens=20, params=SampleParams(temperature=0)))]
+    with pytest.raises(QueueFull):
+        for _ in range(4):
+            jobs.append(eng.submit(GenRequest(tk.encode("a"), max_tokens=20, params=SampleParams(temperature=0))))
+    for j in jobs:
+        j.cancelled = True
+    eng.shutdown()
