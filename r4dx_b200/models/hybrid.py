@@ -232,10 +232,12 @@ class HybridModel:
             self.comm.row_parallel_linear(lin, x, b.x[:T], prologue)
 
     # ---- forward --------------------------------------------------------------------------------
-    def forward_rows(self, T: int, want_logits: bool = True) -> None:
-        """Runs the T rows staged in ``buf.ids`` / ``buf.positions``; results in ``buf.logits`` / ``buf.next_ids``."""
+    def forward_rows(self, T: int, want_logits: bool = True, skip_embed: bool = False) -> None:
+        """Runs the T rows staged in ``buf.ids`` / ``buf.positions``; results in ``buf.logits`` / ``buf.next_ids``.
+        With ``skip_embed`` the caller has already placed the layer-0 input in ``buf.x``."""
         cfg, b, w = self.cfg, self.buf, self.w
-        K.embed_gather(b.ids[:T], w["text.embed_tokens"], out=b.x[:T])
+        if not skip_embed:
+            K.embed_gather(b.ids[:T], w["text.embed_tokens"], out=b.x[:T])
         for i in range(cfg.num_hidden_layers):
             # the two RMSNorms and the SwiGLU of a layer run inside the prologues of the linears
             if cfg.is_attention_layer(i):
@@ -315,7 +317,7 @@ class HybridModel:
         self.pending_rows = 0
         b.n_replay.zero_()
 
-    def forward_chunk(self, T: int, want_logits: bool) -> None:
+    def forward_chunk(self, T: int, want_logits: bool, skip_embed: bool = False) -> None:
         """Runs T (> MAX_ROWS) rows staged in the chunk buffers at positions self.pos .. ; commits them."""
         cfg, w, cb = self.cfg, self.w, self._cb
         H = cfg.hidden_size
@@ -323,7 +325,8 @@ class HybridModel:
         Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
         x, h = cb["x"][:T], cb["h"][:T]
         pos0 = self.pos
-        K.embed_gather(cb["ids"][:T], w["text.embed_tokens"], out=x)
+        if not skip_embed:
+            K.embed_gather(cb["ids"][:T], w["text.embed_tokens"], out=x)
         for i in range(cfg.num_hidden_layers):
             p = f"text.layers.{i}."
             K.rmsnorm(x, w[p + "input_layernorm"], cfg.rms_norm_eps, out=h)
@@ -373,12 +376,17 @@ class HybridModel:
         else:
             self.comm.row_parallel_chunk(lin, inp, x, cb, fused_silu_mul)
 
-    def prefill(self, ids: torch.Tensor, chunk: int = 2048) -> int:
-        """Cold or warm prefill of ``ids`` at the current position; returns the greedy next token."""
+    def prefill(self, ids: torch.Tensor, chunk: int = 2048, hook=None) -> int:
+        """Cold or warm prefill of ``ids`` at the current position; returns the greedy next token.
+        ``hook(start, T, hidden_rows)`` is called after every chunk with the final hidden states of its rows
+        (drafters keep their own caches in lock-step with it)."""
         ids = ids.to(torch.int32)
         n = ids.numel()
         if n <= MAX_ROWS:
-            return self.prefill_small(ids)
+            tok = self.prefill_small(ids)
+            if hook is not None:
+                hook(0, n, self.buf.x[:n])
+            return tok
         if self.pos + n > self.max_ctx:
             raise ValueError("context overflow")
         self.commit_pending()
@@ -392,10 +400,14 @@ class HybridModel:
                 # short tail: the small-batch path logs its rows instead of committing them
                 self.feed(ids[s:e], want_logits=True)
                 last_small = True
+                if hook is not None:
+                    hook(s, T, self.buf.x[:T])
             else:
                 cb["ids"][:T].copy_(ids[s:e].to(self.device), non_blocking=True)
                 cb["positions"][:T].copy_(torch.arange(self.pos, self.pos + T, dtype=torch.int32, device=self.device))
                 self.forward_chunk(T, want_logits=(e == n))
+                if hook is not None:
+                    hook(s, T, cb["x"][:T])
             s = e
         K.check_gemm_status(self.device)
         if last_small:

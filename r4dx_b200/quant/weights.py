@@ -41,7 +41,7 @@ def moe_kb_rule(name: str) -> int:
 
 def is_quantized_linear(name: str) -> bool:
     leaf = name.split(".")[-1]
-    return leaf in ("qg", "k", "v", "o", "in_proj_qkv", "in_proj_z", "out_proj", "gate_up", "down")
+    return leaf in ("qg", "k", "v", "o", "in_proj_qkv", "in_proj_z", "out_proj", "gate_up", "down", "fc")
 
 
 def quantize_weight_set(cfg: ModelConfig, w: Dict[str, torch.Tensor], layout: str = "trellis",

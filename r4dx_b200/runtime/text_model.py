@@ -110,7 +110,8 @@ class LocalTextModel(TextModel):
     def prefill(self, ids: Sequence[int]) -> int:
         self._graph_active = False
         t = torch.as_tensor(list(ids), dtype=torch.int32)
-        tok = self.m.prefill(t)
+        hook = self.drafter.prefill_hook(t) if self.drafter is not None else None
+        tok = self.m.prefill(t, hook=hook)
         if self.drafter is not None:
             self.drafter.after_prefill(t, tok)
         return tok

@@ -130,3 +130,26 @@ def test_checkpoint_restore_replays_identically(tiny):
     m.restore_checkpoint(ck)
     b = [m.decode_step_greedy(t) for t in [tok, 5, 9]]
     assert a == b
+
+
+def test_mtp_speculation_equals_plain_greedy():
+    """Lossless: with an MTP drafter (random weights -> few accepts) the token stream is the plain greedy one,
+    and the drafter's KV stays in lock-step across rounds."""
+    from r4dx_b200.models.hybrid import HybridModel
+    from r4dx_b200.models.mtp import MtpDrafter
+    from r4dx_b200.models.oracle import init_weights
+    from r4dx_b200.quant.weights import quantize_weight_set
+    from r4dx_b200.runtime.text_model import LocalTextModel
+    cfg = tiny_hybrid_config()
+    q = _to_dev(quantize_weight_set(cfg, init_weights(cfg, 0, with_mtp=True)))
+    ids = torch.randint(0, cfg.vocab_size, (37,), generator=torch.Generator().manual_seed(8)).to(torch.int32)
+    plain = HybridModel(cfg, q, max_ctx=256)
+    ref = plain.generate_greedy(ids, 20, use_graph=False)
+    main = HybridModel(cfg, q, max_ctx=256)
+    tm = LocalTextModel(main, drafter=MtpDrafter(main, q))
+    tok = tm.prefill(ids.tolist())
+    out = [tok]
+    while len(out) < 20:
+        out += tm.decode_step_spec_greedy(out[-1], 3)
+    assert out[:20] == ref[:20]
+    assert tm.drafter.head.pos == main.pos - 1
