@@ -115,6 +115,12 @@ class HybridModel:
                 p = f"text.layers.{i}.gdn."
                 self.ab_w[i] = torch.cat([weights[p + "in_proj_a"], weights[p + "in_proj_b"]], 0).contiguous()
         self._alloc_state(attn_splits)
+        self.moe = {}
+        if cfg.is_moe:
+            from .moe import MoeBlock
+            er = getattr(comm, "expert_range", None) if comm is not None else None
+            for i in range(cfg.num_hidden_layers):
+                self.moe[i] = MoeBlock(cfg, weights, i, self.device, MAX_ROWS, *(er or (0, cfg.num_experts)))
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.pos = 0                           # host mirror of the next position
         self.pending_rows = 0                  # rows of the last call not yet committed to the GDN base state
@@ -155,7 +161,7 @@ class HybridModel:
             x=e(R, H), h=e(R, H), mixed=e(R, cfg.conv_dim), z=e(R, cfg.value_dim),
             ab=e(R, 2 * Hv, dtype=torch.float32), core=e(R, max(cfg.value_dim, cfg.q_dim)),
             qg=e(R, 2 * cfg.q_dim), k=e(R, cfg.kv_dim), v=e(R, cfg.kv_dim), q=e(R, cfg.q_dim),
-            gate_up=e(R, 2 * cfg.intermediate_size), act=e(R, cfg.intermediate_size),
+            gate_up=e(R, 2 * max(cfg.intermediate_size, 1)), act=e(R, max(cfg.intermediate_size, 1)),
             logits=e(R, V, dtype=torch.float32), argmax_scratch=e(2 * R * 256, dtype=torch.float32),
             part_acc=e(attn_splits * Hkv * G * D, dtype=torch.float32),
             part_ml=e(attn_splits * Hkv * G * 2, dtype=torch.float32))
@@ -174,7 +180,7 @@ class HybridModel:
 
     def streamed_bytes_per_token(self) -> int:
         """Bytes every decoded token must read: all quantized linears + the LM head shard."""
-        return sum(l.nbytes for l in self.lin.values())
+        return sum(l.nbytes for l in self.lin.values() if ".experts." not in l.name) + sum(m.nbytes for m in self.moe.values())
 
     # ------------------------------------------------------------------------------------------
     def reset(self) -> None:
@@ -218,6 +224,13 @@ class HybridModel:
 
     def _mlp(self, i: int, T: int) -> None:
         cfg, b, w = self.cfg, self.buf, self.w
+        if cfg.is_moe:
+            K.rmsnorm(b.x[:T], w[f"text.layers.{i}.post_attention_layernorm"], cfg.rms_norm_eps, out=b.h[:T])
+            if self.comm is not None and hasattr(self.comm, "moe_forward"):
+                self.comm.moe_forward(self.moe[i], b.h[:T], b.x[:T], T)
+            else:
+                self.moe[i].forward(b.h[:T], b.x[:T], T)
+            return
         p = f"text.layers.{i}.mlp."
         self.lin[p + "gate_up"](b.x[:T], out=b.gate_up[:T], prologue=K.PRO_RMSNORM,
                                 norm_w=w[f"text.layers.{i}.post_attention_layernorm"], eps=cfg.rms_norm_eps)

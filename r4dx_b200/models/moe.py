@@ -1,0 +1,111 @@
+"""Mixture-of-experts feed-forward block of the hybrid MoE variant: 512 routed experts (top-10, softmax
+router, renormalised) + one sigmoid-gated shared expert, experts stored as stacked trellis tensors.
+
+Single rank: router -> device plan (pairs sorted by expert) -> grouped gate_up -> grouped down with the
+SwiGLU in its prologue -> deterministic combine.  Nothing about the routing is read back by the host
+(the reference's host-routed block does one D2H of ids per call:
+reference src/model/qwen4exp/include/r4dx/model/qwen4exp/moe_block.h:1-20, grouped decode
+src/model/qwen4exp/kernels/moe_trellis_decode.hip:86-416).  Under expert parallelism (``parallel/ep.py``)
+the same grouped kernels run on each rank's expert slice and the combine sums across ranks.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import kernels as K
+from ..quant.trellis import TrellisWeight
+
+BF = torch.bfloat16
+
+
+@dataclass
+class ExpertStack:
+    """E experts' packed weights back to back: words [E * per_expert], suh [E, K], svh [E, N]."""
+    words: torch.Tensor
+    suh: torch.Tensor
+    svh: torch.Tensor
+    E: int
+    N: int
+    K: int
+    kb: int
+
+    @staticmethod
+    def from_list(ws) -> "ExpertStack":
+        w0 = ws[0]
+        assert all(w.kb == w0.kb and w.N == w0.N and w.K == w0.K for w in ws), "experts of a stack share shape and bit width"
+        return ExpertStack(torch.cat([w.words for w in ws]).contiguous(), torch.stack([w.suh for w in ws]).contiguous(),
+                           torch.stack([w.svh for w in ws]).contiguous(), len(ws), w0.N, w0.K, w0.kb)
+
+    @property
+    def nbytes(self) -> int:
+        return self.words.numel() * 4 + self.suh.numel() * 2 + self.svh.numel() * 2
+
+
+class MoeBlock:
+    """One layer's routed + shared experts.  ``e_begin/e_count``: the expert slice this rank holds."""
+
+    def __init__(self, cfg: ModelConfig, weights: Dict[str, object], layer: int, device, max_rows: int, e_begin: int = 0,
+                 e_count: Optional[int] = None, tmax: int = 2):
+        self.cfg = cfg
+        p = f"text.layers.{layer}.moe."
+        self.e_begin = e_begin
+        self.e_count = e_count if e_count is not None else cfg.num_experts
+        self.gate_up = ExpertStack.from_list([weights[p + f"experts.{e}.gate_up"] for e in range(e_begin, e_begin + self.e_count)])
+        self.down = ExpertStack.from_list([weights[p + f"experts.{e}.down"] for e in range(e_begin, e_begin + self.e_count)])
+        self.router = weights[p + "router"]
+        self.shared_gate = weights[p + "shared_gate"]
+        self.shared_gu: TrellisWeight = weights[p + "shared.gate_up"]
+        self.shared_down: TrellisWeight = weights[p + "shared.down"]
+        self.tmax = tmax
+        self.k = cfg.num_experts_per_tok
+        H, I = cfg.hidden_size, cfg.moe_intermediate_size
+        R, k, E = max_rows, self.k, cfg.num_experts
+        z = lambda *s, dtype=BF: torch.zeros(*s, dtype=dtype, device=device)
+        self.logits = z(R, E, dtype=torch.float32)
+        self.ids = z(R, k, dtype=torch.int32)
+        self.wts = z(R, k, dtype=torch.float32)
+        self.offsets = z(self.e_count + 1, dtype=torch.int32)
+        self.perm = z(R * k, dtype=torch.int32)
+        self.gu_pairs = z(R * k, 2 * I)
+        self.y_pairs = z(R * k, H)
+        self.sh_gu = z(R, 2 * cfg.shared_expert_intermediate_size)
+        self.sh_out = z(R, H)
+        self.sh_gate = z(R, 1, dtype=torch.float32)
+        self.ks_gu = K.pick_ksplit(self.gate_up.N, self.gate_up.K, target_ctas=1)
+        self.ks_dn = K.pick_ksplit(self.down.N, self.down.K, target_ctas=1)
+
+    def route(self, h: torch.Tensor, T: int) -> None:
+        K.bf16_gemv(self.router, h, out=self.logits[:T])
+        K.moe_router(self.logits[:T], self.k, self.cfg.norm_topk_prob, self.ids, self.wts)
+        K.moe_plan(self.ids, T * self.k, self.cfg.num_experts, self.e_begin, self.e_count, self.offsets, self.perm)
+
+    def experts(self, h: torch.Tensor, T: int) -> None:
+        """y_pairs[pair] = down_e(silu(gate_e h) * up_e h) for every pair routed to a local expert."""
+        n_pass = (T + self.tmax - 1) // self.tmax
+        g, d = self.gate_up, self.down
+        K.trellis_gemv_grouped(g.words, g.suh, g.svh, h, self.gu_pairs, self.offsets, self.perm, self.k, n_pass, self.tmax,
+                               K.PRO_NONE, g.E, g.N, g.K, g.kb, self.ks_gu)
+        K.trellis_gemv_grouped(d.words, d.suh, d.svh, self.gu_pairs, self.y_pairs, self.offsets, self.perm, 1, n_pass, self.tmax,
+                               K.PRO_SILU_MUL, d.E, d.N, d.K, d.kb, self.ks_dn)
+
+    def shared(self, h: torch.Tensor, T: int) -> None:
+        for s in range(0, T, 8):
+            e = min(T, s + 8)
+            K.trellis_gemv(self.shared_gu, h[s:e], out=self.sh_gu[s:e])
+            K.trellis_gemv(self.shared_down, self.sh_gu[s:e], out=self.sh_out[s:e], prologue=K.PRO_SILU_MUL)
+        K.bf16_gemv(self.shared_gate, h, out=self.sh_gate[:T])
+
+    def forward(self, h: torch.Tensor, x: torch.Tensor, T: int) -> None:
+        """x[T, H] += moe(h) (h = post-attention RMSNorm of x)."""
+        self.route(h, T)
+        self.experts(h, T)
+        self.shared(h, T)
+        K.moe_combine(self.y_pairs, self.ids, self.wts, self.sh_out, self.sh_gate, x, x, T, self.cfg.hidden_size, self.k)
+
+    @property
+    def nbytes(self) -> int:
+        return self.gate_up.nbytes + self.down.nbytes + self.shared_gu.nbytes + self.shared_down.nbytes

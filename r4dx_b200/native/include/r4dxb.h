@@ -100,6 +100,16 @@ int r4dxb_trellis_gemv_ex(const void* words, const void* suh, const void* svh, c
                           const void* residual, const void* norm_w, float eps, int prologue, int T, int N, int K, int kb,
                           int ksplit, void* stream);
 
+/* ---- mixture of experts ---------------------------------------------------------------------------- */
+int r4dxb_moe_router(const float* logits, int T, int E, int k, int renorm, int* ids, float* weights, void* stream);
+int r4dxb_moe_plan(const int* ids, int npairs, int E, int e_begin, int e_count, int* offsets, int* perm, void* stream);
+int r4dxb_moe_combine(const void* y_pairs, const int* ids, const float* weights, const void* shared, const float* shared_gate,
+                      const void* residual, void* out, int T, int H, int k, void* stream);
+/* one launch for every local expert; experts' packed weights lie back to back; tmax in {2, 8} */
+int r4dxb_trellis_gemv_grouped(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                               const int* offsets, const int* perm, int in_div, int pass, int tmax, int prologue,
+                               int experts, int N, int K, int kb, int ksplit, void* stream);
+
 /* ---- tensor parallel: collectives issued from inside the compute kernels ------------------------- */
 /* Row-parallel trellis linear (T <= 8) + all-reduce over NVLink peer memory + residual, one kernel.
  * recv[p]: rank p's receive buffer, [2][world][8][N] (fp32 value, u32 sequence) pairs, zero-initialised and

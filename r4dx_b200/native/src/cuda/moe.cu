@@ -1,0 +1,159 @@
+// Mixture-of-experts routing and combine kernels (softmax top-k router, device-side plan, weighted
+// combine with the shared expert).  The grouped expert GEMV itself lives in trellis_gemv.cu.
+//
+// Semantics (reference: src/model/qwen4exp/include/r4dx/model/qwen4exp/moe_kernels.h:18-56):
+//   * router: fp32 softmax over the expert logits, top-k (k <= 16, experts <= 1024), optional
+//     renormalisation, weights rounded through bf16; ties go to the larger logit, then the lower id;
+//   * plan: (token, slot) pairs sorted by expert id (stable), with per-expert offsets, built on
+//     the device so that no routing decision is read back by the host;
+//   * combine: out[t] = residual[t] + sum_j w[t,j] * y[pair(t,j)] in ascending expert id (a fixed
+//     order: no atomics) + sigmoid(shared_gate[t]) * shared[t], one bf16 rounding.
+#include "common.cuh"
+
+namespace r4dxb {
+namespace {
+
+constexpr int kMaxK = 16;
+
+// one warp per token row
+__global__ void MoeRouterKernel(const float* __restrict__ logits, int T, int E, int k, int renorm,
+                                int* __restrict__ ids, float* __restrict__ weights) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const float* row = logits + static_cast<size_t>(t) * E;
+  float mx = -INFINITY;
+  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
+  mx = WarpMax(mx);
+  float z = 0.f;
+  for (int e = lane; e < E; e += 32) z += __expf(row[e] - mx);
+  z = WarpSum(z);
+  // k rounds of arg-max over what is left; a lane keeps a bitmask of its taken entries (E <= 1024 -> 32 per lane)
+  uint32_t taken = 0;
+  float wsum = 0.f;
+  float wv[kMaxK];
+  int wi[kMaxK];
+  for (int j = 0; j < k; ++j) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane, s = 0; e < E; e += 32, ++s) {
+      if (taken & (1u << s)) continue;
+      const float v = row[e];
+      if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+    const float p = __expf(bv - mx) / z;
+    wv[j] = p;
+    wi[j] = bi;
+    wsum += p;
+  }
+  if (lane == 0) {
+    for (int j = 0; j < k; ++j) {
+      const float w = renorm ? wv[j] / wsum : wv[j];
+      ids[static_cast<size_t>(t) * k + j] = wi[j];
+      weights[static_cast<size_t>(t) * k + j] = __bfloat162float(__float2bfloat16(w));
+    }
+  }
+}
+
+// Single CTA: counting sort of the T*k pairs by expert (stable in pair order).
+__global__ void MoePlanKernel(const int* __restrict__ ids, int npairs, int E, int e_begin, int e_count,
+                              int* __restrict__ offsets, int* __restrict__ perm) {
+  extern __shared__ int cnt[];     // [e_count + 1]
+  for (int e = threadIdx.x; e <= e_count; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < npairs; p += blockDim.x) {
+    const int e = ids[p] - e_begin;
+    if (e >= 0 && e < e_count) atomicAdd(&cnt[e + 1], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int e = 0; e < e_count; ++e) cnt[e + 1] += cnt[e];
+    for (int e = 0; e <= e_count; ++e) offsets[e] = cnt[e];
+    // stable placement: pairs in ascending index (serial, npairs is a few hundred)
+    for (int p = 0; p < npairs; ++p) {
+      const int e = ids[p] - e_begin;
+      if (e >= 0 && e < e_count) perm[cnt[e]++] = p;
+    }
+  }
+}
+
+// grid T, block 256: out[t] = residual + sum_j w_j y[pair] (ascending expert id) + sigmoid(sg) * shared
+__global__ void MoeCombineKernel(const __nv_bfloat16* __restrict__ y_pairs, const int* __restrict__ ids,
+                                 const float* __restrict__ weights, const __nv_bfloat16* __restrict__ shared,
+                                 const float* __restrict__ shared_gate, const __nv_bfloat16* __restrict__ residual,
+                                 __nv_bfloat16* __restrict__ out, int H, int k) {
+  const int t = blockIdx.x;
+  __shared__ int order[kMaxK];
+  __shared__ float w[kMaxK];
+  if (threadIdx.x == 0) {
+    int idx[kMaxK];
+    for (int j = 0; j < k; ++j) idx[j] = j;
+    for (int a = 1; a < k; ++a) {          // insertion sort of the slots by expert id
+      const int v = idx[a];
+      int b = a - 1;
+      while (b >= 0 && ids[t * k + idx[b]] > ids[t * k + v]) { idx[b + 1] = idx[b]; --b; }
+      idx[b + 1] = v;
+    }
+    for (int j = 0; j < k; ++j) { order[j] = idx[j]; w[j] = weights[t * k + idx[j]]; }
+  }
+  __syncthreads();
+  const float sg = shared_gate ? Sigmoid(shared_gate[t]) : 0.f;
+  for (int c = threadIdx.x * 2; c < H; c += blockDim.x * 2) {
+    float a0 = 0.f, a1 = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const uint32_t v = *reinterpret_cast<const uint32_t*>(y_pairs + (static_cast<size_t>(t) * k + order[j]) * H + c);
+      a0 = fmaf(w[j], BfLo(v), a0);
+      a1 = fmaf(w[j], BfHi(v), a1);
+    }
+    if (shared) {
+      const uint32_t s = *reinterpret_cast<const uint32_t*>(shared + static_cast<size_t>(t) * H + c);
+      a0 = fmaf(sg, BfLo(s), a0);
+      a1 = fmaf(sg, BfHi(s), a1);
+    }
+    if (residual) {
+      const uint32_t r = *reinterpret_cast<const uint32_t*>(residual + static_cast<size_t>(t) * H + c);
+      a0 += BfLo(r);
+      a1 += BfHi(r);
+    }
+    *reinterpret_cast<uint32_t*>(out + static_cast<size_t>(t) * H + c) = PackBf16(a0, a1);
+  }
+}
+
+}  // namespace
+}  // namespace r4dxb
+
+using namespace r4dxb;
+
+extern "C" {
+
+int r4dxb_moe_router(const float* logits, int T, int E, int k, int renorm, int* ids, float* weights, void* stream) {
+  if (T < 1 || k < 1 || k > kMaxK || E > 1024 || E < k) return R4DXB_BAD_ARG;
+  MoeRouterKernel<<<(T + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, T, E, k, renorm, ids, weights);
+  return FinishLaunch();
+}
+
+/* offsets: [e_count + 1], perm: [npairs] pair indices sorted by expert (only experts in [e_begin, e_begin+e_count)) */
+int r4dxb_moe_plan(const int* ids, int npairs, int E, int e_begin, int e_count, int* offsets, int* perm, void* stream) {
+  if (npairs < 1 || e_count < 1 || e_count > 8192) return R4DXB_BAD_ARG;
+  MoePlanKernel<<<1, 256, (e_count + 1) * sizeof(int), static_cast<cudaStream_t>(stream)>>>(ids, npairs, E, e_begin, e_count,
+                                                                                             offsets, perm);
+  return FinishLaunch();
+}
+
+int r4dxb_moe_combine(const void* y_pairs, const int* ids, const float* weights, const void* shared, const float* shared_gate,
+                      const void* residual, void* out, int T, int H, int k, void* stream) {
+  if (T < 1 || k < 1 || k > kMaxK || H % 2) return R4DXB_BAD_ARG;
+  MoeCombineKernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y_pairs), ids, weights, static_cast<const __nv_bfloat16*>(shared), shared_gate,
+      static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), H, k);
+  return FinishLaunch();
+}
+
+}  // extern "C"

@@ -67,9 +67,16 @@ struct GemvArgs {
   const __nv_bfloat16* norm_w;     // prologue mode 1
   float eps;
   int T, N, K, kblocks_per_cta, stages;
+  // grouped (mixture-of-experts) mode: blockIdx.z = local expert; the expert's rows come from a
+  // device-side plan, so no routing decision is ever read back by the host
+  const int* g_offsets;            // [experts + 1] into g_perm
+  const int* g_perm;               // pair indices sorted by expert; output row = pair
+  int g_in_div;                    // input row = pair / g_in_div (top-k pairs share a token row) or pair (1)
+  int g_pass;                      // which group of TMAX rows of each expert this launch handles
+  long long g_words_stride;        // words between consecutive experts
 };
 
-template <int KB, int TMAX, int PRO, bool kTp>
+template <int KB, int TMAX, int PRO, bool kTp, bool kGrouped = false>
 __global__ void __launch_bounds__(kThreads)
 TrellisGemvKernel(GemvArgs a, TpPush tp) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -80,9 +87,30 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int kslice = a.kblocks_per_cta * 128;
   const int k_begin = krank * kslice;
-  const int T = a.T, N = a.N, K = a.K;
+  int T = a.T;
+  const int N = a.N, K = a.K;
+  int g_base = 0;
+  if constexpr (kGrouped) {
+    // this launch handles rows [g_pass * TMAX, +TMAX) of every expert's list
+    const int e = blockIdx.z;
+    g_base = a.g_offsets[e] + a.g_pass * TMAX;
+    const int left = a.g_offsets[e + 1] - g_base;
+    if (left <= 0) return;         // uniform over the cluster: every CTA of it leaves before any barrier
+    T = left < TMAX ? left : TMAX;
+    a.words += static_cast<size_t>(e) * a.g_words_stride;
+    a.suh += static_cast<size_t>(e) * K;
+    a.svh += static_cast<size_t>(e) * N;
+  }
   constexpr int NW = 8 * KB;
   constexpr int kStageBytes = 8 * 8 * NW * 4;     // 8 k-tiles x 8 n-tiles
+  auto in_row = [&](int t) -> size_t {
+    if constexpr (kGrouped) return static_cast<size_t>(a.g_perm[g_base + t] / a.g_in_div);
+    else return static_cast<size_t>(t);
+  };
+  auto out_row = [&](int t) -> size_t {
+    if constexpr (kGrouped) return static_cast<size_t>(a.g_perm[g_base + t]);
+    else return static_cast<size_t>(t);
+  };
 
   float* part = reinterpret_cast<float*>(smem_raw);                                  // [ksplit][TMAX][128] (used on cluster rank 0)
   float* rnorm = part + ksplit * TMAX * 128;                                          // [8] per-row rsqrt
@@ -130,7 +158,7 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
     if constexpr (PRO == 1) {
       // RMSNorm statistics need the whole row, not just this CTA's slice: warp t reduces row t
       if (warp < T) {
-        const __nv_bfloat16* row = a.x + static_cast<size_t>(warp) * K;
+        const __nv_bfloat16* row = a.x + in_row(warp) * K;
         float ss = 0.f;
         for (int k = lane * 8; k < K; k += 256) {
           const uint4 v = *reinterpret_cast<const uint4*>(row + k);
@@ -149,13 +177,13 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
       const int k = k_begin + b * 128 + lane * 4;
       if (t < T) {
         if constexpr (PRO == 2) {
-          const uint2 g = *reinterpret_cast<const uint2*>(a.x + static_cast<size_t>(t) * 2 * K + k);
-          const uint2 u = *reinterpret_cast<const uint2*>(a.x + static_cast<size_t>(t) * 2 * K + K + k);
+          const uint2 g = *reinterpret_cast<const uint2*>(a.x + in_row(t) * 2 * K + k);
+          const uint2 u = *reinterpret_cast<const uint2*>(a.x + in_row(t) * 2 * K + K + k);
           const uint32_t p01 = PackBf16(Silu(BfLo(g.x)) * BfLo(u.x), Silu(BfHi(g.x)) * BfHi(u.x));
           const uint32_t p23 = PackBf16(Silu(BfLo(g.y)) * BfLo(u.y), Silu(BfHi(g.y)) * BfHi(u.y));
           v[0] = BfLo(p01); v[1] = BfHi(p01); v[2] = BfLo(p23); v[3] = BfHi(p23);
         } else {
-          const uint2 xv = *reinterpret_cast<const uint2*>(a.x + static_cast<size_t>(t) * K + k);
+          const uint2 xv = *reinterpret_cast<const uint2*>(a.x + in_row(t) * K + k);
           v[0] = BfLo(xv.x); v[1] = BfHi(xv.x); v[2] = BfLo(xv.y); v[3] = BfHi(xv.y);
           if constexpr (PRO == 1) {
             const uint2 wv = *reinterpret_cast<const uint2*>(a.norm_w + k);
@@ -317,13 +345,13 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
     }
     if (t < T) {
       if (a.residual != nullptr) {
-        const uint2 rv = *reinterpret_cast<const uint2*>(a.residual + static_cast<size_t>(t) * N + n);
+        const uint2 rv = *reinterpret_cast<const uint2*>(a.residual + out_row(t) * N + n);
         o[0] += BfLo(rv.x); o[1] += BfHi(rv.x); o[2] += BfLo(rv.y); o[3] += BfHi(rv.y);
       }
       uint2 ov;
       ov.x = PackBf16(o[0], o[1]);
       ov.y = PackBf16(o[2], o[3]);
-      *reinterpret_cast<uint2*>(a.y + static_cast<size_t>(t) * N + n) = ov;
+      *reinterpret_cast<uint2*>(a.y + out_row(t) * N + n) = ov;
     }
   }
 }
@@ -363,6 +391,38 @@ int Launch(GemvArgs a, int ksplit, cudaStream_t stream, const TpPush& tp) {
   cfg.attrs = attr;
   cfg.numAttrs = g_use_pdl ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, tp);
+  ++g_launch_count;
+  return static_cast<int>(e);
+}
+
+template <int KB, int TMAX, int PRO>
+int LaunchGrouped(GemvArgs a, int ksplit, int experts, cudaStream_t stream) {
+  a.kblocks_per_cta = a.K / 128 / ksplit;
+  const int kslice = a.kblocks_per_cta * 128;
+  a.stages = a.kblocks_per_cta < 6 ? a.kblocks_per_cta : 6;
+  const size_t smem = SmemBytes(TMAX, kslice, a.stages, KB, ksplit);
+  if (smem > 220 * 1024) return R4DXB_TOO_LARGE;
+  auto kern = TrellisGemvKernel<KB, TMAX, PRO, false, true>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ksplit, a.N / 128, experts);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = ksplit;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_use_pdl ? 2 : 1;
+  TpPush none = {};
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, none);
   ++g_launch_count;
   return static_cast<int>(e);
 }
@@ -410,7 +470,7 @@ int r4dxb_trellis_gemv_ex(const void* words, const void* suh, const void* svh, c
   if (prologue == 1 && (norm_w == nullptr || K % 8)) return R4DXB_BAD_ARG;
   GemvArgs a = {static_cast<const uint32_t*>(words), static_cast<const __half*>(suh), static_cast<const __half*>(svh),
                 static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y),
-                static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_w), eps, T, N, K, 0, 0};
+                static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_w), eps, T, N, K, 0, 0, nullptr, nullptr, 1, 0, 0};
   TpPush none = {};
   return LaunchAll<false>(a, kb, prologue, ksplit, static_cast<cudaStream_t>(stream), none);
 }
@@ -418,6 +478,27 @@ int r4dxb_trellis_gemv_ex(const void* words, const void* suh, const void* svh, c
 int r4dxb_trellis_gemv(const void* words, const void* suh, const void* svh, const void* x, void* y,
                        const void* residual, int T, int N, int K, int kb, int ksplit, void* stream) {
   return r4dxb_trellis_gemv_ex(words, suh, svh, x, y, residual, nullptr, 0.f, 0, T, N, K, kb, ksplit, stream);
+}
+
+// Grouped expert linear: one launch covers every local expert (grid.z); expert e multiplies the rows
+// perm[offsets[e] + pass*tmax ...] (at most tmax of them) by its own weights.  words / suh / svh hold
+// the experts back to back.  Input row of a pair = pair / in_div; output row = pair.  prologue 0 or 2.
+int r4dxb_trellis_gemv_grouped(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                               const int* offsets, const int* perm, int in_div, int pass, int tmax, int prologue,
+                               int experts, int N, int K, int kb, int ksplit, void* stream) {
+  if (int rc = CheckArgs(1, N, K, ksplit)) return rc;
+  if (experts < 1 || experts > 65535 || in_div < 1 || (prologue != 0 && prologue != 2)) return R4DXB_BAD_ARG;
+  GemvArgs a = {static_cast<const uint32_t*>(words), static_cast<const __half*>(suh), static_cast<const __half*>(svh),
+                static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), nullptr, nullptr, 0.f, tmax, N, K, 0, 0,
+                offsets, perm, in_div, pass, static_cast<long long>(N / 16) * (K / 16) * 8 * kb};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define R4DXB_G(KBV, TM, PROV) \
+  if (kb == KBV && tmax == TM && prologue == PROV) return LaunchGrouped<KBV, TM, PROV>(a, ksplit, experts, s);
+  R4DXB_G(3, 2, 0) R4DXB_G(3, 2, 2) R4DXB_G(3, 8, 0) R4DXB_G(3, 8, 2)
+  R4DXB_G(4, 2, 0) R4DXB_G(4, 2, 2) R4DXB_G(4, 8, 0) R4DXB_G(4, 8, 2)
+  R4DXB_G(5, 2, 0) R4DXB_G(5, 2, 2) R4DXB_G(5, 8, 0) R4DXB_G(5, 8, 2)
+#undef R4DXB_G
+  return R4DXB_BAD_ARG;
 }
 
 // Row-parallel linear + all-reduce + residual in one kernel (see TpPush).  recv: `world` peer-mapped
@@ -431,7 +512,7 @@ int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void*
   if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world || prologue == 1) return R4DXB_BAD_ARG;
   GemvArgs a = {static_cast<const uint32_t*>(words), static_cast<const __half*>(suh), static_cast<const __half*>(svh),
                 static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y),
-                static_cast<const __nv_bfloat16*>(residual), nullptr, 0.f, T, N, K, 0, 0};
+                static_cast<const __nv_bfloat16*>(residual), nullptr, 0.f, T, N, K, 0, 0, nullptr, nullptr, 1, 0, 0};
   TpPush tp = {};
   for (int p = 0; p < world; ++p) tp.recv[p] = static_cast<float2*>(recv[p]);
   tp.block_seq = static_cast<unsigned*>(block_seq);

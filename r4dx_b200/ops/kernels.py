@@ -337,3 +337,35 @@ def spec_accept(next_ids: torch.Tensor, draft: torch.Tensor, T: int, out: torch.
     """out[0] = rows to commit, out[1..] = emitted tokens for a T-row speculative window."""
     _check(_lib().r4dxb_spec_accept(_p(next_ids), _p(draft), T, _p(out), _p(n_replay), _stream()), "spec_accept")
     return out
+
+
+register_cuda_sig("r4dxb_moe_router", _I, [_P, _I, _I, _I, _I, _P, _P, _P])
+register_cuda_sig("r4dxb_moe_plan", _I, [_P, _I, _I, _I, _I, _P, _P, _P])
+register_cuda_sig("r4dxb_moe_combine", _I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_trellis_gemv_grouped", _I, [_P] * 7 + [_I] * 9 + [_P])
+
+
+def moe_router(logits: torch.Tensor, k: int, renorm: bool, ids: torch.Tensor, weights: torch.Tensor):
+    T, E = logits.shape
+    _check(_lib().r4dxb_moe_router(_p(logits), T, E, k, 1 if renorm else 0, _p(ids), _p(weights), _stream()), "moe_router")
+    return ids, weights
+
+
+def moe_plan(ids: torch.Tensor, npairs: int, E: int, e_begin: int, e_count: int, offsets: torch.Tensor, perm: torch.Tensor):
+    _check(_lib().r4dxb_moe_plan(_p(ids), npairs, E, e_begin, e_count, _p(offsets), _p(perm), _stream()), "moe_plan")
+    return offsets, perm
+
+
+def moe_combine(y_pairs, ids, weights, shared, shared_gate, residual, out, T: int, H: int, k: int):
+    _check(_lib().r4dxb_moe_combine(_p(y_pairs), _p(ids), _p(weights), _p(shared), _p(shared_gate), _p(residual), _p(out),
+                                    T, H, k, _stream()), "moe_combine")
+    return out
+
+
+def trellis_gemv_grouped(words, suh, svh, x, y, offsets, perm, in_div: int, n_pass: int, tmax: int, prologue: int,
+                         experts: int, N: int, Kd: int, kb: int, ksplit: int):
+    """Every local expert times its planned rows; ``n_pass`` launches cover up to n_pass * tmax rows per expert."""
+    for p_ in range(n_pass):
+        _check(_lib().r4dxb_trellis_gemv_grouped(_p(words), _p(suh), _p(svh), _p(x), _p(y), _p(offsets), _p(perm), in_div, p_,
+                                                 tmax, prologue, experts, N, Kd, kb, ksplit, _stream()), "trellis_gemv_grouped")
+    return y

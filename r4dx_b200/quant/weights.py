@@ -32,10 +32,10 @@ def default_kb_rule(name: str) -> int:
 
 def moe_kb_rule(name: str) -> int:
     """Mixed 3/4-bit plan (~3.3 bpw) for the expert-heavy MoE variant: experts mostly 3 bits."""
-    if ".experts." in name:
-        parts = name.split(".")
-        e = int(parts[parts.index("experts") + 1])
-        return 4 if e % 3 == 0 else 3
+    parts = name.split(".")
+    if ".experts." in name and "layers" in parts:
+        layer = int(parts[parts.index("layers") + 1])
+        return 4 if layer % 3 == 0 else 3      # one width per layer, so a layer's experts share one launch
     return 4
 
 
@@ -94,12 +94,16 @@ def linear_shapes(cfg: ModelConfig, with_mtp: bool = False) -> Iterable[Tuple[st
         if not cfg.is_moe:
             yield p + "mlp.gate_up", 2 * cfg.intermediate_size, H
             yield p + "mlp.down", H, cfg.intermediate_size
+        else:
+            yield p + "moe.shared.gate_up", 2 * cfg.shared_expert_intermediate_size, H
+            yield p + "moe.shared.down", H, cfg.shared_expert_intermediate_size
 
 
 def synthetic_weight_set(cfg: ModelConfig, device="cuda", seed: int = 0, sigma: float = 0.02,
                          kb_rule: Callable[[str], int] = default_kb_rule, head_group: int = 64,
-                         with_mtp: bool = False) -> Dict[str, object]:
-    """Random-init weights created directly in the quantized domain (dense hybrid).
+                         with_mtp: bool = False, expert_range=None) -> Dict[str, object]:
+    """Random-init weights created directly in the quantized domain (dense hybrid or MoE hybrid;
+    ``expert_range`` = (first, count) of the routed experts this rank holds under expert parallelism).
 
     Body linears get random trellis code bits (decoded values ~ N(0,1)) with svh = +-sigma, the LM
     head random nibbles; everything else is N(0, sigma).  ``cfg`` may be a TP shard view, in which
@@ -133,6 +137,19 @@ def synthetic_weight_set(cfg: ModelConfig, device="cuda", seed: int = 0, sigma: 
             w[p + "gdn.norm_weight"] = (1.0 + n(cfg.linear_value_head_dim).float()).to(torch.bfloat16)
     w["text.final_norm"] = n(H)
     w["lm_head"] = w4a16.random_weight(cfg.vocab_shard_size, H, head_group, seed=seed + 17, sigma=sigma, device=device)
+    if cfg.is_moe:
+        e_begin, e_count = expert_range if expert_range is not None else (0, cfg.num_experts)
+        for i in range(cfg.num_hidden_layers):
+            p = f"text.layers.{i}.moe."
+            w[p + "router"] = n(cfg.num_experts, H)
+            w[p + "shared_gate"] = n(1, H)
+            kb = kb_rule(p + "experts.0.gate_up")
+            for j in range(e_count):
+                e = e_begin + j
+                w[p + f"experts.{e}.gate_up"] = trellis.random_weight(2 * cfg.moe_intermediate_size, H, kb, seed=seed * 31 + i * 1009 + e,
+                                                                     sigma=sigma, device=device)
+                w[p + f"experts.{e}.down"] = trellis.random_weight(H, cfg.moe_intermediate_size, kb, seed=seed * 37 + i * 1013 + e,
+                                                                  sigma=sigma, device=device)
     return w
 
 

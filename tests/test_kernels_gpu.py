@@ -342,3 +342,54 @@ def test_trellis_gemv_long_k_uses_the_stage_ring(K):
     ref = trellis.linear_reference(tw, x.float())
     y = K.trellis_gemv(tw.to("cuda"), x.cuda(), ksplit=1)
     assert (y.float().cpu() - ref).abs().max().item() < 0.02 * ref.abs().max().item() + 1e-3
+
+
+def test_moe_router_plan_combine(K):
+    g = torch.Generator().manual_seed(3)
+    T, E, k, H = 9, 64, 6, 256
+    logits = torch.randn(T, E, generator=g)
+    logits[2, 5] = logits[2, 40] = 9.0                      # a tie at the top: the lower id comes first
+    ids = torch.zeros(T, k, dtype=torch.int32, device="cuda")
+    w = torch.zeros(T, k, device="cuda")
+    K.moe_router(logits.cuda(), k, True, ids, w)
+    rid, rw = R.moe_route(logits, k, True)
+    assert torch.equal(ids.cpu().long(), rid)
+    assert torch.allclose(w.cpu(), rw, atol=4e-3)
+    off = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+    perm = torch.zeros(T * k, dtype=torch.int32, device="cuda")
+    K.moe_plan(ids, T * k, E, 0, E, off, perm)
+    flat = ids.cpu().view(-1)
+    exp_perm = torch.sort(flat, stable=True).indices
+    assert torch.equal(perm.cpu().long(), exp_perm)
+    assert off.cpu().tolist() == [0] + torch.cumsum(torch.bincount(flat.long(), minlength=E), 0).tolist()
+    y = torch.randn(T * k, H, generator=g).to(BF)
+    sh = torch.randn(T, H, generator=g).to(BF)
+    sg = torch.randn(T, 1, generator=g)
+    res = torch.randn(T, H, generator=g).to(BF)
+    out = torch.zeros(T, H, dtype=BF, device="cuda")
+    K.moe_combine(y.cuda(), ids, w, sh.cuda(), sg.cuda(), res.cuda(), out, T, H, k)
+    ref = (w.cpu()[:, :, None] * y.float().view(T, k, H)).sum(1) + torch.sigmoid(sg) * sh.float() + res.float()
+    assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=2e-2)
+
+
+def test_grouped_expert_gemv(K):
+    from r4dx_b200.models.moe import ExpertStack
+    from r4dx_b200.quant import trellis
+    g = torch.Generator().manual_seed(4)
+    E, N, Kd, T, k = 6, 256, 256, 11, 2
+    ws = [trellis.random_weight(N, Kd, 3, seed=e, sigma=0.05) for e in range(E)]
+    st = ExpertStack.from_list([w.to("cuda") for w in ws])
+    x = torch.randn(T, Kd, generator=g).to(BF)
+    ids = torch.randint(0, E, (T, k), generator=g).to(torch.int32)
+    ids[:, 1] = (ids[:, 0] + 1) % E
+    ids[:6, 0] = 2                                            # six rows on one expert -> several passes at tmax 2
+    off = torch.zeros(E + 1, dtype=torch.int32, device="cuda")
+    perm = torch.zeros(T * k, dtype=torch.int32, device="cuda")
+    K.moe_plan(ids.cuda(), T * k, E, 0, E, off, perm)
+    y = torch.zeros(T * k, N, dtype=BF, device="cuda")
+    K.trellis_gemv_grouped(st.words, st.suh, st.svh, x.cuda(), y, off, perm, k, (T + 1) // 2, 2, 0, E, N, Kd, 3, 2)
+    for t in range(T):
+        for j in range(k):
+            ref = trellis.linear_reference(ws[int(ids[t, j])], x[t:t + 1].float())[0]
+            got = y[t * k + j].float().cpu()
+            assert (got - ref).abs().max().item() < 0.03 * ref.abs().max().item() + 1e-3
