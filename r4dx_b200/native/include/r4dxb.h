@@ -110,6 +110,23 @@ int r4dxb_trellis_gemv_grouped(const void* words, const void* suh, const void* s
                                const int* offsets, const int* perm, int in_div, int pass, int tmax, int prologue,
                                int experts, int N, int K, int kb, int ksplit, void* stream);
 
+/* Expert-parallel form: input rows arrive from peer GPUs (ready flags, double-buffered by the parity of the
+ * device call counter *seq_ptr + 1) and, when ep_y is given, output rows go to the combine buffer of the rank
+ * that owns the token (ep_y[rank]: [2][ep_P][N] bf16, ep_cnt[rank]: [2][ep_P] arrival counters). */
+int r4dxb_trellis_gemv_grouped_ep(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                                  const int* offsets, const int* perm, int in_div, int pass, int tmax, int prologue,
+                                  int experts, int N, int K, int kb, int ksplit, const void* seq_ptr, const void* ready,
+                                  long long x_par_stride, long long ready_par_stride, void* const* ep_y, void* const* ep_cnt,
+                                  int ep_P, int world, int spin_limit, int* status, void* stream);
+/* expert-parallel all-to-all around it (native/src/cuda/ep.cu) */
+int r4dxb_ep_dispatch(void* const* meta, void* const* xrecv, void* const* xflag, const void* h, const int* ids,
+                      const void* seq_ptr, int T, int k, int H, int P, int world, int rank, int experts_per_rank, void* stream);
+int r4dxb_ep_plan(const void* meta_local, const void* seq_ptr, int world, int P, int e_begin, int e_count, int* offsets,
+                  int* perm, int spin_limit, int* status, void* stream);
+int r4dxb_ep_combine(const void* comb, void* ccount, void* seq_ptr, const int* ids, const float* weights, const void* shared,
+                     const float* shared_gate, void* x, int T, int H, int k, int P, int blocks_per_row, int spin_limit,
+                     int* status, void* stream);
+
 /* ---- tensor parallel: collectives issued from inside the compute kernels ------------------------- */
 /* Row-parallel trellis linear (T <= 8) + all-reduce over NVLink peer memory + residual, one kernel.
  * recv[p]: rank p's receive buffer, [2][world][8][N] (fp32 value, u32 sequence) pairs, zero-initialised and

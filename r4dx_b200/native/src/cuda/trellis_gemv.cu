@@ -55,6 +55,11 @@ struct TpPush {
   unsigned* block_seq;             // local [N/128] call counters
   int* status;                     // local: set to 100 + rank when that rank did not answer in time
   int world, rank, spin_limit;
+  // expert-parallel output (grouped mode): row gp = (rank gp / ep_P, pair gp % ep_P) goes to that rank's
+  // combine buffer ep_y[rank] ([2][ep_P][N] bf16) and bumps ep_cnt[rank] ([2][ep_P]) once per 128-column block
+  __nv_bfloat16* ep_y[kMaxWorld];
+  unsigned* ep_cnt[kMaxWorld];
+  int ep_P;
 };
 
 struct GemvArgs {
@@ -73,6 +78,14 @@ struct GemvArgs {
   const int* g_perm;               // pair indices sorted by expert; output row = pair
   int g_in_div;                    // input row = pair / g_in_div (top-k pairs share a token row) or pair (1)
   int g_pass;                      // which group of TMAX rows of each expert this launch handles
+  // expert-parallel input (optional): rows arrive from peers; g_seq = device call counter (this call is
+  // *g_seq + 1, its parity selects the buffer half), g_ready[par][row] == call number once a row landed
+  const unsigned* g_seq;
+  const unsigned* g_ready;
+  long long g_x_par_stride;        // elements between the two halves of x
+  long long g_ready_par_stride;
+  int g_spin_limit;
+  int* g_status;
   long long g_words_stride;        // words between consecutive experts
 };
 
@@ -97,6 +110,11 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
     const int left = a.g_offsets[e + 1] - g_base;
     if (left <= 0) return;         // uniform over the cluster: every CTA of it leaves before any barrier
     T = left < TMAX ? left : TMAX;
+    if (a.g_seq != nullptr) {
+      const unsigned call = *a.g_seq + 1;
+      a.x += static_cast<size_t>(call & 1) * a.g_x_par_stride;
+      if (a.g_ready != nullptr) a.g_ready += static_cast<size_t>(call & 1) * a.g_ready_par_stride;
+    }
     a.words += static_cast<size_t>(e) * a.g_words_stride;
     a.suh += static_cast<size_t>(e) * K;
     a.svh += static_cast<size_t>(e) * N;
@@ -155,6 +173,24 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
     // ---------------- prologue (consumer warps): xs = fp16(H128(suh * act(x))) for this K slice ----------------
     // everything before this point touched only weights; activations come from the previous kernel
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if constexpr (kGrouped) {
+      if (a.g_ready != nullptr) {
+        // rows are stored by peer GPUs: wait (bounded) for the flag of every row this launch reads
+        const unsigned call = *a.g_seq + 1;
+        if (warp < T && lane == 0) {
+          const unsigned* f = a.g_ready + in_row(warp);
+          bool got = false;
+          for (int i = 0; i < a.g_spin_limit; ++i) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if (v == call) { got = true; break; }
+            if (i > 64) __nanosleep(32);
+          }
+          if (!got) atomicExch(a.g_status, 400 + static_cast<int>(in_row(warp) % 1000));
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+      }
+    }
     if constexpr (PRO == 1) {
       // RMSNorm statistics need the whole row, not just this CTA's slice: warp t reduces row t
       if (warp < T) {
@@ -183,7 +219,9 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
           const uint32_t p23 = PackBf16(Silu(BfLo(g.y)) * BfLo(u.y), Silu(BfHi(g.y)) * BfHi(u.y));
           v[0] = BfLo(p01); v[1] = BfHi(p01); v[2] = BfLo(p23); v[3] = BfHi(p23);
         } else {
-          const uint2 xv = *reinterpret_cast<const uint2*>(a.x + in_row(t) * K + k);
+          // (peer-written rows must not come from a stale L1 line)
+          const uint2 xv = kGrouped ? __ldcg(reinterpret_cast<const uint2*>(a.x + in_row(t) * K + k))
+                                    : *reinterpret_cast<const uint2*>(a.x + in_row(t) * K + k);
           v[0] = BfLo(xv.x); v[1] = BfHi(xv.x); v[2] = BfLo(xv.y); v[3] = BfHi(xv.y);
           if constexpr (PRO == 1) {
             const uint2 wv = *reinterpret_cast<const uint2*>(a.norm_w + k);
@@ -351,7 +389,22 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
       uint2 ov;
       ov.x = PackBf16(o[0], o[1]);
       ov.y = PackBf16(o[2], o[3]);
-      *reinterpret_cast<uint2*>(a.y + out_row(t) * N + n) = ov;
+      if constexpr (kGrouped) {
+        if (tp.ep_P > 0) {
+          const unsigned call = *a.g_seq + 1;
+          const size_t gp = out_row(t);
+          const int dest = static_cast<int>(gp / tp.ep_P);
+          const size_t slot = static_cast<size_t>(call & 1) * tp.ep_P + gp % tp.ep_P;
+          *reinterpret_cast<uint2*>(tp.ep_y[dest] + slot * N + n) = ov;
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) atomicAdd_system(tp.ep_cnt[dest] + slot, 1u);
+        } else {
+          *reinterpret_cast<uint2*>(a.y + out_row(t) * N + n) = ov;
+        }
+      } else {
+        *reinterpret_cast<uint2*>(a.y + out_row(t) * N + n) = ov;
+      }
     }
   }
 }
@@ -396,7 +449,7 @@ int Launch(GemvArgs a, int ksplit, cudaStream_t stream, const TpPush& tp) {
 }
 
 template <int KB, int TMAX, int PRO>
-int LaunchGrouped(GemvArgs a, int ksplit, int experts, cudaStream_t stream) {
+int LaunchGrouped(GemvArgs a, int ksplit, int experts, cudaStream_t stream, const TpPush& ep) {
   a.kblocks_per_cta = a.K / 128 / ksplit;
   const int kslice = a.kblocks_per_cta * 128;
   a.stages = a.kblocks_per_cta < 6 ? a.kblocks_per_cta : 6;
@@ -421,8 +474,7 @@ int LaunchGrouped(GemvArgs a, int ksplit, int experts, cudaStream_t stream) {
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = g_use_pdl ? 2 : 1;
-  TpPush none = {};
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, none);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, ep);
   ++g_launch_count;
   return static_cast<int>(e);
 }
@@ -444,6 +496,22 @@ int LaunchAll(const GemvArgs& a, int kb, int prologue, int ksplit, cudaStream_t 
   R4DXB_CASE(5, 0) R4DXB_CASE(5, 1) R4DXB_CASE(5, 2)
 #undef R4DXB_CASE
   return R4DXB_BAD_ARG;
+}
+
+GemvArgs MakeArgs(const void* words, const void* suh, const void* svh, const void* x, void* y, const void* residual,
+                  const void* norm_w, float eps, int T, int N, int K) {
+  GemvArgs a = {};
+  a.words = static_cast<const uint32_t*>(words);
+  a.suh = static_cast<const __half*>(suh);
+  a.svh = static_cast<const __half*>(svh);
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.y = static_cast<__nv_bfloat16*>(y);
+  a.residual = static_cast<const __nv_bfloat16*>(residual);
+  a.norm_w = static_cast<const __nv_bfloat16*>(norm_w);
+  a.eps = eps;
+  a.T = T; a.N = N; a.K = K;
+  a.g_in_div = 1;
+  return a;
 }
 
 int CheckArgs(int T, int N, int K, int ksplit) {
@@ -468,9 +536,7 @@ int r4dxb_trellis_gemv_ex(const void* words, const void* suh, const void* svh, c
                           int ksplit, void* stream) {
   if (int rc = CheckArgs(T, N, K, ksplit)) return rc;
   if (prologue == 1 && (norm_w == nullptr || K % 8)) return R4DXB_BAD_ARG;
-  GemvArgs a = {static_cast<const uint32_t*>(words), static_cast<const __half*>(suh), static_cast<const __half*>(svh),
-                static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y),
-                static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_w), eps, T, N, K, 0, 0, nullptr, nullptr, 1, 0, 0};
+  GemvArgs a = MakeArgs(words, suh, svh, x, y, residual, norm_w, eps, T, N, K);
   TpPush none = {};
   return LaunchAll<false>(a, kb, prologue, ksplit, static_cast<cudaStream_t>(stream), none);
 }
@@ -483,22 +549,49 @@ int r4dxb_trellis_gemv(const void* words, const void* suh, const void* svh, cons
 // Grouped expert linear: one launch covers every local expert (grid.z); expert e multiplies the rows
 // perm[offsets[e] + pass*tmax ...] (at most tmax of them) by its own weights.  words / suh / svh hold
 // the experts back to back.  Input row of a pair = pair / in_div; output row = pair.  prologue 0 or 2.
-int r4dxb_trellis_gemv_grouped(const void* words, const void* suh, const void* svh, const void* x, void* y,
-                               const int* offsets, const int* perm, int in_div, int pass, int tmax, int prologue,
-                               int experts, int N, int K, int kb, int ksplit, void* stream) {
+int r4dxb_trellis_gemv_grouped_ep(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                                  const int* offsets, const int* perm, int in_div, int pass, int tmax, int prologue,
+                                  int experts, int N, int K, int kb, int ksplit,
+                                  const void* seq_ptr, const void* ready, long long x_par_stride, long long ready_par_stride,
+                                  void* const* ep_y, void* const* ep_cnt, int ep_P, int world, int spin_limit, int* status,
+                                  void* stream) {
   if (int rc = CheckArgs(1, N, K, ksplit)) return rc;
-  if (experts < 1 || experts > 65535 || in_div < 1 || (prologue != 0 && prologue != 2)) return R4DXB_BAD_ARG;
-  GemvArgs a = {static_cast<const uint32_t*>(words), static_cast<const __half*>(suh), static_cast<const __half*>(svh),
-                static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), nullptr, nullptr, 0.f, tmax, N, K, 0, 0,
-                offsets, perm, in_div, pass, static_cast<long long>(N / 16) * (K / 16) * 8 * kb};
+  if (experts < 1 || experts > 65535 || in_div < 1 || (prologue != 0 && prologue != 2) || world > kMaxWorld) return R4DXB_BAD_ARG;
+  GemvArgs a = MakeArgs(words, suh, svh, x, y, nullptr, nullptr, 0.f, tmax, N, K);
+  a.g_offsets = offsets;
+  a.g_perm = perm;
+  a.g_in_div = in_div;
+  a.g_pass = pass;
+  a.g_words_stride = static_cast<long long>(N / 16) * (K / 16) * 8 * kb;
+  a.g_seq = static_cast<const unsigned*>(seq_ptr);
+  a.g_ready = static_cast<const unsigned*>(ready);
+  a.g_x_par_stride = x_par_stride;
+  a.g_ready_par_stride = ready_par_stride;
+  a.g_spin_limit = spin_limit;
+  a.g_status = status;
+  TpPush ep = {};
+  if (ep_y != nullptr) {
+    for (int p = 0; p < world; ++p) {
+      ep.ep_y[p] = static_cast<__nv_bfloat16*>(ep_y[p]);
+      ep.ep_cnt[p] = static_cast<unsigned*>(ep_cnt[p]);
+    }
+    ep.ep_P = ep_P;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define R4DXB_G(KBV, TM, PROV) \
-  if (kb == KBV && tmax == TM && prologue == PROV) return LaunchGrouped<KBV, TM, PROV>(a, ksplit, experts, s);
+  if (kb == KBV && tmax == TM && prologue == PROV) return LaunchGrouped<KBV, TM, PROV>(a, ksplit, experts, s, ep);
   R4DXB_G(3, 2, 0) R4DXB_G(3, 2, 2) R4DXB_G(3, 8, 0) R4DXB_G(3, 8, 2)
   R4DXB_G(4, 2, 0) R4DXB_G(4, 2, 2) R4DXB_G(4, 8, 0) R4DXB_G(4, 8, 2)
   R4DXB_G(5, 2, 0) R4DXB_G(5, 2, 2) R4DXB_G(5, 8, 0) R4DXB_G(5, 8, 2)
 #undef R4DXB_G
   return R4DXB_BAD_ARG;
+}
+
+int r4dxb_trellis_gemv_grouped(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                               const int* offsets, const int* perm, int in_div, int pass, int tmax, int prologue,
+                               int experts, int N, int K, int kb, int ksplit, void* stream) {
+  return r4dxb_trellis_gemv_grouped_ep(words, suh, svh, x, y, offsets, perm, in_div, pass, tmax, prologue, experts, N, K, kb,
+                                       ksplit, nullptr, nullptr, 0, 0, nullptr, nullptr, 0, 0, 0, nullptr, stream);
 }
 
 // Row-parallel linear + all-reduce + residual in one kernel (see TpPush).  recv: `world` peer-mapped
@@ -510,9 +603,7 @@ int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void*
                                  void* stream) {
   if (int rc = CheckArgs(T, N, K, ksplit)) return rc;
   if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world || prologue == 1) return R4DXB_BAD_ARG;
-  GemvArgs a = {static_cast<const uint32_t*>(words), static_cast<const __half*>(suh), static_cast<const __half*>(svh),
-                static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y),
-                static_cast<const __nv_bfloat16*>(residual), nullptr, 0.f, T, N, K, 0, 0, nullptr, nullptr, 1, 0, 0};
+  GemvArgs a = MakeArgs(words, suh, svh, x, y, residual, nullptr, 0.f, T, N, K);
   TpPush tp = {};
   for (int p = 0; p < world; ++p) tp.recv[p] = static_cast<float2*>(recv[p]);
   tp.block_seq = static_cast<unsigned*>(block_seq);

@@ -179,3 +179,27 @@ def test_moe_model_matches_oracle():
     row_err = (got - ref).abs().amax(-1) / ref.abs().amax(-1)
     assert (row_err < 0.08).float().mean().item() >= 0.85, row_err
     assert (got.argmax(-1) == ref.argmax(-1)).float().mean().item() > 0.8
+
+
+def test_expert_parallel_exchange_in_one_gpu_matches_local_moe():
+    """World 1: dispatch, plan, grouped experts with peer-buffer I/O and combine run back to back on one GPU
+    and must reproduce the plain MoE block; repeated calls exercise both halves of the double buffers."""
+    from r4dx_b200.config import tiny_moe_config
+    from r4dx_b200.models.moe import MoeBlock
+    from r4dx_b200.models.oracle import init_weights
+    from r4dx_b200.parallel.ep import EpComm
+    from r4dx_b200.quant.weights import moe_kb_rule, quantize_weight_set
+    cfg = tiny_moe_config()
+    q = _to_dev(quantize_weight_set(cfg, init_weights(cfg, 0), kb_rule=moe_kb_rule))
+    blk = MoeBlock(cfg, q, 0, "cuda", 8)
+    ep = EpComm(1, 0, "cuda", cfg, max_rows=8, spin_limit=200000)
+    g = torch.Generator().manual_seed(2)
+    for it in range(3):
+        T = [8, 5, 8][it]
+        h = torch.randn(T, cfg.hidden_size, generator=g).to(torch.bfloat16).cuda()
+        x0 = torch.randn(T, cfg.hidden_size, generator=g).to(torch.bfloat16).cuda()
+        xa, xb = x0.clone(), x0.clone()
+        blk.forward(h, xa, T)
+        ep.moe_forward(blk, h, xb, T)
+        ep.check_healthy()
+        assert torch.equal(xa, xb), (it, (xa.float() - xb.float()).abs().max())
