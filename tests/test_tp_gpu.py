@@ -71,3 +71,10 @@ def test_tp2_matches_tp1_tokens(mode):
         os.environ.pop("R4DXB_TP_MODE", None)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "TP_OK" in r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_two_ranks():
+    r = _run_ranks(2, os.path.join(ROOT, "tests", "ep_worker.py"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "EP_OK" in r.stdout
