@@ -97,11 +97,14 @@ class StepBuffers:
 
 class HybridModel:
     def __init__(self, cfg: ModelConfig, weights: Dict[str, object], max_ctx: int = 8192 + 1024,
-                 device: str = "cuda", attn_splits: Optional[int] = None, comm=None):
+                 device: str = "cuda", attn_splits: Optional[int] = None, comm=None, layer_range=None):
+        """``layer_range`` = (first, end): a pipeline stage that runs only those layers (embedding with the
+        first stage, head with the last)."""
         cfg.validate() if cfg.tp_world == 1 else None
         self.cfg = cfg
         self.device = torch.device(device)
         self.comm = comm                       # tensor-parallel communicator (None = single rank)
+        self.layer_begin, self.layer_end = layer_range if layer_range is not None else (0, cfg.num_hidden_layers)
         self.max_ctx = ((max_ctx + KV_BLOCK - 1) // KV_BLOCK) * KV_BLOCK
         self.w = weights
         self.lin: Dict[str, Linear] = {}
@@ -110,7 +113,7 @@ class HybridModel:
                 self.lin[name] = Linear(t, name)
         # fused [a; b] gate projection per GDN layer
         self.ab_w: Dict[int, torch.Tensor] = {}
-        for i in range(cfg.num_hidden_layers):
+        for i in range(self.layer_begin, self.layer_end):
             if not cfg.is_attention_layer(i):
                 p = f"text.layers.{i}.gdn."
                 self.ab_w[i] = torch.cat([weights[p + "in_proj_a"], weights[p + "in_proj_b"]], 0).contiguous()
@@ -119,7 +122,7 @@ class HybridModel:
         if cfg.is_moe:
             from .moe import MoeBlock
             er = getattr(comm, "expert_range", None) if comm is not None else None
-            for i in range(cfg.num_hidden_layers):
+            for i in range(self.layer_begin, self.layer_end):
                 self.moe[i] = MoeBlock(cfg, weights, i, self.device, MAX_ROWS, *(er or (0, cfg.num_experts)))
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.pos = 0                           # host mirror of the next position
@@ -139,7 +142,7 @@ class HybridModel:
         self.log_u: Dict[int, torch.Tensor] = {}
         self.log_k: Dict[int, torch.Tensor] = {}
         self.log_eg: Dict[int, torch.Tensor] = {}
-        for i in range(cfg.num_hidden_layers):
+        for i in range(self.layer_begin, self.layer_end):
             if cfg.is_attention_layer(i):
                 self.kv[i] = torch.zeros(nblk, Hkv, 2, KV_BLOCK, D, dtype=torch.uint8, device=dev)
             else:
@@ -249,16 +252,16 @@ class HybridModel:
         """Runs the T rows staged in ``buf.ids`` / ``buf.positions``; results in ``buf.logits`` / ``buf.next_ids``.
         With ``skip_embed`` the caller has already placed the layer-0 input in ``buf.x``."""
         cfg, b, w = self.cfg, self.buf, self.w
-        if not skip_embed:
+        if not skip_embed and self.layer_begin == 0:
             K.embed_gather(b.ids[:T], w["text.embed_tokens"], out=b.x[:T])
-        for i in range(cfg.num_hidden_layers):
+        for i in range(self.layer_begin, self.layer_end):
             # the two RMSNorms and the SwiGLU of a layer run inside the prologues of the linears
             if cfg.is_attention_layer(i):
                 self._attn_layer(i, T)
             else:
                 self._gdn_layer(i, T)
             self._mlp(i, T)
-        if want_logits:
+        if want_logits and self.layer_end == cfg.num_hidden_layers:
             K.rmsnorm(b.x[:T], w["text.final_norm"], cfg.rms_norm_eps, out=b.h[:T])
             self.lin["lm_head"](b.h[:T], out=b.logits[:T])
             K.argmax_rows(b.logits[:T], cfg.vocab_shard_begin, b.next_ids[:T], b.next_vals[:T], b.argmax_scratch)
@@ -338,9 +341,9 @@ class HybridModel:
         Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
         x, h = cb["x"][:T], cb["h"][:T]
         pos0 = self.pos
-        if not skip_embed:
+        if not skip_embed and self.layer_begin == 0:
             K.embed_gather(cb["ids"][:T], w["text.embed_tokens"], out=x)
-        for i in range(cfg.num_hidden_layers):
+        for i in range(self.layer_begin, self.layer_end):
             p = f"text.layers.{i}."
             K.rmsnorm(x, w[p + "input_layernorm"], cfg.rms_norm_eps, out=h)
             if cfg.is_attention_layer(i):
@@ -372,7 +375,7 @@ class HybridModel:
             gu = cb["gate_up"][:T]
             self.lin[pm + "gate_up"].chunk(h, cb["xh"], gu)
             self._row_parallel_chunk(self.lin[pm + "down"], gu, x, cb, fused_silu_mul=True)
-        if want_logits:
+        if want_logits and self.layer_end == cfg.num_hidden_layers:
             b = self.buf
             K.rmsnorm(x[T - 1:T], w["text.final_norm"], cfg.rms_norm_eps, out=b.h[:1])
             self.lin["lm_head"](b.h[:1], out=b.logits[:1])

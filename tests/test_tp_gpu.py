@@ -78,3 +78,10 @@ def test_expert_parallel_two_ranks():
     r = _run_ranks(2, os.path.join(ROOT, "tests", "ep_worker.py"))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "EP_OK" in r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_pipeline_prefill_and_reshard_to_tp():
+    r = _run_ranks(2, os.path.join(ROOT, "tests", "pp_worker.py"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "PP_OK" in r.stdout
