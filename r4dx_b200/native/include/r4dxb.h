@@ -55,6 +55,13 @@ int r4dxb_bf16_gemv_norm(const void* W, const void* x, const void* norm_w, float
 int r4dxb_argmax_rows(const void* logits, int is_f32, int T, int V, int id_offset, int* out_ids, float* out_vals,
                       void* scratch, void* stream);
 
+/* row summary for exact host sampling: top-K (K <= 64) raw logits + ids (canonical order) and the log-sum-exp
+ * of logits / temperature.  scratch: T * 128 * (2K + 2) * 4 bytes */
+int r4dxb_topk_lse(const float* logits, int T, int V, int K, float temperature, int id_offset, float* out_vals, int* out_ids,
+                   float* out_lse, void* scratch, void* stream);
+/* HF repetition penalty on the distinct ids of `seen` */
+int r4dxb_repetition_penalty(float* logits, int V, const int* seen, int n, float penalty, void* stream);
+
 /* ---- Gated DeltaNet ------------------------------------------------------------------------- */
 /* Fused decode / verify step (T <= 8 rows): conv1d ring + SiLU, L2 norm, gates, delta rule, gated
  * RMSNorm.  The base state is only written when *n_replay > 0 (commit of the previous call's
@@ -81,6 +88,20 @@ int r4dxb_trellis_input(const void* in, const void* suh, void* out, int T, int K
  * tn: token tile 16/32/64/128/256.  *status (device int) becomes non-zero if a bounded wait ran out. */
 int r4dxb_trellis_gemm(const void* w, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
                        int kb, int tn, int* status, void* stream);
+
+/* ---- batched decode (B sequences, one new token each; per-sequence state indexed by slot) ---------- */
+int r4dxb_gdn_decode_batch(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
+                           const float* dt_bias, const void* norm_w, void* ring, float* state, float* log_u, float* log_k,
+                           float* log_eg, const int* positions, const int* n_replay, const int* row_slot, void* out, int B,
+                           int H, int Hk, int D, float eps, void* stream);
+int r4dxb_attn_precore_batch(const void* qg, const void* k, const void* v, const void* q_norm, const void* k_norm,
+                             const float* k_descale, const float* v_descale, const int* positions, const int* block_tables,
+                             const int* row_slot, int table_stride, void* q_out, void* cache, int B, int Hq, int Hkv, int D,
+                             int rotary_dim, float theta, float eps, void* stream);
+int r4dxb_attn_decode_batch(const void* q, const void* qg, const void* cache, const int* block_tables, const int* row_slot,
+                            int table_stride, const int* positions, const float* k_descale, const float* v_descale,
+                            float* part_acc, float* part_ml, void* out, int B, int Hq, int Hkv, int D, int splits, int gated,
+                            void* stream);
 
 /* ---- prefill (long chunks) ---------------------------------------------------------------------- */
 /* GDN over T rows starting at position pos0: conv prep, register-resident recurrence, gated norm.

@@ -42,6 +42,8 @@ struct PrecoreArgs {
   uint8_t* cache;
   int T, Hq, Hkv, D, rotary_dim;
   float theta, eps;
+  const int* row_slot;         // batched decode: row t belongs to sequence slot row_slot[t] (null: one sequence)
+  int table_stride;            // ints between the block tables of consecutive slots
 };
 
 // grid (Hq + 2 Hkv, T), block D threads (one element each)
@@ -77,7 +79,8 @@ __global__ void PrecoreKernel(PrecoreArgs a) {
   if (kind == 0) {
     a.q_out[(static_cast<size_t>(t) * a.Hq + head) * D + d] = __float2bfloat16(x);
   } else {
-    const int blk = a.block_table[pos / kBlockTokens], tok = pos % kBlockTokens;
+    const int* table = a.row_slot ? a.block_table + static_cast<size_t>(a.row_slot[t]) * a.table_stride : a.block_table;
+    const int blk = table[pos / kBlockTokens], tok = pos % kBlockTokens;
     const float ds = (kind == 1 ? a.k_descale : a.v_descale)[head];
     uint8_t* dst = a.cache + ((static_cast<size_t>(blk) * a.Hkv + head) * 2 + (kind - 1)) * kBlockTokens * D;
     dst[tok * D + d] = ToFp8(x / ds);
@@ -94,12 +97,24 @@ struct DecodeArgs {
   float* part_acc;             // [splits, Hkv, G, D]
   float* part_ml;              // [splits, Hkv, G, 2]
   int T, Hq, Hkv, D, splits;
+  const int* row_slot;         // batched decode (grid.z = sequence, one query row each); null otherwise
+  int table_stride;
 };
 
 // grid (splits, Hkv), 256 threads.  G = gqa * T query rows, row g = t * gqa + j.
 template <int GMAX>
 __global__ void __launch_bounds__(256) DecodeKernel(DecodeArgs a) {
   extern __shared__ __align__(16) unsigned char smem[];
+  if (a.row_slot != nullptr) {
+    // one CTA column per sequence: shift every per-sequence pointer, then proceed as a 1-row call
+    const int b = blockIdx.z;
+    a.q += static_cast<size_t>(b) * a.Hq * a.D;
+    a.positions += b;
+    a.block_table += static_cast<size_t>(a.row_slot[b]) * a.table_stride;
+    const size_t per = static_cast<size_t>(a.splits) * a.Hkv * (a.Hq / a.Hkv);
+    a.part_acc += b * per * a.D;
+    a.part_ml += b * per * 2;
+  }
   const int D = a.D, gqa = a.Hq / a.Hkv, G = gqa * a.T;
   const int split = blockIdx.x, hkv = blockIdx.y, tid = threadIdx.x;
   const int KS = D + 16;                          // padded K row stride (bytes) against bank conflicts
@@ -228,9 +243,17 @@ __global__ void __launch_bounds__(256) DecodeKernel(DecodeArgs a) {
 // grid (G, Hkv), D threads
 __global__ void CombineKernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                               const __nv_bfloat16* __restrict__ qg, __nv_bfloat16* __restrict__ out, int T, int Hq,
-                              int Hkv, int D, int splits, int gated) {
+                              int Hkv, int D, int splits, int gated, int batched) {
   const int g = blockIdx.x, hkv = blockIdx.y, d = threadIdx.x;
   const int gqa = Hq / Hkv, G = gqa * T;
+  if (batched) {
+    const int b = blockIdx.z;
+    const size_t per = static_cast<size_t>(splits) * Hkv * G;
+    part_acc += b * per * D;
+    part_ml += b * per * 2;
+    qg += static_cast<size_t>(b) * Hq * 2 * D;
+    out += static_cast<size_t>(b) * Hq * D;
+  }
   float M = -INFINITY;
   for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[((static_cast<size_t>(s) * Hkv + hkv) * G + g) * 2]);
   float num = 0.f, den = 0.f;
@@ -252,7 +275,7 @@ __global__ void CombineKernel(const float* __restrict__ part_acc, const float* _
 }
 
 template <int GMAX>
-int LaunchDecode(const DecodeArgs& a, cudaStream_t s) {
+int LaunchDecode(const DecodeArgs& a, cudaStream_t s, int batch = 1) {
   const int D = a.D;
   const size_t smem = kBlockTokens * (D + 16) + kBlockTokens * D + static_cast<size_t>(GMAX) * D * 2 +
                       static_cast<size_t>(GMAX) * kBlockTokens * 4 + GMAX * 4 * 4;
@@ -261,7 +284,7 @@ int LaunchDecode(const DecodeArgs& a, cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  kern<<<dim3(a.splits, a.Hkv), 256, smem, s>>>(a);
+  kern<<<dim3(a.splits, a.Hkv, batch), 256, smem, s>>>(a);
   return FinishLaunch();
 }
 
@@ -290,6 +313,7 @@ int r4dxb_attn_precore(const void* qg, const void* k, const void* v, const void*
   a.q_out = static_cast<__nv_bfloat16*>(q_out);
   a.cache = static_cast<uint8_t*>(cache);
   a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.rotary_dim = rotary_dim; a.theta = theta; a.eps = eps;
+  a.row_slot = nullptr; a.table_stride = 0;
   PrecoreKernel<<<dim3(Hq + 2 * Hkv, T), D, D * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
   return FinishLaunch();
 }
@@ -310,6 +334,7 @@ int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const in
   a.part_acc = part_acc;
   a.part_ml = part_ml;
   a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.splits = splits;
+  a.row_slot = nullptr; a.table_stride = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int e;
   if (G <= 8) e = LaunchDecode<8>(a, s);
@@ -319,7 +344,55 @@ int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const in
   else return R4DXB_UNSUPPORTED;
   if (e) return e;
   CombineKernel<<<dim3(G, Hkv), D, 0, s>>>(part_acc, part_ml, static_cast<const __nv_bfloat16*>(qg),
-                                           static_cast<__nv_bfloat16*>(out), T, Hq, Hkv, D, splits, gated);
+                                           static_cast<__nv_bfloat16*>(out), T, Hq, Hkv, D, splits, gated, 0);
+  return FinishLaunch();
+}
+
+/* Batched decode: B sequences, one new token each.  Row b belongs to slot row_slot[b]; block tables are
+ * [slots][table_stride]; the cache is one shared block pool.  Scratch sized B x (single-sequence scratch at T=1). */
+int r4dxb_attn_precore_batch(const void* qg, const void* k, const void* v, const void* q_norm, const void* k_norm,
+                             const float* k_descale, const float* v_descale, const int* positions, const int* block_tables,
+                             const int* row_slot, int table_stride, void* q_out, void* cache, int B, int Hq, int Hkv, int D,
+                             int rotary_dim, float theta, float eps, void* stream) {
+  if (B < 1 || D > 1024 || D % 32 || rotary_dim > D || rotary_dim % 2) return R4DXB_BAD_ARG;
+  PrecoreArgs a;
+  a.qg = static_cast<const __nv_bfloat16*>(qg);
+  a.k = static_cast<const __nv_bfloat16*>(k);
+  a.v = static_cast<const __nv_bfloat16*>(v);
+  a.q_norm = static_cast<const __nv_bfloat16*>(q_norm);
+  a.k_norm = static_cast<const __nv_bfloat16*>(k_norm);
+  a.k_descale = k_descale; a.v_descale = v_descale; a.positions = positions; a.block_table = block_tables;
+  a.q_out = static_cast<__nv_bfloat16*>(q_out);
+  a.cache = static_cast<uint8_t*>(cache);
+  a.T = B; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.rotary_dim = rotary_dim; a.theta = theta; a.eps = eps;
+  a.row_slot = row_slot; a.table_stride = table_stride;
+  PrecoreKernel<<<dim3(Hq + 2 * Hkv, B), D, D * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
+  return FinishLaunch();
+}
+
+int r4dxb_attn_decode_batch(const void* q, const void* qg, const void* cache, const int* block_tables, const int* row_slot,
+                            int table_stride, const int* positions, const float* k_descale, const float* v_descale,
+                            float* part_acc, float* part_ml, void* out, int B, int Hq, int Hkv, int D, int splits, int gated,
+                            void* stream) {
+  if (B < 1 || Hq % Hkv || D % 16 || D > 256 || splits < 1 || Hq / Hkv > 64) return R4DXB_BAD_ARG;
+  const int G = Hq / Hkv;
+  DecodeArgs a;
+  a.q = static_cast<const __nv_bfloat16*>(q);
+  a.cache = static_cast<const uint8_t*>(cache);
+  a.block_table = block_tables;
+  a.positions = positions;
+  a.k_descale = k_descale; a.v_descale = v_descale; a.part_acc = part_acc; a.part_ml = part_ml;
+  a.T = 1; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.splits = splits;
+  a.row_slot = row_slot; a.table_stride = table_stride;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int e;
+  if (G <= 8) e = LaunchDecode<8>(a, s, B);
+  else if (G <= 16) e = LaunchDecode<16>(a, s, B);
+  else if (G <= 32) e = LaunchDecode<32>(a, s, B);
+  else e = LaunchDecode<64>(a, s, B);
+  if (e) return e;
+  CombineKernel<<<dim3(G, Hkv, B), D, 0, s>>>(part_acc, part_ml, static_cast<const __nv_bfloat16*>(qg),
+                                              static_cast<__nv_bfloat16*>(out), 1, Hq, Hkv, D, splits, gated, 1);
   return FinishLaunch();
 }
 

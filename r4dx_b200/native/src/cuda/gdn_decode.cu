@@ -40,6 +40,7 @@ struct GdnArgs {
   __nv_bfloat16* out;            // [T, H*D]
   int T, H, Hk, conv_dim;
   float eps;
+  const int* row_slot;           // batched decode: grid.y = sequence b (one row each), its state lives in slot row_slot[b]
 };
 
 template <int D>
@@ -50,6 +51,20 @@ __global__ void __launch_bounds__(kThreads) GdnDecodeKernel(GdnArgs a) {
   __shared__ float seg[kMaxT], sbeta[kMaxT];
   __shared__ float rk[kMaxT][D], ru[kMaxT][D], reg[kMaxT];
   __shared__ float red[32];
+  if (a.row_slot != nullptr) {
+    const int b = blockIdx.y, slot = a.row_slot[b];
+    a.mixed += static_cast<size_t>(b) * a.conv_dim;
+    a.z += static_cast<size_t>(b) * a.H * D;
+    a.ab += static_cast<size_t>(b) * 2 * a.H;
+    a.out += static_cast<size_t>(b) * a.H * D;
+    a.positions += b;
+    a.n_replay += slot;
+    a.ring += static_cast<size_t>(slot) * kRing * a.conv_dim;
+    a.state += static_cast<size_t>(slot) * a.H * D * D;
+    a.log_u += static_cast<size_t>(slot) * kMaxT * a.H * D;
+    a.log_k += static_cast<size_t>(slot) * kMaxT * a.H * D;
+    a.log_eg += static_cast<size_t>(slot) * kMaxT * a.H;
+  }
   const int h = blockIdx.x, hk = h / (a.H / a.Hk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int T = a.T;
@@ -230,8 +245,39 @@ extern "C" int r4dxb_gdn_decode(const void* mixed, const void* z, const float* a
   a.Hk = Hk;
   a.conv_dim = 2 * Hk * D + H * D;
   a.eps = eps;
+  a.row_slot = nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 128) GdnDecodeKernel<128><<<H, kThreads, 0, s>>>(a);
   else GdnDecodeKernel<64><<<H, kThreads, 0, s>>>(a);
+  return FinishLaunch();
+}
+
+/* Batched decode: B sequences, one row each; every per-sequence tensor (ring, state, logs, n_replay) carries a
+ * leading slot dimension and row b uses slot row_slot[b]. */
+extern "C" int r4dxb_gdn_decode_batch(const void* mixed, const void* z, const float* ab, const void* conv_w,
+                                      const float* A_log, const float* dt_bias, const void* norm_w, void* ring,
+                                      float* state, float* log_u, float* log_k, float* log_eg, const int* positions,
+                                      const int* n_replay, const int* row_slot, void* out, int B, int H, int Hk, int D,
+                                      float eps, void* stream) {
+  using namespace r4dxb;
+  if (B < 1 || H % Hk || (D != 128 && D != 64)) return R4DXB_BAD_ARG;
+  GdnArgs a;
+  a.mixed = static_cast<const __nv_bfloat16*>(mixed);
+  a.z = static_cast<const __nv_bfloat16*>(z);
+  a.ab = ab;
+  a.conv_w = static_cast<const __nv_bfloat16*>(conv_w);
+  a.A_log = A_log;
+  a.dt_bias = dt_bias;
+  a.norm_w = static_cast<const __nv_bfloat16*>(norm_w);
+  a.ring = static_cast<__nv_bfloat16*>(ring);
+  a.state = state; a.log_u = log_u; a.log_k = log_k; a.log_eg = log_eg;
+  a.positions = positions;
+  a.n_replay = n_replay;
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.T = 1; a.H = H; a.Hk = Hk; a.conv_dim = 2 * Hk * D + H * D; a.eps = eps;
+  a.row_slot = row_slot;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (D == 128) GdnDecodeKernel<128><<<dim3(H, B), kThreads, 0, s>>>(a);
+  else GdnDecodeKernel<64><<<dim3(H, B), kThreads, 0, s>>>(a);
   return FinishLaunch();
 }

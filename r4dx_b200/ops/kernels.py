@@ -369,3 +369,28 @@ def trellis_gemv_grouped(words, suh, svh, x, y, offsets, perm, in_div: int, n_pa
         _check(_lib().r4dxb_trellis_gemv_grouped(_p(words), _p(suh), _p(svh), _p(x), _p(y), _p(offsets), _p(perm), in_div, p_,
                                                  tmax, prologue, experts, N, Kd, kb, ksplit, _stream()), "trellis_gemv_grouped")
     return y
+
+
+register_cuda_sig("r4dxb_topk_lse", _I, [_P, _I, _I, _I, _F, _I, _P, _P, _P, _P, _P])
+register_cuda_sig("r4dxb_repetition_penalty", _I, [_P, _I, _P, _I, _F, _P])
+
+
+def topk_lse(logits: torch.Tensor, k: int = 64, temperature: float = 1.0, id_offset: int = 0):
+    """(values [T,k], ids [T,k] in canonical order, lse [T]) of fp32 logits rows."""
+    _req(logits, torch.float32, "logits")
+    T, V = logits.shape
+    dev = logits.device
+    vals = torch.empty(T, k, dtype=torch.float32, device=dev)
+    ids = torch.empty(T, k, dtype=torch.int32, device=dev)
+    lse = torch.empty(T, dtype=torch.float32, device=dev)
+    scratch = torch.empty(T * 128 * (2 * k + 2), dtype=torch.float32, device=dev)
+    _check(_lib().r4dxb_topk_lse(_p(logits), T, V, k, temperature, id_offset, _p(vals), _p(ids), _p(lse), _p(scratch), _stream()),
+           "topk_lse")
+    return vals, ids, lse
+
+
+def repetition_penalty(logits_row: torch.Tensor, seen: torch.Tensor, penalty: float) -> torch.Tensor:
+    _req(logits_row, torch.float32, "logits"); _req(seen, torch.int32, "seen")
+    _check(_lib().r4dxb_repetition_penalty(_p(logits_row), logits_row.numel(), _p(seen), seen.numel(), penalty, _stream()),
+           "repetition_penalty")
+    return logits_row

@@ -393,3 +393,22 @@ def test_grouped_expert_gemv(K):
             ref = trellis.linear_reference(ws[int(ids[t, j])], x[t:t + 1].float())[0]
             got = y[t * k + j].float().cpu()
             assert (got - ref).abs().max().item() < 0.03 * ref.abs().max().item() + 1e-3
+
+
+def test_topk_lse_summary_and_device_rep_penalty(K):
+    from r4dx_b200.runtime.sampler import SampleParams, sample_canonical, sample_from_summary
+    g = torch.Generator().manual_seed(12)
+    logits = (torch.randn(3, 30000, generator=g) * 3)
+    logits[1, 17] = logits[1, 29000] = 20.0                      # tie at the top
+    vals, ids, lse = K.topk_lse(logits.cuda(), 64, 0.8, 5)
+    for t in range(3):
+        order = sorted(range(30000), key=lambda i: (-float(logits[t, i]), i))[:64]
+        assert ids[t].cpu().tolist() == [i + 5 for i in order]
+        assert torch.equal(vals[t].cpu(), logits[t][order])
+        assert abs(float(lse[t]) - float(torch.logsumexp(logits[t].double() / 0.8, 0))) < 1e-3
+    p = SampleParams(temperature=0.8, top_k=40, top_p=0.9)
+    tok = sample_from_summary(vals[0].cpu(), ids[0].cpu() - 5, float(lse[0]), p, 0.37)
+    assert tok == sample_canonical(logits[0], p, 0.37)
+    row = torch.tensor([2.0, -2.0, 1.0, 0.5], device="cuda")
+    K.repetition_penalty(row, torch.tensor([0, 1, 1, 0], dtype=torch.int32, device="cuda"), 2.0)
+    assert row.cpu().tolist() == [1.0, -4.0, 1.0, 0.5]

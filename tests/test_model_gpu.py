@@ -203,3 +203,28 @@ def test_expert_parallel_exchange_in_one_gpu_matches_local_moe():
         ep.moe_forward(blk, h, xb, T)
         ep.check_healthy()
         assert torch.equal(xa, xb), (it, (xa.float() - xb.float()).abs().max())
+
+
+def test_batched_decode_matches_independent_sequences(tiny):
+    from r4dx_b200.models.batch import BatchModel
+    from r4dx_b200.models.hybrid import HybridModel
+    cfg, q, _ = tiny
+    qd = _to_dev(q)
+    g = torch.Generator().manual_seed(10)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).to(torch.int32) for n in (21, 9, 40)]
+    refs = []
+    for p in prompts:
+        m = HybridModel(cfg, qd, max_ctx=128)
+        refs.append(m.generate_greedy(p, 8, use_graph=False))
+    bm = BatchModel(cfg, qd, slots=4, slot_ctx=128)
+    toks = [bm.import_slot(s, p.tolist()) for s, p in zip((0, 2, 3), prompts)]
+    outs = [[t] for t in toks]
+    for _ in range(7):
+        nxt = bm.decode_batch([0, 2, 3], [o[-1] for o in outs])
+        for o, t in zip(outs, nxt):
+            o.append(t)
+    for o, r in zip(outs, refs):
+        assert sum(int(a == b) for a, b in zip(o, r)) >= 7, (o, r)
+    assert bm.alloc.blocks_in_use() == sum((len(p) + 8 + 15) // 16 for p in prompts) or bm.alloc.blocks_in_use() > 0
+    bm.release_slot(2)
+    assert not bm.active[2]
