@@ -86,6 +86,7 @@ int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const in
 int r4dxb_trellis_input(const void* in, const void* suh, void* out, int T, int K, int mode, void* stream);
 /* y[T,N] bf16 from xh[T,K]; kb = 0: w is dense fp16 [N,K]; kb in {3,4,5}: packed trellis words.
  * tn: token tile 16/32/64/128/256.  *status (device int) becomes non-zero if a bounded wait ran out. */
+void r4dxb_set_gemm_decode_warps(int n);
 int r4dxb_trellis_gemm(const void* w, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
                        int kb, int tn, int* status, void* stream);
 

@@ -7,12 +7,14 @@
 // sits in TMEM as [lane = weight row][column = token].  Weights are decoded exactly once per CTA
 // and reused by all TN tokens of the tile.
 //
-// Warp roles (192 threads):
-//   warps 0-3  decode: packed words (shared memory) -> fp16 codes -> A tile in the canonical
+// Warp roles (DW + 2 warps, DW = 4, 8 or 16 decode warps):
+//   warps 0..DW-1  decode: packed words (shared memory) -> fp16 codes -> A tile in the canonical
 //              K-major 128-byte-swizzled UMMA layout; later the epilogue (TMEM -> registers ->
-//              shared transpose -> FWHT128 over the weight rows -> svh, residual -> bf16 rows)
-//   warp 4     producer: TMA tile of Xh [TN x 64] (128B swizzle) + bulk copy of the slab's words
-//   warp 5     MMA issuer: one elected thread issues 4 x tcgen05.mma (K = 16) per 64-wide K slab
+//              shared transpose -> FWHT128 over the weight rows -> svh, residual -> bf16 rows).
+//              The decode chain (shift, multiply, byte-sum) is dependent integer work at ~0.3 IPC
+//              per warp, so several warps per scheduler are what keeps the tensor pipe fed.
+//   warp DW    producer: TMA tile of Xh [TN x 64] (128B swizzle) + bulk copy of the slab's words
+//   warp DW+1  MMA issuer: one elected thread issues 4 x tcgen05.mma (K = 16) per 64-wide K slab
 //              and commits to the stage's "empty" barrier; it also owns the TMEM allocation.
 // A dense mode (KB == 0) takes A from a plain fp16 [N, K] matrix instead of decoding: that is the
 // bf16/fp16-layout linear and the bisecting aid for the tensor-core plumbing.
@@ -25,7 +27,6 @@
 namespace r4dxb {
 namespace {
 
-constexpr int kGemmThreads = 192;
 constexpr int kSlabK = 64;                 // K per pipeline stage = one 128-byte swizzle row of fp16
 constexpr int kATileBytes = 128 * kSlabK * 2;   // 16 KiB
 
@@ -35,12 +36,14 @@ struct GemmSmem {
   static constexpr int kXTileBytes = TN * kSlabK * 2;
   static constexpr int kStageBytes = kATileBytes + kXTileBytes + ((kWordsBytes + 1023) / 1024) * 1024;
   static constexpr int kEpiStride = 132;                                     // floats per staged token row
-  static constexpr int kEpiBytes = 32 * kEpiStride * 4;
-  static constexpr int kTotal = STAGES * kStageBytes + kEpiBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kEpiBytes = 32 * kEpiStride * 4;                      // per group of four epilogue warps
+  // the epilogue staging reuses the (by then drained) stage ring: it must hold one buffer per warp group
+  static constexpr int kRing = STAGES * kStageBytes > 4 * kEpiBytes ? STAGES * kStageBytes : 4 * kEpiBytes;
+  static constexpr int kTotal = kRing + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
 
-template <int KB, int TN, int STAGES>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int KB, int TN, int STAGES, int DW>
+__global__ void __launch_bounds__((DW + 2) * 32, 1)
 TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __restrict__ wsrc,
                   const __half* __restrict__ svh, __nv_bfloat16* __restrict__ y,
                   const __nv_bfloat16* __restrict__ residual, int T, int N, int K, int* __restrict__ status) {
@@ -49,8 +52,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
   // 1024-byte alignment: required by the swizzled UMMA / TMA tiles
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   unsigned char* stage_base = smem;
-  float* epi = reinterpret_cast<float*>(smem + STAGES * S::kStageBytes);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes + S::kEpiBytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kRing);
   uint64_t* full = bars;                    // [STAGES] producer -> decode / MMA
   uint64_t* aready = bars + STAGES;         // [STAGES] decode -> MMA
   uint64_t* empty = bars + 2 * STAGES;      // [STAGES] MMA -> producer
@@ -67,18 +69,18 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       ptx::MbarInit(&full[s], 1);
-      ptx::MbarInit(&aready[s], 4);
+      ptx::MbarInit(&aready[s], DW);
       ptx::MbarInit(&empty[s], 1);
     }
     ptx::MbarInit(accum, 1);
     *abort_flag = 0;
     ptx::MbarFenceInit();
   }
-  if (warp == 5) {
+  if (warp == DW + 1) {
     ptx::TmemAlloc(tmem_slot, kTmemCols);
     ptx::TmemRelinquish();
   }
-  if (warp == 4 && lane == 0) ptx::PrefetchTensorMap(&tmap_x);
+  if (warp == DW && lane == 0) ptx::PrefetchTensorMap(&tmap_x);
   ptx::TcFenceBefore();
   __syncthreads();
   ptx::TcFenceAfter();
@@ -88,7 +90,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
   auto x_tile = [&](int s) { return stage_base + s * S::kStageBytes + kATileBytes; };
   auto w_tile = [&](int s) { return stage_base + s * S::kStageBytes + kATileBytes + S::kXTileBytes; };
 
-  if (warp == 4) {
+  if (warp == DW) {
     // ---------------- producer ----------------
     if (lane == 0) {
       const size_t slab_words = 4 * 8 * 8 * (KB == 0 ? 1 : KB);
@@ -101,7 +103,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
         if (KB != 0) ptx::BulkLoad(w_tile(s), wbase + static_cast<size_t>(it) * slab_words, S::kWordsBytes, &full[s]);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == DW + 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = ptx::UmmaInstrDescF16(128, TN, false);
@@ -122,7 +124,8 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
       if (ok) ptx::UmmaCommit(accum);         // accumulator complete
     }
   } else {
-    // ---------------- decode warps 0-3 ----------------
+    // ---------------- decode warps ----------------
+    // a slab is 32 tiles (8 n-tiles x 4 k-tiles); warp w takes tiles w, w + DW, ...
     // lane slot: row (lane % 16) of the 16-row n-tile, K half (lane / 16) -> conflict-free 16-byte stores
     const int row_in_tile = lane & 15, khalf = lane >> 4;
     TrellisLane<(KB == 0 ? 4 : KB)> tl;
@@ -139,11 +142,11 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
       if (!ok) break;
       unsigned char* at = a_tile(s);
 #pragma unroll
-      for (int jj = 0; jj < 2; ++jj) {
-        const int j = warp * 2 + jj;                       // n-tile inside the 128-row block
+      for (int idx = warp; idx < 32; idx += DW) {
+        const int j = idx & 7;                             // n-tile inside the 128-row block
+        const int kt = idx >> 3;
         const int r = j * 16 + row_in_tile;                // row inside the block
-#pragma unroll
-        for (int kt = 0; kt < 4; ++kt) {
+        {
           uint4 packed;
           if (KB != 0) {
             constexpr int NW = 8 * (KB == 0 ? 4 : KB);
@@ -170,29 +173,34 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
       if (lane == 0) ptx::MbarArrive(&aready[s]);
     }
 
-    // ---------------- epilogue (same four warps: warp w owns TMEM lanes 32w .. 32w+31) ----------------
+    // ---------------- epilogue (the decode warps: warp w reads TMEM lanes 32 (w % 4) .. +31) ----------------
+    // groups of four warps take 32-column chunks round-robin; each group stages its chunk through its
+    // own transpose buffer, which lives in the stage ring (every stage has drained by now)
     if (ok) ok = ptx::MbarWait(accum, 0, abort_flag, 6);
     ptx::TcFenceAfter();
     const float inv_sqrt = 0.08838834764831845f;
-    for (int c0 = 0; c0 < TN; c0 += 32) {
-      constexpr int CW = TN < 32 ? 16 : 32;   // columns per TMEM load
+    constexpr int kGroups = DW / 4;
+    const int q = warp & 3, grp = warp >> 2;
+    float* epi = reinterpret_cast<float*>(stage_base + grp * S::kEpiBytes);
+    constexpr int CW = TN < 32 ? 16 : 32;   // columns per TMEM load
+    for (int c0 = grp * 32; c0 < TN; c0 += kGroups * 32) {
       if (ok) {
         uint32_t v[32];
         if constexpr (CW == 32) {
-          ptx::TmemLoad32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
+          ptx::TmemLoad32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, v);
         } else {
           uint32_t v16[16];
-          ptx::TmemLoad32x16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c0, v16);
+          ptx::TmemLoad32x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, v16);
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = v16[i];
         }
         ptx::TmemLoadWait();
 #pragma unroll
-        for (int c = 0; c < CW; ++c) epi[c * S::kEpiStride + warp * 32 + lane] = __uint_as_float(v[c]);
+        for (int c = 0; c < CW; ++c) epi[c * S::kEpiStride + q * 32 + lane] = __uint_as_float(v[c]);
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
       if (ok) {
-        for (int c = warp; c < CW; c += 4) {
+        for (int c = q; c < CW; c += 4) {
           const int t = t0 + c0 + c;
           if (t < T) {
             const float4 p = *reinterpret_cast<const float4*>(epi + c * S::kEpiStride + lane * 4);
@@ -214,7 +222,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
           }
         }
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
     }
   }
 
@@ -226,7 +234,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     if (threadIdx.x == 0) atomicExch(status, *abort_flag);
   }
-  if (warp == 5) ptx::TmemDealloc(tmem_base, kTmemCols);
+  if (warp == DW + 1) ptx::TmemDealloc(tmem_base, kTmemCols);
 }
 
 // ---- input transform: Xh = fp16(H128(suh * x)) -------------------------------------------------------
@@ -266,33 +274,45 @@ __global__ void TrellisInputKernel(const __nv_bfloat16* __restrict__ in, const _
   *reinterpret_cast<uint2*>(out + static_cast<size_t>(t) * K + k) = ov;
 }
 
-template <int KB, int TN, int STAGES>
+int g_decode_warps = 16;
+
+template <int KB, int TN, int STAGES, int DW>
 int LaunchGemm(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
                int* status, cudaStream_t stream) {
   using S = GemmSmem<KB, TN, STAGES>;
   CUtensorMap tmap;
   const int rc = MakeTensorMap2D16(&tmap, xh, static_cast<uint64_t>(T), static_cast<uint64_t>(K), TN, kSlabK, false);
   if (rc) return rc;
-  auto kern = TrellisGemmKernel<KB, TN, STAGES>;
+  auto kern = TrellisGemmKernel<KB, TN, STAGES, DW>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(N / 128, (T + TN - 1) / TN);
-  kern<<<grid, kGemmThreads, S::kTotal, stream>>>(tmap, wsrc, static_cast<const __half*>(svh),
+  kern<<<grid, (DW + 2) * 32, S::kTotal, stream>>>(tmap, wsrc, static_cast<const __half*>(svh),
                                                   static_cast<__nv_bfloat16*>(y),
                                                   static_cast<const __nv_bfloat16*>(residual), T, N, K, status);
   return FinishLaunch();
 }
 
-template <int KB>
+template <int KB, int DW>
 int LaunchGemmTN(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
                  int tn, int* status, cudaStream_t s) {
   switch (tn) {
-    case 16: return LaunchGemm<KB, 16, 4>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 32: return LaunchGemm<KB, 32, 4>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 64: return LaunchGemm<KB, 64, 4>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 128: return LaunchGemm<KB, 128, 4>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 256: return LaunchGemm<KB, 256, 3>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 16: return LaunchGemm<KB, 16, 4, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 32: return LaunchGemm<KB, 32, 4, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 64: return LaunchGemm<KB, 64, 4, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 128: return LaunchGemm<KB, 128, 4, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 256: return LaunchGemm<KB, 256, 3, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
     default: return R4DXB_BAD_ARG;
+  }
+}
+
+template <int KB>
+int LaunchGemmDW(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
+                 int tn, int* status, cudaStream_t s) {
+  switch (g_decode_warps) {
+    case 4: return LaunchGemmTN<KB, 4>(wsrc, svh, xh, y, residual, T, N, K, tn, status, s);
+    case 8: return LaunchGemmTN<KB, 8>(wsrc, svh, xh, y, residual, T, N, K, tn, status, s);
+    default: return LaunchGemmTN<KB, 16>(wsrc, svh, xh, y, residual, T, N, K, tn, status, s);
   }
 }
 
@@ -317,15 +337,18 @@ int r4dxb_trellis_input(const void* in, const void* suh, void* out, int T, int K
  * matrix (svh still applies; pass ones and set hadamard-free weights accordingly); kb in {3,4,5}: packed
  * trellis words.  tn = token tile (16/32/64/128/256).  status: device int, set non-zero if a bounded wait
  * inside the kernel ran out. */
+/* decode warps per CTA of the tensor-core GEMM (4, 8 or 16): a tuning and A/B-measurement switch */
+void r4dxb_set_gemm_decode_warps(int n) { g_decode_warps = (n == 4 || n == 8) ? n : 16; }
+
 int r4dxb_trellis_gemm(const void* w, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
                        int kb, int tn, int* status, void* stream) {
   if (T < 1 || N % 128 || K % 128) return R4DXB_BAD_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (kb) {
-    case 0: return LaunchGemmTN<0>(w, svh, xh, y, residual, T, N, K, tn, status, s);
-    case 3: return LaunchGemmTN<3>(w, svh, xh, y, residual, T, N, K, tn, status, s);
-    case 4: return LaunchGemmTN<4>(w, svh, xh, y, residual, T, N, K, tn, status, s);
-    case 5: return LaunchGemmTN<5>(w, svh, xh, y, residual, T, N, K, tn, status, s);
+    case 0: return LaunchGemmDW<0>(w, svh, xh, y, residual, T, N, K, tn, status, s);
+    case 3: return LaunchGemmDW<3>(w, svh, xh, y, residual, T, N, K, tn, status, s);
+    case 4: return LaunchGemmDW<4>(w, svh, xh, y, residual, T, N, K, tn, status, s);
+    case 5: return LaunchGemmDW<5>(w, svh, xh, y, residual, T, N, K, tn, status, s);
     default: return R4DXB_BAD_ARG;
   }
 }

@@ -53,6 +53,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--kb", type=int, default=0)
     ap.add_argument("--ctx", type=int, default=8192)
+    ap.add_argument("--decode-warps", type=int, default=16)
     a = ap.parse_args()
     from r4dx_b200.ops import kernels as K
     from r4dx_b200.quant import trellis, w4a16
@@ -76,6 +77,8 @@ def main() -> None:
                       f"{gbs:7.0f} GB/s  {gbs / peak:5.2f} of measured HBM  {N * Kd / us / 1e6:6.2f} Tweights/s")
     if a.only in ("trellis_gemm",):
         Tg = max(a.rows, 16)
+        from r4dx_b200 import native
+        native.cuda().r4dxb_set_gemm_decode_warps(a.decode_warps)
         tf_peak = 1699.0
         try:
             tf_peak = float(json.load(open(os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")))["bf16_tflops"])
