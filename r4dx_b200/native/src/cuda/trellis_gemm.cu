@@ -30,34 +30,51 @@ namespace {
 constexpr int kSlabK = 64;                 // K per pipeline stage = one 128-byte swizzle row of fp16
 constexpr int kATileBytes = 128 * kSlabK * 2;   // 16 KiB
 
-template <int KB, int TN, int STAGES>
+// Three rings, sized independently so that cheap data is prefetched deep and the big tile is not:
+//   words (<= 5 KiB per slab, WST deep)  producer W -> decode warps
+//   A     (16 KiB per slab, AST deep)    decode warps -> MMA
+//   X     (TN x 128 B per slab, XST deep) producer X -> MMA
+template <int KB, int TN>
 struct GemmSmem {
   static constexpr int kWordsBytes = (KB == 0) ? 0 : 4 * 8 * 8 * KB * 4;   // 4 k-tiles x 8 n-tiles x 8KB words
+  static constexpr int kWordsSlot = ((kWordsBytes + 1023) / 1024) * 1024;
   static constexpr int kXTileBytes = TN * kSlabK * 2;
-  static constexpr int kStageBytes = kATileBytes + kXTileBytes + ((kWordsBytes + 1023) / 1024) * 1024;
+  static constexpr int WST = 6;
+  static constexpr int AST = 3;
+  static constexpr int XST = TN >= 512 ? 2 : (TN >= 256 ? 3 : 4);
+  static constexpr int kABytes = AST * kATileBytes;
+  static constexpr int kXBytes = XST * kXTileBytes;
   static constexpr int kEpiStride = 132;                                     // floats per staged token row
   static constexpr int kEpiBytes = 32 * kEpiStride * 4;                      // per group of four epilogue warps
-  // the epilogue staging reuses the (by then drained) stage ring: it must hold one buffer per warp group
-  static constexpr int kRing = STAGES * kStageBytes > 4 * kEpiBytes ? STAGES * kStageBytes : 4 * kEpiBytes;
-  static constexpr int kTotal = kRing + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  // the epilogue staging reuses the (by then drained) rings: it must hold one buffer per warp group
+  static constexpr int kRingsRaw = kABytes + kXBytes + WST * kWordsSlot;
+  static constexpr int kRing = kRingsRaw > 4 * kEpiBytes ? kRingsRaw : 4 * kEpiBytes;
+  static constexpr int kBars = 2 * WST + 2 * AST + 2 * XST + 1;
+  static constexpr int kTotal = kRing + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
-template <int KB, int TN, int STAGES, int DW>
-__global__ void __launch_bounds__((DW + 2) * 32, 1)
+template <int KB, int TN, int DW>
+__global__ void __launch_bounds__((DW + 3) * 32, 1)
 TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __restrict__ wsrc,
                   const __half* __restrict__ svh, __nv_bfloat16* __restrict__ y,
                   const __nv_bfloat16* __restrict__ residual, int T, int N, int K, int* __restrict__ status) {
-  using S = GemmSmem<KB, TN, STAGES>;
+  using S = GemmSmem<KB, TN>;
+  constexpr int WST = S::WST, AST = S::AST, XST = S::XST;
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment: required by the swizzled UMMA / TMA tiles
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
-  unsigned char* stage_base = smem;
+  unsigned char* a_ring = smem;
+  unsigned char* x_ring = smem + S::kABytes;
+  unsigned char* w_ring = smem + S::kABytes + S::kXBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S::kRing);
-  uint64_t* full = bars;                    // [STAGES] producer -> decode / MMA
-  uint64_t* aready = bars + STAGES;         // [STAGES] decode -> MMA
-  uint64_t* empty = bars + 2 * STAGES;      // [STAGES] MMA -> producer
-  uint64_t* accum = bars + 3 * STAGES;      // [1]      MMA -> epilogue
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * STAGES + 1);
+  uint64_t* wfull = bars;                   // [WST] producer W -> decode
+  uint64_t* wempty = wfull + WST;           // [WST] decode -> producer W
+  uint64_t* afull = wempty + WST;           // [AST] decode -> MMA
+  uint64_t* aempty = afull + AST;           // [AST] MMA -> decode
+  uint64_t* xfull = aempty + AST;           // [XST] producer X -> MMA
+  uint64_t* xempty = xfull + XST;           // [XST] MMA -> producer X
+  uint64_t* accum = xempty + XST;           // [1]   MMA -> epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -65,12 +82,21 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
   const int t0 = blockIdx.y * TN;            // first token of the tile
   const int slabs = K / kSlabK;
   constexpr uint32_t kTmemCols = TN < 32 ? 32 : TN;
+  constexpr int kHalves = TN > 256 ? TN / 256 : 1;     // one MMA covers at most 256 token columns
+  constexpr int kMmaN = TN > 256 ? 256 : TN;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      ptx::MbarInit(&full[s], 1);
-      ptx::MbarInit(&aready[s], DW);
-      ptx::MbarInit(&empty[s], 1);
+    for (int s = 0; s < WST; ++s) {
+      ptx::MbarInit(&wfull[s], 1);
+      ptx::MbarInit(&wempty[s], DW);
+    }
+    for (int s = 0; s < AST; ++s) {
+      ptx::MbarInit(&afull[s], DW);
+      ptx::MbarInit(&aempty[s], 1);
+    }
+    for (int s = 0; s < XST; ++s) {
+      ptx::MbarInit(&xfull[s], 1);
+      ptx::MbarInit(&xempty[s], 1);
     }
     ptx::MbarInit(accum, 1);
     *abort_flag = 0;
@@ -86,40 +112,52 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
   ptx::TcFenceAfter();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto a_tile = [&](int s) { return stage_base + s * S::kStageBytes; };
-  auto x_tile = [&](int s) { return stage_base + s * S::kStageBytes + kATileBytes; };
-  auto w_tile = [&](int s) { return stage_base + s * S::kStageBytes + kATileBytes + S::kXTileBytes; };
-
   if (warp == DW) {
-    // ---------------- producer ----------------
+    // ---------------- producer X: TMA tiles of the transformed activations ----------------
     if (lane == 0) {
+      for (int it = 0; it < slabs; ++it) {
+        const int s = it % XST, round = it / XST;
+        if (!ptx::MbarWait(&xempty[s], (round & 1) ^ 1, abort_flag, 1)) break;
+        ptx::MbarArriveExpectTx(&xfull[s], S::kXTileBytes);
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h)
+          ptx::TmaLoad2D(x_ring + s * S::kXTileBytes + h * (kMmaN * kSlabK * 2), &tmap_x, &xfull[s], it * kSlabK, t0 + h * kMmaN);
+      }
+    }
+  } else if (warp == DW + 2) {
+    // ---------------- producer W: packed words, prefetched WST slabs deep ----------------
+    if (KB != 0 && lane == 0) {
       const size_t slab_words = 4 * 8 * 8 * (KB == 0 ? 1 : KB);
       const uint32_t* wbase = static_cast<const uint32_t*>(wsrc) + static_cast<size_t>(nb) * (K / 16) * 8 * 8 * (KB == 0 ? 1 : KB);
       for (int it = 0; it < slabs; ++it) {
-        const int s = it % STAGES, round = it / STAGES;
-        if (!ptx::MbarWait(&empty[s], (round & 1) ^ 1, abort_flag, 1)) break;
-        ptx::MbarArriveExpectTx(&full[s], S::kXTileBytes + S::kWordsBytes);
-        ptx::TmaLoad2D(x_tile(s), &tmap_x, &full[s], it * kSlabK, t0);
-        if (KB != 0) ptx::BulkLoad(w_tile(s), wbase + static_cast<size_t>(it) * slab_words, S::kWordsBytes, &full[s]);
+        const int s = it % WST, round = it / WST;
+        if (!ptx::MbarWait(&wempty[s], (round & 1) ^ 1, abort_flag, 7)) break;
+        ptx::MbarArriveExpectTx(&wfull[s], S::kWordsBytes);
+        ptx::BulkLoad(w_ring + s * S::kWordsSlot, wbase + static_cast<size_t>(it) * slab_words, S::kWordsBytes, &wfull[s]);
       }
     }
   } else if (warp == DW + 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::UmmaInstrDescF16(128, TN, false);
+      constexpr uint32_t idesc = ptx::UmmaInstrDescF16(128, kMmaN, false);
       bool ok = true;
       for (int it = 0; it < slabs && ok; ++it) {
-        const int s = it % STAGES, round = it / STAGES;
-        ok = ptx::MbarWait(&full[s], round & 1, abort_flag, 2) && ptx::MbarWait(&aready[s], round & 1, abort_flag, 3);
+        const int sa = it % AST, ra = it / AST, sx = it % XST, rx = it / XST;
+        ok = ptx::MbarWait(&xfull[sx], rx & 1, abort_flag, 2) && ptx::MbarWait(&afull[sa], ra & 1, abort_flag, 3);
         if (!ok) break;
         ptx::TcFenceAfter();
-        const uint32_t a_addr = ptx::SmemAddr(a_tile(s)), b_addr = ptx::SmemAddr(x_tile(s));
+        const uint32_t a_addr = ptx::SmemAddr(a_ring + sa * kATileBytes), b_addr = ptx::SmemAddr(x_ring + sx * S::kXTileBytes);
 #pragma unroll
-        for (int k = 0; k < kSlabK / 16; ++k) {
-          const uint64_t da = ptx::UmmaDescSw128(a_addr + k * 32), db = ptx::UmmaDescSw128(b_addr + k * 32);
-          ptx::UmmaF16(tmem_base, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+        for (int h = 0; h < kHalves; ++h) {
+#pragma unroll
+          for (int k = 0; k < kSlabK / 16; ++k) {
+            const uint64_t da = ptx::UmmaDescSw128(a_addr + k * 32);
+            const uint64_t db = ptx::UmmaDescSw128(b_addr + h * (kMmaN * kSlabK * 2) + k * 32);
+            ptx::UmmaF16(tmem_base + h * kMmaN, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+          }
         }
-        ptx::UmmaCommit(&empty[s]);           // frees the stage once these MMAs have read it
+        ptx::UmmaCommit(&aempty[sa]);         // frees the A tile and the X tile once these MMAs have read them
+        ptx::UmmaCommit(&xempty[sx]);
       }
       if (ok) ptx::UmmaCommit(accum);         // accumulator complete
     }
@@ -132,56 +170,53 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
     tl.Init(2 * row_in_tile + khalf);
     bool ok = true;
     for (int it = 0; it < slabs && ok; ++it) {
-      const int s = it % STAGES, round = it / STAGES;
-      if (KB != 0) {
-        ok = ptx::MbarWait(&full[s], round & 1, abort_flag, 4);
-      } else {
-        // dense mode reads global memory directly, but the A tile must be free again
-        ok = ptx::MbarWait(&empty[s], (round & 1) ^ 1, abort_flag, 5);
-      }
+      const int sa = it % AST, ra = it / AST, sw = it % WST, rw = it / WST;
+      if (KB != 0) ok = ptx::MbarWait(&wfull[sw], rw & 1, abort_flag, 4);
+      ok = ok && ptx::MbarWait(&aempty[sa], (ra & 1) ^ 1, abort_flag, 5);
       if (!ok) break;
-      unsigned char* at = a_tile(s);
+      unsigned char* at = a_ring + sa * kATileBytes;
 #pragma unroll
       for (int idx = warp; idx < 32; idx += DW) {
         const int j = idx & 7;                             // n-tile inside the 128-row block
         const int kt = idx >> 3;
         const int r = j * 16 + row_in_tile;                // row inside the block
-        {
-          uint4 packed;
-          if (KB != 0) {
-            constexpr int NW = 8 * (KB == 0 ? 4 : KB);
-            const uint32_t* tw = reinterpret_cast<const uint32_t*>(w_tile(s)) + (kt * 8 + j) * NW;
-            uint32_t hi, lo;
-            tl.Window(tw[tl.i0], tw[tl.i1], (KB == 4) ? 0u : tw[tl.i2], hi, lo);
-            __half2 w[4];
-            TrellisDecode8<(KB == 0 ? 4 : KB)>(hi, lo, w);
-            packed.x = *reinterpret_cast<uint32_t*>(&w[0]);
-            packed.y = *reinterpret_cast<uint32_t*>(&w[1]);
-            packed.z = *reinterpret_cast<uint32_t*>(&w[2]);
-            packed.w = *reinterpret_cast<uint32_t*>(&w[3]);
-          } else {
-            const __half* dense = static_cast<const __half*>(wsrc);
-            packed = __ldg(reinterpret_cast<const uint4*>(dense + (static_cast<size_t>(nb) * 128 + r) * K + it * kSlabK +
-                                                          kt * 16 + khalf * 8));
-          }
-          const int chunk = kt * 2 + khalf;                // 16-byte chunk inside the 128-byte row
-          *reinterpret_cast<uint4*>(at + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4)) = packed;
+        uint4 packed;
+        if (KB != 0) {
+          constexpr int NW = 8 * (KB == 0 ? 4 : KB);
+          const uint32_t* tw = reinterpret_cast<const uint32_t*>(w_ring + sw * S::kWordsSlot) + (kt * 8 + j) * NW;
+          uint32_t hi, lo;
+          tl.Window(tw[tl.i0], tw[tl.i1], (KB == 4) ? 0u : tw[tl.i2], hi, lo);
+          __half2 w[4];
+          TrellisDecode8<(KB == 0 ? 4 : KB)>(hi, lo, w);
+          packed.x = *reinterpret_cast<uint32_t*>(&w[0]);
+          packed.y = *reinterpret_cast<uint32_t*>(&w[1]);
+          packed.z = *reinterpret_cast<uint32_t*>(&w[2]);
+          packed.w = *reinterpret_cast<uint32_t*>(&w[3]);
+        } else {
+          const __half* dense = static_cast<const __half*>(wsrc);
+          packed = __ldg(reinterpret_cast<const uint4*>(dense + (static_cast<size_t>(nb) * 128 + r) * K + it * kSlabK +
+                                                        kt * 16 + khalf * 8));
         }
+        const int chunk = kt * 2 + khalf;                  // 16-byte chunk inside the 128-byte row
+        *reinterpret_cast<uint4*>(at + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4)) = packed;
       }
       ptx::FenceProxyAsyncShared();          // generic-proxy stores -> visible to the tensor core (async proxy)
       __syncwarp();
-      if (lane == 0) ptx::MbarArrive(&aready[s]);
+      if (lane == 0) {
+        ptx::MbarArrive(&afull[sa]);
+        if (KB != 0) ptx::MbarArrive(&wempty[sw]);
+      }
     }
 
     // ---------------- epilogue (the decode warps: warp w reads TMEM lanes 32 (w % 4) .. +31) ----------------
     // groups of four warps take 32-column chunks round-robin; each group stages its chunk through its
-    // own transpose buffer, which lives in the stage ring (every stage has drained by now)
+    // own transpose buffer, which lives in the rings (every slot has drained by now)
     if (ok) ok = ptx::MbarWait(accum, 0, abort_flag, 6);
     ptx::TcFenceAfter();
     const float inv_sqrt = 0.08838834764831845f;
     constexpr int kGroups = DW / 4;
     const int q = warp & 3, grp = warp >> 2;
-    float* epi = reinterpret_cast<float*>(stage_base + grp * S::kEpiBytes);
+    float* epi = reinterpret_cast<float*>(smem + grp * S::kEpiBytes);
     constexpr int CW = TN < 32 ? 16 : 32;   // columns per TMEM load
     for (int c0 = grp * 32; c0 < TN; c0 += kGroups * 32) {
       if (ok) {
@@ -276,20 +311,22 @@ __global__ void TrellisInputKernel(const __nv_bfloat16* __restrict__ in, const _
 
 int g_decode_warps = 16;
 
-template <int KB, int TN, int STAGES, int DW>
+template <int KB, int TN, int DW>
 int LaunchGemm(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
                int* status, cudaStream_t stream) {
-  using S = GemmSmem<KB, TN, STAGES>;
+  using S = GemmSmem<KB, TN>;
+  static_assert(S::kTotal <= 227 * 1024, "shared memory budget");
+  static_assert(S::kBars * 8 + 16 <= 512, "barrier block");
   CUtensorMap tmap;
-  const int rc = MakeTensorMap2D16(&tmap, xh, static_cast<uint64_t>(T), static_cast<uint64_t>(K), TN, kSlabK, false);
+  const int rc = MakeTensorMap2D16(&tmap, xh, static_cast<uint64_t>(T), static_cast<uint64_t>(K), TN > 256 ? 256 : TN, kSlabK, false);
   if (rc) return rc;
-  auto kern = TrellisGemmKernel<KB, TN, STAGES, DW>;
+  auto kern = TrellisGemmKernel<KB, TN, DW>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
   if (e != cudaSuccess) return static_cast<int>(e);
   dim3 grid(N / 128, (T + TN - 1) / TN);
-  kern<<<grid, (DW + 2) * 32, S::kTotal, stream>>>(tmap, wsrc, static_cast<const __half*>(svh),
-                                                  static_cast<__nv_bfloat16*>(y),
-                                                  static_cast<const __nv_bfloat16*>(residual), T, N, K, status);
+  kern<<<grid, (DW + 3) * 32, S::kTotal, stream>>>(tmap, wsrc, static_cast<const __half*>(svh),
+                                                   static_cast<__nv_bfloat16*>(y),
+                                                   static_cast<const __nv_bfloat16*>(residual), T, N, K, status);
   return FinishLaunch();
 }
 
@@ -297,11 +334,12 @@ template <int KB, int DW>
 int LaunchGemmTN(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
                  int tn, int* status, cudaStream_t s) {
   switch (tn) {
-    case 16: return LaunchGemm<KB, 16, 4, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 32: return LaunchGemm<KB, 32, 4, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 64: return LaunchGemm<KB, 64, 4, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 128: return LaunchGemm<KB, 128, 4, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 256: return LaunchGemm<KB, 256, 3, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 16: return LaunchGemm<KB, 16, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 32: return LaunchGemm<KB, 32, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 64: return LaunchGemm<KB, 64, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 128: return LaunchGemm<KB, 128, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 256: return LaunchGemm<KB, 256, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 512: return LaunchGemm<KB, 512, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
     default: return R4DXB_BAD_ARG;
   }
 }
@@ -335,7 +373,7 @@ int r4dxb_trellis_input(const void* in, const void* suh, void* out, int T, int K
 
 /* y[T, N] (bf16) from xh[T, K] (fp16, already input-transformed).  kb = 0: `w` is a dense fp16 [N, K]
  * matrix (svh still applies; pass ones and set hadamard-free weights accordingly); kb in {3,4,5}: packed
- * trellis words.  tn = token tile (16/32/64/128/256).  status: device int, set non-zero if a bounded wait
+ * trellis words.  tn = token tile (16/32/64/128/256/512).  status: device int, set non-zero if a bounded wait
  * inside the kernel ran out. */
 /* decode warps per CTA of the tensor-core GEMM (4, 8 or 16): a tuning and A/B-measurement switch */
 void r4dxb_set_gemm_decode_warps(int n) { g_decode_warps = (n == 4 || n == 8) ? n : 16; }

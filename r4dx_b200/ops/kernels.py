@@ -278,11 +278,26 @@ def trellis_input(x: torch.Tensor, suh: torch.Tensor, out: Optional[torch.Tensor
     return out
 
 
-def pick_token_tile(T: int) -> int:
+_TILE_COST = {128: 0.60, 256: 0.62, 512: 1.0}   # relative time of one CTA's K loop (decode-bound below 512 columns)
+
+
+def pick_token_tile(T: int, N: int = 0) -> int:
+    """Token-tile width of the tensor-core GEMM: the smallest tile that covers T below 512 rows; above,
+    the width whose CTA count wastes the fewest of the 148 SMs' waves (one CTA per SM)."""
     for tn in (16, 32, 64, 128):
         if T <= tn:
             return tn
-    return 256 if T >= 512 else 128
+    if T < 512:
+        return 128
+    if N <= 0:
+        return 512 if T >= 1024 else 256
+    best, best_cost = 256, None
+    for tn, c in _TILE_COST.items():
+        ctas = (N // 128) * ((T + tn - 1) // tn)
+        cost = ((ctas + 147) // 148) * c
+        if best_cost is None or cost < best_cost - 1e-9 or (abs(cost - best_cost) < 1e-9 and tn > best):
+            best, best_cost = tn, cost
+    return best
 
 
 def trellis_gemm(w: TrellisWeight, xh: torch.Tensor, residual: Optional[torch.Tensor] = None,
@@ -291,7 +306,7 @@ def trellis_gemm(w: TrellisWeight, xh: torch.Tensor, residual: Optional[torch.Te
     _req(xh, torch.float16, "xh")
     T = xh.numel() // w.K
     out = out if out is not None else torch.empty(T, w.N, dtype=BF, device=xh.device)
-    tn = tn or pick_token_tile(T)
+    tn = tn or pick_token_tile(T, w.N)
     _check(_lib().r4dxb_trellis_gemm(_p(w.words), _p(w.svh), _p(xh), _p(out), _p(residual), T, w.N, w.K, w.kb, tn,
                                      _p(gemm_status(xh.device)), _stream()), "trellis_gemm")
     return out
@@ -303,7 +318,7 @@ def dense_gemm_hadamard(W: torch.Tensor, svh: torch.Tensor, xh: torch.Tensor, tn
     N, K_ = W.shape
     T = xh.numel() // K_
     out = torch.empty(T, N, dtype=BF, device=xh.device)
-    tn = tn or pick_token_tile(T)
+    tn = tn or pick_token_tile(T, N)
     _check(_lib().r4dxb_trellis_gemm(_p(W), _p(svh), _p(xh), _p(out), None, T, N, K_, 0, tn,
                                      _p(gemm_status(xh.device)), _stream()), "dense_gemm")
     return out

@@ -54,6 +54,7 @@ def main() -> None:
     ap.add_argument("--kb", type=int, default=0)
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--decode-warps", type=int, default=16)
+    ap.add_argument("--tn", type=int, default=0)
     a = ap.parse_args()
     from r4dx_b200.ops import kernels as K
     from r4dx_b200.quant import trellis, w4a16
@@ -92,10 +93,11 @@ def main() -> None:
                 x = torch.randn(Tg, Kd, device=dev).to(BF)
                 xh = K.trellis_input(x, w.suh)
                 y = torch.empty(Tg, N, dtype=BF, device=dev)
-                us = timed(lambda: K.trellis_gemm(w, xh, out=y), a.iters, flush)
+                tn = a.tn or K.pick_token_tile(Tg, N)
+                us = timed(lambda: K.trellis_gemm(w, xh, out=y, tn=tn), a.iters, flush)
                 K.check_gemm_status(dev)
                 tf = 2.0 * N * Kd * Tg / us / 1e6
-                print(f"trellis_gemm {name:12s} N={N:6d} K={Kd:6d} kb={kb} T={Tg} tn={K.pick_token_tile(Tg)}: {us:9.1f} us  "
+                print(f"trellis_gemm {name:12s} N={N:6d} K={Kd:6d} kb={kb} T={Tg} tn={tn}: {us:9.1f} us  "
                       f"{tf:7.1f} TFLOP/s  {tf / tf_peak:5.2f} of measured cuBLAS bf16")
     if a.only in ("", "w4a16"):
         N, Kd = 248320, 5120

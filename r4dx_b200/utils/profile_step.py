@@ -21,13 +21,28 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=1)
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--model", default="27b", choices=["27b", "small"])
+    ap.add_argument("--prefill", type=int, default=0, help="profile one chunked prefill of this many tokens instead of decode steps")
     a = ap.parse_args()
     from r4dx_b200.config import qwen_hybrid_27b_config, small_hybrid_config
     from r4dx_b200.models.hybrid import HybridModel
     from r4dx_b200.quant.weights import synthetic_weight_set
     cfg = qwen_hybrid_27b_config(a.layers) if a.model == "27b" else small_hybrid_config(a.layers)
     w = synthetic_weight_set(cfg, device="cuda", seed=0)
-    m = HybridModel(cfg, w, max_ctx=a.ctx + 64 + a.rows * (a.steps + 2))
+    m = HybridModel(cfg, w, max_ctx=max(a.ctx, a.prefill) + 64 + a.rows * (a.steps + 2))
+    if a.prefill:
+        ids = torch.randint(0, cfg.vocab_size, (a.prefill,), dtype=torch.int32)
+        m.prefill(ids[:4096])          # warm-up (allocates the chunk buffers)
+        m.reset()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.profiler.start()
+        e0.record()
+        m.prefill(ids)
+        e1.record()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(f"prefill of {a.prefill} tokens, {a.layers} layers: {e0.elapsed_time(e1):.2f} ms")
+        return
     m.pos = a.ctx
     ids = torch.randint(0, cfg.vocab_size, (a.rows,), dtype=torch.int32)
     m.feed(ids)

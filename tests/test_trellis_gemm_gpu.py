@@ -27,7 +27,7 @@ def test_input_transform(K):
     assert torch.allclose(out2.float().cpu(), R.fwht(act * suh.float()[None]), atol=2e-2, rtol=1e-2)
 
 
-@pytest.mark.parametrize("T,tn", [(16, 16), (40, 64), (128, 128), (300, 128), (512, 256)])
+@pytest.mark.parametrize("T,tn", [(16, 16), (40, 64), (128, 128), (300, 128), (512, 256), (700, 512), (1024, 512)])
 def test_dense_tensor_core_path(K, T, tn):
     """Dense fp16 A operand: isolates TMA / UMMA descriptors / TMEM epilogue from the trellis decode."""
     g = torch.Generator().manual_seed(T)
@@ -43,7 +43,7 @@ def test_dense_tensor_core_path(K, T, tn):
 
 
 @pytest.mark.parametrize("kb", [3, 4, 5])
-@pytest.mark.parametrize("T,tn", [(16, 16), (100, 128), (512, 256)])
+@pytest.mark.parametrize("T,tn", [(16, 16), (100, 128), (512, 256), (600, 512)])
 def test_trellis_gemm_matches_reference_and_gemv(K, kb, T, tn):
     from r4dx_b200.quant import trellis
     g = torch.Generator().manual_seed(kb * 100 + T)
