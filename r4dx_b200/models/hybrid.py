@@ -315,6 +315,8 @@ class HybridModel:
                   k=e(C, cfg.kv_dim), v=e(C, cfg.kv_dim), q=e(C, cfg.q_dim), gate_up=e(C, 2 * cfg.intermediate_size),
                   gdn=dict(q=e(C, Hk, Dg, dtype=f32), k=e(C, Hk, Dg, dtype=f32), v=e(C, Hv, Dg, dtype=f32),
                            o=e(C, Hv, Dg, dtype=f32), eg=e(C, Hv, dtype=f32), beta=e(C, Hv, dtype=f32)))
+        if Dg == 128 and Hv > 0 and C >= 128:
+            cb["gdn"]["ws"] = e(K.gdn_chunk_ws_floats(C, Hv), dtype=f32)
         self._cb = cb
         return cb
 

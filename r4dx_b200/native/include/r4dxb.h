@@ -109,8 +109,9 @@ int r4dxb_attn_decode_batch(const void* q, const void* qg, const void* cache, co
  * Commits the state (no log).  fp32 scratch: q,k [T,Hk,D], v,o [T,H,D], eg,beta [T,H]. */
 int r4dxb_gdn_prefill(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
                       const float* dt_bias, const void* norm_w, void* ring, float* state, float* q, float* k, float* v,
-                      float* eg, float* beta, float* o, void* out, int T, int H, int Hk, int D, int pos0, float eps,
+                      float* eg, float* beta, float* o, void* out, int T, int H, int Hk, int D, int pos0, float eps, float* ws,
                       void* stream);
+long long r4dxb_gdn_chunk_ws_floats(int T, int H);
 /* causal GQA attention of T query rows at positions pos0.. over the paged fp8 cache (rows already written) */
 int r4dxb_attn_prefill(const void* q, const void* qg, const void* cache, const int* block_table, const float* k_descale,
                        const float* v_descale, void* out, int T, int Hq, int Hkv, int D, int pos0, int gated, void* stream);

@@ -216,17 +216,23 @@ __global__ void GdnGatedNormKernel(const float* __restrict__ o, const __nv_bfloa
 }
 
 }  // namespace
+
+int LaunchGdnChunked(const float* q, const float* k, const float* v, const float* eg, const float* beta, float* state, float* o,
+                     float* ws, int T, int H, int Hk, cudaStream_t s);   // gdn_chunk.cu
+
 }  // namespace r4dxb
 
 using namespace r4dxb;
 
 extern "C" {
 
-/* scratch (fp32): q [T,Hk,D], k [T,Hk,D], v [T,H,D], eg [T,H], beta [T,H], o [T,H,D] */
+/* scratch (fp32): q [T,Hk,D], k [T,Hk,D], v [T,H,D], eg [T,H], beta [T,H], o [T,H,D];
+ * ws: optional workspace of r4dxb_gdn_chunk_ws_floats(T, H) floats - with it, D = 128 and T >= 128 the
+ * recurrence runs in its chunked tensor-core form, otherwise token by token */
 int r4dxb_gdn_prefill(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
                       const float* dt_bias, const void* norm_w, void* ring, float* state, float* q, float* k, float* v,
                       float* eg, float* beta, float* o, void* out, int T, int H, int Hk, int D, int pos0, float eps,
-                      void* stream) {
+                      float* ws, void* stream) {
   if (T < 1 || H % Hk || (D != 128 && D != 64)) return R4DXB_BAD_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   PrepArgs a;
@@ -244,7 +250,10 @@ int r4dxb_gdn_prefill(const void* mixed, const void* z, const float* ab, const v
   GdnRingUpdateKernel<<<dim3((a.conv_dim + 255) / 256, min(T, kRing)), 256, 0, s>>>(a.mixed, a.ring, T, a.conv_dim, pos0);
   e = FinishLaunch();
   if (e) return e;
-  if (D == 128) {
+  if (D == 128 && ws != nullptr && T >= 128) {
+    e = LaunchGdnChunked(q, k, v, eg, beta, state, o, ws, T, H, Hk, s);
+    if (e) return e;
+  } else if (D == 128) {
     const int smem = sizeof(ScanSmem<128>);
     cudaFuncSetAttribute(GdnScanKernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     GdnScanKernel<128><<<dim3(H, 4), 128, smem, s>>>(q, k, v, eg, beta, state, o, T, H, Hk);
@@ -252,7 +261,7 @@ int r4dxb_gdn_prefill(const void* mixed, const void* z, const float* ab, const v
     const int smem = sizeof(ScanSmem<64>);
     GdnScanKernel<64><<<dim3(H, 2), 128, smem, s>>>(q, k, v, eg, beta, state, o, T, H, Hk);
   }
-  e = FinishLaunch();
+  e = FinishLaunch();      // (a second check after the chunked path is harmless)
   if (e) return e;
   const long long rows = static_cast<long long>(T) * H;
   GdnGatedNormKernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, s>>>(

@@ -324,18 +324,25 @@ def dense_gemm_hadamard(W: torch.Tensor, svh: torch.Tensor, xh: torch.Tensor, tn
     return out
 
 
-register_cuda_sig("r4dxb_gdn_prefill", _I, [_P] * 16 + [_I, _I, _I, _I, _I, _F, _P])
+register_cuda_sig("r4dxb_gdn_prefill", _I, [_P] * 16 + [_I, _I, _I, _I, _I, _F, _P, _P])
+register_cuda_sig("r4dxb_gdn_chunk_ws_floats", ctypes.c_longlong, [_I, _I])
 register_cuda_sig("r4dxb_attn_prefill", _I, [_P] * 7 + [_I, _I, _I, _I, _I, _I, _P])
 
 
 def gdn_prefill(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, scratch: dict, out, T: int, H: int, Hk: int,
                 D: int, pos0: int, eps: float = 1e-6):
-    """scratch: dict with fp32 tensors q, k [T,Hk,D]; v, o [T,H,D]; eg, beta [T,H]."""
+    """scratch: dict with fp32 tensors q, k [T,Hk,D]; v, o [T,H,D]; eg, beta [T,H]; optional "ws" (see
+    gdn_chunk_ws_floats) switches D = 128 chunks of >= 128 tokens to the chunked tensor-core recurrence."""
     _check(_lib().r4dxb_gdn_prefill(_p(mixed), _p(z), _p(ab), _p(conv_w), _p(A_log), _p(dt_bias), _p(norm_w), _p(ring),
                                     _p(state), _p(scratch["q"]), _p(scratch["k"]), _p(scratch["v"]), _p(scratch["eg"]),
-                                    _p(scratch["beta"]), _p(scratch["o"]), _p(out), T, H, Hk, D, pos0, eps, _stream()),
+                                    _p(scratch["beta"]), _p(scratch["o"]), _p(out), T, H, Hk, D, pos0, eps,
+                                    _p(scratch.get("ws")), _stream()),
            "gdn_prefill")
     return out
+
+
+def gdn_chunk_ws_floats(T: int, H: int) -> int:
+    return int(_lib().r4dxb_gdn_chunk_ws_floats(T, H))
 
 
 def attn_prefill(q, qg, cache, block_table, k_descale, v_descale, out, T: int, Hq: int, Hkv: int, D: int, pos0: int,
