@@ -1,21 +1,27 @@
 // Causal GQA attention for a long chunk of query rows over the fp8 paged KV cache (prefill).
 //
 // One CTA = one KV head x 16 query tokens; warp j handles query head (kv_head * gqa + j), so the
-// K/V tiles a CTA dequantises (fp8 -> fp16, 64 keys at a time) are shared by all gqa heads.  Scores
+// K/V tiles a CTA dequantises (fp8 -> fp16, 32 keys at a time) are shared by all gqa heads.  Scores
 // and the PV product run on warp-level tensor-core MMAs (m16n8k16, fp16 in, fp32 accumulate) with an
 // online softmax in the log2 domain; the epilogue applies o * sigmoid(gate) and rounds to bf16.
+// The raw fp8 rows of the next key tile are fetched with cp.async while the current tile is in the
+// MMAs; shared memory and registers are sized so that two CTAs share an SM (12 warps hide the rest of
+// the latency); tiles entirely below the diagonal skip the mask, and the accumulator is only rescaled
+// when a row maximum actually moved.
 // The chunk's own K/V rows must already be in the cache (the pre-core kernel writes them first).
 //
 // This is the first-generation prefill kernel: it is not yet on tcgen05/TMEM (the GEMMs are).
 // The reference's counterpart is a query-tiled WMMA kernel with split-KV modes
 // (reference: third_party/libr4d/r4d_attn_prefill_h256_gqa6.hip:112).
+#include <cuda_pipeline.h>
+
 #include "common.cuh"
 
 namespace r4dxb {
 namespace {
 
 constexpr int kBlockTokens = 16;
-constexpr int kKeyTile = 64;
+constexpr int kKeyTile = 32;
 constexpr int kQTile = 16;
 
 __device__ __forceinline__ void LdMatrixX4(uint32_t (&r)[4], const void* p) {
@@ -54,14 +60,15 @@ struct PrefillArgs {
   int T, Hq, Hkv, pos0, gated;
 };
 
-template <int D>
-__global__ void __launch_bounds__(256) AttnPrefillKernel(PrefillArgs a) {
+template <int D, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, (WARPS <= 6 ? 2 : 1)) AttnPrefillKernel(PrefillArgs a) {
   constexpr int LD = D + 8;                 // padded row length (halves)
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int gqa = a.Hq / a.Hkv;
   __half* Qs = reinterpret_cast<__half*>(smem_raw);             // [gqa * 16][LD]
-  __half* Ks = Qs + gqa * kQTile * LD;                           // [64][LD]
-  __half* Vs = Ks + kKeyTile * LD;                               // [64][LD]
+  __half* Ks = Qs + gqa * kQTile * LD;                           // [32][LD]
+  __half* Vs = Ks + kKeyTile * LD;                               // [32][LD]
+  uint8_t* raw = reinterpret_cast<uint8_t*>(Vs + kKeyTile * LD);  // [2][32][D] fp8 rows of the next tile (K then V)
   const int qt = blockIdx.x, hkv = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nthreads = blockDim.x;
   const int t_base = qt * kQTile;
@@ -93,30 +100,45 @@ __global__ void __launch_bounds__(256) AttnPrefillKernel(PrefillArgs a) {
 
   const int last_pos = a.pos0 + min(a.T, t_base + kQTile) - 1;
   const int key_tiles = last_pos / kKeyTile + 1;
-  for (int kt = 0; kt < key_tiles; ++kt) {
-    __syncthreads();     // previous tile fully consumed (also orders the Q staging before first use)
-    // ---- dequantise K and V tiles: 4 cache blocks of 16 tokens ----
+  auto fetch = [&](int kt) {      // raw fp8 rows of key tile kt -> shared memory (16-byte pieces, zero past the end)
     for (int i = threadIdx.x; i < 2 * kKeyTile * (D / 16); i += nthreads) {
       const int which = i / (kKeyTile * (D / 16));                 // 0 = K, 1 = V
       const int rem = i % (kKeyTile * (D / 16));
       const int key = rem / (D / 16), c16 = (rem % (D / 16)) * 16;
       const int kp = kt * kKeyTile + key;
-      uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+      uint8_t* dst = raw + (which * kKeyTile + key) * D + c16;
       if (kp <= last_pos) {
         const int blk = a.block_table[kp / kBlockTokens];
         const uint8_t* src = a.cache + ((static_cast<size_t>(blk) * a.Hkv + hkv) * 2 + which) * kBlockTokens * D +
                              (kp % kBlockTokens) * D + c16;
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
-        lo.x = Fp8x2ToHalf2Bits(raw.x & 0xFFFF); lo.y = Fp8x2ToHalf2Bits(raw.x >> 16);
-        lo.z = Fp8x2ToHalf2Bits(raw.y & 0xFFFF); lo.w = Fp8x2ToHalf2Bits(raw.y >> 16);
-        hi.x = Fp8x2ToHalf2Bits(raw.z & 0xFFFF); hi.y = Fp8x2ToHalf2Bits(raw.z >> 16);
-        hi.z = Fp8x2ToHalf2Bits(raw.w & 0xFFFF); hi.w = Fp8x2ToHalf2Bits(raw.w >> 16);
+        __pipeline_memcpy_async(dst, src, 16);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
       }
+    }
+    __pipeline_commit();
+  };
+  fetch(0);
+  for (int kt = 0; kt < key_tiles; ++kt) {
+    __pipeline_wait_prior(0);
+    __syncthreads();     // raw tile landed; previous tile fully consumed (also orders the Q staging before first use)
+    // ---- dequantise the K and V tiles ----
+    for (int i = threadIdx.x; i < 2 * kKeyTile * (D / 16); i += nthreads) {
+      const int which = i / (kKeyTile * (D / 16));
+      const int rem = i % (kKeyTile * (D / 16));
+      const int key = rem / (D / 16), c16 = (rem % (D / 16)) * 16;
+      const uint4 rw = *reinterpret_cast<const uint4*>(raw + (which * kKeyTile + key) * D + c16);
+      uint4 lo, hi;
+      lo.x = Fp8x2ToHalf2Bits(rw.x & 0xFFFF); lo.y = Fp8x2ToHalf2Bits(rw.x >> 16);
+      lo.z = Fp8x2ToHalf2Bits(rw.y & 0xFFFF); lo.w = Fp8x2ToHalf2Bits(rw.y >> 16);
+      hi.x = Fp8x2ToHalf2Bits(rw.z & 0xFFFF); hi.y = Fp8x2ToHalf2Bits(rw.z >> 16);
+      hi.z = Fp8x2ToHalf2Bits(rw.w & 0xFFFF); hi.w = Fp8x2ToHalf2Bits(rw.w >> 16);
       __half* dst = (which == 0 ? Ks : Vs) + key * LD + c16;
       *reinterpret_cast<uint4*>(dst) = lo;
       *reinterpret_cast<uint4*>(dst + 8) = hi;
     }
     __syncthreads();
+    if (kt + 1 < key_tiles) fetch(kt + 1);      // overlaps with the MMAs below
     if (warp >= gqa) continue;
 
     // ---- S = Q K^T (16 x 64 per warp) ----
@@ -138,15 +160,24 @@ __global__ void __launch_bounds__(256) AttnPrefillKernel(PrefillArgs a) {
     }
     // ---- mask + online softmax (log2 domain) ----
     float mx0 = m0, mx1 = m1;
+    if (kt * kKeyTile + kKeyTile - 1 <= a.pos0 + t_base) {      // the whole tile is visible to every row of the CTA
 #pragma unroll
-    for (int n = 0; n < kKeyTile / 8; ++n) {
-      const int kp = kt * kKeyTile + n * 8 + tq * 2;
-      S[n][0] = (kp <= pos_r0) ? S[n][0] * sm_scale : -INFINITY;
-      S[n][1] = (kp + 1 <= pos_r0) ? S[n][1] * sm_scale : -INFINITY;
-      S[n][2] = (kp <= pos_r1) ? S[n][2] * sm_scale : -INFINITY;
-      S[n][3] = (kp + 1 <= pos_r1) ? S[n][3] * sm_scale : -INFINITY;
-      mx0 = fmaxf(mx0, fmaxf(S[n][0], S[n][1]));
-      mx1 = fmaxf(mx1, fmaxf(S[n][2], S[n][3]));
+      for (int n = 0; n < kKeyTile / 8; ++n) {
+        S[n][0] *= sm_scale; S[n][1] *= sm_scale; S[n][2] *= sm_scale; S[n][3] *= sm_scale;
+        mx0 = fmaxf(mx0, fmaxf(S[n][0], S[n][1]));
+        mx1 = fmaxf(mx1, fmaxf(S[n][2], S[n][3]));
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < kKeyTile / 8; ++n) {
+        const int kp = kt * kKeyTile + n * 8 + tq * 2;
+        S[n][0] = (kp <= pos_r0) ? S[n][0] * sm_scale : -INFINITY;
+        S[n][1] = (kp + 1 <= pos_r0) ? S[n][1] * sm_scale : -INFINITY;
+        S[n][2] = (kp <= pos_r1) ? S[n][2] * sm_scale : -INFINITY;
+        S[n][3] = (kp + 1 <= pos_r1) ? S[n][3] * sm_scale : -INFINITY;
+        mx0 = fmaxf(mx0, fmaxf(S[n][0], S[n][1]));
+        mx1 = fmaxf(mx1, fmaxf(S[n][2], S[n][3]));
+      }
     }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
@@ -170,8 +201,10 @@ __global__ void __launch_bounds__(256) AttnPrefillKernel(PrefillArgs a) {
     l1 = l1 * al1 + rs1;
     m0 = mx0;
     m1 = mx1;
+    if (!__all_sync(0xffffffffu, al0 == 1.f && al1 == 1.f)) {     // no row maximum moved: nothing to rescale
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) { O[n][0] *= al0; O[n][1] *= al0; O[n][2] *= al1; O[n][3] *= al1; }
+      for (int n = 0; n < D / 8; ++n) { O[n][0] *= al0; O[n][1] *= al0; O[n][2] *= al1; O[n][3] *= al1; }
+    }
     // ---- O += P V ----
 #pragma unroll
     for (int j = 0; j < kKeyTile / 16; ++j) {
@@ -238,23 +271,22 @@ extern "C" int r4dxb_attn_prefill(const void* q, const void* qg, const void* cac
   a.v_descale = v_descale;
   a.out = static_cast<__nv_bfloat16*>(out);
   a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.pos0 = pos0; a.gated = gated;
-  const int threads = max(2, gqa) * 32;     // at least two warps so the tile conversion is not single-warp
-  const size_t smem = static_cast<size_t>(gqa * kQTile + 2 * kKeyTile) * (D + 8) * 2;
+  const int warps = gqa <= 2 ? 2 : (gqa <= 4 ? 4 : (gqa <= 6 ? 6 : 8));   // idle warps still help the tile conversion
+  const size_t smem = static_cast<size_t>(gqa * kQTile + 2 * kKeyTile) * (D + 8) * 2 + 2 * kKeyTile * D;
   dim3 grid((T + kQTile - 1) / kQTile, Hkv);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  cudaError_t e = cudaSuccess;
-  if (D == 256) {
-    e = cudaFuncSetAttribute(AttnPrefillKernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  auto launch = [&](auto kern) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
-    AttnPrefillKernel<256><<<grid, threads, smem, s>>>(a);
-  } else if (D == 128) {
-    e = cudaFuncSetAttribute(AttnPrefillKernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    AttnPrefillKernel<128><<<grid, threads, smem, s>>>(a);
-  } else {
-    e = cudaFuncSetAttribute(AttnPrefillKernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return static_cast<int>(e);
-    AttnPrefillKernel<64><<<grid, threads, smem, s>>>(a);
-  }
+    kern<<<grid, warps * 32, smem, s>>>(a);
+    return 0;
+  };
+  int rc = R4DXB_BAD_ARG;
+#define R4DXB_ATTN_CASE(DD, WW) if (D == DD && warps == WW) rc = launch(AttnPrefillKernel<DD, WW>);
+  R4DXB_ATTN_CASE(256, 2) R4DXB_ATTN_CASE(256, 4) R4DXB_ATTN_CASE(256, 6) R4DXB_ATTN_CASE(256, 8)
+  R4DXB_ATTN_CASE(128, 2) R4DXB_ATTN_CASE(128, 4) R4DXB_ATTN_CASE(128, 6) R4DXB_ATTN_CASE(128, 8)
+  R4DXB_ATTN_CASE(64, 2) R4DXB_ATTN_CASE(64, 4) R4DXB_ATTN_CASE(64, 6) R4DXB_ATTN_CASE(64, 8)
+#undef R4DXB_ATTN_CASE
+  if (rc) return rc;
   return FinishLaunch();
 }
