@@ -24,6 +24,8 @@ class ModelConfig:
     num_key_value_heads: int = 0
     head_dim: int = 0
     attn_output_gate: bool = True
+    qk_norm: bool = True               # per-head RMSNorm of q and k before rope
+    norm_zero_centered: bool = True    # checkpoint norm weights are w with scale (1 + w); False: plain scale w
     intermediate_size: int = 0
     partial_rotary_factor: float = 0.25
     rope_theta: float = 1.0e7
@@ -78,6 +80,11 @@ class ModelConfig:
     @property
     def q_dim(self) -> int:
         return self.num_attention_heads * self.head_dim
+
+    @property
+    def q_proj_dim(self) -> int:
+        """Rows of the q projection: q|gate pairs per head when the output gate exists."""
+        return self.q_dim * (2 if self.attn_output_gate else 1)
 
     @property
     def kv_dim(self) -> int:
@@ -224,6 +231,22 @@ def qwen_hybrid_moe_config(layers: int = 48) -> ModelConfig:
         linear_key_head_dim=128, linear_value_head_dim=128, vocab_size=151936,
         num_experts=512, num_experts_per_tok=10, moe_intermediate_size=512,
         shared_expert_intermediate_size=512, mtp_num_hidden_layers=0)
+
+
+def llama_config(hidden: int = 4096, layers: int = 32, heads: int = 32, kv_heads: int = 8, head_dim: int = 128,
+                 intermediate: int = 14336, vocab: int = 128256, theta: float = 5.0e5) -> ModelConfig:
+    """Llama-style dense decoder: every layer full attention, no q/k norm, no output gate, full-width NeoX rope,
+    plain-scale RMSNorm (also the graph of the dense 33B family the reference serves in w8a16;
+    reference: docs/nanbeige.md:1-90)."""
+    return ModelConfig(
+        arch="llama", hidden_size=hidden, num_hidden_layers=layers, layer_types=["full_attention"] * layers,
+        num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, attn_output_gate=False, qk_norm=False,
+        norm_zero_centered=False, intermediate_size=intermediate, partial_rotary_factor=1.0, rope_theta=theta,
+        vocab_size=vocab, mtp_num_hidden_layers=0)
+
+
+def tiny_llama_config() -> ModelConfig:
+    return llama_config(hidden=256, layers=3, heads=4, kv_heads=2, head_dim=64, intermediate=512, vocab=4096, theta=1.0e4)
 
 
 def tiny_moe_config() -> ModelConfig:

@@ -20,7 +20,7 @@ from .hybrid import CONV_RING, KV_BLOCK, MAX_ROWS, HybridModel
 
 BF = torch.bfloat16
 register_cuda_sig("r4dxb_gdn_decode_batch", c_int, [c_ptr] * 16 + [c_int, c_int, c_int, c_int, c_f32, c_ptr])
-register_cuda_sig("r4dxb_attn_precore_batch", c_int, [c_ptr] * 10 + [c_int, c_ptr, c_ptr] + [c_int] * 5 + [c_f32, c_f32, c_ptr])
+register_cuda_sig("r4dxb_attn_precore_batch", c_int, [c_ptr] * 10 + [c_int, c_ptr, c_ptr] + [c_int] * 5 + [c_f32, c_f32, c_int, c_ptr])
 register_cuda_sig("r4dxb_attn_decode_batch", c_int, [c_ptr] * 5 + [c_int] + [c_ptr] * 6 + [c_int] * 6 + [c_ptr])
 
 
@@ -151,11 +151,12 @@ class BatchModel:
                 pa = p + "attn."
                 qg, kk, vv, q = cb["qg"][:B], cb["k"][:B], cb["v"][:B], cb["q"][:B]
                 lin(pa + "qg", h, qg); lin(pa + "k", h, kk); lin(pa + "v", h, vv)
-                rc = L.r4dxb_attn_precore_batch(qg.data_ptr(), kk.data_ptr(), vv.data_ptr(), w[pa + "q_norm"].data_ptr(),
-                                                w[pa + "k_norm"].data_ptr(), w[pa + "k_descale"].data_ptr(), w[pa + "v_descale"].data_ptr(),
+                qn, kn = w.get(pa + "q_norm"), w.get(pa + "k_norm")
+                rc = L.r4dxb_attn_precore_batch(qg.data_ptr(), kk.data_ptr(), vv.data_ptr(), qn.data_ptr() if qn is not None else None,
+                                                kn.data_ptr() if kn is not None else None, w[pa + "k_descale"].data_ptr(), w[pa + "v_descale"].data_ptr(),
                                                 positions.data_ptr(), self.alloc.tables.data_ptr(), row_slot.data_ptr(),
                                                 self.alloc.tables.shape[1], q.data_ptr(), self.kv[i].data_ptr(), B, Hq, Hkv, D,
-                                                cfg.rotary_dim, cfg.rope_theta, cfg.rms_norm_eps, st)
+                                                cfg.rotary_dim, cfg.rope_theta, cfg.rms_norm_eps, cfg.q_proj_dim // Hq, st)
                 assert rc == 0, rc
                 core = cb["core"][:B * cfg.q_dim].view(B, cfg.q_dim)
                 rc = L.r4dxb_attn_decode_batch(q.data_ptr(), qg.data_ptr(), self.kv[i].data_ptr(), self.alloc.tables.data_ptr(),

@@ -163,7 +163,7 @@ class HybridModel:
             next_ids=e(R, dtype=torch.int32), next_vals=e(R, dtype=torch.float32),
             x=e(R, H), h=e(R, H), mixed=e(R, cfg.conv_dim), z=e(R, cfg.value_dim),
             ab=e(R, 2 * Hv, dtype=torch.float32), core=e(R, max(cfg.value_dim, cfg.q_dim)),
-            qg=e(R, 2 * cfg.q_dim), k=e(R, cfg.kv_dim), v=e(R, cfg.kv_dim), q=e(R, cfg.q_dim),
+            qg=e(R, cfg.q_proj_dim), k=e(R, cfg.kv_dim), v=e(R, cfg.kv_dim), q=e(R, cfg.q_dim),
             gate_up=e(R, 2 * max(cfg.intermediate_size, 1)), act=e(R, max(cfg.intermediate_size, 1)),
             logits=e(R, V, dtype=torch.float32), argmax_scratch=e(2 * R * 256, dtype=torch.float32),
             part_acc=e(attn_splits * Hkv * G * D, dtype=torch.float32),
@@ -217,9 +217,9 @@ class HybridModel:
         self.lin[p + "qg"](x, out=b.qg[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
         self.lin[p + "k"](x, out=b.k[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
         self.lin[p + "v"](x, out=b.v[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
-        K.attn_precore(b.qg, b.k, b.v, w[p + "q_norm"], w[p + "k_norm"], w[p + "k_descale"], w[p + "v_descale"],
+        K.attn_precore(b.qg, b.k, b.v, w.get(p + "q_norm"), w.get(p + "k_norm"), w[p + "k_descale"], w[p + "v_descale"],
                        b.positions, self.block_table, b.q, self.kv[i], T, Hq, Hkv, D, cfg.rotary_dim,
-                       cfg.rope_theta, cfg.rms_norm_eps)
+                       cfg.rope_theta, cfg.rms_norm_eps, q_stride=cfg.q_proj_dim // Hq)
         core = b.core.view(-1)[:T * cfg.q_dim].view(T, cfg.q_dim)
         K.attn_decode(b.q, b.qg, self.kv[i], self.block_table, b.positions, w[p + "k_descale"], w[p + "v_descale"],
                       b.part_acc, b.part_ml, core, T, Hq, Hkv, D, self.attn_splits, cfg.attn_output_gate)
@@ -311,7 +311,7 @@ class HybridModel:
         f32 = torch.float32
         cb = dict(C=C, ids=e(C, dtype=torch.int32), positions=e(C, dtype=torch.int32), x=e(C, H), h=e(C, H),
                   xh=e(C * kmax, dtype=torch.float16), mixed=e(C, cfg.conv_dim), z=e(C, cfg.value_dim),
-                  ab=e(C, 2 * Hv, dtype=f32), core=e(C * max(cfg.value_dim, cfg.q_dim)), qg=e(C, 2 * cfg.q_dim),
+                  ab=e(C, 2 * Hv, dtype=f32), core=e(C * max(cfg.value_dim, cfg.q_dim)), qg=e(C, cfg.q_proj_dim),
                   k=e(C, cfg.kv_dim), v=e(C, cfg.kv_dim), q=e(C, cfg.q_dim), gate_up=e(C, 2 * cfg.intermediate_size),
                   gdn=dict(q=e(C, Hk, Dg, dtype=f32), k=e(C, Hk, Dg, dtype=f32), v=e(C, Hv, Dg, dtype=f32),
                            o=e(C, Hv, Dg, dtype=f32), eg=e(C, Hv, dtype=f32), beta=e(C, Hv, dtype=f32)))
@@ -354,9 +354,9 @@ class HybridModel:
                 self.lin[pa + "qg"].chunk(h, cb["xh"], qg)
                 self.lin[pa + "k"].chunk(h, cb["xh"], kk)
                 self.lin[pa + "v"].chunk(h, cb["xh"], vv)
-                K.attn_precore(qg, kk, vv, w[pa + "q_norm"], w[pa + "k_norm"], w[pa + "k_descale"], w[pa + "v_descale"],
+                K.attn_precore(qg, kk, vv, w.get(pa + "q_norm"), w.get(pa + "k_norm"), w[pa + "k_descale"], w[pa + "v_descale"],
                                cb["positions"], self.block_table, q, self.kv[i], T, Hq, Hkv, D, cfg.rotary_dim,
-                               cfg.rope_theta, cfg.rms_norm_eps)
+                               cfg.rope_theta, cfg.rms_norm_eps, q_stride=cfg.q_proj_dim // Hq)
                 core = cb["core"][:T * cfg.q_dim].view(T, cfg.q_dim)
                 K.attn_prefill(q, qg, self.kv[i], self.block_table, w[pa + "k_descale"], w[pa + "v_descale"], core, T,
                                Hq, Hkv, D, pos0, cfg.attn_output_gate)

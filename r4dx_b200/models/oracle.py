@@ -52,12 +52,13 @@ def init_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02, with_mtp: b
     w: Dict[str, torch.Tensor] = {"text.embed_tokens": n(cfg.vocab_size, H)}
 
     def attn_block(p: str):
-        w[p + "attn.qg"] = n(2 * cfg.q_dim, H)
+        w[p + "attn.qg"] = n(cfg.q_proj_dim, H)
         w[p + "attn.k"] = n(cfg.kv_dim, H)
         w[p + "attn.v"] = n(cfg.kv_dim, H)
         w[p + "attn.o"] = n(H, cfg.q_dim)
-        w[p + "attn.q_norm"] = n(cfg.head_dim)
-        w[p + "attn.k_norm"] = n(cfg.head_dim)
+        if cfg.qk_norm:
+            w[p + "attn.q_norm"] = n(cfg.head_dim)
+            w[p + "attn.k_norm"] = n(cfg.head_dim)
         w[p + "attn.k_descale"] = torch.ones(cfg.num_key_value_heads)
         w[p + "attn.v_descale"] = torch.ones(cfg.num_key_value_heads)
 
@@ -139,12 +140,13 @@ class OracleModel:
         cfg, w = self.cfg, self.w
         T = x.shape[0]
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-        qg = self._r(x @ w[p + "attn.qg"].T).view(T, Hq, 2 * D)
-        q, gate = qg[..., :D], qg[..., D:]
+        qg = self._r(x @ w[p + "attn.qg"].T).view(T, Hq, cfg.q_proj_dim // Hq)
+        q, gate = qg[..., :D], (qg[..., D:] if cfg.attn_output_gate else None)
         k = self._r(x @ w[p + "attn.k"].T).view(T, Hkv, D)
         v = self._r(x @ w[p + "attn.v"].T).view(T, Hkv, D)
-        q = R.rmsnorm_1pw(q, w[p + "attn.q_norm"], cfg.rms_norm_eps)
-        k = R.rmsnorm_1pw(k, w[p + "attn.k_norm"], cfg.rms_norm_eps)
+        if cfg.qk_norm:
+            q = R.rmsnorm_1pw(q, w[p + "attn.q_norm"], cfg.rms_norm_eps)
+            k = R.rmsnorm_1pw(k, w[p + "attn.k_norm"], cfg.rms_norm_eps)
         pos = torch.arange(st.pos, st.pos + T)
         q = self._r(R.rope_partial_neox(q, pos, cfg.rotary_dim, cfg.rope_theta))
         k = R.rope_partial_neox(k, pos, cfg.rotary_dim, cfg.rope_theta)
@@ -156,7 +158,7 @@ class OracleModel:
         if store:
             st.k[li], st.v[li] = K, V
         o = R.causal_gqa_attention(q, K, V, st.pos)
-        o = self._r(o * torch.sigmoid(gate))
+        o = self._r(o * torch.sigmoid(gate)) if gate is not None else self._r(o)
         return self._r(o.reshape(T, Hq * D) @ w[p + "attn.o"].T)
 
     def gdn(self, p: str, li, x: torch.Tensor, st: OracleState) -> torch.Tensor:

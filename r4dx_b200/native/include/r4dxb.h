@@ -41,6 +41,11 @@ int r4dxb_trellis_gemv(const void* words, const void* suh, const void* svh, cons
                        const void* residual, int T, int N, int K, int kb, int ksplit, void* stream);
 /* logits[T,N] = x . dequant(wq)^T, asymmetric 4-bit groups of 32/64/128 along K; out_f32 selects
  * fp32 or bf16 output */
+int r4dxb_vit_rope(void* qkv, const int* pos_hw, int T, int H, int D, float theta, void* stream);
+int r4dxb_vit_attention(const void* qkv, void* out, const int* cu_seqlens, int nseg, int T, int H, int D, void* stream);
+int r4dxb_w8a16_gemv(const void* wq, const void* ws, const void* x, void* y, int T, int N, int K, int group, int out_f32,
+                     void* stream);
+int r4dxb_rotate_rows(void* x, const void* signs, long long T, int H, int mode, void* stream);
 int r4dxb_w4a16_gemv(const void* wq, const void* wsz, const void* x, void* y, int T, int N, int K, int group,
                      int out_f32, void* stream);
 /* y[T,N] (fp32) = x[T,K] (bf16) . W[N,K]^T (bf16): small dense projections (gates, router) */
@@ -75,7 +80,7 @@ int r4dxb_gdn_decode(const void* mixed, const void* z, const float* ab, const vo
 int r4dxb_attn_precore(const void* qg, const void* k, const void* v, const void* q_norm, const void* k_norm,
                        const float* k_descale, const float* v_descale, const int* positions, const int* block_table,
                        void* q_out, void* cache, int T, int Hq, int Hkv, int D, int rotary_dim, float theta, float eps,
-                       void* stream);
+                       int q_stride, void* stream);   /* q_norm / k_norm may be null (no per-head norm); q_stride 0 = 2D */
 /* scratch: part_acc = splits*Hkv*G*D floats, part_ml = splits*Hkv*G*2 floats, G = Hq/Hkv*T */
 int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const int* block_table, const int* positions,
                       const float* k_descale, const float* v_descale, float* part_acc, float* part_ml, void* out,
@@ -98,7 +103,7 @@ int r4dxb_gdn_decode_batch(const void* mixed, const void* z, const float* ab, co
 int r4dxb_attn_precore_batch(const void* qg, const void* k, const void* v, const void* q_norm, const void* k_norm,
                              const float* k_descale, const float* v_descale, const int* positions, const int* block_tables,
                              const int* row_slot, int table_stride, void* q_out, void* cache, int B, int Hq, int Hkv, int D,
-                             int rotary_dim, float theta, float eps, void* stream);
+                             int rotary_dim, float theta, float eps, int q_stride, void* stream);
 int r4dxb_attn_decode_batch(const void* q, const void* qg, const void* cache, const int* block_tables, const int* row_slot,
                             int table_stride, const int* positions, const float* k_descale, const float* v_descale,
                             float* part_acc, float* part_ml, void* out, int B, int Hq, int Hkv, int D, int splits, int gated,

@@ -41,6 +41,7 @@ struct PrecoreArgs {
   __nv_bfloat16* q_out;        // [T, Hq, D]
   uint8_t* cache;
   int T, Hq, Hkv, D, rotary_dim;
+  int q_stride;                // elements between consecutive heads of qg (2D with the gate half, D without)
   float theta, eps;
   const int* row_slot;         // batched decode: row t belongs to sequence slot row_slot[t] (null: one sequence)
   int table_stride;            // ints between the block tables of consecutive slots
@@ -57,13 +58,15 @@ __global__ void PrecoreKernel(PrecoreArgs a) {
   else if (hh < a.Hq + a.Hkv) { kind = 1; head = hh - a.Hq; }
   else { kind = 2; head = hh - a.Hq - a.Hkv; }
   float x;
-  if (kind == 0) x = __bfloat162float(a.qg[(static_cast<size_t>(t) * a.Hq + head) * 2 * D + d]);
+  if (kind == 0) x = __bfloat162float(a.qg[(static_cast<size_t>(t) * a.Hq + head) * a.q_stride + d]);
   else if (kind == 1) x = __bfloat162float(a.k[(static_cast<size_t>(t) * a.Hkv + head) * D + d]);
   else x = __bfloat162float(a.v[(static_cast<size_t>(t) * a.Hkv + head) * D + d]);
   if (kind != 2) {
-    const float ss = BlockSum(x * x, red);
-    const float w = 1.0f + __bfloat162float((kind == 0 ? a.q_norm : a.k_norm)[d]);
-    x = x * rsqrtf(ss / D + a.eps) * w;
+    const __nv_bfloat16* nw = kind == 0 ? a.q_norm : a.k_norm;
+    if (nw != nullptr) {        // families without per-head q/k normalisation pass null
+      const float ss = BlockSum(x * x, red);
+      x = x * rsqrtf(ss / D + a.eps) * (1.0f + __bfloat162float(nw[d]));
+    }
     row[d] = x;
     __syncthreads();
     const int half = a.rotary_dim / 2;
@@ -298,7 +301,7 @@ extern "C" {
 int r4dxb_attn_precore(const void* qg, const void* k, const void* v, const void* q_norm, const void* k_norm,
                        const float* k_descale, const float* v_descale, const int* positions, const int* block_table,
                        void* q_out, void* cache, int T, int Hq, int Hkv, int D, int rotary_dim, float theta, float eps,
-                       void* stream) {
+                       int q_stride, void* stream) {
   if (T < 1 || D > 1024 || D % 32 || rotary_dim > D || rotary_dim % 2) return R4DXB_BAD_ARG;
   PrecoreArgs a;
   a.qg = static_cast<const __nv_bfloat16*>(qg);
@@ -314,6 +317,7 @@ int r4dxb_attn_precore(const void* qg, const void* k, const void* v, const void*
   a.cache = static_cast<uint8_t*>(cache);
   a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.rotary_dim = rotary_dim; a.theta = theta; a.eps = eps;
   a.row_slot = nullptr; a.table_stride = 0;
+  a.q_stride = q_stride > 0 ? q_stride : 2 * D;
   PrecoreKernel<<<dim3(Hq + 2 * Hkv, T), D, D * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
   return FinishLaunch();
 }
@@ -353,7 +357,7 @@ int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const in
 int r4dxb_attn_precore_batch(const void* qg, const void* k, const void* v, const void* q_norm, const void* k_norm,
                              const float* k_descale, const float* v_descale, const int* positions, const int* block_tables,
                              const int* row_slot, int table_stride, void* q_out, void* cache, int B, int Hq, int Hkv, int D,
-                             int rotary_dim, float theta, float eps, void* stream) {
+                             int rotary_dim, float theta, float eps, int q_stride, void* stream) {
   if (B < 1 || D > 1024 || D % 32 || rotary_dim > D || rotary_dim % 2) return R4DXB_BAD_ARG;
   PrecoreArgs a;
   a.qg = static_cast<const __nv_bfloat16*>(qg);
@@ -366,6 +370,7 @@ int r4dxb_attn_precore_batch(const void* qg, const void* k, const void* v, const
   a.cache = static_cast<uint8_t*>(cache);
   a.T = B; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.rotary_dim = rotary_dim; a.theta = theta; a.eps = eps;
   a.row_slot = row_slot; a.table_stride = table_stride;
+  a.q_stride = q_stride > 0 ? q_stride : 2 * D;
   PrecoreKernel<<<dim3(Hq + 2 * Hkv, B), D, D * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
   return FinishLaunch();
 }

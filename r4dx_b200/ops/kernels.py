@@ -35,7 +35,7 @@ register_cuda_sig("r4dxb_bf16_gemv", _I, [_P, _P, _P, _I, _I, _I, _P])
 register_cuda_sig("r4dxb_bf16_gemv_norm", _I, [_P, _P, _P, _F, _P, _I, _I, _I, _P])
 register_cuda_sig("r4dxb_argmax_rows", _I, [_P, _I, _I, _I, _I, _P, _P, _P, _P])
 register_cuda_sig("r4dxb_gdn_decode", _I, [_P] * 15 + [_I, _I, _I, _I, _F, _P])
-register_cuda_sig("r4dxb_attn_precore", _I, [_P] * 11 + [_I, _I, _I, _I, _I, _F, _F, _P])
+register_cuda_sig("r4dxb_attn_precore", _I, [_P] * 11 + [_I, _I, _I, _I, _I, _F, _F, _I, _P])
 register_cuda_sig("r4dxb_attn_decode", _I, [_P] * 10 + [_I, _I, _I, _I, _I, _I, _P])
 
 
@@ -232,10 +232,11 @@ def gdn_decode(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, log_u,
 
 
 def attn_precore(qg, k, v, q_norm, k_norm, k_descale, v_descale, positions, block_table, q_out, cache, T: int,
-                 Hq: int, Hkv: int, D: int, rotary_dim: int, theta: float, eps: float = 1e-6):
+                 Hq: int, Hkv: int, D: int, rotary_dim: int, theta: float, eps: float = 1e-6, q_stride: int = 0):
+    """q_norm / k_norm None: no per-head normalisation; q_stride 0: qg rows are q|gate pairs (2D per head)."""
     _check(_lib().r4dxb_attn_precore(_p(qg), _p(k), _p(v), _p(q_norm), _p(k_norm), _p(k_descale), _p(v_descale),
                                      _p(positions), _p(block_table), _p(q_out), _p(cache), T, Hq, Hkv, D, rotary_dim,
-                                     theta, eps, _stream()), "attn_precore")
+                                     theta, eps, q_stride, _stream()), "attn_precore")
     return q_out
 
 
@@ -339,6 +340,28 @@ def gdn_prefill(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, scrat
                                     _p(scratch.get("ws")), _stream()),
            "gdn_prefill")
     return out
+
+
+register_cuda_sig("r4dxb_w8a16_gemv", _I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_rotate_rows", _I, [_P, _P, ctypes.c_longlong, _I, _I, _P])
+
+
+def w8a16_gemv(w, x: torch.Tensor, out: Optional[torch.Tensor] = None, out_f32: bool = False) -> torch.Tensor:
+    """y[T, N] for a quant.w4a16.W8Weight on the device (T <= 8)."""
+    _req(x, BF, "x")
+    T = x.numel() // w.K
+    out = out if out is not None else torch.empty(T, w.N, dtype=torch.float32 if out_f32 else BF, device=x.device)
+    _check(_lib().r4dxb_w8a16_gemv(_p(w.wq), _p(w.ws), _p(x), _p(out), T, w.N, w.K, w.group,
+                                   1 if out.dtype == torch.float32 else 0, _stream()), "w8a16_gemv")
+    return out
+
+
+def rotate_rows(x: torch.Tensor, signs: Optional[torch.Tensor] = None, mode: int = 0) -> torch.Tensor:
+    """In-place 128-block Hadamard rotation of bf16 rows; mode 1 applies ``signs`` before, mode 2 after."""
+    _req(x, BF, "x")
+    H = x.shape[-1]
+    _check(_lib().r4dxb_rotate_rows(_p(x), _p(signs), x.numel() // H, H, mode, _stream()), "rotate_rows")
+    return x
 
 
 def gdn_chunk_ws_floats(T: int, H: int) -> int:

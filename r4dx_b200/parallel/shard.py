@@ -91,8 +91,9 @@ def shard_plan(cfg: ModelConfig, world: int, rank: int) -> Dict[str, tuple]:
            (2 * kd + rank * hv * Dv, 2 * kd + (rank + 1) * hv * Dv)]
     I = c.intermediate_size
     isz = I // world if I else 0
+    qs = (2 if c.attn_output_gate else 1) * D
     plan = {
-        "attn.qg": ("rows", [(q0 * 2 * D, (q0 + hq) * 2 * D)]),
+        "attn.qg": ("rows", [(q0 * qs, (q0 + hq) * qs)]),
         "attn.k": ("rows", [(kv0 * D, (kv0 + hkv) * D)]),
         "attn.v": ("rows", [(kv0 * D, (kv0 + hkv) * D)]),
         "attn.k_descale": ("rows", [(kv0, kv0 + hkv)]),

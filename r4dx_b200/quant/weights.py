@@ -83,7 +83,7 @@ def linear_shapes(cfg: ModelConfig, with_mtp: bool = False) -> Iterable[Tuple[st
     for i in range(cfg.num_hidden_layers):
         p = f"text.layers.{i}."
         if cfg.is_attention_layer(i):
-            yield p + "attn.qg", 2 * cfg.q_dim, H
+            yield p + "attn.qg", cfg.q_proj_dim, H
             yield p + "attn.k", cfg.kv_dim, H
             yield p + "attn.v", cfg.kv_dim, H
             yield p + "attn.o", H, cfg.q_dim
@@ -123,8 +123,9 @@ def synthetic_weight_set(cfg: ModelConfig, device="cuda", seed: int = 0, sigma: 
         w[p + "input_layernorm"] = n(H)
         w[p + "post_attention_layernorm"] = n(H)
         if cfg.is_attention_layer(i):
-            w[p + "attn.q_norm"] = n(cfg.head_dim)
-            w[p + "attn.k_norm"] = n(cfg.head_dim)
+            if cfg.qk_norm:
+                w[p + "attn.q_norm"] = n(cfg.head_dim)
+                w[p + "attn.k_norm"] = n(cfg.head_dim)
             w[p + "attn.k_descale"] = torch.full((cfg.num_key_value_heads,), 1.0 / 16, device=device)
             w[p + "attn.v_descale"] = torch.full((cfg.num_key_value_heads,), 1.0 / 16, device=device)
         else:

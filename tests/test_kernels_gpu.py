@@ -454,3 +454,39 @@ def test_topk_lse_summary_and_device_rep_penalty(K):
     row = torch.tensor([2.0, -2.0, 1.0, 0.5], device="cuda")
     K.repetition_penalty(row, torch.tensor([0, 1, 1, 0], dtype=torch.int32, device="cuda"), 2.0)
     assert row.cpu().tolist() == [1.0, -4.0, 1.0, 0.5]
+
+
+@pytest.mark.parametrize("T,N,Kd,group", [(1, 256, 512, 64), (5, 384, 1024, 128), (8, 96, 256, 32)])
+def test_w8a16_gemv(K, T, N, Kd, group):
+    from r4dx_b200.quant import w4a16
+    g = torch.Generator().manual_seed(N + T)
+    W = torch.randn(N, Kd, generator=g) * 0.05
+    w = w4a16.quantize_w8(W, group)
+    Wd = w4a16.dequantize_w8(w)
+    x = torch.randn(T, Kd, generator=g).to(BF)
+    ref = x.float() @ Wd.T
+    wd = w4a16.W8Weight(w.wq.cuda(), w.ws.cuda(), w.N, w.K, w.group)
+    got = K.w8a16_gemv(wd, x.cuda(), out_f32=True).cpu()
+    assert torch.allclose(got, ref, atol=2e-2 * ref.abs().max().item(), rtol=1e-2)
+    got_bf = K.w8a16_gemv(wd, x.cuda()).float().cpu()
+    assert torch.allclose(got_bf, ref, atol=3e-2 * ref.abs().max().item(), rtol=2e-2)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_rotate_rows_in_place(K, mode):
+    g = torch.Generator().manual_seed(mode)
+    x = torch.randn(7, 512, generator=g).to(BF)
+    s = (torch.randint(0, 2, (512,), generator=g).float() * 2 - 1).to(torch.float16)
+    xf = x.float()
+    if mode == 0:
+        ref = R.fwht(xf)
+    elif mode == 1:
+        ref = R.fwht(xf * s.float())
+    else:
+        ref = R.fwht(xf) * s.float()
+    y = x.cuda().clone()
+    K.rotate_rows(y, s.cuda() if mode else None, mode)
+    assert torch.allclose(y.float().cpu(), ref, atol=3e-2, rtol=2e-2)
+    if mode == 0:      # the normalised transform is its own inverse
+        K.rotate_rows(y, None, 0)
+        assert torch.allclose(y.float().cpu(), xf, atol=5e-2, rtol=3e-2)

@@ -73,3 +73,23 @@ def test_shard_views():
             assert s.intermediate_size % 128 == 0
     s8 = cfg.shard(8, 5)
     assert s8.num_key_value_heads == 1 and s8.kv_replicas == 2 and s8.kv_head_of_rank() == 2
+
+
+def test_llama_style_config_prefill_equals_stepwise():
+    """The dense family (no q/k norm, no gate, full rope) through the same oracle: chunk invariance."""
+    import torch
+    from r4dx_b200.config import tiny_llama_config
+    from r4dx_b200.models.oracle import OracleModel, OracleState, init_weights
+    cfg = tiny_llama_config()
+    cfg.validate()
+    w = init_weights(cfg, 3)
+    assert "text.layers.0.attn.q_norm" not in w and w["text.layers.0.attn.qg"].shape[0] == cfg.q_dim
+    m = OracleModel(cfg, w)
+    ids = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(0))
+    full, _ = m.forward(ids)
+    st = OracleState()
+    rows = []
+    for t in range(12):
+        lg, st = m.forward(ids[t:t + 1], st)
+        rows.append(lg)
+    assert torch.allclose(full, torch.cat(rows), atol=1e-4, rtol=1e-4)
