@@ -255,6 +255,8 @@ class HybridModel:
         if not skip_embed and self.layer_begin == 0:
             K.embed_gather(b.ids[:T], w["text.embed_tokens"], out=b.x[:T])
         for i in range(self.layer_begin, self.layer_end):
+            if i in self.capture_layers:
+                self._capture_rows(i, b.x[:T], T)
             # the two RMSNorms and the SwiGLU of a layer run inside the prologues of the linears
             if cfg.is_attention_layer(i):
                 self._attn_layer(i, T)
@@ -267,6 +269,20 @@ class HybridModel:
             K.argmax_rows(b.logits[:T], cfg.vocab_shard_begin, b.next_ids[:T], b.next_vals[:T], b.argmax_scratch)
             if self.comm is not None and self.comm.world > 1:
                 self.comm.merge_argmax(b.next_ids[:T], b.next_vals[:T])
+
+    # ---- feature capture for drafters that condition on intermediate residuals ----------------------
+    capture_layers: tuple = ()
+
+    def enable_capture(self, layers, max_rows: int) -> None:
+        """Keeps the residual stream entering each of ``layers`` for the rows of the latest call in
+        ``self.captured[j, :T]`` (reference: docs/dflash2.md:58 names the target layers a drafter reads)."""
+        self.capture_layers = tuple(layers)
+        self.captured = torch.zeros(len(self.capture_layers), max_rows, self.cfg.hidden_size, dtype=BF, device=self.device)
+
+    def _capture_rows(self, layer: int, x: torch.Tensor, T: int) -> None:
+        if T > self.captured.shape[1]:
+            self.captured = torch.zeros(len(self.capture_layers), T, self.cfg.hidden_size, dtype=BF, device=self.device)
+        self.captured[self.capture_layers.index(layer), :T].copy_(x)
 
     def _stage(self, ids: torch.Tensor, pos0: int) -> int:
         T = ids.numel()
@@ -347,6 +363,8 @@ class HybridModel:
             K.embed_gather(cb["ids"][:T], w["text.embed_tokens"], out=x)
         for i in range(self.layer_begin, self.layer_end):
             p = f"text.layers.{i}."
+            if i in self.capture_layers:
+                self._capture_rows(i, x, T)
             K.rmsnorm(x, w[p + "input_layernorm"], cfg.rms_norm_eps, out=h)
             if cfg.is_attention_layer(i):
                 pa = p + "attn."

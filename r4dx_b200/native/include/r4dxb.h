@@ -41,6 +41,11 @@ int r4dxb_trellis_gemv(const void* words, const void* suh, const void* svh, cons
                        const void* residual, int T, int N, int K, int kb, int ksplit, void* stream);
 /* logits[T,N] = x . dequant(wq)^T, asymmetric 4-bit groups of 32/64/128 along K; out_f32 selects
  * fp32 or bf16 output */
+int r4dxb_dflash_norm_rope(void* x, const void* w, const int* positions, int T, int heads, int D, float theta, float eps,
+                           void* stream);
+int r4dxb_dflash_conv(const void* h, const void* base, const void* dyn, void* out, int T, int H, void* stream);
+int r4dxb_dflash_attention(const void* q, const void* kb, const void* vb, const void* ring_k, const void* ring_v, void* out,
+                           int T, int Hq, int Hkv, int D, int window, int lo, int n, void* stream);
 int r4dxb_vit_rope(void* qkv, const int* pos_hw, int T, int H, int D, float theta, void* stream);
 int r4dxb_vit_attention(const void* qkv, void* out, const int* cu_seqlens, int nseg, int T, int H, int D, void* stream);
 int r4dxb_w8a16_gemv(const void* wq, const void* ws, const void* x, void* y, int T, int N, int K, int group, int out_f32,

@@ -162,6 +162,44 @@ struct Rng {
 
 }  // namespace r4dxb
 
+namespace r4dxb {
+
+// Selector-lattice walk of the block drafter (greedy chain).  For block position t = 1 .. rows-1 the candidates are
+// the row's top-`cands` tokens with unary scores (their logits); the pairwise term couples a candidate to the token
+// chosen at the previous position through two rank-R codebooks and the row's gate:
+//   score[b] = unary[t][b] + sum_r succ[cand[t][b]][r] * pred[prev][r] * gate[t][r]
+// The chain stops early when the chosen candidate's share of the row's softmax (over the candidates, after the
+// pairwise term) drops below p_min; a chain shorter than n_min is discarded (reference: docs/dflash2.md:162-186).
+int DflashSelect(const int32_t* cand, const float* unary, const float* gate, const float* succ, const float* pred, int rows,
+                 int cands, int rank, int64_t vocab, int32_t anchor, float p_min, int n_min, int32_t* out) {
+  int n = 0;
+  int32_t prev = anchor;
+  std::vector<double> score(cands);
+  for (int t = 1; t < rows; ++t) {
+    double best = -1e300, mx = -1e300;
+    int bi = 0;
+    for (int b = 0; b < cands; ++b) {
+      const int32_t id = cand[t * cands + b];
+      double pair = 0.0;
+      if (id >= 0 && id < vocab && prev >= 0 && prev < vocab)
+        for (int r = 0; r < rank; ++r)
+          pair += static_cast<double>(succ[static_cast<int64_t>(id) * rank + r]) * pred[static_cast<int64_t>(prev) * rank + r] *
+                  gate[t * rank + r];
+      score[b] = unary[t * cands + b] + pair;
+      if (score[b] > best || (score[b] == best && id < cand[t * cands + bi])) { best = score[b]; bi = b; }
+      mx = std::max(mx, score[b]);
+    }
+    double z = 0.0;
+    for (int b = 0; b < cands; ++b) z += std::exp(score[b] - mx);
+    if (std::exp(best - mx) / z < p_min) break;
+    out[n++] = cand[t * cands + bi];
+    prev = out[n - 1];
+  }
+  return n < n_min ? 0 : n;
+}
+
+}  // namespace r4dxb
+
 extern "C" {
 
 void* r4dxb_rng_new(uint64_t seed) { return new r4dxb::Rng(seed); }
@@ -182,6 +220,12 @@ int32_t r4dxb_sample_from_summary(const float* top_logits, const int32_t* top_id
 
 void r4dxb_repetition_penalty(float* logits, int64_t vocab, const int32_t* seen, int64_t n_seen, float penalty) {
   r4dxb::RepetitionPenalty(logits, vocab, seen, n_seen, penalty);
+}
+
+int r4dxb_dflash_select(const int32_t* cand, const float* unary, const float* gate, const float* succ, const float* pred,
+                        int rows, int cands, int rank, int64_t vocab, int32_t anchor, float p_min, int n_min, int32_t* out) {
+  if (rows < 1 || cands < 1 || rank < 0) return -1;
+  return r4dxb::DflashSelect(cand, unary, gate, succ, pred, rows, cands, rank, vocab, anchor, p_min, n_min, out);
 }
 
 }  // extern "C"
