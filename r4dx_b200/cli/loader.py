@@ -52,5 +52,9 @@ def load_text_model(args, device: Optional[str] = None):
     if args.mtp > 0 and any(k.startswith("mtp.") for k in weights):
         from ..models.mtp import MtpDrafter
         drafter = MtpDrafter(model, weights)
+    if getattr(args, "dflash", None):
+        from ..models.dflash import DflashDrafter, load_dflash
+        dcfg, dweights = load_dflash(args.dflash)
+        drafter = DflashDrafter(model, dcfg, dweights)
     tk, tpl = load_tokenizer(args.tokenizer_dir, gcfg.vocab_size)
     return LocalTextModel(model, model_id=model_id, global_config=gcfg, drafter=drafter), tk, tpl

@@ -13,8 +13,17 @@ def main(argv=None) -> int:
     from ..server.request_log import RequestLog
     from .loader import load_text_model
     tm, tk, tpl = load_text_model(args)
-    eng = Engine(tm, tk, max_queue=args.max_queue, prompt_checkpoint=(args.prompt_checkpoint == "on"),
-                 request_log=RequestLog(args.request_log, args.request_log_tokens))
+    if args.batch > 1:
+        # N sequence slots over the same weights; the single-sequence model object only lends its weights
+        from ..models.batch import BatchModel
+        from ..server.batch_executor import BatchEngine
+        m = tm.m
+        bm = BatchModel(m.cfg, m.w, slots=args.batch, slot_ctx=args.batch_ctx, device=str(m.device), comm=m.comm)
+        eng = BatchEngine(bm, tk, max_queue=max(args.max_queue, 2 * args.batch),
+                          request_log=RequestLog(args.request_log, args.request_log_tokens))
+    else:
+        eng = Engine(tm, tk, max_queue=args.max_queue, prompt_checkpoint=(args.prompt_checkpoint == "on"),
+                     request_log=RequestLog(args.request_log, args.request_log_tokens))
     defaults = {"temperature": args.default_temperature, "top_k": args.default_top_k, "top_p": args.default_top_p,
                 "min_p": args.default_min_p, "repetition_penalty": args.default_repetition_penalty}
     srv = ApiServer(eng, tk, tpl, tm.model_id, host=args.host, port=args.port, max_tokens_default=args.max_tokens_default,

@@ -175,6 +175,21 @@ class DflashOracle:
         return xo @ self.lm_head.T, xo
 
 
+def save_dflash(path: str, c: DflashConfig, w: Dict[str, torch.Tensor]) -> None:
+    """fp32/bf16 source weights + config in one torch file (quantized at load)."""
+    import dataclasses
+    torch.save({"config": dataclasses.asdict(c), "weights": w}, path)
+
+
+def load_dflash(path: str):
+    d = torch.load(path, map_location="cpu", weights_only=False)
+    cfgd = dict(d["config"])
+    cfgd["target_layers"] = tuple(cfgd["target_layers"])
+    c = DflashConfig(**cfgd)
+    q, _ = quantize_dflash_weights(c, d["weights"])
+    return c, q
+
+
 def select_chain(c: DflashConfig, cand: torch.Tensor, unary: torch.Tensor, gate: torch.Tensor, succ: torch.Tensor,
                  pred: torch.Tensor, anchor: int) -> List[int]:
     """Host selector walk (C++): cand int32 [B, cands], unary / gate fp32, codebooks fp32 [vocab, rank]."""
@@ -278,7 +293,27 @@ class DflashDrafter:
         main.lin["lm_head"](xo, out=logits)
         return logits, xo
 
-    def draft(self, anchor: int) -> List[int]:
+    # ---- drafter protocol used by runtime.text_model.LocalTextModel --------------------------------------
+    def prefill_hook(self, ids: torch.Tensor):
+        state = {"s": self.frontier}
+
+        def hook(start: int, T: int, _hidden: torch.Tensor) -> None:
+            self.inject(self.main.captured, state["s"], T)
+            state["s"] += T
+
+        return hook
+
+    def after_prefill(self, ids: torch.Tensor, tok: int) -> None:
+        pass
+
+    def after_verify(self, anchor: int, drafts: List[int], emitted: List[int]) -> None:
+        self.accepted += len(emitted) - 1
+        self.inject(self.main.captured, self.frontier, len(emitted))
+
+    def acceptance(self) -> float:
+        return self.accepted / max(1, self.rounds)
+
+    def draft(self, anchor: int, k: int = 7) -> List[int]:
         c = self.c
         logits, xo = self.draft_rows(anchor)
         vals, ids, _ = K.topk_lse(logits, 64)
@@ -288,6 +323,7 @@ class DflashDrafter:
         unary, cand, g = packed[:nb].view(c.block, c.cands), packed[nb:2 * nb].view(c.block, c.cands).to(torch.int32), packed[2 * nb:].view(c.block, -1)
         self.rounds += 1
         out = select_chain(c, cand, unary, g.contiguous(), self.succ, self.pred, anchor)
+        out = out[:min(k, 7)]
         self.proposed += len(out)
         return out
 
@@ -296,19 +332,11 @@ class DflashDrafter:
         main = self.main
         main.reset()
         self.reset()
-        state = {"s": 0}
-
-        def hook(start, T, _hidden):
-            self.inject(main.captured, state["s"], T)
-            state["s"] += T
-
-        tok = main.prefill(prompt, hook=hook)
+        tok = main.prefill(prompt, hook=self.prefill_hook(prompt))
         out = [tok]
         while len(out) < n_tokens:
-            drafts = self.draft(out[-1])[: 7]
-            pos0 = main.pos
+            drafts = self.draft(out[-1])
             emitted = main.verify_window(out[-1], drafts)
-            self.accepted += len(emitted) - 1
-            self.inject(main.captured, pos0, len(emitted))
+            self.after_verify(out[-1], drafts, emitted)
             out += emitted
         return out[:n_tokens]

@@ -151,3 +151,39 @@ def test_queue_full_gives_429():
     for j in jobs:
         j.cancelled = True
     eng.shutdown()
+
+
+def test_batch_engine_runs_requests_together_and_independently():
+    import threading
+    from r4dx_b200.runtime.tokenizer import ByteTokenizer
+    from r4dx_b200.server.batch_executor import BatchEngine, FakeBatchBackend
+    from r4dx_b200.server.engine import GenRequest, QueueFull
+    tk = ByteTokenizer()
+    be = FakeBatchBackend(slots=3, vocab=200)
+    eng = BatchEngine(be, tk, max_queue=4, gather_ms=20.0)
+    prompts = [[5, 6, 7], [9, 9], [1, 2, 3, 4], [8]]
+    results = [None] * 4
+
+    def run(i):
+        results[i] = eng.generate(GenRequest(prompt_ids=prompts[i], max_tokens=6 + i), timeout=10)
+
+    th = [threading.Thread(target=run, args=(i,)) for i in range(4)]
+    for t in th:
+        t.start()
+    for t in th:
+        t.join()
+    # every stream equals the single-sequence continuation of its own prompt
+    for i, r in enumerate(results):
+        assert r.error is None and r.finish_reason == "length" and len(r.token_ids) == 6 + i
+        h = list(prompts[i])
+        for tok in r.token_ids:
+            assert tok == FakeBatchBackend._next(h, 200)
+            h.append(tok)
+    assert max(be.batch_sizes) >= 2            # requests really shared decode steps
+    assert eng.stats["requests"] == 4 and eng.stats["errors"] == 0
+    # a prompt that cannot fit the slot is an error for that request only
+    r = eng.generate(GenRequest(prompt_ids=[1] * 5000, max_tokens=4), timeout=10)
+    assert r.finish_reason == "error" and "slot context" in r.error
+    r = eng.generate(GenRequest(prompt_ids=[3, 3], max_tokens=2), timeout=10)
+    assert r.error is None and len(r.token_ids) == 2
+    eng.shutdown()
