@@ -82,8 +82,19 @@ class BatchModel:
         if cfg.is_moe:
             from .moe import MoeBlock
             er = getattr(comm, "expert_range", None) if comm is not None else None
-            self.moe = {i: MoeBlock(cfg, weights, i, self.device, max(slots, 8), *(er or (0, cfg.num_experts))) for i in range(cfg.num_hidden_layers)}
+            self.moe = {i: MoeBlock(cfg, weights, i, self.device, max(slots, 8), *(er or (0, cfg.num_experts)),
+                                    share_from=b.moe.get(i)) for i in range(cfg.num_hidden_layers)}
         self._L = None
+
+    def _dense_head(self) -> torch.Tensor:
+        if getattr(self, "_head_bf16", None) is None:
+            from ..quant import w4a16
+            w = self.base.lin["lm_head"].w
+            if isinstance(w, torch.Tensor):
+                self._head_bf16 = w.to(BF)
+            else:
+                self._head_bf16 = w4a16.dequantize(w).to(self.device, BF)
+        return self._head_bf16
 
     # ---- slot lifecycle -------------------------------------------------------------------------------
     def _bind(self, slot: int) -> None:
@@ -111,6 +122,15 @@ class BatchModel:
         self.active[slot] = True
         return tok
 
+    def position_slot(self, slot: int, pos: int) -> None:
+        """Benchmark aid: marks ``slot`` active at position ``pos`` without a prefill (its KV blocks hold zeros, which cost
+        the same to read; the recurrent state starts at zero)."""
+        self.release_slot(slot)
+        self.alloc.ensure(slot, pos + 1)
+        self.pos[slot] = pos
+        self.n_replay[slot] = 0
+        self.active[slot] = True
+
     def release_slot(self, slot: int) -> None:
         self.alloc.release(slot)
         self.active[slot] = False
@@ -133,7 +153,7 @@ class BatchModel:
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
         G = Hq // max(1, Hkv)
-        splits = max(1, min(16, 148 // max(1, Hkv * B)))
+        splits = max(1, min(16, 592 // max(1, Hkv * B)))        # about four CTAs per SM
         part_acc = torch.empty(B * splits * Hkv * G * D, dtype=torch.float32, device=dev)
         part_ml = torch.empty(B * splits * Hkv * G * 2, dtype=torch.float32, device=dev)
 
@@ -194,10 +214,12 @@ class BatchModel:
         self.n_replay[row_slot.long()] = 1
         K.rmsnorm(x, w["text.final_norm"], cfg.rms_norm_eps, out=h)
         V = cfg.vocab_shard_size
-        logits = torch.empty(B, V, dtype=torch.float32, device=dev)
-        for s0 in range(0, B, MAX_ROWS):
-            e0 = min(B, s0 + MAX_ROWS)
-            b.lin["lm_head"](h[s0:e0], out=logits[s0:e0])
+        if B > MAX_ROWS:
+            # many rows: the head is a plain dense product (library GEMM) over a bf16 copy of its weights
+            logits = torch.matmul(h, self._dense_head().t()).float()
+        else:
+            logits = torch.empty(B, V, dtype=torch.float32, device=dev)
+            b.lin["lm_head"](h, out=logits)
         nxt, _ = K.argmax_rows(logits, cfg.vocab_shard_begin)
         for s in slots:
             self.pos[s] += 1

@@ -49,13 +49,17 @@ class MoeBlock:
     """One layer's routed + shared experts.  ``e_begin/e_count``: the expert slice this rank holds."""
 
     def __init__(self, cfg: ModelConfig, weights: Dict[str, object], layer: int, device, max_rows: int, e_begin: int = 0,
-                 e_count: Optional[int] = None, tmax: int = 2):
+                 e_count: Optional[int] = None, tmax: int = 2, share_from: Optional["MoeBlock"] = None, cap: int = 16):
         self.cfg = cfg
         p = f"text.layers.{layer}.moe."
         self.e_begin = e_begin
         self.e_count = e_count if e_count is not None else cfg.num_experts
-        self.gate_up = ExpertStack.from_list([weights[p + f"experts.{e}.gate_up"] for e in range(e_begin, e_begin + self.e_count)])
-        self.down = ExpertStack.from_list([weights[p + f"experts.{e}.down"] for e in range(e_begin, e_begin + self.e_count)])
+        if share_from is not None:      # another block object of the same layer already stacked the experts
+            self.gate_up, self.down = share_from.gate_up, share_from.down
+        else:
+            self.gate_up = ExpertStack.from_list([weights[p + f"experts.{e}.gate_up"] for e in range(e_begin, e_begin + self.e_count)])
+            self.down = ExpertStack.from_list([weights[p + f"experts.{e}.down"] for e in range(e_begin, e_begin + self.e_count)])
+        self.cap = cap                   # rows one expert can take per call when more than `cap` rows are in flight
         self.router = weights[p + "router"]
         self.shared_gate = weights[p + "shared_gate"]
         self.shared_gu: TrellisWeight = weights[p + "shared.gate_up"]
@@ -85,14 +89,24 @@ class MoeBlock:
 
     def experts(self, h: torch.Tensor, T: int) -> None:
         """y_pairs[pair] = down_e(silu(gate_e h) * up_e h) for every pair routed to a local expert."""
-        n_pass = (T + self.tmax - 1) // self.tmax
+        # few rows in flight: 2-row passes (an expert rarely sees more than one); many: 8-row passes, two of them
+        tmax = self.tmax if T <= 4 else 8
+        n_pass = (min(T, self.cap) + tmax - 1) // tmax
         g, d = self.gate_up, self.down
-        K.trellis_gemv_grouped(g.words, g.suh, g.svh, h, self.gu_pairs, self.offsets, self.perm, self.k, n_pass, self.tmax,
+        K.trellis_gemv_grouped(g.words, g.suh, g.svh, h, self.gu_pairs, self.offsets, self.perm, self.k, n_pass, tmax,
                                K.PRO_NONE, g.E, g.N, g.K, g.kb, self.ks_gu)
-        K.trellis_gemv_grouped(d.words, d.suh, d.svh, self.gu_pairs, self.y_pairs, self.offsets, self.perm, 1, n_pass, self.tmax,
+        K.trellis_gemv_grouped(d.words, d.suh, d.svh, self.gu_pairs, self.y_pairs, self.offsets, self.perm, 1, n_pass, tmax,
                                K.PRO_SILU_MUL, d.E, d.N, d.K, d.kb, self.ks_dn)
 
     def shared(self, h: torch.Tensor, T: int) -> None:
+        if T > 16:
+            # many rows: the tensor-core path (input transform + GEMM), SwiGLU fused into the second transform
+            xh = K.trellis_input(h[:T], self.shared_gu.suh)
+            K.trellis_gemm(self.shared_gu, xh, out=self.sh_gu[:T])
+            xh2 = K.trellis_input(self.sh_gu[:T], self.shared_down.suh, fused_silu_mul=True)
+            K.trellis_gemm(self.shared_down, xh2, out=self.sh_out[:T])
+            K.bf16_gemv(self.shared_gate, h, out=self.sh_gate[:T])
+            return
         for s in range(0, T, 8):
             e = min(T, s + 8)
             K.trellis_gemv(self.shared_gu, h[s:e], out=self.sh_gu[s:e])
@@ -105,6 +119,11 @@ class MoeBlock:
         self.experts(h, T)
         self.shared(h, T)
         K.moe_combine(self.y_pairs, self.ids, self.wts, self.sh_out, self.sh_gate, x, x, T, self.cfg.hidden_size, self.k)
+
+    def max_rows_of_an_expert(self) -> int:
+        """Largest per-expert row count of the latest plan (one device read; for overflow checks of ``cap``)."""
+        o = self.offsets.cpu()
+        return int((o[1:] - o[:-1]).max().item())
 
     @property
     def nbytes(self) -> int:

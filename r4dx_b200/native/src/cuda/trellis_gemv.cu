@@ -272,6 +272,9 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
         const int kk = it * 128 + kt * 16 + khalf;
 #pragma unroll
         for (int t = 0; t < TMAX; ++t) {
+          // grouped launches are compiled for the widest expert but most experts hold one or two rows:
+          // skip the rows this CTA does not have (T is uniform over the CTA)
+          if (kGrouped && TMAX > 2 && t >= T) break;
           const uint4 xv = *reinterpret_cast<const uint4*>(xs + static_cast<size_t>(t) * kslice + kk);
           __half2 h = __hfma2(w[0], *reinterpret_cast<const __half2*>(&xv.x), hacc[t]);
           h = __hfma2(w[1], *reinterpret_cast<const __half2*>(&xv.y), h);

@@ -141,7 +141,10 @@ __global__ void __launch_bounds__(256) Bf16GemvTiled(const __nv_bfloat16* __rest
   }
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int n = warp; n < N; n += 8) {
+  // grid.y splits the weight rows so that a few activation tiles still fill the machine
+  const int rows_per_cta = (N + gridDim.y - 1) / gridDim.y;
+  const int n_begin = blockIdx.y * rows_per_cta, n_end = min(N, n_begin + rows_per_cta);
+  for (int n = n_begin + warp; n < n_end; n += 8) {
     float acc[8];
 #pragma unroll
     for (int tt = 0; tt < 8; ++tt) acc[tt] = 0.f;
@@ -274,7 +277,9 @@ int r4dxb_bf16_gemv(const void* W, const void* x, float* y, int T, int N, int K,
     const int smem = K * 16;
     cudaError_t e = cudaFuncSetAttribute(Bf16GemvTiled, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
-    Bf16GemvTiled<<<(T + 7) / 8, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+    const int tiles = (T + 7) / 8;
+    const int ysplit = max(1, min((N + 7) / 8, 296 / tiles));
+    Bf16GemvTiled<<<dim3(tiles, ysplit), 256, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(W), static_cast<const __nv_bfloat16*>(x), y, T, N, K);
     return FinishLaunch();
   }

@@ -47,7 +47,7 @@ class EpComm:
     mode = "fused"
 
     def __init__(self, world: int, rank: int, device, cfg, max_rows: int, spin_limit: int = 1 << 22,
-                 max_rows_per_expert: Optional[int] = None, tmax: int = 2):
+                 max_rows_per_expert: Optional[int] = None, tmax: Optional[int] = None):
         self.world, self.rank, self.device = world, rank, torch.device(device)
         self.cfg = cfg
         self.k = cfg.num_experts_per_tok
@@ -57,8 +57,8 @@ class EpComm:
         self.e_per = cfg.num_experts // world
         self.expert_range = (rank * self.e_per, self.e_per)
         self.spin_limit = spin_limit
-        self.tmax = tmax
         self.cap = max_rows_per_expert or min(world * max_rows, 16)
+        self.tmax = tmax or (2 if self.cap <= 4 else 8)       # rows of one expert per grouped launch
         W, P, H = world, self.P, self.H
         a = lambda n: (n + 255) // 256 * 256
         self.off_meta = 0

@@ -1,0 +1,79 @@
+"""Batched decode throughput of the hybrid MoE geometry (hidden 2048, 512 experts top-10 + shared expert):
+``--batch`` concurrent sequences, attention and the recurrent layers data-parallel (each rank owns batch / world
+sequences), routed experts expert-parallel with the in-kernel all-to-all.  Device-timed, max over ranks.
+
+    python -m r4dx_b200.utils.bench_moe_decode --batch 64 --ctx 2048                       # one GPU
+    python -m torch.distributed.run --nproc-per-node 8 -m r4dx_b200.utils.bench_moe_decode --batch 64
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    a = ap.parse_args()
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    from r4dx_b200.config import qwen_hybrid_moe_config
+    from r4dx_b200.models.batch import BatchModel
+    from r4dx_b200.parallel.ep import EpComm, NcclEpBaseline
+    from r4dx_b200.quant.weights import moe_kb_rule, synthetic_weight_set
+    cfg = qwen_hybrid_moe_config(a.layers)
+    e_per = cfg.num_experts // world
+    w = synthetic_weight_set(cfg, device=dev, seed=0, kb_rule=moe_kb_rule, expert_range=(rank * e_per, e_per))
+    B = a.batch // world
+    comm = None
+    if world > 1:
+        comm = (EpComm if a.comm == "fused" else NcclEpBaseline)(world, rank, dev, cfg, max_rows=max(B, 8))
+    bm = BatchModel(cfg, w, slots=B, slot_ctx=a.ctx + a.steps + a.warmup + 16, device=dev, comm=comm)
+    slots = list(range(B))
+    for s in slots:
+        bm.position_slot(s, a.ctx)
+    g = torch.Generator().manual_seed(rank)
+    toks = torch.randint(0, cfg.vocab_size, (B,), generator=g).tolist()
+    for _ in range(a.warmup):
+        toks = bm.decode_batch(slots, toks)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        toks = bm.decode_batch(slots, toks)
+    e1.record()
+    torch.cuda.synchronize()
+    if comm is not None:
+        comm.check_healthy()
+    worst = max(b.max_rows_of_an_expert() for b in bm.moe.values()) if world == 1 else 0
+    t = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms = float(t[0])
+        print(json.dumps({"metric": "batched decode tok/s, hybrid MoE geometry", "batch": a.batch, "world": world, "comm": a.comm,
+                          "ctx": a.ctx, "layers": a.layers, "ms_per_step": ms, "tok_s": a.batch / (ms / 1e3),
+                          "max_rows_of_an_expert_last_step": worst}))
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
+
+
+if __name__ == "__main__":
+    main()
