@@ -36,6 +36,7 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--ttft-lens", default="32768,131072", help="extra prompt lengths whose cold TTFT is measured after the decode run")
     ap.add_argument("--no-pdl", action="store_true", help="A/B: disable programmatic dependent launch")
+    ap.add_argument("--no-overlap", action="store_true", help="A/B: run sibling projections back to back instead of on a side stream")
     return ap.parse_args()
 
 
@@ -133,6 +134,8 @@ def main():
     total = max([args.prompt_len + args.warmup * 2 + args.steps * 2 + 64] + [n + 64 for n in extra_lens])
     w = synthetic_weight_set(cfg, device=dev, seed=0)
     model = HybridModel(cfg, w, max_ctx=total, device=dev, comm=comm)
+    if args.no_overlap:
+        model.overlap_siblings = False
 
     def barrier():
         if world > 1:

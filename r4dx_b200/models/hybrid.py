@@ -69,6 +69,14 @@ class Linear:
         return w.nbytes if hasattr(w, "nbytes") and not isinstance(w, torch.Tensor) else w.numel() * w.element_size()
 
 
+class _NullCtx:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *a):
+        return False
+
+
 @dataclass
 class StepBuffers:
     """Workspaces for one call of up to MAX_ROWS rows (allocated once; graph-safe)."""
@@ -194,15 +202,35 @@ class HybridModel:
         self.pos = 0
         self.pending_rows = 0
 
+    # ---- sibling overlap ----------------------------------------------------------------------------
+    overlap_siblings = True
+
+    def _fork(self):
+        if not self.overlap_siblings:
+            return None
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=self.device)
+        self._side.wait_stream(torch.cuda.current_stream())
+        return self._side
+
+    def _join(self, side) -> None:
+        if side is not None:
+            torch.cuda.current_stream().wait_stream(side)
+
     # ---- layers ---------------------------------------------------------------------------------
     def _gdn_layer(self, i: int, T: int) -> None:
         cfg, b, w = self.cfg, self.buf, self.w
         p = f"text.layers.{i}.gdn."
         Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
         x, nw, eps = b.x[:T], w[f"text.layers.{i}.input_layernorm"], cfg.rms_norm_eps
+        # the three projections read the same rows and write different buffers: the two small ones run on a side
+        # stream (a parallel branch of the captured graph) while the large one fills the machine
+        side = self._fork()
         self.lin[p + "in_proj_qkv"](x, out=b.mixed[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
-        self.lin[p + "in_proj_z"](x, out=b.z[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
-        K.bf16_gemv_norm(self.ab_w[i], x, nw, eps, b.ab[:T])
+        with torch.cuda.stream(side) if side is not None else _NullCtx():
+            self.lin[p + "in_proj_z"](x, out=b.z[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+            K.bf16_gemv_norm(self.ab_w[i], x, nw, eps, b.ab[:T])
+        self._join(side)
         K.gdn_decode(b.mixed, b.z, b.ab, w[p + "conv1d_weight"], w[p + "A_log"], w[p + "dt_bias"], w[p + "norm_weight"],
                      self.ring[i], self.gdn_state[i], self.log_u[i], self.log_k[i], self.log_eg[i], b.positions,
                      b.n_replay, b.core, T, Hv, Hk, Dg, cfg.rms_norm_eps)
@@ -214,9 +242,12 @@ class HybridModel:
         p = f"text.layers.{i}.attn."
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         x, nw, eps = b.x[:T], w[f"text.layers.{i}.input_layernorm"], cfg.rms_norm_eps
+        side = self._fork()
         self.lin[p + "qg"](x, out=b.qg[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
-        self.lin[p + "k"](x, out=b.k[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
-        self.lin[p + "v"](x, out=b.v[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+        with torch.cuda.stream(side) if side is not None else _NullCtx():
+            self.lin[p + "k"](x, out=b.k[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+            self.lin[p + "v"](x, out=b.v[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+        self._join(side)
         K.attn_precore(b.qg, b.k, b.v, w.get(p + "q_norm"), w.get(p + "k_norm"), w[p + "k_descale"], w[p + "v_descale"],
                        b.positions, self.block_table, b.q, self.kv[i], T, Hq, Hkv, D, cfg.rotary_dim,
                        cfg.rope_theta, cfg.rms_norm_eps, q_stride=cfg.q_proj_dim // Hq)
