@@ -356,7 +356,9 @@ class HybridModel:
         kmax = max(H, cfg.value_dim, cfg.q_dim, cfg.intermediate_size)
         e = lambda *s, dtype=BF: torch.empty(*s, dtype=dtype, device=dev)
         f32 = torch.float32
-        cb = dict(C=C, ids=e(C, dtype=torch.int32), positions=e(C, dtype=torch.int32), x=e(C, H), h=e(C, H),
+        # under tensor parallelism the residual stream of a chunk may live in peer-mapped memory (owners push rows into it)
+        x_buf = self.comm.alloc_chunk_x(C, H) if hasattr(self.comm, "alloc_chunk_x") else e(C, H)
+        cb = dict(C=C, ids=e(C, dtype=torch.int32), positions=e(C, dtype=torch.int32), x=x_buf, h=e(C, H),
                   xh=e(C * kmax, dtype=torch.float16), mixed=e(C, cfg.conv_dim), z=e(C, cfg.value_dim),
                   ab=e(C, 2 * Hv, dtype=f32), core=e(C * max(cfg.value_dim, cfg.q_dim)), qg=e(C, cfg.q_proj_dim),
                   k=e(C, cfg.kv_dim), v=e(C, cfg.kv_dim), q=e(C, cfg.q_dim), gate_up=e(C, 2 * cfg.intermediate_size),

@@ -33,7 +33,7 @@ CXX = os.environ.get("CXX", shutil.which("g++") or "g++")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-lineinfo", "-O3", "-std=c++17",
+    "-lineinfo", "-O3", "-std=c++17", "-Xptxas", "-v",
     "--expt-relaxed-constexpr", "--expt-extended-lambda",
     "-Xcompiler", "-fPIC",
     "-I", str(INCLUDE), "-I", str(SRC_CUDA),
@@ -65,13 +65,17 @@ def _compile_one(src: Path, cuda: bool, verbose: bool, force: bool):
         return obj, ""
     for old in OBJ.glob(f"{src.stem}.*.o"):
         old.unlink()
+    for old in OBJ.glob(f"{src.stem}.*.ptxas"):
+        old.unlink()
     if cuda:
-        cmd = [NVCC] + flags + (["-Xptxas", "-v"] if verbose else []) + ["-c", str(src), "-o", str(obj)]
+        cmd = [NVCC] + flags + ["-c", str(src), "-o", str(obj)]
     else:
         cmd = [CXX] + flags + ["-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"compile failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    if cuda:
+        obj.with_suffix(".ptxas").write_text(r.stderr)      # registers / spills / shared memory of every kernel
     return obj, r.stderr
 
 
@@ -116,6 +120,33 @@ def build(force: bool = False, verbose: bool = False, cuda: bool = True, host: b
     return out
 
 
+# ---- resource gate: what ptxas reported for every kernel (registers, spills), kept beside the objects ----------
+SPILL_LIMIT_BYTES = 128         # a handful of spilled bytes in a cold path is tolerated, a spilling inner loop is not
+SPILL_ALLOW = ()                # mangled-name substrings exempt from the limit (none at present)
+
+
+def resource_report() -> list:
+    """[(source, kernel, registers, spill_store_bytes, spill_load_bytes)] parsed from the cached ptxas logs."""
+    import re
+    rows = []
+    for log in sorted(OBJ.glob("*.ptxas")):
+        text = log.read_text()
+        for m in re.finditer(r"Function properties for (\S+)\s+\d+ bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads"
+                             r"\s+ptxas info\s*: Used (\d+) registers", text):
+            rows.append((log.name.split(".")[0], m.group(1), int(m.group(4)), int(m.group(2)), int(m.group(3))))
+    return rows
+
+
+def check_resources(limit: int = SPILL_LIMIT_BYTES) -> list:
+    """Raises if a kernel spills more than ``limit`` bytes; returns the report (reference: the reference build gates
+    its kernels on register and scratch use in CI, tools/check_kernel_resources.py:1-60)."""
+    rows = resource_report()
+    bad = [r for r in rows if max(r[3], r[4]) > limit and not any(a in r[1] for a in SPILL_ALLOW)]
+    if bad:
+        raise RuntimeError("kernels over the spill limit: " + "; ".join(f"{s}:{k} stores {a} loads {b}" for s, k, _, a, b in bad))
+    return rows
+
+
 def _read_stamp(so: Path) -> str:
     s = so.with_suffix(".stamp")
     return s.read_text() if s.exists() else ""
@@ -129,3 +160,8 @@ if __name__ == "__main__":
     res = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     for k, v in res.items():
         print(k, v)
+    if "--gate" in sys.argv:
+        rep = check_resources()
+        worst = sorted(rep, key=lambda r: -r[2])[:5]
+        print(f"resource gate: {len(rep)} kernels, none over {SPILL_LIMIT_BYTES} spilled bytes; most registers: "
+              + ", ".join(f"{s}:{r}" for s, _, r, _, _ in worst))

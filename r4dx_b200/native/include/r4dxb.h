@@ -97,6 +97,11 @@ int r4dxb_trellis_input(const void* in, const void* suh, void* out, int T, int K
 /* y[T,N] bf16 from xh[T,K]; kb = 0: w is dense fp16 [N,K]; kb in {3,4,5}: packed trellis words.
  * tn: token tile 16/32/64/128/256.  *status (device int) becomes non-zero if a bounded wait ran out. */
 void r4dxb_set_gemm_decode_warps(int n);
+int r4dxb_trellis_gemm_rs(const void* w, const void* svh, const void* xh, int T, int N, int K, int kb, int tn, int* status,
+                          void* const* recv, void* const* cnt, int world, int rank, int rows_per_rank, void* stream);
+int r4dxb_tp_reduce_push(void* const* x, void* const* xflag, const void* recv, const void* cnt, unsigned target, int world, int rank,
+                         int rows_per_rank, int rows_own, int H, int spin_limit, int* status, void* stream);
+int r4dxb_tp_wait(const void* flag, unsigned target, int spin_limit, int code, int* status, void* stream);
 int r4dxb_trellis_gemm(const void* w, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
                        int kb, int tn, int* status, void* stream);
 

@@ -53,11 +53,21 @@ struct GemmSmem {
   static constexpr int kTotal = kRing + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
+// Reduce-scatter epilogue (tensor-parallel prefill): instead of its own output tensor, the row-parallel product
+// stores every partial row into the receive buffer of the rank that owns the row (rows are dealt out in
+// contiguous blocks of rows_per_rank), over NVLink peer mappings, tile by tile as the epilogue produces them;
+// one system-scope counter per owner collects the arrivals of every CTA on every rank.
+struct RsArgs {
+  __nv_bfloat16* recv[8];      // peer-mapped receive buffers, indexed by owner rank: [world(src)][rows_per_rank][N]
+  unsigned* cnt[8];            // peer-mapped arrival counters, indexed by owner rank
+  int world, rank, rows_per_rank;
+};
+
 template <int KB, int TN, int DW>
 __global__ void __launch_bounds__((DW + 3) * 32, 1)
 TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __restrict__ wsrc,
                   const __half* __restrict__ svh, __nv_bfloat16* __restrict__ y,
-                  const __nv_bfloat16* __restrict__ residual, int T, int N, int K, int* __restrict__ status) {
+                  const __nv_bfloat16* __restrict__ residual, int T, int N, int K, int* __restrict__ status, RsArgs rs) {
   using S = GemmSmem<KB, TN>;
   constexpr int WST = S::WST, AST = S::AST, XST = S::XST;
   extern __shared__ unsigned char smem_dyn[];
@@ -253,11 +263,26 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
             uint2 ov;
             ov.x = PackBf16(o0, o1);
             ov.y = PackBf16(o2, o3);
-            *reinterpret_cast<uint2*>(y + static_cast<size_t>(t) * N + n) = ov;
+            if (rs.world > 0) {
+              const int owner = t / rs.rows_per_rank, tl = t - owner * rs.rows_per_rank;
+              *reinterpret_cast<uint2*>(rs.recv[owner] + (static_cast<size_t>(rs.rank) * rs.rows_per_rank + tl) * N + n) = ov;
+            } else {
+              *reinterpret_cast<uint2*>(y + static_cast<size_t>(t) * N + n) = ov;
+            }
           }
         }
       }
       asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
+    }
+    if (rs.world > 0) {
+      // every partial row of this tile is on its way: publish them, then count this CTA in at each owner it wrote to
+      // (also when a wait ran out: the peers must not wait for a CTA that gave up; the status word tells the host)
+      __threadfence_system();
+      asm volatile("bar.sync 6, %0;" ::"r"(DW * 32) : "memory");
+      if (threadIdx.x == 0) {
+        const int t_last = min(t0 + TN, T) - 1;
+        for (int o = t0 / rs.rows_per_rank; o <= t_last / rs.rows_per_rank; ++o) atomicAdd_system(rs.cnt[o], 1u);
+      }
     }
   }
 
@@ -313,7 +338,7 @@ int g_decode_warps = 16;
 
 template <int KB, int TN, int DW>
 int LaunchGemm(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
-               int* status, cudaStream_t stream) {
+               int* status, cudaStream_t stream, const RsArgs& rs) {
   using S = GemmSmem<KB, TN>;
   static_assert(S::kTotal <= 227 * 1024, "shared memory budget");
   static_assert(S::kBars * 8 + 16 <= 512, "barrier block");
@@ -326,31 +351,31 @@ int LaunchGemm(const void* wsrc, const void* svh, const void* xh, void* y, const
   dim3 grid(N / 128, (T + TN - 1) / TN);
   kern<<<grid, (DW + 3) * 32, S::kTotal, stream>>>(tmap, wsrc, static_cast<const __half*>(svh),
                                                    static_cast<__nv_bfloat16*>(y),
-                                                   static_cast<const __nv_bfloat16*>(residual), T, N, K, status);
+                                                   static_cast<const __nv_bfloat16*>(residual), T, N, K, status, rs);
   return FinishLaunch();
 }
 
 template <int KB, int DW>
 int LaunchGemmTN(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
-                 int tn, int* status, cudaStream_t s) {
+                 int tn, int* status, cudaStream_t s, const RsArgs& rs) {
   switch (tn) {
-    case 16: return LaunchGemm<KB, 16, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 32: return LaunchGemm<KB, 32, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 64: return LaunchGemm<KB, 64, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 128: return LaunchGemm<KB, 128, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 256: return LaunchGemm<KB, 256, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
-    case 512: return LaunchGemm<KB, 512, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s);
+    case 16: return LaunchGemm<KB, 16, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s, rs);
+    case 32: return LaunchGemm<KB, 32, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s, rs);
+    case 64: return LaunchGemm<KB, 64, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s, rs);
+    case 128: return LaunchGemm<KB, 128, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s, rs);
+    case 256: return LaunchGemm<KB, 256, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s, rs);
+    case 512: return LaunchGemm<KB, 512, DW>(wsrc, svh, xh, y, residual, T, N, K, status, s, rs);
     default: return R4DXB_BAD_ARG;
   }
 }
 
 template <int KB>
 int LaunchGemmDW(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
-                 int tn, int* status, cudaStream_t s) {
+                 int tn, int* status, cudaStream_t s, const RsArgs& rs) {
   switch (g_decode_warps) {
-    case 4: return LaunchGemmTN<KB, 4>(wsrc, svh, xh, y, residual, T, N, K, tn, status, s);
-    case 8: return LaunchGemmTN<KB, 8>(wsrc, svh, xh, y, residual, T, N, K, tn, status, s);
-    default: return LaunchGemmTN<KB, 16>(wsrc, svh, xh, y, residual, T, N, K, tn, status, s);
+    case 4: return LaunchGemmTN<KB, 4>(wsrc, svh, xh, y, residual, T, N, K, tn, status, s, rs);
+    case 8: return LaunchGemmTN<KB, 8>(wsrc, svh, xh, y, residual, T, N, K, tn, status, s, rs);
+    default: return LaunchGemmTN<KB, 16>(wsrc, svh, xh, y, residual, T, N, K, tn, status, s, rs);
   }
 }
 
@@ -382,11 +407,35 @@ int r4dxb_trellis_gemm(const void* w, const void* svh, const void* xh, void* y, 
                        int kb, int tn, int* status, void* stream) {
   if (T < 1 || N % 128 || K % 128) return R4DXB_BAD_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RsArgs rs = {};
   switch (kb) {
-    case 0: return LaunchGemmDW<0>(w, svh, xh, y, residual, T, N, K, tn, status, s);
-    case 3: return LaunchGemmDW<3>(w, svh, xh, y, residual, T, N, K, tn, status, s);
-    case 4: return LaunchGemmDW<4>(w, svh, xh, y, residual, T, N, K, tn, status, s);
-    case 5: return LaunchGemmDW<5>(w, svh, xh, y, residual, T, N, K, tn, status, s);
+    case 0: return LaunchGemmDW<0>(w, svh, xh, y, residual, T, N, K, tn, status, s, rs);
+    case 3: return LaunchGemmDW<3>(w, svh, xh, y, residual, T, N, K, tn, status, s, rs);
+    case 4: return LaunchGemmDW<4>(w, svh, xh, y, residual, T, N, K, tn, status, s, rs);
+    case 5: return LaunchGemmDW<5>(w, svh, xh, y, residual, T, N, K, tn, status, s, rs);
+    default: return R4DXB_BAD_ARG;
+  }
+}
+
+/* Row-parallel product with the reduce-scatter in its epilogue: partial row t goes to rank t / rows_per_rank, into
+ * recv[owner] + (rank * rows_per_rank + t % rows_per_rank) * N (bf16), and every CTA adds 1 to cnt[owner] for each
+ * owner its token tile touches, after its rows are visible at system scope.  recv / cnt: `world` peer-mapped pointers. */
+int r4dxb_trellis_gemm_rs(const void* w, const void* svh, const void* xh, int T, int N, int K, int kb, int tn, int* status,
+                          void* const* recv, void* const* cnt, int world, int rank, int rows_per_rank, void* stream) {
+  if (T < 1 || N % 128 || K % 128 || world < 2 || world > 8 || rank < 0 || rank >= world || rows_per_rank < 1 ||
+      static_cast<long long>(rows_per_rank) * world < T)
+    return R4DXB_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RsArgs rs = {};
+  for (int p = 0; p < world; ++p) {
+    rs.recv[p] = static_cast<__nv_bfloat16*>(recv[p]);
+    rs.cnt[p] = static_cast<unsigned*>(cnt[p]);
+  }
+  rs.world = world; rs.rank = rank; rs.rows_per_rank = rows_per_rank;
+  switch (kb) {
+    case 3: return LaunchGemmDW<3>(w, svh, xh, nullptr, nullptr, T, N, K, tn, status, s, rs);
+    case 4: return LaunchGemmDW<4>(w, svh, xh, nullptr, nullptr, T, N, K, tn, status, s, rs);
+    case 5: return LaunchGemmDW<5>(w, svh, xh, nullptr, nullptr, T, N, K, tn, status, s, rs);
     default: return R4DXB_BAD_ARG;
   }
 }

@@ -3,12 +3,16 @@
 Decode / verify rows (T <= 8): ``r4dxb_trellis_gemv_allreduce`` -- the row-parallel trellis linear
 pushes its fp32 partial blocks into every peer's receive slots over NVLink, exchanges per-block
 flags at system scope and sums in rank order, so the all-reduce costs one NVLink round inside the
-kernel's tail instead of a separate collective launch.  Long prefill chunks and the vocab merge
-still use the NCCL baseline inherited from ``NcclComm``.
+kernel's tail instead of a separate collective launch.  Prefill chunks: ``r4dxb_trellis_gemm_rs`` -- the tensor-core product stores its partial rows straight into the
+receive buffer of the rank that owns each token row (reduce-scatter in the GEMM epilogue, tile by tile);
+``r4dxb_tp_reduce_push`` on the owner sums them in rank order on top of the residual row and stores the result
+into every rank's residual stream (the all-gather half, pushed by the kernel that made the rows);
+``r4dxb_tp_wait`` holds the stream until all rows of the call have arrived.  The vocab merge uses NCCL.
 """
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -21,6 +25,9 @@ from .tp_comm import NcclComm
 
 register_cuda_sig("r4dxb_trellis_gemv_allreduce", c_int,
                   [c_ptr] * 6 + [c_int] * 6 + [c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_ptr])
+register_cuda_sig("r4dxb_trellis_gemm_rs", c_int, [c_ptr, c_ptr, c_ptr] + [c_int] * 5 + [c_ptr, c_ptr, c_ptr] + [c_int] * 3 + [c_ptr])
+register_cuda_sig("r4dxb_tp_reduce_push", c_int, [c_ptr, c_ptr, c_ptr, c_ptr, ctypes.c_uint32] + [c_int] * 6 + [c_ptr, c_ptr])
+register_cuda_sig("r4dxb_tp_wait", c_int, [c_ptr, ctypes.c_uint32, c_int, c_int, c_ptr, c_ptr])
 
 MAX_ROWS = 8
 
@@ -59,7 +66,70 @@ class FusedComm(NcclComm):
         self.stats.all_reduces += 1
         self.stats.all_reduce_bytes += T * w.N * 4
 
+    # ---- prefill chunks: reduce-scatter in the GEMM epilogue, all-gather pushed by the reducing kernel ----
+    def alloc_chunk_x(self, C: int, H: int) -> torch.Tensor:
+        """The residual stream of a prefill chunk, in symmetric memory so that owners can push rows into it."""
+        taken = getattr(self, "pf_x", None) is not None and C <= self.pf_C     # a second model on this communicator
+        if os.environ.get("R4DXB_TP_PREFILL", "fused") != "fused" or H != self.n or taken:
+            return torch.empty(C, H, dtype=torch.bfloat16, device=self.device)
+        W = self.world
+        self.pf_C, self.pf_H = C, H
+        self.pf_rpr_max = (C + W - 1) // W
+        a = lambda v: (v + 255) // 256 * 256
+        self.pf_off_recv = a(C * H * 2)
+        self.pf_recv_bytes = a(W * self.pf_rpr_max * H * 2)
+        self.pf_off_cnt = self.pf_off_recv + 2 * self.pf_recv_bytes
+        self.pf_off_xflag = self.pf_off_cnt + 256
+        self.pf_symm = SymmBuffer(self.pf_off_xflag + 256, self.device, self.group)
+        self.pf_x_tab = self.pf_symm.ptr_table(0)
+        self.pf_recv_tab = [self.pf_symm.ptr_table(self.pf_off_recv + p * self.pf_recv_bytes) for p in (0, 1)]
+        self.pf_cnt_tab = self.pf_symm.ptr_table(self.pf_off_cnt)
+        self.pf_xflag_tab = self.pf_symm.ptr_table(self.pf_off_xflag)
+        self.pf_calls = 0
+        self.pf_cnt_target = 0          # arrivals this rank's counter has been promised so far
+        self.pf_xflag_target = 0
+        self.pf_x = self.pf_symm.local_view(0, C * H * 2, torch.bfloat16).view(C, H)
+        return self.pf_x
+
+    def row_parallel_chunk(self, lin, inp: torch.Tensor, x: torch.Tensor, cb: dict, fused_silu_mul: bool = False) -> None:
+        w = lin.w
+        pf_x = getattr(self, "pf_x", None)
+        if (pf_x is None or x.data_ptr() != pf_x.data_ptr() or not isinstance(w, TrellisWeight) or w.N != self.n):
+            return super().row_parallel_chunk(lin, inp, x, cb, fused_silu_mul)
+        L, W, rank = self._lib, self.world, self.rank
+        T, H = x.shape[0], self.n
+        rpr = (T + W - 1) // W
+        tn = K.pick_token_tile(T, w.N)
+        xh = cb["xh"].view(-1)[:T * w.K].view(T, w.K)
+        K.trellis_input(inp, w.suh, out=xh, fused_silu_mul=fused_silu_mul)
+        st = torch.cuda.current_stream().cuda_stream
+        par = self.pf_calls & 1
+        rc = L.r4dxb_trellis_gemm_rs(w.words.data_ptr(), w.svh.data_ptr(), xh.data_ptr(), T, w.N, w.K, w.kb, tn,
+                                     K.gemm_status(self.device).data_ptr(), self.pf_recv_tab[par], self.pf_cnt_tab, W, rank, rpr, st)
+        if rc != 0:
+            raise K.KernelError(f"trellis_gemm_rs failed with code {rc}")
+        # arrivals promised to this rank's counter: every CTA (all ranks) whose token tile touches my rows
+        lo, hi = rank * rpr, min(T, (rank + 1) * rpr)
+        rows_own = max(0, hi - lo)
+        tiles = 0 if rows_own == 0 else (hi - 1) // tn - lo // tn + 1
+        self.pf_cnt_target = (self.pf_cnt_target + W * (w.N // 128) * tiles) & 0xFFFFFFFF
+        base = self.pf_symm.local.data_ptr()
+        rc = L.r4dxb_tp_reduce_push(self.pf_x_tab, self.pf_xflag_tab, base + self.pf_off_recv + par * self.pf_recv_bytes,
+                                    base + self.pf_off_cnt, self.pf_cnt_target, W, rank, rpr, rows_own, H, self.spin_limit,
+                                    self.status.data_ptr(), st)
+        if rc != 0:
+            raise K.KernelError(f"tp_reduce_push failed with code {rc}")
+        self.pf_xflag_target = (self.pf_xflag_target + T) & 0xFFFFFFFF
+        rc = L.r4dxb_tp_wait(base + self.pf_off_xflag, self.pf_xflag_target, self.spin_limit, 300 + rank, self.status.data_ptr(), st)
+        if rc != 0:
+            raise K.KernelError(f"tp_wait failed with code {rc}")
+        self.pf_calls += 1
+        self.stats.all_reduces += 1
+        self.stats.all_reduce_bytes += T * H * 2
+
     def check_healthy(self) -> None:
         code = int(self.status.item())
+        if code >= 200:
+            raise TpTimeoutError(f"rank {self.rank}: a prefill reduce-scatter / all-gather wait ran out (code {code})")
         if code:
             raise TpTimeoutError(f"rank {self.rank}: no answer from rank {code - 100} inside a fused all-reduce")

@@ -27,3 +27,13 @@ def test_convert_roundtrip_and_reuse(tmp_path):
                          "--reuse-tensors-from", out]) == 0
     _, q2 = load_weight_set(out2)
     assert torch.equal(q2["text.layers.0.mlp.down"].words, q["text.layers.0.mlp.down"].words)
+
+
+def test_native_resource_gate_passes_on_the_built_library():
+    """Every kernel's ptxas figures are kept beside its object; none may spill beyond the gate's limit."""
+    from r4dx_b200.native import build as B
+    B.build()
+    rep = B.check_resources()
+    names = " ".join(k for _, k, _, _, _ in rep)
+    assert len(rep) > 100 and "TrellisGemmKernel" in names and "GdnChunkScanKernel" in names
+    assert max(r for _, _, r, _, _ in rep) <= 255

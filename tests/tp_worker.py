@@ -35,8 +35,18 @@ def main():
     torch.cuda.synchronize()
     if hasattr(comm, "check_healthy"):
         comm.check_healthy()
+    # third pass: a longer prompt whose chunks span several token tiles and owners
+    model.reset()
+    ids3 = torch.randint(0, gcfg.vocab_size, (450,), generator=torch.Generator().manual_seed(8), dtype=torch.int32)
+    tok3 = model.prefill(ids3, chunk=384)
+    logits3 = model.buf.logits[:8].float().cpu().clone()
+    torch.cuda.synchronize()
+    if hasattr(comm, "check_healthy"):
+        comm.check_healthy()
+    if comm.mode == "fused":
+        assert getattr(comm, "pf_calls", 0) > 0, "the fused prefill path did not run"
     gathered = [None] * world
-    dist.all_gather_object(gathered, (toks, tok2))
+    dist.all_gather_object(gathered, (toks, tok2, tok3))
     assert all(g == gathered[0] for g in gathered), f"ranks disagree: {gathered}"
     if rank == 0:
         ref = HybridModel(gcfg, full, max_ctx=512, device=dev)
@@ -45,6 +55,9 @@ def main():
         print("tp tokens", toks, "ref tokens", rt, "mode", comm.mode, flush=True)
         assert same >= 9, (toks, rt)
         assert tok2 == toks[0]
+        ref.reset()
+        rt3 = ref.prefill(ids3, chunk=384)
+        assert rt3 == tok3, (rt3, tok3)
         print(comm.stats.line())
         print("TP_OK", flush=True)
     # leave without tearing NCCL down: communicators referenced by captured graphs can stall the teardown
