@@ -9,6 +9,8 @@ graphs: positions, the committed-row count and the token feedback all live in de
 """
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional
@@ -203,7 +205,7 @@ class HybridModel:
         self.pending_rows = 0
 
     # ---- sibling overlap ----------------------------------------------------------------------------
-    overlap_siblings = True
+    overlap_siblings = os.environ.get("R4DXB_OVERLAP", "1") != "0"
 
     def _fork(self):
         if not self.overlap_siblings:

@@ -49,15 +49,29 @@ def main():
     dist.all_gather_object(gathered, (toks, tok2, tok3))
     assert all(g == gathered[0] for g in gathered), f"ranks disagree: {gathered}"
     if rank == 0:
+        # Random weights make near-ties common, and the sharded sum rounds in a different order than the unsharded
+        # product, so token equality is too strict: every token the sharded model picked must be (nearly) the best
+        # token of the unsharded model when that model is fed the same history (teacher forcing).
         ref = HybridModel(gcfg, full, max_ctx=512, device=dev)
-        rt = ref.generate_greedy(ids, 12, use_graph=False)
-        same = sum(int(a == b) for a, b in zip(toks, rt))
-        print("tp tokens", toks, "ref tokens", rt, "mode", comm.mode, flush=True)
-        assert same >= 9, (toks, rt)
-        assert tok2 == toks[0]
+
+        def near_best(lg: torch.Tensor, tok: int, what: str) -> None:
+            lg = lg.float()
+            scale = lg.abs().max().item()
+            gap = lg.max().item() - lg[tok].item()
+            assert gap <= 0.04 * scale, (what, tok, int(lg.argmax()), gap, scale)
+
+        ref.prefill(ids)
+        near_best(ref.buf.logits[0], toks[0], "prefill")
+        near_best(ref.buf.logits[0], tok2, "prefill in 64-row chunks")
+        same = 0
+        for j in range(1, len(toks)):
+            lg = ref.decode_step_logits(toks[j - 1])
+            near_best(lg.view(-1), toks[j], f"decode {j}")
+            same += int(int(lg.argmax()) == toks[j])
+        print("tp tokens", toks, "argmax agreement under teacher forcing", same, "of", len(toks) - 1, "mode", comm.mode, flush=True)
         ref.reset()
-        rt3 = ref.prefill(ids3, chunk=384)
-        assert rt3 == tok3, (rt3, tok3)
+        ref.prefill(ids3, chunk=384)
+        near_best(ref.buf.logits[0], tok3, "long prefill")
         print(comm.stats.line())
         print("TP_OK", flush=True)
     # leave without tearing NCCL down: communicators referenced by captured graphs can stall the teardown
