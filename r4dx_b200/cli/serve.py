@@ -24,10 +24,23 @@ def main(argv=None) -> int:
     else:
         eng = Engine(tm, tk, max_queue=args.max_queue, prompt_checkpoint=(args.prompt_checkpoint == "on"),
                      request_log=RequestLog(args.request_log, args.request_log_tokens))
+    vision, vcfg, image_id = None, None, -1
+    if args.vision == "on" and args.batch <= 1:
+        # the tower's weights ride in the container under "vision."; synthetic models get a synthetic tower
+        from ..models.vision import VisionConfig, VisionTower, init_vision_weights
+        vw = {k[len("vision."):]: v for k, v in getattr(tm.m, "w", {}).items() if isinstance(k, str) and k.startswith("vision.")}
+        vcfg = VisionConfig(out_hidden_size=tm.config.hidden_size)
+        if not vw:
+            vcfg = VisionConfig(depth=2, hidden_size=144, num_heads=2, intermediate_size=256, patch_size=8,
+                                out_hidden_size=tm.config.hidden_size, num_position_embeddings=64, max_pixels=256 * 256)
+            vw = init_vision_weights(vcfg, 0)
+        vision = VisionTower(vcfg, vw, device=str(tm.m.device))
+        image_id = getattr(tk, "image_pad_id", tm.config.vocab_size - 1)
+        eng.vision = vision
     defaults = {"temperature": args.default_temperature, "top_k": args.default_top_k, "top_p": args.default_top_p,
                 "min_p": args.default_min_p, "repetition_penalty": args.default_repetition_penalty}
     srv = ApiServer(eng, tk, tpl, tm.model_id, host=args.host, port=args.port, max_tokens_default=args.max_tokens_default,
-                    defaults=defaults, spec_k=args.mtp)
+                    defaults=defaults, spec_k=args.mtp, vision_config=vcfg, image_token_id=image_id)
     print(f"[r4dxb-server] {tm.model_id} on http://{args.host}:{srv.port} (tp={tm.tp_world()})", file=sys.stderr)
     try:
         srv.serve_forever()

@@ -449,12 +449,14 @@ class HybridModel:
         else:
             self.comm.row_parallel_chunk(lin, inp, x, cb, fused_silu_mul)
 
-    def prefill(self, ids: torch.Tensor, chunk: int = 2048, hook=None) -> int:
+    def prefill(self, ids: torch.Tensor, chunk: int = 2048, hook=None, embed_overrides=None) -> int:
         """Cold or warm prefill of ``ids`` at the current position; returns the greedy next token.
         ``hook(start, T, hidden_rows)`` is called after every chunk with the final hidden states of its rows
         (drafters keep their own caches in lock-step with it)."""
         ids = ids.to(torch.int32)
         n = ids.numel()
+        if embed_overrides is not None:
+            return self._prefill_with_embeds(ids, chunk, hook, embed_overrides)
         if n <= MAX_ROWS:
             tok = self.prefill_small(ids)
             if hook is not None:
@@ -485,6 +487,36 @@ class HybridModel:
         K.check_gemm_status(self.device)
         if last_small:
             return int(self.buf.next_ids[(n - 1) % cb["C"]].item())
+        return int(self.buf.next_ids[0].item())
+
+    def _prefill_with_embeds(self, ids: torch.Tensor, chunk: int, hook, overrides) -> int:
+        """Prefill in which some rows' input embeddings come from outside (image tokens): ``overrides`` =
+        (positions int64 [M] relative to ``ids``, rows bf16 [M, H]).  Always runs the chunk path
+        (reference: src/model/model.cpp:2062-2113 injects vision embeddings the same way)."""
+        pos, rows = overrides
+        pos = pos.to(self.device, torch.long)
+        rows = rows.to(self.device, BF)
+        n = ids.numel()
+        if self.pos + n > self.max_ctx:
+            raise ValueError("context overflow")
+        self.commit_pending()
+        cb = self._chunk_buffers(max(MAX_ROWS + 1, min(chunk, n)))
+        s = 0
+        while s < n:
+            e = min(n, s + cb["C"])
+            T = e - s
+            cb["ids"][:T].copy_(ids[s:e].to(self.device), non_blocking=True)
+            cb["positions"][:T].copy_(torch.arange(self.pos, self.pos + T, dtype=torch.int32, device=self.device))
+            x = cb["x"][:T]
+            K.embed_gather(cb["ids"][:T], self.w["text.embed_tokens"], out=x)
+            sel = (pos >= s) & (pos < e)
+            if bool(sel.any()):
+                x[pos[sel] - s] = rows[sel]
+            self.forward_chunk(T, want_logits=(e == n), skip_embed=True)
+            if hook is not None:
+                hook(s, T, x)
+            s = e
+        K.check_gemm_status(self.device)
         return int(self.buf.next_ids[0].item())
 
     def logits_rows(self, T: int) -> torch.Tensor:

@@ -39,8 +39,9 @@ class TextModel:
     def has_vision(self) -> bool: return False
 
     # ---- forward ----
-    def prefill(self, ids: Sequence[int]) -> int:
-        """Feeds the tokens; returns the greedy next token (logits of the last row via ``last_logits``)."""
+    def prefill(self, ids: Sequence[int], embed_overrides=None) -> int:
+        """Feeds the tokens; returns the greedy next token (logits of the last row via ``last_logits``).
+        ``embed_overrides`` = (positions [M], rows [M, hidden]) replaces those tokens' input embeddings (images)."""
         raise NotImplementedError
     def last_logits(self) -> torch.Tensor: raise NotImplementedError
     def decode_step_greedy(self, token: int) -> int: raise NotImplementedError
@@ -107,11 +108,11 @@ class LocalTextModel(TextModel):
     def has_checkpoint(self) -> bool:
         return self._ck is not None
 
-    def prefill(self, ids: Sequence[int]) -> int:
+    def prefill(self, ids: Sequence[int], embed_overrides=None) -> int:
         self._graph_active = False
         t = torch.as_tensor(list(ids), dtype=torch.int32)
         hook = self.drafter.prefill_hook(t) if self.drafter is not None else None
-        tok = self.m.prefill(t, hook=hook)
+        tok = self.m.prefill(t, hook=hook, embed_overrides=embed_overrides)
         if self.drafter is not None:
             self.drafter.after_prefill(t, tok)
         return tok
@@ -201,8 +202,9 @@ class FakeTextModel(TextModel):
         g = torch.Generator().manual_seed(int.from_bytes(h[:8], "little") % (2**63))
         return torch.randn(self.vocab, generator=g)
 
-    def prefill(self, ids: Sequence[int]) -> int:
+    def prefill(self, ids: Sequence[int], embed_overrides=None) -> int:
         self._tick()
+        self.last_overrides = embed_overrides
         self.history += list(ids)
         self.prefill_tokens += len(ids)
         return int(torch.argmax(self._logits()))

@@ -38,6 +38,8 @@ class GenRequest:
     thinking: bool = True
     request_id: str = field(default_factory=lambda: "req_" + uuid.uuid4().hex[:16])
     spec_k: int = 0
+    images: List = field(default_factory=list)          # uint8 [H, W, 3] tensors, in the order of the image placeholders
+    image_token_id: int = -1
 
 
 @dataclass
@@ -69,8 +71,9 @@ class _Job:
 
 class Engine:
     def __init__(self, model: TextModel, tokenizer, max_queue: int = 8, prompt_checkpoint: bool = True,
-                 request_log: Optional[RequestLog] = None):
+                 request_log: Optional[RequestLog] = None, vision=None):
         self.model = model
+        self.vision = vision               # object with encode_images(list of uint8 images) -> [tokens, hidden]
         self.tk = tokenizer
         self.q: "queue.Queue[_Job]" = queue.Queue(maxsize=max_queue)
         self.prefix = PrefixState()
@@ -131,6 +134,18 @@ class Engine:
         res.prompt_tokens = len(prompt)
         if len(prompt) + req.max_tokens > m.max_ctx:
             raise ValueError(f"prompt ({len(prompt)}) + max_tokens ({req.max_tokens}) exceeds the context ({m.max_ctx})")
+        overrides = None
+        if req.images:
+            # image requests run from a clean state: a token-exact prefix says nothing about the pixels behind it
+            if self.vision is None:
+                raise ValueError("this model was loaded without a vision tower")
+            import torch
+            emb = self.vision.encode_images(req.images)
+            where = torch.tensor([i for i, t in enumerate(prompt) if t == req.image_token_id], dtype=torch.long)
+            if where.numel() != emb.shape[0]:
+                raise ValueError(f"{where.numel()} image placeholder tokens for {emb.shape[0]} image embeddings")
+            overrides = (where, emb)
+            self.prefix.invalidate()
         plan = self.prefix.plan(prompt) if self.prefix.valid else None
         t0 = time.perf_counter()
         if plan is None or plan.action == "reset":
@@ -142,7 +157,7 @@ class Engine:
         else:
             feed_from = plan.feed_from
         res.reused_tokens = feed_from
-        first = m.prefill(prompt[feed_from:])
+        first = m.prefill(prompt[feed_from:], embed_overrides=overrides) if overrides is not None else m.prefill(prompt[feed_from:])
         if self.prompt_checkpoint:
             m.save_checkpoint()
         rng = Rng(req.params.seed)
@@ -211,7 +226,10 @@ class Engine:
         res.decode_ms = (time.perf_counter() - t1) * 1e3
         self.stats["tokens"] += len(res.token_ids)
         # the model state reflects exactly the tokens it was fed
-        self.prefix.commit(fed[:m.position_count()], checkpoint_len=len(prompt) if self.prompt_checkpoint else None)
+        if req.images:
+            self.prefix.invalidate()
+        else:
+            self.prefix.commit(fed[:m.position_count()], checkpoint_len=len(prompt) if self.prompt_checkpoint else None)
 
     def _emit(self, job: _Job, splitter: ReasoningSplitter, tools, piece: str) -> None:
         c, r = splitter.feed(piece)

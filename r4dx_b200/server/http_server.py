@@ -39,7 +39,8 @@ def parse_sampling(body: Dict, defaults: Dict) -> SampleParams:
                         repetition_penalty=num("repetition_penalty", defaults.get("repetition_penalty", 1.0), 0.01, 10.0))
 
 
-def message_text(m: Dict) -> str:
+def message_text(m: Dict, images: Optional[list] = None) -> str:
+    """Flattens OpenAI content parts; every image part becomes a numbered marker and its URL is appended to ``images``."""
     c = m.get("content", "")
     if isinstance(c, list):
         parts = []
@@ -47,7 +48,12 @@ def message_text(m: Dict) -> str:
             if p.get("type") == "text":
                 parts.append(p.get("text", ""))
             elif p.get("type") == "image_url":
-                raise BadRequest("this model was loaded without a vision tower")
+                if images is None:
+                    raise BadRequest("this model was loaded without a vision tower")
+                u = p.get("image_url")
+                from ..runtime.image_prompt import MARK
+                parts.append(MARK % len(images))
+                images.append(u.get("url", "") if isinstance(u, dict) else str(u))
         c = "".join(parts)
     if not isinstance(c, str):
         raise BadRequest("message content must be a string or a list of parts")
@@ -56,7 +62,9 @@ def message_text(m: Dict) -> str:
 
 class ApiServer:
     def __init__(self, engine: Engine, tokenizer, template, model_id: str, host: str = "127.0.0.1", port: int = 8080,
-                 max_tokens_default: int = 512, defaults: Optional[Dict] = None, spec_k: int = 0):
+                 max_tokens_default: int = 512, defaults: Optional[Dict] = None, spec_k: int = 0, vision_config=None,
+                 image_token_id: int = -1):
+        self.vision_config, self.image_token_id = vision_config, image_token_id
         self.engine, self.tk, self.template, self.model_id = engine, tokenizer, template, model_id
         self.max_tokens_default = max_tokens_default
         self.defaults = defaults or {}
@@ -85,6 +93,16 @@ class ApiServer:
                     if outer.engine.fatal:
                         return self._json(503, {"status": "tp_fatal", "detail": outer.engine.fatal})
                     return self._json(200, {"status": "ok"})
+                if self.path == "/metrics":
+                    st = getattr(outer.engine, "stats", {})
+                    text = "".join(f"# TYPE r4dxb_{k}_total counter\nr4dxb_{k}_total {v}\n" for k, v in st.items())
+                    data = text.encode()
+                    self.send_response(200)
+                    self.send_header("Content-Type", "text/plain; version=0.0.4")
+                    self.send_header("Content-Length", str(len(data)))
+                    self.end_headers()
+                    self.wfile.write(data)
+                    return
                 if self.path == "/v1/models":
                     return self._json(200, {"object": "list", "data": [{"id": outer.model_id, "object": "model", "owned_by": "r4dx_b200"}]})
                 self._error(404, "not found")
@@ -135,13 +153,25 @@ class ApiServer:
         if not isinstance(msgs, list) or not msgs:
             raise BadRequest("'messages' must be a non-empty list")
         norm = []
+        urls: list = []
         for m in msgs:
             if not isinstance(m, dict) or "role" not in m:
                 raise BadRequest("every message needs a role")
-            norm.append({**m, "content": message_text(m)})
+            norm.append({**m, "content": message_text(m, urls if self.vision_config is not None else None)})
         thinking = body.get("enable_thinking", (body.get("chat_template_kwargs") or {}).get("enable_thinking"))
         prompt = self.template.render(norm, add_generation_prompt=True, tools=body.get("tools"), enable_thinking=thinking)
-        req = self._common(body, self.tk.encode(prompt), chat=True)
+        if urls:
+            from ..runtime import image_prompt as IP
+            try:
+                imgs = [IP.decode_image(u) for u in urls]
+                counts = [IP.image_token_count(i, self.vision_config) for i in imgs]
+                ids = IP.assemble_prompt(prompt, counts, self.tk.encode, self.image_token_id)
+            except ValueError as e:
+                raise BadRequest(str(e))
+            req = self._common(body, ids, chat=True)
+            req.images, req.image_token_id = imgs, self.image_token_id
+        else:
+            req = self._common(body, self.tk.encode(prompt), chat=True)
         self._serve(h, req, chat=True)
 
     def _completion(self, h, body: Dict):

@@ -187,3 +187,54 @@ def test_batch_engine_runs_requests_together_and_independently():
     r = eng.generate(GenRequest(prompt_ids=[3, 3], max_tokens=2), timeout=10)
     assert r.error is None and len(r.token_ids) == 2
     eng.shutdown()
+
+
+def test_image_parts_become_placeholder_tokens_and_embedding_overrides():
+    import base64
+    import io
+    import torch
+    from PIL import Image
+    from r4dx_b200.models.vision import tiny_vision_config
+    from r4dx_b200.runtime import image_prompt as IP
+    vcfg = tiny_vision_config()
+
+    class FakeVision:
+        def __init__(self):
+            self.seen = []
+
+        def encode_images(self, images):
+            self.seen.append([tuple(i.shape) for i in images])
+            n = sum(IP.image_token_count(i, vcfg) for i in images)
+            return torch.ones(n, 128)
+
+    model = FakeTextModel(vocab=300)
+    vis = FakeVision()
+    eng = Engine(model, ByteTokenizer(300), vision=vis)
+    srv = ApiServer(eng, ByteTokenizer(300), ChatTemplate(), "fake-vl", port=0, vision_config=vcfg, image_token_id=299)
+    srv.start()
+    try:
+        buf = io.BytesIO()
+        Image.new("RGB", (40, 24), (200, 10, 10)).save(buf, format="PNG")
+        uri = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+        body = {"messages": [{"role": "user", "content": [{"type": "text", "text": "what is "}, {"type": "image_url", "image_url": {"url": uri}},
+                                                           {"type": "text", "text": " ?"}]}], "max_tokens": 4, "temperature": 0}
+        r = json.load(_post(srv.port, "/v1/chat/completions", body))
+        assert r["choices"][0]["finish_reason"] in ("stop", "length")
+        assert vis.seen == [[(24, 40, 3)]]
+        pos, rows = model.last_overrides
+        n = IP.image_token_count(torch.zeros(24, 40, 3, dtype=torch.uint8), vcfg)
+        assert pos.numel() == n == rows.shape[0] and n > 0
+        assert all(model.history[int(p)] == 299 for p in pos)                  # overrides sit exactly on the placeholders
+        assert model.history.count(299) == n
+        assert r["usage"]["prompt_tokens"] > n
+        # a plain-text request afterwards is unaffected, and a non-data URL is a 400
+        r2 = json.load(_post(srv.port, "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 2, "temperature": 0}))
+        assert r2["usage"]["completion_tokens"] <= 2 and model.last_overrides is None
+        body["messages"][0]["content"][1]["image_url"]["url"] = "http://example.com/x.png"
+        with pytest.raises(urllib.error.HTTPError) as e:
+            _post(srv.port, "/v1/chat/completions", body)
+        assert e.value.code == 400
+        m = urllib.request.urlopen(f"http://127.0.0.1:{srv.port}/metrics").read().decode()
+        assert "r4dxb_requests_total" in m
+    finally:
+        srv.stop(); eng.shutdown()
