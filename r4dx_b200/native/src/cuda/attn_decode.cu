@@ -49,6 +49,7 @@ struct PrecoreArgs {
 
 // grid (Hq + 2 Hkv, T), block D threads (one element each)
 __global__ void PrecoreKernel(PrecoreArgs a) {
+  PdlEnter();
   extern __shared__ float row[];
   __shared__ float red[32];
   const int t = blockIdx.y, hh = blockIdx.x, d = threadIdx.x, D = a.D;
@@ -107,6 +108,7 @@ struct DecodeArgs {
 // grid (splits, Hkv), 256 threads.  G = gqa * T query rows, row g = t * gqa + j.
 template <int GMAX>
 __global__ void __launch_bounds__(256) DecodeKernel(DecodeArgs a) {
+  PdlEnter();
   extern __shared__ __align__(16) unsigned char smem[];
   if (a.row_slot != nullptr) {
     // one CTA column per sequence: shift every per-sequence pointer, then proceed as a 1-row call
@@ -247,6 +249,7 @@ __global__ void __launch_bounds__(256) DecodeKernel(DecodeArgs a) {
 __global__ void CombineKernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                               const __nv_bfloat16* __restrict__ qg, __nv_bfloat16* __restrict__ out, int T, int Hq,
                               int Hkv, int D, int splits, int gated, int batched) {
+  PdlEnter();
   const int g = blockIdx.x, hkv = blockIdx.y, d = threadIdx.x;
   const int gqa = Hq / Hkv, G = gqa * T;
   if (batched) {
@@ -287,8 +290,7 @@ int LaunchDecode(const DecodeArgs& a, cudaStream_t s, int batch = 1) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
   }
-  kern<<<dim3(a.splits, a.Hkv, batch), 256, smem, s>>>(a);
-  return FinishLaunch();
+  return LaunchPdl(kern, dim3(a.splits, a.Hkv, batch), dim3(256), smem, s, a);
 }
 
 }  // namespace
@@ -318,8 +320,7 @@ int r4dxb_attn_precore(const void* qg, const void* k, const void* v, const void*
   a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.rotary_dim = rotary_dim; a.theta = theta; a.eps = eps;
   a.row_slot = nullptr; a.table_stride = 0;
   a.q_stride = q_stride > 0 ? q_stride : 2 * D;
-  PrecoreKernel<<<dim3(Hq + 2 * Hkv, T), D, D * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
-  return FinishLaunch();
+  return LaunchPdl(PrecoreKernel, dim3(Hq + 2 * Hkv, T), dim3(D), D * sizeof(float), static_cast<cudaStream_t>(stream), a);
 }
 
 /* scratch: part_acc = splits*Hkv*G*D floats, part_ml = splits*Hkv*G*2 floats (G = Hq/Hkv*T) */
@@ -347,9 +348,8 @@ int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const in
   else if (G <= 64) e = LaunchDecode<64>(a, s);
   else return R4DXB_UNSUPPORTED;
   if (e) return e;
-  CombineKernel<<<dim3(G, Hkv), D, 0, s>>>(part_acc, part_ml, static_cast<const __nv_bfloat16*>(qg),
-                                           static_cast<__nv_bfloat16*>(out), T, Hq, Hkv, D, splits, gated, 0);
-  return FinishLaunch();
+  return LaunchPdl(CombineKernel, dim3(G, Hkv), dim3(D), 0, s, static_cast<const float*>(part_acc), static_cast<const float*>(part_ml),
+                   static_cast<const __nv_bfloat16*>(qg), static_cast<__nv_bfloat16*>(out), T, Hq, Hkv, D, splits, gated, 0);
 }
 
 /* Batched decode: B sequences, one new token each.  Row b belongs to slot row_slot[b]; block tables are
@@ -371,8 +371,7 @@ int r4dxb_attn_precore_batch(const void* qg, const void* k, const void* v, const
   a.T = B; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.rotary_dim = rotary_dim; a.theta = theta; a.eps = eps;
   a.row_slot = row_slot; a.table_stride = table_stride;
   a.q_stride = q_stride > 0 ? q_stride : 2 * D;
-  PrecoreKernel<<<dim3(Hq + 2 * Hkv, B), D, D * sizeof(float), static_cast<cudaStream_t>(stream)>>>(a);
-  return FinishLaunch();
+  return LaunchPdl(PrecoreKernel, dim3(Hq + 2 * Hkv, B), dim3(D), D * sizeof(float), static_cast<cudaStream_t>(stream), a);
 }
 
 int r4dxb_attn_decode_batch(const void* q, const void* qg, const void* cache, const int* block_tables, const int* row_slot,

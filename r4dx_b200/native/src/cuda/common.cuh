@@ -20,6 +20,34 @@ inline int FinishLaunch() {
   return static_cast<int>(cudaGetLastError());
 }
 
+// Programmatic dependent launch for the small kernels between the weight-streaming products of a decode step: the
+// kernel is launched with the stream-serialization attribute, lets its own successor begin launching right away
+// and waits on the device for its predecessor before it touches any buffer (PdlEnter is the first statement of
+// such a kernel).  What this hides is launch latency, a few microseconds at each of the ~500 kernel boundaries of a step.
+extern bool g_use_pdl;
+
+__device__ __forceinline__ void PdlEnter() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline int LaunchPdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_use_pdl ? 1 : 0;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args...);
+  ++g_launch_count;
+  return static_cast<int>(e);
+}
+
 __device__ __forceinline__ float WarpSum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -45,6 +45,7 @@ struct GdnArgs {
 
 template <int D>
 __global__ void __launch_bounds__(kThreads) GdnDecodeKernel(GdnArgs a) {
+  PdlEnter();
   constexpr int RPW = D / 16;        // state rows per warp
   constexpr int CPL = D / 32;        // k columns per lane
   __shared__ float sq[kMaxT][D], sk[kMaxT][D], sv[kMaxT][D], so[kMaxT][D];
@@ -247,9 +248,8 @@ extern "C" int r4dxb_gdn_decode(const void* mixed, const void* z, const float* a
   a.eps = eps;
   a.row_slot = nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (D == 128) GdnDecodeKernel<128><<<H, kThreads, 0, s>>>(a);
-  else GdnDecodeKernel<64><<<H, kThreads, 0, s>>>(a);
-  return FinishLaunch();
+  if (D == 128) return LaunchPdl(GdnDecodeKernel<128>, dim3(H), dim3(kThreads), 0, s, a);
+  return LaunchPdl(GdnDecodeKernel<64>, dim3(H), dim3(kThreads), 0, s, a);
 }
 
 /* Batched decode: B sequences, one row each; every per-sequence tensor (ring, state, logs, n_replay) carries a
@@ -277,7 +277,6 @@ extern "C" int r4dxb_gdn_decode_batch(const void* mixed, const void* z, const fl
   a.T = 1; a.H = H; a.Hk = Hk; a.conv_dim = 2 * Hk * D + H * D; a.eps = eps;
   a.row_slot = row_slot;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (D == 128) GdnDecodeKernel<128><<<dim3(H, B), kThreads, 0, s>>>(a);
-  else GdnDecodeKernel<64><<<dim3(H, B), kThreads, 0, s>>>(a);
-  return FinishLaunch();
+  if (D == 128) return LaunchPdl(GdnDecodeKernel<128>, dim3(H, B), dim3(kThreads), 0, s, a);
+  return LaunchPdl(GdnDecodeKernel<64>, dim3(H, B), dim3(kThreads), 0, s, a);
 }

@@ -37,12 +37,14 @@
 namespace cg = cooperative_groups;
 
 namespace r4dxb {
+
+bool g_use_pdl = true;       // shared with the small decode kernels (common.cuh: LaunchPdl)
+
 namespace {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kMaxWorld = 8;
-bool g_use_pdl = true;
 
 // Tensor-parallel epilogue: all-reduce by one-shot push over NVLink peer memory.  Each value travels
 // as an 8-byte (fp32 value, sequence number) pair, so data and "ready" flag arrive in one store and

@@ -102,6 +102,7 @@ __global__ void Bf16Gemv(const __nv_bfloat16* __restrict__ W, const __nv_bfloat1
 // y[t, n] = W[n, :] . bf16(x[t] * rsqrt(mean x[t]^2 + eps) * (1 + nw))
 __global__ void Bf16GemvNorm(const __nv_bfloat16* __restrict__ W, const __nv_bfloat16* __restrict__ x,
                              const __nv_bfloat16* __restrict__ nw, float eps, float* __restrict__ y, int T, int N, int K) {
+  PdlEnter();
   __shared__ float red[32];
   const int n = blockIdx.x;
   const __nv_bfloat16* w = W + static_cast<size_t>(n) * K;
@@ -291,10 +292,8 @@ int r4dxb_bf16_gemv(const void* W, const void* x, float* y, int T, int N, int K,
 int r4dxb_bf16_gemv_norm(const void* W, const void* x, const void* norm_w, float eps, float* y, int T, int N, int K,
                          void* stream) {
   if (T < 1 || T > 8 || N < 1 || K % 2) return R4DXB_BAD_ARG;
-  Bf16GemvNorm<<<N, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(W),
-                                                                 static_cast<const __nv_bfloat16*>(x),
-                                                                 static_cast<const __nv_bfloat16*>(norm_w), eps, y, T, N, K);
-  return FinishLaunch();
+  return LaunchPdl(Bf16GemvNorm, dim3(N), dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const __nv_bfloat16*>(W),
+                   static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(norm_w), eps, y, T, N, K);
 }
 
 int r4dxb_argmax_rows(const void* logits, int is_f32, int T, int V, int id_offset, int* out_ids, float* out_vals,

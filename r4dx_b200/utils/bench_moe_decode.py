@@ -23,6 +23,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--single", action="store_true", help="one sequence through the CUDA-graph decode path (one GPU)")
     a = ap.parse_args()
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -37,6 +38,25 @@ def main() -> None:
     cfg = qwen_hybrid_moe_config(a.layers)
     e_per = cfg.num_experts // world
     w = synthetic_weight_set(cfg, device=dev, seed=0, kb_rule=moe_kb_rule, expert_range=(rank * e_per, e_per))
+    if a.single:
+        from r4dx_b200.models.hybrid import HybridModel
+        m = HybridModel(cfg, w, max_ctx=a.ctx + a.steps + a.warmup + 64, device=dev)
+        m.pos = a.ctx
+        m.enable_graphs((1,))
+        m.decode_begin(17)
+        for _ in range(a.warmup):
+            m.decode_step_graph()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.steps):
+            m.decode_step_graph()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / a.steps
+        print(json.dumps({"metric": "batch-1 decode tok/s, hybrid MoE geometry", "ctx": a.ctx, "layers": a.layers,
+                          "ms_per_step": ms, "tok_s": 1e3 / ms, "reference_published_tok_s": 50.3}))
+        return
     B = a.batch // world
     comm = None
     if world > 1:

@@ -254,3 +254,26 @@ def test_llama_family_matches_oracle():
     ta = a.generate_greedy(ids.to(torch.int32), 8, use_graph=True)
     ref = oracle.greedy(ids, 8)
     assert sum(int(x == y) for x, y in zip(ta, ref)) >= 6, (ta, ref)
+
+
+def test_prefill_with_embedding_overrides_equals_plain_prefill_when_rows_are_the_token_embeddings(tiny):
+    """The image path: rows whose input embedding comes from outside.  Overriding with the tokens' own embeddings
+    must reproduce the plain prefill; overriding with other rows must change the result."""
+    from r4dx_b200.models.hybrid import HybridModel
+    cfg, q, _ = tiny
+    qd = _to_dev(q)
+    ids = torch.randint(0, cfg.vocab_size, (37,), generator=torch.Generator().manual_seed(11)).to(torch.int32)
+    a = HybridModel(cfg, qd, max_ctx=128)
+    a.prefill(ids, chunk=16)
+    la = a.buf.logits[(37 - 1) % 16].float().cpu().clone()      # the 5-row tail went through the small-batch path: row 4 is the last token
+    pos = torch.tensor([3, 4, 5, 20, 36])
+    rows = qd["text.embed_tokens"][ids[pos].long().cuda()]
+    b = HybridModel(cfg, qd, max_ctx=128)
+    b.prefill(ids, chunk=16, embed_overrides=(pos, rows))
+    lb = b.buf.logits[0].float().cpu().clone()
+    scale = la.abs().max().item()
+    assert (la - lb).abs().max().item() < 0.03 * scale          # (the tail rows take the GEMM path here, the GEMV path there)
+    c = HybridModel(cfg, qd, max_ctx=128)
+    c.prefill(ids, chunk=16, embed_overrides=(pos, torch.zeros_like(rows)))
+    lc = c.buf.logits[0].float().cpu()
+    assert (la - lc).abs().max().item() > 0.03 * scale
