@@ -164,11 +164,13 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
     if (lane == 0) {
       const unsigned char* src = reinterpret_cast<const unsigned char*>(a.words) +
                                  (static_cast<size_t>(nb) * (K / 128) + static_cast<size_t>(krank) * a.kblocks_per_cta) * kStageBytes;
+      int s = 0;
+      uint32_t phase = 1;          // parity to wait for on the "empty" barrier of stage s (fresh barriers pass parity 1)
       for (int it = 0; it < a.kblocks_per_cta; ++it) {
-        const int s = it % a.stages, round = it / a.stages;
-        if (!ptx::MbarWait(&empty[s], (round & 1) ^ 1, abort_flag, 1)) break;
+        if (!ptx::MbarWait(&empty[s], phase, abort_flag, 1)) break;
         ptx::MbarArriveExpectTx(&full[s], kStageBytes);
         ptx::BulkLoad(wst + static_cast<size_t>(s) * kStageBytes, src + static_cast<size_t>(it) * kStageBytes, kStageBytes, &full[s]);
+        if (++s == a.stages) { s = 0; phase ^= 1u; }
       }
     }
   } else {
@@ -256,9 +258,12 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
     for (int t = 0; t < TMAX; ++t) acc[t] = 0.f;
     const int khalf = (lane & 1) * 8;
     bool ok = true;
+    // stage index and barrier parity advance by counting: a division by the run-time ring depth per 128-wide
+    // K block would cost as much as decoding a dozen weights
+    int s = 0;
+    uint32_t phase = 0;
     for (int it = 0; it < a.kblocks_per_cta && ok; ++it) {
-      const int s = it % a.stages, round = it / a.stages;
-      ok = ptx::MbarWait(&full[s], round & 1, abort_flag, 2);
+      ok = ptx::MbarWait(&full[s], phase, abort_flag, 2);
       if (!ok) break;
       const uint32_t* sw = reinterpret_cast<const uint32_t*>(wst + static_cast<size_t>(s) * kStageBytes) + warp * NW;
       __half2 hacc[TMAX];
@@ -293,6 +298,7 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
       }
       __syncwarp();
       if (lane == 0) ptx::MbarArrive(&empty[s]);
+      if (++s == a.stages) { s = 0; phase ^= 1u; }
     }
     // hand the partial rows to cluster rank 0: distributed-shared-memory stores + one remote
     // mbarrier arrival per warp; only rank 0 waits, the other CTAs are done

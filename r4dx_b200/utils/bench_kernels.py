@@ -55,6 +55,7 @@ def main() -> None:
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--decode-warps", type=int, default=16)
     ap.add_argument("--tn", type=int, default=0)
+    ap.add_argument("--ksplit", type=int, default=0, help="override the cluster split of the weight-streaming kernel")
     a = ap.parse_args()
     from r4dx_b200.ops import kernels as K
     from r4dx_b200.quant import trellis, w4a16
@@ -71,7 +72,9 @@ def main() -> None:
                 w = trellis.random_weight(N, Kd, kb, seed=1, device=dev)
                 x = torch.randn(T, Kd, device=dev).to(BF)
                 y = torch.empty(T, N, dtype=BF, device=dev)
-                ks = K.pick_ksplit(N, Kd)
+                ks = a.ksplit or K.pick_ksplit(N, Kd)
+                if (Kd // 128) % ks:
+                    continue
                 us = timed(lambda: K.trellis_gemv(w, x, out=y, ksplit=ks), a.iters, flush)
                 gbs = w.nbytes / us / 1e3
                 print(f"trellis_gemv {name:12s} N={N:6d} K={Kd:6d} kb={kb} T={T} ksplit={ks}: {us:8.1f} us  "
