@@ -12,12 +12,15 @@
 // Cache layout: [block][kv_head][2 (K, V)][16 tokens][D] fp8 -- a K tile and a V tile of one
 // block are each one contiguous 16*D byte run.  The sequence length is read from device memory
 // (positions[T-1] + 1) so that a captured CUDA graph can be replayed as the context grows.
+#include <cuda_pipeline.h>
+
 #include "common.cuh"
 
 namespace r4dxb {
 namespace {
 
 constexpr int kBlockTokens = 16;
+constexpr int kTileTokens = 64;    // decode attention works on four cache blocks at a time
 
 __device__ __forceinline__ uint8_t ToFp8(float v) {
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
@@ -122,20 +125,43 @@ __global__ void __launch_bounds__(256) DecodeKernel(DecodeArgs a) {
   }
   const int D = a.D, gqa = a.Hq / a.Hkv, G = gqa * a.T;
   const int split = blockIdx.x, hkv = blockIdx.y, tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
   const int KS = D + 16;                          // padded K row stride (bytes) against bank conflicts
-  uint8_t* Kt = smem;                              // [16][KS]
-  uint8_t* Vt = Kt + kBlockTokens * KS;            // [16][D]
-  __half* qs = reinterpret_cast<__half*>(Vt + kBlockTokens * D);   // [GMAX][D]
-  float* P = reinterpret_cast<float*>(qs + GMAX * D);              // [GMAX][16]
-  float* mrow = P + GMAX * kBlockTokens;           // [GMAX]
+  // a tile is four cache blocks (64 tokens); two tiles of raw fp8 rows are in flight (cp.async double buffer)
+  uint8_t* Kt = smem;                              // [2][64][KS]
+  uint8_t* Vt = Kt + 2 * kTileTokens * KS;         // [2][64][D]
+  __half* qs = reinterpret_cast<__half*>(Vt + 2 * kTileTokens * D);   // [GMAX][D]
+  float* P = reinterpret_cast<float*>(qs + GMAX * D);                 // [GMAX][64]
+  float* mrow = P + GMAX * kTileTokens;            // [GMAX]
   float* lrow = mrow + GMAX;
-  float* arow = lrow + GMAX;                       // per-block rescale factor
+  float* arow = lrow + GMAX;                       // per-tile rescale factor
   int* qpos = reinterpret_cast<int*>(arow + GMAX); // [GMAX] position of each query row
 
   const int seqlen = a.positions[a.T - 1] + 1;
   const int nblocks = (seqlen + kBlockTokens - 1) / kBlockTokens;
-  const int per = (nblocks + a.splits - 1) / a.splits;
+  const int per = (((nblocks + a.splits - 1) / a.splits) + 3) & ~3;     // blocks per split, whole tiles
   const int b0 = split * per, b1 = min(nblocks, b0 + per);
+  const int ntiles = b1 > b0 ? (b1 - b0 + 3) / 4 : 0;
+
+  auto issue = [&](int tile, int buf) {
+    const int vpb = D;                              // 16-byte vectors per (block, K or V): 16 tokens x D bytes
+    for (int i = tid; i < 2 * 4 * vpb; i += 256) {
+      const int kv = i / (4 * vpb), r = i % (4 * vpb);
+      const int bi = r / vpb, v = r % vpb;
+      const int b = b0 + tile * 4 + bi;
+      uint8_t* dst = kv == 0 ? Kt + (static_cast<size_t>(buf) * kTileTokens + bi * kBlockTokens + (v * 16) / D) * KS + (v * 16) % D
+                             : Vt + (static_cast<size_t>(buf) * kTileTokens + bi * kBlockTokens) * D + v * 16;
+      if (b < b1) {
+        const int blk = a.block_table[b];
+        const uint8_t* src = a.cache + ((static_cast<size_t>(blk) * a.Hkv + hkv) * 2 + kv) * kBlockTokens * D + v * 16;
+        __pipeline_memcpy_async(dst, src, 16);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);     // past the end: zeros (masked, but never NaN)
+      }
+    }
+    __pipeline_commit();
+  };
+  if (ntiles > 0) issue(0, 0);
 
   const float sm_scale = rsqrtf(static_cast<float>(D)) * a.k_descale[hkv] * 1.4426950408889634f;  // into log2 domain
   for (int i = tid; i < GMAX * D; i += 256) {
@@ -155,29 +181,21 @@ __global__ void __launch_bounds__(256) DecodeKernel(DecodeArgs a) {
   float acc[GMAX];
 #pragma unroll
   for (int g = 0; g < GMAX; ++g) acc[g] = 0.f;
-  __syncthreads();
 
-  for (int b = b0; b < b1; ++b) {
-    const int blk = a.block_table[b];
-    const uint8_t* src = a.cache + (static_cast<size_t>(blk) * a.Hkv + hkv) * 2 * kBlockTokens * D;
-    const int vec_per_tile = kBlockTokens * D / 16;
-    for (int i = tid; i < 2 * vec_per_tile; i += 256) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src) + i);
-      if (i < vec_per_tile) {
-        const int tok = (i * 16) / D, off = (i * 16) % D;
-        *reinterpret_cast<uint4*>(Kt + tok * KS + off) = v;
-      } else {
-        *reinterpret_cast<uint4*>(Vt + (i - vec_per_tile) * 16) = v;
-      }
-    }
-    __syncthreads();
+  for (int tile = 0; tile < ntiles; ++tile) {
+    const int buf = tile & 1;
+    __pipeline_wait_prior(0);
+    __syncthreads();                 // this tile's rows have landed; the previous tile is fully consumed by every thread
+    if (tile + 1 < ntiles) issue(tile + 1, buf ^ 1);      // its buffer was last read two tiles ago; overlaps the math below
+    const uint8_t* Kb = Kt + static_cast<size_t>(buf) * kTileTokens * KS;
+    const uint8_t* Vb = Vt + static_cast<size_t>(buf) * kTileTokens * D;
+    const int kp0 = (b0 + tile * 4) * kBlockTokens;
     // scores: one thread per (g, tok)
-    for (int i = tid; i < G * kBlockTokens; i += 256) {
-      const int g = i / kBlockTokens, tok = i % kBlockTokens;
-      const int kp = b * kBlockTokens + tok;
+    for (int i = tid; i < G * kTileTokens; i += 256) {
+      const int g = i / kTileTokens, tok = i % kTileTokens;
       float s = -INFINITY;
-      if (kp <= qpos[g]) {
-        const uint2* kr = reinterpret_cast<const uint2*>(Kt + tok * KS);
+      if (kp0 + tok <= qpos[g]) {
+        const uint2* kr = reinterpret_cast<const uint2*>(Kb + tok * KS);
         const uint4* qr = reinterpret_cast<const uint4*>(qs + g * D);
         float sum = 0.f;
         for (int c = 0; c < D / 8; ++c) {
@@ -194,44 +212,40 @@ __global__ void __launch_bounds__(256) DecodeKernel(DecodeArgs a) {
       P[i] = s;
     }
     __syncthreads();
-    // online softmax per query row (log2 domain)
-    if (tid < G) {
-      const int g = tid;
-      float mx = mrow[g];
-      for (int tok = 0; tok < kBlockTokens; ++tok) mx = fmaxf(mx, P[g * kBlockTokens + tok]);
-      const float alpha = (mx == -INFINITY) ? 1.f : exp2f(mrow[g] - mx);
-      float l = lrow[g] * alpha;
-      for (int tok = 0; tok < kBlockTokens; ++tok) {
-        const float s = P[g * kBlockTokens + tok];
-        const float p = (s == -INFINITY) ? 0.f : exp2f(s - mx);
-        P[g * kBlockTokens + tok] = p;
-        l += p;
+    // online softmax (log2 domain): one warp per query row, two tokens per lane
+    for (int g = warp; g < G; g += 8) {
+      const float s0 = P[g * kTileTokens + lane], s1 = P[g * kTileTokens + 32 + lane];
+      const float m_old = mrow[g];
+      const float mx = WarpMax(fmaxf(m_old, fmaxf(s0, s1)));
+      const float alpha = (mx == -INFINITY) ? 1.f : exp2f(m_old - mx);
+      const float p0 = (s0 == -INFINITY) ? 0.f : exp2f(s0 - mx), p1 = (s1 == -INFINITY) ? 0.f : exp2f(s1 - mx);
+      P[g * kTileTokens + lane] = p0;
+      P[g * kTileTokens + 32 + lane] = p1;
+      const float l = lrow[g] * alpha + WarpSum(p0 + p1);
+      __syncwarp();
+      if (lane == 0) {
+        mrow[g] = mx;
+        lrow[g] = l;
+        arow[g] = alpha;
       }
-      mrow[g] = mx;
-      lrow[g] = l;
-      arow[g] = alpha;
     }
     __syncthreads();
     // PV: thread owns one output dim for every query row
     if (tid < D) {
-      float vcol[kBlockTokens];
 #pragma unroll
-      for (int tok = 0; tok < kBlockTokens; ++tok) {
-        const __half_raw hr = __nv_cvt_fp8_to_halfraw(Vt[tok * D + tid], __NV_E4M3);
-        vcol[tok] = __half2float(*reinterpret_cast<const __half*>(&hr));
-      }
+      for (int g = 0; g < GMAX; ++g)
+        if (g < G) acc[g] *= arow[g];
+#pragma unroll 8
+      for (int tok = 0; tok < kTileTokens; ++tok) {
+        const __half_raw hr = __nv_cvt_fp8_to_halfraw(Vb[tok * D + tid], __NV_E4M3);
+        const float v = __half2float(*reinterpret_cast<const __half*>(&hr));
 #pragma unroll
-      for (int g = 0; g < GMAX; ++g) {
-        if (g < G) {
-          float s = acc[g] * arow[g];
-#pragma unroll
-          for (int tok = 0; tok < kBlockTokens; ++tok) s = fmaf(P[g * kBlockTokens + tok], vcol[tok], s);
-          acc[g] = s;
-        }
+        for (int g = 0; g < GMAX; ++g)
+          if (g < G) acc[g] = fmaf(P[g * kTileTokens + tok], v, acc[g]);
       }
     }
-    __syncthreads();
   }
+  __pipeline_wait_prior(0);
   const float vds = a.v_descale[hkv];
   const size_t base = (static_cast<size_t>(split) * a.Hkv + hkv) * G;
   if (tid < D) {
@@ -283,8 +297,8 @@ __global__ void CombineKernel(const float* __restrict__ part_acc, const float* _
 template <int GMAX>
 int LaunchDecode(const DecodeArgs& a, cudaStream_t s, int batch = 1) {
   const int D = a.D;
-  const size_t smem = kBlockTokens * (D + 16) + kBlockTokens * D + static_cast<size_t>(GMAX) * D * 2 +
-                      static_cast<size_t>(GMAX) * kBlockTokens * 4 + GMAX * 4 * 4;
+  const size_t smem = 2 * kTileTokens * (D + 16) + 2 * kTileTokens * D + static_cast<size_t>(GMAX) * D * 2 +
+                      static_cast<size_t>(GMAX) * kTileTokens * 4 + GMAX * 4 * 4;
   auto kern = DecodeKernel<GMAX>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));

@@ -196,17 +196,31 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
       }
     }
     if constexpr (PRO == 1) {
-      // RMSNorm statistics need the whole row, not just this CTA's slice: warp t reduces row t
-      if (warp < T) {
-        const __nv_bfloat16* row = a.x + in_row(warp) * K;
+      // RMSNorm statistics need the whole row, not just this CTA's slice.  All eight consumer warps share every
+      // row (an eighth of K each) so that the reduction is a couple of loads deep instead of K / 256.
+      float* part_ss = part;              // [TMAX][8] partial sums; the split-K partials that live here come much later
+      const int kw = (K / 8 + 7) & ~7;    // columns per warp, a multiple of 8
+      const int k_lo = warp * kw, k_hi = min(K, k_lo + kw);
+#pragma unroll
+      for (int t = 0; t < TMAX; ++t) {
         float ss = 0.f;
-        for (int k = lane * 8; k < K; k += 256) {
-          const uint4 v = *reinterpret_cast<const uint4*>(row + k);
-          ss += BfLo(v.x) * BfLo(v.x) + BfHi(v.x) * BfHi(v.x) + BfLo(v.y) * BfLo(v.y) + BfHi(v.y) * BfHi(v.y) +
-                BfLo(v.z) * BfLo(v.z) + BfHi(v.z) * BfHi(v.z) + BfLo(v.w) * BfLo(v.w) + BfHi(v.w) * BfHi(v.w);
+        if (t < T) {
+          const __nv_bfloat16* row = a.x + in_row(t) * K;
+          for (int k = k_lo + lane * 8; k < k_hi; k += 256) {
+            const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+            ss += BfLo(v.x) * BfLo(v.x) + BfHi(v.x) * BfHi(v.x) + BfLo(v.y) * BfLo(v.y) + BfHi(v.y) * BfHi(v.y) +
+                  BfLo(v.z) * BfLo(v.z) + BfHi(v.z) * BfHi(v.z) + BfLo(v.w) * BfLo(v.w) + BfHi(v.w) * BfHi(v.w);
+          }
+          ss = WarpSum(ss);
         }
-        ss = WarpSum(ss);
-        if (lane == 0) rnorm[warp] = rsqrtf(ss / K + a.eps);
+        if (lane == 0) part_ss[t * 8 + warp] = ss;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (threadIdx.x < TMAX) {
+        float ss = 0.f;
+#pragma unroll
+        for (int w8 = 0; w8 < 8; ++w8) ss += part_ss[threadIdx.x * 8 + w8];
+        rnorm[threadIdx.x] = rsqrtf(ss / K + a.eps);
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
     }
