@@ -34,6 +34,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=64, help="debug only: fewer layers makes the result invalid")
     ap.add_argument("--model", default="qwen-hybrid-27b", choices=["qwen-hybrid-27b", "small"])
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="rows per prefill chunk (0: the model's default)")
     ap.add_argument("--ttft-lens", default="32768,131072", help="extra prompt lengths whose cold TTFT is measured after the decode run")
     ap.add_argument("--no-pdl", action="store_true", help="A/B: disable programmatic dependent launch")
     ap.add_argument("--no-overlap", action="store_true", help="A/B: run sibling projections back to back instead of on a side stream")
@@ -147,12 +148,14 @@ def main():
 
     # ---- cold TTFT: prompt in, first token out (cold = empty caches and state, not a cold process:
     # one short prefill first loads the kernels and allocates the chunk buffers) ---------------------
-    model.prefill(prompt[:2048 + 300])
+    pf_kw = {"chunk": args.prefill_chunk} if args.prefill_chunk else {}
+    model.reserve_prefill(args.prefill_chunk or 4096)      # workspaces are allocated once, outside the timed prefill
+    model.prefill(prompt[:2048 + 300], **pf_kw)
     model.reset()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    tok = model.prefill(prompt)
+    tok = model.prefill(prompt, **pf_kw)
     e1.record()
     barrier()
     ttft_ms = e0.elapsed_time(e1)
@@ -209,7 +212,7 @@ def main():
         ids = torch.randint(0, gcfg.vocab_size, (n,), generator=g, dtype=torch.int32)
         barrier()
         e0.record()
-        model.prefill(ids)
+        model.prefill(ids, **pf_kw)
         e1.record()
         barrier()
         t = torch.tensor([e0.elapsed_time(e1)], device=dev)

@@ -57,4 +57,5 @@ def load_text_model(args, device: Optional[str] = None):
         dcfg, dweights = load_dflash(args.dflash)
         drafter = DflashDrafter(model, dcfg, dweights)
     tk, tpl = load_tokenizer(args.tokenizer_dir, gcfg.vocab_size)
-    return LocalTextModel(model, model_id=model_id, global_config=gcfg, drafter=drafter), tk, tpl
+    return LocalTextModel(model, model_id=model_id, global_config=gcfg, drafter=drafter,
+                          prefill_chunk=getattr(args, "prefill_chunk", 0)), tk, tpl

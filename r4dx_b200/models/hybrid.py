@@ -449,12 +449,24 @@ class HybridModel:
         else:
             self.comm.row_parallel_chunk(lin, inp, x, cb, fused_silu_mul)
 
-    def prefill(self, ids: torch.Tensor, chunk: int = 2048, hook=None, embed_overrides=None) -> int:
+    def reserve_prefill(self, rows: int) -> None:
+        """Allocates the chunk workspaces for prefill chunks of up to ``rows`` rows ahead of time."""
+        self._chunk_buffers(rows)
+
+    @staticmethod
+    def auto_chunk(n: int) -> int:
+        """Rows per prefill chunk.  Measured on the 27B geometry (one GPU): 1536-row chunks fill whole waves of the
+        148 SMs for the 5120-wide products and win up to ~8k tokens (0.744 s vs 0.777 s at 2048); long prompts
+        amortise launches and tile tails better with 4096 rows (32k: 3.54 s vs 3.88 s)."""
+        return 1536 if n <= 12288 else 4096
+
+    def prefill(self, ids: torch.Tensor, chunk: Optional[int] = None, hook=None, embed_overrides=None) -> int:
         """Cold or warm prefill of ``ids`` at the current position; returns the greedy next token.
         ``hook(start, T, hidden_rows)`` is called after every chunk with the final hidden states of its rows
         (drafters keep their own caches in lock-step with it)."""
         ids = ids.to(torch.int32)
         n = ids.numel()
+        chunk = chunk or self.auto_chunk(n)
         if embed_overrides is not None:
             return self._prefill_with_embeds(ids, chunk, hook, embed_overrides)
         if n <= MAX_ROWS:

@@ -6,6 +6,7 @@ fallback (a missing library raises).  Reference numerics for each op live in ``o
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -147,7 +148,7 @@ def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], act: int = 0) -> tor
     return x
 
 
-def pick_ksplit(N: int, K: int, target_ctas: int = 296) -> int:
+def pick_ksplit(N: int, K: int, target_ctas: int = int(os.environ.get("R4DXB_KSPLIT_TARGET", "296"))) -> int:
     """Smallest cluster split (1/2/4/8) that gives at least ``target_ctas`` CTAs, subject to K/128 % split == 0.
     (In isolation the widest split is the fastest on every 27B shape, by up to 5 us; inside a decode step, where
     the RMSNorm prologue is repeated per K slice and neighbouring kernels overlap, it measured slower:

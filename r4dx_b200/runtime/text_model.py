@@ -67,7 +67,9 @@ class TextModel:
 
 
 class LocalTextModel(TextModel):
-    def __init__(self, model, model_id: str = "r4dx-b200", global_config: Optional[ModelConfig] = None, drafter=None):
+    def __init__(self, model, model_id: str = "r4dx-b200", global_config: Optional[ModelConfig] = None, drafter=None,
+                 prefill_chunk: int = 0):
+        self.prefill_chunk = prefill_chunk
         self.m = model
         self.config = global_config or model.cfg
         self.model_id = model_id
@@ -112,7 +114,7 @@ class LocalTextModel(TextModel):
         self._graph_active = False
         t = torch.as_tensor(list(ids), dtype=torch.int32)
         hook = self.drafter.prefill_hook(t) if self.drafter is not None else None
-        tok = self.m.prefill(t, hook=hook, embed_overrides=embed_overrides)
+        tok = self.m.prefill(t, chunk=self.prefill_chunk or None, hook=hook, embed_overrides=embed_overrides)
         if self.drafter is not None:
             self.drafter.after_prefill(t, tok)
         return tok
