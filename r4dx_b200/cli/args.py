@@ -86,6 +86,7 @@ def convert_parser() -> argparse.ArgumentParser:
     ap.add_argument("--kb-plan", default="mix4.5", choices=["mix4.5", "mix3.3", "kb3", "kb4", "kb5"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--threads", type=int, default=0)
+    ap.add_argument("--encoder", default="cpu", choices=["cpu", "cuda"], help="where the trellis Viterbi search runs")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--mtp", action="store_true")
     ap.add_argument("--keep-bf16", default="", help="comma list of tensor-name substrings kept in bf16")

@@ -96,6 +96,9 @@ int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const in
 int r4dxb_trellis_input(const void* in, const void* suh, void* out, int T, int K, int mode, void* stream);
 /* y[T,N] bf16 from xh[T,K]; kb = 0: w is dense fp16 [N,K]; kb in {3,4,5}: packed trellis words.
  * tn: token tile 16/32/64/128/256.  *status (device int) becomes non-zero if a bounded wait ran out. */
+long long r4dxb_trellis_encode_scratch_bytes(int kb, int ctas);
+int r4dxb_trellis_encode_tiles(const float* vals, int ntiles, int kb, void* words, float* err, void* scratch, int ctas,
+                               void* stream);
 void r4dxb_set_gemm_decode_warps(int n);
 int r4dxb_trellis_gemm_rs(const void* w, const void* svh, const void* xh, int T, int N, int K, int kb, int tn, int* status,
                           void* const* recv, void* const* cnt, int world, int rank, int rows_per_rank, void* stream);

@@ -56,6 +56,47 @@ def quantize(W: torch.Tensor, kb: int, seed: int = 0, threads: int | None = None
     return TrellisWeight(words, suh, svh, N, K, kb), float(err)
 
 
+def quantize_cuda(W: torch.Tensor, kb: int, seed: int = 0, device: str = "cuda") -> tuple[TrellisWeight, float]:
+    """The same quantizer with the Viterbi search on the GPU (one CTA per 16x16 tile): regularisation (per-channel
+    scale, random signs, Hadamard sandwich, global scale) in torch on the device, then ``r4dxb_trellis_encode_tiles``.
+    Returns (weight on ``device``, relative squared error).  The random signs come from torch's generator, so the
+    result is a different - equally valid - encoding than the host quantizer's for the same seed."""
+    import ctypes
+    from ..native import c_f32, c_int, c_ptr, register_cuda_sig
+    from ..ops.reference import fwht
+    register_cuda_sig("r4dxb_trellis_encode_scratch_bytes", ctypes.c_longlong, [c_int, c_int])
+    register_cuda_sig("r4dxb_trellis_encode_tiles", c_int, [c_ptr, c_int, c_int, c_ptr, c_ptr, c_ptr, c_int, c_ptr])
+    L = native.cuda()
+    Wd = W.detach().to(device, torch.float32)
+    N, K = Wd.shape
+    if N % 128 or K % 128:
+        raise ValueError(f"trellis needs N and K multiples of 128, got {N}x{K}")
+    g = torch.Generator(device=device).manual_seed(seed)
+    su = Wd.pow(2).mean(0).sqrt()
+    mean_su = su.mean()
+    su = torch.where((su > 0) & (mean_su > 0), su / mean_su, torch.ones_like(su)).clamp(1.0 / 16, 16.0)
+    su = (su * (torch.randint(0, 2, (K,), device=device, generator=g) * 2 - 1)).to(torch.float16).float()
+    sv = (torch.randint(0, 2, (N,), device=device, generator=g) * 2 - 1).float()
+    D = fwht(Wd / su[None, :] * sv[:, None])                                    # rows: Hadamard along K (normalised)
+    D = fwht(D.t().contiguous()).t().contiguous()                               # columns: Hadamard along N
+    sigma = D.pow(2).mean().sqrt()
+    sigma_h = (sigma if float(sigma) > 0 else torch.ones_like(sigma)).to(torch.float16).float()
+    D = D / sigma_h
+    # tiles in word order [N/128][K/16][8 row tiles][16 x 16 positions]
+    tiles = D.view(N // 128, 8, 16, K // 16, 16).permute(0, 3, 1, 2, 4).contiguous().view(-1, 256)
+    ntiles = tiles.shape[0]
+    ctas = min(ntiles, 148)
+    words = torch.empty(ntiles * 8 * kb, dtype=torch.int32, device=device)
+    err = torch.empty(ntiles, dtype=torch.float32, device=device)
+    scratch = torch.empty(int(L.r4dxb_trellis_encode_scratch_bytes(kb, ctas)), dtype=torch.uint8, device=device)
+    rc = L.r4dxb_trellis_encode_tiles(tiles.data_ptr(), ntiles, kb, words.data_ptr(), err.data_ptr(), scratch.data_ptr(), ctas,
+                                      torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise ValueError(f"r4dxb_trellis_encode_tiles failed with code {rc}")
+    rel = float(err.double().sum().item() / (N * K))
+    return TrellisWeight(words, su.to(torch.float16), (sv * sigma_h).to(torch.float16), N, K, kb), rel
+
+
 def random_weight(N: int, K: int, kb: int, seed: int = 0, sigma: float = 0.02, device="cpu") -> TrellisWeight:
     """Synthetic weight: random code bits (values ~ N(0,1)), random signs, global scale sigma."""
     g = torch.Generator().manual_seed(seed)

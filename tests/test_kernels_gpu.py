@@ -490,3 +490,28 @@ def test_rotate_rows_in_place(K, mode):
     if mode == 0:      # the normalised transform is its own inverse
         K.rotate_rows(y, None, 0)
         assert torch.allclose(y.float().cpu(), xf, atol=5e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("kb", [3, 4, 5])
+def test_gpu_viterbi_encoder_matches_the_host_encoder_in_quality(K, kb):
+    """Same search on both sides; the regularisation signs differ, so compare quality, not bits."""
+    from r4dx_b200.quant import trellis
+    g = torch.Generator().manual_seed(kb)
+    W = torch.randn(128, 256, generator=g) * 0.03
+    wc, err_cpu = trellis.quantize(W, kb, seed=1)
+    wg, err_gpu = trellis.quantize_cuda(W, kb, seed=1)
+    assert abs(err_gpu - err_cpu) < 0.1 * err_cpu, (err_gpu, err_cpu)
+    assert err_gpu < {3: 0.04, 4: 0.012, 5: 0.004}[kb]
+    rec = trellis.reconstruct(TrellisWeightCpu(wg))
+    rel = ((rec - W).pow(2).sum() / W.pow(2).sum()).item()
+    assert abs(rel - err_gpu) < 0.25 * err_gpu + 1e-4, (rel, err_gpu)      # the reported error is the real reconstruction error
+    # and the device kernels read the GPU-made words like any other weight
+    x = torch.randn(2, 256, generator=g).to(BF)
+    y = K.trellis_gemv(wg, x.cuda()).float().cpu()
+    ref = x.float() @ rec.T
+    assert torch.allclose(y, ref, atol=3e-2 * ref.abs().max().item(), rtol=3e-2)
+
+
+def TrellisWeightCpu(w):
+    from r4dx_b200.quant.trellis import TrellisWeight
+    return TrellisWeight(w.words.cpu(), w.suh.cpu(), w.svh.cpu(), w.N, w.K, w.kb)
