@@ -428,6 +428,9 @@ class HybridModel:
                               pos0, cfg.rms_norm_eps)
                 self._row_parallel_chunk(self.lin[pg + "out_proj"], core, x, cb)
             K.rmsnorm(x, w[p + "post_attention_layernorm"], cfg.rms_norm_eps, out=h)
+            if cfg.is_moe:
+                self._moe_chunk(i, h, x, T)
+                continue
             pm = p + "mlp."
             gu = cb["gate_up"][:T]
             self.lin[pm + "gate_up"].chunk(h, cb["xh"], gu)
@@ -441,6 +444,35 @@ class HybridModel:
                 self.comm.merge_argmax(b.next_ids[:1], b.next_vals[:1])
         self.pos += T
         self.pending_rows = 0
+
+    def _moe_chunk(self, i: int, h: torch.Tensor, x: torch.Tensor, T: int) -> None:
+        """MoE block over a prefill chunk.  One GPU: all T rows are routed and planned at once and every expert's rows go
+        through the grouped weight-streaming kernel eight at a time (as many passes as the fullest expert needs).
+        Expert parallel: the exchange buffers are sized for decode, so the chunk goes through them in decode-sized slices."""
+        if self.comm is not None and hasattr(self.comm, "moe_forward"):
+            R = self.comm.R
+            for s in range(0, T, R):
+                e = min(T, s + R)
+                self.comm.moe_forward(self.moe[i], h[s:e], x[s:e], e - s)
+            return
+        from .moe import MoeBlock
+        blk = self._moe_chunk_blocks.get(i) if hasattr(self, "_moe_chunk_blocks") else None
+        if blk is None or blk.logits.shape[0] < T:
+            if not hasattr(self, "_moe_chunk_blocks"):
+                self._moe_chunk_blocks = {}
+            # one set of chunk-sized scratch buffers serves every layer; the expert stacks are the decode block's
+            first = next(iter(self._moe_chunk_blocks.values()), None)
+            if first is not None and first.logits.shape[0] >= T:
+                blk = MoeBlock.__new__(MoeBlock)
+                blk.__dict__.update(first.__dict__)
+                src = self.moe[i]
+                for name in ("gate_up", "down", "router", "shared_gate", "shared_gu", "shared_down", "e_begin", "e_count", "ks_gu", "ks_dn"):
+                    setattr(blk, name, getattr(src, name))
+            else:
+                blk = MoeBlock(self.cfg, self.w, i, self.device, self._cb["C"], self.moe[i].e_begin, self.moe[i].e_count,
+                               share_from=self.moe[i])
+            self._moe_chunk_blocks[i] = blk
+        blk.forward(h, x, T, exact_rows=True)
 
     def _row_parallel_chunk(self, lin: Linear, inp: torch.Tensor, x: torch.Tensor, cb: dict,
                             fused_silu_mul: bool = False) -> None:

@@ -87,11 +87,13 @@ class MoeBlock:
         K.moe_router(self.logits[:T], self.k, self.cfg.norm_topk_prob, self.ids, self.wts)
         K.moe_plan(self.ids, T * self.k, self.cfg.num_experts, self.e_begin, self.e_count, self.offsets, self.perm)
 
-    def experts(self, h: torch.Tensor, T: int) -> None:
-        """y_pairs[pair] = down_e(silu(gate_e h) * up_e h) for every pair routed to a local expert."""
-        # few rows in flight: 2-row passes (an expert rarely sees more than one); many: 8-row passes, two of them
+    def experts(self, h: torch.Tensor, T: int, max_rows: Optional[int] = None) -> None:
+        """y_pairs[pair] = down_e(silu(gate_e h) * up_e h) for every pair routed to a local expert.
+        ``max_rows``: the largest per-expert row count of the current plan when the caller knows it (prefill chunks read
+        it back once per layer); otherwise at most ``cap`` rows per expert are served."""
+        # few rows in flight: 2-row passes (an expert rarely sees more than one); many: 8-row passes
         tmax = self.tmax if T <= 4 else 8
-        n_pass = (min(T, self.cap) + tmax - 1) // tmax
+        n_pass = ((max_rows if max_rows is not None else min(T, self.cap)) + tmax - 1) // tmax
         g, d = self.gate_up, self.down
         K.trellis_gemv_grouped(g.words, g.suh, g.svh, h, self.gu_pairs, self.offsets, self.perm, self.k, n_pass, tmax,
                                K.PRO_NONE, g.E, g.N, g.K, g.kb, self.ks_gu)
@@ -113,10 +115,12 @@ class MoeBlock:
             K.trellis_gemv(self.shared_down, self.sh_gu[s:e], out=self.sh_out[s:e], prologue=K.PRO_SILU_MUL)
         K.bf16_gemv(self.shared_gate, h, out=self.sh_gate[:T])
 
-    def forward(self, h: torch.Tensor, x: torch.Tensor, T: int) -> None:
-        """x[T, H] += moe(h) (h = post-attention RMSNorm of x)."""
+    def forward(self, h: torch.Tensor, x: torch.Tensor, T: int, exact_rows: bool = False) -> None:
+        """x[T, H] += moe(h) (h = post-attention RMSNorm of x).  ``exact_rows``: read the plan's largest per-expert row
+        count back (one small copy) and run exactly as many passes as it needs - the prefill path, where one expert
+        can receive hundreds of rows."""
         self.route(h, T)
-        self.experts(h, T)
+        self.experts(h, T, self.max_rows_of_an_expert() if exact_rows else None)
         self.shared(h, T)
         K.moe_combine(self.y_pairs, self.ids, self.wts, self.sh_out, self.sh_gate, x, x, T, self.cfg.hidden_size, self.k)
 

@@ -135,21 +135,33 @@ class OracleModel:
     def _r(self, x: torch.Tensor) -> torch.Tensor:
         return x if self.act_dtype is None else x.to(self.act_dtype).float()
 
+    # calibration taps: ``on_linear(name, input_rows)`` sees the input of every quantizable linear; ``on_kv(layer, k, v)``
+    # sees the keys (after norm and rope) and values an attention layer is about to cache
+    on_linear = None
+    on_kv = None
+
+    def _mm(self, x: torch.Tensor, name: str) -> torch.Tensor:
+        if self.on_linear is not None:
+            self.on_linear(name, x)
+        return x @ self.w[name].T
+
     # ---- blocks ------------------------------------------------------------------------
     def attention(self, p: str, li, x: torch.Tensor, st: OracleState, store: bool = True) -> torch.Tensor:
         cfg, w = self.cfg, self.w
         T = x.shape[0]
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
-        qg = self._r(x @ w[p + "attn.qg"].T).view(T, Hq, cfg.q_proj_dim // Hq)
+        qg = self._r(self._mm(x, p + "attn.qg")).view(T, Hq, cfg.q_proj_dim // Hq)
         q, gate = qg[..., :D], (qg[..., D:] if cfg.attn_output_gate else None)
-        k = self._r(x @ w[p + "attn.k"].T).view(T, Hkv, D)
-        v = self._r(x @ w[p + "attn.v"].T).view(T, Hkv, D)
+        k = self._r(self._mm(x, p + "attn.k")).view(T, Hkv, D)
+        v = self._r(self._mm(x, p + "attn.v")).view(T, Hkv, D)
         if cfg.qk_norm:
             q = R.rmsnorm_1pw(q, w[p + "attn.q_norm"], cfg.rms_norm_eps)
             k = R.rmsnorm_1pw(k, w[p + "attn.k_norm"], cfg.rms_norm_eps)
         pos = torch.arange(st.pos, st.pos + T)
         q = self._r(R.rope_partial_neox(q, pos, cfg.rotary_dim, cfg.rope_theta))
         k = R.rope_partial_neox(k, pos, cfg.rotary_dim, cfg.rope_theta)
+        if self.on_kv is not None:
+            self.on_kv(li, k, v)
         if self.fp8_kv:
             k = R.fp8_e4m3_roundtrip(k, w[p + "attn.k_descale"][None, :, None])
             v = R.fp8_e4m3_roundtrip(v, w[p + "attn.v_descale"][None, :, None])
@@ -159,15 +171,15 @@ class OracleModel:
             st.k[li], st.v[li] = K, V
         o = R.causal_gqa_attention(q, K, V, st.pos)
         o = self._r(o * torch.sigmoid(gate)) if gate is not None else self._r(o)
-        return self._r(o.reshape(T, Hq * D) @ w[p + "attn.o"].T)
+        return self._r(self._mm(o.reshape(T, Hq * D), p + "attn.o"))
 
     def gdn(self, p: str, li, x: torch.Tensor, st: OracleState) -> torch.Tensor:
         cfg, w = self.cfg, self.w
         T = x.shape[0]
         Hk, H = cfg.linear_num_key_heads, cfg.linear_num_value_heads
         Kd, Vd = cfg.linear_key_head_dim, cfg.linear_value_head_dim
-        mixed = self._r(x @ w[p + "gdn.in_proj_qkv"].T)
-        z = self._r(x @ w[p + "gdn.in_proj_z"].T).view(T, H, Vd)
+        mixed = self._r(self._mm(x, p + "gdn.in_proj_qkv"))
+        z = self._r(self._mm(x, p + "gdn.in_proj_z")).view(T, H, Vd)
         a = x @ w[p + "gdn.in_proj_a"].T
         b = x @ w[p + "gdn.in_proj_b"].T
         mixed, st.conv[li] = R.causal_conv1d_silu(mixed, w[p + "gdn.conv1d_weight"], st.conv.get(li))
@@ -178,12 +190,12 @@ class OracleModel:
         fn = R.gdn_chunked if (self.chunked_gdn and T > 1) else R.gdn_recurrent
         o, st.gdn[li] = fn(q, k, v, g, beta, st.gdn.get(li))
         o = self._r(R.gated_rmsnorm(o, z, w[p + "gdn.norm_weight"], cfg.rms_norm_eps))
-        return self._r(o.reshape(T, H * Vd) @ w[p + "gdn.out_proj"].T)
+        return self._r(self._mm(o.reshape(T, H * Vd), p + "gdn.out_proj"))
 
     def mlp(self, p: str, x: torch.Tensor, name: str = "mlp") -> torch.Tensor:
         w = self.w
-        h = self._r(R.silu_mul(self._r(x @ w[p + f"{name}.gate_up"].T)))
-        return self._r(h @ w[p + f"{name}.down"].T)
+        h = self._r(R.silu_mul(self._r(self._mm(x, p + f"{name}.gate_up"))))
+        return self._r(self._mm(h, p + f"{name}.down"))
 
     def moe(self, p: str, x: torch.Tensor) -> torch.Tensor:
         cfg, w = self.cfg, self.w
@@ -220,7 +232,7 @@ class OracleModel:
             x = self._r(x + (self.moe(p, h) if cfg.is_moe else self.mlp(p, h)))
         st.pos += ids.shape[0]
         hn = self._r(R.rmsnorm_1pw(x, w["text.final_norm"], cfg.rms_norm_eps))
-        logits = hn @ w["lm_head"].T
+        logits = self._mm(hn, "lm_head")
         if return_hidden:
             return logits, x, st, captured
         return logits, st

@@ -181,6 +181,30 @@ def test_moe_model_matches_oracle():
     assert (got.argmax(-1) == ref.argmax(-1)).float().mean().item() > 0.8
 
 
+def test_moe_chunked_prefill_matches_the_small_batch_path():
+    """A prompt longer than 8 rows takes the chunk path: all rows routed at once, experts served in 8-row passes."""
+    from r4dx_b200.config import tiny_moe_config
+    from r4dx_b200.models.hybrid import HybridModel
+    from r4dx_b200.models.oracle import init_weights
+    from r4dx_b200.quant.weights import moe_kb_rule, quantize_weight_set
+    cfg = tiny_moe_config()
+    w = init_weights(cfg, 0)
+    for k_ in w:
+        if k_.endswith("moe.router"):
+            w[k_] = w[k_] * 40.0
+    qd = _to_dev(quantize_weight_set(cfg, w, kb_rule=moe_kb_rule))
+    ids = torch.randint(0, cfg.vocab_size, (70,), generator=torch.Generator().manual_seed(12)).to(torch.int32)
+    a = HybridModel(cfg, qd, max_ctx=128)
+    a.prefill_small(ids)
+    la = a.buf.logits[(70 - 1) % 8].float().cpu().clone()
+    b = HybridModel(cfg, qd, max_ctx=128)
+    b.prefill(ids, chunk=48)            # chunks of 48 and 22 rows
+    lb = b.buf.logits[0].float().cpu().clone()
+    scale = la.abs().max().item()
+    assert (la - lb).abs().max().item() < 0.08 * scale
+    assert int(la.argmax()) == int(lb.argmax())
+
+
 def test_expert_parallel_exchange_in_one_gpu_matches_local_moe():
     """World 1: dispatch, plan, grouped experts with peer-buffer I/O and combine run back to back on one GPU
     and must reproduce the plain MoE block; repeated calls exercise both halves of the double buffers."""

@@ -117,3 +117,39 @@ def test_container_roundtrip(tmp_path):
     from safetensors import safe_open
     with safe_open(p, "pt") as f:
         assert torch.equal(f.get_tensor("a"), a)
+
+
+def test_kv_calibration_and_error_compensated_w4a16():
+    """Calibration taps on the oracle: fp8 descales cover what the prompts produced; the Hessian-aware w4a16 rounding
+    gives a smaller OUTPUT error than round-to-nearest on the calibration distribution, in the same packed layout."""
+    import torch
+    from r4dx_b200.config import tiny_hybrid_config
+    from r4dx_b200.models.oracle import init_weights
+    from r4dx_b200.quant import calibrate as C
+    from r4dx_b200.quant import w4a16
+    cfg = tiny_hybrid_config()
+    w = init_weights(cfg, 0)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg.vocab_size, (48,), generator=g) for _ in range(3)]
+    d = C.kv_descales(cfg, w, prompts)
+    attn_layers = [i for i in range(cfg.num_hidden_layers) if cfg.is_attention_layer(i)]
+    assert sorted(d) == attn_layers
+    k_ds, v_ds = d[attn_layers[0]]
+    assert len(k_ds) == cfg.num_key_value_heads and all(x > 0 for x in k_ds + v_ds)
+    H = C.capture_hessians(cfg, w, prompts)
+    name = f"text.layers.{attn_layers[0]}.attn.o"
+    assert H[name].shape == (cfg.q_dim, cfg.q_dim)
+    # a correlated input distribution, where error feedback has something to exploit
+    K_, N_ = 128, 96
+    A = torch.randn(K_, K_, generator=g) * 0.3 + torch.eye(K_)
+    X = torch.randn(2000, K_, generator=g) @ A
+    Wt = torch.randn(N_, K_, generator=g) * 0.05
+    Hx = (X.T @ X / X.shape[0])
+    q_gptq = C.gptq_w4a16(Wt, Hx, group=64)
+    q_rtn = w4a16.quantize(Wt, 64)
+    e_gptq = (X @ (w4a16.dequantize(q_gptq) - Wt).T).pow(2).mean().item()
+    e_rtn = (X @ (w4a16.dequantize(q_rtn) - Wt).T).pow(2).mean().item()
+    assert e_gptq < 0.8 * e_rtn, (e_gptq, e_rtn)
+    # same layout: the packed tensors have the packer's shapes and decode with the packer's rule
+    assert q_gptq.wq.shape == q_rtn.wq.shape and q_gptq.wsz.shape == q_rtn.wsz.shape
+    assert (w4a16.dequantize(q_gptq) - Wt).abs().max().item() < 0.05
