@@ -73,6 +73,36 @@ class PipelinePrefill:
         return int(tok.item())
 
 
+class LayerSplitDecode:
+    """Static two-stage layer split for decode (models whose weights do not fit one GPU): stage A runs its layers on
+    the new rows and hands the residual rows to stage B, which finishes the stack, runs the head and tells both ranks
+    the token.  The stages keep the KV cache / recurrent state of their own layers, exactly as the pipelined prefill
+    left them, so ``PipelinePrefill.prefill`` followed by ``step`` needs no state movement
+    (reference: src/model/qwen4exp_stage.cpp, qwen35moe_stage.cpp run their two big MoE models this way, with the
+    residual bounced through host memory; here it is one NCCL send over NVLink)."""
+
+    def __init__(self, stage: HybridModel, rank: int, group=None):
+        self.stage, self.rank, self.group = stage, rank, group
+        self.tok = torch.zeros(1, dtype=torch.int32, device=stage.device)
+
+    def step(self, token: int) -> int:
+        st = self.stage
+        b = st.buf
+        T = st._stage(torch.tensor([token], dtype=torch.int32), st.pos)
+        b.n_replay.fill_(st.pending_rows)
+        if self.rank == 0:
+            st.forward_rows(T, want_logits=False)
+            dist.send(b.x[:T], dst=1, group=self.group)
+        else:
+            dist.recv(b.x[:T], src=0, group=self.group)
+            st.forward_rows(T, want_logits=True, skip_embed=True)
+            self.tok.copy_(b.next_ids[:1])
+        st.pending_rows = T
+        st.pos += T
+        dist.broadcast(self.tok, src=1, group=self.group)
+        return int(self.tok.item())
+
+
 def _channel_ranges(gcfg: ModelConfig, world: int, rank: int) -> List[Tuple[int, int]]:
     return shard_plan(gcfg, world, rank)["gdn.conv1d_weight"][1]
 

@@ -15,7 +15,7 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device(dev))
     from r4dx_b200.config import small_hybrid_config
     from r4dx_b200.models.hybrid import HybridModel
-    from r4dx_b200.parallel.pp import PipelinePrefill, reshard_to_tp
+    from r4dx_b200.parallel.pp import LayerSplitDecode, PipelinePrefill, reshard_to_tp
     from r4dx_b200.parallel.shard import shard_weight_set
     from r4dx_b200.parallel.tp_comm import make_comm
     from r4dx_b200.quant.weights import synthetic_weight_set
@@ -41,6 +41,13 @@ def main():
     out_ref = [rtok]
     for _ in range(8):
         out_ref.append(ref.decode_step_greedy(out_ref[-1]))
+    # layer-split decode on the two stages, continuing from the pipelined prefill: same kernels, no sharding, so the
+    # tokens equal the single-GPU model's exactly
+    ls = LayerSplitDecode(stage, rank)
+    out_ls = [tok]
+    for _ in range(8):
+        out_ls.append(ls.step(out_ls[-1]))
+    assert out_ls == out_ref, (out_ls, out_ref)
     same = sum(int(a == b) for a, b in zip(out_tp, out_ref))
     if rank == 0:
         print("pp+reshard tokens", out_tp, "ref", out_ref, flush=True)
