@@ -26,6 +26,13 @@ class ModelConfig:
     attn_output_gate: bool = True
     qk_norm: bool = True               # per-head RMSNorm of q and k before rope
     norm_zero_centered: bool = True    # checkpoint norm weights are w with scale (1 + w); False: plain scale w
+    # Gemma-style blocks
+    sandwich_norm: bool = False        # block outputs pass a second RMSNorm before they join the residual stream
+    mlp_act: str = "silu"              # gate activation of the gated MLP: "silu" | "gelu_tanh"
+    sliding_window: int = 0            # > 0: attention layers are windowed, except every ``sliding_global_every``-th one
+    sliding_global_every: int = 6
+    rope_local_theta: float = 1.0e4    # rope base of the windowed layers
+    embed_scale: float = 1.0           # token embeddings are multiplied by this (sqrt(hidden) for Gemma)
     intermediate_size: int = 0
     partial_rotary_factor: float = 0.25
     rope_theta: float = 1.0e7
@@ -101,6 +108,15 @@ class ModelConfig:
     @property
     def is_moe(self) -> bool:
         return self.num_experts > 0
+
+    def layer_window(self, i: int) -> int:
+        """Sliding-window length of layer ``i`` (0 = global attention)."""
+        if self.sliding_window <= 0 or (i + 1) % self.sliding_global_every == 0:
+            return 0
+        return self.sliding_window
+
+    def layer_theta(self, i: int) -> float:
+        return self.rope_local_theta if self.layer_window(i) > 0 else self.rope_theta
 
     def is_attention_layer(self, i: int) -> bool:
         return self.layer_types[i] == "full_attention"
@@ -243,6 +259,25 @@ def llama_config(hidden: int = 4096, layers: int = 32, heads: int = 32, kv_heads
         num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, attn_output_gate=False, qk_norm=False,
         norm_zero_centered=False, intermediate_size=intermediate, partial_rotary_factor=1.0, rope_theta=theta,
         vocab_size=vocab, mtp_num_hidden_layers=0)
+
+
+def gemma_config(hidden: int = 3840, layers: int = 48, heads: int = 16, kv_heads: int = 8, head_dim: int = 256,
+                 intermediate: int = 15360, vocab: int = 262144, window: int = 1024) -> ModelConfig:
+    """Gemma-style dense decoder: sandwich norms, GeGLU, q/k norm, five sliding-window layers per global layer with
+    their own rope base, scaled embeddings, tied head (reference: src/model/gemma_*.{h,cpp}, docs/gemma4-plan.md)."""
+    import math
+    return ModelConfig(
+        arch="gemma", hidden_size=hidden, num_hidden_layers=layers, layer_types=["full_attention"] * layers,
+        num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, attn_output_gate=False, qk_norm=True,
+        intermediate_size=intermediate, partial_rotary_factor=1.0, rope_theta=1.0e6, vocab_size=vocab,
+        tie_word_embeddings=True, mtp_num_hidden_layers=0, sandwich_norm=True, mlp_act="gelu_tanh", sliding_window=window,
+        sliding_global_every=6, rope_local_theta=1.0e4, embed_scale=math.sqrt(hidden))
+
+
+def tiny_gemma_config() -> ModelConfig:
+    c = gemma_config(hidden=256, layers=4, heads=4, kv_heads=2, head_dim=64, intermediate=512, vocab=4096, window=24)
+    c.sliding_global_every = 2
+    return c
 
 
 def tiny_llama_config() -> ModelConfig:

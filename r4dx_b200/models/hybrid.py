@@ -55,14 +55,14 @@ class Linear:
         raise NotImplementedError(f"layout of {self.name}")
 
     def chunk(self, x: torch.Tensor, xh_buf: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
-              fused_silu_mul: bool = False) -> torch.Tensor:
+              fused_silu_mul: bool = False, gelu: bool = False) -> torch.Tensor:
         """Large-T path: input transform (optionally fused with SwiGLU) + tcgen05 GEMM."""
         w = self.w
         if not isinstance(w, TrellisWeight):
             raise NotImplementedError(f"chunk path for layout of {self.name}")
         T = out.shape[0]
         xh = xh_buf.view(-1)[:T * w.K].view(T, w.K)
-        K.trellis_input(x, w.suh, out=xh, fused_silu_mul=fused_silu_mul)
+        K.trellis_input(x, w.suh, out=xh, fused_silu_mul=fused_silu_mul, gelu=gelu)
         return K.trellis_gemm(w, xh, residual=residual, out=out)
 
     @property
@@ -254,11 +254,12 @@ class HybridModel:
         self._join(side)
         K.attn_precore(b.qg, b.k, b.v, w.get(p + "q_norm"), w.get(p + "k_norm"), w[p + "k_descale"], w[p + "v_descale"],
                        b.positions, self.block_table, b.q, self.kv[i], T, Hq, Hkv, D, cfg.rotary_dim,
-                       cfg.rope_theta, cfg.rms_norm_eps, q_stride=cfg.q_proj_dim // Hq)
+                       cfg.layer_theta(i), cfg.rms_norm_eps, q_stride=cfg.q_proj_dim // Hq)
         core = b.core.view(-1)[:T * cfg.q_dim].view(T, cfg.q_dim)
         K.attn_decode(b.q, b.qg, self.kv[i], self.block_table, b.positions, w[p + "k_descale"], w[p + "v_descale"],
-                      b.part_acc, b.part_ml, core, T, Hq, Hkv, D, self.attn_splits, cfg.attn_output_gate)
-        self._row_parallel(self.lin[p + "o"], core, T)
+                      b.part_acc, b.part_ml, core, T, Hq, Hkv, D, self.attn_splits, cfg.attn_output_gate,
+                      window=cfg.layer_window(i))
+        self._row_parallel(self.lin[p + "o"], core, T, post_norm=w.get(f"text.layers.{i}.post_attn_out_norm"))
 
     def _mlp(self, i: int, T: int) -> None:
         cfg, b, w = self.cfg, self.buf, self.w
@@ -272,11 +273,23 @@ class HybridModel:
         p = f"text.layers.{i}.mlp."
         self.lin[p + "gate_up"](b.x[:T], out=b.gate_up[:T], prologue=K.PRO_RMSNORM,
                                 norm_w=w[f"text.layers.{i}.post_attention_layernorm"], eps=cfg.rms_norm_eps)
-        self._row_parallel(self.lin[p + "down"], b.gate_up[:T], T, prologue=K.PRO_SILU_MUL)
+        self._row_parallel(self.lin[p + "down"], b.gate_up[:T], T,
+                           prologue=K.PRO_GELU_MUL if cfg.mlp_act == "gelu_tanh" else K.PRO_SILU_MUL,
+                           post_norm=w.get(f"text.layers.{i}.post_mlp_out_norm"))
 
-    def _row_parallel(self, lin: Linear, x: torch.Tensor, T: int, prologue: int = 0) -> None:
-        """Row-parallel linear whose result is added to the residual stream ``buf.x``."""
+    def _row_parallel(self, lin: Linear, x: torch.Tensor, T: int, prologue: int = 0, post_norm=None) -> None:
+        """Row-parallel linear whose result is added to the residual stream ``buf.x``.  With ``post_norm`` (sandwich-norm
+        families) the summed output is normalised first, so the add cannot ride in the product's epilogue."""
         b = self.buf
+        if post_norm is not None:
+            tmp = b.h[:T]                     # free here: the norms of a decode step live in the products' prologues
+            if self.comm is None or self.comm.world == 1:
+                lin(x, out=tmp, prologue=prologue)
+            else:
+                tmp.zero_()
+                self.comm.row_parallel_linear(lin, x, tmp, prologue)
+            K.norm_add(b.x[:T], tmp, post_norm, self.cfg.rms_norm_eps)
+            return
         if self.comm is None or self.comm.world == 1:
             lin(x, out=b.x[:T], residual=b.x[:T], prologue=prologue)
         else:
@@ -411,11 +424,11 @@ class HybridModel:
                 self.lin[pa + "v"].chunk(h, cb["xh"], vv)
                 K.attn_precore(qg, kk, vv, w.get(pa + "q_norm"), w.get(pa + "k_norm"), w[pa + "k_descale"], w[pa + "v_descale"],
                                cb["positions"], self.block_table, q, self.kv[i], T, Hq, Hkv, D, cfg.rotary_dim,
-                               cfg.rope_theta, cfg.rms_norm_eps, q_stride=cfg.q_proj_dim // Hq)
+                               cfg.layer_theta(i), cfg.rms_norm_eps, q_stride=cfg.q_proj_dim // Hq)
                 core = cb["core"][:T * cfg.q_dim].view(T, cfg.q_dim)
                 K.attn_prefill(q, qg, self.kv[i], self.block_table, w[pa + "k_descale"], w[pa + "v_descale"], core, T,
-                               Hq, Hkv, D, pos0, cfg.attn_output_gate)
-                self._row_parallel_chunk(self.lin[pa + "o"], core, x, cb)
+                               Hq, Hkv, D, pos0, cfg.attn_output_gate, window=cfg.layer_window(i))
+                self._row_parallel_chunk(self.lin[pa + "o"], core, x, cb, post_norm=w.get(p + "post_attn_out_norm"))
             else:
                 pg = p + "gdn."
                 mixed, z, ab = cb["mixed"][:T], cb["z"][:T], cb["ab"][:T]
@@ -434,7 +447,8 @@ class HybridModel:
             pm = p + "mlp."
             gu = cb["gate_up"][:T]
             self.lin[pm + "gate_up"].chunk(h, cb["xh"], gu)
-            self._row_parallel_chunk(self.lin[pm + "down"], gu, x, cb, fused_silu_mul=True)
+            self._row_parallel_chunk(self.lin[pm + "down"], gu, x, cb, fused_silu_mul=True, gelu=(cfg.mlp_act == "gelu_tanh"),
+                                     post_norm=w.get(p + "post_mlp_out_norm"))
         if want_logits and self.layer_end == cfg.num_hidden_layers:
             b = self.buf
             K.rmsnorm(x[T - 1:T], w["text.final_norm"], cfg.rms_norm_eps, out=b.h[:1])
@@ -475,7 +489,18 @@ class HybridModel:
         blk.forward(h, x, T, exact_rows=True)
 
     def _row_parallel_chunk(self, lin: Linear, inp: torch.Tensor, x: torch.Tensor, cb: dict,
-                            fused_silu_mul: bool = False) -> None:
+                            fused_silu_mul: bool = False, gelu: bool = False, post_norm=None) -> None:
+        if post_norm is not None or gelu:
+            # sandwich-norm / GeGLU families: single-GPU chunk path (the fused tensor-parallel epilogues add into x directly)
+            if self.comm is not None and self.comm.world > 1:
+                raise NotImplementedError("tensor-parallel prefill of sandwich-norm models")
+            if post_norm is None:
+                lin.chunk(inp, cb["xh"], x, residual=x, fused_silu_mul=fused_silu_mul, gelu=gelu)
+                return
+            tmp = cb["h"][:x.shape[0]]
+            lin.chunk(inp, cb["xh"], tmp, fused_silu_mul=fused_silu_mul, gelu=gelu)
+            K.norm_add(x, tmp, post_norm, self.cfg.rms_norm_eps)
+            return
         if self.comm is None or self.comm.world == 1:
             lin.chunk(inp, cb["xh"], x, residual=x, fused_silu_mul=fused_silu_mul)
         else:

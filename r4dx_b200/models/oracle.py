@@ -49,7 +49,8 @@ def init_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02, with_mtp: b
         return torch.randn(*shape, generator=g, dtype=torch.float32) * std
 
     H = cfg.hidden_size
-    w: Dict[str, torch.Tensor] = {"text.embed_tokens": n(cfg.vocab_size, H)}
+    # (the stored table already carries the family's embedding scale; a tied head keeps its own unscaled copy)
+    w: Dict[str, torch.Tensor] = {"text.embed_tokens": n(cfg.vocab_size, H) * cfg.embed_scale}
 
     def attn_block(p: str):
         w[p + "attn.qg"] = n(cfg.q_proj_dim, H)
@@ -70,6 +71,9 @@ def init_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02, with_mtp: b
         p = f"text.layers.{i}."
         w[p + "input_layernorm"] = n(H)
         w[p + "post_attention_layernorm"] = n(H)
+        if cfg.sandwich_norm:
+            w[p + "post_attn_out_norm"] = n(H)
+            w[p + "post_mlp_out_norm"] = n(H)
         if cfg.is_attention_layer(i):
             attn_block(p)
         else:
@@ -158,8 +162,10 @@ class OracleModel:
             q = R.rmsnorm_1pw(q, w[p + "attn.q_norm"], cfg.rms_norm_eps)
             k = R.rmsnorm_1pw(k, w[p + "attn.k_norm"], cfg.rms_norm_eps)
         pos = torch.arange(st.pos, st.pos + T)
-        q = self._r(R.rope_partial_neox(q, pos, cfg.rotary_dim, cfg.rope_theta))
-        k = R.rope_partial_neox(k, pos, cfg.rotary_dim, cfg.rope_theta)
+        theta = cfg.layer_theta(li) if isinstance(li, int) else cfg.rope_theta
+        window = cfg.layer_window(li) if isinstance(li, int) else 0
+        q = self._r(R.rope_partial_neox(q, pos, cfg.rotary_dim, theta))
+        k = R.rope_partial_neox(k, pos, cfg.rotary_dim, theta)
         if self.on_kv is not None:
             self.on_kv(li, k, v)
         if self.fp8_kv:
@@ -169,7 +175,7 @@ class OracleModel:
         V = torch.cat([st.v[li], v], 0) if li in st.v else v
         if store:
             st.k[li], st.v[li] = K, V
-        o = R.causal_gqa_attention(q, K, V, st.pos)
+        o = R.causal_gqa_attention(q, K, V, st.pos, window)
         o = self._r(o * torch.sigmoid(gate)) if gate is not None else self._r(o)
         return self._r(self._mm(o.reshape(T, Hq * D), p + "attn.o"))
 
@@ -194,7 +200,8 @@ class OracleModel:
 
     def mlp(self, p: str, x: torch.Tensor, name: str = "mlp") -> torch.Tensor:
         w = self.w
-        h = self._r(R.silu_mul(self._r(self._mm(x, p + f"{name}.gate_up"))))
+        act = R.gelu_mul if self.cfg.mlp_act == "gelu_tanh" else R.silu_mul
+        h = self._r(act(self._r(self._mm(x, p + f"{name}.gate_up"))))
         return self._r(self._mm(h, p + f"{name}.down"))
 
     def moe(self, p: str, x: torch.Tensor) -> torch.Tensor:
@@ -227,9 +234,15 @@ class OracleModel:
             if capture_layers and i in capture_layers:
                 captured[i] = x.clone()
             h = self._r(R.rmsnorm_1pw(x, w[p + "input_layernorm"], cfg.rms_norm_eps))
-            x = self._r(x + (self.attention(p, i, h, st) if cfg.is_attention_layer(i) else self.gdn(p, i, h, st)))
+            a = self.attention(p, i, h, st) if cfg.is_attention_layer(i) else self.gdn(p, i, h, st)
+            if cfg.sandwich_norm:
+                a = self._r(R.rmsnorm_1pw(a, w[p + "post_attn_out_norm"], cfg.rms_norm_eps))
+            x = self._r(x + a)
             h = self._r(R.rmsnorm_1pw(x, w[p + "post_attention_layernorm"], cfg.rms_norm_eps))
-            x = self._r(x + (self.moe(p, h) if cfg.is_moe else self.mlp(p, h)))
+            m = self.moe(p, h) if cfg.is_moe else self.mlp(p, h)
+            if cfg.sandwich_norm:
+                m = self._r(R.rmsnorm_1pw(m, w[p + "post_mlp_out_norm"], cfg.rms_norm_eps))
+            x = self._r(x + m)
         st.pos += ids.shape[0]
         hn = self._r(R.rmsnorm_1pw(x, w["text.final_norm"], cfg.rms_norm_eps))
         logits = self._mm(hn, "lm_head")

@@ -106,6 +106,7 @@ struct DecodeArgs {
   int T, Hq, Hkv, D, splits;
   const int* row_slot;         // batched decode (grid.z = sequence, one query row each); null otherwise
   int table_stride;
+  int window;                  // sliding-window length in tokens (0: the whole sequence is visible)
 };
 
 // grid (splits, Hkv), 256 threads.  G = gqa * T query rows, row g = t * gqa + j.
@@ -139,8 +140,10 @@ __global__ void __launch_bounds__(256) DecodeKernel(DecodeArgs a) {
 
   const int seqlen = a.positions[a.T - 1] + 1;
   const int nblocks = (seqlen + kBlockTokens - 1) / kBlockTokens;
-  const int per = (((nblocks + a.splits - 1) / a.splits) + 3) & ~3;     // blocks per split, whole tiles
-  const int b0 = split * per, b1 = min(nblocks, b0 + per);
+  // sliding window: the oldest key any row of this call may see opens the range
+  const int first_blk = a.window > 0 ? max(0, a.positions[0] - a.window + 1) / kBlockTokens : 0;
+  const int per = ((((nblocks - first_blk) + a.splits - 1) / a.splits) + 3) & ~3;     // blocks per split, whole tiles
+  const int b0 = first_blk + split * per, b1 = min(nblocks, b0 + per);
   const int ntiles = b1 > b0 ? (b1 - b0 + 3) / 4 : 0;
 
   auto issue = [&](int tile, int buf) {
@@ -194,7 +197,7 @@ __global__ void __launch_bounds__(256) DecodeKernel(DecodeArgs a) {
     for (int i = tid; i < G * kTileTokens; i += 256) {
       const int g = i / kTileTokens, tok = i % kTileTokens;
       float s = -INFINITY;
-      if (kp0 + tok <= qpos[g]) {
+      if (kp0 + tok <= qpos[g] && (a.window == 0 || kp0 + tok > qpos[g] - a.window)) {
         const uint2* kr = reinterpret_cast<const uint2*>(Kb + tok * KS);
         const uint4* qr = reinterpret_cast<const uint4*>(qs + g * D);
         float sum = 0.f;
@@ -340,7 +343,8 @@ int r4dxb_attn_precore(const void* qg, const void* k, const void* v, const void*
 /* scratch: part_acc = splits*Hkv*G*D floats, part_ml = splits*Hkv*G*2 floats (G = Hq/Hkv*T) */
 int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const int* block_table, const int* positions,
                       const float* k_descale, const float* v_descale, float* part_acc, float* part_ml, void* out,
-                      int T, int Hq, int Hkv, int D, int splits, int gated, void* stream) {
+                      int T, int Hq, int Hkv, int D, int splits, int flags, void* stream) {
+  const int gated = flags & 1;      // bit 0: sigmoid output gate; bits 1..: sliding-window length (0 = none)
   if (T < 1 || T > 8 || Hq % Hkv || D % 16 || D > 256 || splits < 1) return R4DXB_BAD_ARG;
   const int G = Hq / Hkv * T;
   DecodeArgs a;
@@ -354,6 +358,7 @@ int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const in
   a.part_ml = part_ml;
   a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.splits = splits;
   a.row_slot = nullptr; a.table_stride = 0;
+  a.window = flags >> 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int e;
   if (G <= 8) e = LaunchDecode<8>(a, s);
@@ -390,8 +395,9 @@ int r4dxb_attn_precore_batch(const void* qg, const void* k, const void* v, const
 
 int r4dxb_attn_decode_batch(const void* q, const void* qg, const void* cache, const int* block_tables, const int* row_slot,
                             int table_stride, const int* positions, const float* k_descale, const float* v_descale,
-                            float* part_acc, float* part_ml, void* out, int B, int Hq, int Hkv, int D, int splits, int gated,
+                            float* part_acc, float* part_ml, void* out, int B, int Hq, int Hkv, int D, int splits, int flags,
                             void* stream) {
+  const int gated = flags & 1;
   if (B < 1 || Hq % Hkv || D % 16 || D > 256 || splits < 1 || Hq / Hkv > 64) return R4DXB_BAD_ARG;
   const int G = Hq / Hkv;
   DecodeArgs a;
@@ -402,6 +408,7 @@ int r4dxb_attn_decode_batch(const void* q, const void* qg, const void* cache, co
   a.k_descale = k_descale; a.v_descale = v_descale; a.part_acc = part_acc; a.part_ml = part_ml;
   a.T = 1; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.splits = splits;
   a.row_slot = row_slot; a.table_stride = table_stride;
+  a.window = flags >> 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int e;
   if (G <= 8) e = LaunchDecode<8>(a, s, B);

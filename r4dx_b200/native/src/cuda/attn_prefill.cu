@@ -58,6 +58,7 @@ struct PrefillArgs {
   const float* v_descale;
   __nv_bfloat16* out;          // [T, Hq, D]
   int T, Hq, Hkv, pos0, gated;
+  int window;                  // sliding-window length in tokens (0: causal over the whole sequence)
 };
 
 template <int D, int WARPS>
@@ -118,8 +119,10 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 6 ? 2 : 1)) AttnPrefillK
     }
     __pipeline_commit();
   };
-  fetch(0);
-  for (int kt = 0; kt < key_tiles; ++kt) {
+  // sliding window: tiles entirely older than the first row's window are never touched
+  const int kt_first = a.window > 0 ? max(0, a.pos0 + t_base - a.window + 1) / kKeyTile : 0;
+  fetch(kt_first);
+  for (int kt = kt_first; kt < key_tiles; ++kt) {
     __pipeline_wait_prior(0);
     __syncthreads();     // raw tile landed; previous tile fully consumed (also orders the Q staging before first use)
     // ---- dequantise the K and V tiles ----
@@ -160,7 +163,8 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 6 ? 2 : 1)) AttnPrefillK
     }
     // ---- mask + online softmax (log2 domain) ----
     float mx0 = m0, mx1 = m1;
-    if (kt * kKeyTile + kKeyTile - 1 <= a.pos0 + t_base) {      // the whole tile is visible to every row of the CTA
+    if (kt * kKeyTile + kKeyTile - 1 <= a.pos0 + t_base &&
+        (a.window == 0 || kt * kKeyTile > a.pos0 + t_base + kQTile - 1 - a.window)) {      // the whole tile is visible to every row of the CTA
 #pragma unroll
       for (int n = 0; n < kKeyTile / 8; ++n) {
         S[n][0] *= sm_scale; S[n][1] *= sm_scale; S[n][2] *= sm_scale; S[n][3] *= sm_scale;
@@ -171,10 +175,11 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 6 ? 2 : 1)) AttnPrefillK
 #pragma unroll
       for (int n = 0; n < kKeyTile / 8; ++n) {
         const int kp = kt * kKeyTile + n * 8 + tq * 2;
-        S[n][0] = (kp <= pos_r0) ? S[n][0] * sm_scale : -INFINITY;
-        S[n][1] = (kp + 1 <= pos_r0) ? S[n][1] * sm_scale : -INFINITY;
-        S[n][2] = (kp <= pos_r1) ? S[n][2] * sm_scale : -INFINITY;
-        S[n][3] = (kp + 1 <= pos_r1) ? S[n][3] * sm_scale : -INFINITY;
+        const int w0 = a.window > 0 ? pos_r0 - a.window : -1, w1 = a.window > 0 ? pos_r1 - a.window : -1;
+        S[n][0] = (kp <= pos_r0 && kp > w0) ? S[n][0] * sm_scale : -INFINITY;
+        S[n][1] = (kp + 1 <= pos_r0 && kp + 1 > w0) ? S[n][1] * sm_scale : -INFINITY;
+        S[n][2] = (kp <= pos_r1 && kp > w1) ? S[n][2] * sm_scale : -INFINITY;
+        S[n][3] = (kp + 1 <= pos_r1 && kp + 1 > w1) ? S[n][3] * sm_scale : -INFINITY;
         mx0 = fmaxf(mx0, fmaxf(S[n][0], S[n][1]));
         mx1 = fmaxf(mx1, fmaxf(S[n][2], S[n][3]));
       }
@@ -258,7 +263,8 @@ using namespace r4dxb;
 
 extern "C" int r4dxb_attn_prefill(const void* q, const void* qg, const void* cache, const int* block_table,
                                   const float* k_descale, const float* v_descale, void* out, int T, int Hq, int Hkv, int D,
-                                  int pos0, int gated, void* stream) {
+                                  int pos0, int flags, void* stream) {
+  const int gated = flags & 1;      // bit 0: sigmoid output gate; bits 1..: sliding-window length (0 = none)
   if (T < 1 || Hq % Hkv || (D != 256 && D != 64 && D != 128)) return R4DXB_BAD_ARG;
   const int gqa = Hq / Hkv;
   if (gqa > 8) return R4DXB_UNSUPPORTED;
@@ -270,7 +276,7 @@ extern "C" int r4dxb_attn_prefill(const void* q, const void* qg, const void* cac
   a.k_descale = k_descale;
   a.v_descale = v_descale;
   a.out = static_cast<__nv_bfloat16*>(out);
-  a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.pos0 = pos0; a.gated = gated;
+  a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.pos0 = pos0; a.gated = gated; a.window = flags >> 1;
   const int warps = gqa <= 2 ? 2 : (gqa <= 4 ? 4 : (gqa <= 6 ? 6 : 8));   // idle warps still help the tile conversion
   const size_t smem = static_cast<size_t>(gqa * kQTile + 2 * kKeyTile) * (D + 8) * 2 + 2 * kKeyTile * D;
   dim3 grid((T + kQTile - 1) / kQTile, Hkv);

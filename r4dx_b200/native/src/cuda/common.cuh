@@ -80,6 +80,11 @@ __device__ __forceinline__ uint32_t PackBf16(float a, float b) {
 }
 __device__ __forceinline__ float Sigmoid(float x) { return 1.0f / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float Silu(float x) { return x / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float GeluTanh(float x) {
+  return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+// gate activation of a gated MLP: 0 = SiLU (SwiGLU), 1 = tanh-GELU (GeGLU)
+__device__ __forceinline__ float GateAct(float x, int act) { return act == 0 ? Silu(x) : GeluTanh(x); }
 
 // 128-point Sylvester FWHT held by one warp: lane l owns elements 4l .. 4l+3 (unnormalised).
 __device__ __forceinline__ void WarpFwht128(float (&v)[4]) {

@@ -61,6 +61,29 @@ __global__ void RmsNormKernel(__nv_bfloat16* __restrict__ res, const __nv_bfloat
   }
 }
 
+// Sandwich-norm residual update: res[t] += rmsnorm(delta[t]) * (1 + w)  (the block's output is normalised BEFORE it
+// joins the residual stream; reference: src/model/gemma_layer.cpp post-attention / post-feed-forward norms).
+__global__ void NormAddKernel(__nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ delta,
+                              const __nv_bfloat16* __restrict__ w, int H, float eps) {
+  __shared__ float red[32];
+  const size_t base = static_cast<size_t>(blockIdx.x) * H;
+  float ss = 0.0f;
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    const uint32_t p = *reinterpret_cast<const uint32_t*>(delta + base + i);
+    ss += BfLo(p) * BfLo(p) + BfHi(p) * BfHi(p);
+  }
+  ss = BlockSum(ss, red);
+  const float r = rsqrtf(ss / H + eps);
+  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
+    const uint32_t p = *reinterpret_cast<const uint32_t*>(delta + base + i);
+    const uint32_t q = *reinterpret_cast<const uint32_t*>(w + i);
+    const uint32_t x = *reinterpret_cast<const uint32_t*>(res + base + i);
+    // the normalised block output is a bf16 tensor in the unfused graph: round it, then add
+    const uint32_t n = PackBf16(BfLo(p) * r * (1.0f + BfLo(q)), BfHi(p) * r * (1.0f + BfHi(q)));
+    *reinterpret_cast<uint32_t*>(res + base + i) = PackBf16(BfLo(x) + BfLo(n), BfHi(x) + BfHi(n));
+  }
+}
+
 __global__ void LayerNormKernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                                 const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ out, int H, float eps) {
   extern __shared__ float row[];
@@ -160,6 +183,13 @@ int r4dxb_add_rmsnorm_bf16(void* res, const void* delta, const void* w, void* ou
   RmsNormKernel<true><<<T, kRowThreads, H * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(delta),
       static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(out), H, eps, mode);
+  return FinishLaunch();
+}
+
+int r4dxb_norm_add_bf16(void* res, const void* delta, const void* w, int T, int H, float eps, void* stream) {
+  if (H % 2 || T <= 0) return R4DXB_BAD_ARG;
+  NormAddKernel<<<T, kRowThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(res), static_cast<const __nv_bfloat16*>(delta), static_cast<const __nv_bfloat16*>(w), H, eps);
   return FinishLaunch();
 }
 

@@ -301,7 +301,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
 // one warp per 128-block; producer variants fold the preceding elementwise op into the transform
 // (reference: src/kernels/src/trellis_transform.hip:84-486 fuses the same producers).
 //   mode 0: x = in[t, k]                      (in: [T, K])
-//   mode 1: x = silu(in[t, k]) * in[t, K + k] (in: [T, 2K] fused gate|up rows)
+//   mode 1: x = silu(in[t, k]) * in[t, K + k] (in: [T, 2K] fused gate|up rows); mode 2: the same with a tanh-GELU gate
 __global__ void TrellisInputKernel(const __nv_bfloat16* __restrict__ in, const __half* __restrict__ suh,
                                    __half* __restrict__ out, int T, int K, int mode) {
   const int lane = threadIdx.x & 31;
@@ -318,8 +318,9 @@ __global__ void TrellisInputKernel(const __nv_bfloat16* __restrict__ in, const _
     const uint2 g = *reinterpret_cast<const uint2*>(in + static_cast<size_t>(t) * 2 * K + k);
     const uint2 u = *reinterpret_cast<const uint2*>(in + static_cast<size_t>(t) * 2 * K + K + k);
     // the product is rounded to bf16 exactly like the unfused silu_mul kernel rounds it
-    const uint32_t p01 = PackBf16(Silu(BfLo(g.x)) * BfLo(u.x), Silu(BfHi(g.x)) * BfHi(u.x));
-    const uint32_t p23 = PackBf16(Silu(BfLo(g.y)) * BfLo(u.y), Silu(BfHi(g.y)) * BfHi(u.y));
+    const int act = mode == 2 ? 1 : 0;
+    const uint32_t p01 = PackBf16(GateAct(BfLo(g.x), act) * BfLo(u.x), GateAct(BfHi(g.x), act) * BfHi(u.x));
+    const uint32_t p23 = PackBf16(GateAct(BfLo(g.y), act) * BfLo(u.y), GateAct(BfHi(g.y), act) * BfHi(u.y));
     v[0] = BfLo(p01); v[1] = BfHi(p01); v[2] = BfLo(p23); v[3] = BfHi(p23);
   }
   const uint2 sv = *reinterpret_cast<const uint2*>(suh + k);
@@ -387,7 +388,7 @@ using namespace r4dxb;
 extern "C" {
 
 int r4dxb_trellis_input(const void* in, const void* suh, void* out, int T, int K, int mode, void* stream) {
-  if (T < 1 || K % 128 || mode < 0 || mode > 1) return R4DXB_BAD_ARG;
+  if (T < 1 || K % 128 || mode < 0 || mode > 2) return R4DXB_BAD_ARG;
   const long long items = static_cast<long long>(T) * (K / 128);
   const int warps_per_cta = 8;
   TrellisInputKernel<<<static_cast<unsigned>((items + warps_per_cta - 1) / warps_per_cta), warps_per_cta * 32, 0,

@@ -89,6 +89,7 @@ struct GemvArgs {
   int g_spin_limit;
   int* g_status;
   long long g_words_stride;        // words between consecutive experts
+  int act;                         // gate activation of the fused gated-MLP prologue (GateAct)
 };
 
 template <int KB, int TMAX, int PRO, bool kTp, bool kGrouped = false>
@@ -233,8 +234,8 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
         if constexpr (PRO == 2) {
           const uint2 g = *reinterpret_cast<const uint2*>(a.x + in_row(t) * 2 * K + k);
           const uint2 u = *reinterpret_cast<const uint2*>(a.x + in_row(t) * 2 * K + K + k);
-          const uint32_t p01 = PackBf16(Silu(BfLo(g.x)) * BfLo(u.x), Silu(BfHi(g.x)) * BfHi(u.x));
-          const uint32_t p23 = PackBf16(Silu(BfLo(g.y)) * BfLo(u.y), Silu(BfHi(g.y)) * BfHi(u.y));
+          const uint32_t p01 = PackBf16(GateAct(BfLo(g.x), a.act) * BfLo(u.x), GateAct(BfHi(g.x), a.act) * BfHi(u.x));
+          const uint32_t p23 = PackBf16(GateAct(BfLo(g.y), a.act) * BfLo(u.y), GateAct(BfHi(g.y), a.act) * BfHi(u.y));
           v[0] = BfLo(p01); v[1] = BfHi(p01); v[2] = BfLo(p23); v[3] = BfHi(p23);
         } else {
           // (peer-written rows must not come from a stale L1 line)
@@ -562,6 +563,7 @@ int r4dxb_trellis_gemv_ex(const void* words, const void* suh, const void* svh, c
   if (int rc = CheckArgs(T, N, K, ksplit)) return rc;
   if (prologue == 1 && (norm_w == nullptr || K % 8)) return R4DXB_BAD_ARG;
   GemvArgs a = MakeArgs(words, suh, svh, x, y, residual, norm_w, eps, T, N, K);
+  if (prologue == 3) { prologue = 2; a.act = 1; }      // GeGLU: the SwiGLU prologue with a tanh-GELU gate
   TpPush none = {};
   return LaunchAll<false>(a, kb, prologue, ksplit, static_cast<cudaStream_t>(stream), none);
 }
@@ -629,6 +631,7 @@ int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void*
   if (int rc = CheckArgs(T, N, K, ksplit)) return rc;
   if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world || prologue == 1) return R4DXB_BAD_ARG;
   GemvArgs a = MakeArgs(words, suh, svh, x, y, residual, nullptr, 0.f, T, N, K);
+  if (prologue == 3) { prologue = 2; a.act = 1; }
   TpPush tp = {};
   for (int p = 0; p < world; ++p) tp.recv[p] = static_cast<float2*>(recv[p]);
   tp.block_seq = static_cast<unsigned*>(block_seq);

@@ -118,6 +118,17 @@ def add_rmsnorm(res: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: fl
     return out
 
 
+register_cuda_sig("r4dxb_norm_add_bf16", _I, [_P, _P, _P, _I, _I, _F, _P])
+
+
+def norm_add(res: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """res += rmsnorm(delta) * (1 + w), in place (sandwich-norm residual update)."""
+    _req(res, BF, "res"); _req(delta, BF, "delta")
+    H = res.shape[-1]
+    _check(_lib().r4dxb_norm_add_bf16(_p(res), _p(delta), _p(w), res.numel() // H, H, eps, _stream()), "norm_add")
+    return res
+
+
 def layernorm(x, w, b, eps: float = 1e-6):
     _req(x, BF, "x")
     H = x.shape[-1]
@@ -164,7 +175,7 @@ def pick_ksplit(N: int, K: int, target_ctas: int = int(os.environ.get("R4DXB_KSP
     return best
 
 
-PRO_NONE, PRO_RMSNORM, PRO_SILU_MUL = 0, 1, 2
+PRO_NONE, PRO_RMSNORM, PRO_SILU_MUL, PRO_GELU_MUL = 0, 1, 2, 3
 
 
 def trellis_gemv(w: TrellisWeight, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
@@ -176,7 +187,7 @@ def trellis_gemv(w: TrellisWeight, x: torch.Tensor, residual: Optional[torch.Ten
     PRO_SILU_MUL: x is fused [gate | up] rows [T, 2K].
     """
     _req(x, BF, "x")
-    T = x.numel() // (2 * w.K if prologue == PRO_SILU_MUL else w.K)
+    T = x.numel() // (2 * w.K if prologue in (PRO_SILU_MUL, PRO_GELU_MUL) else w.K)
     out = out if out is not None else torch.empty(T, w.N, dtype=BF, device=x.device)
     ks = ksplit or pick_ksplit(w.N, w.K)
     _check(_lib().r4dxb_trellis_gemv_ex(_p(w.words), _p(w.suh), _p(w.svh), _p(x), _p(out), _p(residual), _p(norm_w), eps,
@@ -245,10 +256,11 @@ def attn_precore(qg, k, v, q_norm, k_norm, k_descale, v_descale, positions, bloc
 
 
 def attn_decode(q, qg, cache, block_table, positions, k_descale, v_descale, part_acc, part_ml, out, T: int, Hq: int,
-                Hkv: int, D: int, splits: int, gated: bool = True):
+                Hkv: int, D: int, splits: int, gated: bool = True, window: int = 0):
+    """``window`` > 0: every row sees only its last ``window`` keys (sliding-window layers)."""
     _check(_lib().r4dxb_attn_decode(_p(q), _p(qg), _p(cache), _p(block_table), _p(positions), _p(k_descale),
                                     _p(v_descale), _p(part_acc), _p(part_ml), _p(out), T, Hq, Hkv, D, splits,
-                                    1 if gated else 0, _stream()), "attn_decode")
+                                    (1 if gated else 0) | (window << 1), _stream()), "attn_decode")
     return out
 
 
@@ -273,13 +285,15 @@ def check_gemm_status(device) -> None:
         raise KernelError(f"tcgen05 GEMM gave up in a bounded wait (role code {code})")
 
 
-def trellis_input(x: torch.Tensor, suh: torch.Tensor, out: Optional[torch.Tensor] = None, fused_silu_mul: bool = False) -> torch.Tensor:
-    """fp16 H128(suh * x) rows; with ``fused_silu_mul`` x is silu(gate) * up of fused [T, 2K] rows."""
+def trellis_input(x: torch.Tensor, suh: torch.Tensor, out: Optional[torch.Tensor] = None, fused_silu_mul: bool = False,
+                  gelu: bool = False) -> torch.Tensor:
+    """fp16 H128(suh * x) rows; with ``fused_silu_mul`` x is act(gate) * up of fused [T, 2K] rows (SiLU, or tanh-GELU with ``gelu``)."""
     _req(x, BF, "x")
     K_ = suh.numel()
     T = x.numel() // (2 * K_ if fused_silu_mul else K_)
     out = out if out is not None else torch.empty(T, K_, dtype=torch.float16, device=x.device)
-    _check(_lib().r4dxb_trellis_input(_p(x), _p(suh), _p(out), T, K_, 1 if fused_silu_mul else 0, _stream()), "trellis_input")
+    mode = (2 if gelu else 1) if fused_silu_mul else 0
+    _check(_lib().r4dxb_trellis_input(_p(x), _p(suh), _p(out), T, K_, mode, _stream()), "trellis_input")
     return out
 
 
@@ -373,9 +387,9 @@ def gdn_chunk_ws_floats(T: int, H: int) -> int:
 
 
 def attn_prefill(q, qg, cache, block_table, k_descale, v_descale, out, T: int, Hq: int, Hkv: int, D: int, pos0: int,
-                 gated: bool = True):
+                 gated: bool = True, window: int = 0):
     _check(_lib().r4dxb_attn_prefill(_p(q), _p(qg), _p(cache), _p(block_table), _p(k_descale), _p(v_descale), _p(out),
-                                     T, Hq, Hkv, D, pos0, 1 if gated else 0, _stream()), "attn_prefill")
+                                     T, Hq, Hkv, D, pos0, (1 if gated else 0) | (window << 1), _stream()), "attn_prefill")
     return out
 
 

@@ -46,6 +46,12 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     return F.silu(g) * u
 
 
+def gelu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """GeGLU on fused rows [gate | up] (tanh approximation)."""
+    g, u = gate_up.float().chunk(2, dim=-1)
+    return F.gelu(g, approximate="tanh") * u
+
+
 def softplus_linear_above_20(x: torch.Tensor) -> torch.Tensor:
     return torch.where(x > 20.0, x, torch.log1p(torch.exp(torch.clamp(x, max=20.0))))
 
@@ -97,7 +103,7 @@ def fp8_e4m3_roundtrip(x: torch.Tensor, descale: float | torch.Tensor = 1.0) -> 
 # ---------------------------------------------------------------------------------------------
 # attention
 # ---------------------------------------------------------------------------------------------
-def causal_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos0: int) -> torch.Tensor:
+def causal_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos0: int, window: int = 0) -> torch.Tensor:
     """q: [T, Hq, D]; k, v: [S, Hkv, D] holding positions 0..S-1; query row t sits at q_pos0 + t.
 
     q head h reads KV head h // (Hq / Hkv).  Returns [T, Hq, D] fp32.
@@ -111,6 +117,8 @@ def causal_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_po
     scores = torch.einsum("thgd,shd->hgts", qf, kf) / math.sqrt(D)
     pos_q = q_pos0 + torch.arange(T)
     mask = torch.arange(S)[None, :] > pos_q[:, None]
+    if window > 0:          # sliding window: a row sees its last ``window`` keys only
+        mask = mask | (torch.arange(S)[None, :] <= pos_q[:, None] - window)
     scores = scores.masked_fill(mask[None, None], float("-inf"))
     p = torch.softmax(scores, dim=-1)
     out = torch.einsum("hgts,shd->thgd", p, vf)

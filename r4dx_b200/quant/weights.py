@@ -121,13 +121,16 @@ def synthetic_weight_set(cfg: ModelConfig, device="cuda", seed: int = 0, sigma: 
         return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * sigma).to(dtype)
 
     H = cfg.hidden_size
-    w: Dict[str, object] = {"text.embed_tokens": n(cfg.vocab_size, H)}
+    w: Dict[str, object] = {"text.embed_tokens": (n(cfg.vocab_size, H).float() * cfg.embed_scale).to(torch.bfloat16)}
     for i, (name, N, K) in enumerate(linear_shapes(cfg)):
         w[name] = trellis.random_weight(N, K, kb_rule(name), seed=seed * 7919 + i, sigma=sigma, device=device)
     for i in range(cfg.num_hidden_layers):
         p = f"text.layers.{i}."
         w[p + "input_layernorm"] = n(H)
         w[p + "post_attention_layernorm"] = n(H)
+        if cfg.sandwich_norm:
+            w[p + "post_attn_out_norm"] = n(H)
+            w[p + "post_mlp_out_norm"] = n(H)
         if cfg.is_attention_layer(i):
             if cfg.qk_norm:
                 w[p + "attn.q_norm"] = n(cfg.head_dim)

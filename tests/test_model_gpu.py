@@ -301,3 +301,36 @@ def test_prefill_with_embedding_overrides_equals_plain_prefill_when_rows_are_the
     c.prefill(ids, chunk=16, embed_overrides=(pos, torch.zeros_like(rows)))
     lc = c.buf.logits[0].float().cpu()
     assert (la - lc).abs().max().item() > 0.03 * scale
+
+
+def test_gemma_style_family_matches_oracle():
+    """Sandwich norms (norm-add kernel), GeGLU prologue, sliding-window attention in decode and prefill, per-layer rope base."""
+    from r4dx_b200.config import tiny_gemma_config
+    from r4dx_b200.models.hybrid import HybridModel
+    from r4dx_b200.models.oracle import OracleModel, init_weights
+    from r4dx_b200.quant.weights import dequantize_weight_set, quantize_weight_set
+    cfg = tiny_gemma_config()
+    q = quantize_weight_set(cfg, init_weights(cfg, 6))
+    oracle = OracleModel(cfg, dequantize_weight_set(q), fp8_kv=True)
+    ids = torch.randint(0, cfg.vocab_size, (56,), generator=torch.Generator().manual_seed(7))
+    ref_logits, _ = oracle.forward(ids)
+    qd = _to_dev(q)
+    m = HybridModel(cfg, qd, max_ctx=256)
+    rows = []
+    for s in range(0, 56, 8):                 # small-batch path: positions run past the 24-token window
+        m.feed(ids[s:s + 8].to(torch.int32))
+        rows.append(m.logits_rows(8).float().cpu().clone())
+    got = torch.cat(rows)
+    scale = ref_logits.abs().max().item()
+    assert (got - ref_logits).abs().max().item() < 0.06 * scale
+    # chunk path (tensor-core GEMMs, windowed prefill attention) lands on the same last-row logits
+    c = HybridModel(cfg, qd, max_ctx=256)
+    c.prefill(ids.to(torch.int32), chunk=40)
+    lc = c.buf.logits[0].float().cpu()
+    assert (lc - ref_logits[-1]).abs().max().item() < 0.06 * scale
+    # graph decode continues consistently with the eager path
+    a = HybridModel(cfg, qd, max_ctx=256)
+    ta = a.generate_greedy(ids.to(torch.int32), 8, use_graph=True)
+    b = HybridModel(cfg, qd, max_ctx=256)
+    tb = b.generate_greedy(ids.to(torch.int32), 8, use_graph=False)
+    assert ta == tb

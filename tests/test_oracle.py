@@ -93,3 +93,35 @@ def test_llama_style_config_prefill_equals_stepwise():
         lg, st = m.forward(ids[t:t + 1], st)
         rows.append(lg)
     assert torch.allclose(full, torch.cat(rows), atol=1e-4, rtol=1e-4)
+
+
+def test_gemma_style_config_chunk_invariance_and_window():
+    """Sandwich norms, GeGLU, sliding-window layers with their own rope base: prefill == stepwise, and tokens beyond
+    the window do not influence a windowed layer's output."""
+    import torch
+    from r4dx_b200.config import tiny_gemma_config
+    from r4dx_b200.models.oracle import OracleModel, OracleState, init_weights
+    from r4dx_b200.ops import reference as R
+    cfg = tiny_gemma_config()
+    cfg.validate()
+    assert [cfg.layer_window(i) for i in range(4)] == [24, 0, 24, 0]
+    assert cfg.layer_theta(0) == cfg.rope_local_theta and cfg.layer_theta(1) == cfg.rope_theta
+    w = init_weights(cfg, 4)
+    assert "text.layers.0.post_attn_out_norm" in w and "text.layers.0.attn.q_norm" in w
+    m = OracleModel(cfg, w)
+    ids = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(0))
+    full, _ = m.forward(ids)
+    st = OracleState()
+    rows = []
+    for s in range(0, 40, 7):
+        lg, st = m.forward(ids[s:s + 7], st)
+        rows.append(lg)
+    assert torch.allclose(full, torch.cat(rows), atol=2e-4, rtol=1e-4)
+    g = torch.Generator().manual_seed(1)
+    q, k, v = torch.randn(3, 4, 16, generator=g), torch.randn(30, 2, 16, generator=g), torch.randn(30, 2, 16, generator=g)
+    a = R.causal_gqa_attention(q, k, v, 27, window=8)
+    k2, v2 = k.clone(), v.clone()
+    k2[:19] += 5.0
+    v2[:19] -= 3.0                                        # keys 0..18 are outside every row's window (rows at 27..29)
+    assert torch.allclose(a, R.causal_gqa_attention(q, k2, v2, 27, window=8), atol=1e-6)
+    assert not torch.allclose(a, R.causal_gqa_attention(q, k2, v2, 27), atol=1e-3)
