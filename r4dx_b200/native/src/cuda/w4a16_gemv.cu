@@ -31,6 +31,63 @@ W4Gemv(const uint4* __restrict__ wq, const uint32_t* __restrict__ wsz, const __n
   const int vec_per_row = K / 32;            // uint4 per row
   const int groups = K / group;
   const int row0 = blockIdx.x * rows_per_cta;
+  if constexpr (TMAX == 1) {
+    // single-row decode (the vocabulary head): two weight rows per warp iteration, so that twice as many 16-byte
+    // loads are in flight per warp and every activation vector read from shared memory serves two rows
+    for (int r = warp; r < rows_per_cta; r += 2 * (kThreads / 32)) {
+      const int n0 = row0 + r, n1 = n0 + kThreads / 32;
+      if (n0 >= N) break;
+      const bool two = (r + kThreads / 32 < rows_per_cta) && n1 < N;
+      const uint4* rp0 = wq + static_cast<size_t>(n0) * vec_per_row;
+      const uint4* rp1 = wq + static_cast<size_t>(two ? n1 : n0) * vec_per_row;
+      const uint32_t* sz0p = wsz + static_cast<size_t>(n0) * groups;
+      const uint32_t* sz1p = wsz + static_cast<size_t>(two ? n1 : n0) * groups;
+      float a0 = 0.f, a1 = 0.f;
+      for (int v = lane; v < vec_per_row; v += 32) {
+        const uint4 q0 = __ldg(rp0 + v), q1 = __ldg(rp1 + v);
+        const int k0 = v * 32;
+        const uint32_t s0 = __ldg(sz0p + k0 / group), s1 = __ldg(sz1p + k0 / group);
+        const uint32_t nzb0 = (s0 >> 16) | (s0 & 0xFFFF0000u), nzb1 = (s1 >> 16) | (s1 & 0xFFFF0000u);
+        const __half2 nz0 = *reinterpret_cast<const __half2*>(&nzb0), nz1 = *reinterpret_cast<const __half2*>(&nzb1);
+        const uint32_t w0[4] = {q0.x, q0.y, q0.z, q0.w}, w1[4] = {q1.x, q1.y, q1.z, q1.w};
+        float g0 = 0.f, g1 = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xs + k0 + wi * 8);
+          const __half2 x0 = *reinterpret_cast<const __half2*>(&xv.x), x1 = *reinterpret_cast<const __half2*>(&xv.y);
+          const __half2 x2 = *reinterpret_cast<const __half2*>(&xv.z), x3 = *reinterpret_cast<const __half2*>(&xv.w);
+          __half2 p0, p1;
+          {
+            uint32_t b;
+            b = ((w0[wi]) & 0x000F000Fu) | 0x64006400u;        p0 = __hmul2(__hadd2(*reinterpret_cast<const __half2*>(&b), nz0), x0);
+            b = ((w0[wi] >> 4) & 0x000F000Fu) | 0x64006400u;   p0 = __hfma2(__hadd2(*reinterpret_cast<const __half2*>(&b), nz0), x1, p0);
+            b = ((w0[wi] >> 8) & 0x000F000Fu) | 0x64006400u;   p0 = __hfma2(__hadd2(*reinterpret_cast<const __half2*>(&b), nz0), x2, p0);
+            b = ((w0[wi] >> 12) & 0x000F000Fu) | 0x64006400u;  p0 = __hfma2(__hadd2(*reinterpret_cast<const __half2*>(&b), nz0), x3, p0);
+            b = ((w1[wi]) & 0x000F000Fu) | 0x64006400u;        p1 = __hmul2(__hadd2(*reinterpret_cast<const __half2*>(&b), nz1), x0);
+            b = ((w1[wi] >> 4) & 0x000F000Fu) | 0x64006400u;   p1 = __hfma2(__hadd2(*reinterpret_cast<const __half2*>(&b), nz1), x1, p1);
+            b = ((w1[wi] >> 8) & 0x000F000Fu) | 0x64006400u;   p1 = __hfma2(__hadd2(*reinterpret_cast<const __half2*>(&b), nz1), x2, p1);
+            b = ((w1[wi] >> 12) & 0x000F000Fu) | 0x64006400u;  p1 = __hfma2(__hadd2(*reinterpret_cast<const __half2*>(&b), nz1), x3, p1);
+          }
+          g0 += __low2float(p0) + __high2float(p0);
+          g1 += __low2float(p1) + __high2float(p1);
+        }
+        a0 = fmaf(g0, __half2float(__ushort_as_half(static_cast<unsigned short>(s0 & 0xFFFF))), a0);
+        a1 = fmaf(g1, __half2float(__ushort_as_half(static_cast<unsigned short>(s1 & 0xFFFF))), a1);
+      }
+      a0 = WarpSum(a0);
+      a1 = WarpSum(a1);
+      if (lane == 0 && T >= 1) {
+        if (out_f32) {
+          static_cast<float*>(y)[n0] = a0;
+          if (two) static_cast<float*>(y)[n1] = a1;
+        } else {
+          static_cast<__nv_bfloat16*>(y)[n0] = __float2bfloat16(a0);
+          if (two) static_cast<__nv_bfloat16*>(y)[n1] = __float2bfloat16(a1);
+        }
+      }
+    }
+    return;
+  }
   for (int r = warp; r < rows_per_cta; r += kThreads / 32) {
     const int n = row0 + r;
     if (n >= N) break;
