@@ -30,14 +30,21 @@ def load_source(spec: str, layers: int, mtp: bool, seed: int):
         return cfg, init_weights(cfg, seed, with_mtp=mtp)
     from safetensors import safe_open
     d = spec if os.path.isdir(spec) else os.path.dirname(spec)
-    cfg = ModelConfig.from_json(open(os.path.join(d, "config.json")).read())
+    cfg_text = open(os.path.join(d, "config.json")).read()
     files = [os.path.join(d, f) for f in sorted(os.listdir(d)) if f.endswith(".safetensors")] if os.path.isdir(spec) else [spec]
     w = {}
     for f in files:
         with safe_open(f, "pt") as sf:
             for k in sf.keys():
                 w[k] = sf.get_tensor(k)
-    return cfg, w
+    if any(k.startswith("text.layers.") for k in w):       # already in this engine's naming
+        return ModelConfig.from_json(cfg_text), w
+    # a Hugging Face checkpoint: read its config.json and rename / reshape the tensors
+    from ..quant.hf_import import config_from_hf, import_hf_weights
+    cfg = config_from_hf(cfg_text)
+    if layers:
+        cfg.num_hidden_layers, cfg.layer_types = layers, cfg.layer_types[:layers]
+    return cfg, import_hf_weights(cfg, w)
 
 
 def main(argv=None) -> int:

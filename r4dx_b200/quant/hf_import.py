@@ -1,0 +1,215 @@
+"""Hugging Face checkpoint names and layouts -> this engine's weight set.
+
+``config_from_hf`` reads a ``config.json`` (dense hybrid, hybrid MoE, Llama-style, Gemma-style) into a ``ModelConfig``;
+``import_hf_weights`` renames and reshapes the tensors:
+
+* gated attention: ``q_proj`` already holds per-head ``[q | gate]`` rows -> ``attn.qg``; ``k/v/o_proj`` -> ``attn.k/v/o``;
+* Gated DeltaNet: either separate ``in_proj_qkv / in_proj_z / in_proj_a / in_proj_b`` tensors, or the packed
+  ``in_proj_qkvz`` (per key head: q, k, its value heads' v, their z) and ``in_proj_ba`` (per key head: b's then a's),
+  which are unpacked into ``[q heads | k heads | v heads]`` rows, z rows, a rows, b rows;
+  ``conv1d.weight [C, 1, 4]`` -> ``[C, 4]``;
+* MLP: ``gate_proj`` and ``up_proj`` are stacked into ``gate_up`` (gate rows first);
+* MoE: ``mlp.gate`` -> ``moe.router``, ``mlp.experts.E.*`` -> ``moe.experts.E.*``, ``mlp.shared_expert*`` -> shared expert;
+* norms: the engine stores every RMSNorm weight zero-centred (scale = 1 + w); families whose checkpoints hold the plain
+  scale (Llama-style) get ``w - 1``; Gemma-style checkpoints are zero-centred already;
+* embeddings: multiplied by the family's embedding scale; a tied head becomes its own (unscaled) ``lm_head`` tensor.
+
+``export_hf_weights`` is the inverse (used by the round-trip test and for handing weights to other tools)
+(reference: src/model/container.cpp:92-491 name tables, src/convert/main.cpp import paths).
+"""
+from __future__ import annotations
+
+import json
+import math
+from typing import Dict
+
+import torch
+
+from ..config import ModelConfig
+
+
+def config_from_hf(text: str) -> ModelConfig:
+    d = json.loads(text)
+    t = d.get("text_config", d)
+    mt = (t.get("model_type") or d.get("model_type") or "").lower()
+    H, L = t["hidden_size"], t["num_hidden_layers"]
+    heads = t["num_attention_heads"]
+    common = dict(hidden_size=H, num_hidden_layers=L, num_attention_heads=heads,
+                  num_key_value_heads=t.get("num_key_value_heads", heads), head_dim=t.get("head_dim", H // heads),
+                  intermediate_size=t.get("intermediate_size", 0), rms_norm_eps=t.get("rms_norm_eps", 1e-6),
+                  vocab_size=t["vocab_size"], tie_word_embeddings=bool(t.get("tie_word_embeddings", d.get("tie_word_embeddings", False))),
+                  max_position_embeddings=t.get("max_position_embeddings", 262144))
+    if "llama" in mt or "nanbeige" in mt or "mistral" in mt:
+        cfg = ModelConfig(arch="llama", layer_types=["full_attention"] * L, attn_output_gate=False, qk_norm=False,
+                          norm_zero_centered=False, partial_rotary_factor=1.0, rope_theta=t.get("rope_theta", 5.0e5),
+                          mtp_num_hidden_layers=0, **common)
+    elif "gemma" in mt:
+        pattern = t.get("sliding_window_pattern", 6)
+        cfg = ModelConfig(arch="gemma", layer_types=["full_attention"] * L, attn_output_gate=False, qk_norm=True,
+                          partial_rotary_factor=1.0, rope_theta=t.get("rope_theta", 1.0e6), mtp_num_hidden_layers=0,
+                          sandwich_norm=True, mlp_act="gelu_tanh", sliding_window=t.get("sliding_window", 1024),
+                          sliding_global_every=pattern, rope_local_theta=t.get("rope_local_base_freq", 1.0e4),
+                          embed_scale=math.sqrt(H), **{**common, "tie_word_embeddings": True})
+    else:
+        interval = int(t.get("full_attention_interval", 4))
+        types = t.get("layer_types") or ["full_attention" if (i + 1) % interval == 0 else "linear_attention" for i in range(L)]
+        rope = t.get("rope_parameters") or {}
+        cfg = ModelConfig(arch="qwen_hybrid_moe" if t.get("num_experts", 0) else "qwen_hybrid", layer_types=list(types),
+                          attn_output_gate=bool(t.get("attn_output_gate", True)),
+                          partial_rotary_factor=t.get("partial_rotary_factor", rope.get("partial_rotary_factor", 0.25)),
+                          rope_theta=t.get("rope_theta", rope.get("rope_theta", 1.0e7)),
+                          linear_num_key_heads=t.get("linear_num_key_heads", 0), linear_num_value_heads=t.get("linear_num_value_heads", 0),
+                          linear_key_head_dim=t.get("linear_key_head_dim", 0), linear_value_head_dim=t.get("linear_value_head_dim", 0),
+                          linear_conv_kernel_dim=t.get("linear_conv_kernel_dim", 4),
+                          mtp_num_hidden_layers=t.get("mtp_num_hidden_layers", 0), num_experts=t.get("num_experts", 0),
+                          num_experts_per_tok=t.get("num_experts_per_tok", 0), moe_intermediate_size=t.get("moe_intermediate_size", 0),
+                          shared_expert_intermediate_size=t.get("shared_expert_intermediate_size", 0),
+                          norm_topk_prob=bool(t.get("norm_topk_prob", True)), **common)
+    cfg.validate()
+    return cfg
+
+
+def _unpack_qkvz(cfg: ModelConfig, qkvz: torch.Tensor, ba: torch.Tensor):
+    Hk, Hv, Dk, Dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    g = Hv // Hk
+    K = qkvz.shape[1]
+    per = 2 * Dk + 2 * g * Dv
+    x = qkvz.view(Hk, per, K)
+    q, k = x[:, :Dk], x[:, Dk:2 * Dk]
+    v, z = x[:, 2 * Dk:2 * Dk + g * Dv], x[:, 2 * Dk + g * Dv:]
+    qkv = torch.cat([q.reshape(Hk * Dk, K), k.reshape(Hk * Dk, K), v.reshape(Hv * Dv, K)], 0)
+    y = ba.view(Hk, 2 * g, K)
+    b, a = y[:, :g].reshape(Hv, K), y[:, g:].reshape(Hv, K)
+    return qkv.contiguous(), z.reshape(Hv * Dv, K).contiguous(), a.contiguous(), b.contiguous()
+
+
+def _pack_qkvz(cfg: ModelConfig, qkv: torch.Tensor, z: torch.Tensor, a: torch.Tensor, b: torch.Tensor):
+    Hk, Hv, Dk, Dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+    g = Hv // Hk
+    K = qkv.shape[1]
+    q = qkv[:Hk * Dk].view(Hk, Dk, K)
+    k = qkv[Hk * Dk:2 * Hk * Dk].view(Hk, Dk, K)
+    v = qkv[2 * Hk * Dk:].view(Hk, g * Dv, K)
+    zz = z.view(Hk, g * Dv, K)
+    qkvz = torch.cat([q, k, v, zz], 1).reshape(-1, K)
+    ba = torch.cat([b.view(Hk, g, K), a.view(Hk, g, K)], 1).reshape(-1, K)
+    return qkvz.contiguous(), ba.contiguous()
+
+
+def _norm_in(cfg: ModelConfig, w: torch.Tensor) -> torch.Tensor:
+    return w.float() if cfg.norm_zero_centered else w.float() - 1.0
+
+
+def _norm_out(cfg: ModelConfig, w: torch.Tensor) -> torch.Tensor:
+    return w.float() if cfg.norm_zero_centered else w.float() + 1.0
+
+
+def _layer_norm_names(cfg: ModelConfig):
+    """(internal name, HF name) of the per-layer RMSNorms."""
+    if cfg.sandwich_norm:       # HF Gemma: post_attention_layernorm is the norm of the attention OUTPUT
+        return [("input_layernorm", "input_layernorm"), ("post_attn_out_norm", "post_attention_layernorm"),
+                ("post_attention_layernorm", "pre_feedforward_layernorm"), ("post_mlp_out_norm", "post_feedforward_layernorm")]
+    return [("input_layernorm", "input_layernorm"), ("post_attention_layernorm", "post_attention_layernorm")]
+
+
+def import_hf_weights(cfg: ModelConfig, hf: Dict[str, torch.Tensor], prefix: str = "model.") -> Dict[str, torch.Tensor]:
+    """HF-named tensors -> the engine's fp32 weight set (what ``quantize_weight_set`` and the CPU oracle take)."""
+    def get(name: str) -> torch.Tensor:
+        for pre in (prefix, "model.language_model.", "language_model.model.", ""):
+            if pre + name in hf:
+                return hf[pre + name].float()
+        raise KeyError(f"checkpoint has no tensor {prefix}{name}")
+
+    def has(name: str) -> bool:
+        return any(pre + name in hf for pre in (prefix, "model.language_model.", "language_model.model.", ""))
+
+    def gate_up(base: str) -> torch.Tensor:
+        return torch.cat([get(base + "gate_proj.weight"), get(base + "up_proj.weight")], 0).contiguous()
+
+    out: Dict[str, torch.Tensor] = {}
+    emb = get("embed_tokens.weight")
+    out["text.embed_tokens"] = emb * cfg.embed_scale
+    out["text.final_norm"] = _norm_in(cfg, get("norm.weight"))
+    out["lm_head"] = hf["lm_head.weight"].float() if "lm_head.weight" in hf else emb.clone()
+    for i in range(cfg.num_hidden_layers):
+        p, s = f"text.layers.{i}.", f"layers.{i}."
+        for mine, theirs in _layer_norm_names(cfg):
+            out[p + mine] = _norm_in(cfg, get(s + theirs + ".weight"))
+        if cfg.is_attention_layer(i):
+            a = s + "self_attn."
+            out[p + "attn.qg"] = get(a + "q_proj.weight")
+            out[p + "attn.k"], out[p + "attn.v"], out[p + "attn.o"] = get(a + "k_proj.weight"), get(a + "v_proj.weight"), get(a + "o_proj.weight")
+            if cfg.qk_norm:
+                out[p + "attn.q_norm"] = _norm_in(cfg, get(a + "q_norm.weight"))
+                out[p + "attn.k_norm"] = _norm_in(cfg, get(a + "k_norm.weight"))
+            out[p + "attn.k_descale"] = torch.ones(cfg.num_key_value_heads)
+            out[p + "attn.v_descale"] = torch.ones(cfg.num_key_value_heads)
+        else:
+            g = s + "linear_attn."
+            if has(g + "in_proj_qkvz.weight"):
+                qkv, z, a_, b_ = _unpack_qkvz(cfg, get(g + "in_proj_qkvz.weight"), get(g + "in_proj_ba.weight"))
+            else:
+                qkv, z = get(g + "in_proj_qkv.weight"), get(g + "in_proj_z.weight")
+                a_, b_ = get(g + "in_proj_a.weight"), get(g + "in_proj_b.weight")
+            out[p + "gdn.in_proj_qkv"], out[p + "gdn.in_proj_z"], out[p + "gdn.in_proj_a"], out[p + "gdn.in_proj_b"] = qkv, z, a_, b_
+            out[p + "gdn.conv1d_weight"] = get(g + "conv1d.weight").reshape(cfg.conv_dim, -1)
+            out[p + "gdn.A_log"], out[p + "gdn.dt_bias"] = get(g + "A_log"), get(g + "dt_bias")
+            out[p + "gdn.norm_weight"] = get(g + "norm.weight")           # the gated norm's weight is a plain scale
+            out[p + "gdn.out_proj"] = get(g + "out_proj.weight")
+        m = s + "mlp."
+        if cfg.is_moe:
+            out[p + "moe.router"] = get(m + "gate.weight")
+            out[p + "moe.shared_gate"] = get(m + "shared_expert_gate.weight").reshape(1, -1)
+            out[p + "moe.shared.gate_up"], out[p + "moe.shared.down"] = gate_up(m + "shared_expert."), get(m + "shared_expert.down_proj.weight")
+            for e in range(cfg.num_experts):
+                out[p + f"moe.experts.{e}.gate_up"] = gate_up(m + f"experts.{e}.")
+                out[p + f"moe.experts.{e}.down"] = get(m + f"experts.{e}.down_proj.weight")
+        else:
+            out[p + "mlp.gate_up"], out[p + "mlp.down"] = gate_up(m), get(m + "down_proj.weight")
+    return out
+
+
+def export_hf_weights(cfg: ModelConfig, w: Dict[str, torch.Tensor], prefix: str = "model.", packed_gdn: bool = True) -> Dict[str, torch.Tensor]:
+    """The inverse of ``import_hf_weights`` (mtp.* tensors are not part of the HF layout and are dropped)."""
+    hf: Dict[str, torch.Tensor] = {}
+    hf[prefix + "embed_tokens.weight"] = w["text.embed_tokens"].float() / cfg.embed_scale
+    hf[prefix + "norm.weight"] = _norm_out(cfg, w["text.final_norm"])
+    if not cfg.tie_word_embeddings:
+        hf["lm_head.weight"] = w["lm_head"].float()
+    for i in range(cfg.num_hidden_layers):
+        p, s = f"text.layers.{i}.", prefix + f"layers.{i}."
+        for mine, theirs in _layer_norm_names(cfg):
+            hf[s + theirs + ".weight"] = _norm_out(cfg, w[p + mine])
+        if cfg.is_attention_layer(i):
+            a = s + "self_attn."
+            hf[a + "q_proj.weight"], hf[a + "k_proj.weight"] = w[p + "attn.qg"].float(), w[p + "attn.k"].float()
+            hf[a + "v_proj.weight"], hf[a + "o_proj.weight"] = w[p + "attn.v"].float(), w[p + "attn.o"].float()
+            if cfg.qk_norm:
+                hf[a + "q_norm.weight"], hf[a + "k_norm.weight"] = _norm_out(cfg, w[p + "attn.q_norm"]), _norm_out(cfg, w[p + "attn.k_norm"])
+        else:
+            g = s + "linear_attn."
+            if packed_gdn:
+                hf[g + "in_proj_qkvz.weight"], hf[g + "in_proj_ba.weight"] = _pack_qkvz(
+                    cfg, w[p + "gdn.in_proj_qkv"].float(), w[p + "gdn.in_proj_z"].float(), w[p + "gdn.in_proj_a"].float(), w[p + "gdn.in_proj_b"].float())
+            else:
+                for n in ("in_proj_qkv", "in_proj_z", "in_proj_a", "in_proj_b"):
+                    hf[g + n + ".weight"] = w[p + "gdn." + n].float()
+            hf[g + "conv1d.weight"] = w[p + "gdn.conv1d_weight"].float().reshape(cfg.conv_dim, 1, -1)
+            hf[g + "A_log"], hf[g + "dt_bias"] = w[p + "gdn.A_log"].float(), w[p + "gdn.dt_bias"].float()
+            hf[g + "norm.weight"], hf[g + "out_proj.weight"] = w[p + "gdn.norm_weight"].float(), w[p + "gdn.out_proj"].float()
+        m = s + "mlp."
+
+        def split(name: str, base: str):
+            gu = w[p + name + ".gate_up"].float()
+            hf[base + "gate_proj.weight"], hf[base + "up_proj.weight"] = gu[:gu.shape[0] // 2].contiguous(), gu[gu.shape[0] // 2:].contiguous()
+            hf[base + "down_proj.weight"] = w[p + name + ".down"].float()
+
+        if cfg.is_moe:
+            hf[m + "gate.weight"] = w[p + "moe.router"].float()
+            hf[m + "shared_expert_gate.weight"] = w[p + "moe.shared_gate"].float()
+            split("moe.shared", m + "shared_expert.")
+            for e in range(cfg.num_experts):
+                split(f"moe.experts.{e}", m + f"experts.{e}.")
+        else:
+            split("mlp", m)
+    return hf

@@ -153,3 +153,45 @@ def test_kv_calibration_and_error_compensated_w4a16():
     # same layout: the packed tensors have the packer's shapes and decode with the packer's rule
     assert q_gptq.wq.shape == q_rtn.wq.shape and q_gptq.wsz.shape == q_rtn.wsz.shape
     assert (w4a16.dequantize(q_gptq) - Wt).abs().max().item() < 0.05
+
+
+def test_hf_checkpoint_import_round_trips_every_family():
+    """Internal weights -> HF names and layouts (packed GDN projections, split gate/up, plain-scale norms, tied head,
+    unscaled embeddings) -> back: identical tensors, and the oracle gives identical logits on the imported set."""
+    import json
+    import torch
+    from r4dx_b200.config import tiny_gemma_config, tiny_hybrid_config, tiny_llama_config, tiny_moe_config
+    from r4dx_b200.models.oracle import OracleModel, init_weights
+    from r4dx_b200.quant import hf_import as HI
+    for make, packed in ((tiny_hybrid_config, True), (tiny_hybrid_config, False), (tiny_llama_config, True),
+                         (tiny_gemma_config, True), (tiny_moe_config, True)):
+        cfg = make()
+        w = init_weights(cfg, 2)
+        if cfg.tie_word_embeddings:
+            w["lm_head"] = (w["text.embed_tokens"] / cfg.embed_scale).clone()
+        hf = HI.export_hf_weights(cfg, w, packed_gdn=packed)
+        assert "model.layers.0.mlp.gate_proj.weight" in hf or "model.layers.0.mlp.experts.0.gate_proj.weight" in hf
+        if not cfg.norm_zero_centered:
+            assert torch.allclose(hf["model.norm.weight"], w["text.final_norm"] + 1.0)
+        back = HI.import_hf_weights(cfg, hf)
+        for k, v in w.items():
+            if k.startswith("mtp."):
+                continue
+            assert torch.allclose(back[k].float(), v.float(), atol=1e-6), (make.__name__, k)
+        ids = torch.randint(0, cfg.vocab_size, (9,), generator=torch.Generator().manual_seed(0))
+        la, _ = OracleModel(cfg, {k: v for k, v in w.items() if not k.startswith("mtp.")}).forward(ids)
+        lb, _ = OracleModel(cfg, back).forward(ids)
+        assert torch.allclose(la, lb, atol=1e-4)
+    # config.json of the three dense families
+    c = HI.config_from_hf(json.dumps({"model_type": "llama", "hidden_size": 256, "num_hidden_layers": 2, "num_attention_heads": 4,
+                                      "num_key_value_heads": 2, "intermediate_size": 512, "vocab_size": 1000, "rope_theta": 10000.0}))
+    assert c.arch == "llama" and not c.qk_norm and c.head_dim == 64 and c.rotary_dim == 64 and not c.norm_zero_centered
+    c = HI.config_from_hf(json.dumps({"model_type": "gemma3_text", "hidden_size": 256, "num_hidden_layers": 6, "num_attention_heads": 4,
+                                      "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 512, "vocab_size": 1000,
+                                      "sliding_window": 128, "sliding_window_pattern": 3}))
+    assert c.sandwich_norm and c.mlp_act == "gelu_tanh" and [c.layer_window(i) for i in range(3)] == [128, 128, 0] and c.embed_scale == 16.0
+    c = HI.config_from_hf(json.dumps({"text_config": {"model_type": "qwen3_next", "hidden_size": 256, "num_hidden_layers": 4,
+                                                      "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+                                                      "intermediate_size": 512, "vocab_size": 1000, "linear_num_key_heads": 2,
+                                                      "linear_num_value_heads": 4, "linear_key_head_dim": 64, "linear_value_head_dim": 64}}))
+    assert c.layer_types == ["linear_attention"] * 3 + ["full_attention"] and c.conv_dim == 2 * 128 + 256
