@@ -238,3 +238,25 @@ def test_image_parts_become_placeholder_tokens_and_embedding_overrides():
         assert "r4dxb_requests_total" in m
     finally:
         srv.stop(); eng.shutdown()
+
+
+def test_paged_kv_allocator_tables_exhaustion_and_reuse():
+    import torch
+    from r4dx_b200.models.batch import PagedKvAllocator
+    al = PagedKvAllocator(num_blocks=6, slots=3, max_blocks_per_slot=4, device="cpu")
+    al.ensure(0, 17)                       # 2 blocks of 16 tokens
+    al.ensure(1, 40)                       # 3 blocks
+    assert al.blocks_in_use() == 5
+    t0, t1 = al.tables[0, :2].tolist(), al.tables[1, :3].tolist()
+    assert len(set(t0 + t1)) == 5 and all(0 <= b < 6 for b in t0 + t1)
+    al.ensure(0, 30)                       # still 2 blocks: nothing new
+    assert al.blocks_in_use() == 5 and al.tables[0, :2].tolist() == t0
+    with pytest.raises(MemoryError):
+        al.ensure(2, 33)                   # needs 3, one is free; the failed call takes nothing
+    assert al.blocks_in_use() == 5
+    with pytest.raises(ValueError):
+        al.ensure(0, 16 * 4 + 1)           # beyond the slot's table
+    al.release(1)
+    assert al.blocks_in_use() == 2
+    al.ensure(2, 48)                       # the released blocks serve another slot
+    assert set(al.tables[2, :3].tolist()) <= set(t1) | {b for b in range(6) if b not in t0 + t1}
