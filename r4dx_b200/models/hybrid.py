@@ -615,6 +615,28 @@ class HybridModel:
         self.pos += n
         return res[1:1 + n]
 
+    def window_logits(self, anchor: int, drafts: List[int]) -> torch.Tensor:
+        """Runs the window [anchor, d1..dm] and returns its fp32 logits rows WITHOUT committing anything; follow with
+        ``commit_window(n)`` (sampled speculation resolves acceptance on the host, one draw per row)."""
+        m = len(drafts)
+        if m + 1 > MAX_ROWS:
+            raise ValueError("speculative window too long")
+        ids = torch.tensor([anchor] + list(drafts), dtype=torch.int32)
+        T = self._stage(ids, self.pos)
+        if self.pos + T > self.max_ctx:
+            raise ValueError("context overflow")
+        self.buf.n_replay.fill_(self.pending_rows)
+        self.forward_rows(T, True)
+        self._window_rows = T
+        return self.buf.logits[:T]
+
+    def commit_window(self, n: int) -> None:
+        if not 1 <= n <= getattr(self, "_window_rows", 0):
+            raise ValueError("commit_window outside the last window")
+        self.pending_rows = n
+        self.pos += n
+        self._window_rows = 0
+
     # ---- prompt checkpoint ---------------------------------------------------------------------------
     def save_checkpoint(self) -> dict:
         """Snapshot of the recurrent state (KV needs no copy: it is overwritten by position)

@@ -65,6 +65,43 @@ class TextModel:
         """Speculative round (drafter chosen at load): emitted tokens, at least one."""
         return [self.decode_step_greedy(token)]
 
+    # ---- sampled speculation: sample-and-match -------------------------------------------------------------
+    def draft_tokens(self, token: int, k: int) -> List[int]:
+        """Up to k proposed continuations of ``token`` (no drafter: none)."""
+        return []
+
+    def window_logits(self, token: int, drafts: Sequence[int]) -> torch.Tensor:
+        """Logits rows [1 + len(drafts), vocab] of the window [token, drafts...]; commits nothing."""
+        raise NotImplementedError
+
+    def commit_window(self, token: int, drafts: Sequence[int], n: int) -> None:
+        """Commits the first n rows of the window that ``window_logits`` just ran."""
+        raise NotImplementedError
+
+    def decode_step_spec_sampled(self, token: int, k: int, params: SampleParams, rng: Rng,
+                                 seen: Optional[Sequence[int]] = None) -> List[int]:
+        """One speculative round under sampling.  Row i of the verify window is the target distribution after
+        [.., token, d1..di]; one token is drawn per row with the request's generator and a draft is accepted only if the
+        draw equals it - rejection sampling for a point-mass proposal, one draw per emitted token, so the stream is the
+        same as plain sampled decode with the same seed (reference: src/model/model.h:559-581, docs/sampling.md:417-460)."""
+        drafts = list(self.draft_tokens(token, k))
+        if not drafts:
+            return [self.decode_step_sampled(token, params, rng, seen)]
+        rows = self.window_logits(token, drafts).float().cpu()
+        hist = list(seen) if seen is not None else []
+        emitted: List[int] = []
+        for i in range(rows.shape[0]):
+            lg = rows[i].clone()
+            if params.repetition_penalty != 1.0 and hist:
+                apply_repetition_penalty(lg, hist, params.repetition_penalty)
+            t = int(torch.argmax(lg)) if params.greedy else sample_canonical(lg, params, rng.next())
+            emitted.append(t)
+            hist.append(t)
+            if i >= len(drafts) or t != drafts[i]:
+                break
+        self.commit_window(token, drafts, len(emitted))
+        return emitted
+
 
 class LocalTextModel(TextModel):
     def __init__(self, model, model_id: str = "r4dx-b200", global_config: Optional[ModelConfig] = None, drafter=None,
@@ -153,6 +190,19 @@ class LocalTextModel(TextModel):
         self.drafter.after_verify(token, drafts, emitted)
         return emitted
 
+    def draft_tokens(self, token: int, k: int) -> List[int]:
+        return self.drafter.draft(token, k) if self.drafter is not None else []
+
+    def window_logits(self, token: int, drafts: Sequence[int]) -> torch.Tensor:
+        self._graph_active = False
+        return self.m.window_logits(token, list(drafts))
+
+    def commit_window(self, token: int, drafts: Sequence[int], n: int) -> None:
+        emitted_like = list(drafts[:n - 1]) + [0]          # the drafter only needs to know how many drafts were accepted
+        self.m.commit_window(n)
+        if self.drafter is not None:
+            self.drafter.after_verify(token, list(drafts), emitted_like)
+
 
 class FakeTextModel(TextModel):
     """Deterministic CPU model: the logits depend only on the token history."""
@@ -221,3 +271,23 @@ class FakeTextModel(TextModel):
 
     def decode_step_greedy(self, token: int) -> int:
         return int(torch.argmax(self.decode_step(token)))
+
+    # speculation hooks: ``draft_fn(history, token, k)`` plays the drafter
+    draft_fn = None
+
+    def draft_tokens(self, token: int, k: int) -> List[int]:
+        return list(self.draft_fn(list(self.history), token, k)) if self.draft_fn else []
+
+    def window_logits(self, token: int, drafts: Sequence[int]) -> torch.Tensor:
+        self._tick()
+        keep = list(self.history)
+        rows = []
+        for t in [token] + list(drafts):
+            self.history.append(t)
+            rows.append(self._logits())
+        self.history = keep
+        self._window = [token] + list(drafts)
+        return torch.stack(rows)
+
+    def commit_window(self, token: int, drafts: Sequence[int], n: int) -> None:
+        self.history += self._window[:n]

@@ -202,8 +202,12 @@ class Engine:
                 break
             if not pending:
                 fed.append(tok)
-                if req.spec_k > 0 and req.params.greedy:
+                if req.spec_k > 0 and req.params.greedy and req.params.repetition_penalty == 1.0:
                     emitted = m.decode_step_spec_greedy(tok, req.spec_k)
+                    fed += emitted[:-1]
+                    pending = list(emitted)
+                elif req.spec_k > 0:
+                    emitted = m.decode_step_spec_sampled(tok, req.spec_k, req.params, rng, fed)
                     fed += emitted[:-1]
                     pending = list(emitted)
                 elif req.params.greedy and req.params.repetition_penalty == 1.0:

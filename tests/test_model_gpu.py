@@ -155,6 +155,39 @@ def test_mtp_speculation_equals_plain_greedy():
     assert tm.drafter.head.pos == main.pos - 1
 
 
+def test_mtp_sampled_speculation_equals_plain_sampled_decode():
+    """Sample-and-match: one draw per emitted token from the window's own logits rows, so with one seed the speculative
+    stream is the plain sampled stream (the window rows and the single-row step run the same kernels row by row)."""
+    from r4dx_b200.models.hybrid import HybridModel
+    from r4dx_b200.models.mtp import MtpDrafter
+    from r4dx_b200.models.oracle import init_weights
+    from r4dx_b200.quant.weights import quantize_weight_set
+    from r4dx_b200.runtime.sampler import Rng, SampleParams
+    from r4dx_b200.runtime.text_model import LocalTextModel
+    cfg = tiny_hybrid_config()
+    q = _to_dev(quantize_weight_set(cfg, init_weights(cfg, 0, with_mtp=True)))
+    ids = torch.randint(0, cfg.vocab_size, (29,), generator=torch.Generator().manual_seed(3)).to(torch.int32).tolist()
+    params = SampleParams(temperature=0.7, top_k=4, seed=11)
+
+    def run(spec):
+        main = HybridModel(cfg, q, max_ctx=256)
+        tm = LocalTextModel(main, drafter=MtpDrafter(main, q) if spec else None)
+        rng = Rng(params.seed)
+        tm.prefill(ids)
+        out = [tm.sample_from_last(params, rng, ids)]
+        while len(out) < 18:
+            if spec:
+                out += tm.decode_step_spec_sampled(out[-1], 3, params, rng, ids + out[:-1])
+            else:
+                out.append(tm.decode_step_sampled(out[-1], params, rng, ids + out[:-1]))
+        return out[:18], tm
+
+    plain, _ = run(False)
+    spec, tm = run(True)
+    assert spec == plain
+    assert tm.drafter.head.pos == tm.m.pos - 1
+
+
 def test_moe_model_matches_oracle():
     from r4dx_b200.config import tiny_moe_config
     from r4dx_b200.models.hybrid import HybridModel

@@ -260,3 +260,34 @@ def test_paged_kv_allocator_tables_exhaustion_and_reuse():
     assert al.blocks_in_use() == 2
     al.ensure(2, 48)                       # the released blocks serve another slot
     assert set(al.tables[2, :3].tolist()) <= set(t1) | {b for b in range(6) if b not in t0 + t1}
+
+
+def test_sampled_speculation_emits_the_same_stream_as_plain_sampled_decode():
+    """Sample-and-match: with the same seed, the speculative engine path produces exactly the plain sampled stream,
+    whatever the drafter proposes (an oracle-like drafter, a wrong one, none)."""
+    def run(draft_fn, spec_k):
+        model = FakeTextModel(vocab=64)
+        model.draft_fn = draft_fn
+        eng = Engine(model, ByteTokenizer(300))
+        req = GenRequest(prompt_ids=[5, 9, 11], max_tokens=24, params=SampleParams(temperature=0.9, top_k=12, seed=7,
+                                                                                  repetition_penalty=1.1), spec_k=spec_k)
+        r = eng.generate(req, timeout=20)
+        eng.shutdown()
+        assert r.error is None, r.error
+        return r.token_ids, model
+
+    plain, _ = run(None, 0)
+
+    def good(history, token, k):
+        # proposes the plain stream's own continuation where it knows it (so drafts are accepted), junk elsewhere
+        seq = [5, 9, 11] + plain
+        i = len(history) + 1
+        return [seq[j] if j < len(seq) else 1 for j in range(i, i + k)]
+
+    def bad(history, token, k):
+        return [63] * k
+
+    for fn in (good, bad):
+        toks, model = run(fn, 3)
+        assert toks == plain, (fn.__name__, toks, plain)
+        assert model.history[:3 + len(plain) - 1] == ([5, 9, 11] + plain)[:3 + len(plain) - 1]
