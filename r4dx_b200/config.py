@@ -19,7 +19,7 @@ class ModelConfig:
     arch: str = "qwen_hybrid"          # qwen_hybrid | qwen_hybrid_moe | llama
     hidden_size: int = 0
     num_hidden_layers: int = 0
-    layer_types: List[str] = field(default_factory=list)   # "linear_attention" | "full_attention"
+    layer_types: List[str] = field(default_factory=list)   # "linear_attention" | "full_attention" | "conv"
     num_attention_heads: int = 0
     num_key_value_heads: int = 0
     head_dim: int = 0
@@ -54,6 +54,12 @@ class ModelConfig:
     moe_intermediate_size: int = 0
     shared_expert_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    moe_router: str = "softmax"        # "softmax" | "sigmoid" (selection by sigmoid + per-expert bias, unbiased weights)
+    moe_expert_bias: bool = False      # sigmoid router: a learned per-expert bias moves the selection only
+    routed_scaling_factor: float = 1.0
+    num_dense_layers: int = 0          # the first layers keep a dense gated MLP in a MoE model
+    # short-conv layers ("conv" in layer_types): y = C * causal_fir(B * x), taps per channel
+    short_conv_taps: int = 3
     # tensor parallel view
     tp_world: int = 1
     tp_rank: int = 0
@@ -109,6 +115,16 @@ class ModelConfig:
     def is_moe(self) -> bool:
         return self.num_experts > 0
 
+    def layer_is_moe(self, i: int) -> bool:
+        return self.num_experts > 0 and i >= self.num_dense_layers
+
+    def is_conv_layer(self, i: int) -> bool:
+        return self.layer_types[i] == "conv"
+
+    @property
+    def has_conv_layers(self) -> bool:
+        return any(t == "conv" for t in self.layer_types)
+
     def layer_window(self, i: int) -> int:
         """Sliding-window length of layer ``i`` (0 = global attention)."""
         if self.sliding_window <= 0 or (i + 1) % self.sliding_global_every == 0:
@@ -150,6 +166,8 @@ class ModelConfig:
             raise ValueError("shard() must be called on the global config")
         if world == 1:
             return dataclasses.replace(self)
+        if self.has_conv_layers:
+            raise NotImplementedError("tensor-parallel sharding of short-conv layers")
         c = dataclasses.replace(self, tp_world=world, tp_rank=rank)
 
         def div(v: int, what: str) -> int:
@@ -278,6 +296,31 @@ def tiny_gemma_config() -> ModelConfig:
     c = gemma_config(hidden=256, layers=4, heads=4, kv_heads=2, head_dim=64, intermediate=512, vocab=4096, window=24)
     c.sliding_global_every = 2
     return c
+
+
+def lfm2_moe_config(hidden: int = 2048, layers: int = 40, heads: int = 32, kv_heads: int = 8, head_dim: int = 64,
+                    intermediate: int = 11776, experts: int = 64, top_k: int = 4, moe_intermediate: int = 1536,
+                    dense_layers: int = 2, vocab: int = 128000, attention_layers=None) -> ModelConfig:
+    """Short-conv + attention MoE decoder (defaults: the 24B-total / 2B-active geometry): most layers are gated short
+    convolutions, every fourth one (i % 4 == 2) is grouped-query attention (head_dim 64, q/k norm, full rope); the first
+    layers keep a dense SwiGLU MLP, the rest route over sigmoid-scored experts with a selection bias and no shared
+    expert (reference: docs/lfm2-plan.md:12-57)."""
+    if attention_layers is None:
+        attention_layers = [i for i in range(layers) if i % 4 == 2]
+    types = ["full_attention" if i in set(attention_layers) else "conv" for i in range(layers)]
+    return ModelConfig(
+        arch="lfm2_moe", hidden_size=hidden, num_hidden_layers=layers, layer_types=types,
+        num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, attn_output_gate=False, qk_norm=True,
+        norm_zero_centered=False, intermediate_size=intermediate, partial_rotary_factor=1.0, rope_theta=1.0e6,
+        vocab_size=vocab, tie_word_embeddings=True, mtp_num_hidden_layers=0, num_experts=experts,
+        num_experts_per_tok=top_k, moe_intermediate_size=moe_intermediate, shared_expert_intermediate_size=0,
+        norm_topk_prob=True, moe_router="sigmoid", moe_expert_bias=True, routed_scaling_factor=1.0,
+        num_dense_layers=dense_layers, short_conv_taps=3, rms_norm_eps=1e-5)
+
+
+def tiny_lfm2_config() -> ModelConfig:
+    return lfm2_moe_config(hidden=256, layers=5, heads=4, kv_heads=2, head_dim=64, intermediate=512, experts=8, top_k=2,
+                           moe_intermediate=128, dense_layers=1, vocab=4096, attention_layers=(2, 4))
 
 
 def tiny_llama_config() -> ModelConfig:

@@ -124,7 +124,7 @@ class HybridModel:
         # fused [a; b] gate projection per GDN layer
         self.ab_w: Dict[int, torch.Tensor] = {}
         for i in range(self.layer_begin, self.layer_end):
-            if not cfg.is_attention_layer(i):
+            if not cfg.is_attention_layer(i) and not cfg.is_conv_layer(i):
                 p = f"text.layers.{i}.gdn."
                 self.ab_w[i] = torch.cat([weights[p + "in_proj_a"], weights[p + "in_proj_b"]], 0).contiguous()
         self._alloc_state(attn_splits)
@@ -132,7 +132,7 @@ class HybridModel:
         if cfg.is_moe:
             from .moe import MoeBlock
             er = getattr(comm, "expert_range", None) if comm is not None else None
-            for i in range(self.layer_begin, self.layer_end):
+            for i in range(max(self.layer_begin, cfg.num_dense_layers), self.layer_end):
                 self.moe[i] = MoeBlock(cfg, weights, i, self.device, MAX_ROWS, *(er or (0, cfg.num_experts)))
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.pos = 0                           # host mirror of the next position
@@ -155,6 +155,8 @@ class HybridModel:
         for i in range(self.layer_begin, self.layer_end):
             if cfg.is_attention_layer(i):
                 self.kv[i] = torch.zeros(nblk, Hkv, 2, KV_BLOCK, D, dtype=torch.uint8, device=dev)
+            elif cfg.is_conv_layer(i):
+                self.ring[i] = torch.zeros(32, H, dtype=BF, device=dev)             # B * x rows keyed by position & 31
             else:
                 self.gdn_state[i] = torch.zeros(Hv, Dg, Dg, dtype=torch.float32, device=dev)
                 self.ring[i] = torch.zeros(CONV_RING, cfg.conv_dim, dtype=BF, device=dev)
@@ -171,8 +173,8 @@ class HybridModel:
         self.buf = StepBuffers(
             ids=e(R, dtype=torch.int32), positions=e(R, dtype=torch.int32), n_replay=e(1, dtype=torch.int32),
             next_ids=e(R, dtype=torch.int32), next_vals=e(R, dtype=torch.float32),
-            x=e(R, H), h=e(R, H), mixed=e(R, cfg.conv_dim), z=e(R, cfg.value_dim),
-            ab=e(R, 2 * Hv, dtype=torch.float32), core=e(R, max(cfg.value_dim, cfg.q_dim)),
+            x=e(R, H), h=e(R, H), mixed=e(R, max(cfg.conv_dim, 3 * H if cfg.has_conv_layers else 0)), z=e(R, cfg.value_dim),
+            ab=e(R, 2 * Hv, dtype=torch.float32), core=e(R, max(cfg.value_dim, cfg.q_dim, H if cfg.has_conv_layers else 0)),
             qg=e(R, cfg.q_proj_dim), k=e(R, cfg.kv_dim), v=e(R, cfg.kv_dim), q=e(R, cfg.q_dim),
             gate_up=e(R, 2 * max(cfg.intermediate_size, 1)), act=e(R, max(cfg.intermediate_size, 1)),
             logits=e(R, V, dtype=torch.float32), argmax_scratch=e(2 * R * 256, dtype=torch.float32),
@@ -241,6 +243,18 @@ class HybridModel:
         core = b.core.view(-1)[:T * cfg.value_dim].view(T, cfg.value_dim)
         self._row_parallel(self.lin[p + "out_proj"], core, T)
 
+    def _conv_layer(self, i: int, T: int) -> None:
+        """Gated short-convolution mixer: in_proj (RMSNorm in its prologue) -> C * fir(B * x) -> out_proj + residual."""
+        cfg, b, w = self.cfg, self.buf, self.w
+        p = f"text.layers.{i}.conv."
+        H = cfg.hidden_size
+        bcx = b.mixed.view(-1)[:T * 3 * H].view(T, 3 * H)
+        self.lin[p + "in_proj"](b.x[:T], out=bcx, prologue=K.PRO_RMSNORM, norm_w=w[f"text.layers.{i}.input_layernorm"],
+                                eps=cfg.rms_norm_eps)
+        core = b.core.view(-1)[:T * H].view(T, H)
+        K.short_conv(bcx, w[p + "weight"], self.ring[i], b.positions, core, T)
+        self._row_parallel(self.lin[p + "out_proj"], core, T)
+
     def _attn_layer(self, i: int, T: int) -> None:
         cfg, b, w = self.cfg, self.buf, self.w
         p = f"text.layers.{i}.attn."
@@ -263,7 +277,7 @@ class HybridModel:
 
     def _mlp(self, i: int, T: int) -> None:
         cfg, b, w = self.cfg, self.buf, self.w
-        if cfg.is_moe:
+        if cfg.layer_is_moe(i):
             K.rmsnorm(b.x[:T], w[f"text.layers.{i}.post_attention_layernorm"], cfg.rms_norm_eps, out=b.h[:T])
             if self.comm is not None and hasattr(self.comm, "moe_forward"):
                 self.comm.moe_forward(self.moe[i], b.h[:T], b.x[:T], T)
@@ -308,6 +322,8 @@ class HybridModel:
             # the two RMSNorms and the SwiGLU of a layer run inside the prologues of the linears
             if cfg.is_attention_layer(i):
                 self._attn_layer(i, T)
+            elif cfg.is_conv_layer(i):
+                self._conv_layer(i, T)
             else:
                 self._gdn_layer(i, T)
             self._mlp(i, T)
@@ -371,13 +387,14 @@ class HybridModel:
         H = cfg.hidden_size
         Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
         kmax = max(H, cfg.value_dim, cfg.q_dim, cfg.intermediate_size)
+        conv_w = 3 * H if cfg.has_conv_layers else 0
         e = lambda *s, dtype=BF: torch.empty(*s, dtype=dtype, device=dev)
         f32 = torch.float32
         # under tensor parallelism the residual stream of a chunk may live in peer-mapped memory (owners push rows into it)
         x_buf = self.comm.alloc_chunk_x(C, H) if hasattr(self.comm, "alloc_chunk_x") else e(C, H)
         cb = dict(C=C, ids=e(C, dtype=torch.int32), positions=e(C, dtype=torch.int32), x=x_buf, h=e(C, H),
-                  xh=e(C * kmax, dtype=torch.float16), mixed=e(C, cfg.conv_dim), z=e(C, cfg.value_dim),
-                  ab=e(C, 2 * Hv, dtype=f32), core=e(C * max(cfg.value_dim, cfg.q_dim)), qg=e(C, cfg.q_proj_dim),
+                  xh=e(C * kmax, dtype=torch.float16), mixed=e(C * max(cfg.conv_dim, conv_w)), z=e(C, cfg.value_dim),
+                  ab=e(C, 2 * Hv, dtype=f32), core=e(C * max(cfg.value_dim, cfg.q_dim, conv_w // 3)), qg=e(C, cfg.q_proj_dim),
                   k=e(C, cfg.kv_dim), v=e(C, cfg.kv_dim), q=e(C, cfg.q_dim), gate_up=e(C, 2 * cfg.intermediate_size),
                   gdn=dict(q=e(C, Hk, Dg, dtype=f32), k=e(C, Hk, Dg, dtype=f32), v=e(C, Hv, Dg, dtype=f32),
                            o=e(C, Hv, Dg, dtype=f32), eg=e(C, Hv, dtype=f32), beta=e(C, Hv, dtype=f32)))
@@ -429,9 +446,16 @@ class HybridModel:
                 K.attn_prefill(q, qg, self.kv[i], self.block_table, w[pa + "k_descale"], w[pa + "v_descale"], core, T,
                                Hq, Hkv, D, pos0, cfg.attn_output_gate, window=cfg.layer_window(i))
                 self._row_parallel_chunk(self.lin[pa + "o"], core, x, cb, post_norm=w.get(p + "post_attn_out_norm"))
+            elif cfg.is_conv_layer(i):
+                pc = p + "conv."
+                bcx = cb["mixed"][:T * 3 * H].view(T, 3 * H)
+                self.lin[pc + "in_proj"].chunk(h, cb["xh"], bcx)
+                core = cb["core"][:T * H].view(T, H)
+                K.short_conv(bcx, w[pc + "weight"], self.ring[i], cb["positions"], core, T)
+                self._row_parallel_chunk(self.lin[pc + "out_proj"], core, x, cb)
             else:
                 pg = p + "gdn."
-                mixed, z, ab = cb["mixed"][:T], cb["z"][:T], cb["ab"][:T]
+                mixed, z, ab = cb["mixed"][:T * cfg.conv_dim].view(T, cfg.conv_dim), cb["z"][:T], cb["ab"][:T]
                 self.lin[pg + "in_proj_qkv"].chunk(h, cb["xh"], mixed)
                 self.lin[pg + "in_proj_z"].chunk(h, cb["xh"], z)
                 K.bf16_gemv(self.ab_w[i], h, out=ab)
@@ -441,7 +465,7 @@ class HybridModel:
                               pos0, cfg.rms_norm_eps)
                 self._row_parallel_chunk(self.lin[pg + "out_proj"], core, x, cb)
             K.rmsnorm(x, w[p + "post_attention_layernorm"], cfg.rms_norm_eps, out=h)
-            if cfg.is_moe:
+            if cfg.layer_is_moe(i):
                 self._moe_chunk(i, h, x, T)
                 continue
             pm = p + "mlp."
@@ -480,7 +504,7 @@ class HybridModel:
                 blk = MoeBlock.__new__(MoeBlock)
                 blk.__dict__.update(first.__dict__)
                 src = self.moe[i]
-                for name in ("gate_up", "down", "router", "shared_gate", "shared_gu", "shared_down", "e_begin", "e_count", "ks_gu", "ks_dn"):
+                for name in ("gate_up", "down", "router", "shared_gate", "shared_gu", "shared_down", "expert_bias", "e_begin", "e_count", "ks_gu", "ks_dn"):
                     setattr(blk, name, getattr(src, name))
             else:
                 blk = MoeBlock(self.cfg, self.w, i, self.device, self._cb["C"], self.moe[i].e_begin, self.moe[i].e_count,

@@ -61,9 +61,11 @@ class MoeBlock:
             self.down = ExpertStack.from_list([weights[p + f"experts.{e}.down"] for e in range(e_begin, e_begin + self.e_count)])
         self.cap = cap                   # rows one expert can take per call when more than `cap` rows are in flight
         self.router = weights[p + "router"]
-        self.shared_gate = weights[p + "shared_gate"]
-        self.shared_gu: TrellisWeight = weights[p + "shared.gate_up"]
-        self.shared_down: TrellisWeight = weights[p + "shared.down"]
+        self.has_shared = cfg.shared_expert_intermediate_size > 0
+        self.shared_gate = weights[p + "shared_gate"] if self.has_shared else None
+        self.shared_gu: Optional[TrellisWeight] = weights[p + "shared.gate_up"] if self.has_shared else None
+        self.shared_down: Optional[TrellisWeight] = weights[p + "shared.down"] if self.has_shared else None
+        self.expert_bias = weights.get(p + "expert_bias")          # sigmoid router only: moves the selection
         self.tmax = tmax
         self.k = cfg.num_experts_per_tok
         H, I = cfg.hidden_size, cfg.moe_intermediate_size
@@ -76,15 +78,19 @@ class MoeBlock:
         self.perm = z(R * k, dtype=torch.int32)
         self.gu_pairs = z(R * k, 2 * I)
         self.y_pairs = z(R * k, H)
-        self.sh_gu = z(R, 2 * cfg.shared_expert_intermediate_size)
-        self.sh_out = z(R, H)
-        self.sh_gate = z(R, 1, dtype=torch.float32)
+        self.sh_gu = z(R, 2 * cfg.shared_expert_intermediate_size) if self.has_shared else None
+        self.sh_out = z(R, H) if self.has_shared else None
+        self.sh_gate = z(R, 1, dtype=torch.float32) if self.has_shared else None
         self.ks_gu = K.pick_ksplit(self.gate_up.N, self.gate_up.K, target_ctas=1)
         self.ks_dn = K.pick_ksplit(self.down.N, self.down.K, target_ctas=1)
 
     def route(self, h: torch.Tensor, T: int) -> None:
         K.bf16_gemv(self.router, h, out=self.logits[:T])
-        K.moe_router(self.logits[:T], self.k, self.cfg.norm_topk_prob, self.ids, self.wts)
+        if self.cfg.moe_router == "sigmoid":
+            K.moe_router_sigmoid(self.logits[:T], self.expert_bias, self.k, self.cfg.norm_topk_prob,
+                                 self.cfg.routed_scaling_factor, self.ids, self.wts)
+        else:
+            K.moe_router(self.logits[:T], self.k, self.cfg.norm_topk_prob, self.ids, self.wts)
         K.moe_plan(self.ids, T * self.k, self.cfg.num_experts, self.e_begin, self.e_count, self.offsets, self.perm)
 
     def experts(self, h: torch.Tensor, T: int, max_rows: Optional[int] = None) -> None:
@@ -101,6 +107,8 @@ class MoeBlock:
                                K.PRO_SILU_MUL, d.E, d.N, d.K, d.kb, self.ks_dn)
 
     def shared(self, h: torch.Tensor, T: int) -> None:
+        if not self.has_shared:
+            return
         if T > 16:
             # many rows: the tensor-core path (input transform + GEMM), SwiGLU fused into the second transform
             xh = K.trellis_input(h[:T], self.shared_gu.suh)
@@ -131,4 +139,4 @@ class MoeBlock:
 
     @property
     def nbytes(self) -> int:
-        return self.gate_up.nbytes + self.down.nbytes + self.shared_gu.nbytes + self.shared_down.nbytes
+        return self.gate_up.nbytes + self.down.nbytes + (self.shared_gu.nbytes + self.shared_down.nbytes if self.has_shared else 0)

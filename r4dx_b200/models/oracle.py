@@ -29,10 +29,13 @@ def linear_names(cfg: ModelConfig) -> List[str]:
         p = f"text.layers.{i}."
         if cfg.is_attention_layer(i):
             names += [p + "attn.qg", p + "attn.k", p + "attn.v", p + "attn.o"]
+        elif cfg.is_conv_layer(i):
+            names += [p + "conv.in_proj", p + "conv.out_proj"]
         else:
             names += [p + "gdn.in_proj_qkv", p + "gdn.in_proj_z", p + "gdn.out_proj"]
-        if cfg.is_moe:
-            names += [p + "moe.shared.gate_up", p + "moe.shared.down"]
+        if cfg.layer_is_moe(i):
+            if cfg.shared_expert_intermediate_size:
+                names += [p + "moe.shared.gate_up", p + "moe.shared.down"]
             for e in range(cfg.num_experts):
                 names += [p + f"moe.experts.{e}.gate_up", p + f"moe.experts.{e}.down"]
         else:
@@ -76,6 +79,10 @@ def init_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02, with_mtp: b
             w[p + "post_mlp_out_norm"] = n(H)
         if cfg.is_attention_layer(i):
             attn_block(p)
+        elif cfg.is_conv_layer(i):
+            w[p + "conv.in_proj"] = n(3 * H, H)
+            w[p + "conv.weight"] = n(H, cfg.short_conv_taps) * (0.5 / std)
+            w[p + "conv.out_proj"] = n(H, H)
         else:
             w[p + "gdn.in_proj_qkv"] = n(cfg.conv_dim, H)
             w[p + "gdn.in_proj_z"] = n(cfg.value_dim, H)
@@ -86,10 +93,13 @@ def init_weights(cfg: ModelConfig, seed: int = 0, std: float = 0.02, with_mtp: b
             w[p + "gdn.dt_bias"] = n(cfg.linear_num_value_heads)
             w[p + "gdn.norm_weight"] = 1.0 + n(cfg.linear_value_head_dim)
             w[p + "gdn.out_proj"] = n(H, cfg.value_dim)
-        if cfg.is_moe:
+        if cfg.layer_is_moe(i):
             w[p + "moe.router"] = n(cfg.num_experts, H)
-            w[p + "moe.shared_gate"] = n(1, H)
-            mlp_block(p, cfg.shared_expert_intermediate_size, "moe.shared")
+            if cfg.moe_expert_bias:
+                w[p + "moe.expert_bias"] = n(cfg.num_experts)
+            if cfg.shared_expert_intermediate_size:
+                w[p + "moe.shared_gate"] = n(1, H)
+                mlp_block(p, cfg.shared_expert_intermediate_size, "moe.shared")
             for e in range(cfg.num_experts):
                 mlp_block(p, cfg.moe_intermediate_size, f"moe.experts.{e}")
         else:
@@ -198,6 +208,17 @@ class OracleModel:
         o = self._r(R.gated_rmsnorm(o, z, w[p + "gdn.norm_weight"], cfg.rms_norm_eps))
         return self._r(self._mm(o.reshape(T, H * Vd), p + "gdn.out_proj"))
 
+    def short_conv(self, p: str, li, x: torch.Tensor, st: OracleState) -> torch.Tensor:
+        """Gated short-convolution mixer: in_proj -> B | C | x, y = C * fir(B * x), out_proj
+        (reference: src/kernels/include/r4dx/kernels/lfm2_kernels.h:14-34)."""
+        w = self.w
+        bcx = self._r(self._mm(x, p + "conv.in_proj"))
+        wt = w[p + "conv.weight"]
+        if self.act_dtype is not None:
+            wt = wt.to(self.act_dtype).float()
+        y, st.conv[li] = R.short_conv(bcx, wt, st.conv.get(li), round_bf16=self.act_dtype is not None)
+        return self._r(self._mm(self._r(y), p + "conv.out_proj"))
+
     def mlp(self, p: str, x: torch.Tensor, name: str = "mlp") -> torch.Tensor:
         w = self.w
         act = R.gelu_mul if self.cfg.mlp_act == "gelu_tanh" else R.silu_mul
@@ -207,7 +228,11 @@ class OracleModel:
     def moe(self, p: str, x: torch.Tensor) -> torch.Tensor:
         cfg, w = self.cfg, self.w
         logits = self._r(x @ w[p + "moe.router"].T)
-        ids, wts = R.moe_route(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
+        if cfg.moe_router == "sigmoid":
+            ids, wts = R.moe_route_sigmoid(logits, w.get(p + "moe.expert_bias"), cfg.num_experts_per_tok, cfg.norm_topk_prob,
+                                           cfg.routed_scaling_factor)
+        else:
+            ids, wts = R.moe_route(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
         out = torch.zeros_like(x)
         for t in range(x.shape[0]):
             # combine in ascending expert id, fp32 accumulate (deterministic order)
@@ -217,8 +242,9 @@ class OracleModel:
                 e = int(ids[t, j])
                 acc = acc + wts[t, j] * self.mlp(p, x[t:t + 1], f"moe.experts.{e}")[0]
             out[t] = acc
-        sg = torch.sigmoid(x @ w[p + "moe.shared_gate"].T)
-        out = out + sg * self.mlp(p, x, "moe.shared")
+        if cfg.shared_expert_intermediate_size:
+            sg = torch.sigmoid(x @ w[p + "moe.shared_gate"].T)
+            out = out + sg * self.mlp(p, x, "moe.shared")
         return self._r(out)
 
     # ---- model -------------------------------------------------------------------------
@@ -234,12 +260,17 @@ class OracleModel:
             if capture_layers and i in capture_layers:
                 captured[i] = x.clone()
             h = self._r(R.rmsnorm_1pw(x, w[p + "input_layernorm"], cfg.rms_norm_eps))
-            a = self.attention(p, i, h, st) if cfg.is_attention_layer(i) else self.gdn(p, i, h, st)
+            if cfg.is_attention_layer(i):
+                a = self.attention(p, i, h, st)
+            elif cfg.is_conv_layer(i):
+                a = self.short_conv(p, i, h, st)
+            else:
+                a = self.gdn(p, i, h, st)
             if cfg.sandwich_norm:
                 a = self._r(R.rmsnorm_1pw(a, w[p + "post_attn_out_norm"], cfg.rms_norm_eps))
             x = self._r(x + a)
             h = self._r(R.rmsnorm_1pw(x, w[p + "post_attention_layernorm"], cfg.rms_norm_eps))
-            m = self.moe(p, h) if cfg.is_moe else self.mlp(p, h)
+            m = self.moe(p, h) if cfg.layer_is_moe(i) else self.mlp(p, h)
             if cfg.sandwich_norm:
                 m = self._r(R.rmsnorm_1pw(m, w[p + "post_mlp_out_norm"], cfg.rms_norm_eps))
             x = self._r(x + m)

@@ -143,6 +143,11 @@ int r4dxb_trellis_gemv_ex(const void* words, const void* suh, const void* svh, c
 
 /* ---- mixture of experts ---------------------------------------------------------------------------- */
 int r4dxb_moe_router(const float* logits, int T, int E, int k, int renorm, int* ids, float* weights, void* stream);
+int r4dxb_moe_router_sigmoid(const float* logits, const float* bias, int T, int E, int k, int renorm, float scale, int* ids,
+                             float* weights, void* stream);
+/* Gated short convolution: bcx [T, 3H] bf16 (B | C | x), w [H, L] bf16, ring [32, H] bf16 keyed by position & 31 */
+int r4dxb_short_conv(const void* bcx, const void* w, void* ring, const int* positions, void* out, int T, int H, int L,
+                     void* stream);
 int r4dxb_moe_plan(const int* ids, int npairs, int E, int e_begin, int e_count, int* offsets, int* perm, void* stream);
 int r4dxb_moe_combine(const void* y_pairs, const int* ids, const float* weights, const void* shared, const float* shared_gate,
                       const void* residual, void* out, int T, int H, int k, void* stream);

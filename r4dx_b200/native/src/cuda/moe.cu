@@ -16,18 +16,25 @@ namespace {
 constexpr int kMaxK = 16;
 
 // one warp per token row
-__global__ void MoeRouterKernel(const float* __restrict__ logits, int T, int E, int k, int renorm,
-                                int* __restrict__ ids, float* __restrict__ weights) {
+//
+// mode 1 is the sigmoid router of the short-conv MoE family (reference:
+// src/kernels/include/r4dx/kernels/lfm2_kernels.h:38-50): s[e] = sigmoid(logit[e]); the SELECTION ranks s[e] + bias[e]
+// (ties to the lower id), the weights are the unbiased s of the selected experts, divided by (their sum + 1e-6) when
+// renorm is set, then multiplied by `scale`.
+__global__ void MoeRouterKernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int k,
+                                int renorm, int mode, float scale, int* __restrict__ ids, float* __restrict__ weights) {
   const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= T) return;
   const float* row = logits + static_cast<size_t>(t) * E;
   float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
-  mx = WarpMax(mx);
   float z = 0.f;
-  for (int e = lane; e < E; e += 32) z += __expf(row[e] - mx);
-  z = WarpSum(z);
+  if (mode == 0) {
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
+    mx = WarpMax(mx);
+    for (int e = lane; e < E; e += 32) z += __expf(row[e] - mx);
+    z = WarpSum(z);
+  }
   // k rounds of arg-max over what is left; a lane keeps a bitmask of its taken entries (E <= 1024 -> 32 per lane)
   uint32_t taken = 0;
   float wsum = 0.f;
@@ -38,7 +45,7 @@ __global__ void MoeRouterKernel(const float* __restrict__ logits, int T, int E, 
     int bi = 0x7fffffff;
     for (int e = lane, s = 0; e < E; e += 32, ++s) {
       if (taken & (1u << s)) continue;
-      const float v = row[e];
+      const float v = mode == 0 ? row[e] : 1.0f / (1.0f + expf(-row[e])) + (bias ? bias[e] : 0.f);
       if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
     }
 #pragma unroll
@@ -48,14 +55,14 @@ __global__ void MoeRouterKernel(const float* __restrict__ logits, int T, int E, 
       if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
     }
     if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-    const float p = __expf(bv - mx) / z;
+    const float p = mode == 0 ? __expf(bv - mx) / z : 1.0f / (1.0f + expf(-row[bi]));
     wv[j] = p;
     wi[j] = bi;
     wsum += p;
   }
   if (lane == 0) {
     for (int j = 0; j < k; ++j) {
-      const float w = renorm ? wv[j] / wsum : wv[j];
+      const float w = mode == 0 ? (renorm ? wv[j] / wsum : wv[j]) : (renorm ? wv[j] / (wsum + 1e-6f) : wv[j]) * scale;
       ids[static_cast<size_t>(t) * k + j] = wi[j];
       weights[static_cast<size_t>(t) * k + j] = __bfloat162float(__float2bfloat16(w));
     }
@@ -135,7 +142,17 @@ extern "C" {
 
 int r4dxb_moe_router(const float* logits, int T, int E, int k, int renorm, int* ids, float* weights, void* stream) {
   if (T < 1 || k < 1 || k > kMaxK || E > 1024 || E < k) return R4DXB_BAD_ARG;
-  MoeRouterKernel<<<(T + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, T, E, k, renorm, ids, weights);
+  MoeRouterKernel<<<(T + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, nullptr, T, E, k, renorm, 0, 1.0f, ids,
+                                                                              weights);
+  return FinishLaunch();
+}
+
+/* Sigmoid router: selection by sigmoid(logit) + bias (bias may be null), weights = unbiased sigmoids / (sum + 1e-6) * scale */
+int r4dxb_moe_router_sigmoid(const float* logits, const float* bias, int T, int E, int k, int renorm, float scale, int* ids,
+                             float* weights, void* stream) {
+  if (T < 1 || k < 1 || k > kMaxK || E > 1024 || E < k) return R4DXB_BAD_ARG;
+  MoeRouterKernel<<<(T + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, bias, T, E, k, renorm, 1, scale, ids,
+                                                                              weights);
   return FinishLaunch();
 }
 

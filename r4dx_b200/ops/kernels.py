@@ -414,6 +414,27 @@ def moe_router(logits: torch.Tensor, k: int, renorm: bool, ids: torch.Tensor, we
     return ids, weights
 
 
+register_cuda_sig("r4dxb_moe_router_sigmoid", _I, [_P, _P, _I, _I, _I, _I, _F, _P, _P, _P])
+register_cuda_sig("r4dxb_short_conv", _I, [_P, _P, _P, _P, _P, _I, _I, _I, _P])
+
+
+def moe_router_sigmoid(logits: torch.Tensor, bias: Optional[torch.Tensor], k: int, renorm: bool, scale: float,
+                       ids: torch.Tensor, weights: torch.Tensor):
+    """Sigmoid router: experts are selected by sigmoid(logit) + bias, weighted by the unbiased sigmoids."""
+    T, E = logits.shape
+    _check(_lib().r4dxb_moe_router_sigmoid(_p(logits), _p(bias), T, E, k, 1 if renorm else 0, float(scale), _p(ids), _p(weights),
+                                           _stream()), "moe_router_sigmoid")
+    return ids, weights
+
+
+def short_conv(bcx: torch.Tensor, w: torch.Tensor, ring: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, T: int):
+    """out[T, H] = C * causal_fir(B * x) over the thirds of bcx [T, 3H]; ``ring`` [32, H] carries the rows before the call."""
+    H, L = w.shape
+    assert bcx.shape[1] == 3 * H and ring.shape == (32, H) and w.dtype == torch.bfloat16 and bcx.is_contiguous()
+    _check(_lib().r4dxb_short_conv(_p(bcx), _p(w), _p(ring), _p(positions), _p(out), T, H, L, _stream()), "short_conv")
+    return out
+
+
 def moe_plan(ids: torch.Tensor, npairs: int, E: int, e_begin: int, e_count: int, offsets: torch.Tensor, perm: torch.Tensor):
     _check(_lib().r4dxb_moe_plan(_p(ids), npairs, E, e_begin, e_count, _p(offsets), _p(perm), _stream()), "moe_plan")
     return offsets, perm

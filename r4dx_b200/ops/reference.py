@@ -252,6 +252,38 @@ def fwht(x: torch.Tensor, block: int = 128, normalize: bool = True) -> torch.Ten
 # ---------------------------------------------------------------------------------------------
 # MoE
 # ---------------------------------------------------------------------------------------------
+def moe_route_sigmoid(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, renorm: bool = True,
+                      scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Sigmoid router: experts ranked by sigmoid(logit) + bias (ties to the lower id); weights are the unbiased sigmoids of
+    the selected experts / (their sum + 1e-6), times ``scale``, rounded through bf16
+    (reference: src/kernels/include/r4dx/kernels/lfm2_kernels.h:38-50)."""
+    s = torch.sigmoid(logits.float())
+    sel = s + bias.float() if bias is not None else s
+    order = torch.sort(sel, dim=-1, descending=True, stable=True).indices[..., :top_k]
+    w = torch.gather(s, -1, order)
+    if renorm:
+        w = w / (w.sum(-1, keepdim=True) + 1e-6)
+    return order, (w * scale).to(torch.bfloat16).float()
+
+
+def short_conv(bcx: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor], round_bf16: bool = False):
+    """Gated short convolution over [T, 3H] rows B | C | x: y = C * causal_fir(B * x) with taps ``weight`` [H, L].
+    ``state`` holds the previous L - 1 rows of B * x ([L-1, H], zeros at the start).  Returns (y [T, H], new state).
+    (reference: src/kernels/include/r4dx/kernels/lfm2_kernels.h:14-34)"""
+    T, H3 = bcx.shape
+    H, L = weight.shape
+    B, C, x = bcx[:, :H], bcx[:, H:2 * H], bcx[:, 2 * H:]
+    bx = B * x
+    if round_bf16:
+        bx = bx.to(torch.bfloat16).float()
+    prev = state if state is not None else torch.zeros(L - 1, H)
+    full = torch.cat([prev, bx], 0)                       # [L-1+T, H]
+    y = torch.zeros(T, H)
+    for j in range(L):
+        y = y + full[j:j + T] * weight[:, j][None, :]
+    return C * y, full[full.shape[0] - (L - 1):].clone()
+
+
 def moe_route(logits: torch.Tensor, top_k: int, renorm: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
     """fp32 softmax over router logits, top-k with ties to the lower expert id.
 

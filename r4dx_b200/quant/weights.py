@@ -18,7 +18,7 @@ from .container import Container, write_container
 from .trellis import TrellisWeight
 from .w4a16 import W4Weight
 
-F32_NAMES = ("A_log", "dt_bias", "k_descale", "v_descale")
+F32_NAMES = ("A_log", "dt_bias", "k_descale", "v_descale", "expert_bias")
 
 
 def default_kb_rule(name: str) -> int:
@@ -41,7 +41,7 @@ def moe_kb_rule(name: str) -> int:
 
 def is_quantized_linear(name: str) -> bool:
     leaf = name.split(".")[-1]
-    return leaf in ("qg", "k", "v", "o", "in_proj_qkv", "in_proj_z", "out_proj", "gate_up", "down", "fc")
+    return leaf in ("qg", "k", "v", "o", "in_proj_qkv", "in_proj_z", "in_proj", "out_proj", "gate_up", "down", "fc")
 
 
 def quantize_weight_set(cfg: ModelConfig, w: Dict[str, torch.Tensor], layout: str = "trellis",
@@ -93,14 +93,17 @@ def linear_shapes(cfg: ModelConfig, with_mtp: bool = False) -> Iterable[Tuple[st
             yield p + "attn.k", cfg.kv_dim, H
             yield p + "attn.v", cfg.kv_dim, H
             yield p + "attn.o", H, cfg.q_dim
+        elif cfg.is_conv_layer(i):
+            yield p + "conv.in_proj", 3 * H, H
+            yield p + "conv.out_proj", H, H
         else:
             yield p + "gdn.in_proj_qkv", cfg.conv_dim, H
             yield p + "gdn.in_proj_z", cfg.value_dim, H
             yield p + "gdn.out_proj", H, cfg.value_dim
-        if not cfg.is_moe:
+        if not cfg.layer_is_moe(i):
             yield p + "mlp.gate_up", 2 * cfg.intermediate_size, H
             yield p + "mlp.down", H, cfg.intermediate_size
-        else:
+        elif cfg.shared_expert_intermediate_size:
             yield p + "moe.shared.gate_up", 2 * cfg.shared_expert_intermediate_size, H
             yield p + "moe.shared.down", H, cfg.shared_expert_intermediate_size
 
@@ -137,6 +140,8 @@ def synthetic_weight_set(cfg: ModelConfig, device="cuda", seed: int = 0, sigma: 
                 w[p + "attn.k_norm"] = n(cfg.head_dim)
             w[p + "attn.k_descale"] = torch.full((cfg.num_key_value_heads,), 1.0 / 16, device=device)
             w[p + "attn.v_descale"] = torch.full((cfg.num_key_value_heads,), 1.0 / 16, device=device)
+        elif cfg.is_conv_layer(i):
+            w[p + "conv.weight"] = (n(H, cfg.short_conv_taps).float() * (0.5 / sigma)).to(torch.bfloat16)
         else:
             Hv = cfg.linear_num_value_heads
             w[p + "gdn.in_proj_a"] = n(Hv, H)
@@ -149,10 +154,13 @@ def synthetic_weight_set(cfg: ModelConfig, device="cuda", seed: int = 0, sigma: 
     w["lm_head"] = w4a16.random_weight(cfg.vocab_shard_size, H, head_group, seed=seed + 17, sigma=sigma, device=device)
     if cfg.is_moe:
         e_begin, e_count = expert_range if expert_range is not None else (0, cfg.num_experts)
-        for i in range(cfg.num_hidden_layers):
+        for i in range(cfg.num_dense_layers, cfg.num_hidden_layers):
             p = f"text.layers.{i}.moe."
             w[p + "router"] = n(cfg.num_experts, H)
-            w[p + "shared_gate"] = n(1, H)
+            if cfg.moe_expert_bias:
+                w[p + "expert_bias"] = n(cfg.num_experts, dtype=torch.float32)
+            if cfg.shared_expert_intermediate_size:
+                w[p + "shared_gate"] = n(1, H)
             kb = kb_rule(p + "experts.0.gate_up")
             for j in range(e_count):
                 e = e_begin + j

@@ -515,3 +515,49 @@ def test_gpu_viterbi_encoder_matches_the_host_encoder_in_quality(K, kb):
 def TrellisWeightCpu(w):
     from r4dx_b200.quant.trellis import TrellisWeight
     return TrellisWeight(w.words.cpu(), w.suh.cpu(), w.svh.cpu(), w.N, w.K, w.kb)
+
+
+def test_sigmoid_router_matches_reference(K):
+    g = torch.Generator().manual_seed(13)
+    T, E, k = 7, 32, 4
+    logits = torch.randn(T, E, generator=g) * 2
+    bias = torch.randn(E, generator=g) * 0.3
+    ids = torch.zeros(T, k, dtype=torch.int32, device="cuda")
+    w = torch.zeros(T, k, device="cuda")
+    for b, scale in ((None, 1.0), (bias, 2.5)):
+        K.moe_router_sigmoid(logits.cuda(), b.cuda() if b is not None else None, k, True, scale, ids, w)
+        rid, rw = R.moe_route_sigmoid(logits, b, k, True, scale)
+        assert torch.equal(ids.cpu().long(), rid)
+        assert torch.allclose(w.cpu(), rw, rtol=1e-2, atol=4e-3)
+
+
+def test_short_conv_across_calls_matches_reference(K):
+    """Decode-sized calls, a partly rejected speculative window and a prefill-sized call, one state ring: every output
+    equals the reference convolution over the committed sequence."""
+    g = torch.Generator().manual_seed(21)
+    H, L = 384, 3
+    wt = (torch.randn(H, L, generator=g) * 0.5).to(BF)
+    ring = torch.zeros(32, H, dtype=BF, device="cuda")
+    state = None
+    pos = 0
+
+    def call(T, commit):
+        nonlocal state, pos
+        bcx = torch.randn(T, 3 * H, generator=g).to(BF)
+        out = torch.zeros(T, H, dtype=BF, device="cuda")
+        K.short_conv(bcx.cuda(), wt.cuda(), ring, torch.tensor([pos], dtype=torch.int32, device="cuda"), out, T)
+        ref, _ = R.short_conv(bcx.float(), wt.float(), state, round_bf16=True)
+        assert torch.allclose(out.float().cpu(), ref, rtol=2e-2, atol=2e-2), (T, pos)
+        _, state = R.short_conv(bcx[:commit].float(), wt.float(), state, round_bf16=True)   # only the committed rows advance the state
+        pos += commit
+
+    call(1, 1)
+    call(5, 5)
+    call(8, 3)          # a verify window of 8 rows of which 3 are accepted: the next call overwrites the other slots
+    call(1, 1)
+    call(16, 2)         # the widest window
+    call(3, 3)
+    call(45, 45)        # prefill-sized: the ring update is the second launch
+    call(2, 2)
+    call(64, 64)        # a multiple of the ring length
+    call(1, 1)

@@ -313,6 +313,39 @@ def test_llama_family_matches_oracle():
     assert sum(int(x == y) for x, y in zip(ta, ref)) >= 6, (ta, ref)
 
 
+def test_short_conv_moe_family_matches_oracle():
+    """Short-conv + attention MoE graph: conv mixers, one dense-MLP layer, sigmoid-routed experts with a selection bias."""
+    from r4dx_b200.config import tiny_lfm2_config
+    from r4dx_b200.models.hybrid import HybridModel
+    from r4dx_b200.models.oracle import OracleModel, init_weights
+    from r4dx_b200.quant.weights import dequantize_weight_set, moe_kb_rule, quantize_weight_set
+    cfg = tiny_lfm2_config()
+    w = init_weights(cfg, 4)
+    for k_ in w:
+        if k_.endswith("moe.router"):
+            w[k_] = w[k_] * 40.0        # wide routing margins: bf16 rounding of activations must not flip the expert choice
+    q = quantize_weight_set(cfg, w, kb_rule=moe_kb_rule)
+    oracle = OracleModel(cfg, dequantize_weight_set(q), fp8_kv=True)
+    ids = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(6))
+    ref_logits, _ = oracle.forward(ids)
+    m = HybridModel(cfg, _to_dev(q), max_ctx=256)
+    rows = []
+    for s in range(0, 40, 8):
+        m.feed(ids[s:s + 8].to(torch.int32))
+        rows.append(m.logits_rows(8).float().cpu().clone())
+    got = torch.cat(rows)
+    scale = ref_logits.abs().max().item()
+    assert (got - ref_logits).abs().max().item() < 0.06 * scale
+    # chunked prefill (tensor-core GEMMs + the two-launch conv) then single-row steps reproduce the small-batch logits
+    a = HybridModel(cfg, _to_dev(q), max_ctx=256)
+    a.prefill(ids[:33].to(torch.int32), chunk=32)
+    la = a.decode_step_logits(int(ids[33])).float().cpu()
+    assert (la - ref_logits[33]).abs().max().item() < 0.06 * scale
+    ta = HybridModel(cfg, _to_dev(q), max_ctx=256).generate_greedy(ids.to(torch.int32), 8, use_graph=True)
+    ref = oracle.greedy(ids, 8)
+    assert sum(int(x == y) for x, y in zip(ta, ref)) >= 6, (ta, ref)
+
+
 def test_prefill_with_embedding_overrides_equals_plain_prefill_when_rows_are_the_token_embeddings(tiny):
     """The image path: rows whose input embedding comes from outside.  Overriding with the tokens' own embeddings
     must reproduce the plain prefill; overriding with other rows must change the result."""

@@ -125,3 +125,37 @@ def test_gemma_style_config_chunk_invariance_and_window():
     v2[:19] -= 3.0                                        # keys 0..18 are outside every row's window (rows at 27..29)
     assert torch.allclose(a, R.causal_gqa_attention(q, k2, v2, 27, window=8), atol=1e-6)
     assert not torch.allclose(a, R.causal_gqa_attention(q, k2, v2, 27), atol=1e-3)
+
+
+def test_short_conv_moe_family_is_invariant_to_how_the_prompt_is_split():
+    """Short-conv + attention MoE family on the oracle: feeding a prompt whole or in pieces gives the same logits (the conv
+    state carries the last taps - 1 rows of B * x), the dense first layer and the sigmoid-routed layers both run."""
+    from r4dx_b200.config import tiny_lfm2_config
+    from r4dx_b200.models.oracle import OracleModel, init_weights, linear_names
+    cfg = tiny_lfm2_config()
+    assert cfg.layer_types == ["conv", "conv", "full_attention", "conv", "full_attention"]
+    assert not cfg.layer_is_moe(0) and cfg.layer_is_moe(1)
+    w = init_weights(cfg, 3)
+    assert "text.layers.0.mlp.gate_up" in w and "text.layers.1.moe.experts.7.down" in w and "text.layers.1.moe.expert_bias" in w
+    assert "text.layers.1.moe.shared.gate_up" not in w
+    assert set(linear_names(cfg)) <= set(w)
+    m = OracleModel(cfg, w)
+    ids = torch.randint(0, cfg.vocab_size, (11,), generator=torch.Generator().manual_seed(1))
+    whole, _ = m.forward(ids)
+    a, st = m.forward(ids[:4])
+    b, st = m.forward(ids[4:5], st)
+    c, st = m.forward(ids[5:], st)
+    assert torch.allclose(torch.cat([a, b, c]), whole, atol=1e-5, rtol=1e-4)
+
+
+def test_sigmoid_router_bias_moves_the_selection_but_not_the_weights():
+    from r4dx_b200.ops import reference as R
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0]])
+    ids, w = R.moe_route_sigmoid(logits, None, 2, True, 1.0)
+    assert ids.tolist() == [[0, 1]]
+    s = torch.sigmoid(logits[0])
+    assert torch.allclose(w[0], (s[:2] / (s[:2].sum() + 1e-6)).to(torch.bfloat16).float())
+    ids, w = R.moe_route_sigmoid(logits, torch.tensor([0.0, 0.0, 0.0, 5.0]), 2, True, 2.0)
+    assert ids.tolist() == [[3, 0]]
+    sel = torch.stack([s[3], s[0]])
+    assert torch.allclose(w[0], (sel / (sel.sum() + 1e-6) * 2.0).to(torch.bfloat16).float())
