@@ -43,6 +43,18 @@ def config_from_hf(text: str) -> ModelConfig:
         cfg = ModelConfig(arch="llama", layer_types=["full_attention"] * L, attn_output_gate=False, qk_norm=False,
                           norm_zero_centered=False, partial_rotary_factor=1.0, rope_theta=t.get("rope_theta", 5.0e5),
                           mtp_num_hidden_layers=0, **common)
+    elif "lfm2" in mt:
+        types = t.get("layer_types") or ["full_attention" if i % 4 == 2 else "conv" for i in range(L)]
+        rope = t.get("rope_parameters") or {}
+        cfg = ModelConfig(arch="lfm2_moe", layer_types=list(types), attn_output_gate=False, qk_norm=True, norm_zero_centered=False,
+                          partial_rotary_factor=1.0, rope_theta=t.get("rope_theta", rope.get("rope_theta", 1.0e6)),
+                          mtp_num_hidden_layers=0, num_experts=t.get("num_experts", 0),
+                          num_experts_per_tok=t.get("num_experts_per_tok", 0), moe_intermediate_size=t.get("moe_intermediate_size", 0),
+                          shared_expert_intermediate_size=0, norm_topk_prob=bool(t.get("norm_topk_prob", True)),
+                          moe_router="sigmoid", moe_expert_bias=bool(t.get("use_expert_bias", True)),
+                          routed_scaling_factor=float(t.get("routed_scaling_factor", 1.0)),
+                          num_dense_layers=t.get("num_dense_layers", 0), short_conv_taps=t.get("conv_L_cache", 3),
+                          **{**common, "rms_norm_eps": t.get("norm_eps", 1e-5), "tie_word_embeddings": True})
     elif "gemma" in mt:
         pattern = t.get("sliding_window_pattern", 6)
         cfg = ModelConfig(arch="gemma", layer_types=["full_attention"] * L, attn_output_gate=False, qk_norm=True,
@@ -126,6 +138,8 @@ def import_hf_weights(cfg: ModelConfig, hf: Dict[str, torch.Tensor], prefix: str
     def gate_up(base: str) -> torch.Tensor:
         return torch.cat([get(base + "gate_proj.weight"), get(base + "up_proj.weight")], 0).contiguous()
 
+    if cfg.arch == "lfm2_moe":
+        return _import_lfm2(cfg, get, has)
     out: Dict[str, torch.Tensor] = {}
     emb = get("embed_tokens.weight")
     out["text.embed_tokens"] = emb * cfg.embed_scale
@@ -169,8 +183,87 @@ def import_hf_weights(cfg: ModelConfig, hf: Dict[str, torch.Tensor], prefix: str
     return out
 
 
+def _import_lfm2(cfg: ModelConfig, get, has) -> Dict[str, torch.Tensor]:
+    """Short-conv + attention MoE checkpoints: ``operator_norm`` / ``ffn_norm`` per layer, ``embedding_norm`` at the end, conv
+    mixers ``conv.{in_proj,conv,out_proj}``, dense ``feed_forward.{w1 gate, w3 up, w2 down}``, experts either stacked 3-D
+    (``experts.gate_up_proj`` [E, 2I, H], ``experts.down_proj`` [E, H, I]) or one module per expert; the head is tied
+    (reference: docs/lfm2-plan.md:44-57)."""
+    out: Dict[str, torch.Tensor] = {}
+    emb = get("embed_tokens.weight")
+    out["text.embed_tokens"] = emb
+    out["text.final_norm"] = _norm_in(cfg, get("embedding_norm.weight"))
+    out["lm_head"] = get("lm_head.weight") if has("lm_head.weight") else emb.clone()
+    for i in range(cfg.num_hidden_layers):
+        p, s = f"text.layers.{i}.", f"layers.{i}."
+        out[p + "input_layernorm"] = _norm_in(cfg, get(s + "operator_norm.weight"))
+        out[p + "post_attention_layernorm"] = _norm_in(cfg, get(s + "ffn_norm.weight"))
+        if cfg.is_attention_layer(i):
+            a = s + "self_attn."
+            out[p + "attn.qg"], out[p + "attn.k"] = get(a + "q_proj.weight"), get(a + "k_proj.weight")
+            out[p + "attn.v"], out[p + "attn.o"] = get(a + "v_proj.weight"), get(a + "out_proj.weight")
+            out[p + "attn.q_norm"] = _norm_in(cfg, get(a + "q_layernorm.weight"))
+            out[p + "attn.k_norm"] = _norm_in(cfg, get(a + "k_layernorm.weight"))
+            out[p + "attn.k_descale"] = torch.ones(cfg.num_key_value_heads)
+            out[p + "attn.v_descale"] = torch.ones(cfg.num_key_value_heads)
+        else:
+            c = s + "conv."
+            out[p + "conv.in_proj"], out[p + "conv.out_proj"] = get(c + "in_proj.weight"), get(c + "out_proj.weight")
+            out[p + "conv.weight"] = get(c + "conv.weight").reshape(cfg.hidden_size, -1)
+        f = s + "feed_forward."
+        if not cfg.layer_is_moe(i):
+            out[p + "mlp.gate_up"] = torch.cat([get(f + "w1.weight"), get(f + "w3.weight")], 0).contiguous()
+            out[p + "mlp.down"] = get(f + "w2.weight")
+            continue
+        out[p + "moe.router"] = get(f + "gate.weight")
+        if cfg.moe_expert_bias:
+            out[p + "moe.expert_bias"] = get(f + "expert_bias")
+        stacked = has(f + "experts.gate_up_proj")
+        gu, dn = (get(f + "experts.gate_up_proj"), get(f + "experts.down_proj")) if stacked else (None, None)
+        for e in range(cfg.num_experts):
+            if stacked:
+                out[p + f"moe.experts.{e}.gate_up"], out[p + f"moe.experts.{e}.down"] = gu[e].contiguous(), dn[e].contiguous()
+            else:
+                x = f + f"experts.{e}."
+                out[p + f"moe.experts.{e}.gate_up"] = torch.cat([get(x + "w1.weight"), get(x + "w3.weight")], 0).contiguous()
+                out[p + f"moe.experts.{e}.down"] = get(x + "w2.weight")
+    return out
+
+
+def _export_lfm2(cfg: ModelConfig, w: Dict[str, torch.Tensor], prefix: str) -> Dict[str, torch.Tensor]:
+    hf: Dict[str, torch.Tensor] = {prefix + "embed_tokens.weight": w["text.embed_tokens"].float(),
+                                   prefix + "embedding_norm.weight": _norm_out(cfg, w["text.final_norm"])}
+    for i in range(cfg.num_hidden_layers):
+        p, s = f"text.layers.{i}.", prefix + f"layers.{i}."
+        hf[s + "operator_norm.weight"] = _norm_out(cfg, w[p + "input_layernorm"])
+        hf[s + "ffn_norm.weight"] = _norm_out(cfg, w[p + "post_attention_layernorm"])
+        if cfg.is_attention_layer(i):
+            a = s + "self_attn."
+            for mine, theirs in (("qg", "q_proj"), ("k", "k_proj"), ("v", "v_proj"), ("o", "out_proj")):
+                hf[a + theirs + ".weight"] = w[p + "attn." + mine].float()
+            hf[a + "q_layernorm.weight"] = _norm_out(cfg, w[p + "attn.q_norm"])
+            hf[a + "k_layernorm.weight"] = _norm_out(cfg, w[p + "attn.k_norm"])
+        else:
+            c = s + "conv."
+            hf[c + "in_proj.weight"], hf[c + "out_proj.weight"] = w[p + "conv.in_proj"].float(), w[p + "conv.out_proj"].float()
+            hf[c + "conv.weight"] = w[p + "conv.weight"].float().reshape(cfg.hidden_size, 1, -1)
+        f = s + "feed_forward."
+        if not cfg.layer_is_moe(i):
+            gu = w[p + "mlp.gate_up"].float()
+            hf[f + "w1.weight"], hf[f + "w3.weight"] = gu[:gu.shape[0] // 2].contiguous(), gu[gu.shape[0] // 2:].contiguous()
+            hf[f + "w2.weight"] = w[p + "mlp.down"].float()
+            continue
+        hf[f + "gate.weight"] = w[p + "moe.router"].float()
+        if cfg.moe_expert_bias:
+            hf[f + "expert_bias"] = w[p + "moe.expert_bias"].float()
+        hf[f + "experts.gate_up_proj"] = torch.stack([w[p + f"moe.experts.{e}.gate_up"].float() for e in range(cfg.num_experts)])
+        hf[f + "experts.down_proj"] = torch.stack([w[p + f"moe.experts.{e}.down"].float() for e in range(cfg.num_experts)])
+    return hf
+
+
 def export_hf_weights(cfg: ModelConfig, w: Dict[str, torch.Tensor], prefix: str = "model.", packed_gdn: bool = True) -> Dict[str, torch.Tensor]:
     """The inverse of ``import_hf_weights`` (mtp.* tensors are not part of the HF layout and are dropped)."""
+    if cfg.arch == "lfm2_moe":
+        return _export_lfm2(cfg, w, prefix)
     hf: Dict[str, torch.Tensor] = {}
     hf[prefix + "embed_tokens.weight"] = w["text.embed_tokens"].float() / cfg.embed_scale
     hf[prefix + "norm.weight"] = _norm_out(cfg, w["text.final_norm"])

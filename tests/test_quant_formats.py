@@ -195,3 +195,30 @@ def test_hf_checkpoint_import_round_trips_every_family():
                                                       "intermediate_size": 512, "vocab_size": 1000, "linear_num_key_heads": 2,
                                                       "linear_num_value_heads": 4, "linear_key_head_dim": 64, "linear_value_head_dim": 64}}))
     assert c.layer_types == ["linear_attention"] * 3 + ["full_attention"] and c.conv_dim == 2 * 128 + 256
+
+
+def test_hf_import_of_the_short_conv_moe_family_round_trips():
+    import json
+    import torch
+    from r4dx_b200.config import tiny_lfm2_config
+    from r4dx_b200.models.oracle import OracleModel, init_weights
+    from r4dx_b200.quant import hf_import as HI
+    cfg = tiny_lfm2_config()
+    w = init_weights(cfg, 2)
+    w["lm_head"] = w["text.embed_tokens"].clone()
+    hf = HI.export_hf_weights(cfg, w)
+    assert hf["model.layers.1.feed_forward.experts.gate_up_proj"].shape == (8, 256, 256)
+    assert hf["model.layers.0.conv.conv.weight"].shape == (256, 1, 3) and "model.layers.0.feed_forward.w1.weight" in hf
+    assert torch.allclose(hf["model.embedding_norm.weight"], w["text.final_norm"] + 1.0)
+    back = HI.import_hf_weights(cfg, hf)
+    for k, v in w.items():
+        assert torch.allclose(back[k].float(), v.float(), atol=1e-6), k
+    ids = torch.randint(0, cfg.vocab_size, (9,), generator=torch.Generator().manual_seed(0))
+    assert torch.allclose(OracleModel(cfg, w).forward(ids)[0], OracleModel(cfg, back).forward(ids)[0], atol=1e-4)
+    c = HI.config_from_hf(json.dumps({
+        "model_type": "lfm2_moe", "hidden_size": 2048, "num_hidden_layers": 8, "num_attention_heads": 32, "num_key_value_heads": 8,
+        "intermediate_size": 11776, "moe_intermediate_size": 1536, "num_experts": 64, "num_experts_per_tok": 4,
+        "num_dense_layers": 2, "vocab_size": 128000, "norm_eps": 1e-5, "conv_L_cache": 3, "use_expert_bias": True,
+        "layer_types": ["conv", "conv", "full_attention", "conv", "conv", "conv", "full_attention", "conv"]}))
+    assert c.arch == "lfm2_moe" and c.head_dim == 64 and c.moe_router == "sigmoid" and c.is_conv_layer(0) and c.is_attention_layer(2)
+    assert c.layer_is_moe(2) and not c.layer_is_moe(1) and c.rms_norm_eps == 1e-5 and c.short_conv_taps == 3 and c.rotary_dim == 64
