@@ -515,15 +515,20 @@ class HybridModel:
     def _row_parallel_chunk(self, lin: Linear, inp: torch.Tensor, x: torch.Tensor, cb: dict,
                             fused_silu_mul: bool = False, gelu: bool = False, post_norm=None) -> None:
         if post_norm is not None or gelu:
-            # sandwich-norm / GeGLU families: single-GPU chunk path (the fused tensor-parallel epilogues add into x directly)
-            if self.comm is not None and self.comm.world > 1:
-                raise NotImplementedError("tensor-parallel prefill of sandwich-norm models")
-            if post_norm is None:
+            # sandwich-norm / GeGLU families: the fused tensor-parallel epilogues add into x directly, which a norm between
+            # the product and the add rules out, so under tensor parallelism the bare product is summed over the ranks first
+            tp = self.comm is not None and self.comm.world > 1
+            if post_norm is None and not tp:
                 lin.chunk(inp, cb["xh"], x, residual=x, fused_silu_mul=fused_silu_mul, gelu=gelu)
                 return
             tmp = cb["h"][:x.shape[0]]
             lin.chunk(inp, cb["xh"], tmp, fused_silu_mul=fused_silu_mul, gelu=gelu)
-            K.norm_add(x, tmp, post_norm, self.cfg.rms_norm_eps)
+            if tp:
+                self.comm.all_reduce_rows(tmp)
+            if post_norm is None:
+                K.residual_add(x, tmp)
+            else:
+                K.norm_add(x, tmp, post_norm, self.cfg.rms_norm_eps)
             return
         if self.comm is None or self.comm.world == 1:
             lin.chunk(inp, cb["xh"], x, residual=x, fused_silu_mul=fused_silu_mul)

@@ -74,6 +74,13 @@ class NcclComm:
         self.stats.all_reduces += 1
         self.stats.all_reduce_bytes += tmp.numel() * 2
 
+    def all_reduce_rows(self, t: torch.Tensor) -> None:
+        """In-place sum of a bf16 row block over the ranks (the families whose block output is normalised before it joins the
+        residual stream cannot fold the add into the product's epilogue, so they reduce the bare product)."""
+        dist.all_reduce(t, group=self.group)
+        self.stats.all_reduces += 1
+        self.stats.all_reduce_bytes += t.numel() * t.element_size()
+
     # ---- vocab-parallel greedy pick -------------------------------------------------------------
     def merge_argmax(self, ids: torch.Tensor, vals: torch.Tensor) -> None:
         """In place: every rank ends with the global (max value, lowest id) per row."""
