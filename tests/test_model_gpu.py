@@ -321,9 +321,16 @@ def test_short_conv_moe_family_matches_oracle():
     from r4dx_b200.quant.weights import dequantize_weight_set, moe_kb_rule, quantize_weight_set
     cfg = tiny_lfm2_config()
     w = init_weights(cfg, 4)
+    # A sigmoid score lives in (0, 1), so the gap between the k-th and (k+1)-th expert is often below the bf16 noise of the
+    # activations and a model-level comparison would hinge on coin flips.  Here the selection bias is spread two units apart
+    # (a different order per layer), which fixes WHICH experts run while their weights still follow the token's scores;
+    # token-dependent selection is compared exactly at the kernel level (test_sigmoid_router_matches_reference).
     for k_ in w:
         if k_.endswith("moe.router"):
-            w[k_] = w[k_] * 40.0        # wide routing margins: bf16 rounding of activations must not flip the expert choice
+            w[k_] = w[k_] * 6.0
+        if k_.endswith("moe.expert_bias"):
+            layer = int(k_.split(".")[2])
+            w[k_] = torch.roll(torch.arange(cfg.num_experts, dtype=torch.float32) * 2.0, layer)
     q = quantize_weight_set(cfg, w, kb_rule=moe_kb_rule)
     oracle = OracleModel(cfg, dequantize_weight_set(q), fp8_kv=True)
     ids = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(6))
@@ -335,7 +342,8 @@ def test_short_conv_moe_family_matches_oracle():
         rows.append(m.logits_rows(8).float().cpu().clone())
     got = torch.cat(rows)
     scale = ref_logits.abs().max().item()
-    assert (got - ref_logits).abs().max().item() < 0.06 * scale
+    err = (got - ref_logits).abs().max(dim=1).values
+    assert err.max().item() < 0.06 * scale, (err / scale).tolist()
     # chunked prefill (tensor-core GEMMs + the two-launch conv) then single-row steps reproduce the small-batch logits
     a = HybridModel(cfg, _to_dev(q), max_ctx=256)
     a.prefill(ids[:33].to(torch.int32), chunk=32)
