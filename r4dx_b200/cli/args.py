@@ -90,6 +90,9 @@ def convert_parser() -> argparse.ArgumentParser:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--mtp", action="store_true")
     ap.add_argument("--keep-bf16", default="", help="comma list of tensor-name substrings kept in bf16")
+    ap.add_argument("--hessians", default=None,
+                    help="safetensors file from `python -m r4dx_b200.quant.calibrate hessians`: linears found in it are quantized "
+                         "with error compensation (block LDLQ for trellis, GPTQ for w4a16)")
     ap.add_argument("--kv-calib", default=None, help="JSON file with per-layer k/v amax for fp8 descales")
     ap.add_argument("--reuse-tensors-from", default=None, help="older container whose identical tensors are copied, guarded by sha256")
     ap.add_argument("--selftest", action="store_true", help="re-open the output and verify every tensor's reconstruction error")

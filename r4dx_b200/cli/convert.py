@@ -57,8 +57,12 @@ def main(argv=None) -> int:
     keep = [s for s in args.keep_bf16.split(",") if s]
     layout = args.layouts.split(",")[0]
     src = {k: v for k, v in w.items()}
+    hessians = None
+    if args.hessians:
+        from safetensors.torch import load_file
+        hessians = {k: v for k, v in load_file(args.hessians).items() if v.dim() == 2}
     q = quantize_weight_set(cfg, src, layout=layout, kb_rule=_kb_rule(args.kb_plan), head_group=args.lm_head_group, seed=args.seed,
-                            encoder=args.encoder)
+                            encoder=args.encoder, hessians=hessians)
     for k in list(q):
         if any(s in k for s in keep):
             q[k] = w[k].to(torch.bfloat16)

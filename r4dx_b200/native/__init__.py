@@ -75,6 +75,7 @@ def _declare_host(L):
     _sig(L, "r4dxb_trellis_decode", None, [c_ptr, c_i64, c_i64, c_int, c_ptr])
     _sig(L, "r4dxb_trellis_packed_words", c_i64, [c_i64, c_i64, c_int])
     _sig(L, "r4dxb_trellis_quantize", c_f64, [c_ptr, c_i64, c_i64, c_int, c_u64, c_int, c_ptr, c_ptr, c_ptr])
+    _sig(L, "r4dxb_trellis_quantize_ldlq", c_f64, [c_ptr, c_ptr, c_i64, c_i64, c_int, c_u64, c_int, c_f32, c_ptr, c_ptr, c_ptr, c_ptr])
     _sig(L, "r4dxb_trellis_reconstruct", None, [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_int, c_int, c_ptr])
     _sig(L, "r4dxb_trellis_encode_tile", c_f32, [c_ptr, c_int, c_ptr])
     _sig(L, "r4dxb_trellis_random_fill", None, [c_ptr, c_i64, c_u64])

@@ -151,8 +151,9 @@ void StatesToRing(const uint16_t* states, int kb, uint32_t* words) {
 
 }  // namespace
 
-// Encodes 256 values (position order) into a tail-biting ring; returns the squared error.
-float TrellisEncodeTile(const float* w, int kb, uint32_t* words, ViterbiScratch& sc) {
+// Encodes 256 values (position order) into a tail-biting ring; returns the squared error.  With ``q_out`` the decoded
+// value of every position (what the kernels will read back) is returned too.
+float TrellisEncodeTile(const float* w, int kb, uint32_t* words, ViterbiScratch& sc, float* q_out) {
   uint16_t states[256];
   float rot[256];
   for (int i = 0; i < 256; ++i) rot[i] = w[(i + 128) & 255];
@@ -161,7 +162,13 @@ float TrellisEncodeTile(const float* w, int kb, uint32_t* words, ViterbiScratch&
   const int overlap = states[127] & ((1 << (16 - kb)) - 1);
   const float err = ViterbiPass(w, kb, overlap, sc, states);
   StatesToRing(states, kb, words);
+  if (q_out)
+    for (int p = 0; p < 256; ++p) q_out[p] = F16ToFloat(TrellisCodeF16(states[p]));
   return err;
+}
+
+float TrellisEncodeTile(const float* w, int kb, uint32_t* words, ViterbiScratch& sc) {
+  return TrellisEncodeTile(w, kb, words, sc, nullptr);
 }
 
 // ---- Hadamard ---------------------------------------------------------------------------------
@@ -205,10 +212,13 @@ static void ParallelFor(int64_t n, int threads, F fn) {
 // per-input-channel RMS folded into suh and the global RMS of the rotated matrix into svh, so D is
 // close to unit-variance Gaussian, which is what the code book covers.
 // Returns the relative squared error ||Q - D||^2 / ||D||^2.
-double TrellisQuantize(const float* W, int64_t N, int64_t K, int kb, uint64_t seed, int threads,
-                       uint32_t* words_out, uint16_t* suh_out, uint16_t* svh_out) {
-  std::vector<float> D(static_cast<size_t>(N) * K);
-  std::vector<float> su(K), sv(N);
+// Regularisation shared by the plain and the error-compensated quantizer: fills D [N, K] with the rotated, unit-variance
+// matrix, su [K] / sv [N] with the signed scales (su already rounded through fp16) and writes suh / svh.
+static void TrellisRegularize(const float* W, int64_t N, int64_t K, uint64_t seed, int threads, std::vector<float>& D,
+                              std::vector<float>& su, std::vector<float>& sv, uint16_t* suh_out, uint16_t* svh_out) {
+  D.resize(static_cast<size_t>(N) * K);
+  su.resize(K);
+  sv.resize(N);
   uint64_t rng = seed * 0x2545F4914F6CDD1Dull + 0x1234567ull;
   // per-input-channel scale
   for (int64_t k = 0; k < K; ++k) {
@@ -251,6 +261,13 @@ double TrellisQuantize(const float* W, int64_t N, int64_t K, int kb, uint64_t se
   for (int64_t n = 0; n < N; ++n) svh_out[n] = FloatToF16(sv[n] * sigma_h);
   for (int64_t k = 0; k < K; ++k) suh_out[k] = FloatToF16(su[k]);
   const float inv_sigma = 1.0f / sigma_h;
+  for (size_t i = 0; i < D.size(); ++i) D[i] *= inv_sigma;
+}
+
+double TrellisQuantize(const float* W, int64_t N, int64_t K, int kb, uint64_t seed, int threads,
+                       uint32_t* words_out, uint16_t* suh_out, uint16_t* svh_out) {
+  std::vector<float> D, su, sv;
+  TrellisRegularize(W, N, K, seed, threads, D, su, sv, suh_out, svh_out);
   const int64_t tiles_k = K / 16, tiles = (N / 16) * tiles_k;
   std::vector<std::unique_ptr<ViterbiScratch>> scratch;
   const int nthreads = std::max(1, threads);
@@ -259,12 +276,159 @@ double TrellisQuantize(const float* W, int64_t N, int64_t K, int kb, uint64_t se
   ParallelFor(tiles, nthreads, [&](int64_t ti, int tid) {
     const int64_t tn = ti / tiles_k, tk = ti % tiles_k;
     float vals[256];
-    for (int p = 0; p < 256; ++p) vals[p] = D[(tn * 16 + p / 16) * K + tk * 16 + p % 16] * inv_sigma;
+    for (int p = 0; p < 256; ++p) vals[p] = D[(tn * 16 + p / 16) * K + tk * 16 + p % 16];
     err[tid] += TrellisEncodeTile(vals, kb, words_out + TrellisTileWordIndex(K, kb, tn, tk), *scratch[tid]);
   });
   double e = 0;
   for (double v : err) e += v;
   return e / double(D.size());   // D / sigma has unit mean square
+}
+
+// Error-compensated quantization (block LDLQ, the trellis counterpart of GPTQ; reference: the converter's --ldlq mode,
+// src/convert/main.cpp:1-30, and the oracle's block-LDL step, tools/reference/trellis_quant.py:1-110).
+//
+// The code matrix Q multiplies x' = H_K (suh * x), so the layer's proxy loss tr((D - Q) H' (D - Q)^T) uses the Hessian
+// in that basis, H' = H_K diag(suh) Hess diag(suh) H_K (damped by `damp` x its mean diagonal).  With the block LDL
+// factorisation H' = L B L^T (L unit lower triangular in 16-column blocks, from a blocked Cholesky), the tile columns are
+// encoded from the last to the first and each one first absorbs the error already made to its right:
+//     target[:, k] = D[:, k] + sum_{j > k} (D[:, j] - Q[:, j]) L[j, k]
+// Every target tile goes through the same Viterbi search as the plain quantizer; row tiles of one tile column are
+// independent and run on the thread pool.  Work is K^3 / 3 for the factorisation plus N K^2 / 2 for the feedback.
+// Results do not depend on the thread count (each output element is produced by one thread in a fixed order).
+// Returns the relative squared error of Q against D; *proxy_out = tr(E H' E^T) / tr(D H' D^T).
+double TrellisQuantizeLdlq(const float* W, const float* Hess, int64_t N, int64_t K, int kb, uint64_t seed, int threads,
+                           float damp, uint32_t* words_out, uint16_t* suh_out, uint16_t* svh_out, double* proxy_out) {
+  std::vector<float> D, su, sv;
+  TrellisRegularize(W, N, K, seed, threads, D, su, sv, suh_out, svh_out);
+  const float inv_sqrt = 1.0f / std::sqrt(128.0f);
+  // H' = R Hess R^T, R = H_K diag(su)
+  std::vector<float> Hr(static_cast<size_t>(K) * K);
+  ParallelFor(K, threads, [&](int64_t i, int) {
+    float* row = Hr.data() + i * K;
+    for (int64_t j = 0; j < K; ++j) row[j] = Hess[i * K + j] * su[i] * su[j];
+    for (int64_t b = 0; b < K; b += 128) {
+      Fwht128(row + b, 1);
+      for (int t = 0; t < 128; ++t) row[b + t] *= inv_sqrt;
+    }
+  });
+  ParallelFor(K, threads, [&](int64_t j, int) {
+    for (int64_t b = 0; b < K; b += 128) {
+      float* col = Hr.data() + b * K + j;
+      Fwht128(col, static_cast<int>(K));
+      for (int t = 0; t < 128; ++t) col[size_t(t) * K] *= inv_sqrt;
+    }
+  });
+  double mean_diag = 0;
+  for (int64_t i = 0; i < K; ++i) mean_diag += Hr[i * K + i];
+  mean_diag /= K;
+  if (!(mean_diag > 0)) mean_diag = 1.0;
+  for (int64_t i = 0; i < K; ++i) Hr[i * K + i] += static_cast<float>(damp * mean_diag);
+  std::vector<float> Hkeep;
+  if (proxy_out) Hkeep = Hr;                       // the factorisation overwrites Hr's lower triangle
+  // blocked right-looking Cholesky on the lower triangle (block 16), then L <- L diag-block^-1 (unit block diagonal)
+  constexpr int B = 16;
+  const int64_t nb = K / B;
+  auto blk = [&](int64_t bi, int64_t bj) { return Hr.data() + bi * B * K + bj * B; };
+  for (int64_t j = 0; j < nb; ++j) {
+    float* A = blk(j, j);
+    for (int c = 0; c < B; ++c) {                  // unblocked Cholesky of the diagonal block
+      double d = A[c * K + c];
+      for (int t = 0; t < c; ++t) d -= double(A[c * K + t]) * A[c * K + t];
+      d = std::sqrt(d > 1e-20 ? d : 1e-20);
+      A[c * K + c] = static_cast<float>(d);
+      for (int r = c + 1; r < B; ++r) {
+        double v = A[r * K + c];
+        for (int t = 0; t < c; ++t) v -= double(A[r * K + t]) * A[c * K + t];
+        A[r * K + c] = static_cast<float>(v / d);
+      }
+    }
+    // panel: A_ij <- A_ij A_jj^-T, then trailing update of block row i: A_ik -= A_ij A_kj^T for j < k <= i
+    ParallelFor(nb - j - 1, threads, [&](int64_t ii, int) {
+      float* P = blk(j + 1 + ii, j);
+      for (int r = 0; r < B; ++r)
+        for (int c = 0; c < B; ++c) {
+          double v = P[r * K + c];
+          for (int t = 0; t < c; ++t) v -= double(P[r * K + t]) * A[c * K + t];
+          P[r * K + c] = static_cast<float>(v / A[c * K + c]);
+        }
+    });
+    ParallelFor(nb - j - 1, threads, [&](int64_t ii, int) {
+      const int64_t i = j + 1 + ii;
+      const float* Pi = blk(i, j);
+      for (int64_t k = j + 1; k <= i; ++k) {
+        const float* Pk = blk(k, j);
+        float* T = blk(i, k);
+        for (int r = 0; r < B; ++r)
+          for (int c = 0; c < B; ++c) {
+            float acc = 0.f;
+            for (int t = 0; t < B; ++t) acc += Pi[r * K + t] * Pk[c * K + t];
+            T[r * K + c] -= acc;
+          }
+      }
+    });
+  }
+  ParallelFor(nb, threads, [&](int64_t j, int) {    // column block j: X A_jj = L_ij  (A_jj lower triangular)
+    const float* A = blk(j, j);
+    for (int64_t i = j + 1; i < nb; ++i) {
+      float* P = blk(i, j);
+      for (int r = 0; r < B; ++r)
+        for (int c = B - 1; c >= 0; --c) {
+          double v = P[r * K + c];
+          for (int t = c + 1; t < B; ++t) v -= double(P[r * K + t]) * A[t * K + c];
+          P[r * K + c] = static_cast<float>(v / A[c * K + c]);
+        }
+    }
+  });
+  // LDLQ sweep, last tile column first.  E holds D - Q for the columns already encoded.
+  std::vector<float> E(static_cast<size_t>(N) * K, 0.f);
+  const int nthreads = std::max(1, threads);
+  std::vector<std::unique_ptr<ViterbiScratch>> scratch;
+  for (int t = 0; t < nthreads; ++t) scratch.emplace_back(new ViterbiScratch(kb));
+  std::vector<double> err(nthreads, 0.0);
+  for (int64_t tk = nb - 1; tk >= 0; --tk) {
+    ParallelFor(N / 16, nthreads, [&](int64_t tn, int tid) {
+      float vals[256], q[256];
+      for (int r = 0; r < 16; ++r) {
+        const float* e = E.data() + (tn * 16 + r) * K;
+        float acc[16];
+        for (int c = 0; c < 16; ++c) acc[c] = 0.f;
+        for (int64_t j = (tk + 1) * B; j < K; ++j) {
+          const float ev = e[j];
+          const float* l = Hr.data() + j * K + tk * B;
+          for (int c = 0; c < 16; ++c) acc[c] += ev * l[c];
+        }
+        for (int c = 0; c < 16; ++c) vals[r * 16 + c] = D[(tn * 16 + r) * K + tk * 16 + c] + acc[c];
+      }
+      TrellisEncodeTile(vals, kb, words_out + TrellisTileWordIndex(K, kb, tn, tk), *scratch[tid], q);
+      for (int r = 0; r < 16; ++r)
+        for (int c = 0; c < 16; ++c) {
+          const size_t at = (tn * 16 + r) * K + tk * 16 + c;
+          const float d = D[at] - q[r * 16 + c];
+          E[at] = d;
+          err[tid] += double(d) * d;
+        }
+    });
+  }
+  if (proxy_out) {
+    std::vector<double> num(nthreads, 0.0), den(nthreads, 0.0);
+    ParallelFor(N, nthreads, [&](int64_t n, int tid) {
+      const float* e = E.data() + n * K;
+      const float* d = D.data() + n * K;
+      for (int64_t i = 0; i < K; ++i) {
+        const float* h = Hkeep.data() + i * K;
+        double ae = 0, ad = 0;
+        for (int64_t j = 0; j < K; ++j) { ae += double(h[j]) * e[j]; ad += double(h[j]) * d[j]; }
+        num[tid] += ae * e[i];
+        den[tid] += ad * d[i];
+      }
+    });
+    double a = 0, b = 0;
+    for (int t = 0; t < nthreads; ++t) { a += num[t]; b += den[t]; }
+    *proxy_out = b > 0 ? a / b : 0.0;
+  }
+  double e = 0;
+  for (double v : err) e += v;
+  return e / double(D.size());
 }
 
 // Dequantizes to the effective dense weight W_eff [N, K] fp32 = diag(svh) H_N Q H_K diag(suh).
@@ -319,6 +483,13 @@ double r4dxb_trellis_quantize(const float* W, int64_t N, int64_t K, int kb, uint
                               uint32_t* words_out, uint16_t* suh_out, uint16_t* svh_out) {
   if (N % 128 || K % 128 || kb < 3 || kb > 5) return -1.0;
   return r4dxb::TrellisQuantize(W, N, K, kb, seed, threads, words_out, suh_out, svh_out);
+}
+
+/* Hess: [K, K] fp32 second-moment matrix of the layer's inputs (symmetric).  proxy_out may be null. */
+double r4dxb_trellis_quantize_ldlq(const float* W, const float* Hess, int64_t N, int64_t K, int kb, uint64_t seed, int threads,
+                                   float damp, uint32_t* words_out, uint16_t* suh_out, uint16_t* svh_out, double* proxy_out) {
+  if (N % 128 || K % 128 || kb < 3 || kb > 5 || !(damp >= 0)) return -1.0;
+  return r4dxb::TrellisQuantizeLdlq(W, Hess, N, K, kb, seed, threads, damp, words_out, suh_out, svh_out, proxy_out);
 }
 
 void r4dxb_trellis_reconstruct(const uint32_t* words, const uint16_t* suh, const uint16_t* svh, int64_t N,

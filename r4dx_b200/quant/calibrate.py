@@ -110,7 +110,9 @@ def gptq_w4a16(W: torch.Tensor, H: torch.Tensor, group: int = 64, damp: float = 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser("r4dxb-calibrate")
-    ap.add_argument("what", choices=["kv"])
+    ap.add_argument("what", choices=["kv", "hessians", "imatrix"],
+                    help="kv: fp8 KV descales (json); hessians: one [K, K] second-moment matrix per quantizable linear "
+                         "(safetensors, for `convert --hessians`); imatrix: their diagonals only (per-input-channel importance)")
     ap.add_argument("--input", required=True, help="'random:<tiny|small>' or a container / checkpoint readable by the converter")
     ap.add_argument("--tokens", type=int, default=256)
     ap.add_argument("--prompts", type=int, default=4)
@@ -121,6 +123,14 @@ def main(argv=None) -> int:
     cfg, w = load_source(a.input, 0, False, a.seed)
     g = torch.Generator().manual_seed(a.seed)
     prompts = [torch.randint(0, cfg.vocab_size, (a.tokens,), generator=g) for _ in range(a.prompts)]
+    if a.what in ("hessians", "imatrix"):
+        from safetensors.torch import save_file
+        H = capture_hessians(cfg, w, prompts)
+        if a.what == "imatrix":
+            H = {k: torch.diagonal(v).contiguous() for k, v in H.items()}
+        save_file({k: v.contiguous() for k, v in H.items()}, a.out)
+        print(f"wrote {a.what} of {len(H)} linears to {a.out}")
+        return 0
     d = kv_descales(cfg, w, prompts)
     json.dump({str(l): {"k": k, "v": v} for l, (k, v) in d.items()}, open(a.out, "w"), indent=1)
     print(f"wrote fp8 KV descales of {len(d)} attention layers to {a.out}")

@@ -56,6 +56,33 @@ def quantize(W: torch.Tensor, kb: int, seed: int = 0, threads: int | None = None
     return TrellisWeight(words, suh, svh, N, K, kb), float(err)
 
 
+def quantize_ldlq(W: torch.Tensor, H: torch.Tensor, kb: int, seed: int = 0, damp: float = 0.01,
+                  threads: int | None = None) -> tuple[TrellisWeight, float, float]:
+    """Error-compensated trellis quantization (block LDLQ): tile columns are encoded last to first and each absorbs, through
+    the block LDL factor of the rotated Hessian, the error already made to its right.  ``H`` [K, K] is the second-moment
+    matrix of the layer's inputs (``calibrate.capture_hessians``).  Same regularisation (signs, scales) as ``quantize`` for
+    the same seed.  Returns (weight, relative squared error of the codes, proxy loss tr(E H' E^T) / tr(D H' D^T))."""
+    import ctypes
+    L = native.host()
+    W = W.detach().to(torch.float32).contiguous().cpu()
+    H = H.detach().to(torch.float32).contiguous().cpu()
+    N, K = W.shape
+    if N % 128 or K % 128:
+        raise ValueError(f"trellis needs N and K multiples of 128, got {N}x{K}")
+    if H.shape != (K, K):
+        raise ValueError(f"Hessian must be [{K}, {K}], got {tuple(H.shape)}")
+    words = torch.empty(packed_words(N, K, kb), dtype=torch.int32)
+    suh = torch.empty(K, dtype=torch.float16)
+    svh = torch.empty(N, dtype=torch.float16)
+    proxy = ctypes.c_double(0.0)
+    threads = threads or min(32, os.cpu_count() or 1)
+    err = L.r4dxb_trellis_quantize_ldlq(_ptr(W), _ptr(H), N, K, kb, seed, threads, float(damp), _ptr(words), _ptr(suh), _ptr(svh),
+                                        ctypes.addressof(proxy))
+    if err < 0:
+        raise ValueError("r4dxb_trellis_quantize_ldlq rejected the arguments")
+    return TrellisWeight(words, suh, svh, N, K, kb), float(err), float(proxy.value)
+
+
 def quantize_cuda(W: torch.Tensor, kb: int, seed: int = 0, device: str = "cuda") -> tuple[TrellisWeight, float]:
     """The same quantizer with the Viterbi search on the GPU (one CTA per 16x16 tile): regularisation (per-channel
     scale, random signs, Hadamard sandwich, global scale) in torch on the device, then ``r4dxb_trellis_encode_tiles``.

@@ -46,23 +46,31 @@ def is_quantized_linear(name: str) -> bool:
 
 def quantize_weight_set(cfg: ModelConfig, w: Dict[str, torch.Tensor], layout: str = "trellis",
                         kb_rule: Callable[[str], int] = default_kb_rule, head_group: int = 64,
-                        seed: int = 0, encoder: str = "cpu") -> Dict[str, object]:
+                        seed: int = 0, encoder: str = "cpu", hessians: Optional[Dict[str, torch.Tensor]] = None) -> Dict[str, object]:
     """fp32 weights -> quantized set.  layout: trellis | w4a16 | bf16.  ``encoder``: where the Viterbi search of the
     trellis layout runs - "cpu" (threads) or "cuda" (one CTA per tile, ~25x the throughput of 32 host threads); the
-    result lives on the CPU either way."""
+    result lives on the CPU either way.  ``hessians``: name -> [K, K] input second moments; linears that have one are
+    quantized with error compensation (block LDLQ for the trellis layout, GPTQ for w4a16) on the host."""
     out: Dict[str, object] = {}
+    hessians = hessians or {}
     for i, (name, t) in enumerate(w.items()):
         leaf = name.split(".")[-1]
         if name == "lm_head":
             out[name] = w4a16.quantize(t, head_group) if layout != "bf16" else t.to(torch.bfloat16)
         elif is_quantized_linear(name) and layout == "trellis" and t.shape[0] % 128 == 0 and t.shape[1] % 128 == 0:
-            if encoder == "cuda":
+            if name in hessians:
+                out[name], _, _ = trellis.quantize_ldlq(t, hessians[name], kb_rule(name), seed=seed * 100003 + i)
+            elif encoder == "cuda":
                 tw, _ = trellis.quantize_cuda(t, kb_rule(name), seed=seed * 100003 + i)
                 out[name] = TrellisWeight(tw.words.cpu(), tw.suh.cpu(), tw.svh.cpu(), tw.N, tw.K, tw.kb)
             else:
                 out[name], _ = trellis.quantize(t, kb_rule(name), seed=seed * 100003 + i)
         elif is_quantized_linear(name) and layout == "w4a16":
-            out[name] = w4a16.quantize(t, head_group)
+            if name in hessians:
+                from .calibrate import gptq_w4a16
+                out[name] = gptq_w4a16(t, hessians[name], head_group)
+            else:
+                out[name] = w4a16.quantize(t, head_group)
         elif leaf in F32_NAMES:
             out[name] = t.float()
         else:

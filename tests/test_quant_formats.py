@@ -222,3 +222,47 @@ def test_hf_import_of_the_short_conv_moe_family_round_trips():
         "layer_types": ["conv", "conv", "full_attention", "conv", "conv", "conv", "full_attention", "conv"]}))
     assert c.arch == "lfm2_moe" and c.head_dim == 64 and c.moe_router == "sigmoid" and c.is_conv_layer(0) and c.is_attention_layer(2)
     assert c.layer_is_moe(2) and not c.layer_is_moe(1) and c.rms_norm_eps == 1e-5 and c.short_conv_taps == 3 and c.rotary_dim == 64
+
+
+def test_trellis_ldlq_lowers_the_layer_loss_and_is_thread_invariant():
+    """Block LDLQ: with correlated inputs the proxy loss tr(E H E^T) drops well below the plain quantizer's, the loss the
+    quantizer reports matches the one measured on the reconstructed weight, and the bits do not depend on the thread count."""
+    import torch
+    from r4dx_b200.quant import trellis
+    g = torch.Generator().manual_seed(0)
+    N, K = 128, 256
+    W = torch.randn(N, K, generator=g) * 0.02
+    X = torch.randn(2048, 16, generator=g) @ torch.randn(16, K, generator=g) + 0.3 * torch.randn(2048, K, generator=g)
+    H = X.T @ X / 2048
+
+    def loss(tw):
+        E = trellis.reconstruct(tw) - W
+        return float(torch.trace(E @ H @ E.T) / torch.trace(W @ H @ W.T))
+
+    plain, _ = trellis.quantize(W, 4, seed=1)
+    comp, rel, proxy = trellis.quantize_ldlq(W, H, 4, seed=1, damp=0.01, threads=4)
+    assert torch.equal(plain.suh, comp.suh) and torch.equal(plain.svh, comp.svh)       # same regularisation
+    lp, lc = loss(plain), loss(comp)
+    assert lc < 0.35 * lp, (lp, lc)
+    assert abs(proxy - lc) < 0.5 * lc + 1e-5           # the reported proxy includes the damping term
+    one, _, _ = trellis.quantize_ldlq(W, H, 4, seed=1, damp=0.01, threads=1)
+    assert torch.equal(one.words, comp.words)
+    # a Hessian that is the identity in the rotated basis (diag(1 / suh^2) before it) has nothing to compensate
+    same, _, _ = trellis.quantize_ldlq(W, torch.diag(1.0 / plain.suh.float() ** 2), 4, seed=1, damp=0.0)
+    assert torch.equal(same.words, plain.words)
+
+
+def test_converter_uses_hessians_when_given(tmp_path):
+    import torch
+    from safetensors.torch import load_file
+    from r4dx_b200.cli.convert import main as convert_main
+    from r4dx_b200.quant.calibrate import main as calibrate_main
+    hp = str(tmp_path / "h.safetensors")
+    assert calibrate_main(["hessians", "--input", "random:tiny", "--tokens", "48", "--prompts", "2", "--out", hp]) == 0
+    H = load_file(hp)
+    assert H["text.layers.0.mlp.gate_up"].shape == (256, 256) and H["text.layers.0.mlp.down"].shape == (512, 512)
+    ip = str(tmp_path / "i.safetensors")
+    assert calibrate_main(["imatrix", "--input", "random:tiny", "--tokens", "48", "--prompts", "2", "--out", ip]) == 0
+    assert torch.allclose(load_file(ip)["text.layers.0.mlp.down"], torch.diagonal(H["text.layers.0.mlp.down"]))
+    out = str(tmp_path / "m.r4dxb")
+    assert convert_main(["--input", "random:tiny", "--output", out, "--layers", "1", "--hessians", hp, "--selftest"]) == 0
