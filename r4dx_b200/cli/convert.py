@@ -28,6 +28,13 @@ def load_source(spec: str, layers: int, mtp: bool, seed: int):
         if layers:
             cfg.num_hidden_layers, cfg.layer_types = layers, cfg.layer_types[:layers]
         return cfg, init_weights(cfg, seed, with_mtp=mtp)
+    if spec.endswith(".gguf"):
+        from ..quant.gguf import import_gguf
+        cfg, w = import_gguf(spec)
+        if layers:
+            cfg.num_hidden_layers, cfg.layer_types = layers, cfg.layer_types[:layers]
+            w = {k: v for k, v in w.items() if not k.startswith("text.layers.") or int(k.split(".")[2]) < layers}
+        return cfg, w
     from safetensors import safe_open
     d = spec if os.path.isdir(spec) else os.path.dirname(spec)
     cfg_text = open(os.path.join(d, "config.json")).read()
