@@ -93,6 +93,10 @@ def convert_parser() -> argparse.ArgumentParser:
     ap.add_argument("--hessians", default=None,
                     help="safetensors file from `python -m r4dx_b200.quant.calibrate hessians`: linears found in it are quantized "
                          "with error compensation (block LDLQ for trellis, GPTQ for w4a16)")
+    ap.add_argument("--quant", default="rtn", choices=["rtn", "search"],
+                    help="w4a16 layout: round to nearest over the full group range, or search the clipping range per group")
+    ap.add_argument("--imatrix", default=None,
+                    help="safetensors file from `python -m r4dx_b200.quant.calibrate imatrix`: weighs the search by channel importance")
     ap.add_argument("--kv-calib", default=None, help="JSON file with per-layer k/v amax for fp8 descales")
     ap.add_argument("--reuse-tensors-from", default=None, help="older container whose identical tensors are copied, guarded by sha256")
     ap.add_argument("--selftest", action="store_true", help="re-open the output and verify every tensor's reconstruction error")

@@ -68,8 +68,12 @@ def main(argv=None) -> int:
     if args.hessians:
         from safetensors.torch import load_file
         hessians = {k: v for k, v in load_file(args.hessians).items() if v.dim() == 2}
+    imatrix = None
+    if args.imatrix:
+        from safetensors.torch import load_file
+        imatrix = {k: v for k, v in load_file(args.imatrix).items() if v.dim() == 1}
     q = quantize_weight_set(cfg, src, layout=layout, kb_rule=_kb_rule(args.kb_plan), head_group=args.lm_head_group, seed=args.seed,
-                            encoder=args.encoder, hessians=hessians)
+                            encoder=args.encoder, hessians=hessians, imatrix=imatrix, search=args.quant == "search")
     for k in list(q):
         if any(s in k for s in keep):
             q[k] = w[k].to(torch.bfloat16)

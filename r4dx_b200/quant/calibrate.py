@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import argparse
 import json
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -97,7 +97,12 @@ def gptq_w4a16(W: torch.Tensor, H: torch.Tensor, group: int = 64, damp: float = 
             err = (w - sd * (qk - zd)) / Hinv[k, k]
             if k + 1 < K:
                 W[:, k + 1:] -= err[:, None] * Hinv[k, k + 1:][None, :]
-    # pack: nibble i of word j is q for k = 8 j + i; wsz = fp16 scale | fp16 -(1024 + zero) << 16
+    return _pack_w4(q, scales, zeros, group)
+
+
+def _pack_w4(q: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, group: int) -> W4Weight:
+    """Nibble i of word j is q for k = 8 j + i; wsz = fp16 scale | fp16 -(1024 + zero) << 16."""
+    N, K = q.shape
     sh = (torch.arange(K) % 8) * 4
     wq = (q << sh[None, :]).view(N, K // 8, 8).sum(-1)
     wq = torch.where(wq >= 2 ** 31, wq - 2 ** 32, wq).to(torch.int32)
@@ -106,6 +111,41 @@ def gptq_w4a16(W: torch.Tensor, H: torch.Tensor, group: int = 64, damp: float = 
     wsz = s16 | (z16 << 16)
     wsz = torch.where(wsz >= 2 ** 31, wsz - 2 ** 32, wsz).to(torch.int32)
     return W4Weight(wq.contiguous(), wsz.contiguous(), N, K, group)
+
+
+def search_w4a16(W: torch.Tensor, importance: Optional[torch.Tensor] = None, group: int = 64, steps: int = 24,
+                 min_shrink: float = 0.55) -> W4Weight:
+    """Scale search for the w4a16 layout: per (row, group) the [lo, hi] range is shrunk by each of ``steps`` factors in
+    [min_shrink, 1] (values outside clip) and the factor with the lowest importance-weighted squared error is kept.
+    ``importance`` [K] is the per-input-channel second moment E[x_k^2] (the diagonal of the layer's Hessian, the
+    "imatrix"); None weighs all channels equally.  (reference: the converter's ``--quant search --imatrix`` mode,
+    src/convert/main.cpp:1-30.)"""
+    W = W.detach().float()
+    N, K = W.shape
+    imp = torch.ones(K) if importance is None else importance.float().clamp_min(0) + 1e-12 * float(importance.float().mean() + 1e-30)
+    G = K // group
+    w = W.view(N, G, group)
+    iw = imp.view(1, G, group)
+    lo0 = torch.minimum(w.amin(-1), torch.zeros(()))
+    hi0 = torch.maximum(w.amax(-1), torch.zeros(()))
+    best_err = torch.full((N, G), float("inf"))
+    best_scale = torch.ones(N, G)
+    best_zero = torch.zeros(N, G)
+    best_q = torch.zeros(N, G, group, dtype=torch.int64)
+    for f in torch.linspace(1.0, min_shrink, steps).tolist():
+        lo, hi = lo0 * f, hi0 * f
+        scale = (hi - lo) / 15.0
+        scale = torch.where(scale > 0, scale, torch.ones_like(scale)).to(torch.float16).float()
+        scale = torch.where(scale > 0, scale, torch.full_like(scale, 2.0 ** -24))
+        zero = torch.round(-lo / scale).clamp(0, 15)
+        q = (torch.round(w / scale[..., None]) + zero[..., None]).clamp(0, 15)
+        err = (((q - zero[..., None]) * scale[..., None] - w) ** 2 * iw).sum(-1)
+        better = err < best_err
+        best_err = torch.where(better, err, best_err)
+        best_scale = torch.where(better, scale, best_scale)
+        best_zero = torch.where(better, zero, best_zero)
+        best_q = torch.where(better[..., None], q.long(), best_q)
+    return _pack_w4(best_q.view(N, K), best_scale, best_zero, group)
 
 
 def main(argv=None) -> int:

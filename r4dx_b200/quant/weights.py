@@ -46,13 +46,17 @@ def is_quantized_linear(name: str) -> bool:
 
 def quantize_weight_set(cfg: ModelConfig, w: Dict[str, torch.Tensor], layout: str = "trellis",
                         kb_rule: Callable[[str], int] = default_kb_rule, head_group: int = 64,
-                        seed: int = 0, encoder: str = "cpu", hessians: Optional[Dict[str, torch.Tensor]] = None) -> Dict[str, object]:
+                        seed: int = 0, encoder: str = "cpu", hessians: Optional[Dict[str, torch.Tensor]] = None,
+                        imatrix: Optional[Dict[str, torch.Tensor]] = None, search: bool = False) -> Dict[str, object]:
     """fp32 weights -> quantized set.  layout: trellis | w4a16 | bf16.  ``encoder``: where the Viterbi search of the
     trellis layout runs - "cpu" (threads) or "cuda" (one CTA per tile, ~25x the throughput of 32 host threads); the
     result lives on the CPU either way.  ``hessians``: name -> [K, K] input second moments; linears that have one are
-    quantized with error compensation (block LDLQ for the trellis layout, GPTQ for w4a16) on the host."""
+    quantized with error compensation (block LDLQ for the trellis layout, GPTQ for w4a16) on the host.  ``search`` /
+    ``imatrix`` (name -> [K] input second moments): the w4a16 layout picks each group's range by a clipping search, weighted
+    by the channel importances where given."""
     out: Dict[str, object] = {}
     hessians = hessians or {}
+    imatrix = imatrix or {}
     for i, (name, t) in enumerate(w.items()):
         leaf = name.split(".")[-1]
         if name == "lm_head":
@@ -69,6 +73,9 @@ def quantize_weight_set(cfg: ModelConfig, w: Dict[str, torch.Tensor], layout: st
             if name in hessians:
                 from .calibrate import gptq_w4a16
                 out[name] = gptq_w4a16(t, hessians[name], head_group)
+            elif search or name in imatrix:
+                from .calibrate import search_w4a16
+                out[name] = search_w4a16(t, imatrix.get(name), head_group)
             else:
                 out[name] = w4a16.quantize(t, head_group)
         elif leaf in F32_NAMES:

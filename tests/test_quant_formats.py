@@ -266,3 +266,30 @@ def test_converter_uses_hessians_when_given(tmp_path):
     assert torch.allclose(load_file(ip)["text.layers.0.mlp.down"], torch.diagonal(H["text.layers.0.mlp.down"]))
     out = str(tmp_path / "m.r4dxb")
     assert convert_main(["--input", "random:tiny", "--output", out, "--layers", "1", "--hessians", hp, "--selftest"]) == 0
+
+
+def test_w4a16_scale_search_beats_round_to_nearest_under_the_importance_weights(tmp_path):
+    import torch
+    from r4dx_b200.quant import w4a16
+    from r4dx_b200.quant.calibrate import search_w4a16
+    g = torch.Generator().manual_seed(5)
+    W = torch.randn(64, 256, generator=g) * 0.02
+    W[:, ::37] *= 6.0                                    # outliers stretch the full-range scale
+    imp = torch.rand(256, generator=g) ** 4 + 1e-3
+    imp[::37] = 1e-4                                     # ... on channels that barely matter
+
+    def werr(q):
+        return float((((w4a16.dequantize(q) - W) ** 2) * imp[None, :]).sum())
+
+    rtn = w4a16.quantize(W, 64)
+    flat = search_w4a16(W, None, 64)
+    weighted = search_w4a16(W, imp, 64)
+    assert float(((w4a16.dequantize(flat) - W) ** 2).sum()) <= float(((w4a16.dequantize(rtn) - W) ** 2).sum()) * 1.0001
+    assert werr(weighted) < 0.8 * werr(rtn) and werr(weighted) <= werr(flat) * 1.0001
+    # through the converter
+    from r4dx_b200.cli.convert import main as convert_main
+    from r4dx_b200.quant.calibrate import main as calibrate_main
+    ip = str(tmp_path / "i.safetensors")
+    assert calibrate_main(["imatrix", "--input", "random:tiny", "--tokens", "32", "--prompts", "1", "--out", ip]) == 0
+    assert convert_main(["--input", "random:tiny", "--output", str(tmp_path / "m.r4dxb"), "--layers", "1", "--layouts", "w4a16",
+                         "--quant", "search", "--imatrix", ip, "--selftest"]) == 0
