@@ -122,6 +122,11 @@ class ModelConfig:
         return self.layer_types[i] == "conv"
 
     @property
+    def conv_channels(self) -> int:
+        """Channels of a short-conv mixer held by this rank (the hidden width split over the tensor-parallel ranks)."""
+        return self.hidden_size // self.tp_world
+
+    @property
     def has_conv_layers(self) -> bool:
         return any(t == "conv" for t in self.layer_types)
 
@@ -166,8 +171,8 @@ class ModelConfig:
             raise ValueError("shard() must be called on the global config")
         if world == 1:
             return dataclasses.replace(self)
-        if self.has_conv_layers:
-            raise NotImplementedError("tensor-parallel sharding of short-conv layers")
+        if self.has_conv_layers and (self.hidden_size // world) % 128:
+            raise ValueError("per-rank short-conv channels must stay a multiple of 128")
         c = dataclasses.replace(self, tp_world=world, tp_rank=rank)
 
         def div(v: int, what: str) -> int:
@@ -195,6 +200,11 @@ class ModelConfig:
             raise ValueError("vocab shard must be a multiple of 16 rows")
         if self.shared_expert_intermediate_size:
             c.shared_expert_intermediate_size = div(self.shared_expert_intermediate_size, "shared expert")
+        if self.has_conv_layers and self.num_experts:
+            # the short-conv MoE family splits every expert's inner width over the ranks (all experts on every rank)
+            c.moe_intermediate_size = div(self.moe_intermediate_size, "moe_intermediate_size")
+            if c.moe_intermediate_size % 128:
+                raise ValueError("per-rank moe_intermediate_size must stay a multiple of 128")
         return c
 
     def kv_head_of_rank(self) -> int:

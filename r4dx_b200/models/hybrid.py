@@ -156,7 +156,7 @@ class HybridModel:
             if cfg.is_attention_layer(i):
                 self.kv[i] = torch.zeros(nblk, Hkv, 2, KV_BLOCK, D, dtype=torch.uint8, device=dev)
             elif cfg.is_conv_layer(i):
-                self.ring[i] = torch.zeros(32, H, dtype=BF, device=dev)             # B * x rows keyed by position & 31
+                self.ring[i] = torch.zeros(32, cfg.conv_channels, dtype=BF, device=dev)   # B * x rows keyed by position & 31
             else:
                 self.gdn_state[i] = torch.zeros(Hv, Dg, Dg, dtype=torch.float32, device=dev)
                 self.ring[i] = torch.zeros(CONV_RING, cfg.conv_dim, dtype=BF, device=dev)
@@ -247,7 +247,7 @@ class HybridModel:
         """Gated short-convolution mixer: in_proj (RMSNorm in its prologue) -> C * fir(B * x) -> out_proj + residual."""
         cfg, b, w = self.cfg, self.buf, self.w
         p = f"text.layers.{i}.conv."
-        H = cfg.hidden_size
+        H = cfg.conv_channels                  # this rank's channel block; out_proj is row-parallel over it
         bcx = b.mixed.view(-1)[:T * 3 * H].view(T, 3 * H)
         self.lin[p + "in_proj"](b.x[:T], out=bcx, prologue=K.PRO_RMSNORM, norm_w=w[f"text.layers.{i}.input_layernorm"],
                                 eps=cfg.rms_norm_eps)
@@ -281,6 +281,13 @@ class HybridModel:
             K.rmsnorm(b.x[:T], w[f"text.layers.{i}.post_attention_layernorm"], cfg.rms_norm_eps, out=b.h[:T])
             if self.comm is not None and hasattr(self.comm, "moe_forward"):
                 self.comm.moe_forward(self.moe[i], b.h[:T], b.x[:T], T)
+            elif self.comm is not None and self.comm.world > 1:
+                # tensor-parallel experts (every rank holds a slice of every expert's inner width): the routed sum is a
+                # partial product, summed over the ranks before it joins the residual stream
+                part = b.core.view(-1)[:T * cfg.hidden_size].view(T, cfg.hidden_size)
+                self.moe[i].forward(b.h[:T], part, T, residual=False)
+                self.comm.all_reduce_rows(part)
+                K.residual_add(b.x[:T], part)
             else:
                 self.moe[i].forward(b.h[:T], b.x[:T], T)
             return
@@ -448,9 +455,10 @@ class HybridModel:
                 self._row_parallel_chunk(self.lin[pa + "o"], core, x, cb, post_norm=w.get(p + "post_attn_out_norm"))
             elif cfg.is_conv_layer(i):
                 pc = p + "conv."
-                bcx = cb["mixed"][:T * 3 * H].view(T, 3 * H)
+                Hc = cfg.conv_channels
+                bcx = cb["mixed"][:T * 3 * Hc].view(T, 3 * Hc)
                 self.lin[pc + "in_proj"].chunk(h, cb["xh"], bcx)
-                core = cb["core"][:T * H].view(T, H)
+                core = cb["core"][:T * Hc].view(T, Hc)
                 K.short_conv(bcx, w[pc + "weight"], self.ring[i], cb["positions"], core, T)
                 self._row_parallel_chunk(self.lin[pc + "out_proj"], core, x, cb)
             else:
@@ -493,6 +501,7 @@ class HybridModel:
                 e = min(T, s + R)
                 self.comm.moe_forward(self.moe[i], h[s:e], x[s:e], e - s)
             return
+        tp = self.comm is not None and self.comm.world > 1
         from .moe import MoeBlock
         blk = self._moe_chunk_blocks.get(i) if hasattr(self, "_moe_chunk_blocks") else None
         if blk is None or blk.logits.shape[0] < T:
@@ -510,7 +519,13 @@ class HybridModel:
                 blk = MoeBlock(self.cfg, self.w, i, self.device, self._cb["C"], self.moe[i].e_begin, self.moe[i].e_count,
                                share_from=self.moe[i])
             self._moe_chunk_blocks[i] = blk
-        blk.forward(h, x, T, exact_rows=True)
+        if tp:
+            part = self._cb["core"][:T * self.cfg.hidden_size].view(T, self.cfg.hidden_size)
+            blk.forward(h, part, T, exact_rows=True, residual=False)
+            self.comm.all_reduce_rows(part)
+            K.residual_add(x, part)
+        else:
+            blk.forward(h, x, T, exact_rows=True)
 
     def _row_parallel_chunk(self, lin: Linear, inp: torch.Tensor, x: torch.Tensor, cb: dict,
                             fused_silu_mul: bool = False, gelu: bool = False, post_norm=None) -> None:

@@ -123,14 +123,15 @@ class MoeBlock:
             K.trellis_gemv(self.shared_down, self.sh_gu[s:e], out=self.sh_out[s:e], prologue=K.PRO_SILU_MUL)
         K.bf16_gemv(self.shared_gate, h, out=self.sh_gate[:T])
 
-    def forward(self, h: torch.Tensor, x: torch.Tensor, T: int, exact_rows: bool = False) -> None:
+    def forward(self, h: torch.Tensor, x: torch.Tensor, T: int, exact_rows: bool = False, residual: bool = True) -> None:
         """x[T, H] += moe(h) (h = post-attention RMSNorm of x).  ``exact_rows``: read the plan's largest per-expert row
         count back (one small copy) and run exactly as many passes as it needs - the prefill path, where one expert
         can receive hundreds of rows."""
         self.route(h, T)
         self.experts(h, T, self.max_rows_of_an_expert() if exact_rows else None)
         self.shared(h, T)
-        K.moe_combine(self.y_pairs, self.ids, self.wts, self.sh_out, self.sh_gate, x, x, T, self.cfg.hidden_size, self.k)
+        K.moe_combine(self.y_pairs, self.ids, self.wts, self.sh_out, self.sh_gate, x if residual else None, x, T,
+                      self.cfg.hidden_size, self.k)
 
     def max_rows_of_an_expert(self) -> int:
         """Largest per-expert row count of the latest plan (one device read; for overflow checks of ``cap``)."""

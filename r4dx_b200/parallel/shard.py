@@ -5,7 +5,9 @@ Rules (reference: src/model/tp/tp_shard.h:37-107, generalised beyond world 2):
       attn.qg (per-head q|gate rows), attn.k / attn.v (KV heads; replicated when world > KV heads),
       gdn.in_proj_qkv ([q | k | v] segments), gdn.in_proj_z, gdn.in_proj_a/b, gdn.conv1d_weight,
       mlp.gate_up ([gate | up] segments), lm_head (vocab rows)
-  row-parallel (K split): attn.o, gdn.out_proj, mlp.down
+      conv.in_proj ([B | C | x] segments, the rank's channel block of each), conv.weight,
+      moe.experts.E.gate_up of the short-conv MoE family ([gate | up] segments; every rank keeps all experts)
+  row-parallel (K split): attn.o, gdn.out_proj, conv.out_proj, mlp.down, moe.experts.E.down (short-conv MoE family)
   replicated: embeddings, norms
 Trellis tensors split only at multiples of 128 in either dimension, so a shard is a set of whole
 128-row blocks (column-parallel) or a contiguous K range inside every block (row-parallel); the
@@ -110,6 +112,16 @@ def shard_plan(cfg: ModelConfig, world: int, rank: int) -> Dict[str, tuple]:
         "mlp.gate_up": ("rows", [(rank * isz, (rank + 1) * isz), (I + rank * isz, I + (rank + 1) * isz)]),
         "mlp.down": ("cols",),
     }
+    if c.has_conv_layers:
+        H, hc = c.hidden_size, c.hidden_size // world
+        plan["conv.in_proj"] = ("rows", [(s_ * H + rank * hc, s_ * H + (rank + 1) * hc) for s_ in range(3)])
+        plan["conv.weight"] = ("rows", [(rank * hc, (rank + 1) * hc)])
+        plan["conv.out_proj"] = ("cols",)
+        if c.num_experts:
+            MI = c.moe_intermediate_size
+            mi = MI // world
+            plan["moe.expert.gate_up"] = ("rows", [(rank * mi, (rank + 1) * mi), (MI + rank * mi, MI + (rank + 1) * mi)])
+            plan["moe.expert.down"] = ("cols",)
     return plan
 
 
@@ -125,7 +137,9 @@ def shard_weight_set(cfg: ModelConfig, w: Dict[str, object], world: int, rank: i
             out[name] = slice_rows(t, [(rank * vs, (rank + 1) * vs)])
             continue
         rule = None
-        for suffix, r in plan.items():
+        if ".moe.experts." in name and "moe.expert.gate_up" in plan:
+            rule = plan["moe.expert." + name.rsplit(".", 1)[1]]
+        for suffix, r in ([] if rule is not None else plan.items()):
             if name.endswith("." + suffix):
                 rule = r
                 break

@@ -20,14 +20,19 @@ def main() -> None:
     ap.add_argument("--ctx", type=int, default=8192)
     ap.add_argument("--steps", type=int, default=1)
     ap.add_argument("--rows", type=int, default=1)
-    ap.add_argument("--model", default="27b", choices=["27b", "small"])
+    ap.add_argument("--model", default="27b", choices=["27b", "small", "lfm2"])
     ap.add_argument("--prefill", type=int, default=0, help="profile one chunked prefill of this many tokens instead of decode steps")
     a = ap.parse_args()
-    from r4dx_b200.config import qwen_hybrid_27b_config, small_hybrid_config
+    from r4dx_b200.config import lfm2_moe_config, qwen_hybrid_27b_config, small_hybrid_config
     from r4dx_b200.models.hybrid import HybridModel
     from r4dx_b200.quant.weights import synthetic_weight_set
-    cfg = qwen_hybrid_27b_config(a.layers) if a.model == "27b" else small_hybrid_config(a.layers)
-    w = synthetic_weight_set(cfg, device="cuda", seed=0)
+    if a.model == "lfm2":
+        from r4dx_b200.quant.weights import moe_kb_rule
+        cfg = lfm2_moe_config(layers=min(a.layers, 40))
+        w = synthetic_weight_set(cfg, device="cuda", seed=0, kb_rule=moe_kb_rule)
+    else:
+        cfg = qwen_hybrid_27b_config(a.layers) if a.model == "27b" else small_hybrid_config(a.layers)
+        w = synthetic_weight_set(cfg, device="cuda", seed=0)
     m = HybridModel(cfg, w, max_ctx=max(a.ctx, a.prefill) + 64 + a.rows * (a.steps + 2))
     if a.prefill:
         ids = torch.randint(0, cfg.vocab_size, (a.prefill,), dtype=torch.int32)
