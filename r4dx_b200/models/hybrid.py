@@ -513,7 +513,8 @@ class HybridModel:
                 blk = MoeBlock.__new__(MoeBlock)
                 blk.__dict__.update(first.__dict__)
                 src = self.moe[i]
-                for name in ("gate_up", "down", "router", "shared_gate", "shared_gu", "shared_down", "expert_bias", "e_begin", "e_count", "ks_gu", "ks_dn"):
+                for name in ("gate_up", "down", "router", "shared_gate", "shared_gu", "shared_down", "expert_bias", "e_begin", "e_count", "ks_gu", "ks_dn",
+                             "ks_gu_few", "ks_dn_few"):
                     setattr(blk, name, getattr(src, name))
             else:
                 blk = MoeBlock(self.cfg, self.w, i, self.device, self._cb["C"], self.moe[i].e_begin, self.moe[i].e_count,

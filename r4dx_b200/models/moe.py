@@ -10,6 +10,8 @@ the same grouped kernels run on each rank's expert slice and the combine sums ac
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import Dict, Optional
 
@@ -83,6 +85,12 @@ class MoeBlock:
         self.sh_gate = z(R, 1, dtype=torch.float32) if self.has_shared else None
         self.ks_gu = K.pick_ksplit(self.gate_up.N, self.gate_up.K, target_ctas=1)
         self.ks_dn = K.pick_ksplit(self.down.N, self.down.K, target_ctas=1)
+        # one or two rows in flight touch at most k experts each: k * N/128 CTAs leave most of the 148 SMs idle (4 experts of
+        # the short-conv MoE geometry: 96 CTAs), so those calls split K over a cluster until about two CTAs per SM exist
+        few = int(os.environ.get("R4DXB_MOE_KSPLIT_TARGET", "296"))
+        per_expert = max(1, (few + self.k - 1) // self.k)
+        self.ks_gu_few = K.pick_ksplit(self.gate_up.N, self.gate_up.K, target_ctas=per_expert)
+        self.ks_dn_few = K.pick_ksplit(self.down.N, self.down.K, target_ctas=per_expert)
 
     def route(self, h: torch.Tensor, T: int) -> None:
         K.bf16_gemv(self.router, h, out=self.logits[:T])
@@ -101,10 +109,11 @@ class MoeBlock:
         tmax = self.tmax if T <= 4 else 8
         n_pass = ((max_rows if max_rows is not None else min(T, self.cap)) + tmax - 1) // tmax
         g, d = self.gate_up, self.down
+        ks_gu, ks_dn = (self.ks_gu_few, self.ks_dn_few) if T <= 2 else (self.ks_gu, self.ks_dn)
         K.trellis_gemv_grouped(g.words, g.suh, g.svh, h, self.gu_pairs, self.offsets, self.perm, self.k, n_pass, tmax,
-                               K.PRO_NONE, g.E, g.N, g.K, g.kb, self.ks_gu)
+                               K.PRO_NONE, g.E, g.N, g.K, g.kb, ks_gu)
         K.trellis_gemv_grouped(d.words, d.suh, d.svh, self.gu_pairs, self.y_pairs, self.offsets, self.perm, 1, n_pass, tmax,
-                               K.PRO_SILU_MUL, d.E, d.N, d.K, d.kb, self.ks_dn)
+                               K.PRO_SILU_MUL, d.E, d.N, d.K, d.kb, ks_dn)
 
     def shared(self, h: torch.Tensor, T: int) -> None:
         if not self.has_shared:
