@@ -22,7 +22,7 @@ def main():
     from r4dx_b200.parallel.shard import shard_weight_set
     from r4dx_b200.parallel.tp_comm import make_comm
     from r4dx_b200.quant.weights import moe_kb_rule, synthetic_weight_set
-    gcfg = lfm2_moe_config(hidden=512, layers=4, heads=8, kv_heads=2, head_dim=64, intermediate=1024, experts=8, top_k=2,
+    gcfg = lfm2_moe_config(hidden=512, layers=4, heads=8, kv_heads=4, head_dim=64, intermediate=1024, experts=8, top_k=2,
                            moe_intermediate=256, dense_layers=1, vocab=8192, attention_layers=(2,))
     full = synthetic_weight_set(gcfg, device=dev, seed=5, sigma=0.05, kb_rule=moe_kb_rule)
     for i in range(gcfg.num_dense_layers, gcfg.num_hidden_layers):
