@@ -16,6 +16,8 @@ def add_model_flags(ap: argparse.ArgumentParser) -> None:
     g.add_argument("--prefill-chunk", type=int, default=int(os.environ.get("R4DXB_PREFILL_CHUNK", "0")),
                    help="rows per prefill chunk (0: chosen from the prompt length)")
     g.add_argument("--mtp", type=int, default=0, metavar="K", help="MTP speculative decoding with K drafts per round")
+    g.add_argument("--ngram", type=int, default=0, metavar="K",
+                   help="n-gram (prompt-lookup) speculative decoding with up to K drafts per round; needs no drafter weights")
     g.add_argument("--dflash", default=None, metavar="CONTAINER", help="block-diffusion drafter container")
     g.add_argument("--dflash-k", type=int, default=7)
     g.add_argument("--dflash-p-min", type=float, default=0.0)

@@ -52,6 +52,9 @@ def load_text_model(args, device: Optional[str] = None):
     if args.mtp > 0 and any(k.startswith("mtp.") for k in weights):
         from ..models.mtp import MtpDrafter
         drafter = MtpDrafter(model, weights)
+    if getattr(args, "ngram", 0) > 0 and drafter is None:
+        from ..models.ngram import NgramDrafter
+        drafter = NgramDrafter()
     if getattr(args, "dflash", None):
         from ..models.dflash import DflashDrafter, load_dflash
         dcfg, dweights = load_dflash(args.dflash)

@@ -29,8 +29,11 @@ def run_turn(tm, tk, prompt_ids, args, rng, out=sys.stdout):
         out.write(dec.feed(tok)); out.flush()
         if not pending:
             rounds += 1
-            if args.mtp > 0 and params.greedy:
-                pending = tm.decode_step_spec_greedy(tok, args.mtp)
+            spec_k = args.mtp or getattr(args, "ngram", 0) or (args.dflash_k if getattr(args, "dflash", None) else 0)
+            if spec_k > 0 and params.greedy:
+                pending = tm.decode_step_spec_greedy(tok, spec_k)
+            elif spec_k > 0:
+                pending = tm.decode_step_spec_sampled(tok, spec_k, params, rng, list(prompt_ids) + ids[:-1])
             elif params.greedy:
                 pending = [tm.decode_step_greedy(tok)]
             else:

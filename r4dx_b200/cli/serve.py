@@ -40,7 +40,7 @@ def main(argv=None) -> int:
     defaults = {"temperature": args.default_temperature, "top_k": args.default_top_k, "top_p": args.default_top_p,
                 "min_p": args.default_min_p, "repetition_penalty": args.default_repetition_penalty}
     srv = ApiServer(eng, tk, tpl, tm.model_id, host=args.host, port=args.port, max_tokens_default=args.max_tokens_default,
-                    defaults=defaults, spec_k=args.mtp, vision_config=vcfg, image_token_id=image_id)
+                    defaults=defaults, spec_k=args.mtp or getattr(args, "ngram", 0), vision_config=vcfg, image_token_id=image_id)
     print(f"[r4dxb-server] {tm.model_id} on http://{args.host}:{srv.port} (tp={tm.tp_world()})", file=sys.stderr)
     try:
         srv.serve_forever()

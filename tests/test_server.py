@@ -291,3 +291,49 @@ def test_sampled_speculation_emits_the_same_stream_as_plain_sampled_decode():
         toks, model = run(fn, 3)
         assert toks == plain, (fn.__name__, toks, plain)
         assert model.history[:3 + len(plain) - 1] == ([5, 9, 11] + plain)[:3 + len(plain) - 1]
+
+
+def test_ngram_drafter_proposes_what_followed_the_latest_match_and_stays_lossless():
+    from r4dx_b200.models.ngram import NgramDrafter, NgramIndex, simulate
+    ix = NgramIndex(2, 3)
+    ix.extend([1, 2, 3, 4, 5, 9, 1, 2, 3])
+    assert ix.propose(3) == [4, 5, 9]                  # the earlier "1 2 3" was followed by 4 5 9
+    ix.extend([7, 8, 2, 3])
+    assert ix.propose(2) == [7, 8]                     # the LATEST earlier "2 3" wins
+    assert NgramIndex(2, 3).propose(4) == []
+    # drafter protocol: anchor fed by draft(), accepted drafts by after_verify()
+    d = NgramDrafter(2, 4)
+    d.after_prefill([5, 6, 7, 8, 5, 6], 7)
+    assert d.draft(7, 3) == [8, 5, 6]
+    d.after_verify(7, [8, 5, 6], [8, 5, 0])            # two accepted, then a correction
+    assert d.index.tokens == [5, 6, 7, 8, 5, 6, 7, 8, 5]
+    # a stream that repeats a 6-token phrase saves most of the target calls; a random one saves nothing
+    rep = [3, 1, 4, 1, 5, 9] * 12
+    s = simulate(rep, 12, k=4)
+    assert s["calls_saved_frac"] > 0.6 and s["accepted_per_call"] > 2.0
+    import random
+    rnd = random.Random(0)
+    noise = [rnd.randrange(50000) for _ in range(200)]
+    assert simulate(noise, 20, k=4)["calls_saved_frac"] < 0.05
+    # through the engine's sampled speculative path the stream equals plain sampled decode
+    model = FakeTextModel(vocab=16)                    # a small vocabulary repeats itself: the drafter gets matches
+    nd = NgramDrafter(1, 3)
+
+    def draft_fn(history, token, k):
+        ix2 = NgramIndex(1, 3)
+        ix2.extend(history + [token])
+        return ix2.propose(k)
+
+    def run(fn):
+        m = FakeTextModel(vocab=16)
+        m.draft_fn = fn
+        eng = Engine(m, ByteTokenizer(300))
+        r = eng.generate(GenRequest(prompt_ids=[1, 2, 3, 1, 2], max_tokens=40, params=SampleParams(temperature=0.3, top_k=3, seed=3),
+                                    spec_k=3 if fn else 0), timeout=20)
+        eng.shutdown()
+        assert r.error is None, r.error
+        return r.token_ids, m.calls
+
+    plain, calls_plain = run(None)
+    spec, calls_spec = run(draft_fn)
+    assert spec == plain and calls_spec <= calls_plain
