@@ -111,6 +111,11 @@ class HybridModel:
         """``layer_range`` = (first, end): a pipeline stage that runs only those layers (embedding with the
         first stage, head with the last)."""
         cfg.validate() if cfg.tp_world == 1 else None
+        if cfg.has_conv_layers and comm is not None and comm.world > 1 and os.environ.get("R4DXB_UNVALIDATED_TP") != "1":
+            # the sharding of this family is checked on the CPU (shards add up to the unsharded block); its only two-GPU run
+            # did not finish within its time limit and the cause has not been found, so the path stays closed by default
+            raise NotImplementedError("tensor-parallel execution of the short-conv family is not validated on GPUs yet "
+                                      "(set R4DXB_UNVALIDATED_TP=1 to run it anyway)")
         self.cfg = cfg
         self.device = torch.device(device)
         self.comm = comm                       # tensor-parallel communicator (None = single rank)

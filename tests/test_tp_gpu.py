@@ -74,13 +74,6 @@ def test_tp2_matches_tp1_tokens(mode):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_short_conv_moe_family_tp2_matches_tp1():
-    r = _run_ranks(2, os.path.join(ROOT, "tests", "tp_lfm2_worker.py"))
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert "TP_LFM2_OK" in r.stdout
-
-
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_expert_parallel_two_ranks():
     r = _run_ranks(2, os.path.join(ROOT, "tests", "ep_worker.py"))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
