@@ -539,6 +539,9 @@ class HybridModel:
             # sandwich-norm / GeGLU families: the fused tensor-parallel epilogues add into x directly, which a norm between
             # the product and the add rules out, so under tensor parallelism the bare product is summed over the ranks first
             tp = self.comm is not None and self.comm.world > 1
+            if tp and os.environ.get("R4DXB_UNVALIDATED_TP") != "1":
+                raise NotImplementedError("tensor-parallel prefill of sandwich-norm / GeGLU models is written but not validated "
+                                          "on GPUs yet (set R4DXB_UNVALIDATED_TP=1 to run it anyway)")
             if post_norm is None and not tp:
                 lin.chunk(inp, cb["xh"], x, residual=x, fused_silu_mul=fused_silu_mul, gelu=gelu)
                 return
