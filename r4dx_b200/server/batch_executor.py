@@ -17,7 +17,7 @@ from typing import Callable, Dict, List, Optional, Protocol, Sequence
 from ..runtime.sampler import Rng, sample_canonical
 from ..runtime.tokenizer import StreamDecoder
 from .engine import GenRequest, GenResult, QueueFull, _Job
-from .parsers import QwenToolCallParser, ReasoningSplitter
+from .parsers import ReasoningSplitter, detect_dialect, make_tool_call_parser
 from .request_log import RequestLog
 
 
@@ -63,11 +63,11 @@ class FakeBatchBackend:
 
 
 class _Active:
-    def __init__(self, job: _Job, slot: int, tk):
+    def __init__(self, job: _Job, slot: int, tk, dialect: str = "qwen"):
         self.job, self.slot = job, slot
         self.dec = StreamDecoder(tk)
         self.splitter = ReasoningSplitter()
-        self.tools = QwenToolCallParser() if job.req.parse_tools else None
+        self.tools = make_tool_call_parser(dialect) if job.req.parse_tools else None
         self.rng = Rng(job.req.params.seed)
         self.text_all = ""
         self.next_token = 0
@@ -194,7 +194,8 @@ class BatchEngine:
         t0 = time.perf_counter()
         first = self.backend.import_slot(slot, req.prompt_ids)
         res.prefill_ms = (time.perf_counter() - t0) * 1e3
-        a = _Active(job, slot, self.tk)
+        cfg = getattr(self.backend, "config", None)
+        a = _Active(job, slot, self.tk, detect_dialect(getattr(self.backend, "model_id", ""), getattr(cfg, "arch", "")))
         if self._consume(a, first, eos):
             self._finish(a)
             raise_slot_free = True

@@ -19,7 +19,7 @@ from ..runtime.prefix_state import PrefixState
 from ..runtime.sampler import Rng, SampleParams
 from ..runtime.text_model import ModelStateError, TextModel
 from ..runtime.tokenizer import StreamDecoder
-from .parsers import QwenToolCallParser, ReasoningSplitter
+from .parsers import ReasoningSplitter, detect_dialect, make_tool_call_parser
 from .request_log import RequestLog
 
 
@@ -167,7 +167,8 @@ class Engine:
 
         dec = StreamDecoder(self.tk)
         splitter = ReasoningSplitter()
-        tools = QwenToolCallParser() if req.parse_tools else None
+        dialect = detect_dialect(getattr(m, "model_id", ""), getattr(getattr(m, "config", None), "arch", ""))
+        tools = make_tool_call_parser(dialect) if req.parse_tools else None
         eos = set(getattr(self.tk, "eos_ids", []))
         fed = list(prompt)
         text_all = ""

@@ -118,6 +118,319 @@ class QwenToolCallParser:
         return piece
 
 
+class _Incomplete(Exception):
+    """The span ran out of text before it was closed: wait for more."""
+
+
+class _Malformed(Exception):
+    """The span cannot be a tool call: it degrades to literal content."""
+
+
+class _Cursor:
+    def __init__(self, s: str, at: int = 0):
+        self.s, self.p = s, at
+
+    def ws(self) -> None:
+        while self.p < len(self.s) and self.s[self.p].isspace():
+            self.p += 1
+
+    def peek(self) -> str:
+        if self.p >= len(self.s):
+            raise _Incomplete()
+        return self.s[self.p]
+
+    def startswith(self, t: str) -> bool:
+        """True if ``t`` is next; raises _Incomplete if the text ends inside a possible ``t``."""
+        rest = self.s[self.p:self.p + len(t)]
+        if rest == t:
+            return True
+        if len(rest) < len(t) and t.startswith(rest):
+            raise _Incomplete()
+        return False
+
+    def expect(self, t: str) -> None:
+        if not self.startswith(t):
+            raise _Malformed()
+        self.p += len(t)
+
+    def word(self, stop: str) -> str:
+        a = self.p
+        while self.p < len(self.s) and self.s[self.p] not in stop and not self.s[self.p].isspace():
+            self.p += 1
+        if self.p >= len(self.s):
+            raise _Incomplete()
+        return self.s[a:self.p]
+
+
+def _bare(word: str):
+    low = {"true": True, "false": False, "null": None, "True": True, "False": False, "None": None}
+    if word in low:
+        return low[word], True
+    try:
+        return (int(word) if re.fullmatch(r"[-+]?\d+", word) else float(word)), True
+    except ValueError:
+        return word, False
+
+
+class SpanToolCallParser:
+    """Streaming extraction of tool calls written between an opening and a closing marker.  The span is parsed by
+    recursive descent from the opening marker (not by searching for the closing marker), so a string argument that contains
+    the closing marker does not end the call early.  A span that cannot be a call is passed through as literal content,
+    markers included, and ``had_malformed_call`` is set (reference: src/server/gemma_tool_call_parser.cpp:1-16,
+    src/server/lfm2_tool_call_parser.cpp:1-25)."""
+
+    OPEN = ""
+    CLOSE = ""
+    MAX_DEPTH = 64
+
+    def __init__(self):
+        self.buf = ""
+        self.calls: List[Dict] = []
+        self.had_malformed_call = False
+
+    def parse_span(self, c: _Cursor) -> List[Tuple[str, Dict]]:
+        raise NotImplementedError
+
+    def feed(self, delta: str) -> str:
+        self.buf += delta
+        out = ""
+        while self.buf:
+            i = self.buf.find(self.OPEN)
+            if i < 0:
+                hold = 0
+                for k in range(min(len(self.OPEN) - 1, len(self.buf)), 0, -1):
+                    if self.OPEN.startswith(self.buf[-k:]):
+                        hold = k
+                        break
+                out += self.buf[:len(self.buf) - hold]
+                self.buf = self.buf[len(self.buf) - hold:]
+                break
+            out += self.buf[:i]
+            self.buf = self.buf[i:]
+            c = _Cursor(self.buf, len(self.OPEN))
+            try:
+                found = self.parse_span(c)
+                c.ws()
+                c.expect(self.CLOSE)
+            except _Incomplete:
+                break                                   # wait for the rest of the span
+            except (_Malformed, RecursionError):
+                self.had_malformed_call = True
+                out += self.OPEN                        # literal content; what follows is scanned again
+                self.buf = self.buf[len(self.OPEN):]
+                continue
+            for name, args in found:
+                self.calls.append({"id": "call_" + uuid.uuid4().hex[:24], "type": "function",
+                                   "function": {"name": name, "arguments": json.dumps(args, ensure_ascii=False)}})
+            self.buf = self.buf[c.p:]
+        return out
+
+    def flush(self) -> str:
+        piece, self.buf = self.buf, ""
+        if piece.startswith(self.OPEN) and self.OPEN:
+            self.had_malformed_call = True              # a generation cut off inside a call
+        return piece
+
+
+class GemmaToolCallParser(SpanToolCallParser):
+    """``<|tool_call>call:NAME{key:value,key2:<|"|>text<|"|>,obj:{a:1},list:[1,<|"|>x<|"|>]}<tool_call|>``: bare keys
+    (a key wrapped in the string delimiter is accepted too), strings between ``<|"|>`` markers with raw text inside, bare
+    numbers / true / false / null, any other bare word kept as a string."""
+
+    OPEN, CLOSE, ESC = "<|tool_call>", "<tool_call|>", '<|"|>'
+
+    def parse_span(self, c: _Cursor):
+        c.ws()
+        c.expect("call:")
+        name = c.word("{")
+        if not name:
+            raise _Malformed()
+        c.ws()
+        return [(name, self._object(c, 0))]
+
+    def _string(self, c: _Cursor) -> str:
+        c.expect(self.ESC)
+        j = c.s.find(self.ESC, c.p)
+        if j < 0:
+            raise _Incomplete()
+        text, c.p = c.s[c.p:j], j + len(self.ESC)
+        return text
+
+    def _value(self, c: _Cursor, depth: int):
+        if depth > self.MAX_DEPTH:
+            raise _Malformed()
+        c.ws()
+        if c.startswith(self.ESC):
+            return self._string(c)
+        ch = c.peek()
+        if ch == "{":
+            return self._object(c, depth + 1)
+        if ch == "[":
+            c.p += 1
+            items = []
+            while True:
+                c.ws()
+                if c.peek() == "]":
+                    c.p += 1
+                    return items
+                items.append(self._value(c, depth + 1))
+                c.ws()
+                if c.peek() == ",":
+                    c.p += 1
+        word = c.word(",}]")
+        if not word:
+            raise _Malformed()
+        return _bare(word)[0]
+
+    def _object(self, c: _Cursor, depth: int) -> Dict:
+        if depth > self.MAX_DEPTH:
+            raise _Malformed()
+        c.expect("{")
+        obj: Dict = {}
+        while True:
+            c.ws()
+            if c.peek() == "}":
+                c.p += 1
+                return obj
+            key = self._string(c) if c.startswith(self.ESC) else c.word(":")
+            if not key:
+                raise _Malformed()
+            c.ws()
+            c.expect(":")
+            obj[key] = self._value(c, depth)
+            c.ws()
+            if c.peek() == ",":
+                c.p += 1
+            elif c.peek() != "}":
+                raise _Malformed()
+
+
+class Lfm2ToolCallParser(SpanToolCallParser):
+    """``<|tool_call_start|>[name(arg='text', n=3, flag=True, nested=[1, "two", null, {"k": "v"}]), other()]<|tool_call_end|>``:
+    a Python list of keyword-only calls whose values are Python or JSON literals.  Positional arguments, other bare words,
+    an empty list and unbalanced brackets make the whole span malformed; whitespace, trailing commas and call or argument
+    names that are not Python identifiers (``mcp__srv__tool-1``) are accepted."""
+
+    OPEN, CLOSE = "<|tool_call_start|>", "<|tool_call_end|>"
+    _ESC = {"n": "\n", "r": "\r", "t": "\t", "b": "\b", "f": "\f", "\\": "\\", "'": "'", '"': '"', "/": "/"}
+
+    def parse_span(self, c: _Cursor):
+        c.ws()
+        c.expect("[")
+        calls = []
+        while True:
+            c.ws()
+            if c.peek() == "]":
+                c.p += 1
+                break
+            name = c.word("(,[]")
+            if not name or c.peek() != "(":
+                raise _Malformed()
+            c.p += 1
+            args: Dict = {}
+            while True:
+                c.ws()
+                if c.peek() == ")":
+                    c.p += 1
+                    break
+                key = c.word("=,()")
+                c.ws()
+                if not key or c.peek() != "=":
+                    raise _Malformed()                  # positional argument
+                c.p += 1
+                args[key] = self._value(c, 0)
+                c.ws()
+                if c.peek() == ",":
+                    c.p += 1
+                elif c.peek() != ")":
+                    raise _Malformed()
+            calls.append((name, args))
+            c.ws()
+            if c.peek() == ",":
+                c.p += 1
+            elif c.peek() != "]":
+                raise _Malformed()
+        if not calls:
+            raise _Malformed()
+        return calls
+
+    def _string(self, c: _Cursor) -> str:
+        q = c.peek()
+        c.p += 1
+        out = []
+        while True:
+            ch = c.peek()
+            c.p += 1
+            if ch == q:
+                return "".join(out)
+            if ch != "\\":
+                out.append(ch)
+                continue
+            e = c.peek()
+            c.p += 1
+            if e == "u":
+                if c.p + 4 > len(c.s):
+                    raise _Incomplete()
+                try:
+                    out.append(chr(int(c.s[c.p:c.p + 4], 16)))
+                except ValueError:
+                    raise _Malformed()
+                c.p += 4
+            else:
+                out.append(self._ESC.get(e, "\\" + e))
+
+    def _value(self, c: _Cursor, depth: int):
+        if depth > self.MAX_DEPTH:
+            raise _Malformed()
+        c.ws()
+        ch = c.peek()
+        if ch in "'\"":
+            return self._string(c)
+        if ch == "[":
+            c.p += 1
+            items = []
+            while True:
+                c.ws()
+                if c.peek() == "]":
+                    c.p += 1
+                    return items
+                items.append(self._value(c, depth + 1))
+                c.ws()
+                if c.peek() == ",":
+                    c.p += 1
+                elif c.peek() != "]":
+                    raise _Malformed()
+        if ch == "{":
+            c.p += 1
+            obj: Dict = {}
+            while True:
+                c.ws()
+                if c.peek() == "}":
+                    c.p += 1
+                    return obj
+                if c.peek() not in "'\"":
+                    raise _Malformed()
+                key = self._string(c)
+                c.ws()
+                c.expect(":")
+                obj[key] = self._value(c, depth + 1)
+                c.ws()
+                if c.peek() == ",":
+                    c.p += 1
+                elif c.peek() != "}":
+                    raise _Malformed()
+        word = c.word(",)]}")
+        val, ok = _bare(word)
+        if not word or not ok:
+            raise _Malformed()
+        return val
+
+
+def make_tool_call_parser(dialect: str):
+    """The parser of a model family's tool-call syntax (``detect_dialect`` names the family)."""
+    return {"gemma": GemmaToolCallParser, "lfm2": Lfm2ToolCallParser}.get(dialect, QwenToolCallParser)()
+
+
 def detect_dialect(model_id: str, arch: str = "") -> str:
     """Model family -> which tool-call / reasoning conventions apply (reference: src/server/dialect.*)."""
     s = (model_id + " " + arch).lower()

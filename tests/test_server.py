@@ -337,3 +337,43 @@ def test_ngram_drafter_proposes_what_followed_the_latest_match_and_stays_lossles
     plain, calls_plain = run(None)
     spec, calls_spec = run(draft_fn)
     assert spec == plain and calls_spec <= calls_plain
+
+
+def test_gemma_and_pythonic_tool_call_parsers_stream_and_degrade():
+    import json
+    from r4dx_b200.server.parsers import (GemmaToolCallParser, Lfm2ToolCallParser, QwenToolCallParser, detect_dialect,
+                                          make_tool_call_parser)
+
+    def run(p, text, step):
+        out = ""
+        for i in range(0, len(text), step):
+            out += p.feed(text[i:i + step])
+        return out + p.flush()
+
+    for step in (1, 4, 1000):
+        g = GemmaToolCallParser()
+        out = run(g, 'Sure. <|tool_call>call:get_weather{city:<|"|>Paris <tool_call|> x<|"|>,days:3,opts:{metric:true,tags:[1,<|"|>a<|"|>,null]},'
+                     'mode:fast}<tool_call|> done<|tool_call>call:b{}<tool_call|>', step)
+        assert out == "Sure.  done" and not g.had_malformed_call
+        assert [c["function"]["name"] for c in g.calls] == ["get_weather", "b"]
+        assert json.loads(g.calls[0]["function"]["arguments"]) == {
+            "city": "Paris <tool_call|> x", "days": 3, "opts": {"metric": True, "tags": [1, "a", None]}, "mode": "fast"}
+        p = Lfm2ToolCallParser()
+        out = run(p, "ok <|tool_call_start|>[get_w(city='Pa\\'ris <|tool_call_end|>', n=3, x=-1.5, f=True, "
+                     'nested=[1, "two", true, null, {"k": "v\\u00e9"}],), mcp__srv__tool-1()]\n<|tool_call_end|> bye', step)
+        assert out == "ok  bye" and not p.had_malformed_call
+        assert json.loads(p.calls[0]["function"]["arguments"]) == {
+            "city": "Pa'ris <|tool_call_end|>", "n": 3, "x": -1.5, "f": True, "nested": [1, "two", True, None, {"k": "v\u00e9"}]}
+        assert p.calls[1]["function"] == {"name": "mcp__srv__tool-1", "arguments": "{}"}
+    # malformed spans come back as literal content
+    for bad in ("<|tool_call_start|>[f(1)]<|tool_call_end|>", "<|tool_call_start|>[]<|tool_call_end|>",
+                "<|tool_call_start|>[f(a=word)]<|tool_call_end|>", '<|tool_call_start|>[{"name": "f", "arguments": {}}]<|tool_call_end|>'):
+        p = Lfm2ToolCallParser()
+        assert run(p, "a " + bad + " b", 3) == "a " + bad + " b" and p.had_malformed_call and not p.calls
+    p = Lfm2ToolCallParser()
+    assert run(p, "x <|tool_call_start|>[f(a='cut", 2) == "x <|tool_call_start|>[f(a='cut" and p.had_malformed_call
+    g = GemmaToolCallParser()
+    assert run(g, "<|tool_call>oops<tool_call|>", 2) == "<|tool_call>oops<tool_call|>" and g.had_malformed_call
+    assert isinstance(make_tool_call_parser(detect_dialect("gemma-4-12b")), GemmaToolCallParser)
+    assert isinstance(make_tool_call_parser(detect_dialect("LFM2.5-24B")), Lfm2ToolCallParser)
+    assert isinstance(make_tool_call_parser(detect_dialect("qwen-hybrid")), QwenToolCallParser)
