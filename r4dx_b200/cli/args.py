@@ -23,6 +23,8 @@ def add_model_flags(ap: argparse.ArgumentParser) -> None:
     g.add_argument("--dflash-p-min", type=float, default=0.0)
     g.add_argument("--dflash-n-min", type=int, default=0)
     g.add_argument("--vision", default="off", choices=["off", "on"])
+    g.add_argument("--audio", default="off", choices=["off", "on"],
+                   help="accept input_audio parts (the container must hold the audio projection; Gemma-style family)")
     p = ap.add_argument_group("parallelism")
     p.add_argument("--tp", type=int, default=1, choices=[1, 2, 4, 8])
     p.add_argument("--tp-mode", default=os.environ.get("R4DXB_TP_MODE", "fused"), choices=["fused", "nccl", "noop"])

@@ -37,10 +37,15 @@ def main(argv=None) -> int:
         vision = VisionTower(vcfg, vw, device=str(tm.m.device))
         image_id = getattr(tk, "image_pad_id", tm.config.vocab_size - 1)
         eng.vision = vision
+    audio_id = -1
+    if getattr(args, "audio", "off") == "on" and args.batch <= 1:
+        from ..models.audio import load_audio_embedder
+        eng.audio = load_audio_embedder(getattr(tm.m, "w", {}))
+        audio_id = getattr(tk, "audio_token_id", tm.config.vocab_size - 2)
     defaults = {"temperature": args.default_temperature, "top_k": args.default_top_k, "top_p": args.default_top_p,
                 "min_p": args.default_min_p, "repetition_penalty": args.default_repetition_penalty}
     srv = ApiServer(eng, tk, tpl, tm.model_id, host=args.host, port=args.port, max_tokens_default=args.max_tokens_default,
-                    defaults=defaults, spec_k=args.mtp or getattr(args, "ngram", 0), vision_config=vcfg, image_token_id=image_id)
+                    defaults=defaults, spec_k=args.mtp or getattr(args, "ngram", 0), vision_config=vcfg, image_token_id=image_id, audio_token_id=audio_id)
     print(f"[r4dxb-server] {tm.model_id} on http://{args.host}:{srv.port} (tp={tm.tp_world()})", file=sys.stderr)
     try:
         srv.serve_forever()

@@ -14,6 +14,43 @@ from typing import List, Sequence, Tuple
 import torch
 
 MARK = "\x00<r4dxb-image-%d>\x00"
+AUDIO_MARK = "\x00<r4dxb-audio-%d>\x00"
+
+
+def decode_audio(part) -> bytes:
+    """An ``input_audio`` content part ({"data": base64, "format": "wav"}) or a ``data:`` URI -> WAVE bytes."""
+    if isinstance(part, dict):
+        fmt = str(part.get("format", "wav")).lower()
+        if fmt != "wav":
+            raise ValueError(f"audio format {fmt!r} is not supported (wav only)")
+        data = part.get("data", "")
+    else:
+        data = str(part)
+    if data.startswith("data:"):
+        head, _, data = data.partition(",")
+        if ";base64" not in head:
+            raise ValueError("audio data URI must be base64")
+    try:
+        return base64.b64decode(data, validate=False)
+    except Exception:
+        raise ValueError("audio data is not valid base64")
+
+
+def assemble_media_prompt(rendered: str, spans: Sequence[Tuple[str, int, int]], encode) -> List[int]:
+    """Tokenizes the text around media markers.  ``spans``: (marker, placeholder token id, count) in any order; each marker is
+    replaced by ``count`` copies of its token where it stands in the rendered prompt."""
+    found = []
+    for marker, tok, n in spans:
+        at = rendered.find(marker)
+        if at < 0:
+            raise ValueError("a media part has no placeholder in the rendered prompt")
+        found.append((at, marker, tok, n))
+    ids: List[int] = []
+    cur = 0
+    for at, marker, tok, n in sorted(found):
+        ids += encode(rendered[cur:at]) + [tok] * n
+        cur = at + len(marker)
+    return ids + encode(rendered[cur:])
 
 
 def decode_image(url: str) -> torch.Tensor:

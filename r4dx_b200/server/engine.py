@@ -40,6 +40,8 @@ class GenRequest:
     spec_k: int = 0
     images: List = field(default_factory=list)          # uint8 [H, W, 3] tensors, in the order of the image placeholders
     image_token_id: int = -1
+    audio_rows: List = field(default_factory=list)      # one [frames, hidden] tensor per clip, in the order of the audio placeholders
+    audio_token_id: int = -1
 
 
 @dataclass
@@ -71,9 +73,10 @@ class _Job:
 
 class Engine:
     def __init__(self, model: TextModel, tokenizer, max_queue: int = 8, prompt_checkpoint: bool = True,
-                 request_log: Optional[RequestLog] = None, vision=None):
+                 request_log: Optional[RequestLog] = None, vision=None, audio=None):
         self.model = model
         self.vision = vision               # object with encode_images(list of uint8 images) -> [tokens, hidden]
+        self.audio = audio                 # object with embed_clip(wav bytes) -> [frames, hidden] (host side, once per clip)
         self.tk = tokenizer
         self.q: "queue.Queue[_Job]" = queue.Queue(maxsize=max_queue)
         self.prefix = PrefixState()
@@ -145,6 +148,20 @@ class Engine:
             if where.numel() != emb.shape[0]:
                 raise ValueError(f"{where.numel()} image placeholder tokens for {emb.shape[0]} image embeddings")
             overrides = (where, emb)
+            self.prefix.invalidate()
+        if req.audio_rows:
+            import torch
+            rows = torch.cat([r for r in req.audio_rows], 0)
+            where = torch.tensor([i for i, t in enumerate(prompt) if t == req.audio_token_id], dtype=torch.long)
+            if where.numel() != rows.shape[0]:
+                raise ValueError(f"{where.numel()} audio placeholder tokens for {rows.shape[0]} audio rows")
+            if overrides is not None:      # images and audio in one prompt: one override list, ordered by position
+                pos = torch.cat([overrides[0], where])
+                emb_all = torch.cat([overrides[1], rows.to(overrides[1].device, overrides[1].dtype)], 0)
+                order = torch.argsort(pos)
+                overrides = (pos[order], emb_all[order.to(emb_all.device)])
+            else:
+                overrides = (where, rows)
             self.prefix.invalidate()
         plan = self.prefix.plan(prompt) if self.prefix.valid else None
         t0 = time.perf_counter()

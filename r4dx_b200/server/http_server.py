@@ -39,8 +39,9 @@ def parse_sampling(body: Dict, defaults: Dict) -> SampleParams:
                         repetition_penalty=num("repetition_penalty", defaults.get("repetition_penalty", 1.0), 0.01, 10.0))
 
 
-def message_text(m: Dict, images: Optional[list] = None) -> str:
-    """Flattens OpenAI content parts; every image part becomes a numbered marker and its URL is appended to ``images``."""
+def message_text(m: Dict, images: Optional[list] = None, audios: Optional[list] = None) -> str:
+    """Flattens OpenAI content parts; every image / audio part becomes a numbered marker and its payload is appended to
+    ``images`` / ``audios``."""
     c = m.get("content", "")
     if isinstance(c, list):
         parts = []
@@ -54,6 +55,12 @@ def message_text(m: Dict, images: Optional[list] = None) -> str:
                 from ..runtime.image_prompt import MARK
                 parts.append(MARK % len(images))
                 images.append(u.get("url", "") if isinstance(u, dict) else str(u))
+            elif p.get("type") == "input_audio":
+                if audios is None:
+                    raise BadRequest("this model was loaded without an audio embedder")
+                from ..runtime.image_prompt import AUDIO_MARK
+                parts.append(AUDIO_MARK % len(audios))
+                audios.append(p.get("input_audio", ""))
         c = "".join(parts)
     if not isinstance(c, str):
         raise BadRequest("message content must be a string or a list of parts")
@@ -63,8 +70,9 @@ def message_text(m: Dict, images: Optional[list] = None) -> str:
 class ApiServer:
     def __init__(self, engine: Engine, tokenizer, template, model_id: str, host: str = "127.0.0.1", port: int = 8080,
                  max_tokens_default: int = 512, defaults: Optional[Dict] = None, spec_k: int = 0, vision_config=None,
-                 image_token_id: int = -1):
+                 image_token_id: int = -1, audio_token_id: int = -1):
         self.vision_config, self.image_token_id = vision_config, image_token_id
+        self.audio_token_id = audio_token_id          # >= 0 when the engine holds an audio embedder
         self.engine, self.tk, self.template, self.model_id = engine, tokenizer, template, model_id
         self.max_tokens_default = max_tokens_default
         self.defaults = defaults or {}
@@ -154,22 +162,27 @@ class ApiServer:
             raise BadRequest("'messages' must be a non-empty list")
         norm = []
         urls: list = []
+        clips: list = []
         for m in msgs:
             if not isinstance(m, dict) or "role" not in m:
                 raise BadRequest("every message needs a role")
-            norm.append({**m, "content": message_text(m, urls if self.vision_config is not None else None)})
+            norm.append({**m, "content": message_text(m, urls if self.vision_config is not None else None,
+                                                      clips if self.audio_token_id >= 0 else None)})
         thinking = body.get("enable_thinking", (body.get("chat_template_kwargs") or {}).get("enable_thinking"))
         prompt = self.template.render(norm, add_generation_prompt=True, tools=body.get("tools"), enable_thinking=thinking)
-        if urls:
+        if urls or clips:
             from ..runtime import image_prompt as IP
             try:
                 imgs = [IP.decode_image(u) for u in urls]
-                counts = [IP.image_token_count(i, self.vision_config) for i in imgs]
-                ids = IP.assemble_prompt(prompt, counts, self.tk.encode, self.image_token_id)
+                spans = [(IP.MARK % i, self.image_token_id, IP.image_token_count(im, self.vision_config)) for i, im in enumerate(imgs)]
+                rows = [self.engine.audio.embed_clip(IP.decode_audio(c)) for c in clips]
+                spans += [(IP.AUDIO_MARK % i, self.audio_token_id, int(r.shape[0])) for i, r in enumerate(rows)]
+                ids = IP.assemble_media_prompt(prompt, spans, self.tk.encode)
             except ValueError as e:
                 raise BadRequest(str(e))
             req = self._common(body, ids, chat=True)
             req.images, req.image_token_id = imgs, self.image_token_id
+            req.audio_rows, req.audio_token_id = rows, self.audio_token_id
         else:
             req = self._common(body, self.tk.encode(prompt), chat=True)
         self._serve(h, req, chat=True)

@@ -377,3 +377,62 @@ def test_gemma_and_pythonic_tool_call_parsers_stream_and_degrade():
     assert isinstance(make_tool_call_parser(detect_dialect("gemma-4-12b")), GemmaToolCallParser)
     assert isinstance(make_tool_call_parser(detect_dialect("LFM2.5-24B")), Lfm2ToolCallParser)
     assert isinstance(make_tool_call_parser(detect_dialect("qwen-hybrid")), QwenToolCallParser)
+
+
+def test_audio_front_end_and_audio_parts_in_chat_requests():
+    """WAV reader + framing + the encoder-free embedder against an fp32 restatement; then an ``input_audio`` part travels
+    through the HTTP layer as placeholder tokens whose embeddings the engine overrides with the clip's rows."""
+    import base64
+    import math
+    import torch
+    from r4dx_b200.models import audio as A
+    t = torch.arange(16000 // 2) / 16000.0
+    wave = 0.4 * torch.sin(2 * math.pi * 330 * t)
+    back, rate = A.read_wav(A.write_wav(wave))
+    assert rate == 16000 and back.shape == wave.shape and float((back - wave).abs().max()) < 1e-4
+    frames = A.frame_waveform(back)
+    assert frames.shape == (13, 640) and float(frames[-1, 8000 - 12 * 640:].abs().max()) == 0.0      # zero-padded tail
+    assert A.resample(wave, 16000, 8000).numel() == 4000
+    W = torch.randn(128, 640, generator=torch.Generator().manual_seed(0)) * 0.05
+    emb = A.AudioEmbedder(W)
+    rows = emb.embed(frames)
+    x = frames.to(torch.bfloat16).float()
+    ref = (x / torch.sqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6)).to(torch.bfloat16).float() @ W.to(torch.bfloat16).float().T
+    assert rows.dtype == torch.bfloat16 and torch.allclose(rows.float(), ref, atol=2e-2, rtol=2e-2)
+    assert torch.equal(emb.embed(frames[3:5]), rows[3:5])                     # a row depends on its own frame only
+    with pytest.raises(ValueError):
+        A.read_wav(b"not a wave file")
+    with pytest.raises(ValueError):
+        A.load_audio_embedder({})
+
+    model = FakeTextModel(vocab=300)
+    eng = Engine(model, ByteTokenizer(300), audio=emb)
+    srv = ApiServer(eng, ByteTokenizer(300), ChatTemplate(), "fake-audio", port=0, audio_token_id=298)
+    srv.start()
+    try:
+        clip = base64.b64encode(A.write_wav(wave)).decode()
+        body = {"messages": [{"role": "user", "content": [{"type": "text", "text": "transcribe "},
+                                                           {"type": "input_audio", "input_audio": {"data": clip, "format": "wav"}}]}],
+                "max_tokens": 3, "temperature": 0}
+        r = json.load(_post(srv.port, "/v1/chat/completions", body))
+        assert r["choices"][0]["finish_reason"] in ("stop", "length")
+        pos, got = model.last_overrides
+        assert pos.numel() == 13 and torch.equal(got, rows)
+        assert all(model.history[int(p)] == 298 for p in pos) and model.history.count(298) == 13
+        body["messages"][0]["content"][1]["input_audio"]["format"] = "mp3"
+        with pytest.raises(urllib.error.HTTPError) as e:
+            _post(srv.port, "/v1/chat/completions", body)
+        assert e.value.code == 400
+    finally:
+        srv.stop(); eng.shutdown()
+    # a server without the embedder refuses audio parts
+    eng2 = Engine(FakeTextModel(vocab=300), ByteTokenizer(300))
+    srv2 = ApiServer(eng2, ByteTokenizer(300), ChatTemplate(), "fake", port=0)
+    srv2.start()
+    try:
+        body["messages"][0]["content"][1]["input_audio"]["format"] = "wav"
+        with pytest.raises(urllib.error.HTTPError) as e:
+            _post(srv2.port, "/v1/chat/completions", body)
+        assert e.value.code == 400
+    finally:
+        srv2.stop(); eng2.shutdown()
