@@ -293,3 +293,18 @@ def test_w4a16_scale_search_beats_round_to_nearest_under_the_importance_weights(
     assert calibrate_main(["imatrix", "--input", "random:tiny", "--tokens", "32", "--prompts", "1", "--out", ip]) == 0
     assert convert_main(["--input", "random:tiny", "--output", str(tmp_path / "m.r4dxb"), "--layers", "1", "--layouts", "w4a16",
                          "--quant", "search", "--imatrix", ip, "--selftest"]) == 0
+
+
+def test_kl_report_orders_the_bit_widths(capsys):
+    import json
+    import torch
+    from r4dx_b200.utils.kl_report import kl_stats, main as kl_main
+    z = torch.randn(5, 50)
+    same = kl_stats(z, z.clone())
+    assert same["kl_max"] < 1e-12 and same["top1_agreement"] == 1.0
+    res = {}
+    for plan in ("kb3", "kb5"):
+        assert kl_main(["--input", "random:tiny", "--layers", "2", "--kb-plan", plan, "--tokens", "24", "--prompts", "1"]) == 0
+        res[plan] = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert 0 < res["kb5"]["kl_mean"] < res["kb3"]["kl_mean"]
+    assert res["kb5"]["mean_abs_logit_err"] < res["kb3"]["mean_abs_logit_err"]
