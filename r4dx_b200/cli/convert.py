@@ -21,10 +21,17 @@ def _kb_rule(plan: str):
 
 
 def load_source(spec: str, layers: int, mtp: bool, seed: int):
-    from ..config import ModelConfig, small_hybrid_config, tiny_hybrid_config
+    from ..config import (ModelConfig, small_hybrid_config, tiny_gemma_config, tiny_hybrid_config, tiny_lfm2_config,
+                          tiny_llama_config, tiny_moe_config)
     from ..models.oracle import init_weights
     if spec.startswith("random:"):
-        cfg = {"tiny": tiny_hybrid_config, "small": small_hybrid_config}[spec.split(":", 1)[1]]()
+        # tiny random-init models of every family (reference: tools/convert_ref/make_tiny_*.py)
+        makers = {"tiny": tiny_hybrid_config, "small": small_hybrid_config, "moe": tiny_moe_config, "llama": tiny_llama_config,
+                  "gemma": tiny_gemma_config, "lfm2": tiny_lfm2_config}
+        kind = spec.split(":", 1)[1]
+        if kind not in makers:
+            raise SystemExit(f"unknown random model {kind!r}; one of {sorted(makers)}")
+        cfg = makers[kind]()
         if layers:
             cfg.num_hidden_layers, cfg.layer_types = layers, cfg.layer_types[:layers]
         return cfg, init_weights(cfg, seed, with_mtp=mtp)

@@ -37,3 +37,18 @@ def test_native_resource_gate_passes_on_the_built_library():
     names = " ".join(k for _, k, _, _, _ in rep)
     assert len(rep) > 100 and "TrellisGemmKernel" in names and "GdnChunkScanKernel" in names
     assert max(r for _, _, r, _, _ in rep) <= 255
+
+
+def test_converter_builds_a_tiny_model_of_every_family(tmp_path):
+    """random:<family> -> container -> reload: config and tensor set survive, for each model family the engine serves."""
+    from r4dx_b200.cli.convert import main as convert_main
+    from r4dx_b200.quant.weights import load_weight_set
+    for kind, layers, probe in (("llama", 1, "text.layers.0.attn.qg"), ("gemma", 1, "text.layers.0.post_mlp_out_norm"),
+                                ("lfm2", 2, "text.layers.0.conv.in_proj")):
+        out = str(tmp_path / f"{kind}.r4dxb")
+        assert convert_main(["--input", f"random:{kind}", "--output", out, "--layers", str(layers), "--kb-plan", "kb3"]) == 0
+        cfg, w = load_weight_set(out)
+        assert cfg.num_hidden_layers == layers and probe in w, (kind, sorted(w)[:8])
+    cfg, w = load_weight_set(str(tmp_path / "lfm2.r4dxb"))
+    assert cfg.arch == "lfm2_moe" and cfg.moe_router == "sigmoid" and cfg.layer_types == ["conv", "conv"]
+    assert "text.layers.1.moe.expert_bias" in w and w["text.layers.1.moe.expert_bias"].dtype.is_floating_point
