@@ -141,7 +141,15 @@ class ChatTemplate:
 
 def load_tokenizer(directory: Optional[str], vocab_size: int = 4096):
     if directory and os.path.exists(os.path.join(directory, "tokenizer.json")):
-        tk = HfTokenizer(directory)
+        # the engine's own BPE reads byte-level and byte-fallback BPE vocabularies; anything else (Unigram, WordPiece,
+        # normalisers it does not model) falls back to the `tokenizers` library
+        try:
+            if os.environ.get("R4DXB_TOKENIZER", "own") != "own":
+                raise ValueError("library tokenizer requested")
+            from .bpe import BpeTokenizer
+            tk = BpeTokenizer(directory)
+        except (ValueError, KeyError):
+            tk = HfTokenizer(directory)
         tpl_path = os.path.join(directory, "chat_template.jinja")
         tpl = ChatTemplate(open(tpl_path).read() if os.path.exists(tpl_path) else None)
         return tk, tpl
