@@ -98,7 +98,7 @@ def main():
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "reference is a HIP/RDNA4/Windows CMake project with no setup.py/pyproject.toml; "
-                          "pip install /root/reference fails: 'not installable'"}))
+                          "pip install of the reference tree fails: 'not installable'"}))
         return 0
 
     import torch
