@@ -2,8 +2,8 @@
 
     python -m r4dx_b200.utils.ngram_sim --log requests.jsonl [--k 4] [--min-n 2] [--max-n 4]
 
-Each line of the log is a JSON object with ``prompt_ids`` and ``token_ids`` (the server's request log writes them when it is
-started with token logging).  Prints one JSON line per request and a total.
+Each line of the log is a JSON object with ``prompt_ids`` and ``completion_ids`` (what the server's request log writes when
+it is started with token logging; ``token_ids`` is accepted too).  Prints one JSON line per request and a total.
 (reference: tools/ngram, the n-gram speculation simulator.)"""
 from __future__ import annotations
 
@@ -27,7 +27,7 @@ def main(argv=None) -> int:
         if not line:
             continue
         d = json.loads(line)
-        prompt, out = list(d.get("prompt_ids", [])), list(d.get("token_ids", []))
+        prompt, out = list(d.get("prompt_ids", [])), list(d.get("completion_ids", d.get("token_ids", [])))
         if not out:
             continue
         s = simulate(prompt + out, len(prompt), a.k, a.min_n, a.max_n)
