@@ -97,3 +97,66 @@ def test_vision_tower_matches_reference():
                                      torch.cat([b for _, b in taps]), V.segment_offsets(grids))
     assert got.shape == ref.shape == (sum(gh * gw for _, gh, gw in grids) // 4, cfg.out_hidden_size)
     assert torch.allclose(got, ref, atol=0.06 * ref.abs().max().item(), rtol=0.05)
+
+
+def test_gemma_style_vision_host_half():
+    """Preprocessor geometry and raster order, placeholder expansion, image blocks, chunk planning that never cuts a block,
+    the per-row key limits against the dense reference mask, and the embedder chain's shapes and rounding."""
+    import pytest
+    import torch
+    from r4dx_b200.models import gemma_vision as GV
+    # target size: multiples of 48 inside the budget, aspect kept, small images grown
+    for H, W in ((480, 640), (100, 50), (2000, 3000), (48, 48)):
+        h, w = GV.target_size(H, W, 280)
+        assert h % 48 == 0 and w % 48 == 0 and (h // 48) * (w // 48) <= 280
+        assert (h + 48) * (w + 48) > 280 * 48 * 48 * 0.6 and abs(h / w - H / W) < 0.35 * H / W
+    with pytest.raises(ValueError):
+        GV.target_size(10, 100000, 70)
+    with pytest.raises(ValueError):
+        GV.target_size(100, 100, 100)
+    # an image already at its target size is only rescaled: raster order is checkable exactly
+    h, w = GV.target_size(96, 144, 70)
+    img = torch.randint(0, 256, (h, w, 3), generator=torch.Generator().manual_seed(0), dtype=torch.uint8)
+    px, pos, (gh, gw) = GV.preprocess(img, 70)
+    assert px.shape == (gh * gw, 6912) and pos.shape == (gh * gw, 2) and (gh, gw) == (h // 48, w // 48)
+    r, c = 1 % gh, 2 % gw
+    patch = px[r * gw + c].view(48, 48, 3)
+    assert torch.allclose(patch, img[r * 48:(r + 1) * 48, c * 48:(c + 1) * 48].float() * (1.0 / 255.0))
+    assert pos[r * gw + c].tolist() == [c, r]
+    # placeholders and blocks
+    toks, spans = GV.expand_placeholders([5, 9, 6, 9, 7], [3, 2], image_id=9, boi_id=1, eoi_id=2)
+    assert toks == [5, 1, 9, 9, 9, 2, 6, 1, 9, 9, 2, 7] and spans == [(2, 3), (8, 2)]
+    blocks = GV.find_blocks(toks, 9, base=100)
+    assert blocks == [(102, 105), (108, 110)]
+    with pytest.raises(ValueError):
+        GV.expand_placeholders([9], [1, 1], 9, 1, 2)
+    # chunk planning: no block is ever cut, every row is covered once
+    blocks = [(3, 9), (10, 14), (20, 27)]
+    for max_rows in (7, 8, 12, 100):
+        chunks = GV.plan_prefill_chunks(30, blocks, max_rows, max_block=8)
+        assert sum(n for _, n in chunks) == 30 and chunks[0][0] == 0
+        assert all(chunks[i][0] + chunks[i][1] == chunks[i + 1][0] for i in range(len(chunks) - 1))
+        for s, n in chunks:
+            assert all(not (a < s + n < b) and not (a < s < b) for a, b in blocks), (max_rows, chunks)
+    with pytest.raises(ValueError):
+        GV.plan_prefill_chunks(30, [(0, 20)], 8, max_block=8)
+    # key limits reproduce the dense mask of a sliding layer
+    T, window = 30, 6
+    ext = GV.key_limit_ext(0, T, blocks)
+    mask = GV.dense_mask(T, window, True, blocks)
+    for q in range(T):
+        hi = max(q, int(ext[q]))
+        want = torch.zeros(T, dtype=torch.bool)
+        want[max(0, q - window + 1):hi + 1] = True
+        assert torch.equal(mask[q], want), q
+    assert torch.equal(GV.dense_mask(T, 0, False, blocks), torch.tril(torch.ones(T, T, dtype=torch.bool)))
+    # embedder chain
+    g = torch.Generator().manual_seed(1)
+    n = lambda *s: torch.randn(*s, generator=g) * 0.05
+    mm, out = 64, 32
+    w = GV.GemmaEmbedderWeights(1 + n(6912), n(6912), n(mm, 6912), n(mm), 1 + n(mm), n(mm), n(16, 2, mm), 1 + n(mm), n(mm), n(out, mm))
+    rows = GV.embed_reference(px, pos, w)
+    assert rows.shape == (gh * gw, out) and torch.equal(rows, rows.to(torch.bfloat16).float())
+    assert torch.equal(GV.embed_reference(px[2:3], pos[2:3], w), rows[2:3])       # rows are independent
+    moved = GV.embed_reference(px, torch.flip(pos, [1]), w)
+    assert not torch.equal(moved, rows)                                           # the position terms matter
