@@ -75,6 +75,9 @@ def _declare_host(L):
     _sig(L, "r4dxb_trellis_decode", None, [c_ptr, c_i64, c_i64, c_int, c_ptr])
     _sig(L, "r4dxb_trellis_packed_words", c_i64, [c_i64, c_i64, c_int])
     _sig(L, "r4dxb_trellis_quantize", c_f64, [c_ptr, c_i64, c_i64, c_int, c_u64, c_int, c_ptr, c_ptr, c_ptr])
+    _sig(L, "r4dxb_bpe_new", c_ptr, [c_ptr, c_i64])
+    _sig(L, "r4dxb_bpe_free", None, [c_ptr])
+    _sig(L, "r4dxb_bpe_encode", c_i64, [c_ptr, c_ptr, c_i64, c_ptr])
     _sig(L, "r4dxb_trellis_quantize_ldlq", c_f64, [c_ptr, c_ptr, c_i64, c_i64, c_int, c_u64, c_int, c_f32, c_ptr, c_ptr, c_ptr, c_ptr])
     _sig(L, "r4dxb_trellis_reconstruct", None, [c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_int, c_int, c_ptr])
     _sig(L, "r4dxb_trellis_encode_tile", c_f32, [c_ptr, c_int, c_ptr])

@@ -69,6 +69,8 @@ class BpeTokenizer:
         self.id_to_token.update({i: t for t, i in self.added.items()})
         self.vocab_size = max(self.id_to_token) + 1 if self.id_to_token else 0
         self._cache: Dict[str, List[int]] = {}
+        self._native = None
+        self._init_native()
         self.eos_ids: List[int] = []
         gen = os.path.join(directory, "generation_config.json")
         if os.path.exists(gen):
@@ -103,6 +105,43 @@ class BpeTokenizer:
         return any(s.get("type") == "Prepend" for s in steps)
 
     # ---- BPE ---------------------------------------------------------------------------------------
+    def _init_native(self) -> None:
+        """Hands the merge table to the native merge loop as (left id, right id, merged id) triples in rank order.  Needs
+        every merge's two sides and product to be vocabulary entries (true of trained BPE vocabularies); otherwise, or when
+        the native library is missing, pieces go through the Python loop."""
+        if os.environ.get("R4DXB_BPE_NATIVE", "1") == "0":
+            return
+        try:
+            import numpy as np
+            from .. import native
+            L = native.host()
+            tri = np.empty((len(self.ranks), 3), dtype=np.int32)
+            for (a, b), i in self.ranks.items():
+                ia, ib, im = self.vocab.get(a), self.vocab.get(b), self.vocab.get(a + b)
+                if ia is None or ib is None or im is None:
+                    return
+                tri[i] = (ia, ib, im)
+            self._tri = np.ascontiguousarray(tri)
+            self._np = np
+            self._lib = L
+            self._native = L.r4dxb_bpe_new(self._tri.ctypes.data, len(self.ranks))
+        except Exception:
+            self._native = None
+
+    def __del__(self):
+        try:
+            if self._native:
+                self._lib.r4dxb_bpe_free(self._native)
+        except Exception:
+            pass
+
+    def _merge_native(self, ids0: List[int]) -> List[int]:
+        np = self._np
+        src = np.asarray(ids0, dtype=np.int32)
+        out = np.empty(len(ids0), dtype=np.int32)
+        n = self._lib.r4dxb_bpe_encode(self._native, src.ctypes.data, len(ids0), out.ctypes.data)
+        return out[:n].tolist()
+
     def _merge(self, symbols: List[str]) -> List[str]:
         ranks = self.ranks
         while len(symbols) > 1:
@@ -135,8 +174,11 @@ class BpeTokenizer:
             symbols = list(piece)
         ids: List[int] = []
         whole = "".join(symbols)
+        ids0 = [self.vocab.get(s) for s in symbols] if self._native else None
         if self.ignore_merges and whole in self.vocab:       # Llama-3 style: a piece that is a vocabulary entry is taken whole
             ids = [self.vocab[whole]]
+        elif ids0 is not None and None not in ids0:
+            ids = self._merge_native(ids0)
         else:
             for s in self._merge(symbols):
                 i = self.vocab.get(s)

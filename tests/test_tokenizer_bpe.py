@@ -42,6 +42,17 @@ def test_byte_level_bpe_matches_the_hugging_face_encoder(tmp_path):
     hf, path = _train_byte_level(tmp_path)
     mine = BpeTokenizer(path)
     assert mine.byte_level and mine.vocab_size == hf.get_vocab_size()
+    assert mine._native, "the native merge loop should be in use"
+    # the native loop and the Python loop agree piece by piece
+    import random
+    rnd = random.Random(0)
+    alphabet = "abcdefghij THE the quick 0123 \n\t.,'é東😀"
+    for _ in range(300):
+        piece = "".join(rnd.choice(alphabet) for _ in range(rnd.randrange(1, 24)))
+        from r4dx_b200.runtime.bpe import _B2U
+        symbols = [_B2U[b] for b in piece.encode("utf-8")]
+        py = [mine.vocab[t] for t in mine._merge(list(symbols))]
+        assert mine._merge_native([mine.vocab[t] for t in symbols]) == py, piece
     for s in SAMPLES:
         want = hf.encode(s, add_special_tokens=False).ids
         got = mine.encode(s)
