@@ -286,8 +286,9 @@ class HybridModel:
             K.rmsnorm(b.x[:T], w[f"text.layers.{i}.post_attention_layernorm"], cfg.rms_norm_eps, out=b.h[:T])
             if self.comm is not None and hasattr(self.comm, "moe_forward"):
                 self.comm.moe_forward(self.moe[i], b.h[:T], b.x[:T], T)
-            elif self.comm is not None and self.comm.world > 1:
-                # tensor-parallel experts (every rank holds a slice of every expert's inner width): the routed sum is a
+            elif self.comm is not None and self.comm.world > 1 and cfg.has_conv_layers:
+                # tensor-parallel experts (the short-conv family: every rank holds a slice of every expert's inner width;
+                # the hybrid MoE family keeps whole experts per rank and needs no sum): the routed sum is a
                 # partial product, summed over the ranks before it joins the residual stream
                 part = b.core.view(-1)[:T * cfg.hidden_size].view(T, cfg.hidden_size)
                 self.moe[i].forward(b.h[:T], part, T, residual=False)
@@ -506,7 +507,7 @@ class HybridModel:
                 e = min(T, s + R)
                 self.comm.moe_forward(self.moe[i], h[s:e], x[s:e], e - s)
             return
-        tp = self.comm is not None and self.comm.world > 1
+        tp = self.comm is not None and self.comm.world > 1 and self.cfg.has_conv_layers      # experts sliced by inner width
         from .moe import MoeBlock
         blk = self._moe_chunk_blocks.get(i) if hasattr(self, "_moe_chunk_blocks") else None
         if blk is None or blk.logits.shape[0] < T:
