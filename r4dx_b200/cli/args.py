@@ -23,6 +23,8 @@ def add_model_flags(ap: argparse.ArgumentParser) -> None:
     g.add_argument("--dflash-p-min", type=float, default=0.0)
     g.add_argument("--dflash-n-min", type=int, default=0)
     g.add_argument("--vision", default="off", choices=["off", "on"])
+    g.add_argument("--dialect", default="auto", choices=["auto", "qwen", "gemma", "lfm2", "llama"],
+                   help="reasoning markers and tool-call syntax; auto picks by model id and architecture")
     g.add_argument("--audio", default="off", choices=["off", "on"],
                    help="accept input_audio parts (the container must hold the audio projection; Gemma-style family)")
     p = ap.add_argument_group("parallelism")

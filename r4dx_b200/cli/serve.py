@@ -37,6 +37,11 @@ def main(argv=None) -> int:
         vision = VisionTower(vcfg, vw, device=str(tm.m.device))
         image_id = getattr(tk, "image_pad_id", tm.config.vocab_size - 1)
         eng.vision = vision
+    from ..server.parsers import select_dialect
+    eng.dialect = getattr(args, "dialect", "auto")
+    warn = select_dialect(eng.dialect, tm.model_id, tm.config.arch).cross_check(tm.config.arch)
+    if warn:
+        print(f"[r4dxb-server] warning: {warn}", file=sys.stderr)
     audio_id = -1
     if getattr(args, "audio", "off") == "on" and args.batch <= 1:
         from ..models.audio import load_audio_embedder

@@ -64,10 +64,12 @@ class FakeBatchBackend:
 
 class _Active:
     def __init__(self, job: _Job, slot: int, tk, dialect: str = "qwen"):
+        from .parsers import ModelDialect
         self.job, self.slot = job, slot
+        d = ModelDialect(dialect)
         self.dec = StreamDecoder(tk)
-        self.splitter = ReasoningSplitter()
-        self.tools = make_tool_call_parser(dialect) if job.req.parse_tools else None
+        self.splitter = d.reasoning_splitter()
+        self.tools = d.tool_call_parser() if job.req.parse_tools else None
         self.rng = Rng(job.req.params.seed)
         self.text_all = ""
         self.next_token = 0

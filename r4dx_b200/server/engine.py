@@ -19,7 +19,7 @@ from ..runtime.prefix_state import PrefixState
 from ..runtime.sampler import Rng, SampleParams
 from ..runtime.text_model import ModelStateError, TextModel
 from ..runtime.tokenizer import StreamDecoder
-from .parsers import ReasoningSplitter, detect_dialect, make_tool_call_parser
+from .parsers import ReasoningSplitter, detect_dialect, make_tool_call_parser, select_dialect
 from .request_log import RequestLog
 
 
@@ -77,6 +77,7 @@ class Engine:
         self.model = model
         self.vision = vision               # object with encode_images(list of uint8 images) -> [tokens, hidden]
         self.audio = audio                 # object with embed_clip(wav bytes) -> [frames, hidden] (host side, once per clip)
+        self.dialect = "auto"              # "auto" or a dialect name (reasoning markers and tool-call syntax of the family)
         self.tk = tokenizer
         self.q: "queue.Queue[_Job]" = queue.Queue(maxsize=max_queue)
         self.prefix = PrefixState()
@@ -183,9 +184,9 @@ class Engine:
         res.prefill_ms = (time.perf_counter() - t0) * 1e3
 
         dec = StreamDecoder(self.tk)
-        splitter = ReasoningSplitter()
-        dialect = detect_dialect(getattr(m, "model_id", ""), getattr(getattr(m, "config", None), "arch", ""))
-        tools = make_tool_call_parser(dialect) if req.parse_tools else None
+        dialect = select_dialect(self.dialect, getattr(m, "model_id", ""), getattr(getattr(m, "config", None), "arch", ""))
+        splitter = dialect.reasoning_splitter()
+        tools = dialect.tool_call_parser() if req.parse_tools else None
         eos = set(getattr(self.tk, "eos_ids", []))
         fed = list(prompt)
         text_all = ""

@@ -16,9 +16,13 @@ class ReasoningSplitter:
 
     OPEN, CLOSE = "<think>", "</think>"
 
-    def __init__(self, start_in_think: bool = False):
+    def __init__(self, start_in_think: bool = False, open_tag: Optional[str] = None, close_tag: Optional[str] = None):
         self.in_think = start_in_think
         self.buf = ""
+        if open_tag:
+            self.OPEN = open_tag
+        if close_tag:
+            self.CLOSE = close_tag
 
     def feed(self, delta: str) -> Tuple[str, str]:
         """Returns (content_delta, reasoning_delta)."""
@@ -429,6 +433,43 @@ class Lfm2ToolCallParser(SpanToolCallParser):
 def make_tool_call_parser(dialect: str):
     """The parser of a model family's tool-call syntax (``detect_dialect`` names the family)."""
     return {"gemma": GemmaToolCallParser, "lfm2": Lfm2ToolCallParser}.get(dialect, QwenToolCallParser)()
+
+
+class ModelDialect:
+    """The text surface of a model family beyond what its chat template renders: how reasoning is delimited, how tool calls
+    are written, and which architecture names it goes with (reference: src/server/dialect.h:1-40)."""
+
+    TABLE = {
+        # name: (reasoning open, reasoning close, architectures it is expected with)
+        "qwen": ("<think>", "</think>", ("qwen_hybrid", "qwen_hybrid_moe")),
+        "gemma": ("<|channel>thought\n", "<channel|>", ("gemma",)),
+        "lfm2": ("<think>", "</think>", ("lfm2_moe",)),
+        "llama": ("<think>", "</think>", ("llama",)),
+    }
+
+    def __init__(self, name: str):
+        if name not in self.TABLE:
+            raise ValueError(f"unknown dialect {name!r}; one of {sorted(self.TABLE)}")
+        self.name = name
+        self.reasoning_open, self.reasoning_close, self.archs = self.TABLE[name]
+
+    def reasoning_splitter(self, start_in_think: bool = False) -> "ReasoningSplitter":
+        return ReasoningSplitter(start_in_think, self.reasoning_open, self.reasoning_close)
+
+    def tool_call_parser(self):
+        return make_tool_call_parser(self.name)
+
+    def cross_check(self, arch: str) -> Optional[str]:
+        """A warning line when the dialect was forced onto a model of another family (the server still starts: a fine-tune
+        may keep its base architecture and change its surface syntax), else None."""
+        if arch and arch not in self.archs:
+            return f"dialect {self.name!r} is normally used with {list(self.archs)}, the model's architecture is {arch!r}"
+        return None
+
+
+def select_dialect(choice: str, model_id: str, arch: str = "") -> ModelDialect:
+    """``choice``: "auto" (from the model id and architecture) or a dialect name."""
+    return ModelDialect(detect_dialect(model_id, arch) if choice in ("", "auto", None) else choice)
 
 
 def detect_dialect(model_id: str, arch: str = "") -> str:

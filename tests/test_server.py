@@ -436,3 +436,28 @@ def test_audio_front_end_and_audio_parts_in_chat_requests():
         assert e.value.code == 400
     finally:
         srv2.stop(); eng2.shutdown()
+
+
+def test_dialects_carry_reasoning_markers_tool_syntax_and_an_architecture_cross_check():
+    from r4dx_b200.server.parsers import GemmaToolCallParser, ModelDialect, QwenToolCallParser, select_dialect
+    d = select_dialect("auto", "gemma-4-12b-it", "gemma")
+    assert d.name == "gemma" and isinstance(d.tool_call_parser(), GemmaToolCallParser) and d.cross_check("gemma") is None
+    sp = d.reasoning_splitter()
+    out = [sp.feed(x) for x in ("<|chan", "nel>thought\nlet me ", "think<chan", "nel|>The answer", " is 4")]
+    c, r = sp.flush()
+    assert "".join(o[0] for o in out) + c == "The answer is 4" and "".join(o[1] for o in out) + r == "let me think"
+    q = select_dialect("auto", "some-qwen-hybrid", "qwen_hybrid")
+    assert q.name == "qwen" and isinstance(q.tool_call_parser(), QwenToolCallParser)
+    sp = q.reasoning_splitter(start_in_think=True)
+    assert sp.feed("plan</think>\n\nhi") == ("hi", "plan")
+    forced = select_dialect("lfm2", "some-qwen-hybrid", "qwen_hybrid")
+    assert forced.name == "lfm2" and "qwen_hybrid" in forced.cross_check("qwen_hybrid")
+    with pytest.raises(ValueError):
+        ModelDialect("klingon")
+    # the engine uses the forced dialect's tool syntax
+    model = FakeTextModel(vocab=300)
+    eng = Engine(model, ByteTokenizer(300))
+    eng.dialect = "lfm2"
+    r = eng.generate(GenRequest(prompt_ids=[1, 2, 3], max_tokens=4, params=SampleParams(temperature=0.0), parse_tools=True), timeout=20)
+    eng.shutdown()
+    assert r.error is None
