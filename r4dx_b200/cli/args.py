@@ -62,6 +62,8 @@ def cli_parser() -> argparse.ArgumentParser:
     ap.add_argument("--profile", action="store_true", help="per-op device timing of one decode step")
     ap.add_argument("--profile-prefill", action="store_true")
     ap.add_argument("--dump-token-ids", action="store_true")
+    ap.add_argument("--image", action="append", default=[], metavar="FILE",
+                    help="image file placed before the prompt text (repeatable); needs --vision on")
     return ap
 
 

@@ -7,13 +7,43 @@ import time
 from .args import cli_parser
 
 
-def run_turn(tm, tk, prompt_ids, args, rng, out=sys.stdout):
+def image_prompt(tm, tk, tpl, messages, files, think: bool):
+    """Renders a prompt whose last user message starts with the given image files: every image becomes as many placeholder
+    tokens as the vision tower yields rows for it, and those rows override the placeholders' embeddings
+    (reference: src/cli/main.cpp:128, the --image path).  Returns (token ids, (positions, rows))."""
+    import numpy as np
+    import torch
+    from PIL import Image
+    from ..models.vision import VisionConfig, VisionTower, init_vision_weights
+    from ..runtime import image_prompt as IP
+    imgs = [torch.from_numpy(np.asarray(Image.open(f).convert("RGB"), dtype=np.uint8).copy()) for f in files]
+    vw = {k[len("vision."):]: v for k, v in getattr(tm.m, "w", {}).items() if isinstance(k, str) and k.startswith("vision.")}
+    vcfg = VisionConfig(out_hidden_size=tm.config.hidden_size)
+    if not vw:                                   # synthetic models get a synthetic tower
+        vcfg = VisionConfig(depth=2, hidden_size=144, num_heads=2, intermediate_size=256, patch_size=8,
+                            out_hidden_size=tm.config.hidden_size, num_position_embeddings=64, max_pixels=256 * 256)
+        vw = init_vision_weights(vcfg, 0)
+    tower = VisionTower(vcfg, vw, device=str(tm.m.device))
+    image_id = getattr(tk, "image_pad_id", tm.config.vocab_size - 1)
+    msgs = [dict(m) for m in messages]
+    msgs[-1]["content"] = "".join(IP.MARK % i for i in range(len(imgs))) + msgs[-1]["content"]
+    text = tpl.render(msgs, add_generation_prompt=True, enable_thinking=think)
+    spans = [(IP.MARK % i, image_id, IP.image_token_count(im, vcfg)) for i, im in enumerate(imgs)]
+    ids = IP.assemble_media_prompt(text, spans, tk.encode)
+    rows = tower.encode_images(imgs)
+    where = torch.tensor([i for i, t in enumerate(ids) if t == image_id], dtype=torch.long)
+    if where.numel() != rows.shape[0]:
+        raise ValueError(f"{where.numel()} image placeholder tokens for {rows.shape[0]} image rows")
+    return ids, (where, rows)
+
+
+def run_turn(tm, tk, prompt_ids, args, rng, out=sys.stdout, embed_overrides=None):
     """Prefill + decode one answer; returns (token ids, stats dict)."""
     from ..runtime.sampler import SampleParams
     from ..runtime.tokenizer import StreamDecoder
     params = SampleParams(args.temperature, args.top_k, args.top_p, args.min_p, args.seed, args.repetition_penalty)
     t0 = time.perf_counter()
-    tok = tm.prefill(prompt_ids)
+    tok = tm.prefill(prompt_ids, embed_overrides=embed_overrides) if embed_overrides is not None else tm.prefill(prompt_ids)
     if not params.greedy:
         tok = tm.sample_from_last(params, rng, prompt_ids)
     t1 = time.perf_counter()
@@ -82,10 +112,17 @@ def main(argv=None) -> int:
         return 0
     prompt = args.prompt if args.prompt is not None else (open(args.prompt_file).read() if args.prompt_file else "Hello")
     messages.append({"role": "user", "content": prompt})
-    pids = build(messages)
+    overrides = None
+    if args.image:
+        if args.vision != "on":
+            print("--image needs --vision on", file=sys.stderr)
+            return 2
+        pids, overrides = image_prompt(tm, tk, tpl, messages, args.image, args.think == "on")
+    else:
+        pids = build(messages)
     if args.dump_token_ids:
         print(pids, file=sys.stderr)
-    ids, stats = run_turn(tm, tk, pids, args, rng)
+    ids, stats = run_turn(tm, tk, pids, args, rng, embed_overrides=overrides)
     if args.stats:
         print(f"[stats] prefill {stats['prefill_tok_s']:.1f} tok/s (TTFT {stats['ttft_s'] * 1e3:.1f} ms), decode "
               f"{stats['decode_tok_s']:.1f} tok/s, {stats['tokens_per_round']:.2f} tokens/round, tp={tm.tp_world()}", file=sys.stderr)
