@@ -461,3 +461,62 @@ def test_dialects_carry_reasoning_markers_tool_syntax_and_an_architecture_cross_
     r = eng.generate(GenRequest(prompt_ids=[1, 2, 3], max_tokens=4, params=SampleParams(temperature=0.0), parse_tools=True), timeout=20)
     eng.shutdown()
     assert r.error is None
+
+
+def test_ngram_drafter_through_the_local_text_model_protocol():
+    """LocalTextModel + NgramDrafter over a stand-in for the device model (a deterministic next-token rule that repeats
+    itself): the speculative greedy stream equals the plain one and needs fewer target calls."""
+    import torch
+    from r4dx_b200.models.ngram import NgramDrafter
+    from r4dx_b200.runtime.text_model import LocalTextModel
+
+    class StubModel:
+        """next token = (sum of the last two tokens) mod 7: periodic, so earlier n-grams predict the future"""
+        max_ctx = 4096
+
+        def __init__(self):
+            self.hist, self.calls = [], 0
+            self.cfg = type("C", (), {"tp_world": 1})()
+            self.buf = type("B", (), {})()
+
+        @property
+        def pos(self):
+            return len(self.hist)
+
+        def _next(self, h):
+            return (h[-1] + (h[-2] if len(h) > 1 else 0)) % 7
+
+        def reset(self):
+            self.hist = []
+
+        def prefill(self, ids, chunk=None, hook=None, embed_overrides=None):
+            self.calls += 1
+            self.hist += [int(t) for t in ids.tolist()]
+            return self._next(self.hist)
+
+        def verify_window(self, anchor, drafts):
+            self.calls += 1
+            h = self.hist + [anchor]
+            emitted = []
+            for d in list(drafts) + [None]:
+                t = self._next(h)
+                emitted.append(t)
+                if d is None or d != t:
+                    break
+                h.append(d)
+            self.hist += [anchor] + emitted[:-1]
+            return emitted
+
+    def run(drafter, k):
+        m = StubModel()
+        tm = LocalTextModel(m, drafter=drafter)
+        tok = tm.prefill([1, 2, 3, 5, 1])
+        out = [tok]
+        while len(out) < 40:
+            out += tm.decode_step_spec_greedy(out[-1], k) if drafter is not None else [m.verify_window(out[-1], [])[0]]
+        return out[:40], m.calls
+
+    plain, calls_plain = run(None, 0)
+    spec, calls_spec = run(NgramDrafter(2, 4), 4)
+    assert spec == plain
+    assert calls_spec < 0.6 * calls_plain, (calls_spec, calls_plain)
