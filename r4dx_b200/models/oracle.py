@@ -160,6 +160,9 @@ class OracleModel:
         return x @ self.w[name].T
 
     # ---- blocks ------------------------------------------------------------------------
+    # absolute [start, end) image blocks of the current call: rows inside one see their whole block on sliding-window layers
+    image_blocks = None
+
     def attention(self, p: str, li, x: torch.Tensor, st: OracleState, store: bool = True) -> torch.Tensor:
         cfg, w = self.cfg, self.w
         T = x.shape[0]
@@ -185,7 +188,11 @@ class OracleModel:
         V = torch.cat([st.v[li], v], 0) if li in st.v else v
         if store:
             st.k[li], st.v[li] = K, V
-        o = R.causal_gqa_attention(q, K, V, st.pos, window)
+        limit = None
+        if self.image_blocks and window > 0:
+            from .gemma_vision import key_limit_ext
+            limit = key_limit_ext(st.pos, T, self.image_blocks)
+        o = R.causal_gqa_attention(q, K, V, st.pos, window, limit)
         o = self._r(o * torch.sigmoid(gate)) if gate is not None else self._r(o)
         return self._r(self._mm(o.reshape(T, Hq * D), p + "attn.o"))
 
@@ -249,11 +256,17 @@ class OracleModel:
 
     # ---- model -------------------------------------------------------------------------
     def forward(self, ids: torch.Tensor, st: Optional[OracleState] = None, return_hidden: bool = False,
-                capture_layers: Optional[List[int]] = None):
-        """Feeds ``ids`` (1-D) at positions st.pos.. and returns logits [T, vocab] (fp32)."""
+                capture_layers: Optional[List[int]] = None, embed_overrides=None, image_blocks=None):
+        """Feeds ``ids`` (1-D) at positions st.pos.. and returns logits [T, vocab] (fp32).  ``embed_overrides`` =
+        (row indices, rows) replaces those rows' input embeddings (image / audio rows); ``image_blocks`` = absolute
+        [start, end) runs of image rows, which must lie inside this call (a block is never split over calls)."""
         cfg, w = self.cfg, self.w
         st = st if st is not None else OracleState()
         x = w["text.embed_tokens"][ids.long()]
+        if embed_overrides is not None:
+            x = x.clone()
+            x[embed_overrides[0].long()] = embed_overrides[1].float()
+        self.image_blocks = list(image_blocks) if image_blocks else None
         captured = {}
         for i in range(cfg.num_hidden_layers):
             p = f"text.layers.{i}."
@@ -275,6 +288,7 @@ class OracleModel:
                 m = self._r(R.rmsnorm_1pw(m, w[p + "post_mlp_out_norm"], cfg.rms_norm_eps))
             x = self._r(x + m)
         st.pos += ids.shape[0]
+        self.image_blocks = None
         hn = self._r(R.rmsnorm_1pw(x, w["text.final_norm"], cfg.rms_norm_eps))
         logits = self._mm(hn, "lm_head")
         if return_hidden:

@@ -103,10 +103,13 @@ def fp8_e4m3_roundtrip(x: torch.Tensor, descale: float | torch.Tensor = 1.0) -> 
 # ---------------------------------------------------------------------------------------------
 # attention
 # ---------------------------------------------------------------------------------------------
-def causal_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos0: int, window: int = 0) -> torch.Tensor:
+def causal_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_pos0: int, window: int = 0,
+                         key_limit: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q: [T, Hq, D]; k, v: [S, Hkv, D] holding positions 0..S-1; query row t sits at q_pos0 + t.
 
-    q head h reads KV head h // (Hq / Hkv).  Returns [T, Hq, D] fp32.
+    q head h reads KV head h // (Hq / Hkv).  ``key_limit`` [T] (absolute position, -1 = none) lets a row also see keys
+    AFTER its own position up to that limit - the bidirectional mask inside an image block; the window still applies from
+    below.  Returns [T, Hq, D] fp32.
     """
     T, Hq, D = q.shape
     S, Hkv, _ = k.shape
@@ -116,7 +119,8 @@ def causal_gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_po
     vf = v.float()
     scores = torch.einsum("thgd,shd->hgts", qf, kf) / math.sqrt(D)
     pos_q = q_pos0 + torch.arange(T)
-    mask = torch.arange(S)[None, :] > pos_q[:, None]
+    upper = pos_q if key_limit is None else torch.maximum(pos_q, key_limit.to(pos_q.dtype))
+    mask = torch.arange(S)[None, :] > upper[:, None]
     if window > 0:          # sliding window: a row sees its last ``window`` keys only
         mask = mask | (torch.arange(S)[None, :] <= pos_q[:, None] - window)
     scores = scores.masked_fill(mask[None, None], float("-inf"))

@@ -159,3 +159,54 @@ def test_sigmoid_router_bias_moves_the_selection_but_not_the_weights():
     assert ids.tolist() == [[3, 0]]
     sel = torch.stack([s[3], s[0]])
     assert torch.allclose(w[0], (sel / (sel.sum() + 1e-6) * 2.0).to(torch.bfloat16).float())
+
+
+def test_image_blocks_are_bidirectional_on_sliding_layers_only():
+    """Gemma-style image rows: inside a block the sliding-window layers see the whole block, so an early row of the block
+    depends on a later one; outside blocks, and on a model without windows, the mask stays causal.  Chunking that keeps a
+    block whole gives the same logits as one call."""
+    from r4dx_b200.config import tiny_gemma_config, tiny_llama_config
+    from r4dx_b200.models import gemma_vision as GV
+    from r4dx_b200.models.oracle import OracleModel, init_weights
+    from r4dx_b200.ops import reference as R
+    # op level: the dense reference mask and the key-limit form agree
+    g = torch.Generator().manual_seed(0)
+    T, window, blocks = 20, 5, [(4, 9), (12, 15)]
+    q, k, v = torch.randn(T, 4, 16, generator=g), torch.randn(T, 2, 16, generator=g), torch.randn(T, 2, 16, generator=g)
+    got = R.causal_gqa_attention(q, k, v, 0, window, GV.key_limit_ext(0, T, blocks))
+    mask = GV.dense_mask(T, window, True, blocks)
+    s = torch.einsum("thgd,shd->hgts", q.view(T, 2, 2, 16), k) / 4.0
+    ref = torch.einsum("hgts,shd->thgd", torch.softmax(s.masked_fill(~mask[None, None], float("-inf")), -1), v).reshape(T, 4, 16)
+    assert torch.allclose(got, ref, atol=1e-5)
+    # model level
+    cfg = tiny_gemma_config()
+    w = init_weights(cfg, 3)
+    m = OracleModel(cfg, w)
+    ids = torch.randint(0, cfg.vocab_size, (18,), generator=g)
+    rows = torch.randn(5, cfg.hidden_size, generator=g) * 0.5
+    ov = (torch.arange(6, 11), rows)
+    blocks = [(6, 11)]
+    causal, _ = m.forward(ids, embed_overrides=ov)
+    bidir, _ = m.forward(ids, embed_overrides=ov, image_blocks=blocks)
+    assert torch.allclose(causal[:6], bidir[:6], atol=1e-5)                  # rows before the block are untouched
+    assert not torch.allclose(causal[6], bidir[6], atol=1e-4)                # the block's first row now sees the rest of it
+    rows2 = rows.clone()
+    rows2[4] += 1.0                                                          # change the block's LAST row
+    moved, _ = m.forward(ids, embed_overrides=(ov[0], rows2), image_blocks=blocks)
+    assert not torch.allclose(moved[6], bidir[6], atol=1e-4)                 # ... and its first row's logits move
+    moved_c, _ = m.forward(ids, embed_overrides=(ov[0], rows2))
+    assert torch.allclose(moved_c[6], causal[6], atol=1e-5)                  # causal: they do not
+    # block-safe chunking reproduces the single call
+    chunks = GV.plan_prefill_chunks(18, blocks, 8, max_block=8)
+    st, out = None, []
+    for s0, n in chunks:
+        sel = (ov[0] >= s0) & (ov[0] < s0 + n)
+        lg, st = m.forward(ids[s0:s0 + n], st, embed_overrides=(ov[0][sel] - s0, rows[sel]), image_blocks=blocks)
+        out.append(lg)
+    assert torch.allclose(torch.cat(out), bidir, atol=1e-4, rtol=1e-4)
+    # a family without sliding windows ignores the blocks
+    lc = tiny_llama_config()
+    lm = OracleModel(lc, init_weights(lc, 1))
+    a, _ = lm.forward(ids % lc.vocab_size)
+    b, _ = lm.forward(ids % lc.vocab_size, image_blocks=blocks)
+    assert torch.equal(a, b)
