@@ -69,6 +69,11 @@ class BpeTokenizer:
         self.id_to_token.update({i: t for t, i in self.added.items()})
         self.vocab_size = max(self.id_to_token) + 1 if self.id_to_token else 0
         self._cache: Dict[str, List[int]] = {}
+        # SentencePiece-style vocabularies whose tokens carry "▁" only as a leading run never merge across the start of
+        # such a run, so the text can be cut there and every piece encoded (and cached) on its own - same ids, far less work
+        self._sp_split = (not self.byte_level and
+                          all(regex.fullmatch(r"▁*[^▁]*", t) is not None for t in self.vocab))
+        self._sp_pieces = regex.compile(r"▁*[^▁]+|▁+")
         self._native = None
         self._init_native()
         self.eos_ids: List[int] = []
@@ -206,7 +211,7 @@ class BpeTokenizer:
             if self.prefix_space and first:
                 text = " " + text
             text = text.replace(" ", "▁")
-            pieces = [text]
+            pieces = self._sp_pieces.findall(text) if self._sp_split else [text]
         out: List[int] = []
         for p in pieces:
             out += self._piece(p)

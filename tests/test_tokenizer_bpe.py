@@ -98,3 +98,32 @@ def test_loader_prefers_the_own_tokenizer(tmp_path):
     tk, tpl = load_tokenizer(os.path.dirname(path))
     assert isinstance(tk, BpeTokenizer) and 1 in tk.eos_ids
     assert "hello" in tpl.render([{"role": "user", "content": "hello"}])
+
+
+def test_sentencepiece_style_text_is_cut_at_space_runs_without_changing_the_ids(tmp_path):
+    """A vocabulary whose tokens carry the space marker only as a leading run: cutting the text before every run of markers
+    gives the ids of whole-text BPE (and of the Hugging Face encoder)."""
+    from tokenizers import Tokenizer
+    from r4dx_b200.runtime.bpe import BpeTokenizer
+    chars = ["▁", "a", "b", "c", "d", "e", "\n", "."]
+    merges = [("▁", "a"), ("a", "b"), ("▁", "▁"), ("▁a", "b"), ("c", "d"), ("▁▁", "c"), ("ab", "cd"), ("▁", "c"), ("d", "e"), ("▁▁", "▁")]
+    vocab = {c: i for i, c in enumerate(chars)}
+    for a, b in merges:
+        vocab.setdefault(a + b, len(vocab))
+    spec = {"version": "1.0", "truncation": None, "padding": None, "added_tokens": [],
+            "normalizer": {"type": "Replace", "pattern": {"String": " "}, "content": "▁"}, "pre_tokenizer": None,
+            "post_processor": None, "decoder": None,
+            "model": {"type": "BPE", "dropout": None, "unk_token": None, "continuing_subword_prefix": None,
+                      "end_of_word_suffix": None, "fuse_unk": False, "byte_fallback": False, "ignore_merges": False,
+                      "vocab": vocab, "merges": [[a, b] for a, b in merges]}}
+    path = str(tmp_path / "tokenizer.json")
+    json.dump(spec, open(path, "w"))
+    hf = Tokenizer.from_file(path)
+    mine = BpeTokenizer(path)
+    assert mine._sp_split and not mine.byte_level
+    whole = BpeTokenizer(path)
+    whole._sp_split = False
+    for s in ["ab abcd  cde", "  c   ab", "a\nb. ab", "abcd", "   ", " a b c d e "]:
+        want = hf.encode(s, add_special_tokens=False).ids
+        assert mine.encode(s) == want == whole.encode(s), s
+        assert mine.decode(mine.encode(s)) == s
