@@ -35,16 +35,50 @@ __device__ __forceinline__ bool MbarTryWait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool MbarTestWait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(SmemAddr(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// try_wait that lets the hardware park the thread for up to `hint_ns` before it answers "not yet": a waiting
+// thread then costs an issue slot every few microseconds instead of every few dozen clocks.
+__device__ __forceinline__ bool MbarTryWaitHint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(SmemAddr(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  `abort_flag` is a shared-memory word any role sets when it gives up; everyone who
-// sees it leaves too.  Returns false on abort / timeout.
+// sees it leaves too.  Returns false on abort / timeout (about a second of SM clocks).
+// (Measured on the weight-streaming kernel: with a plain try_wait loop a quarter of all issued instructions
+// were the polling of waiting lanes - BRA / SYNCS / ISETP - taken from the warps that had work.)
 constexpr int kSpinLimit = 1 << 22;
+constexpr long long kWaitClocks = 2000000000ll;
 __device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
-  for (int i = 0; i < kSpinLimit; ++i) {
-    if (MbarTryWait(bar, parity)) return true;
-    if ((i & 63) == 63 && *abort_flag) return false;
+  if (MbarTestWait(bar, parity)) return true;      // the common case in a well-fed pipeline: no suspension at all
+  const long long t0 = clock64();
+  for (;;) {
+    if (MbarTryWaitHint(bar, parity, 20000u)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitClocks) break;
   }
   *abort_flag = code;
   return false;
+}
+// The same for a whole (converged) warp: one lane polls, the others sleep in the shuffle.  Thirty-two lanes
+// polling one barrier word serialise in the shared-memory pipe and slow down every other barrier
+// operation of the SM (measured: a satisfied test_wait of another warp went from 15 to ~300 clocks).
+__device__ __forceinline__ bool WarpMbarWait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = MbarWait(bar, parity, abort_flag, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ---- proxies / fences ------------------------------------------------------------------------------
@@ -137,6 +171,58 @@ __device__ __forceinline__ void TmemLoad32x16(uint32_t taddr, uint32_t (&r)[16])
       : "memory");
 }
 __device__ __forceinline__ void TmemLoadWait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 32 lanes x 16 consecutive 32-bit columns: thread t of the warp writes TMEM lane (base lane + t).
+__device__ __forceinline__ void TmemStore32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void TmemStoreWait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major operand without swizzle: 8-row x 16-byte core matrices
+// (128 contiguous bytes each); `lbo` = bytes between the two core matrices that are adjacent in K,
+// `sbo` = bytes between 8-row groups.  The start address needs 16-byte alignment only.
+__device__ __forceinline__ uint64_t UmmaDescNoSwizzle(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(lbo >> 4) << 16;
+  d |= static_cast<uint64_t>(sbo >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;                            // descriptor version (Blackwell)
+  return d;
+}
+// Instruction descriptor, kind::i8: unsigned 8-bit A, signed 8-bit B, both K-major, int32 accumulate.
+__host__ __device__ constexpr uint32_t UmmaInstrDescU8S8(int M, int N) {
+  return (2u << 4) | (0u << 7) | (1u << 10) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+// D[tmem] (+)= A[tmem] * B[smem]^T on 8-bit integers (K = 32 per instruction), issued by ONE thread.
+// A: lane = row, 8 consecutive 32-bit columns = the row's 32 K bytes.
+__device__ __forceinline__ void UmmaI8FromTmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+      "  tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p; }"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]^T on fp16 inputs (K = 16 per instruction), fp32 accumulate, issued by ONE
+// thread.  A: lane = row, 8 consecutive 32-bit columns = the row's 16 K values as half2 pairs.
+__device__ __forceinline__ void UmmaF16FromTmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+      "  tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 lanes x 8 consecutive 32-bit columns.
+__device__ __forceinline__ void TmemStore32x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
 
 __device__ __forceinline__ bool ElectOne() {
   uint32_t pred;

@@ -32,6 +32,7 @@
 #include <cooperative_groups.h>
 
 #include "sm100_ptx.cuh"
+#include "tp_push.cuh"
 #include "trellis_decode.cuh"
 
 namespace cg = cooperative_groups;
@@ -44,26 +45,6 @@ namespace {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kMaxWorld = 8;
-
-// Tensor-parallel epilogue: all-reduce by one-shot push over NVLink peer memory.  Each value travels
-// as an 8-byte (fp32 value, sequence number) pair, so data and "ready" flag arrive in one store and
-// no fence or separate flag round is needed; the receiver polls the pairs it needs (bounded).  Every
-// rank sums the world's partials in rank order, so all ranks hold identical bits.  Receive slots are
-// double-buffered by the parity of a per-block call counter kept in device memory (a captured graph
-// can be replayed).
-struct TpPush {
-  float2* recv[kMaxWorld];         // recv[p]: rank p's buffer [2][world][8][N] of (value, seq) pairs, peer-mapped
-  unsigned* block_seq;             // local [N/128] call counters
-  int* status;                     // local: set to 100 + rank when that rank did not answer in time
-  int world, rank, spin_limit;
-  // expert-parallel output (grouped mode): row gp = (rank gp / ep_P, pair gp % ep_P) goes to that rank's
-  // combine buffer ep_y[rank] ([2][ep_P][N] bf16) and bumps ep_cnt[rank] ([2][ep_P]) once per 128-column block
-  __nv_bfloat16* ep_y[kMaxWorld];
-  unsigned* ep_cnt[kMaxWorld];
-  int ep_P;
-};
-
 struct GemvArgs {
   const uint32_t* words;
   const __half* suh;
@@ -184,14 +165,14 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
         const unsigned call = *a.g_seq + 1;
         if (warp < T && lane == 0) {
           const unsigned* f = a.g_ready + in_row(warp);
-          bool got = false;
-          for (int i = 0; i < a.g_spin_limit; ++i) {
+          bool got = TpStatusNow(a.g_status) != 0;       // sticky: after one timeout nobody waits again
+          for (int i = 0; i < a.g_spin_limit && !got; ++i) {
             unsigned v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
             if (v == call) { got = true; break; }
             if (i > 64) __nanosleep(32);
           }
-          if (!got) atomicExch(a.g_status, 400 + static_cast<int>(in_row(warp) % 1000));
+          if (!got) atomicCAS(a.g_status, 0, 400 + static_cast<int>(in_row(warp) % 1000));
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
       }
@@ -352,6 +333,11 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
             : "=r"(okw) : "r"(ptx::SmemAddr(red_bar)), "r"(0) : "memory");
         landed = okw != 0;
       }
+      // a split-K hand-off that never completes leaves a code in whichever status word this launch was given
+      if (!landed && lane == 0) {
+        if constexpr (kTp) atomicCAS(tp.status, 0, 390);
+        if constexpr (kGrouped) { if (a.g_status != nullptr) atomicCAS(a.g_status, 0, 390); }
+      }
     }
     const float inv_sqrt = 0.08838834764831845f;
     float o[4] = {0.f, 0.f, 0.f, 0.f};
@@ -371,39 +357,7 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
     }
     if constexpr (kTp) {
       const unsigned seq = tp.block_seq[nb] + 1;     // written only by this CTA, after the barrier below
-      const size_t slot_pairs = static_cast<size_t>(tp.world) * 8 * N;
-      if (t < T) {
-        const size_t my_off = (seq & 1) * slot_pairs + (static_cast<size_t>(tp.rank) * 8 + t) * N + n;
-        const float fs = __uint_as_float(seq);
-        for (int p = 0; p < tp.world; ++p) {
-          if (p == tp.rank) continue;
-          float4* dst = reinterpret_cast<float4*>(tp.recv[p] + my_off);
-          dst[0] = make_float4(o[0], fs, o[1], fs);
-          dst[1] = make_float4(o[2], fs, o[3], fs);
-        }
-        float a4[4] = {0.f, 0.f, 0.f, 0.f};
-        const float2* mine = tp.recv[tp.rank] + (seq & 1) * slot_pairs;
-        bool fail = false;
-        for (int r = 0; r < tp.world; ++r) {     // rank order, identical on every rank
-          if (r == tp.rank) {
-            a4[0] += o[0]; a4[1] += o[1]; a4[2] += o[2]; a4[3] += o[3];
-            continue;
-          }
-          const float4* src = reinterpret_cast<const float4*>(mine + (static_cast<size_t>(r) * 8 + t) * N + n);
-          float4 p0, p1;
-          bool got = false;
-          for (int i = 0; i < tp.spin_limit; ++i) {
-            p0 = __ldcv(src);
-            p1 = __ldcv(src + 1);
-            if (__float_as_uint(p0.y) == seq && __float_as_uint(p0.w) == seq && __float_as_uint(p1.y) == seq &&
-                __float_as_uint(p1.w) == seq) { got = true; break; }
-            if (i > 256) __nanosleep(32);
-          }
-          if (!got) { fail = true; atomicExch(tp.status, 100 + r); break; }
-          a4[0] += p0.x; a4[1] += p0.z; a4[2] += p1.x; a4[3] += p1.z;
-        }
-        if (!fail) { o[0] = a4[0]; o[1] = a4[1]; o[2] = a4[2]; o[3] = a4[3]; }
-      }
+      if (t < T) TpAllReduceRow(tp, seq, t, N, n, o);
       asm volatile("bar.sync 2, 256;" ::: "memory");
       if (threadIdx.x == 0) tp.block_seq[nb] = seq;
     }

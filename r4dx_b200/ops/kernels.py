@@ -175,7 +175,39 @@ def pick_ksplit(N: int, K: int, target_ctas: int = int(os.environ.get("R4DXB_KSP
     return best
 
 
+_STATUS = {}
+
+
+def gemm_status(device) -> torch.Tensor:
+    """Device word that a tcgen05 kernel sets when one of its bounded waits runs out."""
+    key = torch.device(device).index or 0
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _STATUS[key]
+
+
+def check_gemm_status(device) -> None:
+    code = int(gemm_status(device).item())
+    if code:
+        gemm_status(device).zero_()
+        raise KernelError(f"tcgen05 GEMM gave up in a bounded wait (role code {code})")
+
+
 PRO_NONE, PRO_RMSNORM, PRO_SILU_MUL, PRO_GELU_MUL = 0, 1, 2, 3
+
+register_cuda_sig("r4dxb_trellis_gemv_mma", _I, [_P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _I, _P, _P])
+
+# Which weight-streaming kernel serves T <= 8 rows: "simt" = CUDA-core decode + fp16 FMA (default: the faster one
+# on the 27B shapes, 56-62 us vs 66-68 us on gate_up), "mma" = code values written to tensor memory and contracted
+# by tcgen05.mma kind::f16 (trellis_gemv_mma.cu).
+GEMV_IMPL = os.environ.get("R4DXB_GEMV", "simt")
+
+
+def set_gemv_impl(name: str) -> None:
+    global GEMV_IMPL
+    if name not in ("mma", "simt"):
+        raise KernelError(f"unknown weight-streaming kernel {name!r}")
+    GEMV_IMPL = name
 
 
 def trellis_gemv(w: TrellisWeight, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
@@ -190,6 +222,11 @@ def trellis_gemv(w: TrellisWeight, x: torch.Tensor, residual: Optional[torch.Ten
     T = x.numel() // (2 * w.K if prologue in (PRO_SILU_MUL, PRO_GELU_MUL) else w.K)
     out = out if out is not None else torch.empty(T, w.N, dtype=BF, device=x.device)
     ks = ksplit or pick_ksplit(w.N, w.K)
+    if GEMV_IMPL == "mma" and w.K // ks <= 6144:
+        _check(_lib().r4dxb_trellis_gemv_mma(_p(w.words), _p(w.suh), _p(w.svh), _p(x), _p(out), _p(residual), _p(norm_w), eps,
+                                             prologue, T, w.N, w.K, w.kb, ks, _p(gemm_status(x.device)), _stream()),
+               "trellis_gemv_mma")
+        return out
     _check(_lib().r4dxb_trellis_gemv_ex(_p(w.words), _p(w.suh), _p(w.svh), _p(x), _p(out), _p(residual), _p(norm_w), eps,
                                         prologue, T, w.N, w.K, w.kb, ks, _stream()), "trellis_gemv")
     return out
@@ -266,24 +303,6 @@ def attn_decode(q, qg, cache, block_table, positions, k_descale, v_descale, part
 
 register_cuda_sig("r4dxb_trellis_input", _I, [_P, _P, _P, _I, _I, _I, _P])
 register_cuda_sig("r4dxb_trellis_gemm", _I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P])
-
-_STATUS = {}
-
-
-def gemm_status(device) -> torch.Tensor:
-    """Device word that a tcgen05 kernel sets when one of its bounded waits runs out."""
-    key = torch.device(device).index or 0
-    if key not in _STATUS:
-        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _STATUS[key]
-
-
-def check_gemm_status(device) -> None:
-    code = int(gemm_status(device).item())
-    if code:
-        gemm_status(device).zero_()
-        raise KernelError(f"tcgen05 GEMM gave up in a bounded wait (role code {code})")
-
 
 def trellis_input(x: torch.Tensor, suh: torch.Tensor, out: Optional[torch.Tensor] = None, fused_silu_mul: bool = False,
                   gelu: bool = False) -> torch.Tensor:

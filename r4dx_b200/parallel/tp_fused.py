@@ -25,6 +25,8 @@ from .tp_comm import NcclComm
 
 register_cuda_sig("r4dxb_trellis_gemv_allreduce", c_int,
                   [c_ptr] * 6 + [c_int] * 6 + [c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_ptr])
+register_cuda_sig("r4dxb_trellis_gemv_mma_allreduce", c_int,
+                  [c_ptr] * 6 + [c_int] * 6 + [c_ptr, c_ptr, c_ptr, c_int, c_int, c_int, c_ptr, c_ptr])
 register_cuda_sig("r4dxb_trellis_gemm_rs", c_int, [c_ptr, c_ptr, c_ptr] + [c_int] * 5 + [c_ptr, c_ptr, c_ptr] + [c_int] * 3 + [c_ptr])
 register_cuda_sig("r4dxb_tp_reduce_push", c_int, [c_ptr, c_ptr, c_ptr, c_ptr, ctypes.c_uint32] + [c_int] * 6 + [c_ptr, c_ptr])
 register_cuda_sig("r4dxb_tp_wait", c_int, [c_ptr, ctypes.c_uint32, c_int, c_int, c_ptr, c_ptr])
@@ -57,10 +59,17 @@ class FusedComm(NcclComm):
         if not isinstance(w, TrellisWeight) or w.N != self.n:
             return super().row_parallel_linear(lin, x, res, prologue)
         T = res.shape[0]
-        rc = self._lib.r4dxb_trellis_gemv_allreduce(
-            w.words.data_ptr(), w.suh.data_ptr(), w.svh.data_ptr(), x.data_ptr(), res.data_ptr(), res.data_ptr(),
-            prologue, T, w.N, w.K, w.kb, lin.ksplit, self.recv_tab, self.block_seq.data_ptr(),
-            self.status.data_ptr(), self.world, self.rank, self.spin_limit, torch.cuda.current_stream().cuda_stream)
+        if K.GEMV_IMPL == "mma" and w.K // lin.ksplit <= 6144:
+            rc = self._lib.r4dxb_trellis_gemv_mma_allreduce(
+                w.words.data_ptr(), w.suh.data_ptr(), w.svh.data_ptr(), x.data_ptr(), res.data_ptr(), res.data_ptr(),
+                prologue, T, w.N, w.K, w.kb, lin.ksplit, self.recv_tab, self.block_seq.data_ptr(),
+                self.status.data_ptr(), self.world, self.rank, self.spin_limit, K.gemm_status(self.device).data_ptr(),
+                torch.cuda.current_stream().cuda_stream)
+        else:
+            rc = self._lib.r4dxb_trellis_gemv_allreduce(
+                w.words.data_ptr(), w.suh.data_ptr(), w.svh.data_ptr(), x.data_ptr(), res.data_ptr(), res.data_ptr(),
+                prologue, T, w.N, w.K, w.kb, lin.ksplit, self.recv_tab, self.block_seq.data_ptr(),
+                self.status.data_ptr(), self.world, self.rank, self.spin_limit, torch.cuda.current_stream().cuda_stream)
         if rc != 0:
             raise K.KernelError(f"trellis_gemv_allreduce failed with code {rc}")
         self.stats.all_reduces += 1

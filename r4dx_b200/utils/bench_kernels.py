@@ -56,9 +56,12 @@ def main() -> None:
     ap.add_argument("--decode-warps", type=int, default=16)
     ap.add_argument("--tn", type=int, default=0)
     ap.add_argument("--ksplit", type=int, default=0, help="override the cluster split of the weight-streaming kernel")
+    ap.add_argument("--impl", default="", help="weight-streaming kernel: mma (tensor memory, default) or simt (CUDA cores)")
     a = ap.parse_args()
     from r4dx_b200.ops import kernels as K
     from r4dx_b200.quant import trellis, w4a16
+    if a.impl:
+        K.set_gemv_impl(a.impl)
     peak = _peak_gbs()
     dev = "cuda"
     flush = torch.zeros(256 << 18, dtype=torch.float32, device=dev)
@@ -77,7 +80,8 @@ def main() -> None:
                     continue
                 us = timed(lambda: K.trellis_gemv(w, x, out=y, ksplit=ks), a.iters, flush)
                 gbs = w.nbytes / us / 1e3
-                print(f"trellis_gemv {name:12s} N={N:6d} K={Kd:6d} kb={kb} T={T} ksplit={ks}: {us:8.1f} us  "
+                K.check_gemm_status(dev)
+                print(f"trellis_gemv[{K.GEMV_IMPL}] {name:12s} N={N:6d} K={Kd:6d} kb={kb} T={T} ksplit={ks}: {us:8.1f} us  "
                       f"{gbs:7.0f} GB/s  {gbs / peak:5.2f} of measured HBM  {N * Kd / us / 1e6:6.2f} Tweights/s")
     if a.only in ("trellis_gemm",):
         Tg = max(a.rows, 16)

@@ -35,13 +35,19 @@ def _peer_push(recv0, slot_pairs, N, seq, value, rows=8):
     blk[:, 1] = seq_f
 
 
-def _call(L, K, w, x, res, tab, block_seq, status, spin):
+def _call(L, K, w, x, res, tab, block_seq, status, spin, impl="simt"):
+    if impl == "mma":
+        return L.r4dxb_trellis_gemv_mma_allreduce(
+            w.words.data_ptr(), w.suh.data_ptr(), w.svh.data_ptr(), x.data_ptr(), res.data_ptr(), res.data_ptr(), K.PRO_NONE,
+            x.shape[0], w.N, w.K, w.kb, K.pick_ksplit(w.N, w.K), tab, block_seq.data_ptr(), status.data_ptr(), 2, 0, spin,
+            K.gemm_status("cuda").data_ptr(), torch.cuda.current_stream().cuda_stream)
     return L.r4dxb_trellis_gemv_allreduce(w.words.data_ptr(), w.suh.data_ptr(), w.svh.data_ptr(), x.data_ptr(), res.data_ptr(),
                                           res.data_ptr(), K.PRO_NONE, x.shape[0], w.N, w.K, w.kb, K.pick_ksplit(w.N, w.K), tab,
                                           block_seq.data_ptr(), status.data_ptr(), 2, 0, spin, torch.cuda.current_stream().cuda_stream)
 
 
-def test_scripted_peer_sum_is_rank_ordered_and_survives_sequence_wrap():
+@pytest.mark.parametrize("impl", ["simt", "mma"])
+def test_scripted_peer_sum_is_rank_ordered_and_survives_sequence_wrap(impl):
     L, K, w, recv, tab, sp = _setup()
     N = w.N
     g = torch.Generator().manual_seed(0)
@@ -55,9 +61,10 @@ def test_scripted_peer_sum_is_rank_ordered_and_survives_sequence_wrap():
         res0 = torch.randn(3, N, generator=g).to(BF).cuda()
         res = res0.clone()
         _peer_push(recv[0], sp, N, seq, 0.25 * (i + 1))
-        assert _call(L, K, w, x, res, tab, block_seq, status, 1 << 16) == 0
+        assert _call(L, K, w, x, res, tab, block_seq, status, 1 << 16, impl) == 0
         torch.cuda.synchronize()
         assert int(status.item()) == 0
+        K.check_gemm_status("cuda")
         own = K.trellis_gemv(w, x).float()
         want = (own + 0.25 * (i + 1) + res0.float())
         assert torch.allclose(res.float(), want, atol=0.03 * want.abs().max().item(), rtol=2e-2)
@@ -66,16 +73,26 @@ def test_scripted_peer_sum_is_rank_ordered_and_survives_sequence_wrap():
         assert torch.equal(mine[:, 1].view(torch.int32), torch.full((3 * N,), seq - (2 ** 32 if seq >= 2 ** 31 else 0), dtype=torch.int32, device="cuda"))
 
 
-def test_a_wait_that_runs_out_reports_the_missing_rank_and_leaves_the_context_usable():
+@pytest.mark.parametrize("impl", ["simt", "mma"])
+def test_a_wait_that_runs_out_reports_the_missing_rank_and_leaves_the_context_usable(impl):
     L, K, w, recv, tab, sp = _setup(seed=2)
     N = w.N
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     block_seq = torch.zeros(N // 128, dtype=torch.int32, device="cuda")
     x = torch.randn(1, w.K).to(BF).cuda()
     res = torch.zeros(1, N, dtype=BF, device="cuda")
-    assert _call(L, K, w, x, res, tab, block_seq, status, 1 << 10) == 0        # nobody pushes: the wait gives up quickly
+    assert _call(L, K, w, x, res, tab, block_seq, status, 1 << 10, impl) == 0  # nobody pushes: the wait gives up quickly
     torch.cuda.synchronize()
     assert int(status.item()) == 101                                          # 100 + the rank that never answered
+    # sticky: with the word still set, the next hundred calls do not wait at all (generous limit, still quick)
+    import time
+    t0 = time.perf_counter()
+    for _ in range(100):
+        assert _call(L, K, w, x, res, tab, block_seq, status, 1 << 22, impl) == 0
+    torch.cuda.synchronize()
+    assert (time.perf_counter() - t0) / 100 < 1e-3
+    assert int(status.item()) == 101
+    assert int(block_seq[0].item()) == 101                                    # counters still advance, so a recovery can rebase them
     # the device is fine: an ordinary product right after gives the right answer
     y = K.trellis_gemv(w, x)
     from r4dx_b200.quant import trellis

@@ -73,6 +73,31 @@ def test_trellis_gemv(K, kb, T, ksplit):
     assert (y2.float().cpu() - (ref + res.float())).abs().max().item() < 0.02 * (scale + 3) + 1e-3
 
 
+@pytest.mark.parametrize("kb", [3, 4, 5])
+@pytest.mark.parametrize("T,ksplit,Kd", [(1, 2, 5120), (4, 8, 17408), (8, 1, 1024), (2, 4, 6144)])
+def test_trellis_gemv_tensor_memory_path_against_reference_and_cuda_core_path(K, kb, T, ksplit, Kd):
+    """The int8 tcgen05 path (hash words in tensor memory) and the CUDA-core path compute the same linear map."""
+    from r4dx_b200.quant import trellis
+    N = 256
+    tw = trellis.random_weight(N, Kd, kb, seed=kb + T, sigma=0.02)
+    x = torch.randn(T, Kd, generator=torch.Generator().manual_seed(T + Kd)).to(BF)
+    ref = trellis.linear_reference(tw, x.float())
+    twd, xd = tw.to("cuda"), x.cuda()
+    scale = ref.abs().max().item()
+    impl0 = K.GEMV_IMPL
+    try:
+        K.set_gemv_impl("mma")
+        y_mma = K.trellis_gemv(twd, xd, ksplit=ksplit).float().cpu()
+        K.check_gemm_status("cuda")
+        K.set_gemv_impl("simt")
+        y_simt = K.trellis_gemv(twd, xd, ksplit=ksplit).float().cpu()
+    finally:
+        K.set_gemv_impl(impl0)
+    assert (y_mma - ref).abs().max().item() < 0.01 * scale + 1e-3        # exact integer sums: tighter than the fp16 path
+    assert (y_simt - ref).abs().max().item() < 0.02 * scale + 1e-3
+    assert (y_mma - y_simt).abs().max().item() < 0.02 * scale + 1e-3
+
+
 def test_trellis_gemv_one_hot_returns_decoded_rows(K):
     """x = e_k after undoing the input transform picks out column k of H Q H exactly (up to bf16)."""
     from r4dx_b200.quant import trellis
