@@ -143,6 +143,18 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def verify_ranks(what: str):
+        """A timed region only counts if no device wait ran out in it and every rank holds the same next token."""
+        model.check_healthy()
+        K.check_gemm_status(dev)
+        if world > 1:
+            mine = model.buf.next_ids[:1].to(torch.int64)
+            every = [torch.zeros_like(mine) for _ in range(world)]
+            dist.all_gather(every, mine)
+            toks = [int(t.item()) for t in every]
+            if len(set(toks)) != 1:
+                raise RuntimeError(f"ranks disagree on the next token after {what}: {toks}")
+
     g = torch.Generator().manual_seed(1)
     prompt = torch.randint(0, gcfg.vocab_size, (args.prompt_len,), generator=g, dtype=torch.int32)
 
@@ -159,6 +171,7 @@ def main():
     e1.record()
     barrier()
     ttft_ms = e0.elapsed_time(e1)
+    verify_ranks("prefill")
 
     # ---- device-timed decode -----------------------------------------------------------------------
     K.launch_count_reset()
@@ -178,6 +191,7 @@ def main():
     barrier()
     dev_ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else {}
+    verify_ranks("decode")
     t = torch.tensor([dev_ms, ttft_ms], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -197,6 +211,7 @@ def main():
             nxt = sess.step(nxt)
         e1.record()
         barrier()
+        verify_ranks("end-to-end decode")
         t = torch.tensor([e0.elapsed_time(e1)], device=dev)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -234,8 +249,9 @@ def main():
             "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dev_ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": value / BASELINE_DECODE_TOK_S, "dtype": "bf16",
-            "data": "synthetic: random-init weights created in the quantized layouts (random trellis codes ~4.5 bpw, "
-                    "random w4a16 head), uniform random prompt ids",
+            "data": "synthetic: random-init weights created in the quantized layouts (random trellis code words ~4.5 bpw - the "
+                    "same bytes per tensor as a Viterbi-quantized N(0, 0.02) set, so the same stream - and a random w4a16 head), "
+                    "uniform random prompt ids",
             "config": {"model": args.model if args.layers == 64 else f"{args.model}-{args.layers}layers(INVALID: debug)",
                        "global_batch": 1, "seq_len": args.prompt_len, "parallelism": f"tp{world}",
                        "kv_cache": "fp8 e4m3 paged, 16-token blocks", "weights": "trellis mixed 4/5-bit + w4a16 g64 head",

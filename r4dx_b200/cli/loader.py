@@ -45,8 +45,9 @@ def load_text_model(args, device: Optional[str] = None):
         weights = shard_weight_set(gcfg, full, args.tp, rank)
         model_id = os.path.splitext(os.path.basename(model_arg))[0]
     if args.tp > 1:
-        from ..parallel.tp_comm import make_comm
-        comm = make_comm(args.tp, rank, device, mode=args.tp_mode, hidden=gcfg.hidden_size)
+        from ..parallel.tp_comm import make_comm, spin_limit_for_ms
+        comm = make_comm(args.tp, rank, device, mode=args.tp_mode, hidden=gcfg.hidden_size,
+                         spin_limit=spin_limit_for_ms(getattr(args, "tp_ar_timeout_ms", 500)))
     model = HybridModel(cfg, weights, max_ctx=args.max_ctx, device=device, comm=comm)
     drafter = None
     if args.mtp > 0 and any(k.startswith("mtp.") for k in weights):
@@ -60,5 +61,14 @@ def load_text_model(args, device: Optional[str] = None):
         dcfg, dweights = load_dflash(args.dflash)
         drafter = DflashDrafter(model, dcfg, dweights)
     tk, tpl = load_tokenizer(args.tokenizer_dir, gcfg.vocab_size)
-    return LocalTextModel(model, model_id=model_id, global_config=gcfg, drafter=drafter,
-                          prefill_chunk=getattr(args, "prefill_chunk", 0)), tk, tpl
+    local = LocalTextModel(model, model_id=model_id, global_config=gcfg, drafter=drafter,
+                           prefill_chunk=getattr(args, "prefill_chunk", 0))
+    if args.tp > 1:
+        # rank 0 leads (tokenizer, sampling, front door); the others replay its commands (see runtime/tp_model.py)
+        import torch.distributed as dist
+        from ..parallel.tp_group import FaultSpec, RankGroup
+        from ..runtime.tp_model import TpTextModel
+        ctl = dist.new_group(backend="gloo")
+        group = RankGroup(rank, world, group=ctl, fault=FaultSpec.parse(getattr(args, "tp_fault", "") or ""))
+        return TpTextModel(local, group, ctl_group=ctl, comm=comm), tk, tpl
+    return local, tk, tpl

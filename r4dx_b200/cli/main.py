@@ -81,6 +81,12 @@ def main(argv=None) -> int:
     from ..runtime.sampler import Rng
     from .loader import load_text_model
     tm, tk, tpl = load_text_model(args)
+    if tm.tp_world() > 1 and getattr(tm, "rank", 0) != 0:
+        tm.follow()                      # follower rank: replay the leader's commands, print nothing
+        return 0
+    import atexit
+    if hasattr(tm, "shutdown"):
+        atexit.register(tm.shutdown)     # releases the follower ranks when the leader is done
     rng = Rng(args.seed)
     if args.profile or args.profile_prefill:
         from ..utils.profiler import profile_decode_step, profile_prefill

@@ -13,6 +13,12 @@ def main(argv=None) -> int:
     from ..server.request_log import RequestLog
     from .loader import load_text_model
     tm, tk, tpl = load_text_model(args)
+    if tm.tp_world() > 1 and getattr(tm, "rank", 0) != 0:
+        # follower rank of a tensor-parallel group: no HTTP port, no engine - replay the leader's commands until it stops
+        tm.follow()
+        return 0
+    if args.batch > 1 and tm.tp_world() > 1:
+        raise SystemExit("--batch with --tp is not supported: the slot scheduler runs on one rank")
     if args.batch > 1:
         # N sequence slots over the same weights; the single-sequence model object only lends its weights
         from ..models.batch import BatchModel
@@ -58,6 +64,8 @@ def main(argv=None) -> int:
         pass
     finally:
         eng.shutdown()
+        if hasattr(tm, "shutdown"):
+            tm.shutdown()
     return 0
 
 

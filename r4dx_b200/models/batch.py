@@ -116,6 +116,7 @@ class BatchModel:
         self.pos[slot] = 0
         self._bind(slot)
         tok = self.base.prefill(torch.as_tensor(list(ids), dtype=torch.int32))
+        self.last_prefill_logits = self.base.buf.logits[getattr(self.base, "last_row", 0)].float().clone()
         self.base.commit_pending()
         self.pos[slot] = self.base.pos
         self.n_replay[slot] = 0

@@ -379,6 +379,20 @@ class HybridModel:
         self.pending_rows = n
         self.pos += n
 
+    def check_healthy(self) -> None:
+        """Raises if a bounded device wait ran out since the last check: a timed-out collective leaves an un-reduced partial
+        in the residual stream, so a token read after it must not be trusted (one small device-to-host read per call)."""
+        if self.comm is not None and self.comm.world > 1:
+            self.comm.check_healthy()
+        if K.GEMV_IMPL == "mma":
+            K.check_gemm_status(self.device)
+
+    def _read_token(self, idx: int) -> int:
+        self.last_row = idx              # the logits row this token was picked from (samplers read it)
+        tok = int(self.buf.next_ids[idx].item())
+        self.check_healthy()
+        return tok
+
     def prefill_small(self, ids: torch.Tensor) -> int:
         """Feeds a prompt through the small-batch path (MAX_ROWS rows per call); returns the greedy next token."""
         ids = ids.to(torch.int32)
@@ -389,7 +403,7 @@ class HybridModel:
             self.feed(ids[s:e], want_logits=(e == n))
             s = e
         last = (n - 1) % MAX_ROWS
-        return int(self.buf.next_ids[last].item())
+        return self._read_token(last)
 
     # ---- chunked prefill (tcgen05 GEMMs, long-chunk GDN scan, tensor-core attention) ----------------
     def _chunk_buffers(self, C: int) -> dict:
@@ -589,10 +603,11 @@ class HybridModel:
             raise ValueError("context overflow")
         self.commit_pending()
         cb = self._chunk_buffers(min(chunk, n))
+        step = min(chunk, cb["C"])         # the buffers may be larger (kept from an earlier call): the chunk size is what was asked for
         s = 0
         last_small = False
         while s < n:
-            e = min(n, s + cb["C"])
+            e = min(n, s + step)
             T = e - s
             if T <= MAX_ROWS:
                 # short tail: the small-batch path logs its rows instead of committing them
@@ -609,8 +624,8 @@ class HybridModel:
             s = e
         K.check_gemm_status(self.device)
         if last_small:
-            return int(self.buf.next_ids[(n - 1) % cb["C"]].item())
-        return int(self.buf.next_ids[0].item())
+            return self._read_token((n - 1) % step)
+        return self._read_token(0)
 
     def _prefill_with_embeds(self, ids: torch.Tensor, chunk: int, hook, overrides) -> int:
         """Prefill in which some rows' input embeddings come from outside (image tokens): ``overrides`` =
@@ -640,7 +655,7 @@ class HybridModel:
                 hook(s, T, x)
             s = e
         K.check_gemm_status(self.device)
-        return int(self.buf.next_ids[0].item())
+        return self._read_token(0)
 
     def logits_rows(self, T: int) -> torch.Tensor:
         return self.buf.logits[:T]
@@ -664,6 +679,7 @@ class HybridModel:
             self._spec_out = torch.zeros(MAX_ROWS + 2, dtype=torch.int32, device=self.device)
         K.spec_accept(b.next_ids, b.ids[1:], T, self._spec_out, None)
         res = self._spec_out[:T + 1].tolist()        # one small read-back per round
+        self.check_healthy()
         n = res[0]
         self.pending_rows = n
         self.pos += n
@@ -782,7 +798,7 @@ class HybridModel:
     def decode_step_greedy(self, token: int) -> int:
         """Eager single step (no graph): feed one token, return the greedy next token."""
         self.feed(torch.tensor([token], dtype=torch.int32))
-        return int(self.buf.next_ids[0].item())
+        return self._read_token(0)
 
     def generate_greedy(self, prompt: torch.Tensor, n: int, use_graph: bool = True) -> List[int]:
         tok = self.prefill(prompt)
@@ -797,6 +813,7 @@ class HybridModel:
                 self.decode_step_graph()
                 toks[j:j + 1].copy_(self.buf.next_ids[:1])
             out += toks.tolist()
+            self.check_healthy()
         else:
             for _ in range(n - 1):
                 tok = self.decode_step_greedy(tok)

@@ -48,6 +48,14 @@ inline int LaunchPdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
   return static_cast<int>(e);
 }
 
+// Status word of a communicator, read past the caches: non-zero means an earlier bounded wait ran out, and
+// every later wait gives up at once (the failure is sticky until the host has recovered and cleared it).
+__device__ __forceinline__ int StatusNow(const int* status) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(status) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ float WarpSum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -84,12 +84,14 @@ __global__ void EpPlanKernel(const uint2* __restrict__ meta, const unsigned* __r
     const volatile uint2* p = reinterpret_cast<const volatile uint2*>(meta + static_cast<size_t>(par) * total + g);
     int e = -1;
     bool got = false;
-    for (int i = 0; i < spin_limit; ++i) {
+    // sticky: once any wait of this communicator has run out nobody waits again until the host clears the word
+    const int limit = StatusNow(status) != 0 ? 1 : spin_limit;
+    for (int i = 0; i < limit; ++i) {
       const unsigned flag = p->y;
       if (flag == seq) { e = static_cast<int>(p->x); got = true; break; }
       if (i > 64) __nanosleep(32);
     }
-    if (!got) atomicExch(status, 200 + g / P);
+    if (!got) atomicCAS(status, 0, 200 + g / P);
     exp_of[g] = e;
   }
   __syncthreads();
@@ -126,11 +128,12 @@ __global__ void EpCombineKernel(const __nv_bfloat16* __restrict__ comb, unsigned
   if (threadIdx.x < k) {
     unsigned* c = ccount + static_cast<size_t>(par) * P + t * k + threadIdx.x;
     bool got = false;
-    for (int i = 0; i < spin_limit; ++i) {
+    const int limit = StatusNow(status) != 0 ? 1 : spin_limit;
+    for (int i = 0; i < limit; ++i) {
       if (LoadAcquireSys(c) >= static_cast<unsigned>(blocks_per_row)) { got = true; break; }
       if (i > 64) __nanosleep(32);
     }
-    if (!got) { fail = 1; atomicExch(status, 300 + t); }
+    if (!got) { fail = 1; atomicCAS(status, 0, 300 + t); }
     *c = 0;                                  // ready for the call after next
   }
   if (threadIdx.x == 0) {

@@ -14,7 +14,10 @@
 namespace r4dxb {
 namespace {
 
-__device__ __forceinline__ bool WaitCounter(const unsigned* p, unsigned target, int spin_limit) {
+// Sticky: with the status word already set (an earlier wait of this communicator ran out) one look is all a
+// wait gets, so a lost rank costs one timeout and not one per collective.
+__device__ __forceinline__ bool WaitCounter(const unsigned* p, unsigned target, int spin_limit, const int* status) {
+  if (StatusNow(status) != 0) spin_limit = 1;
   for (int i = 0; i < spin_limit; ++i) {
     unsigned v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -38,8 +41,8 @@ struct PushArgs {
 __global__ void __launch_bounds__(256) TpReducePushKernel(PushArgs a) {
   __shared__ int ok;
   if (threadIdx.x == 0) {
-    ok = WaitCounter(a.cnt, a.target, a.spin_limit) ? 1 : 0;
-    if (!ok) atomicExch(a.status, 200 + a.rank);
+    ok = WaitCounter(a.cnt, a.target, a.spin_limit, a.status) ? 1 : 0;
+    if (!ok) atomicCAS(a.status, 0, 200 + a.rank);
   }
   __syncthreads();
   const int tl = blockIdx.x;
@@ -64,7 +67,7 @@ __global__ void __launch_bounds__(256) TpReducePushKernel(PushArgs a) {
 }
 
 __global__ void TpWaitKernel(const unsigned* flag, unsigned target, int spin_limit, int code, int* status) {
-  if (threadIdx.x == 0 && !WaitCounter(flag, target, spin_limit)) atomicExch(status, code);
+  if (threadIdx.x == 0 && !WaitCounter(flag, target, spin_limit, status)) atomicCAS(status, 0, code);
 }
 
 }  // namespace

@@ -30,11 +30,7 @@ struct TpPush {
   int ep_P;
 };
 
-__device__ __forceinline__ int TpStatusNow(const int* status) {
-  int v;
-  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(status) : "memory");
-  return v;
-}
+__device__ __forceinline__ int TpStatusNow(const int* status) { return StatusNow(status); }
 
 // One warp finishes row t of a 128-column block: lane holds columns n .. n+3 of its partial in o[], call number
 // `seq` (block_seq[nb] + 1).  Pushes to every peer, then sums all ranks' partials in rank order into o[].

@@ -57,6 +57,17 @@ __device__ __forceinline__ uint32_t TrellisStateFromWindow(uint32_t hi, uint32_t
 // 8 consecutive-K code values of the lane, as 4 x half2 (k, k+1 pairs).
 template <int KB>
 __device__ __forceinline__ void TrellisDecode8(uint32_t hi, uint32_t lo, __half2 (&w)[4]) {
+  if constexpr (KB == 4) {
+    // States sit on nibble boundaries: with the window also shifted by 4, 16 and 20 bits every state is two
+    // whole bytes of some 32-bit word and one byte permute against a zero register extracts it
+    // (11 instructions for 8 states instead of 15 shifts and masks).
+    const uint32_t z = __funnelshift_r(lo, hi, 4), y = __funnelshift_r(lo, hi, 16), u = __funnelshift_r(lo, hi, 20);
+    w[3] = TrellisCode2(__byte_perm(z, 0u, 0x4410), __byte_perm(lo, 0u, 0x4410));     // shifts 4, 0
+    w[2] = TrellisCode2(__byte_perm(z, 0u, 0x4421), __byte_perm(lo, 0u, 0x4421));     // shifts 12, 8
+    w[1] = TrellisCode2(__byte_perm(u, 0u, 0x4410), __byte_perm(y, 0u, 0x4410));      // shifts 20, 16
+    w[0] = TrellisCode2(__byte_perm(u, 0u, 0x4421), __byte_perm(y, 0u, 0x4421));      // shifts 28, 24
+    return;
+  }
   w[0] = TrellisCode2(TrellisStateFromWindow<KB, 0>(hi, lo), TrellisStateFromWindow<KB, 1>(hi, lo));
   w[1] = TrellisCode2(TrellisStateFromWindow<KB, 2>(hi, lo), TrellisStateFromWindow<KB, 3>(hi, lo));
   w[2] = TrellisCode2(TrellisStateFromWindow<KB, 4>(hi, lo), TrellisStateFromWindow<KB, 5>(hi, lo));

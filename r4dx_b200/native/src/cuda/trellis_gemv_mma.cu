@@ -197,9 +197,9 @@ TrellisGemvMmaKernel(MmaArgs a, TpPush tp) {
     }
     for (int c = 0; c < kABufs; ++c) {
       ptx::MbarInit(&ctl->a_full[c], 4);
-      ptx::MbarInit(&ctl->a_empty[c], 1);
+      ptx::MbarInit(&ctl->a_empty[c], 4);         // one commit per issuing warp
     }
-    ptx::MbarInit(&ctl->d_full, 2);
+    ptx::MbarInit(&ctl->d_full, 8);
     ptx::MbarInit(&ctl->red_bar, ksplit * 4);
     ctl->abort_flag = 0;
     ptx::MbarFenceInit();
@@ -360,22 +360,23 @@ TrellisGemvMmaKernel(MmaArgs a, TpPush tp) {
       ptx::TcFenceBefore();
       __syncwarp();
       if (lane == 0) ptx::MbarArrive(&ctl->a_full[buf]);
-      if (w4 == ((it >> 1) & 3) && lane == 0 && ok) {
-        // this warp's turn: wait for the other three, then eight MMAs (one per k-tile) and the release of the buffer
+      if (lane == 0 && ok) {
+        // every warp issues the MMAs of two of the block's eight k-tiles once all four warps' rows are in: the
+        // issue cost (~50 clocks per instruction) is spread evenly instead of making one warp late for the next block
         if (ptx::MbarWait(&ctl->a_full[buf], use_par, abort_flag, 4)) {
           ptx::TcFenceAfter();
-          const uint64_t bdesc = bdesc0 + static_cast<uint64_t>((it * 16 * 128) >> 4);
+          const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(((it * 16 + w4 * 4) * 128) >> 4);
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            ptx::UmmaF16FromTmem(tbase + (wg * 4 + (i & 3)) * 8, tbase + kACol + buf * 64 + i * 8,
-                                 bdesc + static_cast<uint64_t>((i * 2 * 128) >> 4), idesc, (it >= 2 || i >= 4) ? 1u : 0u);
+          for (int i = 0; i < 2; ++i)
+            ptx::UmmaF16FromTmem(tbase + (wg * 4 + w4) * 8, tbase + kACol + buf * 64 + (w4 * 2 + i) * 8,
+                                 bdesc + static_cast<uint64_t>((i * 2 * 128) >> 4), idesc, (it >= 2 || i >= 1) ? 1u : 0u);
           ptx::UmmaCommit(&ctl->a_empty[buf]);
           if (it + 2 >= nstage) ptx::UmmaCommit(&ctl->d_full);      // this group's last block
         }
       }
       __syncwarp();
     }
-    if (wg >= nstage && warp == 4 && lane == 0) ptx::MbarArrive(&ctl->d_full);   // a one-block slice: group 1 has nothing to add
+    if (wg >= nstage && lane == 0) ptx::MbarArrive(&ctl->d_full);   // a one-block slice: group 1 has nothing to add
 
     // ---------------- accumulators -> fp32 partial rows -> cluster rank 0 ----------------
     if (ksplit > 1) asm volatile("barrier.cluster.wait.acquire;" ::: "memory");

@@ -288,7 +288,8 @@ __global__ void ArgmaxFinal(const float* __restrict__ pv, const int* __restrict_
   __syncthreads();
   if (threadIdx.x == 0) {
     for (int w = 1; w < kArgParts / 32; ++w) ArgBetter(sv[w], si[w], bv, bi);
-    out_ids[t] = bi + id_offset;
+    // a row of NaNs / -inf leaves the index unset: report the shard's first id instead of overflowing
+    out_ids[t] = (bi == 0x7fffffff ? 0 : bi) + id_offset;
     if (out_vals) out_vals[t] = bv;
   }
 }

@@ -5,8 +5,9 @@ Two data paths implement the same interface:
 * ``nccl``  -- the baseline: every row-parallel linear is a local GEMM followed by an NCCL
   all-reduce and a residual add; vocab-parallel argmax is an all-gather of (value, id) pairs.
 * ``fused`` -- the product path: the all-reduce is issued from inside the row-parallel GEMM
-  kernel over NVLink peer memory (``parallel/symm.py`` + ``native/src/cuda/tp_fused.cu``); the
-  argmax merge runs in a kernel that reads every rank's pair through peer pointers.
+  kernel over NVLink peer memory (``parallel/symm.py``, ``parallel/tp_fused.py``, the epilogue in
+  ``native/src/cuda/tp_push.cuh``); the argmax merge is a kernel that pushes every rank's pair to
+  every peer (``native/src/cuda/tp_collectives.cu``).
 
 The reference engine has one all-reduce primitive (bf16 rows, fp32 add, identical bits on every
 rank) plus host all-gathers for the vocab merges (reference: src/core/include/r4dx/core/tp_comm.hpp:58-106,
@@ -87,7 +88,8 @@ class NcclComm:
         T = ids.numel()
         pair = self._pair                              # always 8 rows: fixed-size, contiguous exchange
         pair[:T, 0] = vals
-        pair[:T, 1] = ids.to(torch.float32)            # ids < 2^24 are exact in fp32
+        pair[:T, 1] = ids.to(torch.float32)            # exact only below 2^24: every supported vocabulary is (the fused
+        #                                                communicator's kernel carries the ids as raw 32-bit patterns instead)
         dist.all_gather_into_tensor(self._pairs, pair, group=self.group)
         v, i = self._pairs[:, :T, 0], self._pairs[:, :T, 1]
         best = v.max(dim=0, keepdim=True).values
@@ -97,6 +99,14 @@ class NcclComm:
         self.stats.argmax_merges += 1
 
     def barrier(self) -> None:
+        dist.barrier(group=self.group)
+
+    def check_healthy(self) -> None:
+        """Raises if a device-side wait of this communicator ran out (the library path has none)."""
+
+    def recover(self) -> None:
+        """Bring the communicator back to a known state after a failed step (drain + host barrier here)."""
+        torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
 
     def check_lockstep(self, *ints: int) -> None:
@@ -112,11 +122,26 @@ class TpDivergenceError(RuntimeError):
     pass
 
 
-def make_comm(world: int, rank: int, device: str, mode: Optional[str] = None, hidden: int = 5120):
+def make_comm(world: int, rank: int, device: str, mode: Optional[str] = None, hidden: int = 5120,
+              spin_limit: Optional[int] = None):
+    """``mode``: fused (collectives inside the compute kernels), nccl (library collectives between kernels), noop (no
+    exchange: timing aid, wrong results).  Emulated ranks on one device come from ``tp_emulated.EmulatedWorld``."""
     mode = mode or os.environ.get("R4DXB_TP_MODE", "fused")
     if world == 1:
         return None
     if mode == "fused":
         from .tp_fused import FusedComm
-        return FusedComm(world, rank, device, n=hidden)
+        kw = {} if spin_limit is None else {"spin_limit": spin_limit}
+        return FusedComm(world, rank, device, n=hidden, **kw)
+    if mode == "noop":
+        from .tp_emulated import NoopComm
+        return NoopComm(world, rank, device)
+    if mode != "nccl":
+        raise ValueError(f"unknown tensor-parallel mode {mode!r}")
     return NcclComm(world, rank, device)
+
+
+def spin_limit_for_ms(ms: int) -> int:
+    """Poll count of a device wait that should give up after about ``ms`` milliseconds: a poll of peer-written memory
+    with its back-off sleep takes roughly 100 ns."""
+    return max(1 << 12, int(ms) * 10000)

@@ -139,6 +139,7 @@ class RankGroup:
     def _maybe_fault(self) -> None:
         f = self.fault
         if f.rank == self.rank and f.at == self.commands - 1:      # n counts commands from 0
+            self.fault = FaultSpec()                                # one shot: the count restarts after a recovery
             if f.kind == "throw":
                 raise RuntimeError("injected fault (throw before enqueue)")
             if f.kind == "stall":

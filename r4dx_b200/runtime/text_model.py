@@ -175,7 +175,7 @@ class LocalTextModel(TextModel):
         else:
             m.buf.ids[:1].fill_(token)
         m.decode_step_graph()
-        return int(m.buf.next_ids[0].item())
+        return m._read_token(0)
 
     def decode_step(self, token: int) -> torch.Tensor:
         self._graph_active = False
@@ -280,6 +280,8 @@ class FakeTextModel(TextModel):
 
     def window_logits(self, token: int, drafts: Sequence[int]) -> torch.Tensor:
         self._tick()
+        if len(self.history) + 1 + len(drafts) > self._max_ctx:     # same rule as the device model's window
+            raise ValueError("context overflow")
         keep = list(self.history)
         rows = []
         for t in [token] + list(drafts):

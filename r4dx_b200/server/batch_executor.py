@@ -14,9 +14,9 @@ import threading
 import time
 from typing import Callable, Dict, List, Optional, Protocol, Sequence
 
-from ..runtime.sampler import Rng, sample_canonical
+from ..runtime.sampler import Rng, apply_repetition_penalty, sample_canonical
 from ..runtime.tokenizer import StreamDecoder
-from .engine import GenRequest, GenResult, QueueFull, _Job
+from .engine import EngineFatal, GenRequest, GenResult, QueueFull, _Job
 from .parsers import ReasoningSplitter, detect_dialect, make_tool_call_parser
 from .request_log import RequestLog
 
@@ -92,7 +92,7 @@ class BatchEngine:
     # ---- front door (same as Engine) ----
     def submit(self, req: GenRequest, on_delta: Optional[Callable[[str, str], None]] = None) -> _Job:
         if self.fatal:
-            raise RuntimeError(self.fatal)
+            raise EngineFatal(self.fatal)
         job = _Job(req, on_delta)
         try:
             self.q.put_nowait(job)
@@ -172,19 +172,39 @@ class BatchEngine:
                     free.append(s)
                 active.clear()
                 continue
-            for s, tok in zip(order, nxt):
+            rows = getattr(self.backend, "last_logits", None)
+            for j, (s, tok) in enumerate(zip(order, nxt)):
                 a = active[s]
-                if not a.job.req.params.greedy and getattr(self.backend, "last_logits", None) is not None:
-                    row = self.backend.last_logits[order.index(s)]
-                    tok = sample_canonical(row, a.job.req.params, a.rng)
-                if self._consume(a, tok, eos):
-                    self._finish(a)
+                try:                     # one bad request fails alone; the executor and the other slots go on
+                    tok = self._pick(a, tok, None if rows is None else rows[j])
+                    done = self._consume(a, tok, eos)
+                except Exception as e:
+                    self._fail(a.job, e)
+                    done = True
+                else:
+                    if done:
+                        self._finish(a)
+                if done:
                     self.backend.release_slot(s)
                     free.append(s)
                     del active[s]
         for a in active.values():
             a.job.result.finish_reason = "cancelled"
             self._finish(a)
+
+    def _pick(self, a: "_Active", greedy_tok: int, row) -> int:
+        """The slot's next token: the backend's greedy pick, or - for a sampling request when the backend exposes the
+        logits row - one draw of the request's own generator from the penalised row (same sampler as the single-sequence
+        engine, one draw per emitted token)."""
+        p = a.job.req.params
+        if row is None or (p.greedy and p.repetition_penalty == 1.0):
+            return greedy_tok
+        lg = row.detach().to("cpu", dtype=__import__("torch").float32).contiguous().clone()
+        if p.repetition_penalty != 1.0:
+            apply_repetition_penalty(lg, list(a.job.req.prompt_ids) + list(a.job.result.token_ids), p.repetition_penalty)
+        if p.greedy:
+            return int(lg.argmax().item())
+        return sample_canonical(lg, p, a.rng.next())
 
     def _admit(self, job: _Job, slot: int, active: Dict[int, "_Active"], eos) -> None:
         req, res = job.req, job.result
@@ -198,6 +218,8 @@ class BatchEngine:
         res.prefill_ms = (time.perf_counter() - t0) * 1e3
         cfg = getattr(self.backend, "config", None)
         a = _Active(job, slot, self.tk, detect_dialect(getattr(self.backend, "model_id", ""), getattr(cfg, "arch", "")))
+        prow = getattr(self.backend, "last_prefill_logits", None)      # the row the first token is picked from, if kept
+        first = self._pick(a, first, prow)
         if self._consume(a, first, eos):
             self._finish(a)
             raise_slot_free = True

@@ -23,6 +23,10 @@ from .parsers import ReasoningSplitter, detect_dialect, make_tool_call_parser, s
 from .request_log import RequestLog
 
 
+class EngineFatal(RuntimeError):
+    """The engine can no longer serve (e.g. a tensor-parallel rank was lost and recovery failed)."""
+
+
 class QueueFull(RuntimeError):
     pass
 
@@ -92,7 +96,7 @@ class Engine:
     # ---- front door ----
     def submit(self, req: GenRequest, on_delta: Optional[Callable[[str, str], None]] = None) -> _Job:
         if self.fatal:
-            raise RuntimeError(self.fatal)
+            raise EngineFatal(self.fatal)
         job = _Job(req, on_delta)
         try:
             self.q.put_nowait(job)
@@ -123,6 +127,9 @@ class Engine:
                 job.result.finish_reason = "error"
                 self.prefix.invalidate()
                 self.stats["errors"] += 1
+                lost = getattr(self.model, "fatal", None)       # a rank group that cannot be recovered ends the service
+                if lost:
+                    self.fatal = str(lost)
             finally:
                 r = job.result
                 self.log.write(request_id=job.req.request_id, prompt_tokens=r.prompt_tokens,
@@ -221,12 +228,21 @@ class Engine:
                 break
             if not pending:
                 fed.append(tok)
-                if req.spec_k > 0 and req.params.greedy and req.params.repetition_penalty == 1.0:
-                    emitted = m.decode_step_spec_greedy(tok, req.spec_k)
+                # a speculative round stages 1 + k rows: near the end of the context or of the answer it is cut to what
+                # still fits (0: a plain step), so a request admitted up to the limit never overflows in its last rounds
+                max_ctx = getattr(m, "max_ctx", None)
+                k = req.spec_k
+                if k > 0:
+                    k = min(k, req.max_tokens - len(res.token_ids) - 1)
+                    if max_ctx is not None:
+                        k = min(k, max_ctx - len(fed) - 1)
+                    k = max(k, 0)
+                if k > 0 and req.params.greedy and req.params.repetition_penalty == 1.0:
+                    emitted = m.decode_step_spec_greedy(tok, k)
                     fed += emitted[:-1]
                     pending = list(emitted)
-                elif req.spec_k > 0:
-                    emitted = m.decode_step_spec_sampled(tok, req.spec_k, req.params, rng, fed)
+                elif k > 0:
+                    emitted = m.decode_step_spec_sampled(tok, k, req.params, rng, fed)
                     fed += emitted[:-1]
                     pending = list(emitted)
                 elif req.params.greedy and req.params.repetition_penalty == 1.0:
@@ -249,7 +265,7 @@ class Engine:
         res.decode_ms = (time.perf_counter() - t1) * 1e3
         self.stats["tokens"] += len(res.token_ids)
         # the model state reflects exactly the tokens it was fed
-        if req.images:
+        if req.images or req.audio_rows:      # rows computed from one clip's / picture's embeddings must never be reused
             self.prefix.invalidate()
         else:
             self.prefix.commit(fed[:m.position_count()], checkpoint_len=len(prompt) if self.prompt_checkpoint else None)

@@ -12,7 +12,7 @@ from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
 from typing import Dict, List, Optional
 
 from ..runtime.sampler import SampleParams
-from .engine import Engine, GenRequest, QueueFull
+from .engine import Engine, EngineFatal, GenRequest, QueueFull
 
 
 class BadRequest(ValueError):
@@ -134,6 +134,8 @@ class ApiServer:
                     return self._error(400, str(e))
                 except QueueFull:
                     return self._error(429, "the request queue is full, retry later", "rate_limit_error")
+                except EngineFatal as e:
+                    return self._json(503, {"error": {"message": f"the engine is down: {e}", "type": "tp_fatal", "code": 503}})
                 except BrokenPipeError:
                     return
                 self._error(404, "not found")

@@ -520,3 +520,86 @@ def test_ngram_drafter_through_the_local_text_model_protocol():
     spec, calls_spec = run(NgramDrafter(2, 4), 4)
     assert spec == plain
     assert calls_spec < 0.6 * calls_plain, (calls_spec, calls_plain)
+
+
+def test_batch_engine_samples_from_the_backends_logits_and_one_bad_request_fails_alone():
+    """Sampling requests on the batch path: the draw comes from the request's own generator (a float, not the generator
+    object), the first token is sampled too, the repetition penalty applies, and a slot whose handling raises is failed
+    without taking the executor thread - and so every other request - down with it."""
+    import torch
+    from r4dx_b200.runtime.sampler import Rng, SampleParams, apply_repetition_penalty, sample_canonical
+    from r4dx_b200.runtime.tokenizer import ByteTokenizer
+    from r4dx_b200.server.batch_executor import BatchEngine, FakeBatchBackend
+    from r4dx_b200.server.engine import GenRequest
+
+    class LogitBackend(FakeBatchBackend):
+        """Logits are a fixed function of the slot's history; the greedy pick is their argmax."""
+
+        def _row(self, h):
+            g = torch.Generator().manual_seed(sum((i + 1) * t for i, t in enumerate(h[-6:])) % 100003)
+            return torch.randn(self.vocab, generator=g) * 2.0
+
+        def import_slot(self, slot, ids):
+            self.hist[slot] = list(ids)
+            self.last_prefill_logits = self._row(self.hist[slot])
+            return int(self.last_prefill_logits.argmax())
+
+        def decode_batch(self, slots, tokens):
+            rows = []
+            for s, t in zip(slots, tokens):
+                if t == 199:
+                    raise_for = s          # noqa: F841  (kept for readability)
+                self.hist[s].append(t)
+                rows.append(self._row(self.hist[s]))
+            self.last_logits = torch.stack(rows)
+            return [int(r.argmax()) for r in rows]
+
+    tk = ByteTokenizer()
+    be = LogitBackend(slots=2, vocab=200)
+    eng = BatchEngine(be, tk, max_queue=4, gather_ms=1.0)
+    params = SampleParams(temperature=0.8, top_k=20, top_p=0.95, seed=1234, repetition_penalty=1.3)
+    prompt = [5, 6, 7]
+    res = eng.generate(GenRequest(prompt_ids=prompt, max_tokens=6, params=params), timeout=10)
+    assert res.error is None and len(res.token_ids) == 6
+    # replay on the host: same rows, same generator, same penalty
+    rng, h, out = Rng(1234), list(prompt), []
+    for _ in range(6):
+        row = be._row(h).clone()
+        apply_repetition_penalty(row, list(prompt) + out, 1.3)
+        tok = sample_canonical(row, params, rng.next())
+        out.append(tok)
+        h.append(tok)
+    assert res.token_ids == out
+    # a request whose token handling raises (decoder blows up) ends with an error; the next request is served
+    class Boom(Exception):
+        pass
+    orig = eng._consume
+    def consume(a, tok, eos):
+        if a.job.req.request_id == "bad":
+            raise Boom("decoder failed")
+        return orig(a, tok, eos)
+    eng._consume = consume
+    bad = eng.generate(GenRequest(prompt_ids=[1, 2], max_tokens=4, request_id="bad"), timeout=10)
+    assert bad.finish_reason == "error" and "Boom" in (bad.error or "")
+    good = eng.generate(GenRequest(prompt_ids=[3, 4], max_tokens=3), timeout=10)
+    assert good.error is None and len(good.token_ids) == 3
+    assert eng.worker.is_alive()
+    eng.shutdown()
+
+
+def test_speculation_is_cut_to_what_still_fits_when_a_request_runs_up_to_the_context_limit():
+    """prompt + max_tokens == max_ctx with speculation on: the last rounds stage fewer draft rows (none at the very end),
+    so the request finishes with every token instead of failing with a context overflow, and emits the plain stream."""
+    def run(spec_k):
+        model = FakeTextModel(vocab=64, max_ctx=3 + 20)
+        model.draft_fn = (lambda history, token, k: [7] * k) if spec_k else None
+        eng = Engine(model, ByteTokenizer(300))
+        req = GenRequest(prompt_ids=[5, 9, 11], max_tokens=20, params=SampleParams(temperature=0.9, top_k=12, seed=3),
+                         spec_k=spec_k)
+        r = eng.generate(req, timeout=20)
+        eng.shutdown()
+        return r
+
+    plain, spec = run(0), run(4)
+    assert plain.error is None and spec.error is None, (plain.error, spec.error)
+    assert len(spec.token_ids) == 20 and spec.token_ids == plain.token_ids
