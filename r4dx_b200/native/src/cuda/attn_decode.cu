@@ -21,6 +21,7 @@ namespace {
 
 constexpr int kBlockTokens = 16;
 constexpr int kTileTokens = 64;    // decode attention works on four cache blocks at a time
+bool g_decode_row = true;
 
 __device__ __forceinline__ uint8_t ToFp8(float v) {
   return static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
@@ -262,6 +263,247 @@ __global__ void __launch_bounds__(256) DecodeKernel(DecodeArgs a) {
   }
 }
 
+// ---- one query token, at most 8 query heads per KV head: the shape of every decode step ----------------------
+// Split-KV like DecodeKernel, but every warp walks its own 16-token cache blocks from global memory to registers
+// with no block-wide barrier in the loop, so the eight warps of a CTA keep eight blocks (64 KiB per SM) in flight:
+//   scores  : mma.sync m16n8k16, A = the query rows (fp16, pre-scaled, kept in registers for the whole kernel),
+//             B = K read as fp8 and widened in registers.  The k index of the MMA is a permutation of the head
+//             dimensions chosen so that a lane's B values are 16 consecutive cache bytes (one 128-bit load).
+//   softmax : per row inside a lane quad (two shuffles), log2 domain, running (m, l) per row.
+//   P V     : CUDA cores; a lane owns D / 32 output dimensions of all rows, P is handed over through a small
+//             per-warp shared-memory tile as (p, p) half pairs, fp16 FMAs per block folded into fp32 sums.
+// The warps' partials are merged through shared memory, the CTA writes one (m, l, acc) partial like DecodeKernel.
+template <int D>
+__global__ void __launch_bounds__(256, 1) DecodeRowKernel(DecodeArgs a) {
+  PdlEnter();
+  constexpr int DPL = D / 32;                   // output dimensions per lane
+  constexpr int NJ = D / 64;                    // 64-dimension groups: one 128-bit K load per lane each
+  extern __shared__ __align__(16) unsigned char smem[];
+  if (a.row_slot != nullptr) {
+    const int b = blockIdx.z;
+    a.q += static_cast<size_t>(b) * a.Hq * D;
+    a.positions += b;
+    a.block_table += static_cast<size_t>(a.row_slot[b]) * a.table_stride;
+    const size_t per = static_cast<size_t>(a.splits) * a.Hkv * (a.Hq / a.Hkv);
+    a.part_acc += b * per * D;
+    a.part_ml += b * per * 2;
+  }
+  const int G = a.Hq / a.Hkv;                   // <= 8, T == 1
+  const int split = blockIdx.x, hkv = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gid = lane >> 2, c = lane & 3;
+  __half2* P2 = reinterpret_cast<__half2*>(smem) + warp * (16 * 8 + 8);          // [16 tokens][8 rows] (p, p) + 8 alphas (as float)
+  float* alpha_s = reinterpret_cast<float*>(P2 + 16 * 8);
+  float* merge = reinterpret_cast<float*>(smem + 8 * (16 * 8 + 8) * 4);          // [4][8 rows][D + 2]
+
+  const int pos = a.positions[0];
+  const int seqlen = pos + 1;
+  const int nblocks = (seqlen + kBlockTokens - 1) / kBlockTokens;
+  const int first_tok = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+  const int first_blk = first_tok / kBlockTokens;
+  const int per = ((nblocks - first_blk) + a.splits - 1) / a.splits;
+  const int b0 = first_blk + split * per, b1 = min(nblocks, b0 + per);
+
+  // query rows as MMA A fragments: lane holds Q[gid][64 j + 16 c .. + 16) for every j (rows >= G are zero)
+  const float sm_scale = rsqrtf(static_cast<float>(D)) * a.k_descale[hkv] * 1.4426950408889634f;   // into the log2 domain
+  uint32_t qa[NJ][8];
+#pragma unroll
+  for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qa[j][i] = 0u;
+    if (gid < G) {
+      const __nv_bfloat16* qr = a.q + (static_cast<size_t>(hkv) * G + gid) * D + 64 * j + 16 * c;
+      const uint4 v0 = *reinterpret_cast<const uint4*>(qr), v1 = *reinterpret_cast<const uint4*>(qr + 8);
+      const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const __half2 h = __floats2half2_rn(BfLo(w[i]) * sm_scale, BfHi(w[i]) * sm_scale);
+        qa[j][i] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+  }
+  float m_run = -INFINITY, l_run = 0.f;          // of row gid (identical in the four lanes of a quad)
+  float acc[8][DPL];
+#pragma unroll
+  for (int g = 0; g < 8; ++g)
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) acc[g][d] = 0.f;
+
+  for (int b = b0 + warp; b < b1; b += 8) {
+    const int blk = a.block_table[b];
+    const uint8_t* kb = a.cache + (static_cast<size_t>(blk) * a.Hkv + hkv) * 2 * kBlockTokens * D;
+    const uint8_t* vb = kb + kBlockTokens * D;
+    // ---- scores of the block's 16 tokens: two 8-token MMA tiles ----
+    uint4 kraw[2][NJ];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int j = 0; j < NJ; ++j)
+        kraw[nt][j] = __ldg(reinterpret_cast<const uint4*>(kb + (8 * nt + gid) * D + 64 * j + 16 * c));
+    // V of the block: the lane's DPL bytes of each of the 16 token rows (issued now, used after the softmax)
+    uint32_t vraw[16][(DPL + 3) / 4];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+      if constexpr (DPL == 8) {
+        const uint2 v = __ldg(reinterpret_cast<const uint2*>(vb + t * D + 8 * lane));
+        vraw[t][0] = v.x; vraw[t][1] = v.y;
+      } else if constexpr (DPL == 4) {
+        vraw[t][0] = __ldg(reinterpret_cast<const uint32_t*>(vb + t * D + 4 * lane));
+      } else {
+        vraw[t][0] = __ldg(reinterpret_cast<const uint16_t*>(vb + t * D + 2 * lane));
+      }
+    }
+    float sc[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+      sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        const uint32_t kw[4] = {kraw[nt][j].x, kraw[nt][j].y, kraw[nt][j].z, kraw[nt][j].w};
+#pragma unroll
+        for (int st = 0; st < 4; ++st) {        // four k-steps of 16 (permuted) dimensions out of the 16 loaded bytes
+          const __half2 b0h = Fp8x2ToHalf2(static_cast<uint16_t>(kw[st] & 0xFFFFu));
+          const __half2 b1h = Fp8x2ToHalf2(static_cast<uint16_t>(kw[st] >> 16));
+          const uint32_t zero = 0u;
+          asm volatile(
+              "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+              : "+f"(sc[nt][0]), "+f"(sc[nt][1]), "+f"(sc[nt][2]), "+f"(sc[nt][3])
+              : "r"(qa[j][2 * st]), "r"(zero), "r"(qa[j][2 * st + 1]), "r"(zero),
+                "r"(*reinterpret_cast<const uint32_t*>(&b0h)), "r"(*reinterpret_cast<const uint32_t*>(&b1h)));
+        }
+      }
+    }
+    // ---- mask + online softmax of row gid over the 16 tokens (lane holds tokens 8 nt + 2 c, + 1) ----
+    float s4[4];
+    float mx = m_run;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int kp = b * kBlockTokens + 8 * nt + 2 * c + e;
+        const bool ok = kp <= pos && kp >= first_tok;
+        s4[nt * 2 + e] = ok ? sc[nt][e] : -INFINITY;
+        mx = fmaxf(mx, s4[nt * 2 + e]);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float alpha = (mx == -INFINITY) ? 1.f : exp2f(m_run - mx);
+    float psum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float p = (s4[i] == -INFINITY) ? 0.f : exp2f(s4[i] - mx);
+      psum += p;
+      const int tok = 8 * (i >> 1) + 2 * c + (i & 1);
+      P2[tok * 8 + gid] = __float2half2_rn(p);
+    }
+    psum += __shfl_xor_sync(0xffffffffu, psum, 1);
+    psum += __shfl_xor_sync(0xffffffffu, psum, 2);
+    l_run = l_run * alpha + psum;
+    m_run = mx;
+    if (c == 0) alpha_s[gid] = alpha;
+    __syncwarp();
+    // ---- P V: every lane, its DPL dimensions, all rows ----
+    {
+      const float4 a0 = *reinterpret_cast<const float4*>(alpha_s), a1 = *reinterpret_cast<const float4*>(alpha_s + 4);
+      const float al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      __half2 hacc[8][(DPL + 1) / 2];
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+#pragma unroll
+        for (int d = 0; d < (DPL + 1) / 2; ++d) hacc[g][d] = __float2half2_rn(0.f);
+#pragma unroll
+      for (int t = 0; t < 16; ++t) {
+        __half2 vh[(DPL + 1) / 2];
+#pragma unroll
+        for (int d = 0; d < (DPL + 1) / 2; ++d)
+          vh[d] = Fp8x2ToHalf2(static_cast<uint16_t>((vraw[t][d / 2] >> (16 * (d & 1))) & 0xFFFFu));
+        const uint4 p0 = *reinterpret_cast<const uint4*>(P2 + t * 8), p1 = *reinterpret_cast<const uint4*>(P2 + t * 8 + 4);
+        const uint32_t pw[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {
+          const __half2 pg = *reinterpret_cast<const __half2*>(&pw[g]);
+#pragma unroll
+          for (int d = 0; d < (DPL + 1) / 2; ++d) hacc[g][d] = __hfma2(pg, vh[d], hacc[g][d]);
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) {
+          const float add = (d & 1) ? __high2float(hacc[g][d / 2]) : __low2float(hacc[g][d / 2]);
+          acc[g][d] = acc[g][d] * al[g] + add;
+        }
+    }
+    __syncwarp();                                // the tile is rewritten by the next block
+  }
+
+  // ---- merge the eight warps: 4-7 into 0-3, 2-3 into 0-1, 1 into 0 (row statistics travel with the sums) ----
+  // every lane needs (m, l) of all rows: publish the quad's values per warp first
+  alpha_s[gid] = m_run;                          // all four lanes of a quad write the same value
+  __syncwarp();
+  float mrow[8], lrow[8];
+  {
+    const float4 a0 = *reinterpret_cast<const float4*>(alpha_s), a1 = *reinterpret_cast<const float4*>(alpha_s + 4);
+    mrow[0] = a0.x; mrow[1] = a0.y; mrow[2] = a0.z; mrow[3] = a0.w; mrow[4] = a1.x; mrow[5] = a1.y; mrow[6] = a1.z; mrow[7] = a1.w;
+  }
+  __syncwarp();
+  alpha_s[gid] = l_run;
+  __syncwarp();
+  {
+    const float4 a0 = *reinterpret_cast<const float4*>(alpha_s), a1 = *reinterpret_cast<const float4*>(alpha_s + 4);
+    lrow[0] = a0.x; lrow[1] = a0.y; lrow[2] = a0.z; lrow[3] = a0.w; lrow[4] = a1.x; lrow[5] = a1.y; lrow[6] = a1.z; lrow[7] = a1.w;
+  }
+  constexpr int MS = D + 2;                      // floats per row in the merge buffer: D sums, m, l
+  for (int half = 4; half >= 1; half >>= 1) {
+    __syncthreads();
+    if (warp >= half && warp < 2 * half) {
+      float* dst = merge + static_cast<size_t>(warp - half) * 8 * MS;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) dst[g * MS + DPL * lane + d] = acc[g][d];
+        if (lane == 0) { dst[g * MS + D] = mrow[g]; dst[g * MS + D + 1] = lrow[g]; }
+      }
+    }
+    __syncthreads();
+    if (warp < half) {
+      const float* src = merge + static_cast<size_t>(warp) * 8 * MS;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const float mo = src[g * MS + D], lo = src[g * MS + D + 1];
+        const float mn = fmaxf(mrow[g], mo);
+        const float wa = (mrow[g] == -INFINITY) ? 0.f : exp2f(mrow[g] - mn);
+        const float wb = (mo == -INFINITY) ? 0.f : exp2f(mo - mn);
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) acc[g][d] = acc[g][d] * wa + src[g * MS + DPL * lane + d] * wb;
+        lrow[g] = lrow[g] * wa + lo * wb;
+        mrow[g] = mn;
+      }
+    }
+  }
+  if (warp == 0) {
+    const float vds = a.v_descale[hkv];
+    const size_t base = (static_cast<size_t>(split) * a.Hkv + hkv) * G;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+      if (g < G) {
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) a.part_acc[(base + g) * D + DPL * lane + d] = acc[g][d] * vds;
+        if (lane == 0) {
+          a.part_ml[(base + g) * 2] = mrow[g];
+          a.part_ml[(base + g) * 2 + 1] = lrow[g];
+        }
+      }
+    }
+  }
+}
+
+template <int D>
+int LaunchDecodeRow(const DecodeArgs& a, cudaStream_t s, int batch) {
+  const size_t smem = 8 * (16 * 8 + 8) * 4 + static_cast<size_t>(4) * 8 * (D + 2) * 4;
+  return LaunchPdl(DecodeRowKernel<D>, dim3(a.splits, a.Hkv, batch), dim3(256), smem, s, a);
+}
+
 // grid (G, Hkv), D threads
 __global__ void CombineKernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                               const __nv_bfloat16* __restrict__ qg, __nv_bfloat16* __restrict__ out, int T, int Hq,
@@ -277,16 +519,50 @@ __global__ void CombineKernel(const float* __restrict__ part_acc, const float* _
     qg += static_cast<size_t>(b) * Hq * 2 * D;
     out += static_cast<size_t>(b) * Hq * D;
   }
-  float M = -INFINITY;
-  for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[((static_cast<size_t>(s) * Hkv + hkv) * G + g) * 2]);
-  float num = 0.f, den = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const size_t r = (static_cast<size_t>(s) * Hkv + hkv) * G + g;
-    const float m = part_ml[r * 2];
-    if (m == -INFINITY) continue;
-    const float w = exp2f(m - M);
-    num += w * part_acc[r * D + d];
-    den += w * part_ml[r * 2 + 1];
+  // The splits' row statistics first, all at once (one thread per split), then the weighted sums with the loads of
+  // four splits in flight per thread: a loop of dependent loads over 37 splits was 25 us, longer than the attention.
+  __shared__ float wsm[64], lsm[64];
+  __shared__ float red[32];
+  float M = -INFINITY, num = 0.f, den = 0.f;
+  const int cap = min(64, static_cast<int>(blockDim.x));
+  for (int s0 = 0; s0 < splits; s0 += cap) {          // up to 64 splits per round (one round in practice)
+    const int ns = min(cap, splits - s0);
+    float m = -INFINITY, l = 0.f;
+    if (static_cast<int>(threadIdx.x) < ns) {
+      const size_t r = (static_cast<size_t>(s0 + threadIdx.x) * Hkv + hkv) * G + g;
+      m = part_ml[r * 2];
+      l = part_ml[r * 2 + 1];
+    }
+    // block-wide maximum of m (blockDim.x = D >= 64 threads)
+    float mx = WarpMax(m);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) mx = fmaxf(mx, red[w]);
+    const float Mn = fmaxf(M, mx);
+    const float keep = (M == -INFINITY) ? 0.f : exp2f(M - Mn);
+    if (static_cast<int>(threadIdx.x) < ns) {
+      const float w = (m == -INFINITY) ? 0.f : exp2f(m - Mn);
+      wsm[threadIdx.x] = w;
+      lsm[threadIdx.x] = w * l;
+    }
+    __syncthreads();
+    num *= keep;
+    den *= keep;
+    M = Mn;
+    const float* pa = part_acc + ((static_cast<size_t>(s0) * Hkv + hkv) * G + g) * D + d;
+    const size_t stride = static_cast<size_t>(Hkv) * G * D;
+    int s = 0;
+    for (; s + 4 <= ns; s += 4) {
+      const float v0 = pa[(s + 0) * stride], v1 = pa[(s + 1) * stride], v2 = pa[(s + 2) * stride], v3 = pa[(s + 3) * stride];
+      num += wsm[s] * v0 + wsm[s + 1] * v1 + wsm[s + 2] * v2 + wsm[s + 3] * v3;
+      den += lsm[s] + lsm[s + 1] + lsm[s + 2] + lsm[s + 3];
+    }
+    for (; s < ns; ++s) {
+      num += wsm[s] * pa[s * stride];
+      den += lsm[s];
+    }
   }
   float o = den > 0.f ? num / den : 0.f;
   const int t = g / gqa, hq = hkv * gqa + g % gqa;
@@ -316,6 +592,9 @@ int LaunchDecode(const DecodeArgs& a, cudaStream_t s, int batch = 1) {
 using namespace r4dxb;
 
 extern "C" {
+
+/* A/B switch: 1 (default) = one-token decode steps use the warp-autonomous kernel, 0 = the tiled kernel for every shape. */
+void r4dxb_set_attn_decode_row(int on) { g_decode_row = on != 0; }
 
 int r4dxb_attn_precore(const void* qg, const void* k, const void* v, const void* q_norm, const void* k_norm,
                        const float* k_descale, const float* v_descale, const int* positions, const int* block_table,
@@ -361,7 +640,9 @@ int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const in
   a.window = flags >> 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int e;
-  if (G <= 8) e = LaunchDecode<8>(a, s);
+  if (T == 1 && G <= 8 && g_decode_row && (D == 256 || D == 128 || D == 64)) {
+    e = D == 256 ? LaunchDecodeRow<256>(a, s, 1) : (D == 128 ? LaunchDecodeRow<128>(a, s, 1) : LaunchDecodeRow<64>(a, s, 1));
+  } else if (G <= 8) e = LaunchDecode<8>(a, s);
   else if (G <= 16) e = LaunchDecode<16>(a, s);
   else if (G <= 32) e = LaunchDecode<32>(a, s);
   else if (G <= 64) e = LaunchDecode<64>(a, s);
@@ -411,7 +692,9 @@ int r4dxb_attn_decode_batch(const void* q, const void* qg, const void* cache, co
   a.window = flags >> 1;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int e;
-  if (G <= 8) e = LaunchDecode<8>(a, s, B);
+  if (G <= 8 && g_decode_row && (D == 256 || D == 128 || D == 64)) {
+    e = D == 256 ? LaunchDecodeRow<256>(a, s, B) : (D == 128 ? LaunchDecodeRow<128>(a, s, B) : LaunchDecodeRow<64>(a, s, B));
+  } else if (G <= 8) e = LaunchDecode<8>(a, s, B);
   else if (G <= 16) e = LaunchDecode<16>(a, s, B);
   else if (G <= 32) e = LaunchDecode<32>(a, s, B);
   else e = LaunchDecode<64>(a, s, B);

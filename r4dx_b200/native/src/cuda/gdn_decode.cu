@@ -72,6 +72,22 @@ __global__ void __launch_bounds__(kThreads) GdnDecodeKernel(GdnArgs a) {
   const int key_dim = a.Hk * D;
   const int nrep = min(*a.n_replay, kMaxT);
 
+  // ---- base state -> registers first: the kernel's largest load, independent of everything else, so it is in
+  // flight while the conv / gate phase runs ------------------------------------------------------
+  float S[RPW][CPL];
+  float* base = a.state + static_cast<size_t>(h) * D * D;
+#pragma unroll
+  for (int r = 0; r < RPW; ++r) {
+    const int v = warp * RPW + r;
+    if constexpr (CPL == 4) {
+      const float4 p = __ldcs(reinterpret_cast<const float4*>(base + static_cast<size_t>(v) * D + lane * 4));
+      S[r][0] = p.x; S[r][1] = p.y; S[r][2] = p.z; S[r][3] = p.w;
+    } else {
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) S[r][c] = base[static_cast<size_t>(v) * D + lane * CPL + c];
+    }
+  }
+
   // ---- stage the previous log (before anything overwrites it) --------------------------------
   for (int i = threadIdx.x; i < nrep * D; i += kThreads) {
     const int r = i / D, c = i % D;
@@ -123,20 +139,7 @@ __global__ void __launch_bounds__(kThreads) GdnDecodeKernel(GdnArgs a) {
   }
   __syncthreads();
 
-  // ---- phase B: load base state, replay the accepted log prefix, store once --------------------
-  float S[RPW][CPL];
-  float* base = a.state + static_cast<size_t>(h) * D * D;
-#pragma unroll
-  for (int r = 0; r < RPW; ++r) {
-    const int v = warp * RPW + r;
-    if constexpr (CPL == 4) {
-      const float4 p = *reinterpret_cast<const float4*>(base + static_cast<size_t>(v) * D + lane * 4);
-      S[r][0] = p.x; S[r][1] = p.y; S[r][2] = p.z; S[r][3] = p.w;
-    } else {
-#pragma unroll
-      for (int c = 0; c < CPL; ++c) S[r][c] = base[static_cast<size_t>(v) * D + lane * CPL + c];
-    }
-  }
+  // ---- phase B: replay the accepted log prefix into the base state, store once ---------------------
   if (nrep > 0) {
     for (int i = 0; i < nrep; ++i) {
       const float eg = reg[i];

@@ -57,15 +57,15 @@ __device__ __forceinline__ bool MbarTryWaitHint(uint64_t* bar, uint32_t parity, 
 }
 // Bounded wait.  `abort_flag` is a shared-memory word any role sets when it gives up; everyone who
 // sees it leaves too.  Returns false on abort / timeout (about a second of SM clocks).
-// (Measured on the weight-streaming kernel: with a plain try_wait loop a quarter of all issued instructions
-// were the polling of waiting lanes - BRA / SYNCS / ISETP - taken from the warps that had work.)
+// (A suspend-time hint on try_wait - MbarTryWaitHint - was measured too: it changed neither the weight-streaming
+// kernel nor the GEMM, so the plain form stays.)
 constexpr int kSpinLimit = 1 << 22;
 constexpr long long kWaitClocks = 2000000000ll;
 __device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
   if (MbarTestWait(bar, parity)) return true;      // the common case in a well-fed pipeline: no suspension at all
   const long long t0 = clock64();
   for (;;) {
-    if (MbarTryWaitHint(bar, parity, 20000u)) return true;
+    if (MbarTryWait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitClocks) break;
   }
