@@ -405,8 +405,27 @@ def gdn_chunk_ws_floats(T: int, H: int) -> int:
     return int(_lib().r4dxb_gdn_chunk_ws_floats(T, H))
 
 
+register_cuda_sig("r4dxb_attn_prefill_tc", _I, [_P] * 7 + [_I, _I, _I, _I, _I, _I, _P, _P])
+
+# Prefill attention kernel: "tc" = tcgen05 with S, P and O in tensor memory (head dimensions 128 / 256, default),
+# "mma" = the warp-level mma.sync kernel (every head dimension; kill switch / A-B runs).
+ATTN_PREFILL_IMPL = os.environ.get("R4DXB_ATTN_PREFILL", "tc")
+
+
+def set_attn_prefill_impl(name: str) -> None:
+    global ATTN_PREFILL_IMPL
+    if name not in ("tc", "mma"):
+        raise KernelError(f"unknown prefill attention kernel {name!r}")
+    ATTN_PREFILL_IMPL = name
+
+
 def attn_prefill(q, qg, cache, block_table, k_descale, v_descale, out, T: int, Hq: int, Hkv: int, D: int, pos0: int,
                  gated: bool = True, window: int = 0):
+    if ATTN_PREFILL_IMPL == "tc" and D in (128, 256):
+        _check(_lib().r4dxb_attn_prefill_tc(_p(q), _p(qg), _p(cache), _p(block_table), _p(k_descale), _p(v_descale), _p(out),
+                                            T, Hq, Hkv, D, pos0, (1 if gated else 0) | (window << 1),
+                                            _p(gemm_status(out.device)), _stream()), "attn_prefill_tc")
+        return out
     _check(_lib().r4dxb_attn_prefill(_p(q), _p(qg), _p(cache), _p(block_table), _p(k_descale), _p(v_descale), _p(out),
                                      T, Hq, Hkv, D, pos0, (1 if gated else 0) | (window << 1), _stream()), "attn_prefill")
     return out

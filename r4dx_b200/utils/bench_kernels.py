@@ -114,6 +114,23 @@ def main() -> None:
         us = timed(lambda: K.w4a16_gemv(w, x, out=y), a.iters, flush)
         gbs = w.nbytes / us / 1e3
         print(f"w4a16_gemv lm_head N={N} K={Kd} T={T}: {us:8.1f} us  {gbs:7.0f} GB/s  {gbs / peak:5.2f} of measured HBM")
+    if a.only in ("attn_prefill",):
+        Hq, Hkv, D = 24, 4, 256
+        Tq = max(a.rows, 128)
+        ctx = a.ctx
+        nblk = (ctx + Tq + 15) // 16 + 1
+        cache = torch.randint(0, 120, (nblk, Hkv, 2, 16, D), dtype=torch.uint8, device=dev)
+        table = torch.arange(nblk, dtype=torch.int32, device=dev)
+        q = torch.randn(Tq, Hq, D, device=dev).to(BF)
+        qg = torch.randn(Tq, Hq, 2 * D, device=dev).to(BF)
+        ds = torch.full((Hkv,), 1 / 16.0, device=dev)
+        out = torch.zeros(Tq, Hq * D, dtype=BF, device=dev)
+        flops = 4.0 * Hq * D * Tq * (ctx + (Tq + 1) / 2.0)
+        for impl in ("tc", "mma"):
+            K.set_attn_prefill_impl(impl)
+            us = timed(lambda: K.attn_prefill(q, qg, cache, table, ds, ds, out, Tq, Hq, Hkv, D, ctx, True), a.iters, flush)
+            K.check_gemm_status(dev)
+            print(f"attn_prefill[{impl}] T={Tq} ctx={ctx}: {us:9.1f} us  {flops / us / 1e6:7.1f} TFLOP/s (causal-effective)")
     if a.only in ("", "attn"):
         Hq, Hkv, D = 24, 4, 256
         ctx = a.ctx

@@ -292,6 +292,8 @@ def test_attention_precore_and_decode(K, D, Hq, Hkv, T, ctx):
     assert torch.allclose(q_out[:T].float().cpu(), qf[ctx:].to(BF).float(), atol=3e-2, rtol=2e-2)
     o = R.causal_gqa_attention(qf[ctx:].to(BF), kq, vq, ctx)
     o = o * torch.sigmoid(qg_all[ctx:, :, D:].float())
+    K.set_attn_prefill_impl("tc")
+    K.check_gemm_status("cuda")
     assert torch.allclose(out.float().cpu().view(T, Hq, D), o, atol=2e-2, rtol=3e-2)
 
 
@@ -345,8 +347,11 @@ def test_gdn_prefill_matches_recurrence_and_hands_over_to_decode(K, D, Hv, Hk, T
     assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=3e-2)
 
 
-@pytest.mark.parametrize("D,Hq,Hkv,T,ctx", [(256, 6, 1, 40, 0), (256, 12, 2, 70, 100), (64, 4, 2, 33, 17), (256, 3, 1, 20, 64)])
-def test_attention_prefill(K, D, Hq, Hkv, T, ctx):
+@pytest.mark.parametrize("impl", ["tc", "mma"])
+@pytest.mark.parametrize("D,Hq,Hkv,T,ctx", [(256, 6, 1, 40, 0), (256, 12, 2, 70, 100), (64, 4, 2, 33, 17), (256, 3, 1, 20, 64),
+                                            (256, 6, 1, 300, 0), (256, 4, 2, 257, 391), (128, 4, 1, 200, 75)])
+def test_attention_prefill(K, D, Hq, Hkv, T, ctx, impl):
+    K.set_attn_prefill_impl(impl)
     g = torch.Generator().manual_seed(ctx + T)
     dev = "cuda"
     rd, theta = D // 4, 1e7
