@@ -33,7 +33,7 @@ constexpr int kQRows = 128;
 constexpr int kKvTile = 64;
 constexpr int kPage = 16;
 constexpr int kConvGroups = 2;            // conversion groups: group g owns the key tiles of buffer g (tiles g, g + 2, ...)
-constexpr int kGroupWarps = 6;
+constexpr int kGroupWarps = 5;            // 4 + 1 + 10 = 15 warps: registers are granted per four warps, so 16 warps get 128 each
 constexpr int kConvWarps = kConvGroups * kGroupWarps;
 constexpr int kMmaWarp = 4;
 constexpr int kThreads = (4 + 1 + kConvWarps) * 32;
@@ -62,6 +62,16 @@ struct Bars {
 __device__ __forceinline__ uint32_t Fp8x2Bits(uint32_t v16) {
   __half2_raw r = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v16 & 0xFFFFu), __NV_E4M3);
   return *reinterpret_cast<uint32_t*>(&r);
+}
+// four e4m3 bytes of one word -> two half2 words (bytes 0-1, bytes 2-3), without shifts or masks
+__device__ __forceinline__ void Fp8x4ToHalf(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  asm("{ .reg .b16 l, h; mov.b32 {l, h}, %2; cvt.rn.f16x2.e4m3x2 %0, l; cvt.rn.f16x2.e4m3x2 %1, h; }"
+      : "=r"(lo), "=r"(hi) : "r"(w));
+}
+__device__ __forceinline__ float Exp2Approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 // offset of 16-byte chunk c of row r inside a [rows][128 B] tile in the K-major 128-byte-swizzled UMMA layout
 __device__ __forceinline__ int Sw128(int r, int c) { return (r >> 3) * 1024 + (r & 7) * 128 + ((c ^ (r & 7)) << 4); }
@@ -161,38 +171,61 @@ __global__ void __launch_bounds__(kThreads, 1) AttnPrefillTcKernel(TcArgs a) {
     constexpr int KTOT = kKvTile * (D / 16), VTOT = 8 * (D / 4);
     constexpr int KI = (KTOT + GT - 1) / GT;          // 16-byte K items per thread and tile
     constexpr int VI = (VTOT + GT - 1) / GT;          // V items (8 tokens x 4 dimensions) per thread and tile
+    // Item -> thread maps, fixed for the whole kernel (only the page of a token changes from tile to tile):
+    //   K item i: token i / (D/16), 16-dimension chunk i % (D/16): consecutive lanes read consecutive 16 bytes of a row.
+    //   V item i: token group tg = i % 8 (fastest), dimension quad dq = i / 8: the eight lanes of one quad write one
+    //             whole 128-byte row of the transposed tile (no bank conflict); their loads are 16-byte segments.
+    int k_src[KI], k_dst[KI], v_src[VI], v_dst[VI];
+#pragma unroll
+    for (int n = 0; n < KI; ++n) {
+      const int i = gt + n * GT;
+      const int tok = i / (D / 16), ch = i % (D / 16);
+      k_src[n] = i < KTOT ? (tok << 16) | ((tok & 15) * D + ch * 16) : -1;          // token in the high half, byte offset inside the page low
+      k_dst[n] = (ch >> 2) * (kKvTile * 128) + Sw128(tok, (ch & 3) * 2);              // the second chunk sits at dst ^ 16
+    }
+#pragma unroll
+    for (int n = 0; n < VI; ++n) {
+      const int i = gt + n * GT;
+      const int tg = i % 8, dq = i / 8;
+      v_src[n] = i < VTOT ? ((tg * 8) << 16) | (((tg * 8) & 15) * D + dq * 4) : -1;
+      v_dst[n] = (dq * 4) | (tg << 16);
+    }
+    const size_t page_bytes = static_cast<size_t>(a.Hkv) * 2 * kPage * D;
+    const uint8_t* cache_k = a.cache + static_cast<size_t>(hkv) * 2 * kPage * D;
+    const uint8_t* cache_v = cache_k + kPage * D;
     bool ok = true;
     for (int j = grp; j < ntiles; j += kConvGroups) {
       const int b = j & 1;
       const int kv0 = (tile0 + j) * kKvTile;
       const uint32_t prev = static_cast<uint32_t>((j - 2) >> 1) & 1u;      // parity of the buffer's previous use
+      const bool whole = kv0 + kKvTile <= kv_limit;                         // every token of the tile is in the cache
       uint4 kraw[KI];
       uint32_t vraw[VI][8];
 #pragma unroll
       for (int n = 0; n < KI; ++n) {
-        const int i = gt + n * GT;
-        const int tok = i / (D / 16), ch = i % (D / 16);
-        const int kp = kv0 + tok;
         kraw[n] = make_uint4(0u, 0u, 0u, 0u);
-        if (i < KTOT && kp < kv_limit) {
+        const int kp = kv0 + (k_src[n] >> 16);
+        if (k_src[n] >= 0 && (whole || kp < kv_limit)) {
           const int page = a.block_table[kp >> 4];
-          kraw[n] = __ldg(reinterpret_cast<const uint4*>(a.cache + ((static_cast<size_t>(page) * a.Hkv + hkv) * 2) * kPage * D +
-                                                         (kp & 15) * D + ch * 16));
+          kraw[n] = __ldg(reinterpret_cast<const uint4*>(cache_k + page * page_bytes + (k_src[n] & 0xFFFF)));
         }
       }
 #pragma unroll
       for (int n = 0; n < VI; ++n) {
-        const int i = gt + n * GT;
-        const int tg = i / (D / 4), dq = i % (D / 4);
-        const int kp = kv0 + tg * 8;
-        if (i < VTOT && kp < kv_limit) {
+        const int kp = kv0 + (v_src[n] >> 16);
+#pragma unroll
+        for (int tt = 0; tt < 8; ++tt) vraw[n][tt] = 0u;
+        if (v_src[n] >= 0 && (whole || kp < kv_limit)) {
           const int page = a.block_table[kp >> 4];
-          const uint8_t* vrow = a.cache + ((static_cast<size_t>(page) * a.Hkv + hkv) * 2 + 1) * kPage * D + (kp & 15) * D + dq * 4;
+          const uint8_t* vrow = cache_v + page * page_bytes + (v_src[n] & 0xFFFF);
+          if (whole) {
 #pragma unroll
-          for (int tt = 0; tt < 8; ++tt) vraw[n][tt] = (kp + tt < kv_limit) ? __ldg(reinterpret_cast<const uint32_t*>(vrow + tt * D)) : 0u;
-        } else {
+            for (int tt = 0; tt < 8; ++tt) vraw[n][tt] = __ldg(reinterpret_cast<const uint32_t*>(vrow + tt * D));
+          } else {
 #pragma unroll
-          for (int tt = 0; tt < 8; ++tt) vraw[n][tt] = 0u;
+            for (int tt = 0; tt < 8; ++tt)
+              if (kp + tt < kv_limit) vraw[n][tt] = __ldg(reinterpret_cast<const uint32_t*>(vrow + tt * D));
+          }
         }
       }
       // ---- K tile: [64 tokens][D] fp8 -> fp16, K-major ----
@@ -201,15 +234,14 @@ __global__ void __launch_bounds__(kThreads, 1) AttnPrefillTcKernel(TcArgs a) {
         unsigned char* kt = Ks + b * kKBytes;
 #pragma unroll
         for (int n = 0; n < KI; ++n) {
-          const int i = gt + n * GT;
-          if (i >= KTOT) break;
-          const int tok = i / (D / 16), ch = i % (D / 16);
-          const uint4 raw = kraw[n];
-          const uint4 lo = make_uint4(Fp8x2Bits(raw.x), Fp8x2Bits(raw.x >> 16), Fp8x2Bits(raw.y), Fp8x2Bits(raw.y >> 16));
-          const uint4 hi = make_uint4(Fp8x2Bits(raw.z), Fp8x2Bits(raw.z >> 16), Fp8x2Bits(raw.w), Fp8x2Bits(raw.w >> 16));
-          unsigned char* slab = kt + (ch >> 2) * (kKvTile * 128);
-          *reinterpret_cast<uint4*>(slab + Sw128(tok, (ch & 3) * 2)) = lo;
-          *reinterpret_cast<uint4*>(slab + Sw128(tok, (ch & 3) * 2 + 1)) = hi;
+          if (k_src[n] < 0) continue;
+          uint4 lo, hi;
+          Fp8x4ToHalf(kraw[n].x, lo.x, lo.y);
+          Fp8x4ToHalf(kraw[n].y, lo.z, lo.w);
+          Fp8x4ToHalf(kraw[n].z, hi.x, hi.y);
+          Fp8x4ToHalf(kraw[n].w, hi.z, hi.w);
+          *reinterpret_cast<uint4*>(kt + k_dst[n]) = lo;
+          *reinterpret_cast<uint4*>(kt + (k_dst[n] ^ 16)) = hi;
         }
       }
       ptx::FenceProxyAsyncShared();
@@ -221,15 +253,14 @@ __global__ void __launch_bounds__(kThreads, 1) AttnPrefillTcKernel(TcArgs a) {
         unsigned char* vt = Vs + b * kVBytes;
 #pragma unroll
         for (int n = 0; n < VI; ++n) {
-          const int i = gt + n * GT;
-          if (i >= VTOT) break;
-          const int tg = i / (D / 4), dq = i % (D / 4);
+          if (v_src[n] < 0) continue;
+          const int d0 = v_dst[n] & 0xFFFF, tg = v_dst[n] >> 16;
 #pragma unroll
           for (int dd = 0; dd < 4; ++dd) {
             const uint32_t sel = static_cast<uint32_t>(dd) | (static_cast<uint32_t>(4 + dd) << 4);   // byte dd of both words
             const uint4 o = make_uint4(Fp8x2Bits(__byte_perm(vraw[n][0], vraw[n][1], sel)), Fp8x2Bits(__byte_perm(vraw[n][2], vraw[n][3], sel)),
                                        Fp8x2Bits(__byte_perm(vraw[n][4], vraw[n][5], sel)), Fp8x2Bits(__byte_perm(vraw[n][6], vraw[n][7], sel)));
-            *reinterpret_cast<uint4*>(vt + Sw128(dq * 4 + dd, tg)) = o;
+            *reinterpret_cast<uint4*>(vt + Sw128(d0 + dd, tg)) = o;
           }
         }
       }
@@ -343,14 +374,14 @@ __global__ void __launch_bounds__(kThreads, 1) AttnPrefillTcKernel(TcArgs a) {
       const float mref = (m_used == -INFINITY) ? 0.f : m_used;
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
-        const float e0 = exp2f(__uint_as_float(s0[2 * c]) - mref), e1 = exp2f(__uint_as_float(s0[2 * c + 1]) - mref);
+        const float e0 = Exp2Approx(__uint_as_float(s0[2 * c]) - mref), e1 = Exp2Approx(__uint_as_float(s0[2 * c + 1]) - mref);
         sum += e0 + e1;
         const __half2 h = __floats2half2_rn(e0, e1);
         p[c] = *reinterpret_cast<const uint32_t*>(&h);
       }
 #pragma unroll
       for (int c = 0; c < 16; ++c) {
-        const float e0 = exp2f(__uint_as_float(s1[2 * c]) - mref), e1 = exp2f(__uint_as_float(s1[2 * c + 1]) - mref);
+        const float e0 = Exp2Approx(__uint_as_float(s1[2 * c]) - mref), e1 = Exp2Approx(__uint_as_float(s1[2 * c + 1]) - mref);
         sum += e0 + e1;
         const __half2 h = __floats2half2_rn(e0, e1);
         p[16 + c] = *reinterpret_cast<const uint32_t*>(&h);
