@@ -86,16 +86,6 @@ class BatchModel:
                                     share_from=b.moe.get(i)) for i in range(cfg.num_hidden_layers)}
         self._L = None
 
-    def _dense_head(self) -> torch.Tensor:
-        if getattr(self, "_head_bf16", None) is None:
-            from ..quant import w4a16
-            w = self.base.lin["lm_head"].w
-            if isinstance(w, torch.Tensor):
-                self._head_bf16 = w.to(BF)
-            else:
-                self._head_bf16 = w4a16.dequantize(w).to(self.device, BF)
-        return self._head_bf16
-
     # ---- slot lifecycle -------------------------------------------------------------------------------
     def _bind(self, slot: int) -> None:
         b = self.base
@@ -216,8 +206,8 @@ class BatchModel:
         K.rmsnorm(x, w["text.final_norm"], cfg.rms_norm_eps, out=h)
         V = cfg.vocab_shard_size
         if B > MAX_ROWS:
-            # many rows: the head is a plain dense product (library GEMM) over a bf16 copy of its weights
-            logits = torch.matmul(h, self._dense_head().t()).float()
+            # many rows: the head runs on the tensor cores straight from its packed weights
+            logits = b.lin["lm_head"].many(h[:B], out_f32=True)
         else:
             logits = torch.empty(B, V, dtype=torch.float32, device=dev)
             b.lin["lm_head"](h, out=logits)

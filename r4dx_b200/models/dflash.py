@@ -222,12 +222,13 @@ class DflashDrafter:
         self.valid_from, self.frontier = 0, 0
 
     def _lin(self, name: str, x: torch.Tensor) -> torch.Tensor:
-        """w4a16 product in groups of 8 rows (the weight-streaming kernel's row limit)."""
+        """w4a16 product: the weight-streaming kernel up to 8 rows, the tensor-core kernel above."""
         w = self.w[name]
         T = x.shape[0]
+        if T > 8:
+            return K.linear_tc(w, x)
         out = torch.empty(T, w.N, dtype=BF, device=x.device)
-        for s in range(0, T, 8):
-            K.w4a16_gemv(w, x[s:s + 8].contiguous(), out_f32=False, out=out[s:s + 8])
+        K.w4a16_gemv(w, x.contiguous(), out_f32=False, out=out)
         return out
 
     def _norm_rope(self, x: torch.Tensor, w: torch.Tensor, pos: torch.Tensor, heads: int) -> None:
@@ -237,7 +238,7 @@ class DflashDrafter:
         assert rc == 0, rc
 
     def _conv(self, h: torch.Tensor, name: str) -> torch.Tensor:
-        dyn = F.linear(h, self.w[name + ".dyn"])          # [T, 2G]: a 2G-row product, plain library GEMM
+        dyn = K.linear_tc(self.w[name + ".dyn"], h)       # [T, 2G]
         out = torch.empty_like(h)
         rc = self._L.r4dxb_dflash_conv(h.data_ptr(), self.w[name + ".base"].data_ptr(), dyn.data_ptr(), out.data_ptr(),
                                        h.shape[0], h.shape[1], torch.cuda.current_stream().cuda_stream)
@@ -317,7 +318,7 @@ class DflashDrafter:
         c = self.c
         logits, xo = self.draft_rows(anchor)
         vals, ids, _ = K.topk_lse(logits, 64)
-        gate = F.linear(xo, self.w["selector_hidden"]).float()
+        gate = K.linear_tc(self.w["selector_hidden"], xo, out_f32=True)
         packed = torch.cat([vals[:, :c.cands].reshape(-1), ids[:, :c.cands].reshape(-1).float(), gate.reshape(-1)]).cpu()   # one copy
         nb = c.block * c.cands
         unary, cand, g = packed[:nb].view(c.block, c.cands), packed[nb:2 * nb].view(c.block, c.cands).to(torch.int32), packed[2 * nb:].view(c.block, -1)

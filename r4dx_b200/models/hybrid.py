@@ -54,6 +54,16 @@ class Linear:
             return K.w4a16_gemv(w, x, out_f32=(out.dtype == torch.float32), out=out)
         raise NotImplementedError(f"layout of {self.name}")
 
+    def many(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+             out_f32: bool = False) -> torch.Tensor:
+        """Any number of rows of a w4a16 or dense weight on the tensor cores (no input transform in these layouts)."""
+        w = self.w
+        if isinstance(w, TrellisWeight):
+            raise NotImplementedError(f"{self.name}: trellis weights take chunk() for many rows")
+        if out is not None:
+            out_f32 = out.dtype == torch.float32
+        return K.linear_tc(w, x, residual=residual, out=out, out_f32=out_f32)
+
     def chunk(self, x: torch.Tensor, xh_buf: torch.Tensor, out: torch.Tensor, residual: Optional[torch.Tensor] = None,
               fused_silu_mul: bool = False, gelu: bool = False) -> torch.Tensor:
         """Large-T path: input transform (optionally fused with SwiGLU) + tcgen05 GEMM."""

@@ -203,26 +203,26 @@ class VisionTower:
         st = torch.cuda.current_stream().cuda_stream
         pos_hw = pos_hw.to(dev, torch.int32).contiguous()
         cu_d = cu.to(dev, torch.int32).contiguous()
-        x = F.linear(patches.to(dev, BF), w["patch_embed.weight"], w["patch_embed.bias"])
+        x = K.linear_tc(w["patch_embed.weight"], patches.to(dev, BF), bias=w["patch_embed.bias"])
         pe = (w["pos_embed"][idx.to(dev)].float() * wts.to(dev)[..., None]).sum(1)
         x = (x.float() + pe).to(BF)
         for i in range(cfg.depth):
             p = f"blocks.{i}."
             h = K.layernorm(x, w[p + "norm1.weight"], w[p + "norm1.bias"], cfg.layer_norm_eps)
-            qkv = F.linear(h, w[p + "qkv.weight"], w[p + "qkv.bias"]).contiguous()
+            qkv = K.linear_tc(w[p + "qkv.weight"], h, bias=w[p + "qkv.bias"])
             rc = L.r4dxb_vit_rope(qkv.data_ptr(), pos_hw.data_ptr(), T, Hn, D, cfg.rope_theta, st)
             assert rc == 0, rc
             o = torch.empty(T, H, dtype=BF, device=dev)
             rc = L.r4dxb_vit_attention(qkv.data_ptr(), o.data_ptr(), cu_d.data_ptr(), cu_d.numel() - 1, T, Hn, D, st)
             assert rc == 0, rc
-            x = K.residual_add(x, F.linear(o, w[p + "proj.weight"], w[p + "proj.bias"]))
+            x = K.linear_tc(w[p + "proj.weight"], o, bias=w[p + "proj.bias"], residual=x)
             h = K.layernorm(x, w[p + "norm2.weight"], w[p + "norm2.bias"], cfg.layer_norm_eps)
-            h = K.bias_act(F.linear(h, w[p + "fc1.weight"]), w[p + "fc1.bias"], act=1)
-            x = K.residual_add(x, F.linear(h, w[p + "fc2.weight"], w[p + "fc2.bias"]))
+            h = K.linear_tc(w[p + "fc1.weight"], h, bias=w[p + "fc1.bias"], act=1)
+            x = K.linear_tc(w[p + "fc2.weight"], h, bias=w[p + "fc2.bias"], residual=x)
         m = cfg.spatial_merge_size ** 2
         h = K.layernorm(x, w["merger.norm.weight"], w["merger.norm.bias"], cfg.layer_norm_eps).view(T // m, m * H)
-        h = K.bias_act(F.linear(h, w["merger.fc1.weight"]), w["merger.fc1.bias"], act=2)
-        return F.linear(h, w["merger.fc2.weight"], w["merger.fc2.bias"])
+        h = K.linear_tc(w["merger.fc1.weight"], h.contiguous(), bias=w["merger.fc1.bias"], act=2)
+        return K.linear_tc(w["merger.fc2.weight"], h, bias=w["merger.fc2.bias"])
 
     def encode_images(self, images: List[torch.Tensor]) -> torch.Tensor:
         """uint8 [H, W, 3] images -> bf16 embeddings [sum tokens, out_hidden] ready to replace image placeholders."""

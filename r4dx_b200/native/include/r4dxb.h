@@ -108,6 +108,13 @@ int r4dxb_tp_wait(const void* flag, unsigned target, int spin_limit, int code, i
 int r4dxb_trellis_gemm(const void* w, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
                        int kb, int tn, int* status, void* stream);
 
+/* Plain linear on the same tensor-core kernel, any T: y[T,N] = x[T,K] W^T (+ bias[N] bf16) (+ residual[T,N] bf16).
+ * kind 0: dense 16-bit W[N,K] (bf16 != 0: W and x bf16, else fp16); kind 1: w4a16 (w = nibbles [N][K/8] u32,
+ * wsz = [N][K/group] fp16 scale | fp16 -(1024 + zero) << 16; x fp16; N, K multiples of 128).  Dense: N % 4 == 0,
+ * K % 8 == 0.  out_f32 bit 0: y fp32; bits 8-15: activation after the bias (0 none, 1 tanh-GELU, 2 erf-GELU). */
+int r4dxb_linear_tc(const void* w, const void* wsz, int kind, int group, int bf16, const void* x, void* y, int out_f32,
+                    const void* bias, const void* residual, int T, int N, int K, int tn, int* status, void* stream);
+
 /* ---- batched decode (B sequences, one new token each; per-sequence state indexed by slot) ---------- */
 int r4dxb_gdn_decode_batch(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
                            const float* dt_bias, const void* norm_w, void* ring, float* state, float* log_u, float* log_k,

@@ -40,7 +40,7 @@ struct GemmSmem {
   static constexpr int kWordsSlot = ((kWordsBytes + 1023) / 1024) * 1024;
   static constexpr int kXTileBytes = TN * kSlabK * 2;
   static constexpr int WST = 6;
-  static constexpr int AST = 3;
+  static constexpr int AST = KB == 0 ? 4 : 3;
   static constexpr int XST = TN >= 512 ? 2 : (TN >= 256 ? 3 : 4);
   static constexpr int kABytes = AST * kATileBytes;
   static constexpr int kXBytes = XST * kXTileBytes;
@@ -63,11 +63,31 @@ struct RsArgs {
   int world, rank, rows_per_rank;
 };
 
-template <int KB, int TN, int DW>
+// Plain linear modes of the same kernel (MODE 1: dense 16-bit A matrix, MODE 2: w4a16 group-quantised A): y = x W^T
+// (+ bias) (+ residual) with no Hadamard epilogue; activations and a dense A may be bf16 instead of fp16, the result
+// may be written as fp32 (vocabulary logits).  These are the tensor-core paths of the heads and of the dense towers for
+// more than 8 rows (reference: third_party/libr4d/r4d_gemm_w4a16_nt_m64.hip:173 is the WMMA counterpart for w4a16).
+__device__ __forceinline__ float GeluTanh(float v) {
+  return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+}
+__device__ __forceinline__ float GeluErf(float v) { return 0.5f * v * (1.0f + erff(v * 0.7071067811865476f)); }
+
+struct PlainArgs {
+  const uint32_t* wsz;         // MODE 2: [N][K / group] (fp16 scale | fp16 -(1024 + zero) << 16)
+  const __nv_bfloat16* bias;   // [N] or null
+  int group;                   // MODE 2: quantisation group (32, 64 or 128)
+  int bf16;                    // the 16-bit operands are bf16 (MODE 1 only)
+  int out_f32;                 // y is fp32 [T, N] instead of bf16
+  int act;                     // after the bias: 0 none, 1 tanh-GELU, 2 erf-GELU
+};
+
+template <int KB, int TN, int DW, int MODE = 0>
 __global__ void __launch_bounds__((DW + 3) * 32, 1)
-TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __restrict__ wsrc,
+TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_a,
+                  const void* __restrict__ wsrc,
                   const __half* __restrict__ svh, __nv_bfloat16* __restrict__ y,
-                  const __nv_bfloat16* __restrict__ residual, int T, int N, int K, int* __restrict__ status, RsArgs rs) {
+                  const __nv_bfloat16* __restrict__ residual, int T, int N, int K, int* __restrict__ status, RsArgs rs,
+                  PlainArgs pl) {
   using S = GemmSmem<KB, TN>;
   constexpr int WST = S::WST, AST = S::AST, XST = S::XST;
   extern __shared__ unsigned char smem_dyn[];
@@ -90,7 +110,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nb = blockIdx.x;                 // 128-row weight block
   const int t0 = blockIdx.y * TN;            // first token of the tile
-  const int slabs = K / kSlabK;
+  const int slabs = (K + kSlabK - 1) / kSlabK;   // a ragged last slab only in the dense plain mode (TMA zero-fills X)
   constexpr uint32_t kTmemCols = TN < 32 ? 32 : TN;
   constexpr int kHalves = TN > 256 ? TN / 256 : 1;     // one MMA covers at most 256 token columns
   constexpr int kMmaN = TN > 256 ? 256 : TN;
@@ -101,7 +121,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
       ptx::MbarInit(&wempty[s], DW);
     }
     for (int s = 0; s < AST; ++s) {
-      ptx::MbarInit(&afull[s], DW);
+      ptx::MbarInit(&afull[s], MODE == 1 ? 1 : DW);
       ptx::MbarInit(&aempty[s], 1);
     }
     for (int s = 0; s < XST; ++s) {
@@ -136,6 +156,16 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
     }
   } else if (warp == DW + 2) {
     // ---------------- producer W: packed words, prefetched WST slabs deep ----------------
+    if (MODE == 1 && lane == 0) {
+      // dense plain mode: the weight tile comes by TMA as well (rows and columns past the matrix read as zero)
+      ptx::PrefetchTensorMap(&tmap_a);
+      for (int it = 0; it < slabs; ++it) {
+        const int s = it % AST, round = it / AST;
+        if (!ptx::MbarWait(&aempty[s], (round & 1) ^ 1, abort_flag, 5)) break;
+        ptx::MbarArriveExpectTx(&afull[s], kATileBytes);
+        ptx::TmaLoad2D(a_ring + s * kATileBytes, &tmap_a, &afull[s], it * kSlabK, nb * 128);
+      }
+    }
     if (KB != 0 && lane == 0) {
       const size_t slab_words = 4 * 8 * 8 * (KB == 0 ? 1 : KB);
       const uint32_t* wbase = static_cast<const uint32_t*>(wsrc) + static_cast<size_t>(nb) * (K / 16) * 8 * 8 * (KB == 0 ? 1 : KB);
@@ -149,7 +179,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
   } else if (warp == DW + 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::UmmaInstrDescF16(128, kMmaN, false);
+      const uint32_t idesc = ptx::UmmaInstrDescF16(128, kMmaN, MODE == 1 && pl.bf16 != 0);
       bool ok = true;
       for (int it = 0; it < slabs && ok; ++it) {
         const int sa = it % AST, ra = it / AST, sx = it % XST, rx = it / XST;
@@ -179,12 +209,41 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
     TrellisLane<(KB == 0 ? 4 : KB)> tl;
     tl.Init(2 * row_in_tile + khalf);
     bool ok = true;
-    for (int it = 0; it < slabs && ok; ++it) {
+    for (int it = 0; MODE != 1 && it < slabs && ok; ++it) {
       const int sa = it % AST, ra = it / AST, sw = it % WST, rw = it / WST;
       if (KB != 0) ok = ptx::MbarWait(&wfull[sw], rw & 1, abort_flag, 4);
       ok = ok && ptx::MbarWait(&aempty[sa], (ra & 1) ^ 1, abort_flag, 5);
       if (!ok) break;
       unsigned char* at = a_ring + sa * kATileBytes;
+      if constexpr (MODE == 2) {
+        // w4a16: a lane widens 32 consecutive k of one row (16 bytes of nibbles): nibble -> fp16 1024 + n by or-ing
+        // 0x6400, the stored -(1024 + zero) makes n - zero exact, one fp16 multiply by the group scale
+        for (int idx = warp; idx < 8; idx += DW) {
+          const int r = idx * 16 + (lane >> 1), half = lane & 1;
+          const size_t n = static_cast<size_t>(nb) * 128 + r;
+          const int kbase = it * kSlabK + half * 32;
+          const uint4 q = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint32_t*>(wsrc) + n * (K / 8) + kbase / 8));
+          const uint32_t sz = __ldg(pl.wsz + n * (K / pl.group) + kbase / pl.group);
+          const uint32_t scb = (sz & 0xFFFFu) | (sz << 16), nzb = (sz >> 16) | (sz & 0xFFFF0000u);
+          const __half2 sc2 = *reinterpret_cast<const __half2*>(&scb), nz2 = *reinterpret_cast<const __half2*>(&nzb);
+          const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int wi = 0; wi < 4; ++wi) {
+            uint32_t hb[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t b = ((qw[wi] >> (4 * i)) & 0x000F000Fu) | 0x64006400u;       // (k + i, k + i + 4)
+              const __half2 v = __hmul2(__hadd2(*reinterpret_cast<const __half2*>(&b), nz2), sc2);
+              hb[i] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            uint4 packed;
+            packed.x = __byte_perm(hb[0], hb[1], 0x5410); packed.y = __byte_perm(hb[2], hb[3], 0x5410);
+            packed.z = __byte_perm(hb[0], hb[1], 0x7632); packed.w = __byte_perm(hb[2], hb[3], 0x7632);
+            const int chunk = half * 4 + wi;
+            *reinterpret_cast<uint4*>(at + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4)) = packed;
+          }
+        }
+      } else {
 #pragma unroll
       for (int idx = warp; idx < 32; idx += DW) {
         const int j = idx & 7;                             // n-tile inside the 128-row block
@@ -204,11 +263,15 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
           packed.w = *reinterpret_cast<uint32_t*>(&w[3]);
         } else {
           const __half* dense = static_cast<const __half*>(wsrc);
-          packed = __ldg(reinterpret_cast<const uint4*>(dense + (static_cast<size_t>(nb) * 128 + r) * K + it * kSlabK +
-                                                        kt * 16 + khalf * 8));
+          const int n = nb * 128 + r, k = it * kSlabK + kt * 16 + khalf * 8;
+          if (MODE == 0 || (n < N && k < K))
+            packed = __ldg(reinterpret_cast<const uint4*>(dense + static_cast<size_t>(n) * K + k));
+          else
+            packed = make_uint4(0u, 0u, 0u, 0u);
         }
         const int chunk = kt * 2 + khalf;                  // 16-byte chunk inside the 128-byte row
         *reinterpret_cast<uint4*>(at + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4)) = packed;
+      }
       }
       ptx::FenceProxyAsyncShared();          // generic-proxy stores -> visible to the tensor core (async proxy)
       __syncwarp();
@@ -247,15 +310,29 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
       if (ok) {
         for (int c = q; c < CW; c += 4) {
           const int t = t0 + c0 + c;
-          if (t < T) {
+          if (t < T && (MODE != 1 || nb * 128 + lane * 4 < N)) {
             const float4 p = *reinterpret_cast<const float4*>(epi + c * S::kEpiStride + lane * 4);
             float f[4] = {p.x, p.y, p.z, p.w};
-            WarpFwht128(f);
             const int n = nb * 128 + lane * 4;
-            const uint2 sv = *reinterpret_cast<const uint2*>(svh + n);
-            const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
-            float o0 = f[0] * inv_sqrt * __low2float(s01), o1 = f[1] * inv_sqrt * __high2float(s01);
-            float o2 = f[2] * inv_sqrt * __low2float(s23), o3 = f[3] * inv_sqrt * __high2float(s23);
+            float o0, o1, o2, o3;
+            if constexpr (MODE == 0) {
+              WarpFwht128(f);
+              const uint2 sv = *reinterpret_cast<const uint2*>(svh + n);
+              const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
+              o0 = f[0] * inv_sqrt * __low2float(s01); o1 = f[1] * inv_sqrt * __high2float(s01);
+              o2 = f[2] * inv_sqrt * __low2float(s23); o3 = f[3] * inv_sqrt * __high2float(s23);
+            } else {
+              o0 = f[0]; o1 = f[1]; o2 = f[2]; o3 = f[3];
+              if (pl.bias != nullptr) {
+                const uint2 bv = *reinterpret_cast<const uint2*>(pl.bias + n);
+                o0 += BfLo(bv.x); o1 += BfHi(bv.x); o2 += BfLo(bv.y); o3 += BfHi(bv.y);
+              }
+              if (pl.act == 1) {
+                o0 = GeluTanh(o0); o1 = GeluTanh(o1); o2 = GeluTanh(o2); o3 = GeluTanh(o3);
+              } else if (pl.act == 2) {
+                o0 = GeluErf(o0); o1 = GeluErf(o1); o2 = GeluErf(o2); o3 = GeluErf(o3);
+              }
+            }
             if (residual != nullptr) {
               const uint2 rv = *reinterpret_cast<const uint2*>(residual + static_cast<size_t>(t) * N + n);
               o0 += BfLo(rv.x); o1 += BfHi(rv.x); o2 += BfLo(rv.y); o3 += BfHi(rv.y);
@@ -263,7 +340,9 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const void* __rest
             uint2 ov;
             ov.x = PackBf16(o0, o1);
             ov.y = PackBf16(o2, o3);
-            if (rs.world > 0) {
+            if (MODE != 0 && pl.out_f32) {
+              *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + static_cast<size_t>(t) * N + n) = make_float4(o0, o1, o2, o3);
+            } else if (rs.world > 0) {
               const int owner = t / rs.rows_per_rank, tl = t - owner * rs.rows_per_rank;
               *reinterpret_cast<uint2*>(rs.recv[owner] + (static_cast<size_t>(rs.rank) * rs.rows_per_rank + tl) * N + n) = ov;
             } else {
@@ -337,23 +416,44 @@ __global__ void TrellisInputKernel(const __nv_bfloat16* __restrict__ in, const _
 
 int g_decode_warps = 16;
 
-template <int KB, int TN, int DW>
+template <int KB, int TN, int DW, int MODE = 0>
 int LaunchGemm(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
-               int* status, cudaStream_t stream, const RsArgs& rs) {
+               int* status, cudaStream_t stream, const RsArgs& rs, const PlainArgs& pl = PlainArgs{}) {
   using S = GemmSmem<KB, TN>;
   static_assert(S::kTotal <= 227 * 1024, "shared memory budget");
   static_assert(S::kBars * 8 + 16 <= 512, "barrier block");
   CUtensorMap tmap;
-  const int rc = MakeTensorMap2D16(&tmap, xh, static_cast<uint64_t>(T), static_cast<uint64_t>(K), TN > 256 ? 256 : TN, kSlabK, false);
+  const int rc = MakeTensorMap2D16(&tmap, xh, static_cast<uint64_t>(T), static_cast<uint64_t>(K), TN > 256 ? 256 : TN, kSlabK,
+                                   MODE == 1 && pl.bf16 != 0);
   if (rc) return rc;
-  auto kern = TrellisGemmKernel<KB, TN, DW>;
+  CUtensorMap tmap_a = tmap;
+  if (MODE == 1) {
+    const int ra = MakeTensorMap2D16(&tmap_a, wsrc, static_cast<uint64_t>(N), static_cast<uint64_t>(K), 128, kSlabK, pl.bf16 != 0);
+    if (ra) return ra;
+  }
+  auto kern = TrellisGemmKernel<KB, TN, DW, MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 grid(N / 128, (T + TN - 1) / TN);
-  kern<<<grid, (DW + 3) * 32, S::kTotal, stream>>>(tmap, wsrc, static_cast<const __half*>(svh),
+  dim3 grid((N + 127) / 128, (T + TN - 1) / TN);
+  kern<<<grid, (DW + 3) * 32, S::kTotal, stream>>>(tmap, tmap_a, wsrc, static_cast<const __half*>(svh),
                                                    static_cast<__nv_bfloat16*>(y),
-                                                   static_cast<const __nv_bfloat16*>(residual), T, N, K, status, rs);
+                                                   static_cast<const __nv_bfloat16*>(residual), T, N, K, status, rs, pl);
   return FinishLaunch();
+}
+
+template <int MODE>
+int LaunchPlain(const void* w, const void* xh, void* y, const void* residual, int T, int N, int K, int tn, int* status,
+                cudaStream_t s, const PlainArgs& pl) {
+  const RsArgs rs = {};
+  switch (tn) {
+    case 16: return LaunchGemm<0, 16, 8, MODE>(w, nullptr, xh, y, residual, T, N, K, status, s, rs, pl);
+    case 32: return LaunchGemm<0, 32, 8, MODE>(w, nullptr, xh, y, residual, T, N, K, status, s, rs, pl);
+    case 64: return LaunchGemm<0, 64, 8, MODE>(w, nullptr, xh, y, residual, T, N, K, status, s, rs, pl);
+    case 128: return LaunchGemm<0, 128, 8, MODE>(w, nullptr, xh, y, residual, T, N, K, status, s, rs, pl);
+    case 256: return LaunchGemm<0, 256, 8, MODE>(w, nullptr, xh, y, residual, T, N, K, status, s, rs, pl);
+    case 512: return LaunchGemm<0, 512, 8, MODE>(w, nullptr, xh, y, residual, T, N, K, status, s, rs, pl);
+    default: return R4DXB_BAD_ARG;
+  }
 }
 
 template <int KB, int DW>
@@ -416,6 +516,28 @@ int r4dxb_trellis_gemm(const void* w, const void* svh, const void* xh, void* y, 
     case 5: return LaunchGemmDW<5>(w, svh, xh, y, residual, T, N, K, tn, status, s, rs);
     default: return R4DXB_BAD_ARG;
   }
+}
+
+/* Plain linear on the tensor cores, any number of rows: y[T, N] = x[T, K] W^T (+ bias) (+ residual).
+ * kind 0: W is a dense 16-bit [N, K] matrix (bf16 != 0: W and x are bf16, else fp16), N a multiple of 4 and K of 8;
+ * kind 1: W is w4a16 (wq nibbles [N][K/8] + wsz [N][K/group]), x is fp16, N and K multiples of 128.
+ * out_f32: y is fp32 instead of bf16.  act (low byte of out_f32 >> 8): 0 none, 1 tanh-GELU, 2 erf-GELU after the bias. */
+int r4dxb_linear_tc(const void* w, const void* wsz, int kind, int group, int bf16, const void* x, void* y, int out_f32,
+                    const void* bias, const void* residual, int T, int N, int K, int tn, int* status, void* stream) {
+  if (T < 1 || N < 4 || K < 8 || kind < 0 || kind > 1) return R4DXB_BAD_ARG;
+  if (kind == 0 && (N % 4 || K % 8)) return R4DXB_BAD_ARG;
+  if (kind == 1 && (N % 128 || K % 128 || wsz == nullptr || (group != 32 && group != 64 && group != 128) || bf16))
+    return R4DXB_BAD_ARG;
+  PlainArgs pl = {};
+  pl.wsz = static_cast<const uint32_t*>(wsz);
+  pl.bias = static_cast<const __nv_bfloat16*>(bias);
+  pl.group = group;
+  pl.bf16 = bf16;
+  pl.out_f32 = out_f32 & 1;
+  pl.act = (out_f32 >> 8) & 0xFF;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return kind == 0 ? LaunchPlain<1>(w, x, y, residual, T, N, K, tn, status, s, pl)
+                   : LaunchPlain<2>(w, x, y, residual, T, N, K, tn, status, s, pl);
 }
 
 /* Row-parallel product with the reduce-scatter in its epilogue: partial row t goes to rank t / rows_per_rank, into

@@ -362,6 +362,46 @@ def dense_gemm_hadamard(W: torch.Tensor, svh: torch.Tensor, xh: torch.Tensor, tn
     return out
 
 
+register_cuda_sig("r4dxb_linear_tc", _I, [_P, _P, _I, _I, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P])
+
+
+def linear_tc(W, x: torch.Tensor, bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+              out_f32: bool = False, out: Optional[torch.Tensor] = None, tn: Optional[int] = None,
+              act: int = 0) -> torch.Tensor:
+    """y[T, N] = act(x W^T + bias) + residual on the tcgen05 kernel for any number of rows.
+
+    ``W``: a dense bf16 / fp16 [N, K] matrix (x must have the same dtype; N % 4 == 0, K % 8 == 0) or a ``W4Weight``
+    (x bf16 or fp16; bf16 rows are narrowed to fp16 first: the group scales already make the weights fp16; N and K
+    multiples of 128).  ``act``: 0 none, 1 tanh-GELU, 2 erf-GELU.
+    """
+    dev = x.device
+    if isinstance(W, W4Weight):
+        N, K_ = W.N, W.K
+        xk = x if x.dtype == torch.float16 else x.to(torch.float16)
+        kind, group, is_bf, wp, szp = 1, W.group, 0, W.wq, W.wsz
+    else:
+        N, K_ = W.shape
+        if W.dtype not in (BF, torch.float16) or x.dtype != W.dtype:
+            raise KernelError("linear_tc: W and x must both be bf16 or both fp16")
+        xk, kind, group, is_bf, wp, szp = x, 0, 0, int(W.dtype == BF), W, None
+    if (kind == 1 and (N % 128 or K_ % 128)) or N % 4 or K_ % 8:
+        raise KernelError(f"linear_tc: unsupported shape N={N}, K={K_}")
+    xk = xk.reshape(-1, K_)
+    if not xk.is_contiguous():
+        xk = xk.contiguous()
+    T = xk.shape[0]
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.float32 if out_f32 else BF, device=dev)
+    if bias is not None:
+        _req(bias, BF, "bias")
+    if residual is not None:
+        _req(residual, BF, "residual")
+    tn = tn or pick_token_tile(T, N)
+    _check(_lib().r4dxb_linear_tc(_p(wp), _p(szp), kind, group, is_bf, _p(xk), _p(out), (1 if out_f32 else 0) | (act << 8),
+                                  _p(bias), _p(residual), T, N, K_, tn, _p(gemm_status(dev)), _stream()), "linear_tc")
+    return out
+
+
 register_cuda_sig("r4dxb_gdn_prefill", _I, [_P] * 16 + [_I, _I, _I, _I, _I, _F, _P, _P])
 register_cuda_sig("r4dxb_gdn_chunk_ws_floats", ctypes.c_longlong, [_I, _I])
 register_cuda_sig("r4dxb_attn_prefill", _I, [_P] * 7 + [_I, _I, _I, _I, _I, _I, _P])

@@ -126,6 +126,45 @@ def test_w4a16_gemv_and_argmax(K, T):
     assert torch.equal(ids.cpu().long(), y.cpu().argmax(-1) + 7)
 
 
+@pytest.mark.parametrize("T,N,Kd,group", [(16, 256, 512, 64), (40, 1024, 1024, 32), (300, 512, 2048, 128), (1100, 384, 640, 64)])
+def test_linear_tc_w4a16_matches_fp32_reference(K, T, N, Kd, group):
+    """The tensor-core w4a16 product against x @ dequant(W)^T in fp32, with bias, residual and an fp32 output."""
+    from r4dx_b200.quant import w4a16
+    g = torch.Generator().manual_seed(T + N)
+    W = torch.randn(N, Kd, generator=g) * 0.03
+    q = w4a16.quantize(W, group)
+    Wd = w4a16.dequantize(q)
+    x = torch.randn(T, Kd, generator=g).to(BF)
+    ref = x.half().float() @ Wd.T
+    y = K.linear_tc(q.to("cuda"), x.cuda(), out_f32=True)
+    K.check_gemm_status(y.device)
+    assert torch.allclose(y.cpu(), ref, atol=2e-2, rtol=1e-2)
+    bias = torch.randn(N, generator=g).to(BF)
+    res = torch.randn(T, N, generator=g).to(BF)
+    y2 = K.linear_tc(q.to("cuda"), x.cuda(), bias=bias.cuda(), residual=res.cuda())
+    K.check_gemm_status(y2.device)
+    assert y2.dtype == BF
+    assert torch.allclose(y2.float().cpu(), ref + bias.float() + res.float(), atol=6e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,N,Kd", [(24, 256, 384), (520, 1152, 1152), (2050, 128, 4352), (70, 4304, 1152), (33, 1152, 4304), (9, 20, 72)])
+def test_linear_tc_dense_matches_fp32_reference(K, dtype, T, N, Kd):
+    g = torch.Generator().manual_seed(N + Kd)
+    W = (torch.randn(N, Kd, generator=g) * 0.05).to(dtype)
+    x = torch.randn(T, Kd, generator=g).to(dtype)
+    bias = torch.randn(N, generator=g).to(BF)
+    ref = x.float() @ W.float().T + bias.float()
+    y = K.linear_tc(W.cuda(), x.cuda(), bias=bias.cuda(), out_f32=True)
+    K.check_gemm_status(y.device)
+    assert torch.allclose(y.cpu(), ref, atol=3e-2, rtol=1e-2)
+    yb = K.linear_tc(W.cuda(), x.cuda(), bias=bias.cuda())
+    assert torch.allclose(yb.float().cpu(), ref, atol=8e-2, rtol=2e-2)
+    for act, fn in ((1, lambda v: torch.nn.functional.gelu(v, approximate="tanh")), (2, torch.nn.functional.gelu)):
+        ya = K.linear_tc(W.cuda(), x.cuda(), bias=bias.cuda(), act=act, out_f32=True)
+        assert torch.allclose(ya.cpu(), fn(ref), atol=3e-2, rtol=1e-2)
+
+
 def test_argmax_ties_take_lowest_id(K):
     lg = torch.zeros(2, 5000, device="cuda")
     lg[0, 4000] = 1.0
