@@ -22,6 +22,7 @@ from ..ops import kernels as K
 from ..quant.trellis import TrellisWeight
 
 BF = torch.bfloat16
+GROUPED_MIN_ROWS = int(os.environ.get("R4DXB_MOE_GROUPED_MIN_ROWS", "16"))   # above: the grouped tensor-core path
 
 
 @dataclass
@@ -51,7 +52,7 @@ class MoeBlock:
     """One layer's routed + shared experts.  ``e_begin/e_count``: the expert slice this rank holds."""
 
     def __init__(self, cfg: ModelConfig, weights: Dict[str, object], layer: int, device, max_rows: int, e_begin: int = 0,
-                 e_count: Optional[int] = None, tmax: int = 2, share_from: Optional["MoeBlock"] = None, cap: int = 16):
+                 e_count: Optional[int] = None, tmax: int = 2, share_from: Optional["MoeBlock"] = None):
         self.cfg = cfg
         p = f"text.layers.{layer}.moe."
         self.e_begin = e_begin
@@ -61,7 +62,6 @@ class MoeBlock:
         else:
             self.gate_up = ExpertStack.from_list([weights[p + f"experts.{e}.gate_up"] for e in range(e_begin, e_begin + self.e_count)])
             self.down = ExpertStack.from_list([weights[p + f"experts.{e}.down"] for e in range(e_begin, e_begin + self.e_count)])
-        self.cap = cap                   # rows one expert can take per call when more than `cap` rows are in flight
         self.router = weights[p + "router"]
         self.has_shared = cfg.shared_expert_intermediate_size > 0
         self.shared_gate = weights[p + "shared_gate"] if self.has_shared else None
@@ -83,6 +83,12 @@ class MoeBlock:
         self.sh_gu = z(R, 2 * cfg.shared_expert_intermediate_size) if self.has_shared else None
         self.sh_out = z(R, H) if self.has_shared else None
         self.sh_gate = z(R, 1, dtype=torch.float32) if self.has_shared else None
+        # many rows: the grouped tensor-core path; rows of the pairs in expert order, and the plan's token tiles
+        self.max_rows = R
+        if R > GROUPED_MIN_ROWS:
+            self.xh_pairs = z(R * k, max(H, I), dtype=torch.float16)
+            self.tiles = z(2 * (R * k // 16 + self.e_count + 1), dtype=torch.int32)
+            self.ntiles = z(1, dtype=torch.int32)
         self.ks_gu = K.pick_ksplit(self.gate_up.N, self.gate_up.K, target_ctas=1)
         self.ks_dn = K.pick_ksplit(self.down.N, self.down.K, target_ctas=1)
         # one or two rows in flight touch at most k experts each: k * N/128 CTAs leave most of the 148 SMs idle (4 experts of
@@ -103,17 +109,38 @@ class MoeBlock:
 
     def experts(self, h: torch.Tensor, T: int, max_rows: Optional[int] = None) -> None:
         """y_pairs[pair] = down_e(silu(gate_e h) * up_e h) for every pair routed to a local expert.
-        ``max_rows``: the largest per-expert row count of the current plan when the caller knows it (prefill chunks read
-        it back once per layer); otherwise at most ``cap`` rows per expert are served."""
-        # few rows in flight: 2-row passes (an expert rarely sees more than one); many: 8-row passes
-        tmax = self.tmax if T <= 4 else 8
-        n_pass = ((max_rows if max_rows is not None else min(T, self.cap)) + tmax - 1) // tmax
+        ``max_rows``: the largest per-expert row count of the current plan when the caller knows it."""
         g, d = self.gate_up, self.down
+        if T > GROUPED_MIN_ROWS:
+            return self._experts_grouped(h, T)
+        # few rows in flight: 2-row passes (an expert rarely sees more than one); more: 8-row passes.  An expert can
+        # receive every row of the call, so the passes cover T rows unless the caller knows the plan's maximum.
+        tmax = self.tmax if T <= 4 else 8
+        n_pass = ((max_rows if max_rows is not None else T) + tmax - 1) // tmax
         ks_gu, ks_dn = (self.ks_gu_few, self.ks_dn_few) if T <= 2 else (self.ks_gu, self.ks_dn)
         K.trellis_gemv_grouped(g.words, g.suh, g.svh, h, self.gu_pairs, self.offsets, self.perm, self.k, n_pass, tmax,
                                K.PRO_NONE, g.E, g.N, g.K, g.kb, ks_gu)
         K.trellis_gemv_grouped(d.words, d.suh, d.svh, self.gu_pairs, self.y_pairs, self.offsets, self.perm, 1, n_pass, tmax,
                                K.PRO_SILU_MUL, d.E, d.N, d.K, d.kb, ks_dn)
+
+    def _experts_grouped(self, h: torch.Tensor, T: int) -> None:
+        """More rows than the weight-streaming passes serve well: every expert's rows in one tensor-core launch per
+        projection.  The pairs are transformed in expert order (each expert has its own input signs), a token tile is
+        one expert's next ``tn`` rows, and the results land at their pair index.  No row count is read back and no
+        expert's rows are capped."""
+        g, d = self.gate_up, self.down
+        P = T * self.k
+        avg = max(1, P // max(1, min(self.e_count, self.cfg.num_experts)))
+        tn = 16 if avg <= 12 else (32 if avg <= 24 else (64 if avg <= 48 else 128))
+        K.moe_tiles(self.offsets, self.e_count, tn, self.tiles, self.ntiles)
+        xh = self.xh_pairs.view(-1)[:P * g.K].view(P, g.K)
+        K.trellis_input_grouped(h, g.suh, xh, self.offsets, self.perm, P, self.k, 0)
+        K.trellis_gemm_grouped(g.words, g.svh, xh, self.gu_pairs, self.offsets, self.perm, self.tiles, self.ntiles, P, g.E,
+                               g.N, g.K, g.kb, tn)
+        xh2 = self.xh_pairs.view(-1)[:P * d.K].view(P, d.K)
+        K.trellis_input_grouped(self.gu_pairs, d.suh, xh2, self.offsets, self.perm, P, 1, 1)
+        K.trellis_gemm_grouped(d.words, d.svh, xh2, self.y_pairs, self.offsets, self.perm, self.tiles, self.ntiles, P, d.E,
+                               d.N, d.K, d.kb, tn)
 
     def shared(self, h: torch.Tensor, T: int) -> None:
         if not self.has_shared:
@@ -134,16 +161,16 @@ class MoeBlock:
 
     def forward(self, h: torch.Tensor, x: torch.Tensor, T: int, exact_rows: bool = False, residual: bool = True) -> None:
         """x[T, H] += moe(h) (h = post-attention RMSNorm of x).  ``exact_rows``: read the plan's largest per-expert row
-        count back (one small copy) and run exactly as many passes as it needs - the prefill path, where one expert
-        can receive hundreds of rows."""
+        count back (one small copy) and run exactly as many weight-streaming passes as it needs; calls with more than
+        ``GROUPED_MIN_ROWS`` rows take the grouped tensor-core path and read nothing back."""
         self.route(h, T)
-        self.experts(h, T, self.max_rows_of_an_expert() if exact_rows else None)
+        self.experts(h, T, self.max_rows_of_an_expert() if exact_rows and T <= GROUPED_MIN_ROWS else None)
         self.shared(h, T)
         K.moe_combine(self.y_pairs, self.ids, self.wts, self.sh_out, self.sh_gate, x if residual else None, x, T,
                       self.cfg.hidden_size, self.k)
 
     def max_rows_of_an_expert(self) -> int:
-        """Largest per-expert row count of the latest plan (one device read; for overflow checks of ``cap``)."""
+        """Largest per-expert row count of the latest plan (one device read)."""
         o = self.offsets.cpu()
         return int((o[1:] - o[:-1]).max().item())
 

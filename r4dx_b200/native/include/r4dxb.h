@@ -115,6 +115,17 @@ int r4dxb_trellis_gemm(const void* w, const void* svh, const void* xh, void* y, 
 int r4dxb_linear_tc(const void* w, const void* wsz, int kind, int group, int bf16, const void* x, void* y, int out_f32,
                     const void* bias, const void* residual, int T, int N, int K, int tn, int* status, void* stream);
 
+/* Grouped experts on the tensor cores: tile list of a routing plan (E <= 1024 local experts, tiles [2 * max_tiles]),
+ * per-expert input transform of the planned pairs in expert order (xdiv: pairs per input row; mode as
+ * r4dxb_trellis_input), and y[perm[p]] = svh[e] * H128(xh[p] Q_e^T) with one expert's next tn rows per token tile
+ * (tn 16/32/64/128, max_tiles >= P / tn + E). */
+int r4dxb_moe_tiles(const int* offsets, int E, int tn, int* tiles, int* ntiles, int max_tiles, void* stream);
+int r4dxb_trellis_input_grouped(const void* in, const void* suh, void* out, const int* offsets, const int* perm, int E, int P,
+                                int K, int xdiv, int mode, void* stream);
+int r4dxb_trellis_gemm_grouped(const void* words, const void* svh, const void* xh, void* y, const int* offsets, const int* perm,
+                               const int* tiles, const int* ntiles, int max_tiles, int P, int E, int N, int K, int kb, int tn,
+                               int* status, void* stream);
+
 /* ---- batched decode (B sequences, one new token each; per-sequence state indexed by slot) ---------- */
 int r4dxb_gdn_decode_batch(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
                            const float* dt_bias, const void* norm_w, void* ring, float* state, float* log_u, float* log_k,

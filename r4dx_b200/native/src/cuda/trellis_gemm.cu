@@ -79,6 +79,14 @@ struct PlainArgs {
   int bf16;                    // the 16-bit operands are bf16 (MODE 1 only)
   int out_f32;                 // y is fp32 [T, N] instead of bf16
   int act;                     // after the bias: 0 none, 1 tanh-GELU, 2 erf-GELU
+  // MODE 3, grouped experts: the rows of xh are the (row, expert) pairs sorted by expert; a token tile is one expert's
+  // next TN rows.  offsets [E + 1] and perm [pairs] come from the routing plan, tiles/ntiles from MoeTilesKernel.
+  const int* g_offsets;
+  const int* g_perm;           // sorted position -> pair id = output row
+  const int* g_tiles;          // [2 * max_tiles]: (local expert, first sorted row)
+  const int* g_ntiles;
+  long long g_words;           // packed words per expert
+  int g_max_tiles;             // grid height: an upper bound on the tile count
 };
 
 template <int KB, int TN, int DW, int MODE = 0>
@@ -109,7 +117,16 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nb = blockIdx.x;                 // 128-row weight block
-  const int t0 = blockIdx.y * TN;            // first token of the tile
+  int t0 = blockIdx.y * TN;                  // first token of the tile
+  int t_end = T;                             // rows at and past t_end are not stored
+  if constexpr (MODE == 3) {
+    if (static_cast<int>(blockIdx.y) >= __ldg(pl.g_ntiles)) return;       // the whole CTA, before any barrier exists
+    const int e = __ldg(pl.g_tiles + 2 * blockIdx.y);
+    t0 = __ldg(pl.g_tiles + 2 * blockIdx.y + 1);
+    t_end = __ldg(pl.g_offsets + e + 1);
+    wsrc = static_cast<const uint32_t*>(wsrc) + static_cast<long long>(e) * pl.g_words;
+    svh += static_cast<size_t>(e) * N;
+  }
   const int slabs = (K + kSlabK - 1) / kSlabK;   // a ragged last slab only in the dense plain mode (TMA zero-fills X)
   constexpr uint32_t kTmemCols = TN < 32 ? 32 : TN;
   constexpr int kHalves = TN > 256 ? TN / 256 : 1;     // one MMA covers at most 256 token columns
@@ -310,12 +327,12 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       if (ok) {
         for (int c = q; c < CW; c += 4) {
           const int t = t0 + c0 + c;
-          if (t < T && (MODE != 1 || nb * 128 + lane * 4 < N)) {
+          if (t < t_end && (MODE != 1 || nb * 128 + lane * 4 < N)) {
             const float4 p = *reinterpret_cast<const float4*>(epi + c * S::kEpiStride + lane * 4);
             float f[4] = {p.x, p.y, p.z, p.w};
             const int n = nb * 128 + lane * 4;
             float o0, o1, o2, o3;
-            if constexpr (MODE == 0) {
+            if constexpr (MODE == 0 || MODE == 3) {
               WarpFwht128(f);
               const uint2 sv = *reinterpret_cast<const uint2*>(svh + n);
               const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
@@ -340,11 +357,13 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             uint2 ov;
             ov.x = PackBf16(o0, o1);
             ov.y = PackBf16(o2, o3);
-            if (MODE != 0 && pl.out_f32) {
+            if ((MODE == 1 || MODE == 2) && pl.out_f32) {
               *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + static_cast<size_t>(t) * N + n) = make_float4(o0, o1, o2, o3);
             } else if (rs.world > 0) {
               const int owner = t / rs.rows_per_rank, tl = t - owner * rs.rows_per_rank;
               *reinterpret_cast<uint2*>(rs.recv[owner] + (static_cast<size_t>(rs.rank) * rs.rows_per_rank + tl) * N + n) = ov;
+            } else if (MODE == 3) {
+              *reinterpret_cast<uint2*>(y + static_cast<size_t>(__ldg(pl.g_perm + t)) * N + n) = ov;
             } else {
               *reinterpret_cast<uint2*>(y + static_cast<size_t>(t) * N + n) = ov;
             }
@@ -414,6 +433,75 @@ __global__ void TrellisInputKernel(const __nv_bfloat16* __restrict__ in, const _
   *reinterpret_cast<uint2*>(out + static_cast<size_t>(t) * K + k) = ov;
 }
 
+// ---- grouped experts: tile list and per-expert input transform ---------------------------------------
+// One block.  Expert e with n_e planned rows gets ceil(n_e / tn) tiles; tiles are written in expert order.
+__global__ void MoeTilesKernel(const int* __restrict__ offsets, int E, int tn, int* __restrict__ tiles,
+                               int* __restrict__ ntiles, int max_tiles) {
+  __shared__ int scan[1024];
+  const int e = threadIdx.x;
+  const int n = e < E ? offsets[e + 1] - offsets[e] : 0;
+  const int c = (n + tn - 1) / tn;
+  scan[e] = c;
+  __syncthreads();
+  for (int d = 1; d < 1024; d <<= 1) {
+    const int v = e >= d ? scan[e - d] : 0;
+    __syncthreads();
+    scan[e] += v;
+    __syncthreads();
+  }
+  const int base = scan[e] - c;
+  if (e < E) {
+    const int o = offsets[e];
+    for (int j = 0; j < c && base + j < max_tiles; ++j) {
+      tiles[2 * (base + j)] = e;
+      tiles[2 * (base + j) + 1] = o + j * tn;
+    }
+  }
+  if (e == 1023) *ntiles = min(scan[1023], max_tiles);
+}
+
+// xh[p] = fp16(H128(suh[e(p)] * act(in[perm[p] / xdiv]))) for every planned pair p (sorted by expert); one warp per
+// 128-block.  The expert of a sorted position is found by bisection of the offsets.
+__global__ void TrellisInputGroupedKernel(const __nv_bfloat16* __restrict__ in, const __half* __restrict__ suh,
+                                          __half* __restrict__ out, const int* __restrict__ offsets,
+                                          const int* __restrict__ perm, int E, int P, int K, int xdiv, int mode) {
+  const int lane = threadIdx.x & 31;
+  const int blocks_per_row = K / 128;
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= static_cast<long long>(P) * blocks_per_row) return;
+  const int p = static_cast<int>(item / blocks_per_row), b = static_cast<int>(item % blocks_per_row);
+  if (p >= __ldg(offsets + E)) return;
+  int lo = 0, hi = E;                                  // largest e with offsets[e] <= p
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(offsets + mid) <= p) lo = mid; else hi = mid;
+  }
+  const int t = __ldg(perm + p) / xdiv;
+  const int k = b * 128 + lane * 4;
+  float v[4];
+  if (mode == 0) {
+    const uint2 xv = *reinterpret_cast<const uint2*>(in + static_cast<size_t>(t) * K + k);
+    v[0] = BfLo(xv.x); v[1] = BfHi(xv.x); v[2] = BfLo(xv.y); v[3] = BfHi(xv.y);
+  } else {
+    const uint2 g = *reinterpret_cast<const uint2*>(in + static_cast<size_t>(t) * 2 * K + k);
+    const uint2 u = *reinterpret_cast<const uint2*>(in + static_cast<size_t>(t) * 2 * K + K + k);
+    const int act = mode == 2 ? 1 : 0;
+    const uint32_t p01 = PackBf16(GateAct(BfLo(g.x), act) * BfLo(u.x), GateAct(BfHi(g.x), act) * BfHi(u.x));
+    const uint32_t p23 = PackBf16(GateAct(BfLo(g.y), act) * BfLo(u.y), GateAct(BfHi(g.y), act) * BfHi(u.y));
+    v[0] = BfLo(p01); v[1] = BfHi(p01); v[2] = BfLo(p23); v[3] = BfHi(p23);
+  }
+  const uint2 sv = *reinterpret_cast<const uint2*>(suh + static_cast<size_t>(lo) * K + k);
+  const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
+  v[0] *= __low2float(s01); v[1] *= __high2float(s01); v[2] *= __low2float(s23); v[3] *= __high2float(s23);
+  WarpFwht128(v);
+  const float inv_sqrt = 0.08838834764831845f;
+  __half2 o01 = __floats2half2_rn(v[0] * inv_sqrt, v[1] * inv_sqrt), o23 = __floats2half2_rn(v[2] * inv_sqrt, v[3] * inv_sqrt);
+  uint2 ov;
+  ov.x = *reinterpret_cast<uint32_t*>(&o01);
+  ov.y = *reinterpret_cast<uint32_t*>(&o23);
+  *reinterpret_cast<uint2*>(out + static_cast<size_t>(p) * K + k) = ov;
+}
+
 int g_decode_warps = 16;
 
 template <int KB, int TN, int DW, int MODE = 0>
@@ -434,11 +522,24 @@ int LaunchGemm(const void* wsrc, const void* svh, const void* xh, void* y, const
   auto kern = TrellisGemmKernel<KB, TN, DW, MODE>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
   if (e != cudaSuccess) return static_cast<int>(e);
-  dim3 grid((N + 127) / 128, (T + TN - 1) / TN);
+  dim3 grid((N + 127) / 128, MODE == 3 ? pl.g_max_tiles : (T + TN - 1) / TN);
   kern<<<grid, (DW + 3) * 32, S::kTotal, stream>>>(tmap, tmap_a, wsrc, static_cast<const __half*>(svh),
                                                    static_cast<__nv_bfloat16*>(y),
                                                    static_cast<const __nv_bfloat16*>(residual), T, N, K, status, rs, pl);
   return FinishLaunch();
+}
+
+template <int KB>
+int LaunchGrouped(const void* w, const void* svh, const void* xh, void* y, int P, int N, int K, int tn, int* status,
+                  cudaStream_t s, const PlainArgs& pl) {
+  const RsArgs rs = {};
+  switch (tn) {
+    case 16: return LaunchGemm<KB, 16, 8, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
+    case 32: return LaunchGemm<KB, 32, 8, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
+    case 64: return LaunchGemm<KB, 64, 8, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
+    case 128: return LaunchGemm<KB, 128, 8, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
+    default: return R4DXB_BAD_ARG;
+  }
 }
 
 template <int MODE>
@@ -538,6 +639,46 @@ int r4dxb_linear_tc(const void* w, const void* wsz, int kind, int group, int bf1
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return kind == 0 ? LaunchPlain<1>(w, x, y, residual, T, N, K, tn, status, s, pl)
                    : LaunchPlain<2>(w, x, y, residual, T, N, K, tn, status, s, pl);
+}
+
+/* Grouped experts on the tensor cores (prefill and wide batches of the mixture-of-experts block).
+ * r4dxb_moe_tiles: tile list of the routing plan for token tiles of tn rows (E <= 1024 local experts).
+ * r4dxb_trellis_input_grouped: xh[p] = fp16(H128(suh[e(p)] * act(in[perm[p] / xdiv]))) for the planned pairs in expert order.
+ * r4dxb_trellis_gemm_grouped: y[perm[p]] = svh[e] * H128(xh[p] Q_e^T); max_tiles >= P / tn + E bounds the grid. */
+int r4dxb_moe_tiles(const int* offsets, int E, int tn, int* tiles, int* ntiles, int max_tiles, void* stream) {
+  if (E < 1 || E > 1024 || tn < 1 || max_tiles < 1) return R4DXB_BAD_ARG;
+  MoeTilesKernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(offsets, E, tn, tiles, ntiles, max_tiles);
+  return FinishLaunch();
+}
+
+int r4dxb_trellis_input_grouped(const void* in, const void* suh, void* out, const int* offsets, const int* perm, int E, int P,
+                                int K, int xdiv, int mode, void* stream) {
+  if (P < 1 || K % 128 || xdiv < 1 || mode < 0 || mode > 2) return R4DXB_BAD_ARG;
+  const long long items = static_cast<long long>(P) * (K / 128);
+  TrellisInputGroupedKernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(in), static_cast<const __half*>(suh), static_cast<__half*>(out), offsets, perm, E, P, K,
+      xdiv, mode);
+  return FinishLaunch();
+}
+
+int r4dxb_trellis_gemm_grouped(const void* words, const void* svh, const void* xh, void* y, const int* offsets, const int* perm,
+                               const int* tiles, const int* ntiles, int max_tiles, int P, int E, int N, int K, int kb, int tn,
+                               int* status, void* stream) {
+  if (P < 1 || E < 1 || N % 128 || K % 128 || max_tiles < 1 || max_tiles > 65535) return R4DXB_BAD_ARG;
+  PlainArgs pl = {};
+  pl.g_offsets = offsets;
+  pl.g_perm = perm;
+  pl.g_tiles = tiles;
+  pl.g_ntiles = ntiles;
+  pl.g_words = static_cast<long long>(N / 16) * (K / 16) * 8 * kb;
+  pl.g_max_tiles = max_tiles;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (kb) {
+    case 3: return LaunchGrouped<3>(words, svh, xh, y, P, N, K, tn, status, s, pl);
+    case 4: return LaunchGrouped<4>(words, svh, xh, y, P, N, K, tn, status, s, pl);
+    case 5: return LaunchGrouped<5>(words, svh, xh, y, P, N, K, tn, status, s, pl);
+    default: return R4DXB_BAD_ARG;
+  }
 }
 
 /* Row-parallel product with the reduce-scatter in its epilogue: partial row t goes to rank t / rows_per_rank, into

@@ -533,6 +533,33 @@ def trellis_gemv_grouped(words, suh, svh, x, y, offsets, perm, in_div: int, n_pa
     return y
 
 
+register_cuda_sig("r4dxb_moe_tiles", _I, [_P, _I, _I, _P, _P, _I, _P])
+register_cuda_sig("r4dxb_trellis_input_grouped", _I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_trellis_gemm_grouped", _I, [_P] * 8 + [_I] * 7 + [_P, _P])
+
+
+def moe_tiles(offsets: torch.Tensor, E: int, tn: int, tiles: torch.Tensor, ntiles: torch.Tensor):
+    """Token tiles of a routing plan: (local expert, first sorted row) pairs, ``tn`` rows of one expert each."""
+    _check(_lib().r4dxb_moe_tiles(_p(offsets), E, tn, _p(tiles), _p(ntiles), tiles.numel() // 2, _stream()), "moe_tiles")
+
+
+def trellis_input_grouped(x: torch.Tensor, suh: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, perm: torch.Tensor,
+                          P: int, xdiv: int, mode: int = 0):
+    """out[p] = fp16 H128(suh[e(p)] * act(x[perm[p] // xdiv])) for the planned pairs in expert order."""
+    E, K_ = suh.shape
+    _check(_lib().r4dxb_trellis_input_grouped(_p(x), _p(suh), _p(out), _p(offsets), _p(perm), E, P, K_, xdiv, mode, _stream()),
+           "trellis_input_grouped")
+    return out
+
+
+def trellis_gemm_grouped(words, svh, xh, y, offsets, perm, tiles, ntiles, P: int, E: int, N: int, Kd: int, kb: int, tn: int):
+    """y[perm[p]] = expert e(p)'s trellis linear of the transformed row xh[p]; one launch for every expert."""
+    _check(_lib().r4dxb_trellis_gemm_grouped(_p(words), _p(svh), _p(xh), _p(y), _p(offsets), _p(perm), _p(tiles), _p(ntiles),
+                                             tiles.numel() // 2, P, E, N, Kd, kb, tn, _p(gemm_status(xh.device)), _stream()),
+           "trellis_gemm_grouped")
+    return y
+
+
 register_cuda_sig("r4dxb_topk_lse", _I, [_P, _I, _I, _I, _F, _I, _P, _P, _P, _P, _P])
 register_cuda_sig("r4dxb_repetition_penalty", _I, [_P, _I, _P, _I, _F, _P])
 

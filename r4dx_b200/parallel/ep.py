@@ -57,7 +57,8 @@ class EpComm:
         self.e_per = cfg.num_experts // world
         self.expert_range = (rank * self.e_per, self.e_per)
         self.spin_limit = spin_limit
-        self.cap = max_rows_per_expert or min(world * max_rows, 16)
+        # one expert can receive every row of every rank: the passes cover that worst case unless the caller bounds it
+        self.cap = max_rows_per_expert or world * max_rows
         self.tmax = tmax or (2 if self.cap <= 4 else 8)       # rows of one expert per grouped launch
         W, P, H = world, self.P, self.H
         a = lambda n: (n + 255) // 256 * 256

@@ -506,6 +506,64 @@ def test_grouped_expert_gemv(K):
             assert (got - ref).abs().max().item() < 0.03 * ref.abs().max().item() + 1e-3
 
 
+@pytest.mark.parametrize("kb,tn,T", [(3, 16, 40), (4, 32, 90), (5, 64, 150)])
+def test_grouped_expert_gemm_matches_the_per_pair_reference(K, kb, tn, T):
+    """Tile list + grouped input transform + grouped tensor-core product (gate_up then SwiGLU + down) for a skewed plan:
+    one expert holds a third of the rows (several tiles), some hold none, a slice of the experts is local."""
+    from r4dx_b200.models.moe import ExpertStack
+    from r4dx_b200.quant import trellis
+    g = torch.Generator().manual_seed(kb)
+    E, I, H, k = 7, 128, 256, 2
+    e_begin, e_count = 1, 5                                   # experts 1..5 are local; 0 and 6 live elsewhere
+    gu = [trellis.random_weight(2 * I, H, kb, seed=e, sigma=0.06) for e in range(E)]
+    dn = [trellis.random_weight(H, I, kb, seed=50 + e, sigma=0.06) for e in range(E)]
+    sg = ExpertStack.from_list([w.to("cuda") for w in gu[e_begin:e_begin + e_count]])
+    sd = ExpertStack.from_list([w.to("cuda") for w in dn[e_begin:e_begin + e_count]])
+    x = torch.randn(T, H, generator=g).to(BF)
+    ids = torch.randint(0, E, (T, k), generator=g).to(torch.int32)
+    ids[:, 1] = (ids[:, 0] + 1 + torch.randint(0, E - 1, (T,), generator=g).to(torch.int32)) % E
+    ids[: T // 3, 0] = 2
+    ids[: T // 3, 1] = torch.where(ids[: T // 3, 1] == 2, torch.tensor(3, dtype=torch.int32), ids[: T // 3, 1])
+    ids[ids == 4] = 5                                          # expert 4 gets nothing
+    ids[:, 1] = torch.where(ids[:, 1] == ids[:, 0], (ids[:, 0] + 1) % E, ids[:, 1])
+    P = T * k
+    off = torch.zeros(e_count + 1, dtype=torch.int32, device="cuda")
+    perm = torch.zeros(P, dtype=torch.int32, device="cuda")
+    K.moe_plan(ids.cuda(), P, E, e_begin, e_count, off, perm)
+    tiles = torch.zeros(2 * (P // tn + e_count + 1), dtype=torch.int32, device="cuda")
+    nt = torch.zeros(1, dtype=torch.int32, device="cuda")
+    K.moe_tiles(off, e_count, tn, tiles, nt)
+    o = off.cpu().tolist()
+    want = [(e, o[e] + j * tn) for e in range(e_count) for j in range((o[e + 1] - o[e] + tn - 1) // tn)]
+    assert int(nt.item()) == len(want)
+    assert tiles.cpu().view(-1, 2)[:len(want)].tolist() == [list(w) for w in want]
+    xh = torch.zeros(P, H, dtype=torch.float16, device="cuda")
+    gu_pairs = torch.zeros(P, 2 * I, dtype=BF, device="cuda")
+    y_pairs = torch.zeros(P, H, dtype=BF, device="cuda")
+    K.trellis_input_grouped(x.cuda(), sg.suh, xh, off, perm, P, k, 0)
+    K.trellis_gemm_grouped(sg.words, sg.svh, xh, gu_pairs, off, perm, tiles, nt, P, e_count, 2 * I, H, kb, tn)
+    xh2 = xh.view(-1)[:P * I].view(P, I)
+    K.trellis_input_grouped(gu_pairs, sd.suh, xh2, off, perm, P, 1, 1)
+    K.trellis_gemm_grouped(sd.words, sd.svh, xh2, y_pairs, off, perm, tiles, nt, P, e_count, H, I, kb, tn)
+    K.check_gemm_status(y_pairs.device)
+    checked = 0
+    for t in range(T):
+        for j in range(k):
+            e = int(ids[t, j])
+            got_gu, got_y = gu_pairs[t * k + j].float().cpu(), y_pairs[t * k + j].float().cpu()
+            if not (e_begin <= e < e_begin + e_count):
+                assert got_gu.abs().max().item() == 0 and got_y.abs().max().item() == 0      # not ours: untouched
+                continue
+            ref_gu = trellis.linear_reference(gu[e], x[t:t + 1].float())[0]
+            assert (got_gu - ref_gu).abs().max().item() < 0.03 * ref_gu.abs().max().item() + 1e-3
+            a = got_gu.to(BF).float()
+            m = (torch.nn.functional.silu(a[:I]) * a[I:]).to(BF).float()
+            ref_y = trellis.linear_reference(dn[e], m[None])[0]
+            assert (got_y - ref_y).abs().max().item() < 0.03 * ref_y.abs().max().item() + 1e-3
+            checked += 1
+    assert checked > T
+
+
 def test_topk_lse_summary_and_device_rep_penalty(K):
     from r4dx_b200.runtime.sampler import SampleParams, sample_canonical, sample_from_summary
     g = torch.Generator().manual_seed(12)

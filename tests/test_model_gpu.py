@@ -215,7 +215,7 @@ def test_moe_model_matches_oracle():
 
 
 def test_moe_chunked_prefill_matches_the_small_batch_path():
-    """A prompt longer than 8 rows takes the chunk path: all rows routed at once, experts served in 8-row passes."""
+    """A prompt longer than 8 rows takes the chunk path: all rows routed at once, experts served by the grouped tensor-core product."""
     from r4dx_b200.config import tiny_moe_config
     from r4dx_b200.models.hybrid import HybridModel
     from r4dx_b200.models.oracle import init_weights
