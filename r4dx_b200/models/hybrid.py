@@ -238,6 +238,21 @@ class HybridModel:
         if side is not None:
             torch.cuda.current_stream().wait_stream(side)
 
+    # ---- sibling projections in one launch -----------------------------------------------------------
+    fuse_siblings = os.environ.get("R4DXB_SIBLINGS", "1") != "0"
+
+    def _siblings(self, names):
+        """The one-launch group of these projections, or None when they cannot share a launch (other layouts, unequal
+        bit widths) or the switch is off; built once per name tuple."""
+        if not self.fuse_siblings:
+            return None
+        cache = self.__dict__.setdefault("_sibling_groups", {})
+        if names not in cache:
+            ws = [self.lin[n].w for n in names]
+            ok = all(isinstance(w_, TrellisWeight) for w_ in ws) and len({(w_.K, w_.kb) for w_ in ws}) == 1
+            cache[names] = K.SiblingGroup(ws) if ok else None
+        return cache[names]
+
     # ---- layers ---------------------------------------------------------------------------------
     def _gdn_layer(self, i: int, T: int) -> None:
         cfg, b, w = self.cfg, self.buf, self.w
@@ -246,15 +261,22 @@ class HybridModel:
         x, nw, eps = b.x[:T], w[f"text.layers.{i}.input_layernorm"], cfg.rms_norm_eps
         # the three projections read the same rows and write different buffers: the two small ones run on a side
         # stream (a parallel branch of the captured graph) while the large one fills the machine
-        side = self._fork()
-        self.lin[p + "in_proj_qkv"](x, out=b.mixed[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+        grp = self._siblings((p + "in_proj_qkv", p + "in_proj_z"))
+        ab_w = self.ab_w[i] if self.fuse_siblings and self.ab_w[i].shape[0] == 2 * Hv else None   # a / b inside the GDN kernel
+        side = self._fork() if (grp is None or ab_w is None) else None
+        if grp is not None:
+            grp(x, (b.mixed[:T], b.z[:T]), prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+        else:
+            self.lin[p + "in_proj_qkv"](x, out=b.mixed[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
         with torch.cuda.stream(side) if side is not None else _NullCtx():
-            self.lin[p + "in_proj_z"](x, out=b.z[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
-            K.bf16_gemv_norm(self.ab_w[i], x, nw, eps, b.ab[:T])
+            if grp is None:
+                self.lin[p + "in_proj_z"](x, out=b.z[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+            if ab_w is None:
+                K.bf16_gemv_norm(self.ab_w[i], x, nw, eps, b.ab[:T])
         self._join(side)
         K.gdn_decode(b.mixed, b.z, b.ab, w[p + "conv1d_weight"], w[p + "A_log"], w[p + "dt_bias"], w[p + "norm_weight"],
                      self.ring[i], self.gdn_state[i], self.log_u[i], self.log_k[i], self.log_eg[i], b.positions,
-                     b.n_replay, b.core, T, Hv, Hk, Dg, cfg.rms_norm_eps)
+                     b.n_replay, b.core, T, Hv, Hk, Dg, cfg.rms_norm_eps, ab_w=ab_w, x=x, in_norm_w=nw, in_eps=eps)
         core = b.core.view(-1)[:T * cfg.value_dim].view(T, cfg.value_dim)
         self._row_parallel(self.lin[p + "out_proj"], core, T)
 
@@ -275,12 +297,16 @@ class HybridModel:
         p = f"text.layers.{i}.attn."
         Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
         x, nw, eps = b.x[:T], w[f"text.layers.{i}.input_layernorm"], cfg.rms_norm_eps
-        side = self._fork()
-        self.lin[p + "qg"](x, out=b.qg[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
-        with torch.cuda.stream(side) if side is not None else _NullCtx():
-            self.lin[p + "k"](x, out=b.k[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
-            self.lin[p + "v"](x, out=b.v[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
-        self._join(side)
+        grp = self._siblings((p + "qg", p + "k", p + "v"))
+        if grp is not None:
+            grp(x, (b.qg[:T], b.k[:T], b.v[:T]), prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+        else:
+            side = self._fork()
+            self.lin[p + "qg"](x, out=b.qg[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+            with torch.cuda.stream(side) if side is not None else _NullCtx():
+                self.lin[p + "k"](x, out=b.k[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+                self.lin[p + "v"](x, out=b.v[:T], prologue=K.PRO_RMSNORM, norm_w=nw, eps=eps)
+            self._join(side)
         K.attn_precore(b.qg, b.k, b.v, w.get(p + "q_norm"), w.get(p + "k_norm"), w[p + "k_descale"], w[p + "v_descale"],
                        b.positions, self.block_table, b.q, self.kv[i], T, Hq, Hkv, D, cfg.rotary_dim,
                        cfg.layer_theta(i), cfg.rms_norm_eps, q_stride=cfg.q_proj_dim // Hq)

@@ -99,7 +99,10 @@ class MoeBlock:
         self.ks_dn_few = K.pick_ksplit(self.down.N, self.down.K, target_ctas=per_expert)
 
     def route(self, h: torch.Tensor, T: int) -> None:
-        K.bf16_gemv(self.router, h, out=self.logits[:T])
+        if T > 8:
+            K.linear_tc(self.router, h[:T], out=self.logits[:T])      # many rows: the router is a tensor-core product
+        else:
+            K.bf16_gemv(self.router, h, out=self.logits[:T])
         if self.cfg.moe_router == "sigmoid":
             K.moe_router_sigmoid(self.logits[:T], self.expert_bias, self.k, self.cfg.norm_topk_prob,
                                  self.cfg.routed_scaling_factor, self.ids, self.wts)

@@ -76,6 +76,13 @@ int r4dxb_repetition_penalty(float* logits, int V, const int* seen, int n, float
 /* Fused decode / verify step (T <= 8 rows): conv1d ring + SiLU, L2 norm, gates, delta rule, gated
  * RMSNorm.  The base state is only written when *n_replay > 0 (commit of the previous call's
  * accepted rows); this call's rows go to the log.  D (= key = value head dim) in {64, 128}. */
+/* The same step with the a / b projections computed in the kernel (ab_w [2H, K] bf16: a rows then b rows; x [T, K]
+ * residual rows; in_norm_w [K] the layer's zero-centred input RMSNorm weight); ab_w == null reads `ab` instead. */
+int r4dxb_gdn_decode_ab(const void* mixed, const void* z, const float* ab, const void* ab_w, const void* x,
+                        const void* in_norm_w, int K, float in_eps, const void* conv_w, const float* A_log,
+                        const float* dt_bias, const void* norm_w, void* ring, float* state, float* log_u, float* log_k,
+                        float* log_eg, const int* positions, const int* n_replay, void* out, int T, int H, int Hk, int D,
+                        float eps, void* stream);
 int r4dxb_gdn_decode(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
                      const float* dt_bias, const void* norm_w, void* ring, float* state, float* log_u, float* log_k,
                      float* log_eg, const int* positions, const int* n_replay, void* out, int T, int H, int Hk, int D,
@@ -90,6 +97,16 @@ int r4dxb_attn_precore(const void* qg, const void* k, const void* v, const void*
 int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const int* block_table, const int* positions,
                       const float* k_descale, const float* v_descale, float* part_acc, float* part_ml, void* out,
                       int T, int Hq, int Hkv, int D, int splits, int gated, void* stream);
+
+/* Sibling projections in one launch of the weight-streaming kernel: `count` (2 or 3) trellis weights of the same K and
+ * bit width read the same rows x through the same prologue; weight i writes y[i] [T, n[i]] (no residual). */
+int r4dxb_trellis_gemv_siblings(int count, const void* const* words, const void* const* suh, const void* const* svh,
+                                void* const* y, const int* n, const void* x, const void* norm_w, float eps, int prologue, int T,
+                                int K, int kb, int ksplit, void* stream);
+
+/* A/B switch: one-token steps use the warp-autonomous decode-attention kernel (default on); off = the window kernel
+ * for every row count, which makes one-row and many-row calls bit-identical. */
+void r4dxb_set_attn_decode_row(int on);
 
 /* ---- trellis GEMM on tcgen05 / TMEM (T >= 16 rows) ------------------------------------------- */
 /* xh = fp16(H128(suh * x)); mode 1 fuses silu(gate) * up over fused [T, 2K] rows */

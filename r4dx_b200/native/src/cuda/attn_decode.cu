@@ -504,12 +504,20 @@ int LaunchDecodeRow(const DecodeArgs& a, cudaStream_t s, int batch) {
   return LaunchPdl(DecodeRowKernel<D>, dim3(a.splits, a.Hkv, batch), dim3(256), smem, s, a);
 }
 
-// grid (G, Hkv), D threads
-__global__ void CombineKernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                              const __nv_bfloat16* __restrict__ qg, __nv_bfloat16* __restrict__ out, int T, int Hq,
-                              int Hkv, int D, int splits, int gated, int batched) {
+// grid (G * D / 32, Hkv [, B]), 256 threads = 32 output columns x 8 groups of splits.  Every thread has all of its
+// splits' partial sums in flight at once (8 loads for 64 splits), so the kernel is two dependent memory round trips
+// (statistics, partial sums) whatever the number of heads: with three query heads per rank the one-CTA-per-head
+// form took 19 us, longer than the attention itself.
+constexpr int kCombineThreads = 256;
+__global__ void __launch_bounds__(kCombineThreads)
+CombineKernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+              const __nv_bfloat16* __restrict__ qg, __nv_bfloat16* __restrict__ out, int T, int Hq,
+              int Hkv, int D, int splits, int gated, int batched) {
   PdlEnter();
-  const int g = blockIdx.x, hkv = blockIdx.y, d = threadIdx.x;
+  const int chunks = (D + 31) / 32;
+  const int g = blockIdx.x / chunks, dchunk = blockIdx.x % chunks, hkv = blockIdx.y;
+  const int lane = threadIdx.x & 31, sg = threadIdx.x >> 5;
+  const int d = dchunk * 32 + lane;
   const int gqa = Hq / Hkv, G = gqa * T;
   if (batched) {
     const int b = blockIdx.z;
@@ -519,32 +527,30 @@ __global__ void CombineKernel(const float* __restrict__ part_acc, const float* _
     qg += static_cast<size_t>(b) * Hq * 2 * D;
     out += static_cast<size_t>(b) * Hq * D;
   }
-  // The splits' row statistics first, all at once (one thread per split), then the weighted sums with the loads of
-  // four splits in flight per thread: a loop of dependent loads over 37 splits was 25 us, longer than the attention.
-  __shared__ float wsm[64], lsm[64];
-  __shared__ float red[32];
+  __shared__ float wsm[kCombineThreads], lsm[kCombineThreads];
+  __shared__ float red[8];
+  __shared__ float nsum[8][32], dsum[8];
   float M = -INFINITY, num = 0.f, den = 0.f;
-  const int cap = min(64, static_cast<int>(blockDim.x));
-  for (int s0 = 0; s0 < splits; s0 += cap) {          // up to 64 splits per round (one round in practice)
-    const int ns = min(cap, splits - s0);
+  for (int s0 = 0; s0 < splits; s0 += kCombineThreads) {     // one round for up to 256 splits
+    const int ns = min(kCombineThreads, splits - s0);
     float m = -INFINITY, l = 0.f;
     if (static_cast<int>(threadIdx.x) < ns) {
       const size_t r = (static_cast<size_t>(s0 + threadIdx.x) * Hkv + hkv) * G + g;
       m = part_ml[r * 2];
       l = part_ml[r * 2 + 1];
     }
-    // block-wide maximum of m (blockDim.x = D >= 64 threads)
     float mx = WarpMax(m);
     __syncthreads();
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    if (lane == 0) red[sg] = mx;
     __syncthreads();
     mx = red[0];
-    for (int w = 1; w < static_cast<int>(blockDim.x >> 5); ++w) mx = fmaxf(mx, red[w]);
+#pragma unroll
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, red[w]);
     const float Mn = fmaxf(M, mx);
     const float keep = (M == -INFINITY) ? 0.f : exp2f(M - Mn);
-    if (static_cast<int>(threadIdx.x) < ns) {
+    {
       const float w = (m == -INFINITY) ? 0.f : exp2f(m - Mn);
-      wsm[threadIdx.x] = w;
+      wsm[threadIdx.x] = w;                // threads past ns hold m = -inf: weight 0
       lsm[threadIdx.x] = w * l;
     }
     __syncthreads();
@@ -553,24 +559,37 @@ __global__ void CombineKernel(const float* __restrict__ part_acc, const float* _
     M = Mn;
     const float* pa = part_acc + ((static_cast<size_t>(s0) * Hkv + hkv) * G + g) * D + d;
     const size_t stride = static_cast<size_t>(Hkv) * G * D;
-    int s = 0;
-    for (; s + 4 <= ns; s += 4) {
-      const float v0 = pa[(s + 0) * stride], v1 = pa[(s + 1) * stride], v2 = pa[(s + 2) * stride], v3 = pa[(s + 3) * stride];
-      num += wsm[s] * v0 + wsm[s + 1] * v1 + wsm[s + 2] * v2 + wsm[s + 3] * v3;
-      den += lsm[s] + lsm[s + 1] + lsm[s + 2] + lsm[s + 3];
-    }
-    for (; s < ns; ++s) {
-      num += wsm[s] * pa[s * stride];
-      den += lsm[s];
+    for (int sb = sg; sb < ns; sb += 64) {                    // 8 splits of this thread per pass, loads issued together
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = (sb + 8 * i < ns && d < D) ? __ldcs(pa + static_cast<size_t>(sb + 8 * i) * stride) : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (sb + 8 * i < ns) {
+          num += wsm[sb + 8 * i] * v[i];
+          den += lsm[sb + 8 * i];
+        }
+      }
     }
   }
-  float o = den > 0.f ? num / den : 0.f;
-  const int t = g / gqa, hq = hkv * gqa + g % gqa;
-  if (gated) {
-    const float gate = __bfloat162float(qg[(static_cast<size_t>(t) * Hq + hq) * 2 * D + D + d]);
-    o *= Sigmoid(gate);
+  nsum[sg][lane] = num;
+  if (lane == 0) dsum[sg] = den;
+  __syncthreads();
+  if (sg == 0 && d < D) {
+    float n = 0.f, dn = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      n += nsum[w][lane];
+      dn += dsum[w];
+    }
+    float o = dn > 0.f ? n / dn : 0.f;
+    const int t = g / gqa, hq = hkv * gqa + g % gqa;
+    if (gated) {
+      const float gate = __bfloat162float(qg[(static_cast<size_t>(t) * Hq + hq) * 2 * D + D + d]);
+      o *= Sigmoid(gate);
+    }
+    out[(static_cast<size_t>(t) * Hq + hq) * D + d] = __float2bfloat16(o);
   }
-  out[(static_cast<size_t>(t) * Hq + hq) * D + d] = __float2bfloat16(o);
 }
 
 template <int GMAX>
@@ -648,7 +667,7 @@ int r4dxb_attn_decode(const void* q, const void* qg, const void* cache, const in
   else if (G <= 64) e = LaunchDecode<64>(a, s);
   else return R4DXB_UNSUPPORTED;
   if (e) return e;
-  return LaunchPdl(CombineKernel, dim3(G, Hkv), dim3(D), 0, s, static_cast<const float*>(part_acc), static_cast<const float*>(part_ml),
+  return LaunchPdl(CombineKernel, dim3(G * ((D + 31) / 32), Hkv), dim3(kCombineThreads), 0, s, static_cast<const float*>(part_acc), static_cast<const float*>(part_ml),
                    static_cast<const __nv_bfloat16*>(qg), static_cast<__nv_bfloat16*>(out), T, Hq, Hkv, D, splits, gated, 0);
 }
 
@@ -699,7 +718,7 @@ int r4dxb_attn_decode_batch(const void* q, const void* qg, const void* cache, co
   else if (G <= 32) e = LaunchDecode<32>(a, s, B);
   else e = LaunchDecode<64>(a, s, B);
   if (e) return e;
-  CombineKernel<<<dim3(G, Hkv, B), D, 0, s>>>(part_acc, part_ml, static_cast<const __nv_bfloat16*>(qg),
+  CombineKernel<<<dim3(G * ((D + 31) / 32), Hkv, B), kCombineThreads, 0, s>>>(part_acc, part_ml, static_cast<const __nv_bfloat16*>(qg),
                                               static_cast<__nv_bfloat16*>(out), 1, Hq, Hkv, D, splits, gated, 1);
   return FinishLaunch();
 }

@@ -41,6 +41,14 @@ struct GdnArgs {
   int T, H, Hk, conv_dim;
   float eps;
   const int* row_slot;           // batched decode: grid.y = sequence b (one row each), its state lives in slot row_slot[b]
+  // optional: the a / b projections computed here instead of read from `ab` (two K-long dot products per head and
+  // row are too little work for a launch of their own): ab_w [2H, K] bf16 (a rows, then b rows), x [T, K] the
+  // residual stream, in_norm_w [K] the layer's input RMSNorm weight (zero-centred), K columns
+  const __nv_bfloat16* ab_w;
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* in_norm_w;
+  int K;
+  float in_eps;
 };
 
 template <int D>
@@ -119,7 +127,37 @@ __global__ void __launch_bounds__(kThreads) GdnDecodeKernel(GdnArgs a) {
     const float y = Silu(acc);
     if (part == 0) sq[t][c] = y; else if (part == 1) sk[t][c] = y; else sv[t][c] = y;
   }
-  if (threadIdx.x < T) {
+  if (a.ab_w != nullptr) {
+    // a[t, h] and b[t, h] = W rows . bf16(rmsnorm(x[t])): the same rounding points as the stand-alone kernel
+    const __nv_bfloat16* wa = a.ab_w + static_cast<size_t>(h) * a.K;
+    const __nv_bfloat16* wb = a.ab_w + static_cast<size_t>(a.H + h) * a.K;
+    for (int t = 0; t < T; ++t) {
+      const __nv_bfloat16* xr = a.x + static_cast<size_t>(t) * a.K;
+      float ss = 0.f;
+      for (int k = threadIdx.x * 2; k < a.K; k += kThreads * 2) {
+        const uint32_t b = *reinterpret_cast<const uint32_t*>(xr + k);
+        ss += BfLo(b) * BfLo(b) + BfHi(b) * BfHi(b);
+      }
+      const float r = rsqrtf(BlockSum(ss, red) / a.K + a.in_eps);
+      float sa = 0.f, sb = 0.f;
+      for (int k = threadIdx.x * 2; k < a.K; k += kThreads * 2) {
+        const uint32_t b = *reinterpret_cast<const uint32_t*>(xr + k);
+        const uint32_t g = *reinterpret_cast<const uint32_t*>(a.in_norm_w + k);
+        const uint32_t hh = PackBf16(BfLo(b) * r * (1.f + BfLo(g)), BfHi(b) * r * (1.f + BfHi(g)));
+        const uint32_t va = *reinterpret_cast<const uint32_t*>(wa + k), vb = *reinterpret_cast<const uint32_t*>(wb + k);
+        sa += BfLo(va) * BfLo(hh) + BfHi(va) * BfHi(hh);
+        sb += BfLo(vb) * BfLo(hh) + BfHi(vb) * BfHi(hh);
+      }
+      sa = BlockSum(sa, red);
+      sb = BlockSum(sb, red);
+      if (threadIdx.x == 0) {
+        const float xs = sa + a.dt_bias[h];
+        const float sp = xs > 20.f ? xs : log1pf(__expf(xs));
+        seg[t] = __expf(-__expf(a.A_log[h]) * sp);
+        sbeta[t] = Sigmoid(sb);
+      }
+    }
+  } else if (threadIdx.x < T) {
     const int t = threadIdx.x;
     const float av = a.ab[static_cast<size_t>(t) * 2 * a.H + h], bv = a.ab[static_cast<size_t>(t) * 2 * a.H + a.H + h];
     const float xs = av + a.dt_bias[h];
@@ -222,12 +260,16 @@ __global__ void __launch_bounds__(kThreads) GdnDecodeKernel(GdnArgs a) {
 }  // namespace
 }  // namespace r4dxb
 
-extern "C" int r4dxb_gdn_decode(const void* mixed, const void* z, const float* ab, const void* conv_w,
-                                const float* A_log, const float* dt_bias, const void* norm_w, void* ring,
-                                float* state, float* log_u, float* log_k, float* log_eg, const int* positions,
-                                const int* n_replay, void* out, int T, int H, int Hk, int D, float eps, void* stream) {
+/* ab_w != null: the a / b projections are computed inside the kernel from the residual rows x [T, K], the layer's
+ * input RMSNorm weight and ab_w [2H, K] (a rows, then b rows); `ab` is then unused. */
+extern "C" int r4dxb_gdn_decode_ab(const void* mixed, const void* z, const float* ab, const void* ab_w, const void* x,
+                                   const void* in_norm_w, int K, float in_eps, const void* conv_w,
+                                   const float* A_log, const float* dt_bias, const void* norm_w, void* ring,
+                                   float* state, float* log_u, float* log_k, float* log_eg, const int* positions,
+                                   const int* n_replay, void* out, int T, int H, int Hk, int D, float eps, void* stream) {
   using namespace r4dxb;
   if (T < 0 || T > kMaxT || H % Hk || (D != 128 && D != 64)) return R4DXB_BAD_ARG;
+  if (ab_w != nullptr && (x == nullptr || in_norm_w == nullptr || K < 2 || K % 2)) return R4DXB_BAD_ARG;
   GdnArgs a;
   a.mixed = static_cast<const __nv_bfloat16*>(mixed);
   a.z = static_cast<const __nv_bfloat16*>(z);
@@ -250,9 +292,22 @@ extern "C" int r4dxb_gdn_decode(const void* mixed, const void* z, const float* a
   a.conv_dim = 2 * Hk * D + H * D;
   a.eps = eps;
   a.row_slot = nullptr;
+  a.ab_w = static_cast<const __nv_bfloat16*>(ab_w);
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.in_norm_w = static_cast<const __nv_bfloat16*>(in_norm_w);
+  a.K = K;
+  a.in_eps = in_eps;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 128) return LaunchPdl(GdnDecodeKernel<128>, dim3(H), dim3(kThreads), 0, s, a);
   return LaunchPdl(GdnDecodeKernel<64>, dim3(H), dim3(kThreads), 0, s, a);
+}
+
+extern "C" int r4dxb_gdn_decode(const void* mixed, const void* z, const float* ab, const void* conv_w,
+                                const float* A_log, const float* dt_bias, const void* norm_w, void* ring,
+                                float* state, float* log_u, float* log_k, float* log_eg, const int* positions,
+                                const int* n_replay, void* out, int T, int H, int Hk, int D, float eps, void* stream) {
+  return r4dxb_gdn_decode_ab(mixed, z, ab, nullptr, nullptr, nullptr, 0, 0.f, conv_w, A_log, dt_bias, norm_w, ring, state, log_u,
+                             log_k, log_eg, positions, n_replay, out, T, H, Hk, D, eps, stream);
 }
 
 /* Batched decode: B sequences, one row each; every per-sequence tensor (ring, state, logs, n_replay) carries a
@@ -279,6 +334,7 @@ extern "C" int r4dxb_gdn_decode_batch(const void* mixed, const void* z, const fl
   a.out = static_cast<__nv_bfloat16*>(out);
   a.T = 1; a.H = H; a.Hk = Hk; a.conv_dim = 2 * Hk * D + H * D; a.eps = eps;
   a.row_slot = row_slot;
+  a.ab_w = nullptr; a.x = nullptr; a.in_norm_w = nullptr; a.K = 0; a.in_eps = 0.f;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 128) return LaunchPdl(GdnDecodeKernel<128>, dim3(H, B), dim3(kThreads), 0, s, a);
   return LaunchPdl(GdnDecodeKernel<64>, dim3(H, B), dim3(kThreads), 0, s, a);

@@ -534,10 +534,10 @@ int LaunchGrouped(const void* w, const void* svh, const void* xh, void* y, int P
                   cudaStream_t s, const PlainArgs& pl) {
   const RsArgs rs = {};
   switch (tn) {
-    case 16: return LaunchGemm<KB, 16, 8, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
-    case 32: return LaunchGemm<KB, 32, 8, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
-    case 64: return LaunchGemm<KB, 64, 8, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
-    case 128: return LaunchGemm<KB, 128, 8, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
+    case 16: return LaunchGemm<KB, 16, 16, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
+    case 32: return LaunchGemm<KB, 32, 16, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
+    case 64: return LaunchGemm<KB, 64, 16, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
+    case 128: return LaunchGemm<KB, 128, 16, 3>(w, svh, xh, y, nullptr, P, N, K, status, s, rs, pl);
     default: return R4DXB_BAD_ARG;
   }
 }

@@ -71,7 +71,18 @@ struct GemvArgs {
   int* g_status;
   long long g_words_stride;        // words between consecutive experts
   int act;                         // gate activation of the fused gated-MLP prologue (GateAct)
+  // sibling mode: up to kMaxSiblings weights that read the same activations through the same prologue (q / k / v,
+  // the GDN qkv / z pair) share one launch; blockIdx.y runs over the row blocks of all of them back to back
+  int nsib;
+  struct Sibling {
+    const uint32_t* words;
+    const __half* suh;
+    const __half* svh;
+    __nv_bfloat16* y;
+    int N, nb_end;                 // row blocks [previous nb_end, nb_end) belong to this sibling
+  } sib[3];
 };
+constexpr int kMaxSiblings = 3;
 
 template <int KB, int TMAX, int PRO, bool kTp, bool kGrouped = false>
 __global__ void __launch_bounds__(kThreads)
@@ -80,12 +91,29 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
   cg::cluster_group cluster = cg::this_cluster();
   const int ksplit = gridDim.x;
   const int krank = blockIdx.x;            // == rank inside the cluster
-  const int nb = blockIdx.y;
+  int nb = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // the weight this CTA serves: the launch's only one, or one of the siblings (kernel parameters stay read-only)
+  const uint32_t* w_words = a.words;
+  const __half* w_suh = a.suh;
+  const __half* w_svh = a.svh;
+  __nv_bfloat16* w_y = a.y;
+  int N = a.N;
+  if (!kGrouped && !kTp && a.nsib > 0) {
+    int sidx = 0;
+    while (sidx + 1 < a.nsib && nb >= a.sib[sidx].nb_end) ++sidx;
+    if (sidx > 0) nb -= a.sib[sidx - 1].nb_end;
+    w_words = a.sib[sidx].words; w_suh = a.sib[sidx].suh; w_svh = a.sib[sidx].svh; w_y = a.sib[sidx].y; N = a.sib[sidx].N;
+  }
+  // K blocks are dealt out as evenly as the count allows (17 blocks over 4 CTAs: 4, 4, 4, 5); shared memory is laid
+  // out for the longest slice
   const int kslice = a.kblocks_per_cta * 128;
-  const int k_begin = krank * kslice;
+  const int kblocks_total = a.K / 128;
+  const int kb_lo = krank * kblocks_total / ksplit;
+  const int my_blocks = (krank + 1) * kblocks_total / ksplit - kb_lo;
+  const int k_begin = kb_lo * 128;
   int T = a.T;
-  const int N = a.N, K = a.K;
+  const int K = a.K;
   int g_base = 0;
   if constexpr (kGrouped) {
     // this launch handles rows [g_pass * TMAX, +TMAX) of every expert's list
@@ -99,9 +127,9 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
       a.x += static_cast<size_t>(call & 1) * a.g_x_par_stride;
       if (a.g_ready != nullptr) a.g_ready += static_cast<size_t>(call & 1) * a.g_ready_par_stride;
     }
-    a.words += static_cast<size_t>(e) * a.g_words_stride;
-    a.suh += static_cast<size_t>(e) * K;
-    a.svh += static_cast<size_t>(e) * N;
+    w_words += static_cast<size_t>(e) * a.g_words_stride;
+    w_suh += static_cast<size_t>(e) * K;
+    w_svh += static_cast<size_t>(e) * N;
   }
   constexpr int NW = 8 * KB;
   constexpr int kStageBytes = 8 * 8 * NW * 4;     // 8 k-tiles x 8 n-tiles
@@ -144,11 +172,11 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
   if (warp == kConsumerWarps) {
     // ---------------- producer: stream this CTA's words through the stage ring ----------------
     if (lane == 0) {
-      const unsigned char* src = reinterpret_cast<const unsigned char*>(a.words) +
-                                 (static_cast<size_t>(nb) * (K / 128) + static_cast<size_t>(krank) * a.kblocks_per_cta) * kStageBytes;
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(w_words) +
+                                 (static_cast<size_t>(nb) * (K / 128) + static_cast<size_t>(kb_lo)) * kStageBytes;
       int s = 0;
       uint32_t phase = 1;          // parity to wait for on the "empty" barrier of stage s (fresh barriers pass parity 1)
-      for (int it = 0; it < a.kblocks_per_cta; ++it) {
+      for (int it = 0; it < my_blocks; ++it) {
         if (!ptx::MbarWait(&empty[s], phase, abort_flag, 1)) break;
         ptx::MbarArriveExpectTx(&full[s], kStageBytes);
         ptx::BulkLoad(wst + static_cast<size_t>(s) * kStageBytes, src + static_cast<size_t>(it) * kStageBytes, kStageBytes, &full[s]);
@@ -207,8 +235,8 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
       asm volatile("bar.sync 1, 256;" ::: "memory");
     }
     const float inv_sqrt = 0.08838834764831845f;   // 1 / sqrt(128)
-    for (int item = warp; item < a.kblocks_per_cta * TMAX; item += kConsumerWarps) {
-      const int t = item / a.kblocks_per_cta, b = item % a.kblocks_per_cta;
+    for (int item = warp; item < my_blocks * TMAX; item += kConsumerWarps) {
+      const int t = item / my_blocks, b = item % my_blocks;
       float v[4] = {0.f, 0.f, 0.f, 0.f};
       const int k = k_begin + b * 128 + lane * 4;
       if (t < T) {
@@ -232,7 +260,7 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
             v[0] = BfLo(p01); v[1] = BfHi(p01); v[2] = BfLo(p23); v[3] = BfHi(p23);
           }
         }
-        const uint2 sv = *reinterpret_cast<const uint2*>(a.suh + k);
+        const uint2 sv = *reinterpret_cast<const uint2*>(w_suh + k);
         const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
         v[0] *= __low2float(s01); v[1] *= __high2float(s01); v[2] *= __low2float(s23); v[3] *= __high2float(s23);
       }
@@ -258,7 +286,7 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
     // K block would cost as much as decoding a dozen weights
     int s = 0;
     uint32_t phase = 0;
-    for (int it = 0; it < a.kblocks_per_cta && ok; ++it) {
+    for (int it = 0; it < my_blocks && ok; ++it) {
       ok = ptx::MbarWait(&full[s], phase, abort_flag, 2);
       if (!ok) break;
       const uint32_t* sw = reinterpret_cast<const uint32_t*>(wst + static_cast<size_t>(s) * kStageBytes) + warp * NW;
@@ -350,7 +378,7 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
         v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
       }
       WarpFwht128(v);
-      const uint2 sv = *reinterpret_cast<const uint2*>(a.svh + n);
+      const uint2 sv = *reinterpret_cast<const uint2*>(w_svh + n);
       const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
       o[0] = v[0] * inv_sqrt * __low2float(s01); o[1] = v[1] * inv_sqrt * __high2float(s01);
       o[2] = v[2] * inv_sqrt * __low2float(s23); o[3] = v[3] * inv_sqrt * __high2float(s23);
@@ -380,10 +408,10 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
           __syncwarp();
           if (lane == 0) atomicAdd_system(tp.ep_cnt[dest] + slot, 1u);
         } else {
-          *reinterpret_cast<uint2*>(a.y + out_row(t) * N + n) = ov;
+          *reinterpret_cast<uint2*>(w_y + out_row(t) * N + n) = ov;
         }
       } else {
-        *reinterpret_cast<uint2*>(a.y + out_row(t) * N + n) = ov;
+        *reinterpret_cast<uint2*>(w_y + out_row(t) * N + n) = ov;
       }
     }
   }
@@ -396,7 +424,7 @@ size_t SmemBytes(int tmax, int kslice, int stages, int kb, int ksplit) {
 
 template <int KB, int TMAX, int PRO, bool kTp>
 int Launch(GemvArgs a, int ksplit, cudaStream_t stream, const TpPush& tp) {
-  a.kblocks_per_cta = a.K / 128 / ksplit;
+  a.kblocks_per_cta = (a.K / 128 + ksplit - 1) / ksplit;       // the longest slice
   const int kslice = a.kblocks_per_cta * 128;
   // ring depth: everything in flight for short slices, otherwise up to 6 stages (48-60 KiB)
   a.stages = a.kblocks_per_cta < 6 ? a.kblocks_per_cta : 6;
@@ -408,7 +436,7 @@ int Launch(GemvArgs a, int ksplit, cudaStream_t stream, const TpPush& tp) {
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(ksplit, a.N / 128, 1);
+  cfg.gridDim = dim3(ksplit, a.nsib > 0 ? a.sib[a.nsib - 1].nb_end : a.N / 128, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -430,7 +458,7 @@ int Launch(GemvArgs a, int ksplit, cudaStream_t stream, const TpPush& tp) {
 
 template <int KB, int TMAX, int PRO>
 int LaunchGrouped(GemvArgs a, int ksplit, int experts, cudaStream_t stream, const TpPush& ep) {
-  a.kblocks_per_cta = a.K / 128 / ksplit;
+  a.kblocks_per_cta = (a.K / 128 + ksplit - 1) / ksplit;
   const int kslice = a.kblocks_per_cta * 128;
   a.stages = a.kblocks_per_cta < 6 ? a.kblocks_per_cta : 6;
   const size_t smem = SmemBytes(TMAX, kslice, a.stages, KB, ksplit);
@@ -497,7 +525,7 @@ GemvArgs MakeArgs(const void* words, const void* suh, const void* svh, const voi
 int CheckArgs(int T, int N, int K, int ksplit) {
   if (T < 1 || T > 8 || N % 128 || K % 128) return R4DXB_BAD_ARG;
   if (ksplit != 1 && ksplit != 2 && ksplit != 4 && ksplit != 8) return R4DXB_BAD_ARG;
-  if ((K / 128) % ksplit) return R4DXB_BAD_ARG;
+  if (K / 128 < ksplit) return R4DXB_BAD_ARG;       // every CTA of the cluster needs at least one K block
   return 0;
 }
 
@@ -518,6 +546,32 @@ int r4dxb_trellis_gemv_ex(const void* words, const void* suh, const void* svh, c
   if (prologue == 1 && (norm_w == nullptr || K % 8)) return R4DXB_BAD_ARG;
   GemvArgs a = MakeArgs(words, suh, svh, x, y, residual, norm_w, eps, T, N, K);
   if (prologue == 3) { prologue = 2; a.act = 1; }      // GeGLU: the SwiGLU prologue with a tanh-GELU gate
+  TpPush none = {};
+  return LaunchAll<false>(a, kb, prologue, ksplit, static_cast<cudaStream_t>(stream), none);
+}
+
+/* Sibling projections in one launch: `count` (2 or 3) trellis weights of the same K and bit width that read the same
+ * rows x through the same prologue; weight i writes y[i] [T, n[i]].  No residual, no all-reduce. */
+int r4dxb_trellis_gemv_siblings(int count, const void* const* words, const void* const* suh, const void* const* svh,
+                                void* const* y, const int* n, const void* x, const void* norm_w, float eps, int prologue, int T,
+                                int K, int kb, int ksplit, void* stream) {
+  if (count < 2 || count > kMaxSiblings) return R4DXB_BAD_ARG;
+  for (int i = 0; i < count; ++i)
+    if (int rc = CheckArgs(T, n[i], K, ksplit)) return rc;
+  if (prologue == 1 && (norm_w == nullptr || K % 8)) return R4DXB_BAD_ARG;
+  GemvArgs a = MakeArgs(words[0], suh[0], svh[0], x, y[0], nullptr, norm_w, eps, T, n[0], K);
+  if (prologue == 3) { prologue = 2; a.act = 1; }
+  a.nsib = count;
+  int end = 0;
+  for (int i = 0; i < count; ++i) {
+    end += n[i] / 128;
+    a.sib[i].words = static_cast<const uint32_t*>(words[i]);
+    a.sib[i].suh = static_cast<const __half*>(suh[i]);
+    a.sib[i].svh = static_cast<const __half*>(svh[i]);
+    a.sib[i].y = static_cast<__nv_bfloat16*>(y[i]);
+    a.sib[i].N = n[i];
+    a.sib[i].nb_end = end;
+  }
   TpPush none = {};
   return LaunchAll<false>(a, kb, prologue, ksplit, static_cast<cudaStream_t>(stream), none);
 }

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -160,15 +160,16 @@ def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], act: int = 0) -> tor
 
 
 def pick_ksplit(N: int, K: int, target_ctas: int = int(os.environ.get("R4DXB_KSPLIT_TARGET", "296"))) -> int:
-    """Smallest cluster split (1/2/4/8) that gives at least ``target_ctas`` CTAs, subject to K/128 % split == 0.
+    """Smallest cluster split (1/2/4/8) that gives at least ``target_ctas`` CTAs; every CTA needs at least one 128-wide
+    K block, and a block count the split does not divide is dealt out unevenly (17 blocks over 8 CTAs: 2 or 3 each).
     (In isolation the widest split is the fastest on every 27B shape, by up to 5 us; inside a decode step, where
     the RMSNorm prologue is repeated per K slice and neighbouring kernels overlap, it measured slower:
     90.3 vs 92.2 tok/s.)"""
     kblocks = K // 128
     best = 1
     for s in (1, 2, 4, 8):
-        if kblocks % s:
-            continue
+        if kblocks < s:
+            break
         best = s
         if (N // 128) * s >= target_ctas:
             break
@@ -222,7 +223,7 @@ def trellis_gemv(w: TrellisWeight, x: torch.Tensor, residual: Optional[torch.Ten
     T = x.numel() // (2 * w.K if prologue in (PRO_SILU_MUL, PRO_GELU_MUL) else w.K)
     out = out if out is not None else torch.empty(T, w.N, dtype=BF, device=x.device)
     ks = ksplit or pick_ksplit(w.N, w.K)
-    if GEMV_IMPL == "mma" and w.K // ks <= 6144:
+    if GEMV_IMPL == "mma" and w.K // ks <= 6144 and (w.K // 128) % ks == 0:
         _check(_lib().r4dxb_trellis_gemv_mma(_p(w.words), _p(w.suh), _p(w.svh), _p(x), _p(out), _p(residual), _p(norm_w), eps,
                                              prologue, T, w.N, w.K, w.kb, ks, _p(gemm_status(x.device)), _stream()),
                "trellis_gemv_mma")
@@ -230,6 +231,40 @@ def trellis_gemv(w: TrellisWeight, x: torch.Tensor, residual: Optional[torch.Ten
     _check(_lib().r4dxb_trellis_gemv_ex(_p(w.words), _p(w.suh), _p(w.svh), _p(x), _p(out), _p(residual), _p(norm_w), eps,
                                         prologue, T, w.N, w.K, w.kb, ks, _stream()), "trellis_gemv")
     return out
+
+
+register_cuda_sig("r4dxb_trellis_gemv_siblings", _I, [_I, _P, _P, _P, _P, _P, _P, _P, _F, _I, _I, _I, _I, _I, _P])
+
+
+class SiblingGroup:
+    """Trellis weights that read the same rows through the same prologue (q / k / v; the GDN qkv / z pair), served by
+    one launch of the weight-streaming kernel.  Holds the pointer tables so a call allocates nothing."""
+
+    def __init__(self, weights: Sequence[TrellisWeight]):
+        w0 = weights[0]
+        if not (2 <= len(weights) <= 3) or any(w.K != w0.K or w.kb != w0.kb for w in weights):
+            raise KernelError("siblings must be 2 or 3 trellis weights of one K and one bit width")
+        self.weights = list(weights)
+        self.K, self.kb = w0.K, w0.kb
+        arr = lambda vals: (ctypes.c_void_p * len(vals))(*vals)
+        self._words = arr([w.words.data_ptr() for w in weights])
+        self._suh = arr([w.suh.data_ptr() for w in weights])
+        self._svh = arr([w.svh.data_ptr() for w in weights])
+        self._n = (ctypes.c_int * len(weights))(*[w.N for w in weights])
+        self.ksplit = pick_ksplit(sum(w.N for w in weights), w0.K)
+        self._outs = {}
+
+    def __call__(self, x: torch.Tensor, outs: Sequence[torch.Tensor], prologue: int = PRO_NONE,
+                 norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6) -> None:
+        _req(x, BF, "x")
+        T = x.numel() // (2 * self.K if prologue in (PRO_SILU_MUL, PRO_GELU_MUL) else self.K)
+        key = tuple(o.data_ptr() for o in outs)
+        y = self._outs.get(key)
+        if y is None:
+            y = self._outs[key] = (ctypes.c_void_p * len(outs))(*key)
+        _check(_lib().r4dxb_trellis_gemv_siblings(len(self.weights), self._words, self._suh, self._svh, y, self._n, _p(x),
+                                                  _p(norm_w), eps, prologue, T, self.K, self.kb, self.ksplit, _stream()),
+               "trellis_gemv_siblings")
 
 
 def w4a16_gemv(w: W4Weight, x: torch.Tensor, out_f32: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -275,8 +310,20 @@ def argmax_rows(logits: torch.Tensor, id_offset: int = 0, out_ids: Optional[torc
     return out_ids, out_vals
 
 
+register_cuda_sig("r4dxb_gdn_decode_ab", _I, [_P] * 6 + [_I, _F] + [_P] * 12 + [_I, _I, _I, _I, _F, _P])
+
+
 def gdn_decode(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, log_u, log_k, log_eg, positions,
-               n_replay, out, T: int, H: int, Hk: int, D: int, eps: float = 1e-6) -> torch.Tensor:
+               n_replay, out, T: int, H: int, Hk: int, D: int, eps: float = 1e-6, ab_w=None, x=None, in_norm_w=None,
+               in_eps: float = 1e-6) -> torch.Tensor:
+    """With ``ab_w`` ([2H, K] bf16) the a / b projections of the residual rows ``x`` (input RMSNorm ``in_norm_w``) are
+    computed inside the kernel and ``ab`` is not read."""
+    if ab_w is not None:
+        _check(_lib().r4dxb_gdn_decode_ab(_p(mixed), _p(z), _p(ab), _p(ab_w), _p(x), _p(in_norm_w), ab_w.shape[1], in_eps,
+                                          _p(conv_w), _p(A_log), _p(dt_bias), _p(norm_w), _p(ring), _p(state), _p(log_u),
+                                          _p(log_k), _p(log_eg), _p(positions), _p(n_replay), _p(out), T, H, Hk, D, eps,
+                                          _stream()), "gdn_decode_ab")
+        return out
     _check(_lib().r4dxb_gdn_decode(_p(mixed), _p(z), _p(ab), _p(conv_w), _p(A_log), _p(dt_bias), _p(norm_w), _p(ring),
                                    _p(state), _p(log_u), _p(log_k), _p(log_eg), _p(positions), _p(n_replay), _p(out),
                                    T, H, Hk, D, eps, _stream()), "gdn_decode")
@@ -392,6 +439,10 @@ def linear_tc(W, x: torch.Tensor, bias: Optional[torch.Tensor] = None, residual:
     T = xk.shape[0]
     if out is None:
         out = torch.empty(T, N, dtype=torch.float32 if out_f32 else BF, device=dev)
+    else:
+        if out.dtype not in (torch.float32, BF) or out.numel() != T * N or not out.is_contiguous():
+            raise KernelError("linear_tc: out must be a contiguous fp32 or bf16 [T, N] tensor")
+        out_f32 = out.dtype == torch.float32
     if bias is not None:
         _req(bias, BF, "bias")
     if residual is not None:

@@ -21,6 +21,9 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=1)
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--model", default="27b", choices=["27b", "small", "lfm2"])
+    ap.add_argument("--tp", type=int, default=1, help="rank 0's shard of this tensor-parallel degree with the no-op communicator: "
+                    "the kernels of one rank at its real shapes, nothing exchanged (results are wrong by design)")
+    ap.add_argument("--graph", type=int, default=0, help="also time this many CUDA-graph replays of the step")
     ap.add_argument("--prefill", type=int, default=0, help="profile one chunked prefill of this many tokens instead of decode steps")
     a = ap.parse_args()
     from r4dx_b200.config import lfm2_moe_config, qwen_hybrid_27b_config, small_hybrid_config
@@ -32,8 +35,14 @@ def main() -> None:
         w = synthetic_weight_set(cfg, device="cuda", seed=0, kb_rule=moe_kb_rule)
     else:
         cfg = qwen_hybrid_27b_config(a.layers) if a.model == "27b" else small_hybrid_config(a.layers)
+        comm = None
+        if a.tp > 1:
+            from r4dx_b200.parallel.tp_emulated import NoopComm
+            comm = NoopComm(a.tp, 0, "cuda:0", None)
+            cfg = cfg.shard(a.tp, 0)
         w = synthetic_weight_set(cfg, device="cuda", seed=0)
-    m = HybridModel(cfg, w, max_ctx=max(a.ctx, a.prefill) + 64 + a.rows * (a.steps + 2))
+    m = HybridModel(cfg, w, max_ctx=max(a.ctx, a.prefill) + 64 + a.rows * (a.steps + 2 + a.graph),
+                    **({"comm": comm} if a.model != "lfm2" and comm is not None else {}))
     if a.prefill:
         ids = torch.randint(0, cfg.vocab_size, (a.prefill,), dtype=torch.int32)
         m.prefill(ids[:4096])          # warm-up (allocates the chunk buffers)
@@ -61,6 +70,18 @@ def main() -> None:
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
     print(f"eager {a.steps} step(s) of {a.rows} row(s): {e0.elapsed_time(e1) / a.steps:.3f} ms/step")
+    if a.graph and a.rows == 1:
+        m.enable_graphs((1,))
+        m.decode_begin(int(ids[0]))
+        for _ in range(3):
+            m.decode_step_graph()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.graph):
+            m.decode_step_graph()
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"graph replay, tp shard {a.tp}: {e0.elapsed_time(e1) / a.graph:.3f} ms/step")
 
 
 if __name__ == "__main__":

@@ -111,6 +111,38 @@ def test_trellis_gemv_one_hot_returns_decoded_rows(K):
     assert torch.allclose(y[1], 2 * Wr[:, 77], atol=0.06, rtol=0.02)
 
 
+@pytest.mark.parametrize("T,ksplit", [(1, 1), (3, 2), (8, 4)])
+def test_sibling_launch_equals_separate_launches(K, T, ksplit):
+    """Three weights of one K and bit width in one launch give bit-identical rows to three launches."""
+    from r4dx_b200.quant import trellis
+    g = torch.Generator().manual_seed(T)
+    ws = [trellis.random_weight(n, 640, 4, seed=n, sigma=0.05).to("cuda") for n in (384, 128, 256)]
+    x = torch.randn(T, 640, generator=g).to(BF).cuda()
+    nw = (torch.randn(640, generator=g) * 0.1).to(BF).cuda()
+    grp = K.SiblingGroup(ws)
+    grp.ksplit = ksplit
+    outs = [torch.zeros(T, w.N, dtype=BF, device="cuda") for w in ws]
+    grp(x, outs, prologue=K.PRO_RMSNORM, norm_w=nw, eps=1e-6)
+    for w, o in zip(ws, outs):
+        ref = K.trellis_gemv(w, x, ksplit=ksplit, prologue=K.PRO_RMSNORM, norm_w=nw, eps=1e-6)
+        assert torch.equal(o, ref)
+
+
+@pytest.mark.parametrize("ksplit", [2, 4, 8])
+def test_trellis_gemv_uneven_k_split(K, ksplit):
+    """17 K blocks over 2 / 4 / 8 CTAs of a cluster (uneven slices) against the unsplit launch and the reference."""
+    from r4dx_b200.quant import trellis
+    g = torch.Generator().manual_seed(ksplit)
+    w = trellis.random_weight(256, 17 * 128, 5, seed=9, sigma=0.05)
+    x = torch.randn(4, 17 * 128, generator=g).to(BF)
+    ref = trellis.linear_reference(w, x.float())
+    y1 = K.trellis_gemv(w.to("cuda"), x.cuda(), ksplit=1).float().cpu()
+    ys = K.trellis_gemv(w.to("cuda"), x.cuda(), ksplit=ksplit).float().cpu()
+    scale = ref.abs().max().item()
+    assert (ys - ref).abs().max().item() < 0.02 * scale
+    assert (ys - y1).abs().max().item() < 0.01 * scale
+
+
 @pytest.mark.parametrize("T", [1, 2, 5, 8])
 def test_w4a16_gemv_and_argmax(K, T):
     from r4dx_b200.quant import w4a16
@@ -182,6 +214,42 @@ def test_bf16_gemv(K):
     x = torch.randn(4, 1024, generator=g).to(BF)
     y = K.bf16_gemv(W.cuda(), x.cuda())
     assert torch.allclose(y.cpu(), x.float() @ W.float().T, atol=1e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("T", [1, 3, 8])
+def test_gdn_decode_with_in_kernel_ab_projection(K, T):
+    """The a / b projections computed inside the GDN kernel give the rows of the stand-alone norm + product kernel."""
+    g = torch.Generator().manual_seed(T)
+    D, Hv, Hk, Kd = 128, 6, 2, 1024
+    conv_dim = 2 * Hk * D + Hv * D
+    dev = "cuda"
+    mixed = (torch.randn(T, conv_dim, generator=g) * 0.5).to(BF).to(dev)
+    z = torch.randn(T, Hv * D, generator=g).to(BF).to(dev)
+    x = torch.randn(T, Kd, generator=g).to(BF).to(dev)
+    nw = (torch.randn(Kd, generator=g) * 0.1).to(BF).to(dev)
+    ab_w = (torch.randn(2 * Hv, Kd, generator=g) * 0.05).to(BF).to(dev)
+    conv_w = (torch.randn(conv_dim, 4, generator=g) * 0.5).to(BF).to(dev)
+    A_log = (torch.randn(Hv, generator=g) * 0.3).to(dev)
+    dt_bias = (torch.randn(Hv, generator=g) * 0.3).to(dev)
+    norm_w = (1 + 0.1 * torch.randn(D, generator=g)).to(BF).to(dev)
+    positions = torch.arange(0, T, dtype=torch.int32, device=dev)
+    outs, logs = [], []
+    for fused in (False, True):
+        ring = torch.zeros(16, conv_dim, dtype=BF, device=dev)
+        state = torch.zeros(Hv, D, D, device=dev)
+        log_u, log_k = torch.zeros(8, Hv, D, device=dev), torch.zeros(8, Hv, D, device=dev)
+        log_eg = torch.zeros(8, Hv, device=dev)
+        n_replay = torch.zeros(1, dtype=torch.int32, device=dev)
+        out = torch.zeros(8, Hv * D, dtype=BF, device=dev)
+        ab = torch.zeros(T, 2 * Hv, device=dev)
+        if not fused:
+            K.bf16_gemv_norm(ab_w, x, nw, 1e-6, ab)
+        K.gdn_decode(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, log_u, log_k, log_eg, positions, n_replay,
+                     out, T, Hv, Hk, D, ab_w=ab_w if fused else None, x=x, in_norm_w=nw, in_eps=1e-6)
+        outs.append(out[:T].float().cpu())
+        logs.append(log_eg[:T].cpu())
+    assert torch.allclose(logs[0], logs[1], atol=1e-5, rtol=1e-4)
+    assert torch.allclose(outs[0], outs[1], atol=2e-2, rtol=2e-2)
 
 
 @pytest.mark.parametrize("D,Hv,Hk", [(128, 6, 2), (64, 4, 2)])

@@ -91,7 +91,18 @@ def test_chunked_prefill_matches_small_batch_prefill(tiny):
     assert sum(int(x == y) for x, y in zip(ta, tb)) >= 5
 
 
-def test_speculative_verify_is_lossless(tiny):
+@pytest.fixture
+def same_attention_kernel_for_every_row_count():
+    """One-token steps normally take their own decode-attention kernel, whose rounding differs from the window kernel's
+    by ~0.3 % of the logit scale: enough to flip a near-tie.  Bit-exact comparisons between one-row and many-row calls
+    pin both to the window kernel."""
+    from r4dx_b200 import native
+    native.cuda().r4dxb_set_attn_decode_row(0)
+    yield
+    native.cuda().r4dxb_set_attn_decode_row(1)
+
+
+def test_speculative_verify_is_lossless(tiny, same_attention_kernel_for_every_row_count):
     """Windows with correct, partly wrong and fully wrong drafts reproduce the plain greedy stream."""
     from r4dx_b200.models.hybrid import HybridModel
     cfg, q, _ = tiny
@@ -117,6 +128,26 @@ def test_speculative_verify_is_lossless(tiny):
         rounds += 1
     assert out[:24] == ref[:24]
     assert rounds < 23          # speculation did accept drafts
+
+
+def test_window_rows_match_one_row_steps_within_rounding(tiny):
+    """With the default kernels (a dedicated one-token attention kernel) the rows of a verify window equal the rows of
+    one-token steps up to rounding: 1 % of the logit scale."""
+    from r4dx_b200.models.hybrid import HybridModel
+    cfg, q, _ = tiny
+    ids = torch.randint(0, cfg.vocab_size, (21,), generator=torch.Generator().manual_seed(5)).to(torch.int32)
+    a = HybridModel(cfg, _to_dev(q), max_ctx=256)
+    seq, rows = [a.prefill(ids)], []
+    for _ in range(6):
+        a.feed(torch.tensor([seq[-1]], dtype=torch.int32))
+        rows.append(a.buf.logits[0].float().cpu().clone())
+        seq.append(int(rows[-1].argmax()))
+    b = HybridModel(cfg, _to_dev(q), max_ctx=256)
+    assert b.prefill(ids) == seq[0]
+    b.feed(torch.tensor(seq[:6], dtype=torch.int32))
+    win = b.buf.logits[:6].float().cpu()
+    for i in range(6):
+        assert (win[i] - rows[i]).abs().max().item() < 0.01 * rows[i].abs().max().item()
 
 
 def test_checkpoint_restore_replays_identically(tiny):
