@@ -22,9 +22,20 @@ def load_text_model(args, device: Optional[str] = None):
     device = device or f"cuda:{local}"
     torch.cuda.set_device(torch.device(device))
     comm = None
-    if args.tp > 1:
-        if world != args.tp:
-            raise SystemExit(f"--tp {args.tp} needs {args.tp} ranks (python -m torch.distributed.run --nproc-per-node {args.tp} ...)")
+    pp = getattr(args, "pp", 1)
+    hybrid = bool(getattr(args, "hybrid", False))
+    ep = getattr(args, "ep", 1)
+    if hybrid and not (pp == 2 and args.tp == 2):
+        raise SystemExit("--hybrid is pipelined prefill + tensor-parallel decode on two ranks: use --pp 2 --tp 2 --hybrid")
+    if pp > 1 and not hybrid and args.tp > 1:
+        raise SystemExit("--pp 2 with --tp N needs --hybrid (pipelined prefill, then tensor-parallel decode)")
+    if ep > 1 and (args.tp > 1 or pp > 1):
+        raise SystemExit("--ep N runs data-parallel attention with expert-parallel experts: it does not combine with --tp / --pp")
+    ranks_needed = max(args.tp, pp, ep)
+    if ranks_needed > 1:
+        if world != ranks_needed:
+            raise SystemExit(f"this configuration needs {ranks_needed} ranks "
+                             f"(python -m torch.distributed.run --nproc-per-node {ranks_needed} ...)")
         import torch.distributed as dist
         if not dist.is_initialized():
             os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -37,13 +48,23 @@ def load_text_model(args, device: Optional[str] = None):
             gcfg.num_hidden_layers = args.layers
             gcfg.layer_types = gcfg.layer_types[:args.layers]
         cfg = gcfg.shard(args.tp, rank) if args.tp > 1 else gcfg
-        weights = synthetic_weight_set(cfg, device=device, seed=0)
+        if pp > 1:
+            # the pipeline stages run full-width layers of the same model the tensor-parallel ranks hold shards of
+            full = synthetic_weight_set(gcfg, device=device, seed=0)
+            weights = shard_weight_set(gcfg, full, args.tp, rank) if args.tp > 1 else full
+        else:
+            full = None
+            weights = synthetic_weight_set(cfg, device=device, seed=0)
         model_id = f"synthetic-{kind}"
     else:
         gcfg, full = load_weight_set(model_arg, device=device)
         cfg = gcfg.shard(args.tp, rank) if args.tp > 1 else gcfg
         weights = shard_weight_set(gcfg, full, args.tp, rank)
         model_id = os.path.splitext(os.path.basename(model_arg))[0]
+    if pp > 1:
+        return _load_pipeline(args, gcfg, cfg, weights, full, model_id, device, rank, world, hybrid)
+    if ep > 1:
+        return _load_expert_parallel(args, gcfg, weights, model_id, device, rank, world)
     if args.tp > 1:
         from ..parallel.tp_comm import make_comm, spin_limit_for_ms
         comm = make_comm(args.tp, rank, device, mode=args.tp_mode, hidden=gcfg.hidden_size,
@@ -72,3 +93,62 @@ def load_text_model(args, device: Optional[str] = None):
         group = RankGroup(rank, world, group=ctl, fault=FaultSpec.parse(getattr(args, "tp_fault", "") or ""))
         return TpTextModel(local, group, ctl_group=ctl, comm=comm), tk, tpl
     return local, tk, tpl
+
+
+def _facade(local, rank: int, world: int, args, comm=None):
+    """Leader/follower facade over ``world`` ranks (rank 0 serves; the others replay its calls)."""
+    import torch.distributed as dist
+    from ..parallel.tp_group import FaultSpec, RankGroup
+    from ..runtime.tp_model import TpTextModel
+    ctl = dist.new_group(backend="gloo")
+    group = RankGroup(rank, world, group=ctl, fault=FaultSpec.parse(getattr(args, "tp_fault", "") or ""))
+    return TpTextModel(local, group, ctl_group=ctl, comm=comm)
+
+
+def _load_pipeline(args, gcfg, cfg, weights, full, model_id, device, rank, world, hybrid):
+    """``--pp 2``: two-stage layer split (prefill pipelined over chunks, decode through both stages);
+    with ``--hybrid --tp 2`` the pipeline serves long prompts and decode runs tensor-parallel after a reshard."""
+    from ..models.hybrid import HybridModel
+    from ..parallel.pp import default_split
+    from ..runtime.pp_model import HybridPpTextModel, LayerSplitTextModel
+    from ..runtime.tokenizer import load_tokenizer
+    split = args.pp_split or default_split(gcfg)
+    if not 0 < split < gcfg.num_hidden_layers:
+        raise SystemExit(f"--pp-split {split} must leave both stages at least one of the {gcfg.num_hidden_layers} layers")
+    rng = (0, split) if rank == 0 else (split, gcfg.num_hidden_layers)
+    # the stage runs full-width layers: the unsharded weights (a synthetic set is re-created unsharded)
+    stage_w = full if full is not None else weights
+    stage = HybridModel(gcfg, stage_w, max_ctx=args.max_ctx, device=device, layer_range=rng)
+    chunk = getattr(args, "prefill_chunk", 0) or 1024
+    tk, tpl = load_tokenizer(args.tokenizer_dir, gcfg.vocab_size)
+    if not hybrid:
+        local = LayerSplitTextModel(stage, rank, split, gcfg, model_id=model_id, chunk=chunk)
+        return _facade(local, rank, world, args), tk, tpl
+    from ..parallel.tp_comm import make_comm, spin_limit_for_ms
+    comm = make_comm(args.tp, rank, device, mode=args.tp_mode, hidden=gcfg.hidden_size,
+                     spin_limit=spin_limit_for_ms(getattr(args, "tp_ar_timeout_ms", 500)))
+    tp_model = HybridModel(cfg, weights, max_ctx=args.max_ctx, device=device, comm=comm)
+    local = HybridPpTextModel(tp_model, stage, rank, world, split, gcfg, model_id=model_id, chunk=chunk,
+                              min_rows=getattr(args, "pp_min_rows", 512), prefill_chunk=getattr(args, "prefill_chunk", 0))
+    return _facade(local, rank, world, args, comm=comm), tk, tpl
+
+
+def _load_expert_parallel(args, gcfg, weights, model_id, device, rank, world):
+    """``--ep N`` (mixture-of-experts models): every rank keeps the attention / recurrent layers whole and a slice of the
+    experts; tokens travel to their experts and back inside the dispatch / combine kernels.  Every rank runs the same
+    requests here (the leader serves, followers replay), so the ranks' rows are identical copies."""
+    from ..models.hybrid import HybridModel
+    from ..parallel.ep import EpComm
+    from ..parallel.tp_comm import spin_limit_for_ms
+    from ..runtime.text_model import LocalTextModel
+    from ..runtime.tokenizer import load_tokenizer
+    if not gcfg.is_moe:
+        raise SystemExit("--ep needs a mixture-of-experts model")
+    if gcfg.num_experts % world:
+        raise SystemExit(f"--ep {world} must divide the {gcfg.num_experts} experts")
+    from ..models.hybrid import MAX_ROWS
+    comm = EpComm(world, rank, device, gcfg, max_rows=MAX_ROWS, spin_limit=spin_limit_for_ms(getattr(args, "tp_ar_timeout_ms", 500)))
+    model = HybridModel(gcfg, weights, max_ctx=args.max_ctx, device=device, comm=comm)
+    tk, tpl = load_tokenizer(args.tokenizer_dir, gcfg.vocab_size)
+    local = LocalTextModel(model, model_id=model_id, global_config=gcfg, prefill_chunk=getattr(args, "prefill_chunk", 0))
+    return _facade(local, rank, world, args), tk, tpl

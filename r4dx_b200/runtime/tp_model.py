@@ -67,10 +67,10 @@ class TpTextModel(TextModel):
 
     def _full_logits(self, t: torch.Tensor) -> torch.Tensor:
         """Concatenates the ranks' vocabulary shards (rank order = vocabulary order)."""
-        shard = getattr(self.local.config, "vocab_shard_size", None)
-        full = getattr(self.config, "vocab_size", None)
-        if not t.is_cuda or shard is None or shard == full or self.world == 1:
+        cfg_local = getattr(getattr(self.local, "m", None), "cfg", None)    # the rank-local device model knows its shard
+        if not t.is_cuda or self.world == 1 or cfg_local is None or getattr(cfg_local, "tp_world", 1) == 1:
             return t
+        full = self.config.vocab_size
         rows = t.reshape(-1, t.shape[-1]).float().contiguous()
         parts = torch.empty(self.world, rows.shape[0], rows.shape[1], dtype=rows.dtype, device=rows.device)
         dist.all_gather_into_tensor(parts, rows, group=self.data_group)

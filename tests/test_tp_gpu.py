@@ -54,10 +54,10 @@ def test_fused_allreduce_wait_runs_out_and_reports(tmp_path):
     assert torch.isfinite(K.trellis_gemv(tw, x).float()).all()
 
 
-def _run_ranks(n, script, timeout=420):
+def _run_ranks(n, script, timeout=420, args=()):
     env = dict(os.environ, MASTER_ADDR="127.0.0.1", NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-           "--master-addr", "127.0.0.1", "--master-port", "29541", script]
+           "--master-addr", "127.0.0.1", "--master-port", "29541", script, *args]
     return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=ROOT)
 
 
@@ -84,3 +84,13 @@ def test_pipeline_prefill_and_reshard_to_tp():
     r = _run_ranks(2, os.path.join(ROOT, "tests", "pp_worker.py"))
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "PP_OK" in r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("mode", ["split", "hybrid"])
+def test_loader_products_for_pipeline_flags(mode):
+    """--pp 2 (layer split) and --pp 2 --tp 2 --hybrid (pipelined prefill, reshard, tensor-parallel decode) through the
+    loader and the leader/follower facade, against the whole model on one GPU."""
+    r = _run_ranks(2, os.path.join(ROOT, "tests", "pp_product_worker.py"), args=(mode,))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert f"PP_PRODUCT_OK {mode}" in r.stdout
