@@ -36,6 +36,11 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--prefill-chunk", type=int, default=0, help="rows per prefill chunk (0: the model's default)")
     ap.add_argument("--ttft-lens", default="32768,131072", help="extra prompt lengths whose cold TTFT is measured after the decode run")
+    ap.add_argument("--extras", default="mtp,dflash",
+                    help="comma list of extra arms reported under \"extras\" (the headline value is unaffected): mtp = MTP "
+                         "speculation with 3 drafts per round, dflash = block-diffusion drafter with 7 drafts per round, "
+                         "pp2 = pipelined-prefill TTFT (2 ranks only); empty for none")
+    ap.add_argument("--spec-rounds", type=int, default=48)
     ap.add_argument("--no-pdl", action="store_true", help="A/B: disable programmatic dependent launch")
     ap.add_argument("--no-overlap", action="store_true", help="A/B: run sibling projections back to back instead of on a side stream")
     return ap.parse_args()
@@ -133,7 +138,8 @@ def main():
     cfg = gcfg.shard(world, rank) if world > 1 else gcfg
     extra_lens = [int(x) for x in args.ttft_lens.split(",") if x.strip()]
     total = max([args.prompt_len + args.warmup * 2 + args.steps * 2 + 64] + [n + 64 for n in extra_lens])
-    w = synthetic_weight_set(cfg, device=dev, seed=0)
+    want = [x for x in args.extras.split(",") if x.strip()]
+    w = synthetic_weight_set(cfg, device=dev, seed=0, with_mtp="mtp" in want and gcfg.mtp_num_hidden_layers > 0)
     model = HybridModel(cfg, w, max_ctx=total, device=dev, comm=comm)
     if args.no_overlap:
         model.overlap_siblings = False
@@ -235,6 +241,62 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ttft_all[str(n)] = float(t[0]) / 1e3
 
+    # ---- extra arms: speculative decoding rounds on the same model and prompt -----------------------------
+    extras = {}
+
+    def spec_arm(drafter, k: int) -> dict:
+        """Prefills the prompt with the drafter's hooks, then times ``--spec-rounds`` draft + verify rounds.  The weights
+        are random, so nearly every draft is rejected: tokens per round is what this model gives, not what a trained
+        drafter gives; the round time is the cost of a round whatever the acceptance."""
+        from r4dx_b200.runtime.text_model import LocalTextModel
+        lm = LocalTextModel(model, drafter=drafter)
+        lm.reset()
+        t0 = lm.prefill(prompt.tolist())
+        out = [t0]
+        for _ in range(3):
+            out += lm.decode_step_spec_greedy(out[-1], k)
+        barrier()
+        n0 = len(out)
+        e0.record()
+        for _ in range(args.spec_rounds):
+            out += lm.decode_step_spec_greedy(out[-1], k)
+        e1.record()
+        barrier()
+        verify_ranks("speculative rounds")
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        emitted = len(out) - n0
+        return {"k": k, "rounds": args.spec_rounds, "ms_per_round": ms / args.spec_rounds,
+                "tokens_per_round": emitted / args.spec_rounds, "tok_s": emitted / (ms / 1e3),
+                "tok_s_if_every_draft_were_accepted": (k + 1) / (ms / args.spec_rounds / 1e3)}
+
+    if "mtp" in want and any(k_.startswith("mtp.") for k_ in w):
+        from r4dx_b200.models.mtp import MtpDrafter
+        extras["mtp_k3"] = spec_arm(MtpDrafter(model, w), 3)
+    if "dflash" in want and args.model == "qwen-hybrid-27b" and world == 1:
+        from r4dx_b200.models.dflash import DflashConfig, DflashDrafter, synthetic_dflash_weights
+        dcfg = DflashConfig(target_layers=tuple(l for l in (6, 20, 34, 48, 62) if l < gcfg.num_hidden_layers))
+        extras["dflash_k7"] = spec_arm(DflashDrafter(model, dcfg, synthetic_dflash_weights(dcfg, gcfg.vocab_size, device=dev)), 7)
+        model.capture_layers = ()
+    if "pp2" in want and world == 2:
+        from r4dx_b200.parallel.pp import PipelinePrefill, default_split
+        split = default_split(gcfg)
+        rng_ = (0, split) if rank == 0 else (split, gcfg.num_hidden_layers)
+        stage = HybridModel(gcfg, synthetic_weight_set(gcfg, device=dev, seed=0), max_ctx=total, device=dev, layer_range=rng_)
+        pp = PipelinePrefill(stage, rank, split, chunk=args.prefill_chunk or 1024)
+        pp.prefill(prompt[:2048 + 300])
+        stage.reset()
+        barrier()
+        e0.record()
+        pp.prefill(prompt)
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        extras["pp2_ttft_s"] = {str(args.prompt_len): float(t[0]) / 1e3, "split": split}
+
     if rank == 0:
         value = args.steps / (dev_ms / 1e3)
         stream_gb = model.streamed_bytes_per_token() / 1e9
@@ -265,6 +327,8 @@ def main():
         }
         if e2e:
             out["e2e"] = e2e
+        if extras:
+            out["extras"] = extras
         print(json.dumps(out))
     if world > 1:
         # leave without tearing NCCL down: communicators referenced by captured graphs can stall the teardown

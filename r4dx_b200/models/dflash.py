@@ -79,6 +79,31 @@ def init_dflash_weights(c: DflashConfig, vocab: int, seed: int = 0) -> Dict[str,
     return w
 
 
+def synthetic_dflash_weights(c: DflashConfig, vocab: int, device="cuda", seed: int = 0) -> Dict[str, object]:
+    """A random drafter created directly in the device layouts (random w4a16 nibbles for the large linears): the same
+    bytes and kernels per round as a converted drafter, without a minutes-long host quantization.  Benchmarks only."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    n = lambda *s, sc=0.05: (torch.randn(*s, generator=g, device=device) * sc)
+    H, G = c.hidden, c.hidden // 16
+    big = lambda N, K_, i: w4a16.random_weight(N, K_, c.group, seed=seed * 1000 + i, sigma=0.02, device=device)
+    gc = torch.Generator().manual_seed(seed)
+    q: Dict[str, object] = {"fc": big(H, len(c.target_layers) * H, 0), "inject_norm": (1 + n(H)).to(BF), "out_norm": (1 + n(H)).to(BF),
+                            "mask_embed": n(H, sc=0.5).to(BF), "selector_hidden": n(c.rank, H).to(BF),
+                            "succ": (torch.randn(vocab, c.rank, generator=gc) * 0.3).contiguous(),
+                            "pred": (torch.randn(vocab, c.rank, generator=gc) * 0.3).contiguous()}
+    for i in range(c.layers):
+        p = f"layers.{i}."
+        q.update({p + "in_norm": (1 + n(H)).to(BF), p + "post_norm": (1 + n(H)).to(BF), p + "q_norm": (1 + n(c.head_dim)).to(BF),
+                  p + "k_norm": (1 + n(c.head_dim)).to(BF),
+                  p + "wq": big(c.heads * c.head_dim, H, 10 * i + 1), p + "wk": big(c.kv_heads * c.head_dim, H, 10 * i + 2),
+                  p + "wv": big(c.kv_heads * c.head_dim, H, 10 * i + 3), p + "wo": big(H, c.heads * c.head_dim, 10 * i + 4),
+                  p + "gate_up": big(2 * c.intermediate, H, 10 * i + 5), p + "down": big(H, c.intermediate, 10 * i + 6)})
+        for j in range(4):
+            q[p + f"conv{j}.base"] = torch.cat([1 + n(1, G), n(1, G)], 0).to(BF)
+            q[p + f"conv{j}.dyn"] = n(2 * G, H, sc=0.02).to(BF)
+    return q
+
+
 def quantize_dflash_weights(c: DflashConfig, w: Dict[str, torch.Tensor]):
     """(device-format dict, fp32 dict holding exactly the values the device will use)."""
     q, dq = {}, {}
@@ -225,7 +250,8 @@ class DflashDrafter:
         """w4a16 product: the weight-streaming kernel up to 8 rows, the tensor-core kernel above."""
         w = self.w[name]
         T = x.shape[0]
-        if T > 8:
+        tmax = 1 if T == 1 else (2 if T == 2 else (4 if T <= 4 else 8))       # rows the streaming kernel stages in shared memory
+        if T > 8 or tmax * w.K * 2 > 200 * 1024:
             return K.linear_tc(w, x)
         out = torch.empty(T, w.N, dtype=BF, device=x.device)
         K.w4a16_gemv(w, x.contiguous(), out_f32=False, out=out)

@@ -167,6 +167,21 @@ def synthetic_weight_set(cfg: ModelConfig, device="cuda", seed: int = 0, sigma: 
             w[p + "gdn.norm_weight"] = (1.0 + n(cfg.linear_value_head_dim).float()).to(torch.bfloat16)
     w["text.final_norm"] = n(H)
     w["lm_head"] = w4a16.random_weight(cfg.vocab_shard_size, H, head_group, seed=seed + 17, sigma=sigma, device=device)
+    if with_mtp and cfg.mtp_num_hidden_layers:
+        # the next-token-prediction head: fc over [embedding | hidden], one gated attention layer, one MLP, its own norm
+        p = "mtp."
+        inner = cfg.intermediate_size if cfg.intermediate_size else cfg.moe_intermediate_size
+        shapes = [("fc", H, 2 * H), ("attn.qg", cfg.q_proj_dim, H), ("attn.k", cfg.kv_dim, H), ("attn.v", cfg.kv_dim, H),
+                  ("attn.o", H, cfg.q_dim), ("mlp.gate_up", 2 * inner, H), ("mlp.down", H, inner)]
+        for j, (name, N, K) in enumerate(shapes):
+            w[p + name] = trellis.random_weight(N, K, kb_rule(p + name), seed=seed * 7919 + 100003 + j, sigma=sigma, device=device)
+        for name in ("pre_fc_norm_embedding", "pre_fc_norm_hidden", "input_layernorm", "post_attention_layernorm", "norm"):
+            w[p + name] = n(H)
+        if cfg.qk_norm:
+            w[p + "attn.q_norm"] = n(cfg.head_dim)
+            w[p + "attn.k_norm"] = n(cfg.head_dim)
+        w[p + "attn.k_descale"] = torch.full((cfg.num_key_value_heads,), 1.0 / 16, device=device)
+        w[p + "attn.v_descale"] = torch.full((cfg.num_key_value_heads,), 1.0 / 16, device=device)
     if cfg.is_moe:
         e_begin, e_count = expert_range if expert_range is not None else (0, cfg.num_experts)
         for i in range(cfg.num_dense_layers, cfg.num_hidden_layers):
