@@ -159,13 +159,34 @@ def bias_act(x: torch.Tensor, bias: Optional[torch.Tensor], act: int = 0) -> tor
     return x
 
 
-def pick_ksplit(N: int, K: int, target_ctas: int = int(os.environ.get("R4DXB_KSPLIT_TARGET", "296"))) -> int:
+def _load_tuning() -> dict:
+    """Measured exceptions to the two heuristics below (written by ``utils/tune_gemm.py``); ``R4DXB_TUNING=0`` ignores it."""
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tuning_table.json")
+    if os.environ.get("R4DXB_TUNING", "1") == "0" or not os.path.exists(path):
+        return {}
+    import json
+    try:
+        t = json.load(open(path))
+    except (OSError, ValueError):
+        return {}
+    out = {("gemv",) + tuple(k.split("x")): v["ksplit"] for k, v in t.get("gemv", {}).items()}
+    out.update({("gemm",) + tuple(k.split("x")): v["tn"] for k, v in t.get("gemm", {}).items()})
+    return out
+
+
+TUNING = _load_tuning()
+
+
+def pick_ksplit(N: int, K: int, target_ctas: int = int(os.environ.get("R4DXB_KSPLIT_TARGET", "296")), rows: int = 1) -> int:
     """Smallest cluster split (1/2/4/8) that gives at least ``target_ctas`` CTAs; every CTA needs at least one 128-wide
     K block, and a block count the split does not divide is dealt out unevenly (17 blocks over 8 CTAs: 2 or 3 each).
     (In isolation the widest split is the fastest on every 27B shape, by up to 5 us; inside a decode step, where
     the RMSNorm prologue is repeated per K slice and neighbouring kernels overlap, it measured slower:
     90.3 vs 92.2 tok/s.)"""
     kblocks = K // 128
+    hit = TUNING.get(("gemv", str(N), str(K), "1" if rows == 1 else "n")) if target_ctas == 296 else None
+    if hit is not None and kblocks >= hit:
+        return hit
     best = 1
     for s in (1, 2, 4, 8):
         if kblocks < s:
@@ -366,14 +387,17 @@ def trellis_input(x: torch.Tensor, suh: torch.Tensor, out: Optional[torch.Tensor
 _TILE_COST = {128: 0.60, 256: 0.62, 512: 1.0}   # relative time of one CTA's K loop (decode-bound below 512 columns)
 
 
-def pick_token_tile(T: int, N: int = 0) -> int:
+def pick_token_tile(T: int, N: int = 0, K: int = 0) -> int:
     """Token-tile width of the tensor-core GEMM: the smallest tile that covers T below 512 rows; above,
     the width whose CTA count wastes the fewest of the 148 SMs' waves (one CTA per SM)."""
     for tn in (16, 32, 64, 128):
         if T <= tn:
             return tn
+    hit = TUNING.get(("gemm", str(N), str(K), str(T))) if K else None
+    if hit is not None:
+        return hit
     if T < 512:
-        return 128
+        return 256 if T > 192 else 128      # measured at 256 rows: one 256-row tile per CTA is 1.6-1.7x faster than two 128-row CTAs
     if N <= 0:
         return 512 if T >= 1024 else 256
     best, best_cost = 256, None
@@ -391,7 +415,7 @@ def trellis_gemm(w: TrellisWeight, xh: torch.Tensor, residual: Optional[torch.Te
     _req(xh, torch.float16, "xh")
     T = xh.numel() // w.K
     out = out if out is not None else torch.empty(T, w.N, dtype=BF, device=xh.device)
-    tn = tn or pick_token_tile(T, w.N)
+    tn = tn or pick_token_tile(T, w.N, w.K)
     _check(_lib().r4dxb_trellis_gemm(_p(w.words), _p(w.svh), _p(xh), _p(out), _p(residual), T, w.N, w.K, w.kb, tn,
                                      _p(gemm_status(xh.device)), _stream()), "trellis_gemm")
     return out
