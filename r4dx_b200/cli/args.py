@@ -109,5 +109,22 @@ def convert_parser() -> argparse.ArgumentParser:
                     help="safetensors file from `python -m r4dx_b200.quant.calibrate imatrix`: weighs the search by channel importance")
     ap.add_argument("--kv-calib", default=None, help="JSON file with per-layer k/v amax for fp8 descales")
     ap.add_argument("--reuse-tensors-from", default=None, help="older container whose identical tensors are copied, guarded by sha256")
+    ap.add_argument("--rotate", default="none", choices=["none", "q2a", "q2ab"],
+                    help="residual-stream rotation folded into the weights before quantization (dense hybrid family); "
+                         "q2ab equals q2a for trellis bodies, whose linears already carry their own block Hadamards")
+    ap.add_argument("--rotation-seed", type=lambda v: int(v, 0), default=0x5EED, help="u64, decimal or 0x hex")
+    ap.add_argument("--rotation-block", type=int, default=0, help="Hadamard block of the rotation (default: up to 1024)")
+    ap.add_argument("--rotation-out", default=None, metavar="FILE.safetensors",
+                    help="with --rotate and no quantization wanted: write only the rotation tensors and exit")
+    ap.add_argument("--no-bf16", action="store_true", help="quantize the small linears that normally stay bf16 as well "
+                                                           "(GDN a / b projections, routers): an all-w8a16 container")
+    ap.add_argument("--vision", default="off", choices=["on", "off"], help="keep the checkpoint's vision tower tensors (bf16)")
+    ap.add_argument("--dflash-hf", default=None, metavar="DIR",
+                    help="also convert a block-diffusion drafter checkpoint (safetensors + config.json) into <output>.dflash")
+    ap.add_argument("--trellis-from", default=None, metavar="DIR",
+                    help="import already-encoded trellis tensors (<name>.trellis.words/.suh/.svh in safetensors files of DIR, "
+                         "this engine's tile order) instead of encoding those linears; every imported tensor is reconstructed on "
+                         "the CPU and checked against the checkpoint")
+    ap.add_argument("--trellis-verify", default="full", choices=["full", "none"])
     ap.add_argument("--selftest", action="store_true", help="re-open the output and verify every tensor's reconstruction error")
     return ap

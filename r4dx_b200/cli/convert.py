@@ -71,6 +71,22 @@ def main(argv=None) -> int:
     keep = [s for s in args.keep_bf16.split(",") if s]
     layout = args.layouts.split(",")[0]
     src = {k: v for k, v in w.items()}
+    extra_meta = {}
+    if args.rotate != "none":
+        # the fold happens in fp32 before anything is quantized; the container carries the rotation tensors and their seed
+        from ..quant import rotation as rot
+        try:
+            spec = rot.make_spec(args.rotate, args.rotation_seed, cfg.hidden_size, args.rotation_block or None)
+            if args.rotation_out:
+                from safetensors.torch import save_file
+                save_file(rot.rotation_tensors(spec), args.rotation_out, metadata={"rotation": json.dumps(spec.to_meta())})
+                print(f"wrote {args.rotation_out}: rotation tensors only", file=sys.stderr)
+                return 0
+            src = rot.fold_rotation(cfg, src, spec)
+        except ValueError as e:
+            raise SystemExit(f"--rotate {args.rotate}: {e}")
+        w = src                                  # hashes, reuse and the self test refer to the folded weights
+        extra_meta["rotation"] = json.dumps(spec.to_meta())
     hessians = None
     if args.hessians:
         from safetensors.torch import load_file
@@ -101,8 +117,8 @@ def main(argv=None) -> int:
                 q[k] = oldq[k]
                 reused += 1
     hashes = {k: hashlib.sha256(v.detach().float().contiguous().numpy().tobytes()).hexdigest() for k, v in w.items()}
-    save_weight_set(args.output, cfg, q, {"source_sha256": json.dumps(hashes), "converter": "r4dxb-convert 0.1",
-                                         "kb_plan": args.kb_plan})
+    extra_meta.update({"source_sha256": json.dumps(hashes), "converter": "r4dxb-convert 0.1", "kb_plan": args.kb_plan})
+    save_weight_set(args.output, cfg, q, extra_meta)
     print(f"wrote {args.output}: {len(q)} tensors, {reused} reused", file=sys.stderr)
     if args.selftest:
         _, back = load_weight_set(args.output)

@@ -137,6 +137,14 @@ class HybridModel:
             if isinstance(t, (TrellisWeight, W4Weight)):
                 self.lin[name] = Linear(t, name)
         # fused [a; b] gate projection per GDN layer
+        # residual-stream rotation: a weight set that carries it runs its layers in the basis x Q (quant/rotation.py)
+        self.rot = None
+        if "rotation.signs" in weights and self.layer_begin is not None:
+            signs = weights["rotation.signs"].to(self.device, torch.float32).contiguous()
+            mix = weights["rotation.mix"].to(self.device, torch.float32).contiguous()
+            if signs.numel() != cfg.hidden_size or mix.dim() != 2 or mix.shape[0] != mix.shape[1] or cfg.hidden_size % mix.shape[0]:
+                raise ValueError("rotation tensors do not fit the model's hidden size")
+            self.rot = (signs, mix)
         self.ab_w: Dict[int, torch.Tensor] = {}
         for i in range(self.layer_begin, self.layer_end):
             if not cfg.is_attention_layer(i) and not cfg.is_conv_layer(i):
@@ -358,6 +366,15 @@ class HybridModel:
         else:
             self.comm.row_parallel_linear(lin, x, b.x[:T], prologue)
 
+    # ---- residual rotation: rows enter the stack through Q and leave it through Q^T -------------------
+    def _enter_stack(self, x: torch.Tensor) -> None:
+        if self.rot is not None and self.layer_begin == 0:
+            K.rotate_residual(x, self.rot[0], self.rot[1], inverse=False)
+
+    def _leave_stack(self, x: torch.Tensor) -> None:
+        if self.rot is not None and self.layer_end == self.cfg.num_hidden_layers:
+            K.rotate_residual(x, self.rot[0], self.rot[1], inverse=True)
+
     # ---- forward --------------------------------------------------------------------------------
     def forward_rows(self, T: int, want_logits: bool = True, skip_embed: bool = False) -> None:
         """Runs the T rows staged in ``buf.ids`` / ``buf.positions``; results in ``buf.logits`` / ``buf.next_ids``.
@@ -365,6 +382,7 @@ class HybridModel:
         cfg, b, w = self.cfg, self.buf, self.w
         if not skip_embed and self.layer_begin == 0:
             K.embed_gather(b.ids[:T], w["text.embed_tokens"], out=b.x[:T])
+            self._enter_stack(b.x[:T])
         for i in range(self.layer_begin, self.layer_end):
             if i in self.capture_layers:
                 self._capture_rows(i, b.x[:T], T)
@@ -376,6 +394,7 @@ class HybridModel:
             else:
                 self._gdn_layer(i, T)
             self._mlp(i, T)
+        self._leave_stack(b.x[:T])
         if want_logits and self.layer_end == cfg.num_hidden_layers:
             K.rmsnorm(b.x[:T], w["text.final_norm"], cfg.rms_norm_eps, out=b.h[:T])
             self.lin["lm_head"](b.h[:T], out=b.logits[:T])
@@ -395,7 +414,10 @@ class HybridModel:
     def _capture_rows(self, layer: int, x: torch.Tensor, T: int) -> None:
         if T > self.captured.shape[1]:
             self.captured = torch.zeros(len(self.capture_layers), T, self.cfg.hidden_size, dtype=BF, device=self.device)
-        self.captured[self.capture_layers.index(layer), :T].copy_(x)
+        dst = self.captured[self.capture_layers.index(layer), :T]
+        dst.copy_(x)
+        if self.rot is not None:              # consumers (drafters) read rows in the un-rotated basis
+            K.rotate_residual(dst, self.rot[0], self.rot[1], inverse=True)
 
     def _stage(self, ids: torch.Tensor, pos0: int) -> int:
         T = ids.numel()
@@ -491,6 +513,7 @@ class HybridModel:
         pos0 = self.pos
         if not skip_embed and self.layer_begin == 0:
             K.embed_gather(cb["ids"][:T], w["text.embed_tokens"], out=x)
+            self._enter_stack(x)
         for i in range(self.layer_begin, self.layer_end):
             p = f"text.layers.{i}."
             if i in self.capture_layers:
@@ -537,6 +560,7 @@ class HybridModel:
             self.lin[pm + "gate_up"].chunk(h, cb["xh"], gu)
             self._row_parallel_chunk(self.lin[pm + "down"], gu, x, cb, fused_silu_mul=True, gelu=(cfg.mlp_act == "gelu_tanh"),
                                      post_norm=w.get(p + "post_mlp_out_norm"))
+        self._leave_stack(x)
         if want_logits and self.layer_end == cfg.num_hidden_layers:
             b = self.buf
             K.rmsnorm(x[T - 1:T], w["text.final_norm"], cfg.rms_norm_eps, out=b.h[:1])
@@ -686,6 +710,7 @@ class HybridModel:
             sel = (pos >= s) & (pos < e)
             if bool(sel.any()):
                 x[pos[sel] - s] = rows[sel]
+            self._enter_stack(x)                 # spliced rows are rotated along with the text rows
             self.forward_chunk(T, want_logits=(e == n), skip_embed=True)
             if hook is not None:
                 hook(s, T, x)

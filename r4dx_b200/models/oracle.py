@@ -268,10 +268,13 @@ class OracleModel:
             x[embed_overrides[0].long()] = embed_overrides[1].float()
         self.image_blocks = list(image_blocks) if image_blocks else None
         captured = {}
+        rot = self._rotation()
+        if rot is not None:                      # rows enter the stack: the stack's basis is x Q
+            x = self._r(rot[0](x.float()))
         for i in range(cfg.num_hidden_layers):
             p = f"text.layers.{i}."
             if capture_layers and i in capture_layers:
-                captured[i] = x.clone()
+                captured[i] = x.clone() if rot is None else self._r(rot[1](x.float()))     # consumers read un-rotated rows
             h = self._r(R.rmsnorm_1pw(x, w[p + "input_layernorm"], cfg.rms_norm_eps))
             if cfg.is_attention_layer(i):
                 a = self.attention(p, i, h, st)
@@ -289,11 +292,22 @@ class OracleModel:
             x = self._r(x + m)
         st.pos += ids.shape[0]
         self.image_blocks = None
+        if rot is not None:                      # rows leave the stack
+            x = self._r(rot[1](x.float()))
         hn = self._r(R.rmsnorm_1pw(x, w["text.final_norm"], cfg.rms_norm_eps))
         logits = self._mm(hn, "lm_head")
         if return_hidden:
             return logits, x, st, captured
         return logits, st
+
+    def _rotation(self):
+        """(x -> x Q, x -> x Q^T) when the weight set carries a residual rotation, else None."""
+        if "rotation.signs" not in self.w:
+            return None
+        from ..quant import rotation as rot
+        signs, mix = self.w["rotation.signs"].float(), self.w["rotation.mix"].float()
+        spec = rot.RotationSpec("q2a", 0, signs.numel(), signs.numel() // mix.shape[0])
+        return (lambda t: rot.apply_q(t, spec, signs, mix)), (lambda t: rot.apply_qt(t, spec, signs, mix))
 
     def mtp_step(self, token: torch.Tensor, hidden: torch.Tensor, st: OracleState) -> tuple:
         """One MTP draft step: x = fc([norm_e(embed(t)), norm_h(h)]) -> attention layer -> norm -> lm_head.

@@ -51,6 +51,9 @@ int r4dxb_vit_attention(const void* qkv, void* out, const int* cu_seqlens, int n
 int r4dxb_w8a16_gemv(const void* wq, const void* ws, const void* x, void* y, int T, int N, int K, int group, int out_f32,
                      void* stream);
 int r4dxb_rotate_rows(void* x, const void* signs, long long T, int H, int mode, void* stream);
+/* Residual-stream rotation in place on bf16 rows [T, H]: x <- x Q (inverse 0) or x Q^T (inverse 1),
+ * Q = diag(signs) . blockdiag(Hadamard_B / sqrt(B)) . (mix (x) I_B); signs fp32 [H], mix fp32 [H/B, H/B], H/B <= 8. */
+int r4dxb_rotate_residual(void* x, const float* signs, const float* mix, long long T, int H, int B, int inverse, void* stream);
 int r4dxb_w4a16_gemv(const void* wq, const void* wsz, const void* x, void* y, int T, int N, int K, int group,
                      int out_f32, void* stream);
 /* y[T,N] (fp32) = x[T,K] (bf16) . W[N,K]^T (bf16): small dense projections (gates, router) */

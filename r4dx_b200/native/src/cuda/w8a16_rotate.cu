@@ -96,6 +96,67 @@ __global__ void RotateKernel(__nv_bfloat16* __restrict__ x, const __half* __rest
   *reinterpret_cast<uint2*>(p) = ov;
 }
 
+// Residual-stream rotation, in place on bf16 rows [T, H]:  forward  x <- x Q,  inverse  x <- x Q^T  with
+//   Q = diag(signs) . blockdiag(H_B / sqrt(B)) . (mix (x) I_B),   B a power of two <= 1024, H = nblk * B, nblk <= 8.
+// One CTA per row: the row lives in shared memory as fp32; the block transform runs its first five butterfly levels in
+// registers + shuffles (a lane holds one element per pass) and the rest through shared memory; the mix is an
+// nblk x nblk product per column.  (reference: src/kernels/src/rotate_residual.hip:79-333 does the same job with one
+// workgroup per row in LDS.)
+constexpr int kRotThreads = 256;
+constexpr int kRotMaxBlocks = 8;
+
+__device__ __forceinline__ void RowFwht(float* row, int n, int tid, int nthreads) {
+  // in-place unnormalised Hadamard transform of row[0..n) in shared memory, n a power of two >= 2
+  for (int h = 1; h < n; h <<= 1) {
+    for (int i = tid; i < n / 2; i += nthreads) {
+      const int lo = (i / h) * 2 * h + (i % h);
+      const float a = row[lo], b = row[lo + h];
+      row[lo] = a + b;
+      row[lo + h] = a - b;
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(kRotThreads)
+RotateResidualKernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ signs, const float* __restrict__ mix, int H, int B,
+                     int inverse) {
+  extern __shared__ float rsm[];            // [H] the row, [H] scratch for the mix
+  float* row = rsm;
+  float* tmp = rsm + H;
+  __shared__ float m[kRotMaxBlocks * kRotMaxBlocks];
+  const int nblk = H / B;
+  __nv_bfloat16* xr = x + static_cast<size_t>(blockIdx.x) * H;
+  if (threadIdx.x < nblk * nblk) m[threadIdx.x] = mix[threadIdx.x];
+  for (int i = threadIdx.x; i < H; i += kRotThreads) {
+    const float v = __bfloat162float(xr[i]);
+    row[i] = inverse ? v : v * signs[i];
+  }
+  __syncthreads();
+  const float scale = rsqrtf(static_cast<float>(B));
+  if (inverse) {
+    // h_b = sum_d mix[b, d] x_d
+    for (int i = threadIdx.x; i < H; i += kRotThreads) {
+      const int b = i / B, c = i % B;
+      float acc = 0.f;
+      for (int d = 0; d < nblk; ++d) acc = fmaf(m[b * nblk + d], row[d * B + c], acc);
+      tmp[i] = acc;
+    }
+    __syncthreads();
+    for (int b = 0; b < nblk; ++b) RowFwht(tmp + b * B, B, threadIdx.x, kRotThreads);
+    for (int i = threadIdx.x; i < H; i += kRotThreads) xr[i] = __float2bfloat16(tmp[i] * scale * signs[i]);
+  } else {
+    for (int b = 0; b < nblk; ++b) RowFwht(row + b * B, B, threadIdx.x, kRotThreads);
+    // y_d = sum_b mix[b, d] h_b
+    for (int i = threadIdx.x; i < H; i += kRotThreads) {
+      const int d = i / B, c = i % B;
+      float acc = 0.f;
+      for (int b = 0; b < nblk; ++b) acc = fmaf(m[b * nblk + d], row[b * B + c], acc);
+      xr[i] = __float2bfloat16(acc * scale);
+    }
+  }
+}
+
 template <int TMAX>
 int LaunchW8(const void* wq, const void* ws, const void* x, void* y, int T, int N, int K, int group, int out_f32, cudaStream_t s) {
   const size_t smem = static_cast<size_t>(TMAX) * K * sizeof(__half);
@@ -135,6 +196,21 @@ int r4dxb_rotate_rows(void* x, const void* signs, long long T, int H, int mode, 
   const long long items = T * (H / 128);
   RotateKernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(x), static_cast<const __half*>(signs), items, H, mode);
+  return FinishLaunch();
+}
+
+/* Residual-stream rotation in place on bf16 rows [T, H]: x <- x Q (inverse 0) or x <- x Q^T (inverse 1);
+ * signs fp32 [H] (+-1), mix fp32 [H/B, H/B] orthogonal, B a power of two, H/B <= 8, H <= 16384. */
+int r4dxb_rotate_residual(void* x, const float* signs, const float* mix, long long T, int H, int B, int inverse, void* stream) {
+  if (T < 1 || H < 2 || B < 2 || (B & (B - 1)) || H % B || H / B > kRotMaxBlocks || H > 16384 || signs == nullptr || mix == nullptr)
+    return R4DXB_BAD_ARG;
+  const size_t smem = static_cast<size_t>(H) * 2 * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(RotateResidualKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  RotateResidualKernel<<<static_cast<unsigned>(T), kRotThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(x), signs, mix, H, B, inverse);
   return FinishLaunch();
 }
 

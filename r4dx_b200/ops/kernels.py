@@ -608,6 +608,19 @@ def trellis_gemv_grouped(words, suh, svh, x, y, offsets, perm, in_div: int, n_pa
     return y
 
 
+register_cuda_sig("r4dxb_rotate_residual", _I, [_P, _P, _P, ctypes.c_longlong, _I, _I, _I, _P])
+
+
+def rotate_residual(x: torch.Tensor, signs: torch.Tensor, mix: torch.Tensor, inverse: bool = False) -> torch.Tensor:
+    """In place on bf16 rows [T, H]: x <- x Q (or x Q^T), the residual-stream rotation of ``quant/rotation.py``."""
+    _req(x, BF, "x")
+    H = x.shape[-1]
+    B = H // mix.shape[0]
+    _check(_lib().r4dxb_rotate_residual(_p(x), _p(signs), _p(mix), x.numel() // H, H, B, 1 if inverse else 0, _stream()),
+           "rotate_residual")
+    return x
+
+
 register_cuda_sig("r4dxb_moe_tiles", _I, [_P, _I, _I, _P, _P, _I, _P])
 register_cuda_sig("r4dxb_trellis_input_grouped", _I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P])
 register_cuda_sig("r4dxb_trellis_gemm_grouped", _I, [_P] * 8 + [_I] * 7 + [_P, _P])

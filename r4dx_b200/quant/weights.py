@@ -78,7 +78,7 @@ def quantize_weight_set(cfg: ModelConfig, w: Dict[str, torch.Tensor], layout: st
                 out[name] = search_w4a16(t, imatrix.get(name), head_group)
             else:
                 out[name] = w4a16.quantize(t, head_group)
-        elif leaf in F32_NAMES:
+        elif leaf in F32_NAMES or name.startswith("rotation."):
             out[name] = t.float()
         else:
             out[name] = t.to(torch.bfloat16)
