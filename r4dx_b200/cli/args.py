@@ -116,8 +116,6 @@ def convert_parser() -> argparse.ArgumentParser:
     ap.add_argument("--rotation-block", type=int, default=0, help="Hadamard block of the rotation (default: up to 1024)")
     ap.add_argument("--rotation-out", default=None, metavar="FILE.safetensors",
                     help="with --rotate and no quantization wanted: write only the rotation tensors and exit")
-    ap.add_argument("--no-bf16", action="store_true", help="quantize the small linears that normally stay bf16 as well "
-                                                           "(GDN a / b projections, routers): an all-w8a16 container")
     ap.add_argument("--vision", default="off", choices=["on", "off"], help="keep the checkpoint's vision tower tensors (bf16)")
     ap.add_argument("--dflash-hf", default=None, metavar="DIR",
                     help="also convert a block-diffusion drafter checkpoint (safetensors + config.json) into <output>.dflash")

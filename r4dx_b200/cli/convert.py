@@ -20,7 +20,9 @@ def _kb_rule(plan: str):
     return {"mix4.5": default_kb_rule, "mix3.3": moe_kb_rule, "kb3": lambda n: 3, "kb4": lambda n: 4, "kb5": lambda n: 5}[plan]
 
 
-def load_source(spec: str, layers: int, mtp: bool, seed: int):
+def load_source(spec: str, layers: int, mtp: bool, seed: int, raw_out=None):
+    """(config, fp32 weights under this engine's names).  ``raw_out``: a dict that receives the checkpoint's own tensors
+    when the source is a Hugging Face directory (the vision tower is imported from them)."""
     from ..config import (ModelConfig, small_hybrid_config, tiny_gemma_config, tiny_hybrid_config, tiny_lfm2_config,
                           tiny_llama_config, tiny_moe_config)
     from ..models.oracle import init_weights
@@ -55,6 +57,8 @@ def load_source(spec: str, layers: int, mtp: bool, seed: int):
         return ModelConfig.from_json(cfg_text), w
     # a Hugging Face checkpoint: read its config.json and rename / reshape the tensors
     from ..quant.hf_import import config_from_hf, import_hf_weights
+    if raw_out is not None:
+        raw_out.update(w)
     cfg = config_from_hf(cfg_text)
     if layers:
         cfg.num_hidden_layers, cfg.layer_types = layers, cfg.layer_types[:layers]
@@ -67,7 +71,8 @@ def main(argv=None) -> int:
     from ..quant.weights import dequantize_weight_set, load_weight_set, quantize_weight_set, save_weight_set
     if args.threads:
         torch.set_num_threads(args.threads)
-    cfg, w = load_source(args.input, args.layers, args.mtp, args.seed)
+    raw = {}
+    cfg, w = load_source(args.input, args.layers, args.mtp, args.seed, raw_out=raw)
     keep = [s for s in args.keep_bf16.split(",") if s]
     layout = args.layouts.split(",")[0]
     src = {k: v for k, v in w.items()}
@@ -95,8 +100,38 @@ def main(argv=None) -> int:
     if args.imatrix:
         from safetensors.torch import load_file
         imatrix = {k: v for k, v in load_file(args.imatrix).items() if v.dim() == 1}
+    imported = {}
+    if args.trellis_from:
+        # already-encoded body linears: taken as they are (checked against the checkpoint), everything else is quantized here
+        from ..quant.weights import import_trellis_dir
+        if args.rotate != "none":
+            raise SystemExit("--trellis-from cannot be combined with --rotate: the imported codes were fitted to the unrotated weights")
+        try:
+            imported, errs = import_trellis_dir(args.trellis_from, src, verify=args.trellis_verify == "full")
+        except (OSError, ValueError) as e:
+            raise SystemExit(f"--trellis-from {args.trellis_from}: {e}")
+        src = {k: v for k, v in src.items() if k not in imported}
+        worst = max(errs.items(), key=lambda kv: kv[1]) if errs else ("", 0.0)
+        extra_meta["trellis_import"] = json.dumps({"dir": os.path.abspath(args.trellis_from), "tensors": len(imported),
+                                                   "verify": args.trellis_verify, "worst": worst[1], "worst_tensor": worst[0]})
+        print(f"imported {len(imported)} trellis tensors from {args.trellis_from} (worst reconstruction error {worst[1]:.4f} at {worst[0]})",
+              file=sys.stderr)
     q = quantize_weight_set(cfg, src, layout=layout, kb_rule=_kb_rule(args.kb_plan), head_group=args.lm_head_group, seed=args.seed,
                             encoder=args.encoder, hessians=hessians, imatrix=imatrix, search=args.quant == "search")
+    q.update(imported)
+    if args.vision == "on":
+        # the tower stays bf16 under "vision."; a random source gets a small random tower of the serving code's test geometry
+        if raw:
+            from ..quant.hf_import import import_hf_vision
+            vw = import_hf_vision(raw)
+            if not vw:
+                raise SystemExit("--vision on: the checkpoint has no visual.* tensors")
+        else:
+            from ..models.vision import VisionConfig, init_vision_weights
+            vw = init_vision_weights(VisionConfig(depth=2, hidden_size=144, num_heads=2, intermediate_size=256, patch_size=8,
+                                                  out_hidden_size=cfg.hidden_size, num_position_embeddings=64), args.seed)
+        for k, v in vw.items():
+            q["vision." + k] = v.to(torch.bfloat16)
     for k in list(q):
         if any(s in k for s in keep):
             q[k] = w[k].to(torch.bfloat16)
@@ -120,6 +155,20 @@ def main(argv=None) -> int:
     extra_meta.update({"source_sha256": json.dumps(hashes), "converter": "r4dxb-convert 0.1", "kb_plan": args.kb_plan})
     save_weight_set(args.output, cfg, q, extra_meta)
     print(f"wrote {args.output}: {len(q)} tensors, {reused} reused", file=sys.stderr)
+    if args.dflash_hf:
+        # the drafter rides next to the container: <output>.dflash holds its config and source weights (quantized at load)
+        from ..models.dflash import save_dflash
+        from ..quant.dflash_hf import import_dflash_hf
+        try:
+            dcfg, dw = import_dflash_hf(args.dflash_hf, w["text.embed_tokens"], cfg.vocab_size)
+        except (KeyError, ValueError) as e:
+            raise SystemExit(f"--dflash-hf {args.dflash_hf}: {e}")
+        if dcfg.hidden != cfg.hidden_size:
+            raise SystemExit(f"--dflash-hf: drafter hidden size {dcfg.hidden} != target hidden size {cfg.hidden_size}")
+        if max(dcfg.target_layers) >= cfg.num_hidden_layers + 1:
+            raise SystemExit(f"--dflash-hf: target layers {dcfg.target_layers} exceed the target's {cfg.num_hidden_layers} layers")
+        save_dflash(args.output + ".dflash", dcfg, dw)
+        print(f"wrote {args.output}.dflash: {dcfg.layers} layers, taps at layers {list(dcfg.target_layers)}", file=sys.stderr)
     if args.selftest:
         _, back = load_weight_set(args.output)
         dq = dequantize_weight_set(back)

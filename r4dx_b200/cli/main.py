@@ -18,7 +18,7 @@ def image_prompt(tm, tk, tpl, messages, files, think: bool):
     from ..runtime import image_prompt as IP
     imgs = [torch.from_numpy(np.asarray(Image.open(f).convert("RGB"), dtype=np.uint8).copy()) for f in files]
     vw = {k[len("vision."):]: v for k, v in getattr(tm.m, "w", {}).items() if isinstance(k, str) and k.startswith("vision.")}
-    vcfg = VisionConfig(out_hidden_size=tm.config.hidden_size)
+    vcfg = VisionConfig.from_weights(vw) if vw else None
     if not vw:                                   # synthetic models get a synthetic tower
         vcfg = VisionConfig(depth=2, hidden_size=144, num_heads=2, intermediate_size=256, patch_size=8,
                             out_hidden_size=tm.config.hidden_size, num_position_embeddings=64, max_pixels=256 * 256)

@@ -35,7 +35,7 @@ def main(argv=None) -> int:
         # the tower's weights ride in the container under "vision."; synthetic models get a synthetic tower
         from ..models.vision import VisionConfig, VisionTower, init_vision_weights
         vw = {k[len("vision."):]: v for k, v in getattr(tm.m, "w", {}).items() if isinstance(k, str) and k.startswith("vision.")}
-        vcfg = VisionConfig(out_hidden_size=tm.config.hidden_size)
+        vcfg = VisionConfig.from_weights(vw) if vw else None
         if not vw:
             vcfg = VisionConfig(depth=2, hidden_size=144, num_heads=2, intermediate_size=256, patch_size=8,
                                 out_hidden_size=tm.config.hidden_size, num_position_embeddings=64, max_pixels=256 * 256)

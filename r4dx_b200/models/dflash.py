@@ -74,7 +74,7 @@ def init_dflash_weights(c: DflashConfig, vocab: int, seed: int = 0) -> Dict[str,
                   p + "wq": n(c.heads * c.head_dim, H), p + "wk": n(c.kv_heads * c.head_dim, H), p + "wv": n(c.kv_heads * c.head_dim, H),
                   p + "wo": n(H, c.heads * c.head_dim), p + "gate_up": n(2 * c.intermediate, H), p + "down": n(H, c.intermediate)})
         for j in range(4):
-            w[p + f"conv{j}.base"] = torch.cat([1 + n(1, G), n(1, G)], 0)
+            w[p + f"conv{j}.base"] = torch.cat([1 + n(1, H), n(1, H)], 0)      # per channel: [tap, H]
             w[p + f"conv{j}.dyn"] = n(2 * G, H, sc=0.02)
     return w
 
@@ -99,7 +99,7 @@ def synthetic_dflash_weights(c: DflashConfig, vocab: int, device="cuda", seed: i
                   p + "wv": big(c.kv_heads * c.head_dim, H, 10 * i + 3), p + "wo": big(H, c.heads * c.head_dim, 10 * i + 4),
                   p + "gate_up": big(2 * c.intermediate, H, 10 * i + 5), p + "down": big(H, c.intermediate, 10 * i + 6)})
         for j in range(4):
-            q[p + f"conv{j}.base"] = torch.cat([1 + n(1, G), n(1, G)], 0).to(BF)
+            q[p + f"conv{j}.base"] = torch.cat([1 + n(1, H), n(1, H)], 0).to(BF)
             q[p + f"conv{j}.dyn"] = n(2 * G, H, sc=0.02).to(BF)
     return q
 
@@ -138,10 +138,12 @@ def _rope_full(x, pos, theta):
 
 
 def _conv_ref(h, base, dyn_w):
-    G = base.shape[1]
+    """Two-tap causal conv over the block's rows: a per-channel base kernel [2, H] plus a per-row dynamic part shared by
+    groups of 16 channels (dyn_w [2G, H], G = H / 16)."""
+    G = dyn_w.shape[0] // 2
     dyn = _r(h @ dyn_w.T)                                   # [T, 2G]
-    a0 = (base[0] + dyn[:, :G]).repeat_interleave(16, -1)
-    a1 = (base[1] + dyn[:, G:]).repeat_interleave(16, -1)
+    a0 = base[0] + dyn[:, :G].repeat_interleave(16, -1)
+    a1 = base[1] + dyn[:, G:].repeat_interleave(16, -1)
     prev = torch.cat([torch.zeros_like(h[:1]), h[:-1]], 0)
     return _r(a0 * h + a1 * prev)
 

@@ -47,6 +47,22 @@ class VisionConfig:
     def head_dim(self) -> int:
         return self.hidden_size // self.num_heads
 
+    @staticmethod
+    def from_weights(w: Dict[str, torch.Tensor], **overrides) -> "VisionConfig":
+        """The geometry a stored tower implies (containers carry the tensors, not a separate vision config): sizes from
+        the tensor shapes, head count from the family's head width of 72 where it divides the hidden size."""
+        H, pd = w["patch_embed.weight"].shape
+        depth = 1 + max(int(k.split(".")[1]) for k in w if k.startswith("blocks."))
+        merged = w["merger.fc1.weight"].shape[0]
+        merge = int(round(math.sqrt(merged // H)))
+        c = VisionConfig()
+        patch = int(round(math.sqrt(pd / (c.in_channels * c.temporal_patch_size))))
+        kw = dict(depth=depth, hidden_size=H, num_heads=(H // 72 if H % 72 == 0 else c.num_heads), intermediate_size=w["blocks.0.fc1.weight"].shape[0],
+                  patch_size=patch, spatial_merge_size=merge, out_hidden_size=w["merger.fc2.weight"].shape[0],
+                  num_position_embeddings=w["pos_embed"].shape[0])
+        kw.update(overrides)
+        return VisionConfig(**kw)
+
     @property
     def patch_dim(self) -> int:
         return self.in_channels * self.temporal_patch_size * self.patch_size * self.patch_size

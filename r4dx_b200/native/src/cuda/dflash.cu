@@ -19,8 +19,9 @@ __global__ void DflashConvKernel(const __nv_bfloat16* __restrict__ h, const __nv
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= H) return;
   const int G = H / 16, g = c / 16;
-  const float a0 = __bfloat162float(base[g]) + __bfloat162float(dyn[static_cast<size_t>(t) * 2 * G + g]);
-  const float a1 = __bfloat162float(base[G + g]) + __bfloat162float(dyn[static_cast<size_t>(t) * 2 * G + G + g]);
+  // base is per channel [2, H]; the dynamic part is shared by the 16 channels of a group
+  const float a0 = __bfloat162float(base[c]) + __bfloat162float(dyn[static_cast<size_t>(t) * 2 * G + g]);
+  const float a1 = __bfloat162float(base[H + c]) + __bfloat162float(dyn[static_cast<size_t>(t) * 2 * G + G + g]);
   float v = a0 * __bfloat162float(h[static_cast<size_t>(t) * H + c]);
   if (t >= 1) v += a1 * __bfloat162float(h[static_cast<size_t>(t - 1) * H + c]);
   out[static_cast<size_t>(t) * H + c] = __float2bfloat16(v);

@@ -306,3 +306,31 @@ def export_hf_weights(cfg: ModelConfig, w: Dict[str, torch.Tensor], prefix: str 
         else:
             split("mlp", m)
     return hf
+
+
+# ---- vision tower -------------------------------------------------------------------------------------------------
+_VISION_RENAMES = (("attn.qkv.", "qkv."), ("attn.proj.", "proj."), ("mlp.linear_fc1.", "fc1."), ("mlp.linear_fc2.", "fc2."),
+                   ("mlp.fc1.", "fc1."), ("mlp.fc2.", "fc2."), ("merger.linear_fc1.", "merger.fc1."), ("merger.linear_fc2.", "merger.fc2."),
+                   ("merger.ln_q.", "merger.norm."), ("patch_embed.proj.", "patch_embed."), ("pos_embed.weight", "pos_embed"))
+
+
+def import_hf_vision(raw: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+    """The vision tower's tensors of a Hugging Face checkpoint under this engine's names (without the ``vision.``
+    prefix the container adds): ``[model.]visual.*`` -> patch_embed / pos_embed / blocks.i.{norm1,qkv,proj,norm2,fc1,fc2} /
+    merger.{norm,fc1,fc2}.  The patch embedding's convolution kernel [hidden, C, t, p, p] becomes a [hidden, C*t*p*p]
+    matrix (patches are flattened in the same order by the preprocessor).
+    (reference: src/convert/ keeps the tower in bf16 with --vision on; docs/vision.md lists the tensors.)"""
+    out: Dict[str, torch.Tensor] = {}
+    for k, v in raw.items():
+        for pre in ("model.visual.", "visual.", "model.vision_tower.", "vision_tower."):
+            if k.startswith(pre):
+                name = k[len(pre):]
+                break
+        else:
+            continue
+        for a, b in _VISION_RENAMES:
+            name = name.replace(a, b)
+        if name == "patch_embed.weight" and v.dim() > 2:
+            v = v.reshape(v.shape[0], -1)
+        out[name] = v
+    return out

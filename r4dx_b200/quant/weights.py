@@ -8,6 +8,7 @@ norms / conv stay bf16 or fp32 -- the same split the reference container uses
 from __future__ import annotations
 
 import json
+import os
 from typing import Callable, Dict, Iterable, Optional, Tuple
 
 import torch
@@ -251,3 +252,70 @@ def load_weight_set(path: str, device="cpu", names: Optional[Callable[[str], boo
         out[name] = ct_get.tensor(name)
     ct.close()
     return cfg, out
+
+
+# ---- pre-encoded trellis tensors ---------------------------------------------------------------------------------
+def export_trellis_dir(q: Dict[str, object], d: str, rel_err: Optional[Dict[str, float]] = None) -> None:
+    """Writes every trellis tensor of ``q`` as <name>.trellis.{words,suh,svh} into ``d``/trellis.safetensors plus a
+    manifest (shape, bit width and, when given, the encoder's relative squared error per tensor): the input of
+    ``convert --trellis-from``."""
+    from safetensors.torch import save_file
+    os.makedirs(d, exist_ok=True)
+    tensors, manifest = {}, {"format": "r4dxb-trellis-1", "tensors": {}}
+    for name, t in q.items():
+        if isinstance(t, TrellisWeight):
+            tensors[name + ".trellis.words"] = t.words.cpu().contiguous()
+            tensors[name + ".trellis.suh"] = t.suh.cpu().contiguous()
+            tensors[name + ".trellis.svh"] = t.svh.cpu().contiguous()
+            manifest["tensors"][name] = {"N": t.N, "K": t.K, "kb": t.kb}
+            if rel_err and name in rel_err:
+                manifest["tensors"][name]["rel_err"] = float(rel_err[name])
+    save_file(tensors, os.path.join(d, "trellis.safetensors"))
+    with open(os.path.join(d, "trellis_manifest.json"), "w") as f:
+        json.dump(manifest, f, indent=1)
+
+
+def import_trellis_dir(d: str, w: Dict[str, torch.Tensor], verify: bool = True) -> Tuple[Dict[str, TrellisWeight], Dict[str, float]]:
+    """Trellis tensors written by ``export_trellis_dir`` (or any tool that writes the same names in this engine's tile
+    order), checked against the fp32 checkpoint ``w``: shape and bit width must fit, and with ``verify`` every tensor is
+    reconstructed on the CPU and its relative squared error must stay within the encoder's range for its bit width
+    (6 * 4^-kb) and, where the manifest records the encoder's own error, within 2 % + 1e-4 of that record.
+    Returns (name -> weight, name -> measured error).  (reference: src/convert/trellis_import.hpp does the same gate for its
+    imported tensors: reconstruct from the file's bytes, compare with the recorded error.)"""
+    from safetensors import safe_open
+    man = json.load(open(os.path.join(d, "trellis_manifest.json")))
+    if man.get("format") != "r4dxb-trellis-1":
+        raise ValueError(f"unknown trellis manifest format {man.get('format')!r}")
+    raw = {}
+    for f in sorted(os.listdir(d)):
+        if f.endswith(".safetensors"):
+            with safe_open(os.path.join(d, f), "pt") as sf:
+                for k in sf.keys():
+                    raw[k] = sf.get_tensor(k)
+    out, errs = {}, {}
+    for name, rec in man["tensors"].items():
+        if name not in w:
+            raise ValueError(f"{name}: not a tensor of this checkpoint")
+        N, K_, kb = int(rec["N"]), int(rec["K"]), int(rec["kb"])
+        if tuple(w[name].shape) != (N, K_):
+            raise ValueError(f"{name}: manifest shape {(N, K_)} != checkpoint shape {tuple(w[name].shape)}")
+        if kb not in (3, 4, 5):
+            raise ValueError(f"{name}: bit width {kb} is not 3, 4 or 5")
+        try:
+            words, suh, svh = raw[name + ".trellis.words"], raw[name + ".trellis.suh"], raw[name + ".trellis.svh"]
+        except KeyError as e:
+            raise ValueError(f"{name}: missing {e.args[0]}")
+        if words.numel() != trellis.packed_words(N, K_, kb) or suh.numel() != K_ or svh.numel() != N:
+            raise ValueError(f"{name}: tensor sizes do not match N={N}, K={K_}, kb={kb}")
+        tw = TrellisWeight(words.to(torch.int32).contiguous(), suh.to(torch.float16).contiguous(), svh.to(torch.float16).contiguous(), N, K_, kb)
+        if verify:
+            ref = w[name].float()
+            rel = float(((trellis.reconstruct(tw) - ref) ** 2).sum() / (ref ** 2).sum().clamp_min(1e-30))
+            errs[name] = rel
+            if rel > 6.0 * 4.0 ** (-kb):
+                raise ValueError(f"{name}: reconstruction error {rel:.4f} is outside the range of a {kb}-bit encoding of this tensor")
+            rec_err = rec.get("rel_err")
+            if rec_err is not None and abs(rel - rec_err) > 0.02 * rec_err + 1e-4:
+                raise ValueError(f"{name}: reconstruction error {rel:.5f} differs from the recorded {rec_err:.5f}")
+        out[name] = tw
+    return out, errs

@@ -1,4 +1,5 @@
 """Argument parsers and the converter round trip (CPU)."""
+import pytest
 import torch
 
 from r4dx_b200.cli.args import cli_parser, convert_parser, server_parser
@@ -52,3 +53,83 @@ def test_converter_builds_a_tiny_model_of_every_family(tmp_path):
     cfg, w = load_weight_set(str(tmp_path / "lfm2.r4dxb"))
     assert cfg.arch == "lfm2_moe" and cfg.moe_router == "sigmoid" and cfg.layer_types == ["conv", "conv"]
     assert "text.layers.1.moe.expert_bias" in w and w["text.layers.1.moe.expert_bias"].dtype.is_floating_point
+
+
+def test_converter_imports_encoded_trellis_tensors_and_rejects_wrong_ones(tmp_path):
+    """--trellis-from: tensors encoded elsewhere are taken as they are after a CPU reconstruction check."""
+    import json
+    import torch
+    from r4dx_b200.cli.convert import load_source, main as convert
+    from r4dx_b200.quant.weights import export_trellis_dir, load_weight_set, quantize_weight_set
+    from r4dx_b200.quant.trellis import TrellisWeight
+    cfg, w = load_source("random:tiny", 0, False, 0)
+    q = quantize_weight_set(cfg, w, kb_rule=lambda n: 4)
+    body = {k: v for k, v in q.items() if isinstance(v, TrellisWeight) and ".layers.0." in k}
+    d = str(tmp_path / "enc")
+    export_trellis_dir(body, d)
+    out = str(tmp_path / "m.r4dxb")
+    assert convert(["--input", "random:tiny", "--output", out, "--trellis-from", d, "--kb-plan", "kb5"]) == 0
+    _, back = load_weight_set(out)
+    for k, v in body.items():
+        assert back[k].kb == 4 and torch.equal(back[k].words, v.words)          # imported, not re-encoded at 5 bits
+    other = next(k for k, v in back.items() if isinstance(v, TrellisWeight) and ".layers.1." in k)
+    assert back[other].kb == 5
+    # a tensor whose codes belong to other weights fails the reconstruction check
+    name = next(iter(body))
+    bad = dict(body)
+    bad[name] = TrellisWeight(torch.roll(body[name].words, 17), body[name].suh, body[name].svh, body[name].N, body[name].K, 4)
+    d2 = str(tmp_path / "bad")
+    export_trellis_dir(bad, d2)
+    with pytest.raises(SystemExit) as e:
+        convert(["--input", "random:tiny", "--output", str(tmp_path / "x.r4dxb"), "--trellis-from", d2])
+    assert "reconstruction error" in str(e.value)
+    man = json.load(open(d + "/trellis_manifest.json"))
+    assert man["format"] == "r4dxb-trellis-1" and name in man["tensors"]
+
+
+def test_converter_keeps_a_vision_tower_and_imports_a_drafter(tmp_path):
+    import json
+    import torch
+    from safetensors.torch import save_file
+    from r4dx_b200.cli.convert import main as convert
+    from r4dx_b200.models.dflash import load_dflash
+    from r4dx_b200.models.vision import VisionConfig
+    from r4dx_b200.quant.hf_import import import_hf_vision
+    from r4dx_b200.quant.weights import load_weight_set
+    # a second-generation drafter checkpoint in the Hugging Face naming, geometry matched to the tiny target (hidden 256)
+    H, G, L, V, R, I = 256, 16, 2, 4096, 8, 512
+    g = torch.Generator().manual_seed(0)
+    n = lambda *s: torch.randn(*s, generator=g) * 0.05
+    t = {"fc.weight": n(H, 2 * H), "hidden_norm.weight": 1 + n(H), "norm.weight": 1 + n(H),
+         "candidate_selector.hidden_projection.weight": n(R, H), "candidate_selector.predecessor_codebook": n(V, R),
+         "candidate_selector.successor_codebook": n(V, R)}
+    for i in range(L):
+        p = f"layers.{i}."
+        t.update({p + "input_layernorm.weight": 1 + n(H), p + "post_attention_layernorm.weight": 1 + n(H),
+                  p + "self_attn.q_proj.weight": n(4 * 64, H), p + "self_attn.k_proj.weight": n(2 * 64, H), p + "self_attn.v_proj.weight": n(2 * 64, H),
+                  p + "self_attn.o_proj.weight": n(H, 4 * 64), p + "self_attn.q_norm.weight": 1 + n(64), p + "self_attn.k_norm.weight": 1 + n(64),
+                  p + "mlp.gate_proj.weight": n(I, H), p + "mlp.up_proj.weight": n(I, H), p + "mlp.down_proj.weight": n(H, I)})
+        for mod in ("attention_conv", "mlp_conv"):
+            t[p + mod + ".base_kernel"] = n(2, 2, H)
+            t[p + mod + ".kernel_projection.weight"] = n(4 * G, H)
+    d = tmp_path / "drafter"
+    d.mkdir()
+    save_file({("model." + k): v.contiguous() for k, v in t.items()}, str(d / "model.safetensors"))
+    json.dump({"hidden_size": H, "num_hidden_layers": L, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+               "intermediate_size": I, "rope_theta": 1e6, "rms_norm_eps": 1e-6, "sliding_window": 48,
+               "dflash_config": {"target_layer_ids": [0, 2], "mask_token_id": 3, "block_size": 8}}, open(d / "config.json", "w"))
+    out = str(tmp_path / "m.r4dxb")
+    assert convert(["--input", "random:tiny", "--output", out, "--layouts", "bf16", "--vision", "on", "--dflash-hf", str(d)]) == 0
+    cfg, q = load_weight_set(out)
+    vw = {k[len("vision."):]: v for k, v in q.items() if k.startswith("vision.")}
+    vc = VisionConfig.from_weights(vw)
+    assert (vc.depth, vc.hidden_size, vc.num_heads, vc.patch_size, vc.out_hidden_size) == (2, 144, 2, 8, cfg.hidden_size)
+    dc, dq = load_dflash(out + ".dflash")
+    assert dc.target_layers == (1, 3) and dc.block == 8 and dc.mask_token_id == 3 and dc.rank == R
+    assert tuple(dq["layers.1.conv2.base"].shape) == (2, H) and tuple(dq["layers.1.conv3.dyn"].shape) == (2 * G, H)
+    assert torch.allclose(dq["layers.0.conv1.base"].float(), t["layers.0.attention_conv.base_kernel"][1].to(torch.bfloat16).float())
+    assert tuple(dq["layers.0.gate_up"].wq.shape)[0] == 2 * I
+    # Hugging Face vision names map onto the tower's names, the patch kernel is flattened
+    hv = import_hf_vision({"model.visual.patch_embed.proj.weight": torch.zeros(144, 3, 2, 8, 8), "model.visual.blocks.0.attn.qkv.bias": torch.zeros(432),
+                           "model.visual.merger.linear_fc2.weight": torch.zeros(256, 576), "model.language_model.x": torch.zeros(1)})
+    assert set(hv) == {"patch_embed.weight", "blocks.0.qkv.bias", "merger.fc2.weight"} and hv["patch_embed.weight"].shape == (144, 384)
