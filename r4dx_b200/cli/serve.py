@@ -35,12 +35,20 @@ def main(argv=None) -> int:
         # the tower's weights ride in the container under "vision."; synthetic models get a synthetic tower
         from ..models.vision import VisionConfig, VisionTower, init_vision_weights
         vw = {k[len("vision."):]: v for k, v in getattr(tm.m, "w", {}).items() if isinstance(k, str) and k.startswith("vision.")}
-        vcfg = VisionConfig.from_weights(vw) if vw else None
-        if not vw:
+        if tm.config.arch == "gemma":
+            # encoder-free embedder of this family: the front object sizes the images and marks their rows as blocks
+            from ..models.gemma_vision import GemmaVisionFront, random_embedder_weights
+            vision = (GemmaVisionFront.from_container_tensors(vw, str(tm.m.device)) if vw
+                      else GemmaVisionFront(random_embedder_weights(tm.config.hidden_size), str(tm.m.device)))
+            vcfg, vw = vision, None
+        else:
+            vcfg = VisionConfig.from_weights(vw) if vw else None
+        if vision is None and not vw:
             vcfg = VisionConfig(depth=2, hidden_size=144, num_heads=2, intermediate_size=256, patch_size=8,
                                 out_hidden_size=tm.config.hidden_size, num_position_embeddings=64, max_pixels=256 * 256)
             vw = init_vision_weights(vcfg, 0)
-        vision = VisionTower(vcfg, vw, device=str(tm.m.device))
+        if vision is None:
+            vision = VisionTower(vcfg, vw, device=str(tm.m.device))
         image_id = getattr(tk, "image_pad_id", tm.config.vocab_size - 1)
         eng.vision = vision
     from ..server.parsers import select_dialect

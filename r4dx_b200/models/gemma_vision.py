@@ -182,3 +182,78 @@ def embed_reference(pixels: torch.Tensor, positions: torch.Tensor, w: GemmaEmbed
     h = _layer_norm(h, f(w.pos_norm_w), f(w.pos_norm_b), w.eps)
     h = _bf(h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + w.eps))
     return _bf(h @ f(w.proj_w).T)
+
+
+class GemmaEmbedder:
+    """Device half of the encoder-free embedder: the chain of ``embed_reference`` with the two products on the
+    tensor-core linear (bias fused) and the norms on the LayerNorm / RMSNorm kernels; the positional rows are two table
+    gathers.  Rows come back in bf16, ready to override the image placeholders' embeddings.
+    (reference: src/vision/gemma_vision.cpp runs the same chain on its GEMM library.)"""
+
+    def __init__(self, w: GemmaEmbedderWeights, device="cuda"):
+        BF = torch.bfloat16
+        d = torch.device(device)
+        t = lambda x: x.to(d, BF).contiguous()
+        self.eps, self.device = w.eps, d
+        self.ln1_w, self.ln1_b, self.ln2_w, self.ln2_b = t(w.ln1_w), t(w.ln1_b), t(w.ln2_w), t(w.ln2_b)
+        self.dense_w, self.dense_b, self.proj_w = t(w.dense_w), t(w.dense_b), t(w.proj_w)
+        self.pos_embedding, self.pos_norm_w, self.pos_norm_b = t(w.pos_embedding), t(w.pos_norm_w), t(w.pos_norm_b)
+        self.ones = torch.ones(w.proj_w.shape[1], dtype=BF, device=d)
+
+    def embed(self, pixels: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        from ..ops import kernels as K
+        BF = torch.bfloat16
+        x = pixels.to(self.device, BF).contiguous()
+        pos = positions.to(self.device, torch.long)
+        h = K.layernorm(x, self.ln1_w, self.ln1_b, self.eps)
+        h = K.linear_tc(self.dense_w, h, bias=self.dense_b)
+        h = K.layernorm(h, self.ln2_w, self.ln2_b, self.eps)
+        pe = (self.pos_embedding[pos[:, 0], 0].float() + self.pos_embedding[pos[:, 1], 1].float()).to(BF)
+        h = K.residual_add(h, pe)
+        h = K.layernorm(h, self.pos_norm_w, self.pos_norm_b, self.eps)
+        h = K.rmsnorm(h, self.ones, self.eps, zero_centered=False)
+        return K.linear_tc(self.proj_w, h)
+
+
+EMBEDDER_FIELDS = ("ln1_w", "ln1_b", "dense_w", "dense_b", "ln2_w", "ln2_b", "pos_embedding", "pos_norm_w", "pos_norm_b", "proj_w")
+
+
+def random_embedder_weights(out_dim: int, mm_dim: int = 256, posemb: int = 64, seed: int = 0) -> GemmaEmbedderWeights:
+    """A random embedder for synthetic models and tests."""
+    g = torch.Generator().manual_seed(seed)
+    n = lambda *s: torch.randn(*s, generator=g) * 0.05
+    return GemmaEmbedderWeights(1 + n(PATCH_DIM), n(PATCH_DIM), n(mm_dim, PATCH_DIM), n(mm_dim), 1 + n(mm_dim), n(mm_dim),
+                                n(posemb, 2, mm_dim), 1 + n(mm_dim), n(mm_dim), n(out_dim, mm_dim))
+
+
+class GemmaVisionFront:
+    """What the serving layer needs of this family's image path: how many soft tokens an image takes, the rows for a list
+    of images, and the fact that image rows form bidirectional blocks (the engine then passes the blocks to the prefill).
+    Weights ride in the container as ``vision.embedder.<field>``."""
+
+    bidirectional_blocks = True
+
+    def __init__(self, w: GemmaEmbedderWeights, device="cuda", max_soft_tokens: int = 280):
+        self.embedder = GemmaEmbedder(w, device)
+        self.max_soft_tokens = max_soft_tokens
+        self.posemb = w.pos_embedding.shape[0]
+
+    @staticmethod
+    def from_container_tensors(vw: dict, device="cuda") -> "GemmaVisionFront":
+        missing = [f for f in EMBEDDER_FIELDS if "embedder." + f not in vw]
+        if missing:
+            raise ValueError(f"the container's vision tensors lack embedder.{missing[0]}")
+        return GemmaVisionFront(GemmaEmbedderWeights(*[vw["embedder." + f].float() for f in EMBEDDER_FIELDS]), device)
+
+    def token_count(self, img: torch.Tensor) -> int:
+        h, w = target_size(int(img.shape[0]), int(img.shape[1]), self.max_soft_tokens)
+        return (h // SIDE) * (w // SIDE)
+
+    def encode_images(self, images) -> torch.Tensor:
+        rows = []
+        for img in images:
+            px, pos, (gh, gw) = preprocess(img, self.max_soft_tokens)
+            if max(gh, gw) > self.posemb:
+                raise ValueError(f"image grid {gh}x{gw} exceeds the positional table ({self.posemb})")
+            rows.append(self.embedder.embed(px, pos))
+        return torch.cat(rows, 0)

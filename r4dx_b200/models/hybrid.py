@@ -366,6 +366,8 @@ class HybridModel:
         else:
             self.comm.row_parallel_linear(lin, x, b.x[:T], prologue)
 
+    _key_limit = None      # per-row key limits of the chunk being prefilled (image blocks on sliding-window layers)
+
     # ---- residual rotation: rows enter the stack through Q and leave it through Q^T -------------------
     def _enter_stack(self, x: torch.Tensor) -> None:
         if self.rot is not None and self.layer_begin == 0:
@@ -529,8 +531,10 @@ class HybridModel:
                                cb["positions"], self.block_table, q, self.kv[i], T, Hq, Hkv, D, cfg.rotary_dim,
                                cfg.layer_theta(i), cfg.rms_norm_eps, q_stride=cfg.q_proj_dim // Hq)
                 core = cb["core"][:T * cfg.q_dim].view(T, cfg.q_dim)
+                win = cfg.layer_window(i)
                 K.attn_prefill(q, qg, self.kv[i], self.block_table, w[pa + "k_descale"], w[pa + "v_descale"], core, T,
-                               Hq, Hkv, D, pos0, cfg.attn_output_gate, window=cfg.layer_window(i))
+                               Hq, Hkv, D, pos0, cfg.attn_output_gate, window=win,
+                               key_limit=self._key_limit if win > 0 else None)
                 self._row_parallel_chunk(self.lin[pa + "o"], core, x, cb, post_norm=w.get(p + "post_attn_out_norm"))
             elif cfg.is_conv_layer(i):
                 pc = p + "conv."
@@ -645,15 +649,17 @@ class HybridModel:
         amortise launches and tile tails better with 4096 rows (32k: 3.54 s vs 3.88 s)."""
         return 1536 if n <= 12288 else 4096
 
-    def prefill(self, ids: torch.Tensor, chunk: Optional[int] = None, hook=None, embed_overrides=None) -> int:
+    def prefill(self, ids: torch.Tensor, chunk: Optional[int] = None, hook=None, embed_overrides=None, image_blocks=None) -> int:
         """Cold or warm prefill of ``ids`` at the current position; returns the greedy next token.
         ``hook(start, T, hidden_rows)`` is called after every chunk with the final hidden states of its rows
-        (drafters keep their own caches in lock-step with it)."""
+        (drafters keep their own caches in lock-step with it).  ``image_blocks``: [start, end) runs of image rows
+        (indices into ``ids``) that attend to each other in both directions on sliding-window layers; chunks never
+        cut such a block."""
         ids = ids.to(torch.int32)
         n = ids.numel()
         chunk = chunk or self.auto_chunk(n)
-        if embed_overrides is not None:
-            return self._prefill_with_embeds(ids, chunk, hook, embed_overrides)
+        if embed_overrides is not None or image_blocks:
+            return self._prefill_with_embeds(ids, chunk, hook, embed_overrides, image_blocks)
         if n <= MAX_ROWS:
             tok = self.prefill_small(ids)
             if hook is not None:
@@ -687,22 +693,40 @@ class HybridModel:
             return self._read_token((n - 1) % step)
         return self._read_token(0)
 
-    def _prefill_with_embeds(self, ids: torch.Tensor, chunk: int, hook, overrides) -> int:
+    def _prefill_with_embeds(self, ids: torch.Tensor, chunk: int, hook, overrides, image_blocks=None) -> int:
         """Prefill in which some rows' input embeddings come from outside (image tokens): ``overrides`` =
         (positions int64 [M] relative to ``ids``, rows bf16 [M, H]).  Always runs the chunk path
-        (reference: src/model/model.cpp:2062-2113 injects vision embeddings the same way)."""
-        pos, rows = overrides
-        pos = pos.to(self.device, torch.long)
-        rows = rows.to(self.device, BF)
+        (reference: src/model/model.cpp:2062-2113 injects vision embeddings the same way).  With ``image_blocks`` the
+        chunks are planned so that no block is cut, and the sliding-window layers get a per-row key limit: a row of a block
+        sees its whole block (reference: src/vision/gemma_vision.cpp plans chunks and masks the same way)."""
         n = ids.numel()
+        if overrides is not None:
+            pos, rows = overrides
+            pos = pos.to(self.device, torch.long)
+            rows = rows.to(self.device, BF)
+        else:
+            pos, rows = torch.zeros(0, dtype=torch.long, device=self.device), None
         if self.pos + n > self.max_ctx:
             raise ValueError("context overflow")
         self.commit_pending()
-        cb = self._chunk_buffers(max(MAX_ROWS + 1, min(chunk, n)))
+        blocks = [(int(a), int(b)) for a, b in (image_blocks or [])]
+        if blocks:
+            from .gemma_vision import key_limit_ext, plan_prefill_chunks
+            plan = plan_prefill_chunks(n, blocks, max(MAX_ROWS + 1, min(chunk, n)))
+            base = self.pos
+        else:
+            plan = None
+        cb = self._chunk_buffers(max([MAX_ROWS + 1, min(chunk, n)] + ([t for _, t in plan] if plan else [])))
         s = 0
+        ci = 0
         while s < n:
-            e = min(n, s + cb["C"])
+            e = min(n, s + cb["C"]) if plan is None else s + plan[ci][1]
+            ci += 1
             T = e - s
+            if blocks:
+                lim = key_limit_ext(s, T, blocks)
+                lim = torch.where(lim >= 0, lim + base, lim)         # absolute key positions
+                self._key_limit = lim.to(self.device) if bool((lim >= 0).any()) else None
             cb["ids"][:T].copy_(ids[s:e].to(self.device), non_blocking=True)
             cb["positions"][:T].copy_(torch.arange(self.pos, self.pos + T, dtype=torch.int32, device=self.device))
             x = cb["x"][:T]
@@ -711,7 +735,10 @@ class HybridModel:
             if bool(sel.any()):
                 x[pos[sel] - s] = rows[sel]
             self._enter_stack(x)                 # spliced rows are rotated along with the text rows
-            self.forward_chunk(T, want_logits=(e == n), skip_embed=True)
+            try:
+                self.forward_chunk(T, want_logits=(e == n), skip_embed=True)
+            finally:
+                self._key_limit = None
             if hook is not None:
                 hook(s, T, x)
             s = e

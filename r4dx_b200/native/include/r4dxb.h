@@ -169,6 +169,11 @@ int r4dxb_gdn_prefill(const void* mixed, const void* z, const float* ab, const v
                       void* stream);
 long long r4dxb_gdn_chunk_ws_floats(int T, int H);
 /* causal GQA attention of T query rows at positions pos0.. over the paged fp8 cache (rows already written) */
+/* The same with per-row key limits: key_limit [T] int32 (-1 = none) lets row t also see keys up to that absolute position,
+ * which must belong to this call (rows of an image block attend to the whole block on sliding-window layers). */
+int r4dxb_attn_prefill_ex(const void* q, const void* qg, const void* cache, const int* block_table, const float* k_descale,
+                          const float* v_descale, void* out, int T, int Hq, int Hkv, int D, int pos0, int flags,
+                          const int* key_limit, void* stream);
 int r4dxb_attn_prefill(const void* q, const void* qg, const void* cache, const int* block_table, const float* k_descale,
                        const float* v_descale, void* out, int T, int Hq, int Hkv, int D, int pos0, int gated, void* stream);
 

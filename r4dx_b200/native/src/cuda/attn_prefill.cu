@@ -59,6 +59,8 @@ struct PrefillArgs {
   __nv_bfloat16* out;          // [T, Hq, D]
   int T, Hq, Hkv, pos0, gated;
   int window;                  // sliding-window length in tokens (0: causal over the whole sequence)
+  const int* key_limit;        // optional [T]: a row also sees keys up to this absolute position (-1: none), for rows of an
+                               // image block that attend to the whole block; the block's keys are part of the same call
 };
 
 template <int D, int WARPS>
@@ -99,7 +101,14 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 6 ? 2 : 1)) AttnPrefillK
 #pragma unroll
   for (int n = 0; n < D / 8; ++n) { O[n][0] = O[n][1] = O[n][2] = O[n][3] = 0.f; }
 
-  const int last_pos = a.pos0 + min(a.T, t_base + kQTile) - 1;
+  int last_pos = a.pos0 + min(a.T, t_base + kQTile) - 1;
+  int lim0 = pos_r0, lim1 = pos_r1;               // last visible key of this lane's two rows
+  if (a.key_limit != nullptr) {
+    if (t_base + g < a.T) lim0 = max(lim0, a.key_limit[t_base + g]);
+    if (t_base + g + 8 < a.T) lim1 = max(lim1, a.key_limit[t_base + g + 8]);
+    for (int i = 0; i < kQTile && t_base + i < a.T; ++i) last_pos = max(last_pos, a.key_limit[t_base + i]);
+    last_pos = min(last_pos, a.pos0 + a.T - 1);
+  }
   const int key_tiles = last_pos / kKeyTile + 1;
   auto fetch = [&](int kt) {      // raw fp8 rows of key tile kt -> shared memory (16-byte pieces, zero past the end)
     for (int i = threadIdx.x; i < 2 * kKeyTile * (D / 16); i += nthreads) {
@@ -176,10 +185,10 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 6 ? 2 : 1)) AttnPrefillK
       for (int n = 0; n < kKeyTile / 8; ++n) {
         const int kp = kt * kKeyTile + n * 8 + tq * 2;
         const int w0 = a.window > 0 ? pos_r0 - a.window : -1, w1 = a.window > 0 ? pos_r1 - a.window : -1;
-        S[n][0] = (kp <= pos_r0 && kp > w0) ? S[n][0] * sm_scale : -INFINITY;
-        S[n][1] = (kp + 1 <= pos_r0 && kp + 1 > w0) ? S[n][1] * sm_scale : -INFINITY;
-        S[n][2] = (kp <= pos_r1 && kp > w1) ? S[n][2] * sm_scale : -INFINITY;
-        S[n][3] = (kp + 1 <= pos_r1 && kp + 1 > w1) ? S[n][3] * sm_scale : -INFINITY;
+        S[n][0] = (kp <= lim0 && kp > w0) ? S[n][0] * sm_scale : -INFINITY;
+        S[n][1] = (kp + 1 <= lim0 && kp + 1 > w0) ? S[n][1] * sm_scale : -INFINITY;
+        S[n][2] = (kp <= lim1 && kp > w1) ? S[n][2] * sm_scale : -INFINITY;
+        S[n][3] = (kp + 1 <= lim1 && kp + 1 > w1) ? S[n][3] * sm_scale : -INFINITY;
         mx0 = fmaxf(mx0, fmaxf(S[n][0], S[n][1]));
         mx1 = fmaxf(mx1, fmaxf(S[n][2], S[n][3]));
       }
@@ -261,9 +270,10 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS <= 6 ? 2 : 1)) AttnPrefillK
 
 using namespace r4dxb;
 
-extern "C" int r4dxb_attn_prefill(const void* q, const void* qg, const void* cache, const int* block_table,
-                                  const float* k_descale, const float* v_descale, void* out, int T, int Hq, int Hkv, int D,
-                                  int pos0, int flags, void* stream) {
+/* key_limit (optional, [T] int32, -1 = none): row t also attends to keys up to that absolute position (image blocks). */
+extern "C" int r4dxb_attn_prefill_ex(const void* q, const void* qg, const void* cache, const int* block_table,
+                                     const float* k_descale, const float* v_descale, void* out, int T, int Hq, int Hkv, int D,
+                                     int pos0, int flags, const int* key_limit, void* stream) {
   const int gated = flags & 1;      // bit 0: sigmoid output gate; bits 1..: sliding-window length (0 = none)
   if (T < 1 || Hq % Hkv || (D != 256 && D != 64 && D != 128)) return R4DXB_BAD_ARG;
   const int gqa = Hq / Hkv;
@@ -277,6 +287,7 @@ extern "C" int r4dxb_attn_prefill(const void* q, const void* qg, const void* cac
   a.v_descale = v_descale;
   a.out = static_cast<__nv_bfloat16*>(out);
   a.T = T; a.Hq = Hq; a.Hkv = Hkv; a.pos0 = pos0; a.gated = gated; a.window = flags >> 1;
+  a.key_limit = key_limit;
   const int warps = gqa <= 2 ? 2 : (gqa <= 4 ? 4 : (gqa <= 6 ? 6 : 8));   // idle warps still help the tile conversion
   const size_t smem = static_cast<size_t>(gqa * kQTile + 2 * kKeyTile) * (D + 8) * 2 + 2 * kKeyTile * D;
   dim3 grid((T + kQTile - 1) / kQTile, Hkv);
@@ -295,4 +306,10 @@ extern "C" int r4dxb_attn_prefill(const void* q, const void* qg, const void* cac
 #undef R4DXB_ATTN_CASE
   if (rc) return rc;
   return FinishLaunch();
+}
+
+extern "C" int r4dxb_attn_prefill(const void* q, const void* qg, const void* cache, const int* block_table,
+                                  const float* k_descale, const float* v_descale, void* out, int T, int Hq, int Hkv, int D,
+                                  int pos0, int flags, void* stream) {
+  return r4dxb_attn_prefill_ex(q, qg, cache, block_table, k_descale, v_descale, out, T, Hq, Hkv, D, pos0, flags, nullptr, stream);
 }

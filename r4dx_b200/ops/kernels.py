@@ -534,8 +534,18 @@ def set_attn_prefill_impl(name: str) -> None:
     ATTN_PREFILL_IMPL = name
 
 
+register_cuda_sig("r4dxb_attn_prefill_ex", _I, [_P] * 7 + [_I, _I, _I, _I, _I, _I, _P, _P])
+
+
 def attn_prefill(q, qg, cache, block_table, k_descale, v_descale, out, T: int, Hq: int, Hkv: int, D: int, pos0: int,
-                 gated: bool = True, window: int = 0):
+                 gated: bool = True, window: int = 0, key_limit: Optional[torch.Tensor] = None):
+    """``key_limit`` ([T] int32, -1 = none): row t also sees keys up to that absolute position (rows of an image block
+    attend to their whole block); such calls take the mma.sync kernel, which carries the per-row limit."""
+    if key_limit is not None:
+        _check(_lib().r4dxb_attn_prefill_ex(_p(q), _p(qg), _p(cache), _p(block_table), _p(k_descale), _p(v_descale), _p(out),
+                                            T, Hq, Hkv, D, pos0, (1 if gated else 0) | (window << 1), _p(key_limit), _stream()),
+               "attn_prefill_ex")
+        return out
     if ATTN_PREFILL_IMPL == "tc" and D in (128, 256):
         _check(_lib().r4dxb_attn_prefill_tc(_p(q), _p(qg), _p(cache), _p(block_table), _p(k_descale), _p(v_descale), _p(out),
                                             T, Hq, Hkv, D, pos0, (1 if gated else 0) | (window << 1),

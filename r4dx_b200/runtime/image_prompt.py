@@ -68,6 +68,8 @@ def decode_image(url: str) -> torch.Tensor:
 
 
 def image_token_count(img: torch.Tensor, vcfg) -> int:
+    if hasattr(vcfg, "token_count"):           # families with their own sizing rule (soft-token budgets)
+        return int(vcfg.token_count(img))
     from ..models.vision import smart_resize
     f = vcfg.patch_size * vcfg.spatial_merge_size
     h, w = smart_resize(int(img.shape[0]), int(img.shape[1]), f, vcfg.min_pixels, vcfg.max_pixels)

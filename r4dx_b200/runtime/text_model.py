@@ -147,11 +147,14 @@ class LocalTextModel(TextModel):
     def has_checkpoint(self) -> bool:
         return self._ck is not None
 
-    def prefill(self, ids: Sequence[int], embed_overrides=None) -> int:
+    def prefill(self, ids: Sequence[int], embed_overrides=None, image_blocks=None) -> int:
+        """``image_blocks``: [start, end) runs of image rows that attend to each other in both directions on sliding-window
+        layers (the Gemma-style family); the chunk plan never cuts one."""
         self._graph_active = False
         t = torch.as_tensor(list(ids), dtype=torch.int32)
         hook = self.drafter.prefill_hook(t) if self.drafter is not None else None
-        tok = self.m.prefill(t, chunk=self.prefill_chunk or None, hook=hook, embed_overrides=embed_overrides)
+        kw = {"image_blocks": image_blocks} if image_blocks else {}
+        tok = self.m.prefill(t, chunk=self.prefill_chunk or None, hook=hook, embed_overrides=embed_overrides, **kw)
         if self.drafter is not None:
             self.drafter.after_prefill(t, tok)
         return tok
@@ -254,9 +257,10 @@ class FakeTextModel(TextModel):
         g = torch.Generator().manual_seed(int.from_bytes(h[:8], "little") % (2**63))
         return torch.randn(self.vocab, generator=g)
 
-    def prefill(self, ids: Sequence[int], embed_overrides=None) -> int:
+    def prefill(self, ids: Sequence[int], embed_overrides=None, image_blocks=None) -> int:
         self._tick()
         self.last_overrides = embed_overrides
+        self.last_image_blocks = image_blocks
         self.history += list(ids)
         self.prefill_tokens += len(ids)
         return int(torch.argmax(self._logits()))

@@ -159,11 +159,13 @@ class TpTextModel(TextModel):
     def save_checkpoint(self) -> None: self._call("save_checkpoint")
     def restore_checkpoint(self) -> None: self._call("restore_checkpoint")
 
-    def prefill(self, ids: Sequence[int], embed_overrides=None) -> int:
+    def prefill(self, ids: Sequence[int], embed_overrides=None, image_blocks=None) -> int:
         ids = [int(t) for t in ids]
         if embed_overrides is not None:
             pos, rows = embed_overrides
             embed_overrides = (pos.cpu(), rows.detach().float().cpu())     # travels inside the command
+            if image_blocks:
+                return self._call("prefill", ids, embed_overrides, [tuple(b) for b in image_blocks])
             return self._call("prefill", ids, embed_overrides)
         return self._call("prefill", ids)
 

@@ -182,7 +182,14 @@ class Engine:
         else:
             feed_from = plan.feed_from
         res.reused_tokens = feed_from
-        first = m.prefill(prompt[feed_from:], embed_overrides=overrides) if overrides is not None else m.prefill(prompt[feed_from:])
+        if overrides is not None and req.images and getattr(self.vision, "bidirectional_blocks", False):
+            # this family's image rows attend to their whole block on sliding-window layers: the prefill gets the blocks
+            from ..models.gemma_vision import find_blocks
+            first = m.prefill(prompt[feed_from:], embed_overrides=overrides, image_blocks=find_blocks(prompt[feed_from:], req.image_token_id))
+        elif overrides is not None:
+            first = m.prefill(prompt[feed_from:], embed_overrides=overrides)
+        else:
+            first = m.prefill(prompt[feed_from:])
         if self.prompt_checkpoint:
             m.save_checkpoint()
         rng = Rng(req.params.seed)

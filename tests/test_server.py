@@ -240,6 +240,49 @@ def test_image_parts_become_placeholder_tokens_and_embedding_overrides():
         srv.stop(); eng.shutdown()
 
 
+def test_block_style_image_front_sizes_images_and_hands_the_blocks_to_the_prefill():
+    """The family whose image rows form bidirectional blocks: the front object decides the soft-token count, and the
+    engine passes the runs of image placeholders to the model's prefill."""
+    import base64
+    import io
+    import torch
+    from PIL import Image
+    from r4dx_b200.models import gemma_vision as GV
+
+    class Front:
+        bidirectional_blocks = True
+
+        def token_count(self, img):
+            h, w = GV.target_size(int(img.shape[0]), int(img.shape[1]), 70)
+            return (h // GV.SIDE) * (w // GV.SIDE)
+
+        def encode_images(self, images):
+            return torch.ones(sum(self.token_count(i) for i in images), 128)
+
+    model = FakeTextModel(vocab=300)
+    front = Front()
+    eng = Engine(model, ByteTokenizer(300), vision=front)
+    srv = ApiServer(eng, ByteTokenizer(300), ChatTemplate(), "fake-gemma", port=0, vision_config=front, image_token_id=299)
+    srv.start()
+    try:
+        parts = [{"type": "text", "text": "a "}]
+        for size in ((96, 96), (200, 100)):
+            buf = io.BytesIO()
+            Image.new("RGB", size, (10, 200, 10)).save(buf, format="PNG")
+            parts += [{"type": "image_url", "image_url": {"url": "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()}},
+                      {"type": "text", "text": " b "}]
+        r = json.load(_post(srv.port, "/v1/chat/completions", {"messages": [{"role": "user", "content": parts}], "max_tokens": 2, "temperature": 0}))
+        assert r["choices"][0]["finish_reason"] in ("stop", "length")
+        blocks = model.last_image_blocks
+        assert len(blocks) == 2 and all(b > a for a, b in blocks)
+        n = [front.token_count(torch.zeros(96, 96, 3)), front.token_count(torch.zeros(100, 200, 3))]
+        assert [b - a for a, b in blocks] == n
+        assert all(model.history[i] == 299 for a, b in blocks for i in range(a, b))
+        assert model.history[blocks[0][0] - 1] != 299 and model.history[blocks[0][1]] != 299
+    finally:
+        srv.stop(); eng.shutdown()
+
+
 def test_paged_kv_allocator_tables_exhaustion_and_reuse():
     import torch
     from r4dx_b200.models.batch import PagedKvAllocator

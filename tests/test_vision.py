@@ -160,3 +160,53 @@ def test_gemma_style_vision_host_half():
     assert torch.equal(GV.embed_reference(px[2:3], pos[2:3], w), rows[2:3])       # rows are independent
     moved = GV.embed_reference(px, torch.flip(pos, [1]), w)
     assert not torch.equal(moved, rows)                                           # the position terms matter
+
+
+@pytest.mark.gpu
+def test_gemma_embedder_on_the_device_matches_the_host_chain():
+    from r4dx_b200.models import gemma_vision as GV
+    g = torch.Generator().manual_seed(4)
+    n = lambda *s: torch.randn(*s, generator=g) * 0.05
+    mm, out, pd, rows = 128, 256, 6912, 37
+    w = GV.GemmaEmbedderWeights(1 + n(pd), n(pd), n(mm, pd), n(mm), 1 + n(mm), n(mm), n(16, 2, mm), 1 + n(mm), n(mm), n(out, mm))
+    px = torch.rand(rows, pd, generator=g)
+    pos = torch.randint(0, 16, (rows, 2), generator=g)
+    ref = GV.embed_reference(px, pos, w)
+    got = GV.GemmaEmbedder(w).embed(px, pos).float().cpu()
+    assert got.shape == ref.shape
+    assert (got - ref).abs().max().item() < 0.03 * ref.abs().max().item()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,window", [(64, 24), (256, 40), (128, 0)])
+def test_prefill_attention_with_per_row_key_limits(D, window):
+    """Rows of a block see keys up to the block's end: the windowed prefill kernel against the reference attention."""
+    from r4dx_b200.models import gemma_vision as GV
+    from r4dx_b200.ops import kernels as K
+    from r4dx_b200.ops import reference as R
+    g = torch.Generator().manual_seed(D)
+    T, Hq, Hkv, pos0 = 90, 4, 2, 0
+    blocks = [(7, 23), (40, 71)]
+    q = torch.randn(T, Hq, D, generator=g).to(torch.bfloat16)
+    k = (torch.randn(T, Hkv, D, generator=g) * 0.5)
+    v = (torch.randn(T, Hkv, D, generator=g) * 0.5)
+    lim = GV.key_limit_ext(pos0, T, blocks)
+    nblk = (T + 15) // 16
+    dev = "cuda"
+    cache = torch.zeros(nblk, Hkv, 2, 16, D, dtype=torch.uint8, device=dev)
+    k8 = (k * 16).to(torch.float8_e4m3fn)
+    v8 = (v * 16).to(torch.float8_e4m3fn)
+    for t in range(T):
+        cache[t // 16, :, 0, t % 16] = k8[t].view(torch.uint8).to(dev)
+        cache[t // 16, :, 1, t % 16] = v8[t].view(torch.uint8).to(dev)
+    table = torch.arange(nblk, dtype=torch.int32, device=dev)
+    ds = torch.full((Hkv,), 1 / 16.0, device=dev)
+    out = torch.zeros(T, Hq * D, dtype=torch.bfloat16, device=dev)
+    qg = torch.zeros(T, Hq, 2 * D, dtype=torch.bfloat16, device=dev)
+    K.attn_prefill(q.to(dev), qg, cache, table, ds, ds, out, T, Hq, Hkv, D, pos0, gated=False, window=window, key_limit=lim.to(dev))
+    kd, vd = k8.float() / 16, v8.float() / 16
+    ref = R.causal_gqa_attention(q.float(), kd, vd, pos0, window=window, key_limit=lim).reshape(T, Hq * D)
+    assert (out.float().cpu() - ref).abs().max().item() < 0.03 * ref.abs().max().item() + 1e-3
+    # without the limits the block rows come out differently
+    K.attn_prefill(q.to(dev), qg, cache, table, ds, ds, out, T, Hq, Hkv, D, pos0, gated=False, window=window)
+    assert (out.float().cpu() - ref).abs().max().item() > 0.05 * ref.abs().max().item()
