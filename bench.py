@@ -167,7 +167,7 @@ def main():
     # ---- cold TTFT: prompt in, first token out (cold = empty caches and state, not a cold process:
     # one short prefill first loads the kernels and allocates the chunk buffers) ---------------------
     pf_kw = {"chunk": args.prefill_chunk} if args.prefill_chunk else {}
-    model.reserve_prefill(args.prefill_chunk or 4096)      # workspaces are allocated once, outside the timed prefill
+    model.reserve_prefill(args.prefill_chunk or 8192)      # workspaces are allocated once, outside the timed prefill
     model.prefill(prompt[:2048 + 300], **pf_kw)
     model.reset()
     barrier()

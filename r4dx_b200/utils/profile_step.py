@@ -24,6 +24,7 @@ def main() -> None:
     ap.add_argument("--tp", type=int, default=1, help="rank 0's shard of this tensor-parallel degree with the no-op communicator: "
                     "the kernels of one rank at its real shapes, nothing exchanged (results are wrong by design)")
     ap.add_argument("--graph", type=int, default=0, help="also time this many CUDA-graph replays of the step")
+    ap.add_argument("--chunk", type=int, default=0, help="rows per prefill chunk (0: the model's own choice)")
     ap.add_argument("--prefill", type=int, default=0, help="profile one chunked prefill of this many tokens instead of decode steps")
     a = ap.parse_args()
     from r4dx_b200.config import lfm2_moe_config, qwen_hybrid_27b_config, small_hybrid_config
@@ -45,17 +46,18 @@ def main() -> None:
                     **({"comm": comm} if a.model != "lfm2" and comm is not None else {}))
     if a.prefill:
         ids = torch.randint(0, cfg.vocab_size, (a.prefill,), dtype=torch.int32)
-        m.prefill(ids[:4096])          # warm-up (allocates the chunk buffers)
+        kw = {"chunk": a.chunk} if a.chunk else {}
+        m.prefill(ids[:max(4096, a.chunk)], **kw)          # warm-up (allocates the chunk buffers)
         m.reset()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.profiler.start()
         e0.record()
-        m.prefill(ids)
+        m.prefill(ids, **kw)
         e1.record()
         torch.cuda.synchronize()
         torch.cuda.profiler.stop()
-        print(f"prefill of {a.prefill} tokens, {a.layers} layers: {e0.elapsed_time(e1):.2f} ms")
+        print(f"prefill of {a.prefill} tokens, {a.layers} layers, tp shard {a.tp}, chunk {a.chunk or 'auto'}: {e0.elapsed_time(e1):.2f} ms")
         return
     m.pos = a.ctx
     ids = torch.randint(0, cfg.vocab_size, (a.rows,), dtype=torch.int32)

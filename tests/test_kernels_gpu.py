@@ -756,3 +756,39 @@ def test_short_conv_across_calls_matches_reference(K):
     call(2, 2)
     call(64, 64)        # a multiple of the ring length
     call(1, 1)
+
+
+def test_viterbi_quantized_layer_times_like_a_random_code_layer(K):
+    """The benchmarks use random code words in the trellis layout.  A layer quantized from N(0, 0.02) weights by the
+    Viterbi encoder has the same shapes and bytes, and the kernels' work does not depend on the code values: the
+    weight-streaming kernel's time for the two differs by less than 2 % (median of repeated cold launches)."""
+    from r4dx_b200.quant import trellis
+    N, Kd, kb = 2048, 2048, 4
+    g = torch.Generator().manual_seed(0)
+    W = torch.randn(N, Kd, generator=g) * 0.02
+    tq, _ = trellis.quantize_cuda(W, kb, seed=3)
+    tr = trellis.random_weight(N, Kd, kb, seed=4, device="cuda")
+    assert tq.words.numel() == tr.words.numel() and tq.kb == tr.kb
+    x = torch.randn(1, Kd, generator=g).to(BF).cuda()
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device="cuda")
+
+    def med(w):
+        y = torch.empty(1, N, dtype=BF, device="cuda")
+        ts = []
+        for i in range(60):
+            flush.add_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            K.trellis_gemv(w, x, out=y)
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 10:
+                ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    tqd = trellis.TrellisWeight(tq.words.cuda(), tq.suh.cuda(), tq.svh.cuda(), tq.N, tq.K, tq.kb)
+    a, b = med(tqd), med(tr)
+    a2, b2 = med(tqd), med(tr)                      # interleaved repeats guard against drift between the two series
+    ta, tb = min(a, a2), min(b, b2)
+    assert abs(ta - tb) <= 0.02 * max(ta, tb) + 0.0003, (ta, tb)     # 2 % plus the event timer's 0.3 us granularity

@@ -91,17 +91,6 @@ def test_chunked_prefill_matches_small_batch_prefill(tiny):
     assert sum(int(x == y) for x, y in zip(ta, tb)) >= 5
 
 
-@pytest.fixture
-def same_attention_kernel_for_every_row_count():
-    """One-token steps normally take their own decode-attention kernel, whose rounding differs from the window kernel's
-    by ~0.3 % of the logit scale: enough to flip a near-tie.  Bit-exact comparisons between one-row and many-row calls
-    pin both to the window kernel."""
-    from r4dx_b200 import native
-    native.cuda().r4dxb_set_attn_decode_row(0)
-    yield
-    native.cuda().r4dxb_set_attn_decode_row(1)
-
-
 def test_speculative_verify_is_lossless(tiny, same_attention_kernel_for_every_row_count):
     """Windows with correct, partly wrong and fully wrong drafts reproduce the plain greedy stream."""
     from r4dx_b200.models.hybrid import HybridModel
@@ -163,7 +152,7 @@ def test_checkpoint_restore_replays_identically(tiny):
     assert a == b
 
 
-def test_mtp_speculation_equals_plain_greedy():
+def test_mtp_speculation_equals_plain_greedy(same_attention_kernel_for_every_row_count):
     """Lossless: with an MTP drafter (random weights -> few accepts) the token stream is the plain greedy one,
     and the drafter's KV stays in lock-step across rounds."""
     from r4dx_b200.models.hybrid import HybridModel
@@ -186,7 +175,7 @@ def test_mtp_speculation_equals_plain_greedy():
     assert tm.drafter.head.pos == main.pos - 1
 
 
-def test_mtp_sampled_speculation_equals_plain_sampled_decode():
+def test_mtp_sampled_speculation_equals_plain_sampled_decode(same_attention_kernel_for_every_row_count):
     """Sample-and-match: one draw per emitted token from the window's own logits rows, so with one seed the speculative
     stream is the plain sampled stream (the window rows and the single-row step run the same kernels row by row)."""
     from r4dx_b200.models.hybrid import HybridModel
