@@ -766,7 +766,7 @@ class HybridModel:
             raise ValueError("context overflow")
         b = self.buf
         b.n_replay.fill_(self.pending_rows)
-        self.forward_rows(T, True)
+        self._run_rows(T)
         if not hasattr(self, "_spec_out"):
             self._spec_out = torch.zeros(MAX_ROWS + 2, dtype=torch.int32, device=self.device)
         K.spec_accept(b.next_ids, b.ids[1:], T, self._spec_out, None)
@@ -776,6 +776,16 @@ class HybridModel:
         self.pending_rows = n
         self.pos += n
         return res[1:1 + n]
+
+    def _run_rows(self, T: int) -> None:
+        """The staged T rows through the layer stack and the head: a replay of the captured graph for this row count when
+        there is one (``enable_graphs((T,))``: a window is ~360 launches, which an eager call issues one by one), else
+        eagerly.  The graph's trailing bookkeeping only touches buffers every caller of this method stages again."""
+        g = self._graphs.get(T)
+        if g is not None:
+            g.replay()
+        else:
+            self.forward_rows(T, True)
 
     def window_logits(self, anchor: int, drafts: List[int]) -> torch.Tensor:
         """Runs the window [anchor, d1..dm] and returns its fp32 logits rows WITHOUT committing anything; follow with
@@ -788,7 +798,7 @@ class HybridModel:
         if self.pos + T > self.max_ctx:
             raise ValueError("context overflow")
         self.buf.n_replay.fill_(self.pending_rows)
-        self.forward_rows(T, True)
+        self._run_rows(T)
         self._window_rows = T
         return self.buf.logits[:T]
 

@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(kThreads) GdnDecodeKernel(GdnArgs a) {
   __shared__ float sq[kMaxT][D], sk[kMaxT][D], sv[kMaxT][D], so[kMaxT][D];
   __shared__ float seg[kMaxT], sbeta[kMaxT];
   __shared__ float rk[kMaxT][D], ru[kMaxT][D], reg[kMaxT];
-  __shared__ float red[32];
+  __shared__ float red[32], red2[32];
   if (a.row_slot != nullptr) {
     const int b = blockIdx.y, slot = a.row_slot[b];
     a.mixed += static_cast<size_t>(b) * a.conv_dim;
@@ -148,8 +148,14 @@ __global__ void __launch_bounds__(kThreads) GdnDecodeKernel(GdnArgs a) {
         sa += BfLo(va) * BfLo(hh) + BfHi(va) * BfHi(hh);
         sb += BfLo(vb) * BfLo(hh) + BfHi(vb) * BfHi(hh);
       }
-      sa = BlockSum(sa, red);
-      sb = BlockSum(sb, red);
+      // both dot products through one block reduction (two values per warp slot)
+      sa = WarpSum(sa);
+      sb = WarpSum(sb);
+      __syncthreads();
+      if (lane == 0) { red[warp] = sa; red2[warp] = sb; }
+      __syncthreads();
+      sa = WarpSum(lane < kThreads / 32 ? red[lane] : 0.f);
+      sb = WarpSum(lane < kThreads / 32 ? red2[lane] : 0.f);
       if (threadIdx.x == 0) {
         const float xs = sa + a.dt_bias[h];
         const float sp = xs > 20.f ? xs : log1pf(__expf(xs));

@@ -189,15 +189,29 @@ class LocalTextModel(TextModel):
             return [self.decode_step_greedy(token)]
         self._graph_active = False
         drafts = self.drafter.draft(token, k)
+        self._window_graph(len(drafts) + 1)
         emitted = self.m.verify_window(token, drafts)
         self.drafter.after_verify(token, drafts, emitted)
         return emitted
+
+    def _window_graph(self, T: int) -> None:
+        """Captures the verify window of T rows once it has been used a few times with that size (windows shrink near the
+        end of a request: those sizes stay eager)."""
+        if T < 2 or not self.window_graphs or T in getattr(self.m, "_graphs", {T: None}):
+            return
+        seen = self.__dict__.setdefault("_window_uses", {})
+        seen[T] = seen.get(T, 0) + 1
+        if seen[T] == 3:
+            self.m.enable_graphs((T,))
+
+    window_graphs = True
 
     def draft_tokens(self, token: int, k: int) -> List[int]:
         return self.drafter.draft(token, k) if self.drafter is not None else []
 
     def window_logits(self, token: int, drafts: Sequence[int]) -> torch.Tensor:
         self._graph_active = False
+        self._window_graph(len(drafts) + 1)
         return self.m.window_logits(token, list(drafts))
 
     def commit_window(self, token: int, drafts: Sequence[int], n: int) -> None:
