@@ -39,7 +39,8 @@ def parse():
     ap.add_argument("--extras", default="mtp,dflash",
                     help="comma list of extra arms reported under \"extras\" (the headline value is unaffected): mtp = MTP "
                          "speculation with 3 drafts per round, dflash = block-diffusion drafter with 7 drafts per round, "
-                         "pp2 = pipelined-prefill TTFT (2 ranks only); empty for none")
+                         "pp2 = pipelined-prefill TTFT (2 ranks only), f8 = TTFT with the opt-in 8-bit prefill products and the KL of "
+                         "its last-row logits against the 16-bit prefill; empty for none")
     ap.add_argument("--spec-rounds", type=int, default=48)
     ap.add_argument("--no-pdl", action="store_true", help="A/B: disable programmatic dependent launch")
     ap.add_argument("--no-overlap", action="store_true", help="A/B: run sibling projections back to back instead of on a side stream")
@@ -280,6 +281,39 @@ def main():
         dcfg = DflashConfig(target_layers=tuple(l for l in (6, 20, 34, 48, 62) if l < gcfg.num_hidden_layers))
         extras["dflash_k7"] = spec_arm(DflashDrafter(model, dcfg, synthetic_dflash_weights(dcfg, gcfg.vocab_size, device=dev)), 7)
         model.capture_layers = ()
+    if "f8" in want:
+        # opt-in 8-bit prefill products: same prompt, same model; reported beside the 16-bit TTFT, never instead of it
+        K.set_prefill_f8(True)
+        try:
+            model.reset()
+            model.prefill(prompt[:2048 + 300], **pf_kw)
+            model.reset()
+            barrier()
+            e0.record()
+            tok8 = model.prefill(prompt, **pf_kw)
+            e1.record()
+            barrier()
+            verify_ranks("8-bit prefill")
+            lg8 = model.buf.logits[0].float().clone()
+        finally:
+            K.set_prefill_f8(False)
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        model.reset()
+        tok16 = model.prefill(prompt, **pf_kw)
+        lg16 = model.buf.logits[0].float()
+        p16 = torch.log_softmax(lg16, -1)
+        kl = float((p16.exp() * (p16 - torch.log_softmax(lg8, -1))).sum())
+        # the noise floor of this random-weight model: the same 16-bit prefill in smaller chunks differs only in summation
+        # order (64 layers of random weights amplify any rounding difference)
+        model.reset()
+        model.prefill(prompt, chunk=2048)
+        pf = torch.log_softmax(model.buf.logits[0].float(), -1)
+        kl_floor = float((p16.exp() * (p16 - pf)).sum())
+        extras["prefill_8bit"] = {"ttft_s": {str(args.prompt_len): float(t[0]) / 1e3}, "same_first_token": bool(tok8 == tok16),
+                                  "kl_last_row_vs_16bit" + ("_vocab_shard" if world > 1 else ""): kl,
+                                  "kl_16bit_rechunked_vs_16bit (noise floor of the random model)": kl_floor}
     if "pp2" in want and world == 2:
         from r4dx_b200.parallel.pp import PipelinePrefill, default_split
         split = default_split(gcfg)

@@ -73,6 +73,16 @@ class Linear:
         T = out.shape[0]
         xh = xh_buf.view(-1)[:T * w.K].view(T, w.K)
         K.trellis_input(x, w.suh, out=xh, fused_silu_mul=fused_silu_mul, gelu=gelu)
+        if K.PREFILL_F8 and T >= 128 and w.K % 128 == 0:
+            # opt-in 8-bit product: the e4m3 rows and their scales live in the unused tail of the transform buffer
+            tail = xh_buf.view(-1)[T * w.K:]
+            if tail.numel() * 2 >= T * w.K + 4 * T + 16:
+                xq = tail.view(torch.uint8)[:T * w.K].view(T, w.K)
+                sc = tail.view(torch.uint8)[(T * w.K + 15) // 16 * 16:][:4 * T].view(torch.float32)
+            else:
+                xq, sc = None, None
+            xq, sc = K.quantize_rows_e4m3(xh, xq, sc)
+            return K.trellis_gemm_f8(w, xq, sc, residual=residual, out=out)
         return K.trellis_gemm(w, xh, residual=residual, out=out)
 
     @property

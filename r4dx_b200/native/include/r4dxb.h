@@ -135,6 +135,13 @@ int r4dxb_trellis_gemm(const void* w, const void* svh, const void* xh, void* y, 
 int r4dxb_linear_tc(const void* w, const void* wsz, int kind, int group, int bf16, const void* x, void* y, int out_f32,
                     const void* bias, const void* residual, int T, int N, int K, int tn, int* status, void* stream);
 
+/* 8-bit prefill product (opt-in): r4dxb_quantize_rows_e4m3 turns fp16 rows [T, K] into e4m3 rows + one fp32 scale per row
+ * (scale = rowmax / 448); r4dxb_trellis_gemm_f8 multiplies them with e4m3 code values on tcgen05.mma kind::f8f6f4
+ * (K per shared-memory slab 128, fp32 accumulate, row scale in the epilogue).  K a multiple of 128, tn 128 / 256 / 512. */
+int r4dxb_quantize_rows_e4m3(const void* xh, void* xq, float* scale, int T, int K, void* stream);
+int r4dxb_trellis_gemm_f8(const void* w, const void* svh, const void* xq, const float* x_scale, void* y, const void* residual,
+                          int T, int N, int K, int kb, int tn, int* status, void* stream);
+
 /* Grouped experts on the tensor cores: tile list of a routing plan (E <= 1024 local experts, tiles [2 * max_tiles]),
  * per-expert input transform of the planned pairs in expert order (xdiv: pairs per input row; mode as
  * r4dxb_trellis_input), and y[perm[p]] = svh[e] * H128(xh[p] Q_e^T) with one expert's next tn rows per token tile

@@ -144,6 +144,17 @@ __device__ __forceinline__ void UmmaF16(uint32_t tmem_d, uint64_t desc_a, uint64
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// kind::f8f6f4 with e4m3 A and B (format code 0 for both), both K-major, fp32 accumulate; K = 32 per instruction.
+__host__ __device__ constexpr uint32_t UmmaInstrDescE4m3(int M, int N) {
+  return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+__device__ __forceinline__ void UmmaF8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+      "  tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p; }"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrives once on `bar` when every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void UmmaCommit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(SmemAddr(bar)) : "memory");
@@ -249,6 +260,20 @@ inline PFN_encodeTiled GetEncodeTiled() {
 }
 
 // 2-D row-major tensor [rows, cols] of 2-byte elements, box [box_rows, box_cols], 128-byte swizzle.
+// 2-D map over a row-major matrix of bytes (8-bit activations) with the 128-byte swizzle: box_cols bytes x box_rows rows.
+inline int MakeTensorMap2D8(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
+  PFN_encodeTiled enc = GetEncodeTiled();
+  if (!enc) return 10004;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : 10005;
+}
+
 inline int MakeTensorMap2D16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows,
                              uint32_t box_cols, bool is_bf16) {
   PFN_encodeTiled enc = GetEncodeTiled();

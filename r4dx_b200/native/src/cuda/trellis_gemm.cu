@@ -21,6 +21,8 @@
 //
 // The reference engine's counterparts are WMMA kernels whose decoded fragments are shared through
 // LDS (reference: third_party/libr4d/r4d_gemm_trellis_nt_m256.hip:1-60); nothing is shared with them.
+#include <cuda_fp8.h>
+
 #include "sm100_ptx.cuh"
 #include "trellis_decode.cuh"
 
@@ -34,12 +36,14 @@ constexpr int kATileBytes = 128 * kSlabK * 2;   // 16 KiB
 //   words (<= 5 KiB per slab, WST deep)  producer W -> decode warps
 //   A     (16 KiB per slab, AST deep)    decode warps -> MMA
 //   X     (TN x 128 B per slab, XST deep) producer X -> MMA
-template <int KB, int TN>
+template <int KB, int TN, int F8 = 0>
 struct GemmSmem {
-  static constexpr int kWordsBytes = (KB == 0) ? 0 : 4 * 8 * 8 * KB * 4;   // 4 k-tiles x 8 n-tiles x 8KB words
+  // a slab is one 128-byte swizzle row of K per operand row: 64 fp16 values (4 k-tiles of 16) or 128 e4m3 values (8 k-tiles)
+  static constexpr int kKTiles = F8 ? 8 : 4;
+  static constexpr int kWordsBytes = (KB == 0) ? 0 : kKTiles * 8 * 8 * KB * 4;   // k-tiles x 8 n-tiles x 8KB words
   static constexpr int kWordsSlot = ((kWordsBytes + 1023) / 1024) * 1024;
   static constexpr int kXTileBytes = TN * kSlabK * 2;
-  static constexpr int WST = 6;
+  static constexpr int WST = F8 ? 4 : 6;      // (8-bit slabs carry twice the words: four of them are as much K in flight as six 16-bit ones)
   static constexpr int AST = KB == 0 ? 4 : 3;
   static constexpr int XST = TN >= 512 ? 2 : (TN >= 256 ? 3 : 4);
   static constexpr int kABytes = AST * kATileBytes;
@@ -87,6 +91,9 @@ struct PlainArgs {
   const int* g_ntiles;
   long long g_words;           // packed words per expert
   int g_max_tiles;             // grid height: an upper bound on the tile count
+  // MODE 4, 8-bit operands: the decode warps emit e4m3 code values, the activations are e4m3 rows with one fp32 scale per
+  // row (xh = scale * e4m3); K per slab is 128 and the products run at the 8-bit rate with half the activation bytes
+  const float* x_scale;        // [T]
 };
 
 template <int KB, int TN, int DW, int MODE = 0>
@@ -96,7 +103,9 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
                   const __half* __restrict__ svh, __nv_bfloat16* __restrict__ y,
                   const __nv_bfloat16* __restrict__ residual, int T, int N, int K, int* __restrict__ status, RsArgs rs,
                   PlainArgs pl) {
-  using S = GemmSmem<KB, TN>;
+  using S = GemmSmem<KB, TN, MODE == 4>;
+  constexpr int kSlabElems = MODE == 4 ? 2 * kSlabK : kSlabK;      // K values per slab (one 128-byte row per operand row)
+  constexpr int kKTiles = S::kKTiles;
   constexpr int WST = S::WST, AST = S::AST, XST = S::XST;
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment: required by the swizzled UMMA / TMA tiles
@@ -127,7 +136,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     wsrc = static_cast<const uint32_t*>(wsrc) + static_cast<long long>(e) * pl.g_words;
     svh += static_cast<size_t>(e) * N;
   }
-  const int slabs = (K + kSlabK - 1) / kSlabK;   // a ragged last slab only in the dense plain mode (TMA zero-fills X)
+  const int slabs = (K + kSlabElems - 1) / kSlabElems;   // a ragged last slab only in the dense plain mode (TMA zero-fills X)
   constexpr uint32_t kTmemCols = TN < 32 ? 32 : TN;
   constexpr int kHalves = TN > 256 ? TN / 256 : 1;     // one MMA covers at most 256 token columns
   constexpr int kMmaN = TN > 256 ? 256 : TN;
@@ -168,7 +177,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         ptx::MbarArriveExpectTx(&xfull[s], S::kXTileBytes);
 #pragma unroll
         for (int h = 0; h < kHalves; ++h)
-          ptx::TmaLoad2D(x_ring + s * S::kXTileBytes + h * (kMmaN * kSlabK * 2), &tmap_x, &xfull[s], it * kSlabK, t0 + h * kMmaN);
+          ptx::TmaLoad2D(x_ring + s * S::kXTileBytes + h * (kMmaN * kSlabK * 2), &tmap_x, &xfull[s], it * kSlabElems, t0 + h * kMmaN);
       }
     }
   } else if (warp == DW + 2) {
@@ -184,7 +193,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       }
     }
     if (KB != 0 && lane == 0) {
-      const size_t slab_words = 4 * 8 * 8 * (KB == 0 ? 1 : KB);
+      const size_t slab_words = kKTiles * 8 * 8 * (KB == 0 ? 1 : KB);
       const uint32_t* wbase = static_cast<const uint32_t*>(wsrc) + static_cast<size_t>(nb) * (K / 16) * 8 * 8 * (KB == 0 ? 1 : KB);
       for (int it = 0; it < slabs; ++it) {
         const int s = it % WST, round = it / WST;
@@ -196,7 +205,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   } else if (warp == DW + 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      const uint32_t idesc = ptx::UmmaInstrDescF16(128, kMmaN, MODE == 1 && pl.bf16 != 0);
+      const uint32_t idesc = MODE == 4 ? ptx::UmmaInstrDescE4m3(128, kMmaN) : ptx::UmmaInstrDescF16(128, kMmaN, MODE == 1 && pl.bf16 != 0);
       bool ok = true;
       for (int it = 0; it < slabs && ok; ++it) {
         const int sa = it % AST, ra = it / AST, sx = it % XST, rx = it / XST;
@@ -210,7 +219,8 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
           for (int k = 0; k < kSlabK / 16; ++k) {
             const uint64_t da = ptx::UmmaDescSw128(a_addr + k * 32);
             const uint64_t db = ptx::UmmaDescSw128(b_addr + h * (kMmaN * kSlabK * 2) + k * 32);
-            ptx::UmmaF16(tmem_base + h * kMmaN, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+            if constexpr (MODE == 4) ptx::UmmaF8(tmem_base + h * kMmaN, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
+            else ptx::UmmaF16(tmem_base + h * kMmaN, da, db, idesc, (it > 0 || k > 0) ? 1u : 0u);
           }
         }
         ptx::UmmaCommit(&aempty[sa]);         // frees the A tile and the X tile once these MMAs have read them
@@ -259,6 +269,26 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             const int chunk = half * 4 + wi;
             *reinterpret_cast<uint4*>(at + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4)) = packed;
           }
+        }
+      } else if constexpr (MODE == 4) {
+        // 8-bit operands: a slab is 8 k-tiles; a lane's 8 code values become 8 e4m3 bytes, the two K halves of a row share
+        // one 16-byte swizzle chunk (chunk index = k-tile)
+#pragma unroll 4
+        for (int idx = warp; idx < 64; idx += DW) {
+          const int j = idx & 7, kt = idx >> 3;
+          const int r = j * 16 + row_in_tile;
+          constexpr int NW = 8 * (KB == 0 ? 4 : KB);
+          const uint32_t* tw = reinterpret_cast<const uint32_t*>(w_ring + sw * S::kWordsSlot) + (kt * 8 + j) * NW;
+          uint32_t hi, lo;
+          tl.Window(tw[tl.i0], tw[tl.i1], (KB == 4) ? 0u : tw[tl.i2], hi, lo);
+          __half2 w[4];
+          TrellisDecode8<(KB == 0 ? 4 : KB)>(hi, lo, w);
+          uint2 packed;
+          packed.x = static_cast<uint32_t>(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<__half2_raw*>(&w[0]), __NV_SATFINITE, __NV_E4M3)) |
+                     (static_cast<uint32_t>(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<__half2_raw*>(&w[1]), __NV_SATFINITE, __NV_E4M3)) << 16);
+          packed.y = static_cast<uint32_t>(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<__half2_raw*>(&w[2]), __NV_SATFINITE, __NV_E4M3)) |
+                     (static_cast<uint32_t>(__nv_cvt_halfraw2_to_fp8x2(*reinterpret_cast<__half2_raw*>(&w[3]), __NV_SATFINITE, __NV_E4M3)) << 16);
+          *reinterpret_cast<uint2*>(at + (r >> 3) * 1024 + (r & 7) * 128 + ((kt ^ (r & 7)) << 4) + khalf * 8) = packed;
         }
       } else {
 #pragma unroll
@@ -332,7 +362,11 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             float f[4] = {p.x, p.y, p.z, p.w};
             const int n = nb * 128 + lane * 4;
             float o0, o1, o2, o3;
-            if constexpr (MODE == 0 || MODE == 3) {
+            if constexpr (MODE == 0 || MODE == 3 || MODE == 4) {
+              if constexpr (MODE == 4) {
+                const float xs = __ldg(pl.x_scale + t);               // the row's activation scale
+                f[0] *= xs; f[1] *= xs; f[2] *= xs; f[3] *= xs;
+              }
               WarpFwht128(f);
               const uint2 sv = *reinterpret_cast<const uint2*>(svh + n);
               const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x), s23 = *reinterpret_cast<const __half2*>(&sv.y);
@@ -502,17 +536,55 @@ __global__ void TrellisInputGroupedKernel(const __nv_bfloat16* __restrict__ in, 
   *reinterpret_cast<uint2*>(out + static_cast<size_t>(p) * K + k) = ov;
 }
 
+// ---- 8-bit activations: xq = e4m3(xh / scale), scale = rowmax |xh| / 448, one CTA per row ---------------------------
+__global__ void __launch_bounds__(256) QuantizeRowsE4m3Kernel(const __half* __restrict__ xh, uint8_t* __restrict__ xq,
+                                                              float* __restrict__ scale, int K) {
+  __shared__ float red[32];
+  const __half* row = xh + static_cast<size_t>(blockIdx.x) * K;
+  float amax = 0.f;
+  for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fmaxf(fabsf(__low2float(h[i])), fabsf(__high2float(h[i]))));
+  }
+  amax = WarpMax(amax);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, red[w]);
+  const float sc = amax > 0.f ? amax * (1.0f / 448.0f) : 1.0f;
+  const float inv = 1.0f / sc;
+  if (threadIdx.x == 0) scale[blockIdx.x] = sc;
+  uint8_t* out = xq + static_cast<size_t>(blockIdx.x) * K;
+  for (int k = threadIdx.x * 8; k < K; k += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    uint32_t o[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float2 a = __half22float2(h[2 * i]), b = __half22float2(h[2 * i + 1]);
+      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a.x * inv, a.y * inv), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(b.x * inv, b.y * inv), __NV_SATFINITE, __NV_E4M3);
+      o[i] = lo | (hi << 16);
+    }
+    *reinterpret_cast<uint2*>(out + k) = make_uint2(o[0], o[1]);
+  }
+}
+
 int g_decode_warps = 16;
 
 template <int KB, int TN, int DW, int MODE = 0>
 int LaunchGemm(const void* wsrc, const void* svh, const void* xh, void* y, const void* residual, int T, int N, int K,
                int* status, cudaStream_t stream, const RsArgs& rs, const PlainArgs& pl = PlainArgs{}) {
-  using S = GemmSmem<KB, TN>;
+  using S = GemmSmem<KB, TN, MODE == 4>;
   static_assert(S::kTotal <= 227 * 1024, "shared memory budget");
   static_assert(S::kBars * 8 + 16 <= 512, "barrier block");
   CUtensorMap tmap;
-  const int rc = MakeTensorMap2D16(&tmap, xh, static_cast<uint64_t>(T), static_cast<uint64_t>(K), TN > 256 ? 256 : TN, kSlabK,
-                                   MODE == 1 && pl.bf16 != 0);
+  const int rc = MODE == 4 ? MakeTensorMap2D8(&tmap, xh, static_cast<uint64_t>(T), static_cast<uint64_t>(K), TN > 256 ? 256 : TN, 128)
+                           : MakeTensorMap2D16(&tmap, xh, static_cast<uint64_t>(T), static_cast<uint64_t>(K), TN > 256 ? 256 : TN, kSlabK,
+                                               MODE == 1 && pl.bf16 != 0);
   if (rc) return rc;
   CUtensorMap tmap_a = tmap;
   if (MODE == 1) {
@@ -639,6 +711,29 @@ int r4dxb_linear_tc(const void* w, const void* wsz, int kind, int group, int bf1
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return kind == 0 ? LaunchPlain<1>(w, x, y, residual, T, N, K, tn, status, s, pl)
                    : LaunchPlain<2>(w, x, y, residual, T, N, K, tn, status, s, pl);
+}
+
+/* 8-bit prefill product: rows of fp16 transformed activations -> e4m3 rows + one fp32 scale per row, then the trellis GEMM
+ * with e4m3 code values and e4m3 activations on tcgen05.mma kind::f8f6f4 (fp32 accumulate, the row scale applied in the
+ * epilogue).  K a multiple of 128; token tiles 128 / 256 / 512. */
+int r4dxb_quantize_rows_e4m3(const void* xh, void* xq, float* scale, int T, int K, void* stream) {
+  if (T < 1 || K < 8 || K % 8) return R4DXB_BAD_ARG;
+  QuantizeRowsE4m3Kernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(xh), static_cast<uint8_t*>(xq), scale, K);
+  return FinishLaunch();
+}
+
+int r4dxb_trellis_gemm_f8(const void* w, const void* svh, const void* xq, const float* x_scale, void* y, const void* residual,
+                          int T, int N, int K, int kb, int tn, int* status, void* stream) {
+  if (T < 1 || N % 128 || K % 128 || x_scale == nullptr) return R4DXB_BAD_ARG;
+  const RsArgs rs = {};
+  PlainArgs pl = {};
+  pl.x_scale = x_scale;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define R4DXB_F8(KBV, TNV) if (kb == KBV && tn == TNV) return LaunchGemm<KBV, TNV, 16, 4>(w, svh, xq, y, residual, T, N, K, status, s, rs, pl);
+  R4DXB_F8(3, 128) R4DXB_F8(3, 256) R4DXB_F8(3, 512) R4DXB_F8(4, 128) R4DXB_F8(4, 256) R4DXB_F8(4, 512)
+  R4DXB_F8(5, 128) R4DXB_F8(5, 256) R4DXB_F8(5, 512)
+#undef R4DXB_F8
+  return R4DXB_BAD_ARG;
 }
 
 /* Grouped experts on the tensor cores (prefill and wide batches of the mixture-of-experts block).

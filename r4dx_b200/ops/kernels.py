@@ -421,6 +421,42 @@ def trellis_gemm(w: TrellisWeight, xh: torch.Tensor, residual: Optional[torch.Te
     return out
 
 
+register_cuda_sig("r4dxb_quantize_rows_e4m3", _I, [_P, _P, _P, _I, _I, _P])
+register_cuda_sig("r4dxb_trellis_gemm_f8", _I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P])
+
+# Opt-in 8-bit prefill products (R4DXB_PREFILL_F8=1): e4m3 activations (one scale per row) times e4m3 code values.  Half the
+# activation bytes per product and the 8-bit tensor-core rate; the rounding of both operands to three mantissa bits shows
+# in the logits (see the KL figures in the design notes), so the 16-bit path stays the default.
+PREFILL_F8 = os.environ.get("R4DXB_PREFILL_F8", "0") == "1"
+
+
+def set_prefill_f8(on: bool) -> None:
+    global PREFILL_F8
+    PREFILL_F8 = bool(on)
+
+
+def quantize_rows_e4m3(xh: torch.Tensor, xq: Optional[torch.Tensor] = None, scale: Optional[torch.Tensor] = None):
+    """fp16 rows [T, K] -> (e4m3 bytes [T, K], fp32 scale [T]) with xh ~= scale * e4m3."""
+    _req(xh, torch.float16, "xh")
+    T, K_ = xh.shape
+    xq = xq if xq is not None else torch.empty(T, K_, dtype=torch.uint8, device=xh.device)
+    scale = scale if scale is not None else torch.empty(T, dtype=torch.float32, device=xh.device)
+    _check(_lib().r4dxb_quantize_rows_e4m3(_p(xh), _p(xq), _p(scale), T, K_, _stream()), "quantize_rows_e4m3")
+    return xq, scale
+
+
+def trellis_gemm_f8(w: TrellisWeight, xq: torch.Tensor, x_scale: torch.Tensor, residual: Optional[torch.Tensor] = None,
+                    out: Optional[torch.Tensor] = None, tn: Optional[int] = None) -> torch.Tensor:
+    """y[T, N] from e4m3 transformed activations (``quantize_rows_e4m3``) on the 8-bit tcgen05 path."""
+    T = xq.numel() // w.K
+    out = out if out is not None else torch.empty(T, w.N, dtype=BF, device=xq.device)
+    # 512-column tiles as soon as there are that many rows: below, the decode warps and not the operand bytes set the pace
+    tn = tn or (512 if T > 256 else (256 if T > 128 else 128))
+    _check(_lib().r4dxb_trellis_gemm_f8(_p(w.words), _p(w.svh), _p(xq), _p(x_scale), _p(out), _p(residual), T, w.N, w.K, w.kb, tn,
+                                        _p(gemm_status(xq.device)), _stream()), "trellis_gemm_f8")
+    return out
+
+
 def dense_gemm_hadamard(W: torch.Tensor, svh: torch.Tensor, xh: torch.Tensor, tn: Optional[int] = None) -> torch.Tensor:
     """Same kernel with a dense fp16 A operand: y = svh * H128(xh W^T) over 128-row blocks of N."""
     _req(W, torch.float16, "W"); _req(xh, torch.float16, "xh")
