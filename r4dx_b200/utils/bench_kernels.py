@@ -56,6 +56,7 @@ def main() -> None:
     ap.add_argument("--decode-warps", type=int, default=16)
     ap.add_argument("--tn", type=int, default=0)
     ap.add_argument("--ksplit", type=int, default=0, help="override the cluster split of the weight-streaming kernel")
+    ap.add_argument("--f8", action="store_true", help="with --only trellis_gemm: also time the 8-bit (e4m3 x e4m3) product")
     ap.add_argument("--impl", default="", help="weight-streaming kernel: mma (tensor memory, default) or simt (CUDA cores)")
     a = ap.parse_args()
     from r4dx_b200.ops import kernels as K
@@ -106,6 +107,15 @@ def main() -> None:
                 tf = 2.0 * N * Kd * Tg / us / 1e6
                 print(f"trellis_gemm {name:12s} N={N:6d} K={Kd:6d} kb={kb} T={Tg} tn={tn}: {us:9.1f} us  "
                       f"{tf:7.1f} TFLOP/s  {tf / tf_peak:5.2f} of measured cuBLAS bf16")
+                if a.f8:
+                    xq, sc = K.quantize_rows_e4m3(xh)
+                    tn8 = a.tn or (512 if Tg > 256 else 256)
+                    us8 = timed(lambda: K.trellis_gemm_f8(w, xq, sc, out=y, tn=tn8), a.iters, flush)
+                    usq = timed(lambda: K.quantize_rows_e4m3(xh, xq, sc), a.iters, flush)
+                    K.check_gemm_status(dev)
+                    tf8 = 2.0 * N * Kd * Tg / us8 / 1e6
+                    print(f"trellis_gemm_f8 {name:9s} N={N:6d} K={Kd:6d} kb={kb} T={Tg} tn={tn8}: {us8:9.1f} us  "
+                          f"{tf8:7.1f} TFLOP/s effective  {tf8 / tf_peak:5.2f} of measured cuBLAS bf16  (+ {usq:.1f} us row quantizer)")
     if a.only in ("", "w4a16"):
         N, Kd = 248320, 5120
         w = w4a16.random_weight(N, Kd, 64, device=dev)
