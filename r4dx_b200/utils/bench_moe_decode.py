@@ -23,6 +23,10 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--prefill", type=int, default=0, help="one GPU: time a cold prefill of this many tokens instead of decode steps")
+    ap.add_argument("--real-prefill", type=int, default=0, metavar="P",
+                    help="batched decode: every slot is prefilled with P random tokens (real caches and recurrent state) "
+                         "instead of being positioned at --ctx with empty caches")
     ap.add_argument("--single", action="store_true", help="one sequence through the CUDA-graph decode path (one GPU)")
     ap.add_argument("--family", default="qwen_moe", choices=["qwen_moe", "lfm2"],
                     help="lfm2: the short-conv + attention MoE geometry (40 layers, 64 experts top-4); --single only")
@@ -45,6 +49,24 @@ def main() -> None:
         cfg = qwen_hybrid_moe_config(a.layers)
     e_per = cfg.num_experts // world
     w = synthetic_weight_set(cfg, device=dev, seed=0, kb_rule=moe_kb_rule, expert_range=(rank * e_per, e_per))
+    if a.prefill:
+        from r4dx_b200.models.hybrid import HybridModel
+        from r4dx_b200.ops import kernels as K
+        m = HybridModel(cfg, w, max_ctx=a.prefill + 64, device=dev)
+        ids = torch.randint(0, cfg.vocab_size, (a.prefill,), dtype=torch.int32)
+        m.prefill(ids[:min(a.prefill, 4096)])
+        m.reset()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        m.prefill(ids)
+        e1.record()
+        torch.cuda.synchronize()
+        K.check_gemm_status(dev)
+        ms = e0.elapsed_time(e1)
+        print(json.dumps({"metric": f"prefill tok/s, {a.family} geometry", "tokens": a.prefill, "layers": cfg.num_hidden_layers,
+                          "ms": ms, "tok_s": a.prefill / (ms / 1e3)}))
+        return
     if a.single:
         from r4dx_b200.models.hybrid import HybridModel
         m = HybridModel(cfg, w, max_ctx=a.ctx + a.steps + a.warmup + 64, device=dev)
@@ -69,12 +91,15 @@ def main() -> None:
     comm = None
     if world > 1:
         comm = (EpComm if a.comm == "fused" else NcclEpBaseline)(world, rank, dev, cfg, max_rows=max(B, 8))
-    bm = BatchModel(cfg, w, slots=B, slot_ctx=a.ctx + a.steps + a.warmup + 16, device=dev, comm=comm)
+    bm = BatchModel(cfg, w, slots=B, slot_ctx=max(a.ctx, a.real_prefill) + a.steps + a.warmup + 16, device=dev, comm=comm)
     slots = list(range(B))
-    for s in slots:
-        bm.position_slot(s, a.ctx)
     g = torch.Generator().manual_seed(rank)
-    toks = torch.randint(0, cfg.vocab_size, (B,), generator=g).tolist()
+    if a.real_prefill:
+        toks = [bm.import_slot(s, torch.randint(0, cfg.vocab_size, (a.real_prefill,), generator=g, dtype=torch.int32)) for s in slots]
+    else:
+        for s in slots:
+            bm.position_slot(s, a.ctx)
+        toks = torch.randint(0, cfg.vocab_size, (B,), generator=g).tolist()
     for _ in range(a.warmup):
         toks = bm.decode_batch(slots, toks)
     torch.cuda.synchronize()
@@ -95,7 +120,7 @@ def main() -> None:
     if rank == 0:
         ms = float(t[0])
         print(json.dumps({"metric": "batched decode tok/s, hybrid MoE geometry", "batch": a.batch, "world": world, "comm": a.comm,
-                          "ctx": a.ctx, "layers": a.layers, "ms_per_step": ms, "tok_s": a.batch / (ms / 1e3),
+                          "ctx": a.real_prefill or a.ctx, "slots_prefilled": bool(a.real_prefill), "layers": a.layers, "ms_per_step": ms, "tok_s": a.batch / (ms / 1e3),
                           "max_rows_of_an_expert_last_step": worst}))
     if world > 1:
         dist.barrier()
