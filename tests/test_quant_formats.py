@@ -308,3 +308,33 @@ def test_kl_report_orders_the_bit_widths(capsys):
         res[plan] = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert 0 < res["kb5"]["kl_mean"] < res["kb3"]["kl_mean"]
     assert res["kb5"]["mean_abs_logit_err"] < res["kb3"]["mean_abs_logit_err"]
+
+
+def test_kernel_registry_lists_every_entry_point_and_answers_coverage_questions():
+    """The registry is complete (every kernel entry point of the C header has a row) and its constraints are testable."""
+    import os
+    import re
+    from r4dx_b200.ops import registry
+    ks = registry.kernels()
+    names = {k["name"] for k in ks}
+    assert len(names) == len(ks) >= 50
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    hdr = open(os.path.join(root, "r4dx_b200", "native", "include", "r4dxb.h")).read()
+    declared = set(re.findall(r"^(?:int|long long|void) r4dxb_([a-z0-9_]+)\(", hdr, re.M))
+    not_kernels = {"launch_count_reset", "launch_count", "set_pdl", "set_attn_decode_row", "set_gemm_decode_warps",
+                   "trellis_encode_scratch_bytes", "gdn_chunk_ws_floats"}
+    aliases = {"trellis_gemv": "trellis_gemv_ex", "gdn_decode": "gdn_decode_ab", "attn_prefill": "attn_prefill_ex"}   # thin wrappers
+    missing = sorted(d for d in declared - not_kernels if d not in names and aliases.get(d) not in names)
+    assert not missing, missing
+    assert all(k["engine"].split("+")[0] in ("tcgen05", "mma.sync", "simt") for k in ks)
+    assert sum(k["engine"].startswith("tcgen05") for k in ks) >= 7
+    # coverage questions
+    assert registry.covers("trellis_gemm", N=5120, K=17408, kb=4, tn=512)
+    assert not registry.covers("trellis_gemm", N=5000, K=17408)
+    assert not registry.covers("trellis_gemv_ex", T=9)
+    assert registry.covering("paged_prefill_attention", D=256) == ["attn_prefill_tc", "attn_prefill_ex"]
+    assert registry.covering("paged_prefill_attention", D=64) == ["attn_prefill_ex"]
+    assert registry.covering("trellis_linear_rows_le_8", T=4, N=5120, K=5120, kb=5)[0] == "trellis_gemv_ex"
+    import pytest
+    with pytest.raises(KeyError):
+        registry.covers("no_such_kernel", T=1)
