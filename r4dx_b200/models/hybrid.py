@@ -449,12 +449,14 @@ class HybridModel:
         self.pending_rows = n
         self.pos += n
 
-    def check_healthy(self) -> None:
+    def check_healthy(self, rows: int = 1) -> None:
         """Raises if a bounded device wait ran out since the last check: a timed-out collective leaves an un-reduced partial
-        in the residual stream, so a token read after it must not be trusted (one small device-to-host read per call)."""
+        in the residual stream, so a token read after it must not be trusted (one small device-to-host read per call).
+        ``rows``: the row count of the call being checked (calls of four rows and more may have run the tensor-memory
+        weight-streaming kernel, whose waits report through the GEMM status word)."""
         if self.comm is not None and self.comm.world > 1:
             self.comm.check_healthy()
-        if K.GEMV_IMPL == "mma":
+        if K.GEMV_IMPL == "mma" or (K.GEMV_IMPL == "auto" and rows >= 4):
             K.check_gemm_status(self.device)
 
     def _read_token(self, idx: int) -> int:
@@ -781,7 +783,7 @@ class HybridModel:
             self._spec_out = torch.zeros(MAX_ROWS + 2, dtype=torch.int32, device=self.device)
         K.spec_accept(b.next_ids, b.ids[1:], T, self._spec_out, None)
         res = self._spec_out[:T + 1].tolist()        # one small read-back per round
-        self.check_healthy()
+        self.check_healthy(T)
         n = res[0]
         self.pending_rows = n
         self.pos += n

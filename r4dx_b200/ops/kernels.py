@@ -222,14 +222,27 @@ register_cuda_sig("r4dxb_trellis_gemv_mma", _I, [_P, _P, _P, _P, _P, _P, _P, _F,
 # Which weight-streaming kernel serves T <= 8 rows: "simt" = CUDA-core decode + fp16 FMA (default: the faster one
 # on the 27B shapes, 56-62 us vs 66-68 us on gate_up), "mma" = code values written to tensor memory and contracted
 # by tcgen05.mma kind::f16 (trellis_gemv_mma.cu).
-GEMV_IMPL = os.environ.get("R4DXB_GEMV", "simt")
+# "auto" (the default) takes the CUDA-core kernel for one to three rows and the tensor-memory kernel where it measured faster:
+# from six rows everywhere (gate_up at 8 rows: 95 against 121 us, down 69 against 97 us) and from four rows on the two large
+# MLP products (80 against 83 us, 57 against 67 us).
+GEMV_IMPL = os.environ.get("R4DXB_GEMV", "auto")
 
 
 def set_gemv_impl(name: str) -> None:
     global GEMV_IMPL
-    if name not in ("mma", "simt"):
+    if name not in ("mma", "simt", "auto"):
         raise KernelError(f"unknown weight-streaming kernel {name!r}")
     GEMV_IMPL = name
+
+
+def use_mma_gemv(T: int, N: int, K: int, ksplit: int) -> bool:
+    """Whether a product of T rows goes to the tensor-memory weight-streaming kernel (it needs an even K split of at most
+    6144 columns per CTA)."""
+    if GEMV_IMPL == "simt" or K // ksplit > 6144 or (K // 128) % ksplit:
+        return False
+    if GEMV_IMPL == "mma":
+        return True
+    return T >= 6 or (T >= 4 and N * K >= (1 << 26))
 
 
 def trellis_gemv(w: TrellisWeight, x: torch.Tensor, residual: Optional[torch.Tensor] = None,
@@ -244,7 +257,7 @@ def trellis_gemv(w: TrellisWeight, x: torch.Tensor, residual: Optional[torch.Ten
     T = x.numel() // (2 * w.K if prologue in (PRO_SILU_MUL, PRO_GELU_MUL) else w.K)
     out = out if out is not None else torch.empty(T, w.N, dtype=BF, device=x.device)
     ks = ksplit or pick_ksplit(w.N, w.K)
-    if GEMV_IMPL == "mma" and w.K // ks <= 6144 and (w.K // 128) % ks == 0:
+    if use_mma_gemv(T, w.N, w.K, ks):
         _check(_lib().r4dxb_trellis_gemv_mma(_p(w.words), _p(w.suh), _p(w.svh), _p(x), _p(out), _p(residual), _p(norm_w), eps,
                                              prologue, T, w.N, w.K, w.kb, ks, _p(gemm_status(x.device)), _stream()),
                "trellis_gemv_mma")

@@ -129,7 +129,7 @@ class FusedComm(NcclComm):
         if not isinstance(w, TrellisWeight) or w.N != self.n:
             return super().row_parallel_linear(lin, x, res, prologue)
         T = res.shape[0]
-        if K.GEMV_IMPL == "mma" and w.K // lin.ksplit <= 6144:
+        if K.use_mma_gemv(T, w.N, w.K, lin.ksplit):
             rc = self._lib.r4dxb_trellis_gemv_mma_allreduce(
                 w.words.data_ptr(), w.suh.data_ptr(), w.svh.data_ptr(), x.data_ptr(), res.data_ptr(), res.data_ptr(),
                 prologue, T, w.N, w.K, w.kb, lin.ksplit, self.recv_tab, self.block_seq.data_ptr(),

@@ -33,7 +33,7 @@ def test_selector_walk_matches_python_restatement():
 
 
 @pytest.mark.gpu
-def test_device_round_matches_restatement_and_speculation_is_lossless(same_attention_kernel_for_every_row_count):
+def test_device_round_matches_restatement_and_speculation_is_lossless(same_kernels_for_every_row_count):
     from r4dx_b200.config import tiny_hybrid_config
     from r4dx_b200.models.hybrid import HybridModel
     from r4dx_b200.models.oracle import init_weights

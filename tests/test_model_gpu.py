@@ -91,7 +91,7 @@ def test_chunked_prefill_matches_small_batch_prefill(tiny):
     assert sum(int(x == y) for x, y in zip(ta, tb)) >= 5
 
 
-def test_speculative_verify_is_lossless(tiny, same_attention_kernel_for_every_row_count):
+def test_speculative_verify_is_lossless(tiny, same_kernels_for_every_row_count):
     """Windows with correct, partly wrong and fully wrong drafts reproduce the plain greedy stream."""
     from r4dx_b200.models.hybrid import HybridModel
     cfg, q, _ = tiny
@@ -121,7 +121,8 @@ def test_speculative_verify_is_lossless(tiny, same_attention_kernel_for_every_ro
 
 def test_window_rows_match_one_row_steps_within_rounding(tiny):
     """With the default kernels (a dedicated one-token attention kernel) the rows of a verify window equal the rows of
-    one-token steps up to rounding: 1 % of the logit scale."""
+    one-token steps up to rounding (a few tenths of a percent per kernel family; the six-row window also takes the
+    tensor-memory weight-streaming kernel, whose fp32 accumulation differs from the CUDA-core kernel's fp16 partial sums)."""
     from r4dx_b200.models.hybrid import HybridModel
     cfg, q, _ = tiny
     ids = torch.randint(0, cfg.vocab_size, (21,), generator=torch.Generator().manual_seed(5)).to(torch.int32)
@@ -135,8 +136,9 @@ def test_window_rows_match_one_row_steps_within_rounding(tiny):
     assert b.prefill(ids) == seq[0]
     b.feed(torch.tensor(seq[:6], dtype=torch.int32))
     win = b.buf.logits[:6].float().cpu()
-    for i in range(6):
-        assert (win[i] - rows[i]).abs().max().item() < 0.01 * rows[i].abs().max().item()
+    worst = max((win[i] - rows[i]).abs().max().item() / rows[i].abs().max().item() for i in range(6))
+    print("window vs one-row steps, worst relative logit difference:", worst)
+    assert worst < 0.025, worst
 
 
 def test_checkpoint_restore_replays_identically(tiny):
@@ -152,7 +154,7 @@ def test_checkpoint_restore_replays_identically(tiny):
     assert a == b
 
 
-def test_mtp_speculation_equals_plain_greedy(same_attention_kernel_for_every_row_count):
+def test_mtp_speculation_equals_plain_greedy(same_kernels_for_every_row_count):
     """Lossless: with an MTP drafter (random weights -> few accepts) the token stream is the plain greedy one,
     and the drafter's KV stays in lock-step across rounds."""
     from r4dx_b200.models.hybrid import HybridModel
@@ -175,7 +177,7 @@ def test_mtp_speculation_equals_plain_greedy(same_attention_kernel_for_every_row
     assert tm.drafter.head.pos == main.pos - 1
 
 
-def test_mtp_sampled_speculation_equals_plain_sampled_decode(same_attention_kernel_for_every_row_count):
+def test_mtp_sampled_speculation_equals_plain_sampled_decode(same_kernels_for_every_row_count):
     """Sample-and-match: one draw per emitted token from the window's own logits rows, so with one seed the speculative
     stream is the plain sampled stream (the window rows and the single-row step run the same kernels row by row)."""
     from r4dx_b200.models.hybrid import HybridModel
