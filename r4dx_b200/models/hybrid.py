@@ -376,6 +376,36 @@ class HybridModel:
         else:
             self.comm.row_parallel_linear(lin, x, b.x[:T], prologue)
 
+    # race detector for tensor-parallel runs (R4DXB_TP_LOCKSTEP=1): before every forward call the ranks compare a fingerprint
+    # of the call (kind, rows, position, checksum of the staged token ids) on the host and stop at the first difference,
+    # instead of meeting later inside a collective with different shapes
+    lockstep_checks = os.environ.get("R4DXB_TP_LOCKSTEP", "0") == "1"
+
+    def _lockstep(self, kind: int, T: int, ids: torch.Tensor) -> None:
+        if self.lockstep_checks and self.comm is not None and getattr(self.comm, "world", 1) > 1 and hasattr(self.comm, "check_lockstep"):
+            self.comm.check_lockstep(kind, T, int(self.pos), int(ids[:T].to(torch.int64).sum().item()))
+
+    # debug probe: ``probe(layer, residual_rows)`` is called after every layer of an eager call (never inside a captured
+    # graph) - per-layer digests for locating where two runs diverge (utils/probe.py)
+    probe = None
+
+    def state_digest(self) -> Dict[str, float]:
+        """Position and fp64 checksums of every piece of per-sequence state (recurrent states, conv rings, written KV
+        blocks).  Equal digests mean equal state: tests compare them across a checkpoint round trip, a debugging session
+        compares them between two runs or two ranks."""
+        self.commit_pending()
+        d: Dict[str, float] = {"pos": float(self.pos)}
+        blocks = (self.pos + KV_BLOCK - 1) // KV_BLOCK
+        for i, t in self.gdn_state.items():
+            d[f"gdn.{i}"] = float(t.double().sum())
+            d[f"ring.{i}"] = float(self.ring[i].double().sum())
+        if blocks:
+            tab = self.block_table[:blocks].long()
+            live = (torch.arange(blocks * KV_BLOCK, device=self.device) < self.pos).view(blocks, 1, 1, KV_BLOCK, 1)
+            for i, kv in self.kv.items():          # only rows below the position count: later rows of the last block are stale
+                d[f"kv.{i}"] = float((kv[tab].view(torch.uint8).double() * live).sum())
+        return d
+
     _key_limit = None      # per-row key limits of the chunk being prefilled (image blocks on sliding-window layers)
 
     # ---- residual rotation: rows enter the stack through Q and leave it through Q^T -------------------
@@ -392,6 +422,8 @@ class HybridModel:
         """Runs the T rows staged in ``buf.ids`` / ``buf.positions``; results in ``buf.logits`` / ``buf.next_ids``.
         With ``skip_embed`` the caller has already placed the layer-0 input in ``buf.x``."""
         cfg, b, w = self.cfg, self.buf, self.w
+        if not skip_embed:
+            self._lockstep(0, T, b.ids)
         if not skip_embed and self.layer_begin == 0:
             K.embed_gather(b.ids[:T], w["text.embed_tokens"], out=b.x[:T])
             self._enter_stack(b.x[:T])
@@ -406,6 +438,8 @@ class HybridModel:
             else:
                 self._gdn_layer(i, T)
             self._mlp(i, T)
+            if self.probe is not None and not torch.cuda.is_current_stream_capturing():
+                self.probe(i, b.x[:T])
         self._leave_stack(b.x[:T])
         if want_logits and self.layer_end == cfg.num_hidden_layers:
             K.rmsnorm(b.x[:T], w["text.final_norm"], cfg.rms_norm_eps, out=b.h[:T])
@@ -525,6 +559,7 @@ class HybridModel:
         Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
         x, h = cb["x"][:T], cb["h"][:T]
         pos0 = self.pos
+        self._lockstep(1, T, cb["ids"])
         if not skip_embed and self.layer_begin == 0:
             K.embed_gather(cb["ids"][:T], w["text.embed_tokens"], out=x)
             self._enter_stack(x)

@@ -495,3 +495,32 @@ def test_8bit_prefill_products_stay_close_to_the_16bit_prefill(tiny):
     top = la.topk(2).values
     if float(top[0] - top[1]) > 0.1 * la.abs().max().item():
         assert ta == tb
+
+
+def test_layer_digests_locate_a_perturbed_layer_and_state_digests_survive_a_checkpoint(tiny):
+    from r4dx_b200.models.hybrid import HybridModel
+    from r4dx_b200.utils.probe import LayerDigests
+    cfg, q, _ = tiny
+    qd = _to_dev(q)
+    ids = torch.randint(0, cfg.vocab_size, (6,), generator=torch.Generator().manual_seed(1)).to(torch.int32)
+    a, b = HybridModel(cfg, qd, max_ctx=64), HybridModel(cfg, dict(qd), max_ctx=64)
+    da, db = LayerDigests.attach(a), LayerDigests.attach(b)
+    a.feed(ids); b.feed(ids)
+    assert len(da.rows) == cfg.num_hidden_layers and LayerDigests.first_difference(da.rows, db.rows) is None
+    # perturb one norm weight of layer 2 in the second model: the digests part ways exactly there
+    b.w = dict(b.w)
+    b.w["text.layers.2.input_layernorm"] = b.w["text.layers.2.input_layernorm"] + 0.5
+    a.feed(ids[:2]); b.feed(ids[:2])
+    diff = LayerDigests.first_difference(da.rows, db.rows)
+    assert diff is not None and diff["call"] == 1 and diff["layer"] == 2
+    # state digests: equal after the same calls, restored exactly by a checkpoint, changed by further tokens
+    c = HybridModel(cfg, qd, max_ctx=64)
+    c.feed(ids)
+    c.feed(ids[:2])
+    assert c.state_digest() == a.state_digest()
+    ck = a.save_checkpoint()
+    before = a.state_digest()
+    a.feed(ids[:3])
+    assert a.state_digest() != before
+    a.restore_checkpoint(ck)
+    assert a.state_digest() == before

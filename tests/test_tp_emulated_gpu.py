@@ -55,3 +55,31 @@ def test_emulated_ranks_match_the_unsharded_model(world):
     for j in range(1, len(toks)):
         lg = ref.decode_step_logits(toks[j - 1]).view(-1)
         _near_best(lg, toks[j], 0.04, f"decode {j}")
+
+
+def test_lockstep_check_stops_ranks_that_feed_different_tokens():
+    """The race detector: with the fingerprint exchange on, a rank that stages a different token is caught on the host before
+    the ranks meet in a collective; with equal calls nothing fires."""
+    from r4dx_b200.config import small_hybrid_config
+    from r4dx_b200.models.hybrid import HybridModel
+    from r4dx_b200.parallel.shard import shard_weight_set
+    from r4dx_b200.parallel.tp_comm import TpDivergenceError
+    from r4dx_b200.parallel.tp_emulated import EmulatedWorld
+    from r4dx_b200.quant.weights import synthetic_weight_set
+    dev, world = "cuda:0", 2
+    gcfg = dataclasses.replace(small_hybrid_config(layers=2), linear_num_key_heads=8, linear_num_value_heads=16)
+    full = synthetic_weight_set(gcfg, device=dev, seed=3, sigma=0.05)
+
+    def body(bad):
+        def rank_body(rank, comm):
+            m = HybridModel(gcfg.shard(world, rank), shard_weight_set(gcfg, full, world, rank), max_ctx=64, device=dev, comm=comm)
+            m.overlap_siblings = False
+            m.lockstep_checks = True
+            m.feed(torch.tensor([5, 6, 7], dtype=torch.int32))
+            m.feed(torch.tensor([9 if (bad and rank == 1) else 8], dtype=torch.int32))
+            return m.pos
+        return EmulatedWorld(world, dev).run(rank_body)
+
+    assert body(False) == [4, 4]
+    with pytest.raises(TpDivergenceError):
+        body(True)
