@@ -90,7 +90,7 @@ def convert_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser("r4dxb-convert", description="checkpoint -> quantized container")
     ap.add_argument("--input", required=True, help="safetensors file/dir with config.json, or 'random:<tiny|small>'")
     ap.add_argument("--output", required=True)
-    ap.add_argument("--layouts", default="trellis", help="comma list: trellis,w4a16,bf16")
+    ap.add_argument("--layouts", default="trellis", help="body layout: trellis, w4a16, w8a16 or bf16")
     ap.add_argument("--lm-head", default="w4a16", choices=["w4a16", "bf16"])
     ap.add_argument("--lm-head-group", type=int, default=64)
     ap.add_argument("--kb-plan", default="mix4.5", choices=["mix4.5", "mix3.3", "kb3", "kb4", "kb5"])

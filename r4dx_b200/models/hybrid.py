@@ -20,7 +20,7 @@ import torch
 from ..config import ModelConfig
 from ..ops import kernels as K
 from ..quant.trellis import TrellisWeight
-from ..quant.w4a16 import W4Weight
+from ..quant.w4a16 import W4Weight, W8Weight
 
 BF = torch.bfloat16
 MAX_ROWS = 8          # rows per small-batch call (decode = 1, verify window <= 8)
@@ -37,7 +37,7 @@ class Linear:
         if isinstance(w, TrellisWeight):
             self.N, self.K = w.N, w.K
             self.ksplit = K.pick_ksplit(w.N, w.K)
-        elif isinstance(w, W4Weight):
+        elif isinstance(w, (W4Weight, W8Weight)):
             self.N, self.K = w.N, w.K
         else:
             self.N, self.K = w.shape
@@ -48,10 +48,24 @@ class Linear:
         if isinstance(w, TrellisWeight):
             return K.trellis_gemv(w, x, residual=residual, out=out, ksplit=self.ksplit, prologue=prologue,
                                   norm_w=norm_w, eps=eps)
-        if isinstance(w, W4Weight):
-            if residual is not None:
-                raise NotImplementedError("w4a16 with a residual epilogue")
-            return K.w4a16_gemv(w, x, out_f32=(out.dtype == torch.float32), out=out)
+        if isinstance(w, (W4Weight, W8Weight)):
+            # group-quantised layouts: the streaming kernels have no prologue / residual modes, so the producer of the
+            # activations and the residual add are kernels of their own (the w8a16 body of the dense and short-conv
+            # families; reference: docs/w8a16.md)
+            xin = x
+            if prologue == K.PRO_RMSNORM:
+                xin = K.rmsnorm(x, norm_w, eps)           # containers hold every norm weight in the (1 + w) convention
+            elif prologue == K.PRO_SILU_MUL:
+                xin = K.silu_mul(x)
+            elif prologue == K.PRO_GELU_MUL:
+                raise NotImplementedError("GeGLU with a group-quantised down projection")
+            gemv = K.w8a16_gemv if isinstance(w, W8Weight) else K.w4a16_gemv
+            if residual is None:
+                return gemv(w, xin, out_f32=(out.dtype == torch.float32), out=out)
+            tmp = gemv(w, xin, out_f32=False)
+            if residual.data_ptr() != out.data_ptr():
+                out.copy_(residual)
+            return K.residual_add(out, tmp)
         raise NotImplementedError(f"layout of {self.name}")
 
     def many(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
@@ -68,6 +82,13 @@ class Linear:
               fused_silu_mul: bool = False, gelu: bool = False) -> torch.Tensor:
         """Large-T path: input transform (optionally fused with SwiGLU) + tcgen05 GEMM."""
         w = self.w
+        if isinstance(w, (W4Weight, W8Weight)):
+            xin = x
+            if fused_silu_mul:
+                if gelu:
+                    raise NotImplementedError("GeGLU with a group-quantised down projection")
+                xin = K.silu_mul(x)
+            return K.linear_tc(w, xin, residual=residual, out=out)
         if not isinstance(w, TrellisWeight):
             raise NotImplementedError(f"chunk path for layout of {self.name}")
         T = out.shape[0]
@@ -144,7 +165,7 @@ class HybridModel:
         self.w = weights
         self.lin: Dict[str, Linear] = {}
         for name, t in weights.items():
-            if isinstance(t, (TrellisWeight, W4Weight)):
+            if isinstance(t, (TrellisWeight, W4Weight, W8Weight)):
                 self.lin[name] = Linear(t, name)
         # fused [a; b] gate projection per GDN layer
         # residual-stream rotation: a weight set that carries it runs its layers in the basis x Q (quant/rotation.py)

@@ -242,7 +242,33 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       ok = ok && ptx::MbarWait(&aempty[sa], (ra & 1) ^ 1, abort_flag, 5);
       if (!ok) break;
       unsigned char* at = a_ring + sa * kATileBytes;
-      if constexpr (MODE == 2) {
+      if constexpr (MODE == 5) {
+        // w8a16: a lane widens 32 consecutive k of one row (32 offset-binary bytes): a byte b becomes the fp16 1024 + b by
+        // pairing it with 0x64; subtracting 1152 gives b - 128 exactly, the group scale is the only rounding
+        for (int idx = warp; idx < 8; idx += DW) {
+          const int r = idx * 16 + (lane >> 1), half = lane & 1;
+          const size_t n = static_cast<size_t>(nb) * 128 + r;
+          const int kbase = it * kSlabK + half * 32;
+          const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(wsrc) + n * K + kbase);
+          const uint4 q0 = __ldg(src), q1 = __ldg(src + 1);
+          const __half sc = __ldg(reinterpret_cast<const __half*>(pl.wsz) + n * (K / pl.group) + kbase / pl.group);
+          const __half2 sc2 = __half2half2(sc), off2 = __half2half2(__float2half(1152.0f));      // 1024 + 128
+          const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t hb[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const uint32_t w32 = qw[2 * c + (i >> 1)];
+              const uint32_t b = __byte_perm(w32, 0x00000064u, (i & 1) ? 0x4342 : 0x4140);      // (1024 + b_lo, 1024 + b_hi)
+              const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&b), off2), sc2);   // (b - 128) exactly, one rounding
+              hb[i] = *reinterpret_cast<const uint32_t*>(&v);
+            }
+            const int chunk = half * 4 + c;
+            *reinterpret_cast<uint4*>(at + (r >> 3) * 1024 + (r & 7) * 128 + ((chunk ^ (r & 7)) << 4)) = make_uint4(hb[0], hb[1], hb[2], hb[3]);
+          }
+        }
+      } else if constexpr (MODE == 2) {
         // w4a16: a lane widens 32 consecutive k of one row (16 bytes of nibbles): nibble -> fp16 1024 + n by or-ing
         // 0x6400, the stored -(1024 + zero) makes n - zero exact, one fp16 multiply by the group scale
         for (int idx = warp; idx < 8; idx += DW) {
@@ -391,7 +417,7 @@ TrellisGemmKernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
             uint2 ov;
             ov.x = PackBf16(o0, o1);
             ov.y = PackBf16(o2, o3);
-            if ((MODE == 1 || MODE == 2) && pl.out_f32) {
+            if ((MODE == 1 || MODE == 2 || MODE == 5) && pl.out_f32) {
               *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + static_cast<size_t>(t) * N + n) = make_float4(o0, o1, o2, o3);
             } else if (rs.world > 0) {
               const int owner = t / rs.rows_per_rank, tl = t - owner * rs.rows_per_rank;
@@ -693,13 +719,14 @@ int r4dxb_trellis_gemm(const void* w, const void* svh, const void* xh, void* y, 
 
 /* Plain linear on the tensor cores, any number of rows: y[T, N] = x[T, K] W^T (+ bias) (+ residual).
  * kind 0: W is a dense 16-bit [N, K] matrix (bf16 != 0: W and x are bf16, else fp16), N a multiple of 4 and K of 8;
- * kind 1: W is w4a16 (wq nibbles [N][K/8] + wsz [N][K/group]), x is fp16, N and K multiples of 128.
+ * kind 1: W is w4a16 (wq nibbles [N][K/8] + wsz [N][K/group]), x is fp16, N and K multiples of 128;
+ * kind 2: W is w8a16 (offset-binary bytes [N][K] + fp16 scales [N][K/group] passed as wsz), x is fp16, N and K multiples of 128.
  * out_f32: y is fp32 instead of bf16.  act (low byte of out_f32 >> 8): 0 none, 1 tanh-GELU, 2 erf-GELU after the bias. */
 int r4dxb_linear_tc(const void* w, const void* wsz, int kind, int group, int bf16, const void* x, void* y, int out_f32,
                     const void* bias, const void* residual, int T, int N, int K, int tn, int* status, void* stream) {
-  if (T < 1 || N < 4 || K < 8 || kind < 0 || kind > 1) return R4DXB_BAD_ARG;
+  if (T < 1 || N < 4 || K < 8 || kind < 0 || kind > 2) return R4DXB_BAD_ARG;
   if (kind == 0 && (N % 4 || K % 8)) return R4DXB_BAD_ARG;
-  if (kind == 1 && (N % 128 || K % 128 || wsz == nullptr || (group != 32 && group != 64 && group != 128) || bf16))
+  if (kind >= 1 && (N % 128 || K % 128 || wsz == nullptr || (group != 32 && group != 64 && group != 128) || bf16))
     return R4DXB_BAD_ARG;
   PlainArgs pl = {};
   pl.wsz = static_cast<const uint32_t*>(wsz);
@@ -709,6 +736,7 @@ int r4dxb_linear_tc(const void* w, const void* wsz, int kind, int group, int bf1
   pl.out_f32 = out_f32 & 1;
   pl.act = (out_f32 >> 8) & 0xFF;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (kind == 2) return LaunchPlain<5>(w, x, y, residual, T, N, K, tn, status, s, pl);
   return kind == 0 ? LaunchPlain<1>(w, x, y, residual, T, N, K, tn, status, s, pl)
                    : LaunchPlain<2>(w, x, y, residual, T, N, K, tn, status, s, pl);
 }

@@ -14,7 +14,7 @@ import torch
 from .. import native
 from ..native import c_f32, c_i64, c_int, c_ptr, register_cuda_sig
 from ..quant.trellis import TrellisWeight
-from ..quant.w4a16 import W4Weight
+from ..quant.w4a16 import W4Weight, W8Weight
 
 _I = c_int
 _P = c_ptr
@@ -490,12 +490,16 @@ def linear_tc(W, x: torch.Tensor, bias: Optional[torch.Tensor] = None, residual:
               act: int = 0) -> torch.Tensor:
     """y[T, N] = act(x W^T + bias) + residual on the tcgen05 kernel for any number of rows.
 
-    ``W``: a dense bf16 / fp16 [N, K] matrix (x must have the same dtype; N % 4 == 0, K % 8 == 0) or a ``W4Weight``
-    (x bf16 or fp16; bf16 rows are narrowed to fp16 first: the group scales already make the weights fp16; N and K
-    multiples of 128).  ``act``: 0 none, 1 tanh-GELU, 2 erf-GELU.
+    ``W``: a dense bf16 / fp16 [N, K] matrix (x must have the same dtype; N % 4 == 0, K % 8 == 0), a ``W4Weight`` or a
+    ``W8Weight`` (x bf16 or fp16; bf16 rows are narrowed to fp16 first: the group scales already make the weights fp16;
+    N and K multiples of 128).  ``act``: 0 none, 1 tanh-GELU, 2 erf-GELU.
     """
     dev = x.device
-    if isinstance(W, W4Weight):
+    if isinstance(W, W8Weight):
+        N, K_ = W.N, W.K
+        xk = x if x.dtype == torch.float16 else x.to(torch.float16)
+        kind, group, is_bf, wp, szp = 2, W.group, 0, W.wq, W.ws
+    elif isinstance(W, W4Weight):
         N, K_ = W.N, W.K
         xk = x if x.dtype == torch.float16 else x.to(torch.float16)
         kind, group, is_bf, wp, szp = 1, W.group, 0, W.wq, W.wsz
@@ -504,7 +508,7 @@ def linear_tc(W, x: torch.Tensor, bias: Optional[torch.Tensor] = None, residual:
         if W.dtype not in (BF, torch.float16) or x.dtype != W.dtype:
             raise KernelError("linear_tc: W and x must both be bf16 or both fp16")
         xk, kind, group, is_bf, wp, szp = x, 0, 0, int(W.dtype == BF), W, None
-    if (kind == 1 and (N % 128 or K_ % 128)) or N % 4 or K_ % 8:
+    if (kind >= 1 and (N % 128 or K_ % 128)) or N % 4 or K_ % 8:
         raise KernelError(f"linear_tc: unsupported shape N={N}, K={K_}")
     xk = xk.reshape(-1, K_)
     if not xk.is_contiguous():

@@ -66,6 +66,13 @@ class W8Weight:
     K: int
     group: int
 
+    def to(self, device) -> "W8Weight":
+        return W8Weight(self.wq.to(device), self.ws.to(device), self.N, self.K, self.group)
+
+    @property
+    def nbytes(self) -> int:
+        return self.wq.numel() + self.ws.numel() * 2
+
 
 def quantize_w8(W: torch.Tensor, group: int = 64) -> W8Weight:
     L = native.host()

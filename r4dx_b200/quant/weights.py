@@ -17,7 +17,7 @@ from ..config import ModelConfig
 from . import trellis, w4a16
 from .container import Container, write_container
 from .trellis import TrellisWeight
-from .w4a16 import W4Weight
+from .w4a16 import W4Weight, W8Weight
 
 F32_NAMES = ("A_log", "dt_bias", "k_descale", "v_descale", "expert_bias")
 
@@ -70,6 +70,8 @@ def quantize_weight_set(cfg: ModelConfig, w: Dict[str, torch.Tensor], layout: st
                 out[name] = TrellisWeight(tw.words.cpu(), tw.suh.cpu(), tw.svh.cpu(), tw.N, tw.K, tw.kb)
             else:
                 out[name], _ = trellis.quantize(t, kb_rule(name), seed=seed * 100003 + i)
+        elif is_quantized_linear(name) and layout == "w8a16" and t.shape[0] % 128 == 0 and t.shape[1] % 128 == 0:
+            out[name] = w4a16.quantize_w8(t, head_group)          # symmetric int8, fp16 group scales, round to nearest
         elif is_quantized_linear(name) and layout == "w4a16":
             if name in hessians:
                 from .calibrate import gptq_w4a16
@@ -92,6 +94,8 @@ def dequantize_weight_set(q: Dict[str, object]) -> Dict[str, torch.Tensor]:
     for name, t in q.items():
         if isinstance(t, TrellisWeight):
             out[name] = trellis.reconstruct(t)
+        elif isinstance(t, W8Weight):
+            out[name] = w4a16.dequantize_w8(W8Weight(t.wq.cpu(), t.ws.cpu(), t.N, t.K, t.group))
         elif isinstance(t, W4Weight):
             out[name] = w4a16.dequantize(t)
         else:
@@ -210,6 +214,9 @@ def save_weight_set(path: str, cfg: ModelConfig, q: Dict[str, object], extra_met
         if isinstance(t, TrellisWeight):
             quant[name] = {"layout": "trellis", "kb": t.kb, "N": t.N, "K": t.K}
             tensors += [(name + ".trellis.words", t.words), (name + ".trellis.suh", t.suh), (name + ".trellis.svh", t.svh)]
+        elif isinstance(t, W8Weight):
+            quant[name] = {"layout": "w8a16", "group": t.group, "N": t.N, "K": t.K}
+            tensors += [(name + ".w8a16.wq", t.wq), (name + ".w8a16.ws", t.ws)]
         elif isinstance(t, W4Weight):
             quant[name] = {"layout": "w4a16", "group": t.group, "N": t.N, "K": t.K}
             tensors += [(name + ".w4a16.wq", t.wq), (name + ".w4a16.wsz", t.wsz)]
@@ -241,11 +248,13 @@ def load_weight_set(path: str, device="cpu", names: Optional[Callable[[str], boo
         if qi["layout"] == "trellis":
             out[name] = TrellisWeight(ct_get.tensor(name + ".trellis.words"), ct_get.tensor(name + ".trellis.suh"),
                                       ct_get.tensor(name + ".trellis.svh"), qi["N"], qi["K"], qi["kb"])
+        elif qi["layout"] == "w8a16":
+            out[name] = W8Weight(ct_get.tensor(name + ".w8a16.wq"), ct_get.tensor(name + ".w8a16.ws"), qi["N"], qi["K"], qi["group"])
         else:
             out[name] = W4Weight(ct_get.tensor(name + ".w4a16.wq"), ct_get.tensor(name + ".w4a16.wsz"),
                                  qi["N"], qi["K"], qi["group"])
     for name in ct.names:
-        if ".trellis." in name or ".w4a16." in name:
+        if ".trellis." in name or ".w4a16." in name or ".w8a16." in name:
             continue
         if names and not names(name):
             continue

@@ -133,3 +133,16 @@ def test_converter_keeps_a_vision_tower_and_imports_a_drafter(tmp_path):
     hv = import_hf_vision({"model.visual.patch_embed.proj.weight": torch.zeros(144, 3, 2, 8, 8), "model.visual.blocks.0.attn.qkv.bias": torch.zeros(432),
                            "model.visual.merger.linear_fc2.weight": torch.zeros(256, 576), "model.language_model.x": torch.zeros(1)})
     assert set(hv) == {"patch_embed.weight", "blocks.0.qkv.bias", "merger.fc2.weight"} and hv["patch_embed.weight"].shape == (144, 384)
+
+
+def test_converter_writes_and_reads_the_w8a16_body_layout(tmp_path):
+    from r4dx_b200.cli.convert import main as convert
+    from r4dx_b200.quant.w4a16 import W8Weight
+    from r4dx_b200.quant.weights import dequantize_weight_set, load_weight_set
+    out = str(tmp_path / "w8.r4dxb")
+    assert convert(["--input", "random:llama", "--output", out, "--layouts", "w8a16", "--selftest"]) == 0
+    cfg, q = load_weight_set(out)
+    body = [k for k, v in q.items() if isinstance(v, W8Weight)]
+    assert len(body) >= 6 * cfg.num_hidden_layers and all(q[k].wq.dtype == torch.uint8 for k in body)
+    dq = dequantize_weight_set(q)
+    assert dq[body[0]].shape == (q[body[0]].N, q[body[0]].K)

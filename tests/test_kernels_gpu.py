@@ -792,3 +792,20 @@ def test_viterbi_quantized_layer_times_like_a_random_code_layer(K):
     a2, b2 = med(tqd), med(tr)                      # interleaved repeats guard against drift between the two series
     ta, tb = min(a, a2), min(b, b2)
     assert abs(ta - tb) <= 0.02 * max(ta, tb) + 0.0003, (ta, tb)     # 2 % plus the event timer's 0.3 us granularity
+
+
+@pytest.mark.parametrize("T,N,Kd,group", [(20, 256, 512, 64), (300, 384, 1024, 128)])
+def test_linear_tc_w8a16_matches_fp32_reference(K, T, N, Kd, group):
+    from r4dx_b200.quant import w4a16
+    g = torch.Generator().manual_seed(T)
+    W = torch.randn(N, Kd, generator=g) * 0.05
+    w = w4a16.quantize_w8(W, group)
+    Wd = w4a16.dequantize_w8(w)
+    x = torch.randn(T, Kd, generator=g).to(BF)
+    res = torch.randn(T, N, generator=g).to(BF)
+    ref = x.half().float() @ Wd.T
+    y = K.linear_tc(w.to("cuda"), x.cuda(), out_f32=True)
+    K.check_gemm_status(y.device)
+    assert torch.allclose(y.cpu(), ref, atol=2e-2, rtol=1e-2)
+    y2 = K.linear_tc(w.to("cuda"), x.cuda(), residual=res.cuda())
+    assert torch.allclose(y2.float().cpu(), ref + res.float(), atol=6e-2, rtol=2e-2)

@@ -524,3 +524,34 @@ def test_layer_digests_locate_a_perturbed_layer_and_state_digests_survive_a_chec
     assert a.state_digest() != before
     a.restore_checkpoint(ck)
     assert a.state_digest() == before
+
+
+def test_llama_family_in_the_w8a16_layout_matches_its_oracle():
+    """Symmetric int8 body weights with fp16 group scales: small-batch path (streaming kernel + separate norm / SwiGLU /
+    add kernels), chunked prefill (tensor-core linear with the bytes widened by the decode warps) and graph decode."""
+    from r4dx_b200.config import tiny_llama_config
+    from r4dx_b200.models.hybrid import HybridModel
+    from r4dx_b200.models.oracle import OracleModel, init_weights
+    from r4dx_b200.quant.w4a16 import W8Weight
+    from r4dx_b200.quant.weights import dequantize_weight_set, quantize_weight_set
+    cfg = tiny_llama_config()
+    q = quantize_weight_set(cfg, init_weights(cfg, 2), layout="w8a16")
+    assert sum(isinstance(v, W8Weight) for v in q.values()) >= 6 * cfg.num_hidden_layers
+    oracle = OracleModel(cfg, dequantize_weight_set(q), fp8_kv=True)
+    ids = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(5))
+    ref, _ = oracle.forward(ids)
+    qd = _to_dev(q)
+    m = HybridModel(cfg, qd, max_ctx=128)
+    rows = []
+    for s in range(0, 40, 8):
+        m.feed(ids[s:s + 8].to(torch.int32))
+        rows.append(m.logits_rows(8).float().cpu().clone())
+    got = torch.cat(rows)
+    scale = ref.abs().max().item()
+    assert (got - ref).abs().max().item() < 0.05 * scale
+    c = HybridModel(cfg, qd, max_ctx=128)
+    c.prefill(ids.to(torch.int32))
+    assert (c.buf.logits[0].float().cpu() - ref[-1]).abs().max().item() < 0.05 * scale
+    a = HybridModel(cfg, qd, max_ctx=128).generate_greedy(ids.to(torch.int32), 6, use_graph=True)
+    b = HybridModel(cfg, qd, max_ctx=128).generate_greedy(ids.to(torch.int32), 6, use_graph=False)
+    assert a == b
