@@ -91,6 +91,79 @@ __global__ void MoePlanKernel(const int* __restrict__ ids, int npairs, int E, in
   }
 }
 
+// The same plan for many pairs (prefill chunks, wide batches): one CTA of 32 warps, warp w owns a contiguous run of the
+// pairs.  Pass 1 counts per (warp, expert), a prefix over experts and warps turns the counts into each warp's first slot
+// per expert, pass 2 places the pairs; inside a 32-pair step the lanes of one expert are ranked with match_any, so the
+// order inside an expert is the pair order, exactly as the serial kernel leaves it.
+constexpr int kPlanWarps = 32;
+__global__ void __launch_bounds__(kPlanWarps * 32)
+MoePlanParallelKernel(const int* __restrict__ ids, int npairs, int e_begin, int e_count, int* __restrict__ offsets,
+                      int* __restrict__ perm) {
+  extern __shared__ int sm[];                  // [kPlanWarps][e_count] counts / cursors, then [e_count + 1] offsets
+  int* hist = sm;
+  int* offs = sm + kPlanWarps * e_count;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kPlanWarps * e_count; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+  const int per = ((npairs + kPlanWarps - 1) / kPlanWarps + 31) & ~31;       // pairs per warp, a multiple of 32
+  const int p0 = warp * per, p1 = min(npairs, p0 + per);
+  int* mine = hist + warp * e_count;
+  for (int base = p0; base < p1; base += 32) {
+    const int p = base + lane;
+    int e = p < p1 ? ids[p] - e_begin : -1;
+    if (e >= e_count) e = -1;
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && lane == __ffs(same) - 1) mine[e] += __popc(same);
+    __syncwarp();
+  }
+  __syncthreads();
+  // per expert: total, then each warp's first slot
+  for (int e = threadIdx.x; e < e_count; e += blockDim.x) {
+    int tot = 0;
+    for (int w = 0; w < kPlanWarps; ++w) tot += hist[w * e_count + e];
+    offs[e + 1] = tot;
+  }
+  if (threadIdx.x == 0) offs[0] = 0;
+  __syncthreads();
+  if (warp == 0) {                             // inclusive scan over the experts by one warp
+    int carry = 0;
+    for (int b = 0; b < e_count; b += 32) {
+      const int e = b + lane;
+      int v = e < e_count ? offs[e + 1] : 0;
+      for (int d = 1; d < 32; d <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, v, d);
+        if (lane >= d) v += u;
+      }
+      if (e < e_count) offs[e + 1] = v + carry;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= e_count; e += blockDim.x) offsets[e] = offs[e];
+  for (int e = threadIdx.x; e < e_count; e += blockDim.x) {
+    int at = offs[e];
+    for (int w = 0; w < kPlanWarps; ++w) {
+      const int c = hist[w * e_count + e];
+      hist[w * e_count + e] = at;              // becomes the warp's cursor
+      at += c;
+    }
+  }
+  __syncthreads();
+  for (int base = p0; base < p1; base += 32) {
+    const int p = base + lane;
+    int e = p < p1 ? ids[p] - e_begin : -1;
+    if (e >= e_count) e = -1;
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    if (e >= 0) {
+      const int rank = __popc(same & ((1u << lane) - 1u));
+      perm[mine[e] + rank] = p;
+    }
+    __syncwarp();
+    if (e >= 0 && lane == __ffs(same) - 1) mine[e] += __popc(same);
+    __syncwarp();
+  }
+}
+
 // grid T, block 256: out[t] = residual + sum_j w_j y[pair] (ascending expert id) + sigmoid(sg) * shared
 __global__ void MoeCombineKernel(const __nv_bfloat16* __restrict__ y_pairs, const int* __restrict__ ids,
                                  const float* __restrict__ weights, const __nv_bfloat16* __restrict__ shared,
@@ -159,6 +232,16 @@ int r4dxb_moe_router_sigmoid(const float* logits, const float* bias, int T, int 
 /* offsets: [e_count + 1], perm: [npairs] pair indices sorted by expert (only experts in [e_begin, e_begin+e_count)) */
 int r4dxb_moe_plan(const int* ids, int npairs, int E, int e_begin, int e_count, int* offsets, int* perm, void* stream) {
   if (npairs < 1 || e_count < 1 || e_count > 8192) return R4DXB_BAD_ARG;
+  const size_t big = (static_cast<size_t>(kPlanWarps) * e_count + e_count + 1) * sizeof(int);
+  if (npairs > 1024 && big <= 200 * 1024) {
+    // many pairs: the serial placement of the small kernel would take milliseconds (2 ms for 40960 pairs)
+    if (big > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(MoePlanParallelKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(big));
+      if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    MoePlanParallelKernel<<<1, kPlanWarps * 32, big, static_cast<cudaStream_t>(stream)>>>(ids, npairs, e_begin, e_count, offsets, perm);
+    return FinishLaunch();
+  }
   MoePlanKernel<<<1, 256, (e_count + 1) * sizeof(int), static_cast<cudaStream_t>(stream)>>>(ids, npairs, E, e_begin, e_count,
                                                                                              offsets, perm);
   return FinishLaunch();

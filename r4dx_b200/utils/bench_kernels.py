@@ -116,6 +116,42 @@ def main() -> None:
                     tf8 = 2.0 * N * Kd * Tg / us8 / 1e6
                     print(f"trellis_gemm_f8 {name:9s} N={N:6d} K={Kd:6d} kb={kb} T={Tg} tn={tn8}: {us8:9.1f} us  "
                           f"{tf8:7.1f} TFLOP/s effective  {tf8 / tf_peak:5.2f} of measured cuBLAS bf16  (+ {usq:.1f} us row quantizer)")
+    if a.only in ("linear_tc",):
+        # plain tensor-core linear: the w4a16 head over a wide batch, a w4a16 drafter product, dense vision-tower products
+        Tg = max(a.rows, 16)
+        for label, N, Kd, kind in (("head w4a16", 248320, 5120, "w4"), ("drafter gate_up w4a16", 27648, 5120, "w4"),
+                                   ("vision qkv bf16", 3456, 1152, "bf16"), ("vision fc1 bf16", 4304, 1152, "bf16")):
+            if kind == "w4":
+                W = w4a16.random_weight(N, Kd, 64, device=dev)
+            else:
+                W = (torch.randn(N, Kd, device=dev) * 0.03).to(BF)
+            x = torch.randn(Tg, Kd, device=dev).to(BF)
+            y = torch.empty(Tg, N, dtype=BF, device=dev)
+            us = timed(lambda: K.linear_tc(W, x, out=y), a.iters, flush)
+            K.check_gemm_status(dev)
+            print(f"linear_tc {label:22s} N={N:6d} K={Kd:5d} T={Tg}: {us:8.1f} us  {2.0 * N * Kd * Tg / us / 1e6:7.1f} TFLOP/s")
+    if a.only in ("moe_grouped",):
+        # one mixture-of-experts block of the 512-expert geometry on a.rows rows (grouped tensor-core path above 16 rows)
+        from r4dx_b200.config import qwen_hybrid_moe_config
+        from r4dx_b200.models import moe as M
+        cfg = qwen_hybrid_moe_config(1)
+        H, I, E = cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts
+        p = "text.layers.0.moe."
+        gu0, dn0 = trellis.random_weight(2 * I, H, 3, seed=1, device=dev), trellis.random_weight(H, I, 3, seed=2, device=dev)
+        wts = {p + f"experts.{e}.gate_up": gu0 for e in range(E)}
+        wts.update({p + f"experts.{e}.down": dn0 for e in range(E)})
+        wts[p + "router"] = (torch.randn(E, H, device=dev) * 0.5).to(BF)
+        wts[p + "shared_gate"] = (torch.randn(1, H, device=dev) * 0.02).to(BF)
+        wts[p + "shared.gate_up"] = trellis.random_weight(2 * cfg.shared_expert_intermediate_size, H, 4, seed=3, device=dev)
+        wts[p + "shared.down"] = trellis.random_weight(H, cfg.shared_expert_intermediate_size, 4, seed=4, device=dev)
+        Tm = max(a.rows, 17)
+        blk = M.MoeBlock(cfg, wts, 0, dev, Tm)
+        h = torch.randn(Tm, H, device=dev).to(BF)
+        xr = torch.zeros(Tm, H, device=dev, dtype=BF)
+        us = timed(lambda: blk.forward(h, xr, Tm), a.iters, flush)
+        K.check_gemm_status(dev)
+        print(f"moe block (512 experts top-10, hidden {H}, inner {I}) T={Tm}: {us:8.1f} us  "
+              f"{2.0 * Tm * cfg.num_experts_per_tok * 3 * I * H / us / 1e6:6.1f} TFLOP/s over the routed experts")
     if a.only in ("", "w4a16"):
         N, Kd = 248320, 5120
         w = w4a16.random_weight(N, Kd, 64, device=dev)

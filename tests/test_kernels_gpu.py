@@ -551,6 +551,25 @@ def test_moe_router_plan_combine(K):
     assert torch.allclose(out.float().cpu(), ref, atol=3e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("npairs,E,e_begin,e_count", [(40960, 512, 0, 512), (5000, 64, 16, 32), (1025, 8, 0, 8), (20000, 128, 64, 64)])
+def test_moe_plan_many_pairs(K, npairs, E, e_begin, e_count):
+    """Prefill-sized plans take the 32-warp kernel: same offsets and the same stable order as a stable sort."""
+    g = torch.Generator().manual_seed(npairs)
+    flat = torch.randint(0, E, (npairs,), generator=g, dtype=torch.int32)
+    flat[:40] = e_begin                                        # one expert with a run that spans lanes of one step
+    off = torch.zeros(e_count + 1, dtype=torch.int32, device="cuda")
+    perm = torch.full((npairs,), -1, dtype=torch.int32, device="cuda")
+    K.moe_plan(flat.cuda(), npairs, E, e_begin, e_count, off, perm)
+    local = (flat >= e_begin) & (flat < e_begin + e_count)
+    idx = torch.nonzero(local).view(-1)
+    order = idx[torch.sort(flat[idx], stable=True).indices]
+    n = int(local.sum())
+    assert torch.equal(perm.cpu()[:n].long(), order)
+    assert bool((perm.cpu()[n:] == -1).all())
+    counts = torch.bincount((flat[idx] - e_begin).long(), minlength=e_count)
+    assert off.cpu().tolist() == [0] + torch.cumsum(counts, 0).tolist()
+
+
 def test_grouped_expert_gemv(K):
     from r4dx_b200.models.moe import ExpertStack
     from r4dx_b200.quant import trellis
