@@ -134,7 +134,8 @@ class MoeBlock:
         g, d = self.gate_up, self.down
         P = T * self.k
         avg = max(1, P // max(1, min(self.e_count, self.cfg.num_experts)))
-        tn = 16 if avg <= 12 else (32 if avg <= 24 else (64 if avg <= 48 else 128))
+        # the weights of an expert are decoded once per token tile, so a tile should hold all of an expert's rows
+        tn = 16 if avg <= 12 else (32 if avg <= 24 else (64 if avg <= 48 else (128 if avg <= 100 else 256)))
         K.moe_tiles(self.offsets, self.e_count, tn, self.tiles, self.ntiles)
         xh = self.xh_pairs.view(-1)[:P * g.K].view(P, g.K)
         K.trellis_input_grouped(h, g.suh, xh, self.offsets, self.perm, P, self.k, 0)

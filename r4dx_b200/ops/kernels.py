@@ -705,8 +705,10 @@ def trellis_input_grouped(x: torch.Tensor, suh: torch.Tensor, out: torch.Tensor,
 
 def trellis_gemm_grouped(words, svh, xh, y, offsets, perm, tiles, ntiles, P: int, E: int, N: int, Kd: int, kb: int, tn: int):
     """y[perm[p]] = expert e(p)'s trellis linear of the transformed row xh[p]; one launch for every expert."""
+    # grid height: no plan of P pairs over E experts has more than P / tn + E tiles (CTAs past the plan's count leave at once)
+    bound = min(tiles.numel() // 2, P // tn + E)
     _check(_lib().r4dxb_trellis_gemm_grouped(_p(words), _p(svh), _p(xh), _p(y), _p(offsets), _p(perm), _p(tiles), _p(ntiles),
-                                             tiles.numel() // 2, P, E, N, Kd, kb, tn, _p(gemm_status(xh.device)), _stream()),
+                                             bound, P, E, N, Kd, kb, tn, _p(gemm_status(xh.device)), _stream()),
            "trellis_gemm_grouped")
     return y
 

@@ -53,7 +53,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--kb", type=int, default=0)
     ap.add_argument("--ctx", type=int, default=8192)
-    ap.add_argument("--decode-warps", type=int, default=16)
+    ap.add_argument("--decode-warps", type=int, default=0, help="4, 8 or 16; 0 leaves the library's own choice")
     ap.add_argument("--tn", type=int, default=0)
     ap.add_argument("--ksplit", type=int, default=0, help="override the cluster split of the weight-streaming kernel")
     ap.add_argument("--f8", action="store_true", help="with --only trellis_gemm: also time the 8-bit (e4m3 x e4m3) product")
@@ -132,7 +132,9 @@ def main() -> None:
             print(f"linear_tc {label:22s} N={N:6d} K={Kd:5d} T={Tg}: {us:8.1f} us  {2.0 * N * Kd * Tg / us / 1e6:7.1f} TFLOP/s")
     if a.only in ("moe_grouped",):
         # one mixture-of-experts block of the 512-expert geometry on a.rows rows (grouped tensor-core path above 16 rows)
+        from r4dx_b200 import native
         from r4dx_b200.config import qwen_hybrid_moe_config
+        native.cuda().r4dxb_set_gemm_decode_warps(a.decode_warps)
         from r4dx_b200.models import moe as M
         cfg = qwen_hybrid_moe_config(1)
         H, I, E = cfg.hidden_size, cfg.moe_intermediate_size, cfg.num_experts

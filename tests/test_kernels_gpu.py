@@ -593,7 +593,7 @@ def test_grouped_expert_gemv(K):
             assert (got - ref).abs().max().item() < 0.03 * ref.abs().max().item() + 1e-3
 
 
-@pytest.mark.parametrize("kb,tn,T", [(3, 16, 40), (4, 32, 90), (5, 64, 150)])
+@pytest.mark.parametrize("kb,tn,T", [(3, 16, 40), (4, 32, 90), (5, 64, 150), (3, 128, 300), (4, 256, 700)])
 def test_grouped_expert_gemm_matches_the_per_pair_reference(K, kb, tn, T):
     """Tile list + grouped input transform + grouped tensor-core product (gate_up then SwiGLU + down) for a skewed plan:
     one expert holds a third of the rows (several tiles), some hold none, a slice of the experts is local."""
