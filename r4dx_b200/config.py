@@ -60,6 +60,22 @@ class ModelConfig:
     num_dense_layers: int = 0          # the first layers keep a dense gated MLP in a MoE model
     # short-conv layers ("conv" in layer_types): y = C * causal_fir(B * x), taps per channel
     short_conv_taps: int = 3
+    # qwen4_exp extras (reference: docs/qwen4exp-plan.md 2.2-2.4): gated multi-stream residual, hashed n-gram embedding
+    # layer, block-indexed sparse attention; all off (0 / empty) for the other families
+    hc_count: int = 0                  # residual streams (4); 0 = the plain single-stream residual
+    hc_lowrank: int = 0                # width of the gate's low-rank bottleneck (320)
+    ple_layers: List[int] = field(default_factory=list)   # 0-indexed layers that add the n-gram embedding block first
+    ple_embed_dim: int = 0             # ngram_heads * ngram_head_dim
+    ple_conv_kernel: int = 4
+    ple_conv_dilation: int = 3
+    ngram_heads: int = 16              # half of them hash 2-grams, the other half 3-grams
+    indexer_heads: int = 0             # > 0: attention layers select key blocks with an indexer (QSA)
+    indexer_dim: int = 128
+    indexer_ratio: int = 4             # tokens per key block
+    indexer_budget: int = 2048         # selected tokens: the top budget / ratio complete blocks, plus the open tail
+    gdn_gate_act: str = "silu"         # output gate of the GDN norm: "silu" | "sigmoid"
+    final_norm: bool = True            # False: the stack ends in the final stream mixer, no norm before the head
+    eos_token_id: int = -1             # n-gram history is cut at this token
     # tensor parallel view
     tp_world: int = 1
     tp_rank: int = 0
@@ -145,9 +161,27 @@ class ModelConfig:
     def num_attention_layers(self) -> int:
         return sum(1 for t in self.layer_types if t == "full_attention")
 
+    @property
+    def is_qwen4_exp(self) -> bool:
+        return self.hc_count > 0
+
+    @property
+    def ngram_head_dim(self) -> int:
+        return self.ple_embed_dim // max(1, self.ngram_heads)
+
     def validate(self) -> None:
         if len(self.layer_types) != self.num_hidden_layers:
             raise ValueError("layer_types length != num_hidden_layers")
+        if self.hc_count:
+            if self.hc_lowrank < 1 or self.ple_embed_dim % max(1, self.ngram_heads) or self.ngram_heads % 2:
+                raise ValueError("qwen4_exp: hc_lowrank, ple_embed_dim / ngram_heads")
+            if any(not 0 <= i < self.num_hidden_layers for i in self.ple_layers):
+                raise ValueError("qwen4_exp: ple_layers out of range")
+            if self.indexer_heads and (self.indexer_budget % self.indexer_ratio or self.indexer_dim % 32 or self.indexer_dim > 128
+                                       or self.rotary_dim > self.indexer_dim):
+                raise ValueError("qwen4_exp: indexer geometry")
+            if self.gdn_gate_act not in ("silu", "sigmoid"):
+                raise ValueError("gdn_gate_act")
         if self.num_attention_heads % max(1, self.num_key_value_heads):
             raise ValueError("attention heads not a multiple of KV heads")
         if self.linear_num_value_heads % max(1, self.linear_num_key_heads):
@@ -224,6 +258,19 @@ class ModelConfig:
             d = d["text_config"]
         known = {f.name for f in dataclasses.fields(ModelConfig)}
         cfg = ModelConfig(**{k: v for k, v in d.items() if k in known})
+        if d.get("model_type") == "qwen4_exp" and "arch" not in d:
+            # the checkpoint's own key names (reference: src/model/qwen4exp_config.h:1-110); ple_layer_ids is 1-indexed there
+            cfg.arch = "qwen4_exp"
+            cfg.ple_layers = [int(i) - 1 for i in d.get("ple_layer_ids", [])]
+            cfg.ple_conv_kernel = int(d.get("ple_conv_kernel_size", 4))
+            cfg.ple_conv_dilation = int(d.get("ngram_size", 3))
+            cfg.indexer_heads = int(d.get("indexer_heads", d.get("index_n_heads", 4)))
+            cfg.indexer_dim = int(d.get("indexer_head_dim", d.get("index_head_dim", 128)))
+            cfg.indexer_ratio = int(d.get("indexer_compress_ratio", 4))
+            cfg.indexer_budget = int(d.get("indexer_budget", 2048))
+            cfg.gdn_gate_act = str(d.get("output_gate_type", "sigmoid"))
+            cfg.final_norm = False
+            cfg.mtp_num_hidden_layers = 0
         if not cfg.layer_types and cfg.num_hidden_layers:
             interval = int(d.get("full_attention_interval", 4))
             cfg.layer_types = ["full_attention" if (i + 1) % interval == 0 else "linear_attention"
@@ -345,3 +392,31 @@ def tiny_moe_config() -> ModelConfig:
         linear_key_head_dim=64, linear_value_head_dim=64, vocab_size=4096,
         num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128,
         shared_expert_intermediate_size=128, mtp_num_hidden_layers=0)
+
+
+def qwen4_exp_config(layers: int = 48) -> ModelConfig:
+    """The 4-stream MoE geometry: GDN + block-indexed sparse attention, 512 experts top-10 + shared expert, gated
+    multi-stream residual, one n-gram embedding layer (reference: docs/qwen4exp-plan.md 2.1-2.4)."""
+    return ModelConfig(
+        arch="qwen4_exp", hidden_size=2560, num_hidden_layers=layers, layer_types=_pattern(layers),
+        num_attention_heads=24, num_key_value_heads=2, head_dim=256, intermediate_size=0,
+        linear_num_key_heads=16, linear_num_value_heads=48, linear_key_head_dim=128, linear_value_head_dim=128,
+        vocab_size=248320, num_experts=512, num_experts_per_tok=10, moe_intermediate_size=640,
+        shared_expert_intermediate_size=640, mtp_num_hidden_layers=0, mrope_section=[11, 11, 10],
+        hc_count=4, hc_lowrank=320, ple_layers=[1] if layers > 1 else [], ple_embed_dim=2560, ngram_heads=16,
+        indexer_heads=4, indexer_dim=128, indexer_ratio=4, indexer_budget=2048, gdn_gate_act="sigmoid", final_norm=False,
+        eos_token_id=248044)
+
+
+def tiny_qwen4_exp_config() -> ModelConfig:
+    """4 layers (GDN, GDN with the n-gram block, GDN, sparse attention) small enough for the CPU oracle; the indexer's
+    budget is 16 tokens, so a prompt of a few dozen tokens already exercises the block selection."""
+    return ModelConfig(
+        arch="qwen4_exp", hidden_size=256, num_hidden_layers=4, layer_types=_pattern(4),
+        num_attention_heads=4, num_key_value_heads=2, head_dim=64, intermediate_size=0,
+        linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=64, linear_value_head_dim=64,
+        vocab_size=4096, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=128,
+        shared_expert_intermediate_size=128, mtp_num_hidden_layers=0,
+        hc_count=4, hc_lowrank=32, ple_layers=[1], ple_embed_dim=256, ngram_heads=16,
+        indexer_heads=2, indexer_dim=64, indexer_ratio=4, indexer_budget=16, gdn_gate_act="sigmoid", final_norm=False,
+        eos_token_id=7)

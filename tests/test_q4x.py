@@ -1,0 +1,183 @@
+"""qwen4_exp family on the CPU: n-gram ids and table file, the oracle's stream gate, n-gram layer and block-selecting
+attention (chunking invariance, the dense limit, the tie rule)."""
+import dataclasses
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from r4dx_b200.config import ModelConfig, qwen4_exp_config, tiny_qwen4_exp_config
+from r4dx_b200.models.q4x_oracle import Q4xOracle, Q4xState, init_q4x_weights, select_blocks
+from r4dx_b200.runtime import ngram as NG
+
+
+@pytest.fixture(scope="module")
+def table(tmp_path_factory):
+    cfg = tiny_qwen4_exp_config()
+    path = str(tmp_path_factory.mktemp("ngram") / "tiny.r4dx-ngram")
+    NG.synthetic_sidecar(path, cfg.vocab_size, cfg.ngram_head_dim, cfg.eos_token_id, seed=3)
+    t = NG.NgramTable.open(path, mode="file")
+    yield t
+    t.close()
+
+
+def rows_fn(table):
+    def f(tokens, history):
+        ids = np.asarray(NG.ngram_ids_reference(tokens, table.header, history), dtype=np.int64)
+        return table.rows(ids).reshape(len(tokens), -1)
+    return f
+
+
+def test_config_presets_and_json_round_trip():
+    for c in (tiny_qwen4_exp_config(), qwen4_exp_config()):
+        c.validate()
+        assert ModelConfig.from_json(c.to_json()) == c
+    c = qwen4_exp_config()
+    assert c.is_qwen4_exp and c.ple_layers == [1] and c.num_attention_layers() == 12 and c.ngram_head_dim == 160
+    bad = dataclasses.replace(tiny_qwen4_exp_config(), indexer_budget=18)
+    with pytest.raises(ValueError):
+        bad.validate()
+    hf = {"model_type": "qwen4_exp", "text_config": {"model_type": "qwen4_exp", "hidden_size": 256, "num_hidden_layers": 4,
+          "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "linear_num_key_heads": 2, "linear_num_value_heads": 4,
+          "linear_key_head_dim": 64, "linear_value_head_dim": 64, "vocab_size": 4096, "num_experts": 16, "num_experts_per_tok": 4,
+          "moe_intermediate_size": 128, "shared_expert_intermediate_size": 128, "hc_count": 4, "hc_lowrank": 32,
+          "ple_layer_ids": [2], "ple_embed_dim": 256, "ngram_size": 3, "indexer_budget": 16, "indexer_heads": 2,
+          "indexer_head_dim": 64, "output_gate_type": "sigmoid"}}
+    import json
+    c = ModelConfig.from_json(json.dumps(hf))
+    assert c.arch == "qwen4_exp" and c.ple_layers == [1] and c.gdn_gate_act == "sigmoid" and not c.final_norm
+
+
+def test_ngram_header_round_trip_and_refusals(table, tmp_path):
+    h = table.header
+    assert NG.NgramHeader.parse(h.pack()) == h
+    assert table.verify_sha256()
+    raw = bytearray(h.pack())
+    raw[0] = ord("X")
+    with pytest.raises(NG.NgramError, match="magic"):
+        NG.NgramHeader.parse(bytes(raw))
+    raw = bytearray(h.pack())
+    raw[400] = 1
+    with pytest.raises(NG.NgramError, match="padding"):
+        NG.NgramHeader.parse(bytes(raw))
+    short = tmp_path / "short.r4dx-ngram"
+    data = open(table.path, "rb").read()
+    short.write_bytes(data[:-h.row_bytes * 3])
+    with pytest.raises(NG.NgramError, match="bytes on disk"):
+        NG.NgramTable.open(str(short), mode="file")
+    t = NG.NgramTable.open(str(short), mode="file", allow_truncated=True)
+    with pytest.raises(NG.NgramError, match="could not be read"):
+        t.rows(np.asarray([h.rows - 1], dtype=np.int64))          # a short read is an error, never a zero row
+    t.close()
+
+
+def test_ngram_ids_native_equal_reference_for_any_chunking(table):
+    h = table.header
+    eos = h.eos_token_id
+    g = torch.Generator().manual_seed(0)
+    toks = torch.randint(0, 4096, (200,), generator=g).tolist()
+    for at in (5, 6, 40, 41, 43, 120):
+        toks[at] = eos
+    want = NG.ngram_ids_reference(toks, h)
+    gen = NG.NgramIds(h)
+    assert gen.generate(toks).tolist() == want
+    gen.reset()
+    got, at = [], 0
+    for n in (1, 1, 7, 1, 64, 3, 123):
+        got += gen.generate(toks[at:at + n]).tolist()
+        at += n
+    assert got == want
+    # segmentation: right after an end-of-sequence token the 3-gram sees it twice, whatever came before it
+    a = NG.ngram_ids_reference([11, eos, 5], h)[2]
+    b = NG.ngram_ids_reference([99, eos, 5], h)[2]
+    c = NG.ngram_ids_reference([5], h)[0]
+    assert a == b == c
+    x = NG.ngram_ids_reference([11, 12, 5], h)[2]
+    y = NG.ngram_ids_reference([99, 12, 5], h)[2]
+    assert x[:8] == y[:8] and x[8:] != y[8:]                      # 2-gram heads ignore the token two back
+    for row in want:
+        for hd, i in enumerate(row):
+            assert h.head_offsets[hd] <= i < h.head_offsets[hd] + h.head_primes[hd]
+    with pytest.raises(NG.NgramError):
+        gen.generate([-1])
+    snap = gen.snapshot()
+    r1 = gen.generate([3, 4]).tolist()
+    gen.restore(snap)
+    assert gen.generate([3, 4]).tolist() == r1
+
+
+def test_table_placements_agree(table):
+    toks = [1, 2, 3, 7, 9, 10]
+    a = table.gather_host(toks)
+    t2 = NG.NgramTable.open(table.path, mode="pinned", device="cpu")
+    b = t2.gather_host(toks)
+    t2.close()
+    assert a.shape == (6, 256) and torch.equal(a, b)
+
+
+def test_select_blocks_prefers_recent_blocks_on_ties():
+    s = torch.tensor([0.0, 2.0, 0.0, 2.0, 0.0, 1.0, 0.0])
+    assert select_blocks(s, 3).tolist() == [1, 3, 5]
+    assert select_blocks(s, 4).tolist() == [1, 3, 5, 6]           # among the zero scores the latest block wins
+    assert select_blocks(s, 6).tolist() == [1, 2, 3, 4, 5, 6]
+
+
+@pytest.fixture(scope="module")
+def tiny(table):
+    cfg = tiny_qwen4_exp_config()
+    w = init_q4x_weights(cfg, seed=1)
+    return cfg, w, Q4xOracle(cfg, w, rows_fn(table))
+
+
+def test_oracle_is_chunking_invariant_and_selects_blocks(tiny):
+    cfg, w, m = tiny
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, cfg.vocab_size, (45,), generator=g)
+    ids[20] = cfg.eos_token_id
+    full, st = m.forward(ids)
+    sel = st.selected[3]
+    assert sel[10] is None and sel[18] is None                   # up to budget / ratio complete blocks: dense
+    assert sel[19] is not None and len(sel[19]) == 16 + 0        # 5 complete blocks, the best 4 kept, no open tail
+    assert len(sel[44]) == 16 + 1 and sel[44][-1] == 44 and sel[44] == sorted(sel[44])
+    st2 = Q4xState()
+    parts = []
+    for a, b in ((0, 1), (1, 8), (8, 9), (9, 30), (30, 45)):
+        lg, st2 = m.forward(ids[a:b], st2)
+        parts.append(lg)
+    got = torch.cat(parts, 0)
+    assert (got - full).abs().max().item() < 2e-4 * full.abs().max().item() + 1e-5
+    assert st2.selected[3][-1] == sel[44]
+
+
+def test_sparse_attention_equals_dense_while_everything_fits_the_budget(tiny, table):
+    cfg, w, _ = tiny
+    wide = dataclasses.replace(cfg, indexer_budget=4096)
+    dense = dataclasses.replace(cfg, indexer_heads=0)
+    ids = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(9))
+    a, _ = Q4xOracle(wide, w, rows_fn(table)).forward(ids)
+    b, _ = Q4xOracle(dense, w, rows_fn(table)).forward(ids)
+    c, _ = Q4xOracle(cfg, w, rows_fn(table)).forward(ids)
+    assert torch.allclose(a, b, atol=1e-5)
+    assert (c[:19] - b[:19]).abs().max().item() < 1e-5            # rows that still see everything
+    assert (c[30:] - b[30:]).abs().max().item() > 1e-4            # later rows drop blocks
+
+
+def test_stream_gate_and_ngram_layer_move_the_output(tiny, table):
+    cfg, w, m = tiny
+    ids = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(2))
+    base, _ = m.forward(ids)
+    zero_rows = lambda toks, hist: torch.zeros(len(toks), cfg.ple_embed_dim)
+    other, _ = Q4xOracle(cfg, w, zero_rows).forward(ids)
+    assert (base - other).abs().max().item() > 1e-4
+    # the injection weights are 2 * sigmoid(.): a zero inject projection gives exactly 1 per stream
+    w2 = dict(w)
+    for k in w:
+        if k.endswith(".inject"):
+            w2[k] = torch.zeros_like(w[k])
+    m2 = Q4xOracle(cfg, w2, rows_fn(table))
+    h = torch.randn(3, cfg.hc_count * cfg.hidden_size)
+    x, inj = m2.hc_prep("text.layers.0.hc.attn.", h)
+    assert x.shape == (3, cfg.hidden_size) and torch.allclose(inj, torch.ones(3, cfg.hc_count))
+    out = torch.randn(3, cfg.hidden_size)
+    assert torch.allclose(m2.hc_inject(h, out, inj), h + out.repeat(1, cfg.hc_count))
