@@ -233,6 +233,46 @@ int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void*
                                  void* const* recv, void* block_seq, int* status, int world, int rank, int spin_limit,
                                  void* stream);
 
+/* GDN decode step with the output gate of its norm chosen by the caller: gate_act 0 = silu(z), 1 = sigmoid(z). */
+int r4dxb_gdn_decode_gate(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
+                          const float* dt_bias, const void* norm_w, void* ring, float* state, float* log_u, float* log_k,
+                          float* log_eg, const int* positions, const int* n_replay, void* out, int T, int H, int Hk, int D,
+                          float eps, int gate_act, void* stream);
+
+/* ---- qwen4_exp family: gated multi-stream residual, n-gram embedding layer, block-selecting attention ------------- */
+/* out = bf16(x * rsqrt(mean(x^2 over the group) + eps) * (1 + w)) for `groups` groups of `group_size` channels per row */
+int r4dxb_q4x_grouped_rmsnorm(const void* x, const void* w, void* out, int rows, int groups, int group_size, float eps, void* stream);
+/* mid [rows, lowrank] bf16 = silu(down / hc); down = the first `lowrank` columns of an fp32 product with `stride` columns */
+int r4dxb_q4x_hc_mid(const float* down, void* mid, int rows, int lowrank, int stride, int hc, void* stream);
+/* x [rows, hidden] = mean over the hc streams of sigmoid(up) * n;  n bf16 [rows, hc * hidden], up fp32 of the same shape */
+int r4dxb_q4x_hc_mix(const void* n, const float* up, void* x, int rows, int hc, int hidden, void* stream);
+/* h [rows, hc * hidden] += block_out [rows, hidden] * 2 sigmoid(inject / hc) per stream; inject = hc fp32 columns of a row of `stride` */
+int r4dxb_q4x_hc_inject(void* h, const void* block_out, const float* inject, int rows, int hc, int hidden, int stride, void* stream);
+/* out [rows, hc * hidden] = embedding row of ids[r] repeated over the streams (ids outside the table give NaN rows) */
+int r4dxb_q4x_embed_repeat(const void* table, const int* ids, void* out, int rows, int vocab, int hidden, int hc, void* stream);
+/* n-gram rows of T tokens from the device-resident table: ids hashed from the device token history `hist` (indexed by
+ * position; read for the two positions before the call, written for the call's rows) and gathered into emb [T, heads * head_dim] */
+int r4dxb_q4x_ngram_gather(const int* ids, const int* positions, int* hist, const void* table, void* emb, int T, int heads,
+                           int head_dim, long long table_rows, const long long* mult, const unsigned long long* primes,
+                           const unsigned long long* offsets, long long eos, void* stream);
+/* gated_value [rows, hc * hidden] = sigmoid(signed sqrt(<norm(key_proj), norm(h)> / sqrt(hidden))) * value, per stream */
+int r4dxb_q4x_ple_gate_value(const float* key_proj, const void* h, const float* value, const void* norm_key, const void* norm_query,
+                             void* gated_value, int rows, int hc, int hidden, float eps, void* stream);
+/* h += gated_value + silu(dilated depthwise causal conv of gvn); ring [32, channels] holds gvn by position & 31 */
+int r4dxb_q4x_ple_conv(const void* gvn, const void* gated_value, const void* conv_w, void* ring, void* h, const int* positions,
+                       int rows, int channels, int kernel, int dilation, void* stream);
+/* indexer prologue: queries normed + roped, raw keys stored by position, block keys of the blocks these rows complete */
+int r4dxb_q4x_qsa_index(const float* qk, const void* q_norm, const void* k_norm, const int* positions, void* idx_q, void* raw_keys,
+                        void* block_keys, int T, int Hi, int Di, int ratio, int rotary_dim, float theta, float eps, void* stream);
+/* block scores + exact top-k selection (ties: the most recent block wins); sel_count[t] = -1 for rows that attend densely */
+int r4dxb_q4x_qsa_select(const void* idx_q, const void* block_keys, const int* positions, float* scores, int* sel_tokens, int* sel_count,
+                         int T, int Hi, int Di, int ratio, int topk, int nb_max, int stride, int sel_stride, void* stream);
+/* attention over each row's token list (fp8 paged cache), split merge, sigmoid output gate */
+int r4dxb_q4x_qsa_attn(const void* q, const void* qg, const void* cache, const int* block_table, const int* positions,
+                       const int* sel_tokens, const int* sel_count, const float* k_descale, const float* v_descale, float* part_acc,
+                       float* part_ml, void* out, int T, int Hq, int Hkv, int D, int sel_stride, int max_tokens, int nsplit, int gated,
+                       void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -49,6 +49,7 @@ struct GdnArgs {
   const __nv_bfloat16* in_norm_w;
   int K;
   float in_eps;
+  int gate_act;                  // output gate of the norm: 0 silu(z), 1 sigmoid(z)
 };
 
 template <int D>
@@ -258,7 +259,7 @@ __global__ void __launch_bounds__(kThreads) GdnDecodeKernel(GdnArgs a) {
       const float r = rsqrtf(ss / D + a.eps);
       const float zv = __bfloat162float(a.z[(static_cast<size_t>(t) * a.H + h) * D + threadIdx.x]);
       a.out[(static_cast<size_t>(t) * a.H + h) * D + threadIdx.x] =
-          __float2bfloat16(o * r * __bfloat162float(a.norm_w[threadIdx.x]) * Silu(zv));
+          __float2bfloat16(o * r * __bfloat162float(a.norm_w[threadIdx.x]) * (a.gate_act ? Sigmoid(zv) : Silu(zv)));
     }
   }
 }
@@ -268,11 +269,11 @@ __global__ void __launch_bounds__(kThreads) GdnDecodeKernel(GdnArgs a) {
 
 /* ab_w != null: the a / b projections are computed inside the kernel from the residual rows x [T, K], the layer's
  * input RMSNorm weight and ab_w [2H, K] (a rows, then b rows); `ab` is then unused. */
-extern "C" int r4dxb_gdn_decode_ab(const void* mixed, const void* z, const float* ab, const void* ab_w, const void* x,
-                                   const void* in_norm_w, int K, float in_eps, const void* conv_w,
-                                   const float* A_log, const float* dt_bias, const void* norm_w, void* ring,
-                                   float* state, float* log_u, float* log_k, float* log_eg, const int* positions,
-                                   const int* n_replay, void* out, int T, int H, int Hk, int D, float eps, void* stream) {
+static int GdnDecodeLaunch(const void* mixed, const void* z, const float* ab, const void* ab_w, const void* x,
+                           const void* in_norm_w, int K, float in_eps, const void* conv_w,
+                           const float* A_log, const float* dt_bias, const void* norm_w, void* ring,
+                           float* state, float* log_u, float* log_k, float* log_eg, const int* positions,
+                           const int* n_replay, void* out, int T, int H, int Hk, int D, float eps, int gate_act, void* stream) {
   using namespace r4dxb;
   if (T < 0 || T > kMaxT || H % Hk || (D != 128 && D != 64)) return R4DXB_BAD_ARG;
   if (ab_w != nullptr && (x == nullptr || in_norm_w == nullptr || K < 2 || K % 2)) return R4DXB_BAD_ARG;
@@ -303,9 +304,31 @@ extern "C" int r4dxb_gdn_decode_ab(const void* mixed, const void* z, const float
   a.in_norm_w = static_cast<const __nv_bfloat16*>(in_norm_w);
   a.K = K;
   a.in_eps = in_eps;
+  a.gate_act = gate_act;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 128) return LaunchPdl(GdnDecodeKernel<128>, dim3(H), dim3(kThreads), 0, s, a);
   return LaunchPdl(GdnDecodeKernel<64>, dim3(H), dim3(kThreads), 0, s, a);
+}
+
+extern "C" int r4dxb_gdn_decode_ab(const void* mixed, const void* z, const float* ab, const void* ab_w, const void* x,
+                                   const void* in_norm_w, int K, float in_eps, const void* conv_w,
+                                   const float* A_log, const float* dt_bias, const void* norm_w, void* ring,
+                                   float* state, float* log_u, float* log_k, float* log_eg, const int* positions,
+                                   const int* n_replay, void* out, int T, int H, int Hk, int D, float eps, void* stream) {
+  return GdnDecodeLaunch(mixed, z, ab, ab_w, x, in_norm_w, K, in_eps, conv_w, A_log, dt_bias, norm_w, ring, state, log_u, log_k,
+                         log_eg, positions, n_replay, out, T, H, Hk, D, eps, 0, stream);
+}
+
+/* The step with the norm's output gate chosen by the caller (0 silu, 1 sigmoid: the qwen4_exp family; reference:
+ * src/model/qwen4exp/include/r4dx/model/qwen4exp/gdn_sigmoid_norm.h:1-20). */
+extern "C" int r4dxb_gdn_decode_gate(const void* mixed, const void* z, const float* ab, const void* conv_w,
+                                     const float* A_log, const float* dt_bias, const void* norm_w, void* ring,
+                                     float* state, float* log_u, float* log_k, float* log_eg, const int* positions,
+                                     const int* n_replay, void* out, int T, int H, int Hk, int D, float eps, int gate_act,
+                                     void* stream) {
+  if (gate_act != 0 && gate_act != 1) return R4DXB_BAD_ARG;
+  return GdnDecodeLaunch(mixed, z, ab, nullptr, nullptr, nullptr, 0, 0.f, conv_w, A_log, dt_bias, norm_w, ring, state, log_u,
+                         log_k, log_eg, positions, n_replay, out, T, H, Hk, D, eps, gate_act, stream);
 }
 
 extern "C" int r4dxb_gdn_decode(const void* mixed, const void* z, const float* ab, const void* conv_w,
@@ -340,7 +363,7 @@ extern "C" int r4dxb_gdn_decode_batch(const void* mixed, const void* z, const fl
   a.out = static_cast<__nv_bfloat16*>(out);
   a.T = 1; a.H = H; a.Hk = Hk; a.conv_dim = 2 * Hk * D + H * D; a.eps = eps;
   a.row_slot = row_slot;
-  a.ab_w = nullptr; a.x = nullptr; a.in_norm_w = nullptr; a.K = 0; a.in_eps = 0.f;
+  a.ab_w = nullptr; a.x = nullptr; a.in_norm_w = nullptr; a.K = 0; a.in_eps = 0.f; a.gate_act = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 128) return LaunchPdl(GdnDecodeKernel<128>, dim3(H, B), dim3(kThreads), 0, s, a);
   return LaunchPdl(GdnDecodeKernel<64>, dim3(H, B), dim3(kThreads), 0, s, a);

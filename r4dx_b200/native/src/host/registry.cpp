@@ -24,7 +24,7 @@ const R4dxbConstraint c10[] = {{"world", R4DXB_C_LE, 8, nullptr}, {"N", R4DXB_C_
 const R4dxbConstraint c11[] = {{"world", R4DXB_C_LE, 8, nullptr}, {"world", R4DXB_C_GE, 2, nullptr}, {"H", R4DXB_C_DIV, 8, nullptr}};
 const R4dxbConstraint c13[] = {{"T", R4DXB_C_LE, 8, nullptr}, {"world", R4DXB_C_LE, 8, nullptr}};
 const R4dxbConstraint c14[] = {{"world", R4DXB_C_LE, 8, nullptr}};
-const R4dxbConstraint c15[] = {{"N", R4DXB_C_DIV, 128, nullptr}, {"K", R4DXB_C_DIV, 128, nullptr}, {"kb", R4DXB_C_IN, 0, "3 4 5"}, {"tn", R4DXB_C_IN, 0, "16 32 64 128"}, {"E", R4DXB_C_LE, 1024, nullptr}};
+const R4dxbConstraint c15[] = {{"N", R4DXB_C_DIV, 128, nullptr}, {"K", R4DXB_C_DIV, 128, nullptr}, {"kb", R4DXB_C_IN, 0, "3 4 5"}, {"tn", R4DXB_C_IN, 0, "16 32 64 128 256"}, {"E", R4DXB_C_LE, 1024, nullptr}};
 const R4dxbConstraint c16[] = {{"K", R4DXB_C_DIV, 128, nullptr}};
 const R4dxbConstraint c17[] = {{"E", R4DXB_C_LE, 1024, nullptr}};
 const R4dxbConstraint c18[] = {{"N", R4DXB_C_DIV, 4, nullptr}, {"K", R4DXB_C_DIV, 8, nullptr}};
@@ -57,7 +57,33 @@ const R4dxbConstraint c55[] = {{"D", R4DXB_C_DIV, 32, nullptr}};
 const R4dxbConstraint cx0[] = {{"D", R4DXB_C_DIV, 32, nullptr}};
 const R4dxbConstraint cx1[] = {{"world", R4DXB_C_LE, 8, nullptr}};
 
+const R4dxbConstraint cq0[] = {{"group_size", R4DXB_C_GE, 1, nullptr}};
+const R4dxbConstraint cq1[] = {{"heads", R4DXB_C_LE, 16, nullptr}, {"heads", R4DXB_C_DIV, 2, nullptr}};
+const R4dxbConstraint cq2[] = {{"kernel", R4DXB_C_LE, 8, nullptr}};
+const R4dxbConstraint cq3[] = {{"Di", R4DXB_C_DIV, 32, nullptr}, {"Di", R4DXB_C_LE, 128, nullptr}, {"Hi", R4DXB_C_LE, 8, nullptr}};
+const R4dxbConstraint cq4[] = {{"D", R4DXB_C_IN, 0, "64 128 256"}, {"gqa", R4DXB_C_LE, 16, nullptr}};
+const R4dxbConstraint cq5[] = {{"T", R4DXB_C_LE, 8, nullptr}, {"D", R4DXB_C_IN, 0, "64 128"}, {"gate_act", R4DXB_C_IN, 0, "0 1"}};
+
 const R4dxbKernelInfo kKernels[] = {
+    {"gdn_decode_gate", "gdn", "gdn_decode_rows_le_8", "the GDN step with the norm's output gate chosen by the caller (silu or sigmoid)",
+     "as gdn_decode_ab without the in-kernel a / b projections", "bf16 rows, fp32 state", "simt", cq5, 3},
+    {"q4x_grouped_rmsnorm", "elementwise", "grouped_rmsnorm", "zero-centred RMSNorm over consecutive channel groups of a row (stream gate, n-gram layer)",
+     "any group size", "bf16", "simt", cq0, 1},
+    {"q4x_hc_mid", "elementwise", "stream_gate", "silu of the scaled low-rank product of the stream gate", "", "fp32 in, bf16 out", "simt", nullptr, 0},
+    {"q4x_hc_mix", "elementwise", "stream_gate", "block input = mean over the streams of sigmoid(up) * normalised stream", "", "bf16 / fp32 in, bf16 out", "simt", nullptr, 0},
+    {"q4x_hc_inject", "elementwise", "stream_gate", "every stream += block output * 2 sigmoid(inject / streams)", "", "bf16 in place", "simt", nullptr, 0},
+    {"q4x_embed_repeat", "elementwise", "stream_embedding", "embedding rows repeated over the residual streams", "", "bf16", "simt", nullptr, 0},
+    {"q4x_ngram_gather", "elementwise", "ngram_rows", "n-gram row ids hashed from the device token history and rows gathered from the device-resident table",
+     "up to 16 heads, even", "int32 tokens, bf16 rows", "simt", cq1, 2},
+    {"q4x_ple_gate_value", "elementwise", "ngram_layer", "per-stream gate from the normalised key projection and residual, times the value row", "", "fp32 products, bf16 out", "simt", nullptr, 0},
+    {"q4x_ple_conv", "conv", "ngram_layer", "dilated depthwise causal conv over a position-keyed ring + silu + the layer's adds",
+     "(kernel - 1) * dilation < 32", "bf16", "simt", cq2, 1},
+    {"q4x_qsa_index", "attn", "block_index", "indexer queries normed + roped, raw keys by position, pooled block keys of completed blocks",
+     "index dim a multiple of 32 up to 128", "fp32 projection in, bf16 out", "simt", cq3, 3},
+    {"q4x_qsa_select", "attn", "block_select", "block scores and the exact top-k blocks by (score, recency) as ascending token lists",
+     "index dim a multiple of 32 up to 128", "bf16 keys, fp32 scores, int32 lists", "simt", cq3, 3},
+    {"q4x_qsa_attn", "attn", "sparse_paged_attention", "attention over each row's token list in the fp8 paged cache, split merge, output gate",
+     "head_dim 64 / 128 / 256, up to 16 query heads per KV head", "bf16 q, fp8 cache, bf16 out", "simt", cq4, 2},
     {"trellis_gemv_ex", "gemm", "trellis_linear_rows_le_8", "y = svh * H128(Q * H128(suh * act(x))) (+ residual) for up to 8 rows; RMSNorm / SwiGLU / GeGLU prologues",
      "N, K multiples of 128; cluster split 1/2/4/8 of K; kb 3/4/5", "bf16 x, packed trellis words, bf16 y", "simt+bulk-copy", c0, 5},
     {"trellis_gemv_siblings", "gemm", "trellis_linear_rows_le_8", "2 or 3 weights of one K and bit width over the same rows in one launch",

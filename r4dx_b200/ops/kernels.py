@@ -736,3 +736,128 @@ def repetition_penalty(logits_row: torch.Tensor, seen: torch.Tensor, penalty: fl
     _check(_lib().r4dxb_repetition_penalty(_p(logits_row), logits_row.numel(), _p(seen), seen.numel(), penalty, _stream()),
            "repetition_penalty")
     return logits_row
+
+
+# ---- qwen4_exp family: gated multi-stream residual, n-gram embedding layer, block-selecting attention ----------------
+_LL = ctypes.c_longlong
+register_cuda_sig("r4dxb_gdn_decode_gate", _I, [_P] * 15 + [_I, _I, _I, _I, _F, _I, _P])
+register_cuda_sig("r4dxb_q4x_grouped_rmsnorm", _I, [_P, _P, _P, _I, _I, _I, _F, _P])
+register_cuda_sig("r4dxb_q4x_hc_mid", _I, [_P, _P, _I, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_q4x_hc_mix", _I, [_P, _P, _P, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_q4x_hc_inject", _I, [_P, _P, _P, _I, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_q4x_embed_repeat", _I, [_P, _P, _P, _I, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_q4x_ngram_gather", _I, [_P, _P, _P, _P, _P, _I, _I, _I, _LL, _P, _P, _P, _LL, _P])
+register_cuda_sig("r4dxb_q4x_ple_gate_value", _I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _F, _P])
+register_cuda_sig("r4dxb_q4x_ple_conv", _I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P])
+register_cuda_sig("r4dxb_q4x_qsa_index", _I, [_P] * 7 + [_I, _I, _I, _I, _I, _F, _F, _P])
+register_cuda_sig("r4dxb_q4x_qsa_select", _I, [_P] * 6 + [_I] * 8 + [_P])
+register_cuda_sig("r4dxb_q4x_qsa_attn", _I, [_P] * 12 + [_I] * 8 + [_P])
+
+
+def gdn_decode_gate(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, log_u, log_k, log_eg, positions, n_replay, out,
+                    T: int, H: int, Hk: int, D: int, eps: float, gate_act: int):
+    """One GDN step for T <= 8 rows with the norm's output gate chosen by the caller (0 silu, 1 sigmoid)."""
+    _check(_lib().r4dxb_gdn_decode_gate(_p(mixed), _p(z), _p(ab), _p(conv_w), _p(A_log), _p(dt_bias), _p(norm_w), _p(ring), _p(state),
+                                        _p(log_u), _p(log_k), _p(log_eg), _p(positions), _p(n_replay), _p(out), T, H, Hk, D, eps,
+                                        gate_act, _stream()), "gdn_decode_gate")
+    return out
+
+
+def q4x_grouped_rmsnorm(x: torch.Tensor, w: torch.Tensor, groups: int, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _req(x, BF, "x"); _req(w, BF, "w")
+    rows, C = x.shape
+    out = out if out is not None else torch.empty_like(x)
+    _check(_lib().r4dxb_q4x_grouped_rmsnorm(_p(x), _p(w), _p(out), rows, groups, C // groups, eps, _stream()), "q4x_grouped_rmsnorm")
+    return out
+
+
+def q4x_hc_mid(down: torch.Tensor, mid: torch.Tensor, lowrank: int, hc: int) -> torch.Tensor:
+    _req(down, torch.float32, "down"); _req(mid, BF, "mid")
+    rows, stride = down.shape
+    _check(_lib().r4dxb_q4x_hc_mid(_p(down), _p(mid), rows, lowrank, stride, hc, _stream()), "q4x_hc_mid")
+    return mid
+
+
+def q4x_hc_mix(n: torch.Tensor, up: torch.Tensor, x: torch.Tensor, hc: int) -> torch.Tensor:
+    _req(n, BF, "n"); _req(up, torch.float32, "up"); _req(x, BF, "x")
+    rows, H = x.shape
+    _check(_lib().r4dxb_q4x_hc_mix(_p(n), _p(up), _p(x), rows, hc, H, _stream()), "q4x_hc_mix")
+    return x
+
+
+def q4x_hc_inject(h: torch.Tensor, block_out: torch.Tensor, inject: torch.Tensor, hc: int) -> torch.Tensor:
+    """``inject``: the hc inject columns of the gate's fp32 product (a column slice of a wider row is fine)."""
+    _req(h, BF, "h"); _req(block_out, BF, "block_out")
+    rows, H = block_out.shape
+    if inject.dtype != torch.float32 or inject.stride(1) != 1:
+        raise ValueError("inject: fp32 with unit column stride")
+    _check(_lib().r4dxb_q4x_hc_inject(_p(h), _p(block_out), inject.data_ptr(), rows, hc, H, inject.stride(0), _stream()), "q4x_hc_inject")
+    return h
+
+
+def q4x_embed_repeat(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, hc: int) -> torch.Tensor:
+    _req(table, BF, "table"); _req(ids, torch.int32, "ids"); _req(out, BF, "out")
+    rows = ids.numel()
+    _check(_lib().r4dxb_q4x_embed_repeat(_p(table), _p(ids), _p(out), rows, table.shape[0], table.shape[1], hc, _stream()), "q4x_embed_repeat")
+    return out
+
+
+class NgramDeviceArgs:
+    """Host arrays of the hash parameters, built once per table (ctypes reads them at every launch)."""
+
+    def __init__(self, header):
+        self.heads, self.head_dim, self.rows, self.eos = header.heads, header.head_dim, header.rows, header.eos_token_id
+        self.mult = (ctypes.c_longlong * 3)(*header.multipliers)
+        self.primes = (ctypes.c_ulonglong * 16)(*header.head_primes)
+        self.offsets = (ctypes.c_ulonglong * 16)(*header.head_offsets)
+
+
+def q4x_ngram_gather(ids: torch.Tensor, positions: torch.Tensor, hist: torch.Tensor, table: torch.Tensor, emb: torch.Tensor, T: int,
+                     args: NgramDeviceArgs) -> torch.Tensor:
+    _req(ids, torch.int32, "ids"); _req(hist, torch.int32, "hist"); _req(table, BF, "table"); _req(emb, BF, "emb")
+    _check(_lib().r4dxb_q4x_ngram_gather(_p(ids), _p(positions), _p(hist), _p(table), _p(emb), T, args.heads, args.head_dim, args.rows,
+                                         ctypes.addressof(args.mult), ctypes.addressof(args.primes), ctypes.addressof(args.offsets),
+                                         args.eos, _stream()), "q4x_ngram_gather")
+    return emb
+
+
+def q4x_ple_gate_value(key_proj, h, value, norm_key, norm_query, gated_value, hc: int, eps: float):
+    _req(key_proj, torch.float32, "key_proj"); _req(value, torch.float32, "value"); _req(h, BF, "h")
+    rows, H = value.shape
+    _check(_lib().r4dxb_q4x_ple_gate_value(_p(key_proj), _p(h), _p(value), _p(norm_key), _p(norm_query), _p(gated_value), rows, hc, H,
+                                           eps, _stream()), "q4x_ple_gate_value")
+    return gated_value
+
+
+def q4x_ple_conv(gvn, gated_value, conv_w, ring, h, positions, rows: int, kernel: int, dilation: int):
+    _req(gvn, BF, "gvn"); _req(ring, BF, "ring"); _req(conv_w, BF, "conv_w")
+    C = gvn.shape[1]
+    assert ring.shape == (32, C) and conv_w.shape == (C, kernel)
+    _check(_lib().r4dxb_q4x_ple_conv(_p(gvn), _p(gated_value), _p(conv_w), _p(ring), _p(h), _p(positions), rows, C, kernel, dilation,
+                                     _stream()), "q4x_ple_conv")
+    return h
+
+
+def q4x_qsa_index(qk, q_norm, k_norm, positions, idx_q, raw_keys, block_keys, T: int, Hi: int, Di: int, ratio: int, rotary_dim: int,
+                  theta: float, eps: float):
+    _req(qk, torch.float32, "qk"); _req(idx_q, BF, "idx_q"); _req(raw_keys, BF, "raw_keys"); _req(block_keys, BF, "block_keys")
+    _check(_lib().r4dxb_q4x_qsa_index(_p(qk), _p(q_norm), _p(k_norm), _p(positions), _p(idx_q), _p(raw_keys), _p(block_keys), T, Hi, Di,
+                                      ratio, rotary_dim, theta, eps, _stream()), "q4x_qsa_index")
+
+
+def q4x_qsa_select(idx_q, block_keys, positions, scores, sel_tokens, sel_count, T: int, Hi: int, Di: int, ratio: int, topk: int,
+                   nb_max: int):
+    _req(scores, torch.float32, "scores"); _req(sel_tokens, torch.int32, "sel_tokens"); _req(sel_count, torch.int32, "sel_count")
+    _check(_lib().r4dxb_q4x_qsa_select(_p(idx_q), _p(block_keys), _p(positions), _p(scores), _p(sel_tokens), _p(sel_count), T, Hi, Di,
+                                       ratio, topk, nb_max, scores.shape[1], sel_tokens.shape[1], _stream()), "q4x_qsa_select")
+
+
+def q4x_qsa_attn(q, qg, cache, block_table, positions, sel_tokens, sel_count, k_descale, v_descale, part_acc, part_ml, out, T: int,
+                 Hq: int, Hkv: int, D: int, max_tokens: int, nsplit: int, gated: bool = True):
+    need = T * Hq * nsplit
+    if part_acc.numel() < need * D or part_ml.numel() < need * 2:
+        raise ValueError("q4x_qsa_attn: partial buffers too small for this split count")
+    _check(_lib().r4dxb_q4x_qsa_attn(_p(q), _p(qg), _p(cache), _p(block_table), _p(positions), _p(sel_tokens), _p(sel_count),
+                                     _p(k_descale), _p(v_descale), _p(part_acc), _p(part_ml), _p(out), T, Hq, Hkv, D,
+                                     sel_tokens.shape[1], max_tokens, nsplit, 1 if gated else 0, _stream()), "q4x_qsa_attn")
+    return out

@@ -42,6 +42,8 @@ def moe_kb_rule(name: str) -> int:
 
 def is_quantized_linear(name: str) -> bool:
     leaf = name.split(".")[-1]
+    if ".hc." in name or name.startswith("text.hc_final."):
+        return False                  # the stream gates of the qwen4_exp family stay bf16 (their "down" is not an MLP's)
     return leaf in ("qg", "k", "v", "o", "in_proj_qkv", "in_proj_z", "in_proj", "out_proj", "gate_up", "down", "fc")
 
 
