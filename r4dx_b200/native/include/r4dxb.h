@@ -248,6 +248,10 @@ int r4dxb_q4x_hc_mid(const float* down, void* mid, int rows, int lowrank, int st
 int r4dxb_q4x_hc_mix(const void* n, const float* up, void* x, int rows, int hc, int hidden, void* stream);
 /* h [rows, hc * hidden] += block_out [rows, hidden] * 2 sigmoid(inject / hc) per stream; inject = hc fp32 columns of a row of `stride` */
 int r4dxb_q4x_hc_inject(void* h, const void* block_out, const float* inject, int rows, int hc, int hidden, int stride, void* stream);
+/* the stream gate for T <= 8 rows in two launches (norm statistics, [down; inject] product, silu, up product, mix):
+ * x [T, hidden] = the block input, injv [T, n_inject] fp32 = the raw injection logits (n_inject = 0: the final mixer) */
+int r4dxb_q4x_hc_gate(const void* h, const void* norm_w, const void* w_down_inject, const void* w_up, void* mid, float* injv,
+                      float* rstd, void* x, int T, int hc, int hidden, int lowrank, int n_inject, float eps, void* stream);
 /* out [rows, hc * hidden] = embedding row of ids[r] repeated over the streams (ids outside the table give NaN rows) */
 int r4dxb_q4x_embed_repeat(const void* table, const int* ids, void* out, int rows, int vocab, int hidden, int hc, void* stream);
 /* n-gram rows of T tokens from the device-resident table: ids hashed from the device token history `hist` (indexed by

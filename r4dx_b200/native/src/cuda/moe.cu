@@ -164,28 +164,32 @@ MoePlanParallelKernel(const int* __restrict__ ids, int npairs, int e_begin, int 
   }
 }
 
-// grid T, block 256: out[t] = residual + sum_j w_j y[pair] (ascending expert id) + sigmoid(sg) * shared
+// grid (T, ceil(H / 512)), block 256: out[t] = residual + sum_j w_j y[pair] (ascending expert id) + sigmoid(sg) * shared
+constexpr int kCombineCols = 512;
 __global__ void MoeCombineKernel(const __nv_bfloat16* __restrict__ y_pairs, const int* __restrict__ ids,
                                  const float* __restrict__ weights, const __nv_bfloat16* __restrict__ shared,
                                  const float* __restrict__ shared_gate, const __nv_bfloat16* __restrict__ residual,
                                  __nv_bfloat16* __restrict__ out, int H, int k) {
   const int t = blockIdx.x;
-  __shared__ int order[kMaxK];
-  __shared__ float w[kMaxK];
-  if (threadIdx.x == 0) {
-    int idx[kMaxK];
-    for (int j = 0; j < k; ++j) idx[j] = j;
-    for (int a = 1; a < k; ++a) {          // insertion sort of the slots by expert id
-      const int v = idx[a];
-      int b = a - 1;
-      while (b >= 0 && ids[t * k + idx[b]] > ids[t * k + v]) { idx[b + 1] = idx[b]; --b; }
-      idx[b + 1] = v;
-    }
-    for (int j = 0; j < k; ++j) { order[j] = idx[j]; w[j] = weights[t * k + idx[j]]; }
+  __shared__ int order[kMaxK], sid[kMaxK];
+  __shared__ float w[kMaxK], sw[kMaxK];
+  if (threadIdx.x < k) {                     // one parallel read of the row's ids and weights; the sort runs on shared memory
+    sid[threadIdx.x] = ids[t * k + threadIdx.x];
+    sw[threadIdx.x] = weights[t * k + threadIdx.x];
+  }
+  __syncthreads();
+  if (threadIdx.x < k) {                     // rank of slot j among the row's expert ids (ids of a row are distinct; ties by slot)
+    const int mine = sid[threadIdx.x];
+    int rank = 0;
+    for (int j = 0; j < k; ++j) rank += (sid[j] < mine || (sid[j] == mine && j < static_cast<int>(threadIdx.x))) ? 1 : 0;
+    order[rank] = threadIdx.x;
+    w[rank] = sw[threadIdx.x];
   }
   __syncthreads();
   const float sg = shared_gate ? Sigmoid(shared_gate[t]) : 0.f;
-  for (int c = threadIdx.x * 2; c < H; c += blockDim.x * 2) {
+  // grid.y splits the columns: a single row (decode) still spreads over several SMs
+  const int c_lo = blockIdx.y * kCombineCols, c_hi = min(H, c_lo + kCombineCols);
+  for (int c = c_lo + threadIdx.x * 2; c < c_hi; c += blockDim.x * 2) {
     float a0 = 0.f, a1 = 0.f;
     for (int j = 0; j < k; ++j) {
       const uint32_t v = *reinterpret_cast<const uint32_t*>(y_pairs + (static_cast<size_t>(t) * k + order[j]) * H + c);
@@ -250,7 +254,7 @@ int r4dxb_moe_plan(const int* ids, int npairs, int E, int e_begin, int e_count, 
 int r4dxb_moe_combine(const void* y_pairs, const int* ids, const float* weights, const void* shared, const float* shared_gate,
                       const void* residual, void* out, int T, int H, int k, void* stream) {
   if (T < 1 || k < 1 || k > kMaxK || H % 2) return R4DXB_BAD_ARG;
-  MoeCombineKernel<<<T, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  MoeCombineKernel<<<dim3(T, (H + kCombineCols - 1) / kCombineCols), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(y_pairs), ids, weights, static_cast<const __nv_bfloat16*>(shared), shared_gate,
       static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(out), H, k);
   return FinishLaunch();

@@ -65,6 +65,128 @@ __global__ void HcInjectKernel(__nv_bfloat16* __restrict__ h, const __nv_bfloat1
   h[i] = __float2bfloat16(__bfloat162float(h[i]) + Rb(__bfloat162float(out[static_cast<size_t>(r) * H + d]) * inj));
 }
 
+// ---- the stream gate in two launches (decode: every intermediate of the five-kernel chain stays on chip) ----------------
+// Kernel 1, grid (L + hc) CTAs of 512 threads: CTA n owns output n of the [down; inject] product for all T <= 8 rows.  Every
+// CTA recomputes the per-stream RMS statistics of the rows (the rows are 20 KB each and come from L2), normalises on the
+// fly with the same roundings as the separate norm kernel, and finishes its output: mid = silu(Rb(Rb(down) / hc)) for
+// n < L, the raw injection logit otherwise.  CTA 0 also leaves the statistics for kernel 2.
+constexpr int kGateThreads = 512;
+constexpr int kGateRows = 8;
+__global__ void __launch_bounds__(kGateThreads)
+HcDownKernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ norm_w, const __nv_bfloat16* __restrict__ W,
+             __nv_bfloat16* __restrict__ mid, float* __restrict__ injv, float* __restrict__ rstd, int T, int hc, int H, int L,
+             int n_inject, float eps) {
+  __shared__ float s_r[kGateRows][8];                   // [row][stream] reciprocal RMS
+  __shared__ float red[kGateThreads / 32][kGateRows];
+  const int n = blockIdx.x, C = hc * H, nvec = C / 8;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // statistics: one stream at a time, all rows
+  for (int g = 0; g < hc; ++g) {
+    float ss[kGateRows];
+#pragma unroll
+    for (int t = 0; t < kGateRows; ++t) ss[t] = 0.f;
+    for (int v = threadIdx.x; v < H / 8; v += kGateThreads) {
+#pragma unroll
+      for (int t = 0; t < kGateRows; ++t) {
+        if (t >= T) break;
+        const uint4 x = *reinterpret_cast<const uint4*>(h + static_cast<size_t>(t) * C + g * H + v * 8);
+        const uint32_t w4[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ss[t] += BfLo(w4[j]) * BfLo(w4[j]) + BfHi(w4[j]) * BfHi(w4[j]);
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < kGateRows; ++t) ss[t] = WarpSum(ss[t]);
+    __syncthreads();
+    if (lane == 0)
+      for (int t = 0; t < kGateRows; ++t) red[warp][t] = ss[t];
+    __syncthreads();
+    if (threadIdx.x < T) {
+      float tot = 0.f;
+      for (int w = 0; w < kGateThreads / 32; ++w) tot += red[w][threadIdx.x];
+      s_r[threadIdx.x][g] = rsqrtf(tot / H + eps);
+    }
+  }
+  __syncthreads();
+  if (n == 0 && threadIdx.x < T * hc) rstd[threadIdx.x] = s_r[threadIdx.x / hc][threadIdx.x % hc];
+  float acc[kGateRows];
+#pragma unroll
+  for (int t = 0; t < kGateRows; ++t) acc[t] = 0.f;
+  const __nv_bfloat16* wrow = W + static_cast<size_t>(n) * C;
+  for (int v = threadIdx.x; v < nvec; v += kGateThreads) {
+    const uint4 wv = *reinterpret_cast<const uint4*>(wrow + v * 8);
+    const uint4 nv = *reinterpret_cast<const uint4*>(norm_w + v * 8);
+    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w}, nn[4] = {nv.x, nv.y, nv.z, nv.w};
+    const int g = (v * 8) / H;
+#pragma unroll
+    for (int t = 0; t < kGateRows; ++t) {
+      if (t >= T) break;
+      const uint4 x = *reinterpret_cast<const uint4*>(h + static_cast<size_t>(t) * C + v * 8);
+      const uint32_t xx[4] = {x.x, x.y, x.z, x.w};
+      const float r = s_r[t][g];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[t] += BfLo(ww[j]) * Rb(BfLo(xx[j]) * r * (1.0f + BfLo(nn[j]))) + BfHi(ww[j]) * Rb(BfHi(xx[j]) * r * (1.0f + BfHi(nn[j])));
+      }
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kGateRows; ++t) acc[t] = WarpSum(acc[t]);
+  __syncthreads();
+  if (lane == 0)
+    for (int t = 0; t < kGateRows; ++t) red[warp][t] = acc[t];
+  __syncthreads();
+  if (threadIdx.x < T) {
+    float tot = 0.f;
+    for (int w = 0; w < kGateThreads / 32; ++w) tot += red[w][threadIdx.x];
+    if (n < L) mid[static_cast<size_t>(threadIdx.x) * L + n] = __float2bfloat16(Silu(Rb(Rb(tot) * (1.0f / hc))));
+    else if (n - L < n_inject) injv[threadIdx.x * n_inject + (n - L)] = tot;
+  }
+}
+
+// Kernel 2, grid H / 8 CTAs of 8 warps: warp d computes the hc rows g H + d of the up product for all rows, gates the
+// normalised streams with them and averages: x[t, d] = Rb(mean_g Rb(Rb(sigmoid(Rb(up))) * n)).
+__global__ void __launch_bounds__(256)
+HcUpMixKernel(const __nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ norm_w, const __nv_bfloat16* __restrict__ Wup,
+              const __nv_bfloat16* __restrict__ mid, const float* __restrict__ rstd, __nv_bfloat16* __restrict__ x, int T, int hc,
+              int H, int L) {
+  extern __shared__ float s_mid[];                      // [T][L]
+  for (int i = threadIdx.x; i < T * L; i += blockDim.x) s_mid[i] = __bfloat162float(mid[i]);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int d = blockIdx.x * 8 + warp;
+  if (d >= H) return;
+  const int C = hc * H;
+  float out[kGateRows];
+#pragma unroll
+  for (int t = 0; t < kGateRows; ++t) out[t] = 0.f;
+  for (int g = 0; g < hc; ++g) {
+    const __nv_bfloat16* wrow = Wup + static_cast<size_t>(g * H + d) * L;
+    float up[kGateRows];
+#pragma unroll
+    for (int t = 0; t < kGateRows; ++t) up[t] = 0.f;
+    for (int j = lane * 2; j < L; j += 64) {
+      const uint32_t wv = *reinterpret_cast<const uint32_t*>(wrow + j);
+      const float w0 = BfLo(wv), w1 = BfHi(wv);
+#pragma unroll
+      for (int t = 0; t < kGateRows; ++t) {
+        if (t >= T) break;
+        up[t] += w0 * s_mid[t * L + j] + w1 * s_mid[t * L + j + 1];
+      }
+    }
+    const float wn = 1.0f + __bfloat162float(norm_w[g * H + d]);
+#pragma unroll
+    for (int t = 0; t < kGateRows; ++t) {
+      if (t >= T) break;
+      const float u = WarpSum(up[t]);
+      const float nv = Rb(__bfloat162float(h[static_cast<size_t>(t) * C + g * H + d]) * rstd[t * hc + g] * wn);
+      out[t] += Rb(Rb(Sigmoid(Rb(u))) * nv);
+    }
+  }
+  if (lane == 0)
+    for (int t = 0; t < T; ++t) x[static_cast<size_t>(t) * H + d] = __float2bfloat16(out[t] / hc);
+}
+
 // h0[r, g H + d] = table[ids[r], d]
 __global__ void EmbedRepeatKernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids, __nv_bfloat16* __restrict__ out,
                                   int rows, int vocab, int H, int hc) {
@@ -268,9 +390,11 @@ QsaSelectKernel(const float* __restrict__ scores, const int* __restrict__ positi
     return;
   }
   const float* sc = scores + static_cast<size_t>(t) * stride;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   auto key_of = [&](int b) { return (static_cast<unsigned long long>(__float_as_uint(fmaxf(sc[b], 0.f))) << 32) | static_cast<unsigned>(b); };
   if (threadIdx.x == 0) { s_prefix = 0ull; s_k = topk; }
   for (int byte = 7; byte >= 0; --byte) {
+    if (byte == 3) continue;                            // block indices stay below 2^24: this byte of every key is 0
     for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0u;
     __syncthreads();
     const unsigned long long prefix = s_prefix;
@@ -280,14 +404,26 @@ QsaSelectKernel(const float* __restrict__ scores, const int* __restrict__ positi
       if ((k & hi_mask) == prefix) atomicAdd(&hist[(k >> (8 * byte)) & 0xFF], 1u);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int k = s_k, above = 0, d = 255;
-      for (; d > 0; --d) {
-        if (above + static_cast<int>(hist[d]) >= k) break;
-        above += hist[d];
+    // the bin that holds the k-th largest: above(d) = count in bins > d, by a suffix scan over 256 bins (8 warps)
+    const int kk = s_k;
+    int above = 0, mine = 0;
+    if (threadIdx.x < 256) {
+      mine = static_cast<int>(hist[255 - threadIdx.x]);                      // thread i looks at bin 255 - i
+      int incl = mine;
+      for (int d = 1; d < 32; d <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += u;
       }
-      s_k = k - above;
-      s_prefix = prefix | (static_cast<unsigned long long>(d) << (8 * byte));
+      if (lane == 31) wsum[warp] = incl;
+      above = incl - mine;
+    }
+    __syncthreads();
+    if (threadIdx.x < 256) {
+      for (int w = 0; w < warp; ++w) above += wsum[w];
+      if (above < kk && kk <= above + mine) {                                  // exactly one bin qualifies
+        s_k = kk - above;
+        s_prefix = prefix | (static_cast<unsigned long long>(255 - threadIdx.x) << (8 * byte));
+      }
     }
     __syncthreads();
   }
@@ -295,7 +431,6 @@ QsaSelectKernel(const float* __restrict__ scores, const int* __restrict__ positi
   if (threadIdx.x == 0) s_base = 0;
   __syncthreads();
   int* out = sel_tokens + static_cast<size_t>(t) * sel_stride;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int b0 = 0; b0 < nb; b0 += kSelThreads) {
     const int b = b0 + threadIdx.x;
     const int flag = (b < nb && key_of(b) >= kth) ? 1 : 0;
@@ -475,6 +610,24 @@ int r4dxb_q4x_hc_inject(void* h, const void* block_out, const float* inject, int
   if (rows < 1 || hc < 1 || hidden < 1 || stride < hc) return R4DXB_BAD_ARG;
   HcInjectKernel<<<Flat(static_cast<long long>(rows) * hc * hidden), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(block_out), inject, rows, hc, hidden, stride);
+  return FinishLaunch();
+}
+
+/* The whole gate in two launches for T <= 8 rows: mid [T, L] bf16 scratch, injv [T, n_inject] fp32 (the raw injection
+ * logits; n_inject = 0 for the final mixer), rstd [T, hc] fp32 scratch, x [T, H] the block input.  w_down_inject: the down
+ * rows followed by the inject rows, [L + n_inject, hc * H]. */
+int r4dxb_q4x_hc_gate(const void* h, const void* norm_w, const void* w_down_inject, const void* w_up, void* mid, float* injv,
+                      float* rstd, void* x, int T, int hc, int hidden, int lowrank, int n_inject, float eps, void* stream) {
+  if (T < 1 || T > kGateRows || hc < 1 || hc > 8 || hidden % 8 || lowrank % 2 || lowrank < 2 || n_inject < 0) return R4DXB_BAD_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  HcDownKernel<<<lowrank + n_inject, kGateThreads, 0, s>>>(static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(norm_w),
+                                                           static_cast<const __nv_bfloat16*>(w_down_inject), static_cast<__nv_bfloat16*>(mid),
+                                                           injv, rstd, T, hc, hidden, lowrank, n_inject, eps);
+  ++g_launch_count;
+  const size_t smem = static_cast<size_t>(T) * lowrank * sizeof(float);
+  HcUpMixKernel<<<(hidden + 7) / 8, 256, smem, s>>>(static_cast<const __nv_bfloat16*>(h), static_cast<const __nv_bfloat16*>(norm_w),
+                                                    static_cast<const __nv_bfloat16*>(w_up), static_cast<const __nv_bfloat16*>(mid), rstd,
+                                                    static_cast<__nv_bfloat16*>(x), T, hc, hidden, lowrank);
   return FinishLaunch();
 }
 

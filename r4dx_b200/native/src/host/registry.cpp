@@ -62,6 +62,7 @@ const R4dxbConstraint cq1[] = {{"heads", R4DXB_C_LE, 16, nullptr}, {"heads", R4D
 const R4dxbConstraint cq2[] = {{"kernel", R4DXB_C_LE, 8, nullptr}};
 const R4dxbConstraint cq3[] = {{"Di", R4DXB_C_DIV, 32, nullptr}, {"Di", R4DXB_C_LE, 128, nullptr}, {"Hi", R4DXB_C_LE, 8, nullptr}};
 const R4dxbConstraint cq4[] = {{"D", R4DXB_C_IN, 0, "64 128 256"}, {"gqa", R4DXB_C_LE, 16, nullptr}};
+const R4dxbConstraint cq6[] = {{"T", R4DXB_C_LE, 8, nullptr}, {"hc", R4DXB_C_LE, 8, nullptr}};
 const R4dxbConstraint cq5[] = {{"T", R4DXB_C_LE, 8, nullptr}, {"D", R4DXB_C_IN, 0, "64 128"}, {"gate_act", R4DXB_C_IN, 0, "0 1"}};
 
 const R4dxbKernelInfo kKernels[] = {
@@ -69,6 +70,8 @@ const R4dxbKernelInfo kKernels[] = {
      "as gdn_decode_ab without the in-kernel a / b projections", "bf16 rows, fp32 state", "simt", cq5, 3},
     {"q4x_grouped_rmsnorm", "elementwise", "grouped_rmsnorm", "zero-centred RMSNorm over consecutive channel groups of a row (stream gate, n-gram layer)",
      "any group size", "bf16", "simt", cq0, 1},
+    {"q4x_hc_gate", "gemm", "stream_gate", "the whole stream gate of up to 8 rows in two launches: statistics + [down; inject] product + silu, then up product + mix",
+     "T <= 8, up to 8 streams", "bf16 in, bf16 block input, fp32 injection logits", "simt", cq6, 2},
     {"q4x_hc_mid", "elementwise", "stream_gate", "silu of the scaled low-rank product of the stream gate", "", "fp32 in, bf16 out", "simt", nullptr, 0},
     {"q4x_hc_mix", "elementwise", "stream_gate", "block input = mean over the streams of sigmoid(up) * normalised stream", "", "bf16 / fp32 in, bf16 out", "simt", nullptr, 0},
     {"q4x_hc_inject", "elementwise", "stream_gate", "every stream += block output * 2 sigmoid(inject / streams)", "", "bf16 in place", "simt", nullptr, 0},

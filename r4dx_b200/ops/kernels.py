@@ -861,3 +861,17 @@ def q4x_qsa_attn(q, qg, cache, block_table, positions, sel_tokens, sel_count, k_
                                      _p(k_descale), _p(v_descale), _p(part_acc), _p(part_ml), _p(out), T, Hq, Hkv, D,
                                      sel_tokens.shape[1], max_tokens, nsplit, 1 if gated else 0, _stream()), "q4x_qsa_attn")
     return out
+
+
+register_cuda_sig("r4dxb_q4x_hc_gate", _I, [_P] * 8 + [_I, _I, _I, _I, _I, _F, _P])
+
+
+def q4x_hc_gate(h, norm_w, w_down_inject, w_up, mid, injv, rstd, x, T: int, hc: int, lowrank: int, n_inject: int, eps: float):
+    """The stream gate of T <= 8 rows in two launches; ``x`` [T, H] receives the block input, ``injv`` [T, n_inject] the raw
+    injection logits (the same numbers the five-kernel chain produces)."""
+    _req(h, BF, "h"); _req(w_down_inject, BF, "w_down_inject"); _req(w_up, BF, "w_up"); _req(x, BF, "x")
+    H = x.shape[1]
+    assert w_down_inject.shape == (lowrank + n_inject, hc * H) and w_up.shape == (hc * H, lowrank)
+    _check(_lib().r4dxb_q4x_hc_gate(_p(h), _p(norm_w), _p(w_down_inject), _p(w_up), _p(mid), _p(injv), _p(rstd), _p(x), T, hc, H,
+                                    lowrank, n_inject, eps, _stream()), "q4x_hc_gate")
+    return x

@@ -173,6 +173,35 @@ def synthetic_weight_set(cfg: ModelConfig, device="cuda", seed: int = 0, sigma: 
             w[p + "gdn.dt_bias"] = n(Hv, dtype=torch.float32)
             w[p + "gdn.norm_weight"] = (1.0 + n(cfg.linear_value_head_dim).float()).to(torch.bfloat16)
     w["text.final_norm"] = n(H)
+    if cfg.is_qwen4_exp:
+        # the stream gates are this family's only norms; they, the indexer and the n-gram layer stay bf16
+        # (reference: src/model/qwen4exp_container.h:11-25 lists the tensors)
+        for k_ in [k_ for k_ in w if k_.endswith("layernorm") or k_ == "text.final_norm"]:
+            del w[k_]
+        hc, L, C = cfg.hc_count, cfg.hc_lowrank, cfg.hc_count * H
+
+        def gate(p: str, inject: bool = True):
+            w[p + "norm"] = n(C)
+            w[p + "down"] = n(L, C)
+            w[p + "up"] = (n(C, L).float() * 8).to(torch.bfloat16)
+            if inject:
+                w[p + "inject"] = n(hc, C)
+
+        for i in range(cfg.num_hidden_layers):
+            p = f"text.layers.{i}."
+            gate(p + "hc.attn.")
+            gate(p + "hc.mlp.")
+            if cfg.is_attention_layer(i) and cfg.indexer_heads:
+                w[p + "attn.indexer.qk"] = (n((cfg.indexer_heads + 1) * cfg.indexer_dim, H).float() * 4).to(torch.bfloat16)
+                w[p + "attn.indexer.q_norm"] = n(cfg.indexer_dim)
+                w[p + "attn.indexer.k_norm"] = n(cfg.indexer_dim)
+            if i in cfg.ple_layers:
+                w[p + "ple.key_proj"] = (n(C, cfg.ple_embed_dim).float() * 10).to(torch.bfloat16)
+                w[p + "ple.value_proj"] = (n(H, cfg.ple_embed_dim).float() * 10).to(torch.bfloat16)
+                for name in ("norm_key", "norm_query", "norm_conv"):
+                    w[p + "ple." + name] = n(C)
+                w[p + "ple.conv1d"] = (n(C, cfg.ple_conv_kernel).float() * 10).to(torch.bfloat16)
+        gate("text.hc_final.", inject=False)
     w["lm_head"] = w4a16.random_weight(cfg.vocab_shard_size, H, head_group, seed=seed + 17, sigma=sigma, device=device)
     if with_mtp and cfg.mtp_num_hidden_layers:
         # the next-token-prediction head: fc over [embedding | hidden], one gated attention layer, one MLP, its own norm

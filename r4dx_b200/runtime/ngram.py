@@ -286,6 +286,17 @@ class NgramTable:
             raise
         return NgramTable(path, head, mode, torch.device(device), fd, body, threads)
 
+    @staticmethod
+    def synthetic_device(header: NgramHeader, device="cuda", std: float = 0.02, seed: int = 0) -> "NgramTable":
+        """A table of random rows created directly in device memory (benchmarks: no file behind it)."""
+        g = torch.Generator(device=device).manual_seed(seed)
+        body = torch.empty(header.rows, header.head_dim, dtype=torch.bfloat16, device=device)
+        step = 1 << 22
+        for at in range(0, header.rows, step):
+            n = min(step, header.rows - at)
+            body[at:at + n] = (torch.randn(n, header.head_dim, generator=g, device=device) * std).to(torch.bfloat16)
+        return NgramTable("", header, "device", torch.device(device), -1, body, 1)
+
     def close(self) -> None:
         if self._fd >= 0:
             os.close(self._fd)

@@ -28,8 +28,12 @@ def main() -> None:
                     help="batched decode: every slot is prefilled with P random tokens (real caches and recurrent state) "
                          "instead of being positioned at --ctx with empty caches")
     ap.add_argument("--single", action="store_true", help="one sequence through the CUDA-graph decode path (one GPU)")
-    ap.add_argument("--family", default="qwen_moe", choices=["qwen_moe", "lfm2"],
-                    help="lfm2: the short-conv + attention MoE geometry (40 layers, 64 experts top-4); --single only")
+    ap.add_argument("--family", default="qwen_moe", choices=["qwen_moe", "lfm2", "qwen4_exp"],
+                    help="lfm2: the short-conv + attention MoE geometry (40 layers, 64 experts top-4); qwen4_exp: 4-stream "
+                         "residual, block-selecting attention, n-gram layer, 512 experts of inner width 640; both --single only")
+    ap.add_argument("--positioned", action="store_true", help="qwen4_exp: skip the real prefill, start at --ctx with empty caches")
+    ap.add_argument("--ngram-first-prime", type=int, default=1_000_000,
+                    help="qwen4_exp: per-head vocabulary of the synthetic device table (16 heads; 20,000,000 is the full 95 GiB table)")
     a = ap.parse_args()
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -45,6 +49,11 @@ def main() -> None:
         if not a.single or world > 1:
             raise SystemExit("--family lfm2 runs with --single on one GPU")
         cfg = lfm2_moe_config(layers=min(a.layers, 40))
+    elif a.family == "qwen4_exp":
+        if not a.single or world > 1:
+            raise SystemExit("--family qwen4_exp runs with --single on one GPU")
+        from r4dx_b200.config import qwen4_exp_config
+        cfg = qwen4_exp_config(min(a.layers, 48))
     else:
         cfg = qwen_hybrid_moe_config(a.layers)
     e_per = cfg.num_experts // world
@@ -66,6 +75,44 @@ def main() -> None:
         ms = e0.elapsed_time(e1)
         print(json.dumps({"metric": f"prefill tok/s, {a.family} geometry", "tokens": a.prefill, "layers": cfg.num_hidden_layers,
                           "ms": ms, "tok_s": a.prefill / (ms / 1e3)}))
+        return
+    if a.single and a.family == "qwen4_exp":
+        # really prefilled context (the 8-row path is this family's prompt path), then graph decode
+        from r4dx_b200.models.q4x import Qwen4ExpModel
+        from r4dx_b200.runtime import ngram as NG
+        hd = NG.make_header(cfg.vocab_size, cfg.ngram_head_dim, cfg.eos_token_id, seed=0, first_prime_after=a.ngram_first_prime)
+        table = NG.NgramTable.synthetic_device(hd, dev)
+        m = Qwen4ExpModel(cfg, w, ngram_table=table, max_ctx=a.ctx + a.steps + a.warmup + 64, device=dev)
+        ids = torch.randint(0, cfg.vocab_size, (a.ctx,), dtype=torch.int32)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if a.positioned:
+            m.pos, tok, pre_ms = a.ctx, 17, float("nan")       # empty caches at the position: for launch lists under a profiler
+        else:
+            m.prefill(ids[:64])
+            m.reset()
+            torch.cuda.synchronize()
+            e0.record()
+            tok = m.prefill(ids)
+            e1.record()
+            torch.cuda.synchronize()
+            pre_ms = e0.elapsed_time(e1)
+        m.enable_graphs((1,))
+        m.decode_begin(tok)
+        for _ in range(a.warmup):
+            m.decode_step_graph()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.steps):
+            m.decode_step_graph()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / a.steps
+        from r4dx_b200 import native
+        print(json.dumps({"metric": "batch-1 decode tok/s, qwen4_exp geometry", "ctx": a.ctx, "layers": cfg.num_hidden_layers,
+                          "ms_per_step": ms, "tok_s": 1e3 / ms, "prefill_tok_s": a.ctx / (pre_ms / 1e3),
+                          "weights_gib": m.weight_bytes() / 2**30, "ngram_table_gib": table.body.numel() * 2 / 2**30,
+                          "sparse_rows": bool(a.ctx + 1 > cfg.indexer_budget + cfg.indexer_ratio - 1),
+                          "reference_published_tok_s": 57.5 if a.ctx >= 2000 else 50.3, "reference_published_prefill_tok_s": "231-450"}))
         return
     if a.single:
         from r4dx_b200.models.hybrid import HybridModel

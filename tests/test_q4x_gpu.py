@@ -65,6 +65,19 @@ def test_stream_gate_kernels_match_the_oracle(K):
     hd = d(h)
     K.q4x_hc_inject(hd, d(out), dn[:, L:], hc)
     assert torch.allclose(hd.float().cpu(), h_ref, atol=4e-2, rtol=2e-2)
+    # the two-launch gate gives the same block input and injection logits as the chain
+    injv = torch.zeros(T, hc, dtype=torch.float32, device="cuda")
+    x2 = torch.zeros(T, H, dtype=BF, device="cuda")
+    K.q4x_hc_gate(d(h), d(w[p + "norm"]), d(torch.cat([w[p + "down"], w[p + "inject"]], 0)), d(w[p + "up"]),
+                  torch.zeros(8, L, dtype=BF, device="cuda"), injv, torch.zeros(8, hc, dtype=torch.float32, device="cuda"), x2, T, hc, L, hc,
+                  cfg.rms_norm_eps)
+    assert (x2.float() - x.float()).abs().max().item() <= 2e-2 and torch.allclose(x2.float().cpu(), x_ref, atol=3e-2, rtol=2e-2)
+    assert torch.allclose(injv, dn[:, L:], atol=2e-3, rtol=1e-3)
+    x3 = torch.zeros(T, H, dtype=BF, device="cuda")
+    K.q4x_hc_gate(d(h), d(w["text.hc_final.norm"]), d(w["text.hc_final.down"]), d(w["text.hc_final.up"]),
+                  torch.zeros(8, L, dtype=BF, device="cuda"), injv, torch.zeros(8, hc, dtype=torch.float32, device="cuda"), x3, T, hc, L, 0,
+                  cfg.rms_norm_eps)
+    assert torch.allclose(x3.float().cpu(), o.hc_prep("text.hc_final.", h, inject=False)[0], atol=3e-2, rtol=2e-2)
     # embedding rows repeated over the streams; an id outside the table is loud
     ids = torch.tensor([3, 9, 4095, 5000], dtype=torch.int32, device="cuda")
     e = K.q4x_embed_repeat(d(w["text.embed_tokens"]), ids, torch.empty(4, hc * H, dtype=BF, device="cuda"), hc)
