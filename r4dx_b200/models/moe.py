@@ -98,6 +98,8 @@ class MoeBlock:
         self.ks_gu_few = K.pick_ksplit(self.gate_up.N, self.gate_up.K, target_ctas=per_expert)
         self.ks_dn_few = K.pick_ksplit(self.down.N, self.down.K, target_ctas=per_expert)
 
+    compact_grid = os.environ.get("R4DXB_MOE_COMPACT_GRID", "1") != "0"
+
     def route(self, h: torch.Tensor, T: int) -> None:
         if T > 8:
             K.linear_tc(self.router, h[:T], out=self.logits[:T])      # many rows: the router is a tensor-core product
@@ -121,6 +123,14 @@ class MoeBlock:
         tmax = self.tmax if T <= 4 else 8
         n_pass = ((max_rows if max_rows is not None else T) + tmax - 1) // tmax
         ks_gu, ks_dn = (self.ks_gu_few, self.ks_dn_few) if T <= 2 else (self.ks_gu, self.ks_dn)
+        P = T * self.k
+        if P < g.E and self.compact_grid:
+            # fewer routed pairs than local experts (a decode step: 10 of 512): launch CTAs for the named experts only
+            K.trellis_gemv_grouped_pairs(g.words, g.suh, g.svh, h, self.gu_pairs, self.offsets, self.perm, self.ids, P, self.e_begin,
+                                         self.k, n_pass, tmax, K.PRO_NONE, g.E, g.N, g.K, g.kb, ks_gu)
+            K.trellis_gemv_grouped_pairs(d.words, d.suh, d.svh, self.gu_pairs, self.y_pairs, self.offsets, self.perm, self.ids, P,
+                                         self.e_begin, 1, n_pass, tmax, K.PRO_SILU_MUL, d.E, d.N, d.K, d.kb, ks_dn)
+            return
         K.trellis_gemv_grouped(g.words, g.suh, g.svh, h, self.gu_pairs, self.offsets, self.perm, self.k, n_pass, tmax,
                                K.PRO_NONE, g.E, g.N, g.K, g.kb, ks_gu)
         K.trellis_gemv_grouped(d.words, d.suh, d.svh, self.gu_pairs, self.y_pairs, self.offsets, self.perm, 1, n_pass, tmax,

@@ -233,6 +233,12 @@ int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void*
                                  void* const* recv, void* block_seq, int* status, int world, int rank, int spin_limit,
                                  void* stream);
 
+/* grouped expert product over a compact grid: blockIdx.z runs over the call's `pairs` routed (row, slot) pairs (pair_ids =
+ * their global expert ids) instead of every local expert; results equal r4dxb_trellis_gemv_grouped */
+int r4dxb_trellis_gemv_grouped_pairs(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                                     const int* offsets, const int* perm, const int* pair_ids, int pairs, int e_begin,
+                                     int in_div, int pass, int tmax, int prologue, int experts, int N, int K, int kb, int ksplit,
+                                     void* stream);
 /* GDN decode step with the output gate of its norm chosen by the caller: gate_act 0 = silu(z), 1 = sigmoid(z). */
 int r4dxb_gdn_decode_gate(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
                           const float* dt_bias, const void* norm_w, void* ring, float* state, float* log_u, float* log_k,

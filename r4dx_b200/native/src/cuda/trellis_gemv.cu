@@ -70,6 +70,11 @@ struct GemvArgs {
   int g_spin_limit;
   int* g_status;
   long long g_words_stride;        // words between consecutive experts
+  // compact grid (optional): blockIdx.z runs over the call's (row, slot) pairs instead of every local expert; the CTAs of
+  // the first pair in an expert's list run that expert, the others leave.  A decode step touches 10 of 512 experts: the
+  // full grid spent most of the kernel's time launching CTAs that return at once.
+  const int* g_pair_ids;           // [pairs] global expert id of each pair (the router's output)
+  int g_e_begin, g_experts;
   int act;                         // gate activation of the fused gated-MLP prologue (GateAct)
   // sibling mode: up to kMaxSiblings weights that read the same activations through the same prologue (q / k / v,
   // the GDN qkv / z pair) share one launch; blockIdx.y runs over the row blocks of all of them back to back
@@ -117,7 +122,12 @@ TrellisGemvKernel(GemvArgs a, TpPush tp) {
   int g_base = 0;
   if constexpr (kGrouped) {
     // this launch handles rows [g_pass * TMAX, +TMAX) of every expert's list
-    const int e = blockIdx.z;
+    int e = blockIdx.z;
+    if (a.g_pair_ids != nullptr) {
+      e = a.g_pair_ids[blockIdx.z] - a.g_e_begin;
+      if (e < 0 || e >= a.g_experts) return;                                   // (uniform over the cluster, like the exit below)
+      if (a.g_perm[a.g_offsets[e]] != static_cast<int>(blockIdx.z)) return;   // not the first pair of its expert
+    }
     g_base = a.g_offsets[e] + a.g_pass * TMAX;
     const int left = a.g_offsets[e + 1] - g_base;
     if (left <= 0) return;         // uniform over the cluster: every CTA of it leaves before any barrier
@@ -469,7 +479,7 @@ int LaunchGrouped(GemvArgs a, int ksplit, int experts, cudaStream_t stream, cons
     if (e != cudaSuccess) return static_cast<int>(e);
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(ksplit, a.N / 128, experts);
+  cfg.gridDim = dim3(ksplit, a.N / 128, experts);       // (experts = the pair count when the grid is compact)
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -615,6 +625,35 @@ int r4dxb_trellis_gemv_grouped_ep(const void* words, const void* suh, const void
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define R4DXB_G(KBV, TM, PROV) \
   if (kb == KBV && tmax == TM && prologue == PROV) return LaunchGrouped<KBV, TM, PROV>(a, ksplit, experts, s, ep);
+  R4DXB_G(3, 2, 0) R4DXB_G(3, 2, 2) R4DXB_G(3, 8, 0) R4DXB_G(3, 8, 2)
+  R4DXB_G(4, 2, 0) R4DXB_G(4, 2, 2) R4DXB_G(4, 8, 0) R4DXB_G(4, 8, 2)
+  R4DXB_G(5, 2, 0) R4DXB_G(5, 2, 2) R4DXB_G(5, 8, 0) R4DXB_G(5, 8, 2)
+#undef R4DXB_G
+  return R4DXB_BAD_ARG;
+}
+
+/* The grouped product over a compact grid: pair_ids [pairs] are the routed expert ids of the call's (row, slot) pairs;
+ * only experts that some pair names get CTAs (a decode step: 10 of 512).  Same results as the full grid. */
+int r4dxb_trellis_gemv_grouped_pairs(const void* words, const void* suh, const void* svh, const void* x, void* y,
+                                     const int* offsets, const int* perm, const int* pair_ids, int pairs, int e_begin,
+                                     int in_div, int pass, int tmax, int prologue, int experts, int N, int K, int kb, int ksplit,
+                                     void* stream) {
+  if (int rc = CheckArgs(1, N, K, ksplit)) return rc;
+  if (experts < 1 || pairs < 1 || pairs > 65535 || in_div < 1 || (prologue != 0 && prologue != 2) || pair_ids == nullptr)
+    return R4DXB_BAD_ARG;
+  GemvArgs a = MakeArgs(words, suh, svh, x, y, nullptr, nullptr, 0.f, tmax, N, K);
+  a.g_offsets = offsets;
+  a.g_perm = perm;
+  a.g_in_div = in_div;
+  a.g_pass = pass;
+  a.g_words_stride = static_cast<long long>(N / 16) * (K / 16) * 8 * kb;
+  a.g_pair_ids = pair_ids;
+  a.g_e_begin = e_begin;
+  a.g_experts = experts;
+  const TpPush ep = {};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define R4DXB_G(KBV, TM, PROV) \
+  if (kb == KBV && tmax == TM && prologue == PROV) return LaunchGrouped<KBV, TM, PROV>(a, ksplit, pairs, s, ep);
   R4DXB_G(3, 2, 0) R4DXB_G(3, 2, 2) R4DXB_G(3, 8, 0) R4DXB_G(3, 8, 2)
   R4DXB_G(4, 2, 0) R4DXB_G(4, 2, 2) R4DXB_G(4, 8, 0) R4DXB_G(4, 8, 2)
   R4DXB_G(5, 2, 0) R4DXB_G(5, 2, 2) R4DXB_G(5, 8, 0) R4DXB_G(5, 8, 2)

@@ -97,6 +97,8 @@ const R4dxbKernelInfo kKernels[] = {
      "world 2..8; hidden up to the symmetric buffer", "bf16 x, packed trellis words, bf16 y, fp32 pairs over NVLink", "simt+peer-stores", c3, 5},
     {"trellis_gemv_grouped", "gemm", "moe_experts_rows_le_16", "every local expert times its planned rows (8 rows per pass), SwiGLU prologue for the down projection",
      "experts <= 65535", "bf16 x, stacked trellis words", "simt+bulk-copy", c4, 4},
+    {"trellis_gemv_grouped_pairs", "gemm", "moe_experts_rows_le_16", "the grouped expert product over a compact grid: only experts named by the call's routed pairs get CTAs",
+     "pairs <= 65535", "bf16 x, stacked trellis words", "simt+bulk-copy", c4, 4},
     {"trellis_gemv_grouped_ep", "gemm+collective", "moe_experts_expert_parallel", "grouped experts over rows that arrive from peers; results pushed back to the owning rank",
      "world <= 8", "bf16 rows over NVLink", "simt+peer-stores", c5, 3},
     {"trellis_input", "quant", "trellis_input_transform", "xh = fp16(H128(suh * x)), optionally x = act(gate) * up",

@@ -662,6 +662,21 @@ def moe_combine(y_pairs, ids, weights, shared, shared_gate, residual, out, T: in
     return out
 
 
+register_cuda_sig("r4dxb_trellis_gemv_grouped_pairs", _I, [_P] * 8 + [_I] * 11 + [_P])
+
+
+def trellis_gemv_grouped_pairs(words, suh, svh, x, y, offsets, perm, pair_ids, pairs: int, e_begin: int, in_div: int, n_pass: int,
+                               tmax: int, prologue: int, experts: int, N: int, Kd: int, kb: int, ksplit: int):
+    """The grouped expert product launched over the call's routed pairs only (``pair_ids`` = the router's expert ids,
+    [pairs] int32): the CTAs of the first pair of each expert's list run that expert, so a decode step launches
+    10 experts' CTAs instead of 512 experts' (most of which returned at once)."""
+    for p_ in range(n_pass):
+        _check(_lib().r4dxb_trellis_gemv_grouped_pairs(_p(words), _p(suh), _p(svh), _p(x), _p(y), _p(offsets), _p(perm), _p(pair_ids),
+                                                       pairs, e_begin, in_div, p_, tmax, prologue, experts, N, Kd, kb, ksplit,
+                                                       _stream()), "trellis_gemv_grouped_pairs")
+    return y
+
+
 def trellis_gemv_grouped(words, suh, svh, x, y, offsets, perm, in_div: int, n_pass: int, tmax: int, prologue: int,
                          experts: int, N: int, Kd: int, kb: int, ksplit: int):
     """Every local expert times its planned rows; ``n_pass`` launches cover up to n_pass * tmax rows per expert."""

@@ -591,6 +591,20 @@ def test_grouped_expert_gemv(K):
             ref = trellis.linear_reference(ws[int(ids[t, j])], x[t:t + 1].float())[0]
             got = y[t * k + j].float().cpu()
             assert (got - ref).abs().max().item() < 0.03 * ref.abs().max().item() + 1e-3
+    # the compact grid (CTAs for the experts the pairs name, here a local slice 1..4 of the six) writes the same rows
+    e_begin, e_count = 1, 4
+    sub = ExpertStack.from_list([w.to("cuda") for w in ws[e_begin:e_begin + e_count]])
+    off2 = torch.zeros(e_count + 1, dtype=torch.int32, device="cuda")
+    perm2 = torch.zeros(T * k, dtype=torch.int32, device="cuda")
+    K.moe_plan(ids.cuda(), T * k, E, e_begin, e_count, off2, perm2)
+    y_full = torch.zeros(T * k, N, dtype=BF, device="cuda")
+    y_pairs = torch.zeros(T * k, N, dtype=BF, device="cuda")
+    K.trellis_gemv_grouped(sub.words, sub.suh, sub.svh, x.cuda(), y_full, off2, perm2, k, (T + 1) // 2, 2, 0, e_count, N, Kd, 3, 2)
+    K.trellis_gemv_grouped_pairs(sub.words, sub.suh, sub.svh, x.cuda(), y_pairs, off2, perm2, ids.cuda(), T * k, e_begin, k,
+                                 (T + 1) // 2, 2, 0, e_count, N, Kd, 3, 2)
+    assert torch.equal(y_full, y_pairs)
+    local = ((ids >= e_begin) & (ids < e_begin + e_count)).view(-1)
+    assert torch.equal(y_full[local.cuda()], y[local.cuda()]) and float(y_pairs[~local.cuda()].abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("kb,tn,T", [(3, 16, 40), (4, 32, 90), (5, 64, 150), (3, 128, 300), (4, 256, 700)])
