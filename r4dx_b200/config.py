@@ -259,18 +259,8 @@ class ModelConfig:
         known = {f.name for f in dataclasses.fields(ModelConfig)}
         cfg = ModelConfig(**{k: v for k, v in d.items() if k in known})
         if d.get("model_type") == "qwen4_exp" and "arch" not in d:
-            # the checkpoint's own key names (reference: src/model/qwen4exp_config.h:1-110); ple_layer_ids is 1-indexed there
-            cfg.arch = "qwen4_exp"
-            cfg.ple_layers = [int(i) - 1 for i in d.get("ple_layer_ids", [])]
-            cfg.ple_conv_kernel = int(d.get("ple_conv_kernel_size", 4))
-            cfg.ple_conv_dilation = int(d.get("ngram_size", 3))
-            cfg.indexer_heads = int(d.get("indexer_heads", d.get("index_n_heads", 4)))
-            cfg.indexer_dim = int(d.get("indexer_head_dim", d.get("index_head_dim", 128)))
-            cfg.indexer_ratio = int(d.get("indexer_compress_ratio", 4))
-            cfg.indexer_budget = int(d.get("indexer_budget", 2048))
-            cfg.gdn_gate_act = str(d.get("output_gate_type", "sigmoid"))
-            cfg.final_norm = False
-            cfg.mtp_num_hidden_layers = 0
+            from .quant.hf_import import config_from_hf      # the checkpoint's own key names (1-based ple_layer_ids, indexer_n_heads, ...)
+            return config_from_hf(text)
         if not cfg.layer_types and cfg.num_hidden_layers:
             interval = int(d.get("full_attention_interval", 4))
             cfg.layer_types = ["full_attention" if (i + 1) % interval == 0 else "linear_attention"

@@ -55,6 +55,31 @@ def config_from_hf(text: str) -> ModelConfig:
                           routed_scaling_factor=float(t.get("routed_scaling_factor", 1.0)),
                           num_dense_layers=t.get("num_dense_layers", 0), short_conv_taps=t.get("conv_L_cache", 3),
                           **{**common, "rms_norm_eps": t.get("norm_eps", 1e-5), "tie_word_embeddings": True})
+    elif mt == "qwen4_exp" or t.get("hc_count", 0):
+        # 4-stream gated residual, block-selecting attention, one n-gram layer (reference: src/convert/qwen4exp_layout.cpp:60-108
+        # reads these keys; ple_layer_ids is 1-based there)
+        rope = t.get("rope_parameters") or {}
+        types = t.get("layer_types") or ["full_attention" if (i + 1) % int(t.get("full_attention_interval", 4)) == 0 else "linear_attention"
+                                         for i in range(L)]
+        cfg = ModelConfig(arch="qwen4_exp", layer_types=list(types), attn_output_gate=True,
+                          partial_rotary_factor=t.get("partial_rotary_factor", rope.get("partial_rotary_factor", 0.25)),
+                          rope_theta=t.get("rope_theta", rope.get("rope_theta", 1.0e7)),
+                          linear_num_key_heads=t["linear_num_key_heads"], linear_num_value_heads=t["linear_num_value_heads"],
+                          linear_key_head_dim=t["linear_key_head_dim"], linear_value_head_dim=t["linear_value_head_dim"],
+                          linear_conv_kernel_dim=t.get("linear_conv_kernel_dim", 4), mtp_num_hidden_layers=0,
+                          num_experts=t["num_experts"], num_experts_per_tok=t.get("num_experts_per_tok", 10),
+                          moe_intermediate_size=t["moe_intermediate_size"],
+                          shared_expert_intermediate_size=t.get("shared_expert_intermediate_size", 0),
+                          norm_topk_prob=bool(t.get("norm_topk_prob", True)), hc_count=t["hc_count"], hc_lowrank=t["hc_lowrank"],
+                          ple_layers=[int(i) - 1 for i in t.get("ple_layer_ids", [])], ple_embed_dim=t.get("ple_embed_dim", 0),
+                          ple_conv_kernel=t.get("ple_conv_kernel_size", 4), ple_conv_dilation=t.get("ngram_size", 3),
+                          indexer_heads=t.get("indexer_n_heads", t.get("indexer_heads", 4)), indexer_dim=t.get("indexer_head_dim", 128),
+                          indexer_ratio=t.get("indexer_compress_ratio", 4), indexer_budget=t.get("indexer_budget", 2048),
+                          gdn_gate_act=t.get("output_gate_type", "sigmoid"), final_norm=False,
+                          eos_token_id=int(t.get("eos_token_id", d.get("eos_token_id", 248044)) or 248044),
+                          **{**common, "tie_word_embeddings": False})
+        if t.get("indexer_kv_heads", 1) != 1:
+            raise ValueError("qwen4_exp: the indexer is built for one key head")
     elif "gemma" in mt:
         pattern = t.get("sliding_window_pattern", 6)
         cfg = ModelConfig(arch="gemma", layer_types=["full_attention"] * L, attn_output_gate=False, qk_norm=True,
@@ -140,6 +165,8 @@ def import_hf_weights(cfg: ModelConfig, hf: Dict[str, torch.Tensor], prefix: str
 
     if cfg.arch == "lfm2_moe":
         return _import_lfm2(cfg, get, has)
+    if cfg.is_qwen4_exp:
+        return _import_qwen4_exp(cfg, get, has, hf)
     out: Dict[str, torch.Tensor] = {}
     emb = get("embed_tokens.weight")
     out["text.embed_tokens"] = emb * cfg.embed_scale
@@ -180,6 +207,97 @@ def import_hf_weights(cfg: ModelConfig, hf: Dict[str, torch.Tensor], prefix: str
                 out[p + f"moe.experts.{e}.down"] = get(m + f"experts.{e}.down_proj.weight")
         else:
             out[p + "mlp.gate_up"], out[p + "mlp.down"] = gate_up(m), get(m + "down_proj.weight")
+    return out
+
+
+_Q4X_GATE = (("norm", "hc_norm.weight"), ("down", "input_mix_weight_down.weight"), ("up", "input_mix_weight_up.weight"),
+             ("inject", "block_inject_weight.weight"))
+_Q4X_PLE = ("key_proj", "value_proj", "norm_key", "norm_query", "norm_conv")
+
+
+def _import_qwen4_exp(cfg: ModelConfig, get, has, hf) -> Dict[str, torch.Tensor]:
+    """qwen4_exp checkpoint names -> container names (reference: src/convert/qwen4exp_layout.cpp:140-228 is the same
+    table).  Norm weights keep the checkpoint's zero-centred convention; the n-gram table itself (``*.ple.ple_embedding.*``)
+    is not part of the weight set: it becomes the table file (``runtime/ngram.py``)."""
+    out: Dict[str, torch.Tensor] = {"text.embed_tokens": get("embed_tokens.weight")}
+    if "lm_head.weight" not in hf:
+        raise KeyError("qwen4_exp checkpoint without lm_head.weight (the head is not tied in this family)")
+    out["lm_head"] = hf["lm_head.weight"].float()
+    for mine, theirs in _Q4X_GATE[:3]:
+        out["text.hc_final." + mine] = get("hyper_connection_mixer." + theirs)
+    for i in range(cfg.num_hidden_layers):
+        p, s = f"text.layers.{i}.", f"layers.{i}."
+        for blk in ("attn", "mlp"):
+            for mine, theirs in _Q4X_GATE:
+                out[p + f"hc.{blk}.{mine}"] = get(s + f"{blk}_hyper_connection.{theirs}")
+        if cfg.is_attention_layer(i):
+            a = s + "self_attn."
+            out[p + "attn.qg"], out[p + "attn.o"] = get(a + "q_proj.weight"), get(a + "o_proj.weight")
+            out[p + "attn.k"], out[p + "attn.v"] = get(a + "k_proj.weight"), get(a + "v_proj.weight")
+            out[p + "attn.q_norm"], out[p + "attn.k_norm"] = get(a + "q_norm.weight"), get(a + "k_norm.weight")
+            out[p + "attn.k_descale"] = torch.ones(cfg.num_key_value_heads)
+            out[p + "attn.v_descale"] = torch.ones(cfg.num_key_value_heads)
+            out[p + "attn.indexer.qk"] = get(a + "indexer.index_qk_proj.weight")
+            out[p + "attn.indexer.q_norm"] = get(a + "indexer.q_layernorm.weight")
+            out[p + "attn.indexer.k_norm"] = get(a + "indexer.k_layernorm.weight")
+        else:
+            g = s + "linear_attn."
+            for name in ("in_proj_qkv", "in_proj_z", "in_proj_a", "in_proj_b", "out_proj"):
+                out[p + "gdn." + name] = get(g + name + ".weight")
+            out[p + "gdn.conv1d_weight"] = get(g + "conv1d.weight").reshape(cfg.conv_dim, -1)
+            out[p + "gdn.A_log"], out[p + "gdn.dt_bias"] = get(g + "A_log"), get(g + "dt_bias")
+            out[p + "gdn.norm_weight"] = get(g + "norm.weight")
+        if i in cfg.ple_layers:
+            for name in _Q4X_PLE:
+                out[p + "ple." + name] = get(s + f"ple.{name}.weight")
+            out[p + "ple.conv1d"] = get(s + "ple.conv1d.weight").reshape(cfg.hc_count * cfg.hidden_size, -1)
+        m = s + "mlp."
+        out[p + "moe.router"] = get(m + "gate.weight")
+        out[p + "moe.shared_gate"] = get(m + "shared_expert_gate.weight").reshape(1, -1)
+        gu = lambda b: torch.cat([get(b + "gate_proj.weight"), get(b + "up_proj.weight")], 0).contiguous()
+        out[p + "moe.shared.gate_up"], out[p + "moe.shared.down"] = gu(m + "shared_expert."), get(m + "shared_expert.down_proj.weight")
+        for e in range(cfg.num_experts):
+            out[p + f"moe.experts.{e}.gate_up"] = gu(m + f"experts.{e}.")
+            out[p + f"moe.experts.{e}.down"] = get(m + f"experts.{e}.down_proj.weight")
+    return out
+
+
+def export_qwen4_exp(cfg: ModelConfig, w: Dict[str, torch.Tensor], prefix: str = "model.language_model.") -> Dict[str, torch.Tensor]:
+    """Container names -> the checkpoint's names (round-trip tests and synthetic checkpoints)."""
+    H, I = cfg.hidden_size, cfg.moe_intermediate_size
+    out: Dict[str, torch.Tensor] = {prefix + "embed_tokens.weight": w["text.embed_tokens"], "lm_head.weight": w["lm_head"]}
+    for mine, theirs in _Q4X_GATE[:3]:
+        out[prefix + "hyper_connection_mixer." + theirs] = w["text.hc_final." + mine]
+    for i in range(cfg.num_hidden_layers):
+        p, s = f"text.layers.{i}.", prefix + f"layers.{i}."
+        for blk in ("attn", "mlp"):
+            for mine, theirs in _Q4X_GATE:
+                out[s + f"{blk}_hyper_connection.{theirs}"] = w[p + f"hc.{blk}.{mine}"]
+        if cfg.is_attention_layer(i):
+            a = s + "self_attn."
+            for mine, theirs in (("qg", "q_proj"), ("k", "k_proj"), ("v", "v_proj"), ("o", "o_proj"), ("q_norm", "q_norm"), ("k_norm", "k_norm")):
+                out[a + theirs + ".weight"] = w[p + "attn." + mine]
+            out[a + "indexer.index_qk_proj.weight"] = w[p + "attn.indexer.qk"]
+            out[a + "indexer.q_layernorm.weight"], out[a + "indexer.k_layernorm.weight"] = w[p + "attn.indexer.q_norm"], w[p + "attn.indexer.k_norm"]
+        else:
+            g = s + "linear_attn."
+            for name in ("in_proj_qkv", "in_proj_z", "in_proj_a", "in_proj_b", "out_proj"):
+                out[g + name + ".weight"] = w[p + "gdn." + name]
+            out[g + "conv1d.weight"] = w[p + "gdn.conv1d_weight"].reshape(cfg.conv_dim, 1, -1)
+            out[g + "A_log"], out[g + "dt_bias"], out[g + "norm.weight"] = w[p + "gdn.A_log"], w[p + "gdn.dt_bias"], w[p + "gdn.norm_weight"]
+        if i in cfg.ple_layers:
+            for name in _Q4X_PLE:
+                out[s + f"ple.{name}.weight"] = w[p + "ple." + name]
+            out[s + "ple.conv1d.weight"] = w[p + "ple.conv1d"].reshape(cfg.hc_count * H, 1, -1)
+        m = s + "mlp."
+        out[m + "gate.weight"], out[m + "shared_expert_gate.weight"] = w[p + "moe.router"], w[p + "moe.shared_gate"]
+        S = cfg.shared_expert_intermediate_size
+
+        def split(base: str, gu: torch.Tensor, down: torch.Tensor, inner: int):
+            out[base + "gate_proj.weight"], out[base + "up_proj.weight"], out[base + "down_proj.weight"] = gu[:inner], gu[inner:], down
+        split(m + "shared_expert.", w[p + "moe.shared.gate_up"], w[p + "moe.shared.down"], S)
+        for e in range(cfg.num_experts):
+            split(m + f"experts.{e}.", w[p + f"moe.experts.{e}.gate_up"], w[p + f"moe.experts.{e}.down"], I)
     return out
 
 

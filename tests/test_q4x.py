@@ -181,3 +181,55 @@ def test_stream_gate_and_ngram_layer_move_the_output(tiny, table):
     assert x.shape == (3, cfg.hidden_size) and torch.allclose(inj, torch.ones(3, cfg.hc_count))
     out = torch.randn(3, cfg.hidden_size)
     assert torch.allclose(m2.hc_inject(h, out, inj), h + out.repeat(1, cfg.hc_count))
+
+
+def test_awq_pack_quantized_round_trip_and_view():
+    from r4dx_b200.quant import awq
+    g = torch.Generator().manual_seed(0)
+    w = torch.randn(20, 256, generator=g) * 0.05               # N not a multiple of 8: the zero points pad their last word
+    t = awq.quantize(w, 128)
+    assert t["weight_packed"].shape == (20, 32) and t["weight_zero_point"].shape == (3, 2) and t["weight_packed"].dtype == torch.int32
+    d = awq.dequantize(t["weight_packed"], t["weight_scale"], t["weight_zero_point"], 20, 256, 128)
+    assert d.dtype == torch.bfloat16 and (d.float() - w).abs().max().item() < 0.6 * float(t["weight_scale"].float().max())
+    # element by element from the definition: nibble j of word c is column 8 c + j; nibble n % 8 of zero-point row n / 8
+    for n, k in ((0, 0), (7, 9), (19, 255), (8, 128)):
+        q = (int(t["weight_packed"][n, k // 8]) >> (4 * (k % 8))) & 0xF
+        zp = (int(t["weight_zero_point"][n // 8, k // 128]) >> (4 * (n % 8))) & 0xF
+        want = torch.tensor(float(q - zp) * float(t["weight_scale"][n, k // 128])).to(torch.bfloat16)
+        assert d[n, k] == want
+    raw = {"a.b." + k_: v for k_, v in t.items()}
+    raw["a.norm.weight"] = torch.ones(4)
+    view = awq.AwqView(raw)
+    assert sorted(view) == ["a.b.weight", "a.norm.weight"] and "a.b.weight_packed" not in view and "a.b.weight" in view
+    assert torch.equal(view["a.b.weight"], d) and torch.equal(view["a.norm.weight"], torch.ones(4))
+    with pytest.raises(KeyError):
+        view["a.b.weight_scale"]
+    del raw["a.b.weight_shape"]
+    with pytest.raises(ValueError, match="weight_shape"):
+        awq.AwqView(raw)
+    cfg_ok = '{"quantization_config": {"format": "pack-quantized", "config_groups": {"g0": {"weights": {"num_bits": 4, "strategy": "group", "symmetric": false, "group_size": 128}}}}}'
+    assert awq.pack_scheme(cfg_ok) == 128 and awq.pack_scheme("{}") is None
+    with pytest.raises(ValueError):
+        awq.pack_scheme(cfg_ok.replace('"num_bits": 4', '"num_bits": 8'))
+
+
+def test_checkpoint_names_round_trip_through_the_importer(tiny):
+    from r4dx_b200.quant.hf_import import config_from_hf, export_qwen4_exp, import_hf_weights
+    cfg, w, _ = tiny
+    hf = export_qwen4_exp(cfg, w)
+    assert "model.language_model.layers.3.self_attn.indexer.index_qk_proj.weight" in hf
+    assert "model.language_model.layers.1.ple.conv1d.weight" in hf and hf["model.language_model.layers.1.ple.conv1d.weight"].dim() == 3
+    assert "model.language_model.layers.0.attn_hyper_connection.block_inject_weight.weight" in hf
+    back = import_hf_weights(cfg, hf)
+    assert set(back) == set(w)
+    for k_ in w:
+        assert torch.equal(back[k_], w[k_].float()), k_
+    import json
+    text = {"model_type": "qwen4_exp", "hidden_size": 256, "num_hidden_layers": 4, "layer_types": cfg.layer_types,
+            "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "linear_num_key_heads": 2, "linear_num_value_heads": 4,
+            "linear_key_head_dim": 64, "linear_value_head_dim": 64, "vocab_size": 4096, "num_experts": 16, "num_experts_per_tok": 4,
+            "moe_intermediate_size": 128, "shared_expert_intermediate_size": 128, "hc_count": 4, "hc_lowrank": 32,
+            "ple_layer_ids": [2], "ple_embed_dim": 256, "ple_conv_kernel_size": 4, "ngram_size": 3, "indexer_n_heads": 2,
+            "indexer_kv_heads": 1, "indexer_head_dim": 64, "indexer_budget": 16, "output_gate_type": "sigmoid", "eos_token_id": 7}
+    c2 = config_from_hf(json.dumps({"model_type": "qwen4_exp", "text_config": text}))
+    assert c2 == cfg
