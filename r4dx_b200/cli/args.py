@@ -23,6 +23,11 @@ def add_model_flags(ap: argparse.ArgumentParser) -> None:
     g.add_argument("--dflash-p-min", type=float, default=0.0)
     g.add_argument("--dflash-n-min", type=int, default=0)
     g.add_argument("--vision", default="off", choices=["off", "on"])
+    g.add_argument("--ngram-sidecar", default=None, metavar="FILE",
+                   help="qwen4_exp: the n-gram table file (default: the one the container records, next to it)")
+    g.add_argument("--ngram-placement", default="device", choices=["device", "pinned", "file"],
+                   help="qwen4_exp: where the n-gram table lives; device (95 GiB for the full table, no host work per token, "
+                        "CUDA-graph decode), pinned host memory, or positioned reads from the file (both: host ids, eager decode)")
     g.add_argument("--dialect", default="auto", choices=["auto", "qwen", "gemma", "lfm2", "llama"],
                    help="reasoning markers and tool-call syntax; auto picks by model id and architecture")
     g.add_argument("--audio", default="off", choices=["off", "on"],
@@ -117,6 +122,9 @@ def convert_parser() -> argparse.ArgumentParser:
     ap.add_argument("--rotation-out", default=None, metavar="FILE.safetensors",
                     help="with --rotate and no quantization wanted: write only the rotation tensors and exit")
     ap.add_argument("--vision", default="off", choices=["on", "off"], help="keep the checkpoint's vision tower tensors (bf16)")
+    ap.add_argument("--ngram-sidecar", default=None, metavar="FILE",
+                    help="qwen4_exp: the n-gram table file the container refers to (required for that family; a random:q4x source "
+                         "writes a small synthetic table there if the file does not exist)")
     ap.add_argument("--dflash-hf", default=None, metavar="DIR",
                     help="also convert a block-diffusion drafter checkpoint (safetensors + config.json) into <output>.dflash")
     ap.add_argument("--trellis-from", default=None, metavar="DIR",

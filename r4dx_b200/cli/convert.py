@@ -28,14 +28,19 @@ def load_source(spec: str, layers: int, mtp: bool, seed: int, raw_out=None):
     from ..models.oracle import init_weights
     if spec.startswith("random:"):
         # tiny random-init models of every family (reference: tools/convert_ref/make_tiny_*.py)
+        from ..config import tiny_qwen4_exp_config
         makers = {"tiny": tiny_hybrid_config, "small": small_hybrid_config, "moe": tiny_moe_config, "llama": tiny_llama_config,
-                  "gemma": tiny_gemma_config, "lfm2": tiny_lfm2_config}
+                  "gemma": tiny_gemma_config, "lfm2": tiny_lfm2_config, "q4x": tiny_qwen4_exp_config}
         kind = spec.split(":", 1)[1]
         if kind not in makers:
             raise SystemExit(f"unknown random model {kind!r}; one of {sorted(makers)}")
         cfg = makers[kind]()
         if layers:
             cfg.num_hidden_layers, cfg.layer_types = layers, cfg.layer_types[:layers]
+            cfg.ple_layers = [i for i in cfg.ple_layers if i < layers]
+        if cfg.is_qwen4_exp:
+            from ..models.q4x_oracle import init_q4x_weights
+            return cfg, init_q4x_weights(cfg, seed)
         return cfg, init_weights(cfg, seed, with_mtp=mtp)
     if spec.endswith(".gguf"):
         from ..quant.gguf import import_gguf
@@ -57,8 +62,12 @@ def load_source(spec: str, layers: int, mtp: bool, seed: int, raw_out=None):
         return ModelConfig.from_json(cfg_text), w
     # a Hugging Face checkpoint: read its config.json and rename / reshape the tensors
     from ..quant.hf_import import config_from_hf, import_hf_weights
+    from ..quant import awq
+    group = awq.pack_scheme(cfg_text)
+    if group is not None:
+        w = awq.AwqView(w, group)            # int4 pack-quantized linears read as bf16 weights, dequantized when touched
     if raw_out is not None:
-        raw_out.update(w)
+        raw_out.update({k: w[k] for k in w if "visual." in k or "vision_tower." in k} if group is not None else w)
     cfg = config_from_hf(cfg_text)
     if layers:
         cfg.num_hidden_layers, cfg.layer_types = layers, cfg.layer_types[:layers]
@@ -73,6 +82,14 @@ def main(argv=None) -> int:
         torch.set_num_threads(args.threads)
     raw = {}
     cfg, w = load_source(args.input, args.layers, args.mtp, args.seed, raw_out=raw)
+    if cfg.is_qwen4_exp:
+        # text only, its own residual structure: the flags below do not apply (reference: docs/qwen4exp.md "Convert" refuses the same)
+        bad = [f for f, on in (("--rotate", args.rotate != "none"), ("--vision on", args.vision == "on"), ("--mtp", args.mtp),
+                               ("--dflash-hf", bool(args.dflash_hf)), ("--reuse-tensors-from", bool(args.reuse_tensors_from))) if on]
+        if bad:
+            raise SystemExit("qwen4_exp does not support: " + ", ".join(bad))
+        if not args.ngram_sidecar:
+            raise SystemExit("qwen4_exp: --ngram-sidecar FILE is required (the container records the n-gram table it was built for)")
     keep = [s for s in args.keep_bf16.split(",") if s]
     layout = args.layouts.split(",")[0]
     src = {k: v for k, v in w.items()}
@@ -151,6 +168,21 @@ def main(argv=None) -> int:
             if src_hash.get(k) == h and k in oldq:
                 q[k] = oldq[k]
                 reused += 1
+    if cfg.is_qwen4_exp:
+        from ..runtime import ngram as NG
+        if not os.path.exists(args.ngram_sidecar):
+            if not args.input.startswith("random:"):
+                raise SystemExit(f"--ngram-sidecar {args.ngram_sidecar}: no such file")
+            NG.synthetic_sidecar(args.ngram_sidecar, cfg.vocab_size, cfg.ngram_head_dim, cfg.eos_token_id, seed=args.seed)
+        t = NG.NgramTable.open(args.ngram_sidecar, mode="file")
+        hd = t.header
+        t.close()
+        if hd.heads * hd.head_dim != cfg.ple_embed_dim or hd.eos_token_id != cfg.eos_token_id:
+            raise SystemExit("--ngram-sidecar: the table's geometry or end-of-sequence id does not match the model")
+        # recorded, never rehashed at load: name (relative to the container when they share a directory), rows, sha256 of the body
+        same_dir = os.path.dirname(os.path.abspath(args.ngram_sidecar)) == os.path.dirname(os.path.abspath(args.output))
+        extra_meta["ngram_sidecar"] = json.dumps({"path": os.path.basename(args.ngram_sidecar) if same_dir else os.path.abspath(args.ngram_sidecar),
+                                                  "rows": hd.rows, "row_bytes": hd.row_bytes, "sha256": hd.body_sha256.hex()})
     hashes = {k: hashlib.sha256(v.detach().float().contiguous().numpy().tobytes()).hexdigest() for k, v in w.items()}
     extra_meta.update({"source_sha256": json.dumps(hashes), "converter": "r4dxb-convert 0.1", "kb_plan": args.kb_plan})
     save_weight_set(args.output, cfg, q, extra_meta)

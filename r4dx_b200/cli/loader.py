@@ -61,6 +61,8 @@ def load_text_model(args, device: Optional[str] = None):
         cfg = gcfg.shard(args.tp, rank) if args.tp > 1 else gcfg
         weights = shard_weight_set(gcfg, full, args.tp, rank)
         model_id = os.path.splitext(os.path.basename(model_arg))[0]
+    if gcfg.is_qwen4_exp:
+        return _load_qwen4_exp(args, gcfg, weights, model_arg, model_id, device)
     if pp > 1:
         return _load_pipeline(args, gcfg, cfg, weights, full, model_id, device, rank, world, hybrid)
     if ep > 1:
@@ -93,6 +95,38 @@ def load_text_model(args, device: Optional[str] = None):
         group = RankGroup(rank, world, group=ctl, fault=FaultSpec.parse(getattr(args, "tp_fault", "") or ""))
         return TpTextModel(local, group, ctl_group=ctl, comm=comm), tk, tpl
     return local, tk, tpl
+
+
+def _load_qwen4_exp(args, gcfg, weights, model_arg: str, model_id: str, device):
+    """The 4-stream MoE family: one GPU, text only, its n-gram table next to the container (or --ngram-sidecar)."""
+    import json
+    from ..models.q4x import Qwen4ExpModel
+    from ..quant.container import Container
+    from ..runtime import ngram as NG
+    from ..runtime.text_model import LocalTextModel
+    from ..runtime.tokenizer import load_tokenizer
+    bad = [f for f, on in (("--tp", args.tp > 1), ("--pp", getattr(args, "pp", 1) > 1), ("--ep", getattr(args, "ep", 1) > 1),
+                           ("--mtp", getattr(args, "mtp", 0) > 0), ("--dflash", bool(getattr(args, "dflash", None))),
+                           ("--ngram", getattr(args, "ngram", 0) > 0), ("--vision on", getattr(args, "vision", "off") == "on")) if on]
+    if bad:
+        raise SystemExit("qwen4_exp does not support: " + ", ".join(bad))
+    table = None
+    if gcfg.ple_layers:
+        path = getattr(args, "ngram_sidecar", None)
+        if not path:
+            rec = json.loads(Container(model_arg).metadata.get("ngram_sidecar", "{}"))
+            if not rec:
+                raise SystemExit("this container records no n-gram table; pass --ngram-sidecar FILE")
+            path = rec["path"] if os.path.isabs(rec["path"]) else os.path.join(os.path.dirname(os.path.abspath(model_arg)), rec["path"])
+        try:
+            table = NG.NgramTable.open(path, mode=getattr(args, "ngram_placement", "device"), device=device)
+        except (OSError, NG.NgramError) as e:
+            raise SystemExit(f"n-gram table {path}: {e}")
+        if not getattr(args, "ngram_sidecar", None) and rec.get("sha256") and table.header.body_sha256.hex() != rec["sha256"]:
+            raise SystemExit(f"n-gram table {path} is not the one this container was converted with (sha256 in its header differs)")
+    model = Qwen4ExpModel(gcfg, weights, ngram_table=table, max_ctx=args.max_ctx, device=device)
+    tk, tpl = load_tokenizer(args.tokenizer_dir, gcfg.vocab_size)
+    return LocalTextModel(model, model_id=model_id, global_config=gcfg), tk, tpl
 
 
 def _facade(local, rank: int, world: int, args, comm=None):

@@ -59,11 +59,16 @@ class Qwen4ExpModel(HybridModel):
         self.hc_inj, self.hc_rstd = e(R, hc, dtype=f32), e(R, hc, dtype=f32)
         # ---- n-gram layer ----
         self.ngram = None
+        self.host_ngram = False
         self.tok_hist = e(self.max_ctx + 2 * R, dtype=torch.int32)
         self.ple_ring: Dict[int, torch.Tensor] = {i: e(32, C) for i in cfg.ple_layers}
         if cfg.ple_layers:
-            if ngram_table is None or ngram_table.body is None or ngram_table.body.device.type != "cuda":
-                raise ValueError("this model needs the n-gram table in device memory (NgramTable.open(mode='device'))")
+            if ngram_table is None:
+                raise ValueError("this model has an n-gram layer: pass its table (runtime.ngram.NgramTable.open)")
+            # table in device memory: ids and rows by one kernel, graph decode.  Otherwise (pinned host memory, file): ids and
+            # rows on the host for every call, one host-to-device copy, eager decode.
+            self.host_ngram = ngram_table.body is None or ngram_table.body.device.type != "cuda"
+            self._host_tokens: list = []
             hd = ngram_table.header
             if hd.heads != cfg.ngram_heads or hd.heads * hd.head_dim != cfg.ple_embed_dim:
                 raise ValueError("n-gram table geometry does not match the model's ple_embed_dim")
@@ -190,7 +195,7 @@ class Qwen4ExpModel(HybridModel):
         if skip_embed:
             raise NotImplementedError("embedding overrides for the qwen4_exp family (it is text only)")
         K.q4x_embed_repeat(w["text.embed_tokens"], b.ids[:T], self.hx[:T], cfg.hc_count)
-        if self.ngram is not None:
+        if self.ngram is not None and not self.host_ngram:
             K.q4x_ngram_gather(b.ids, b.positions, self.tok_hist, self.ngram.body, self.emb, T, self.ngram_args)
         for i in range(cfg.num_hidden_layers):
             p = f"text.layers.{i}."
@@ -215,12 +220,37 @@ class Qwen4ExpModel(HybridModel):
     def feed(self, ids: torch.Tensor, want_logits: bool = True, accepted: Optional[int] = None) -> None:
         if accepted is not None and accepted != ids.numel():
             raise NotImplementedError("speculative windows (partly accepted rows) for the qwen4_exp family")
+        if self.host_ngram:
+            # the history is keyed by position, so a rewind (checkpoint restore, reset) needs no repair here either
+            toks = [int(t) for t in ids.tolist()]
+            del self._host_tokens[self.pos:]
+            eos = self.cfg.eos_token_id
+            self.ngram.ids.restore(([eos, eos] + self._host_tokens)[-2:])
+            self.emb[:len(toks)].copy_(self.ngram.gather_host(toks), non_blocking=False)
+            self._host_tokens += toks
         super().feed(ids, want_logits)
 
     def prefill(self, ids: torch.Tensor, chunk: Optional[int] = None, hook=None, embed_overrides=None, image_blocks=None) -> int:
         if embed_overrides is not None or image_blocks or hook is not None:
             raise NotImplementedError("the qwen4_exp family is text only and has no drafter hooks")
-        return self.prefill_small(ids)
+        tok = self.prefill_small(ids)
+        last = (ids.numel() - 1) % MAX_ROWS
+        if last:                                   # callers read the prompt's last logits row at index 0, as after a chunked prefill
+            self.buf.logits[0].copy_(self.buf.logits[last])
+            self.buf.next_ids[:1].copy_(self.buf.next_ids[last:last + 1])
+            self.last_row = 0
+        return tok
+
+    def enable_graphs(self, rows=(1,)) -> None:
+        if not self.host_ngram:
+            super().enable_graphs(rows)
+
+    def decode_step_graph(self) -> None:
+        if not self.host_ngram:
+            return super().decode_step_graph()
+        tok = int(self.buf.ids[0].item())          # host placement of the table: the ids are hashed on the host, so the step is eager
+        self.feed(torch.tensor([tok], dtype=torch.int32))
+        self.buf.ids[:1].copy_(self.buf.next_ids[:1])
 
     def forward_chunk(self, T: int, want_logits: bool, skip_embed: bool = False) -> None:
         raise NotImplementedError("no tensor-core chunk path for the qwen4_exp family: prompts take prefill_small")

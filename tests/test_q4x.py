@@ -233,3 +233,25 @@ def test_checkpoint_names_round_trip_through_the_importer(tiny):
             "indexer_kv_heads": 1, "indexer_head_dim": 64, "indexer_budget": 16, "output_gate_type": "sigmoid", "eos_token_id": 7}
     c2 = config_from_hf(json.dumps({"model_type": "qwen4_exp", "text_config": text}))
     assert c2 == cfg
+
+
+def test_converter_writes_a_container_that_records_its_ngram_table(tmp_path):
+    import json
+    from r4dx_b200.cli.convert import main as convert_main
+    from r4dx_b200.quant.container import Container
+    from r4dx_b200.quant.weights import load_weight_set
+    out, side = str(tmp_path / "q4x.r4dxb"), str(tmp_path / "q4x.r4dx-ngram")
+    with pytest.raises(SystemExit, match="ngram-sidecar"):
+        convert_main(["--input", "random:q4x", "--output", out, "--layers", "2", "--kb-plan", "kb3"])
+    with pytest.raises(SystemExit, match="does not support: --rotate, --mtp"):
+        convert_main(["--input", "random:q4x", "--output", out, "--layers", "2", "--ngram-sidecar", side, "--rotate", "q2a", "--mtp"])
+    assert convert_main(["--input", "random:q4x", "--output", out, "--layers", "2", "--kb-plan", "kb3", "--ngram-sidecar", side]) == 0
+    cfg, w = load_weight_set(out)
+    assert cfg.is_qwen4_exp and cfg.num_hidden_layers == 2 and cfg.ple_layers == [1]
+    assert w["text.layers.0.hc.attn.down"].dtype == torch.bfloat16 and "text.layers.1.ple.conv1d" in w and "text.hc_final.up" in w
+    assert type(w["text.layers.0.gdn.in_proj_qkv"]).__name__ == "TrellisWeight"
+    rec = json.loads(Container(out).metadata["ngram_sidecar"])
+    t = NG.NgramTable.open(side, mode="file")
+    assert rec["path"] == "q4x.r4dx-ngram" and rec["rows"] == t.header.rows and rec["sha256"] == t.header.body_sha256.hex()
+    assert t.verify_sha256()
+    t.close()

@@ -285,3 +285,30 @@ def test_tiny_model_graph_replay_and_checkpoint(tiny_pair):
     assert a == b
     with pytest.raises(NotImplementedError):
         m.feed(prompt[:4], accepted=2)
+
+
+def test_container_loads_through_the_cli_loader_and_table_placements_agree(tmp_path):
+    """convert -> load_text_model -> prefill + greedy decode; the table in device memory (graph decode, ids on the device) and
+    read from the file (host ids, eager decode) give the same tokens; flags this family refuses are refused."""
+    from types import SimpleNamespace
+    from r4dx_b200.cli.convert import main as convert_main
+    from r4dx_b200.cli.loader import load_text_model
+    out, side = str(tmp_path / "q4x.r4dxb"), str(tmp_path / "q4x.r4dx-ngram")
+    assert convert_main(["--input", "random:q4x", "--output", out, "--kb-plan", "mix3.3", "--ngram-sidecar", side]) == 0
+    base = dict(model=out, layers=0, tp=1, pp=1, hybrid=False, ep=1, max_ctx=256, mtp=0, ngram=0, dflash=None, tokenizer_dir=None,
+                prefill_chunk=0, vision="off", ngram_sidecar=None)
+    prompt = torch.randint(0, 4096, (37,), generator=torch.Generator().manual_seed(3)).tolist()
+    runs = {}
+    for placement in ("device", "file"):
+        tm, _, _ = load_text_model(SimpleNamespace(ngram_placement=placement, **base), device="cuda:0")
+        tok = tm.prefill(prompt)
+        first_row = tm.last_logits().float().cpu().clone()
+        toks = [tok]
+        for _ in range(10):
+            toks.append(tm.decode_step_greedy(toks[-1]))
+        runs[placement] = (toks, first_row)
+        assert int(first_row.argmax()) == tok                       # the prompt's last logits row sits where callers read it
+    assert runs["device"][0] == runs["file"][0]
+    assert torch.equal(runs["device"][1], runs["file"][1])
+    with pytest.raises(SystemExit, match="does not support: --tp, --mtp"):
+        load_text_model(SimpleNamespace(ngram_placement="device", **{**base, "tp": 2, "mtp": 3}), device="cuda:0")
