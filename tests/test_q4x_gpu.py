@@ -310,5 +310,5 @@ def test_container_loads_through_the_cli_loader_and_table_placements_agree(tmp_p
         assert int(first_row.argmax()) == tok                       # the prompt's last logits row sits where callers read it
     assert runs["device"][0] == runs["file"][0]
     assert torch.equal(runs["device"][1], runs["file"][1])
-    with pytest.raises(SystemExit, match="does not support: --tp, --mtp"):
-        load_text_model(SimpleNamespace(ngram_placement="device", **{**base, "tp": 2, "mtp": 3}), device="cuda:0")
+    with pytest.raises(SystemExit, match="does not support: --mtp, --ngram"):
+        load_text_model(SimpleNamespace(ngram_placement="device", **{**base, "mtp": 3, "ngram": 4}), device="cuda:0")
