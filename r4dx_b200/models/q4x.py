@@ -18,8 +18,9 @@ What differs from the reference's runtime (src/model/qwen4exp_stage.cpp, qwen4ex
   * every launch has position-independent geometry (the selection kernels take the context bound, attention splits are
     sized by the selection budget), so the whole step is captured in one CUDA graph, n-gram layer and sparse attention
     included (the reference launches those two outside its graphs).
-Prompts run through the 8-row weight-streaming path (this family has no tensor-core chunk path here); speculative windows
-are refused, as the reference refuses them for this family.
+Prompts run in chunks of ``chunk_rows`` rows on the tensor cores (trellis products, stream-gate products, router and grouped
+experts; the recurrence stays token by token, which is exact for any gate range); speculative windows are refused, as the
+reference refuses them for this family.
 """
 from __future__ import annotations
 
@@ -230,16 +231,157 @@ class Qwen4ExpModel(HybridModel):
             self._host_tokens += toks
         super().feed(ids, want_logits)
 
+    chunk_rows = int(os.environ.get("R4DXB_Q4X_CHUNK", "1024"))       # rows per prefill chunk (0: 8-row passes only)
+
     def prefill(self, ids: torch.Tensor, chunk: Optional[int] = None, hook=None, embed_overrides=None, image_blocks=None) -> int:
         if embed_overrides is not None or image_blocks or hook is not None:
             raise NotImplementedError("the qwen4_exp family is text only and has no drafter hooks")
-        tok = self.prefill_small(ids)
-        last = (ids.numel() - 1) % MAX_ROWS
-        if last:                                   # callers read the prompt's last logits row at index 0, as after a chunked prefill
+        ids = ids.to(torch.int32)
+        n = ids.numel()
+        step = chunk or self.chunk_rows
+        if self.pos + n > self.max_ctx:
+            raise ValueError("context overflow")
+        if self.host_ngram or step <= 2 * MAX_ROWS or n <= 2 * MAX_ROWS:
+            tok = self.prefill_small(ids)
+            last = (n - 1) % MAX_ROWS
+        else:
+            # chunks on the tensor cores, a tail of up to 8 rows through the small-batch path
+            self.commit_pending()
+            step = min(step, n)
+            self._chunk_buffers(step)
+            self._q4x_chunk_buffers(step)
+            s, last = 0, 0
+            while s < n:
+                e = min(n, s + step)
+                T = e - s
+                if T <= MAX_ROWS:
+                    self.feed(ids[s:e], want_logits=True)
+                    last = T - 1
+                else:
+                    cb = self._cb
+                    cb["ids"][:T].copy_(ids[s:e].to(self.device), non_blocking=True)
+                    cb["positions"][:T].copy_(torch.arange(self.pos, self.pos + T, dtype=torch.int32, device=self.device))
+                    self.forward_chunk(T, want_logits=(e == n))
+                    last = 0
+                s = e
+            K.check_gemm_status(self.device)
+            tok = self._read_token(last)
+        if last:                                   # callers read the prompt's last logits row at index 0
             self.buf.logits[0].copy_(self.buf.logits[last])
             self.buf.next_ids[:1].copy_(self.buf.next_ids[last:last + 1])
             self.last_row = 0
         return tok
+
+    def _q4x_chunk_buffers(self, C: int) -> dict:
+        qb = getattr(self, "_qb", None)
+        if qb is not None and qb["C"] >= C:
+            return qb
+        cfg, dev = self.cfg, self.device
+        H, hc, L = cfg.hidden_size, cfg.hc_count, cfg.hc_lowrank
+        Ch = hc * H
+        e = lambda *s, dtype=BF: torch.empty(*s, dtype=dtype, device=dev)
+        f32 = torch.float32
+        qb = dict(C=C, hx=e(C, Ch), hn=e(C, Ch), dn=e(C * (L + hc), dtype=f32), mid=e(C, L), up=e(C, Ch, dtype=f32), bout=e(C, H))
+        if self.ngram is not None:
+            qb.update(emb=e(C, cfg.ple_embed_dim), kp=e(C, Ch, dtype=f32), val=e(C, H, dtype=f32), gv=e(C, Ch), gvn=e(C, Ch))
+        if cfg.indexer_heads:
+            Hi, Di = cfg.indexer_heads, cfg.indexer_dim
+            qb.update(idx_qk=e(C, (Hi + 1) * Di, dtype=f32), idx_q=e(C, Hi, Di), scores=e(C, self.nb_bound, dtype=f32),
+                      sel_tokens=e(C, self.sel_stride, dtype=torch.int32), sel_count=e(C, dtype=torch.int32),
+                      acc=e(C * cfg.num_attention_heads * self.qsa_splits * cfg.head_dim, dtype=f32),
+                      ml=e(C * cfg.num_attention_heads * self.qsa_splits * 2, dtype=f32))
+        self._qb = qb
+        return qb
+
+    def _gate_chunk(self, p: str, T: int) -> torch.Tensor:
+        """The stream gate for a chunk: the products run on the tensor cores; block input in the chunk's x rows."""
+        cfg, w, cb, qb = self.cfg, self.w, self._cb, self._qb
+        hc, L = cfg.hc_count, cfg.hc_lowrank
+        hn = qb["hn"][:T]
+        K.q4x_grouped_rmsnorm(qb["hx"][:T], w[p + "norm"], hc, cfg.rms_norm_eps, out=hn)
+        dn = qb["dn"][:T * (L + hc)].view(T, L + hc)
+        K.linear_tc(self.hc_w[p], hn, out=dn)
+        K.q4x_hc_mid(dn, qb["mid"][:T], L, hc)
+        K.linear_tc(w[p + "up"], qb["mid"][:T], out=qb["up"][:T])
+        K.q4x_hc_mix(hn, qb["up"][:T], cb["x"][:T], hc)
+        return dn[:, L:]
+
+    def forward_chunk(self, T: int, want_logits: bool, skip_embed: bool = False) -> None:
+        """T (> 8) rows staged in the chunk buffers at positions self.pos ..: trellis products, stream-gate products, router
+        and experts on the tensor cores; the recurrence token by token (exact for any gate range); attention over each row's
+        selected tokens.  Commits the rows."""
+        cfg, w, cb, qb, b = self.cfg, self.w, self._cb, self._qb, self.buf
+        H, hc = cfg.hidden_size, cfg.hc_count
+        Hq, Hkv, D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+        Hv, Hk, Dg = cfg.linear_num_value_heads, cfg.linear_num_key_heads, cfg.linear_key_head_dim
+        x, hx, bout, pos = cb["x"][:T], qb["hx"][:T], qb["bout"][:T], cb["positions"]
+        pos0 = self.pos
+        K.q4x_embed_repeat(w["text.embed_tokens"], cb["ids"][:T], hx, hc)
+        if self.ngram is not None:
+            K.q4x_ngram_gather(cb["ids"], pos, self.tok_hist, self.ngram.body, qb["emb"], T, self.ngram_args)
+        for i in range(cfg.num_hidden_layers):
+            p = f"text.layers.{i}."
+            if i in self.ple_ring:
+                pp = p + "ple."
+                K.linear_tc(w[pp + "key_proj"], qb["emb"][:T], out=qb["kp"][:T])
+                K.linear_tc(w[pp + "value_proj"], qb["emb"][:T], out=qb["val"][:T])
+                K.q4x_ple_gate_value(qb["kp"][:T], hx, qb["val"][:T], w[pp + "norm_key"], w[pp + "norm_query"], qb["gv"][:T], hc,
+                                     cfg.rms_norm_eps)
+                K.q4x_grouped_rmsnorm(qb["gv"][:T], w[pp + "norm_conv"], hc, cfg.rms_norm_eps, out=qb["gvn"][:T])
+                K.q4x_ple_conv(qb["gvn"][:T], qb["gv"][:T], w[pp + "conv1d"], self.ple_ring[i], hx, pos, T, cfg.ple_conv_kernel,
+                               cfg.ple_conv_dilation)
+            inj = self._gate_chunk(p + "hc.attn.", T)
+            if cfg.is_attention_layer(i):
+                pa = p + "attn."
+                qg, kk, vv, q = cb["qg"][:T], cb["k"][:T], cb["v"][:T], cb["q"][:T]
+                self.lin[pa + "qg"].chunk(x, cb["xh"], qg)
+                self.lin[pa + "k"].chunk(x, cb["xh"], kk)
+                self.lin[pa + "v"].chunk(x, cb["xh"], vv)
+                K.attn_precore(qg, kk, vv, w.get(pa + "q_norm"), w.get(pa + "k_norm"), w[pa + "k_descale"], w[pa + "v_descale"],
+                               pos, self.block_table, q, self.kv[i], T, Hq, Hkv, D, cfg.rotary_dim, cfg.rope_theta,
+                               cfg.rms_norm_eps, q_stride=cfg.q_proj_dim // Hq)
+                core = cb["core"][:T * cfg.q_dim].view(T, cfg.q_dim)
+                if cfg.indexer_heads:
+                    Hi, Di, ratio = cfg.indexer_heads, cfg.indexer_dim, cfg.indexer_ratio
+                    K.linear_tc(w[pa + "indexer.qk"], x, out=qb["idx_qk"][:T])
+                    K.q4x_qsa_index(qb["idx_qk"][:T], w[pa + "indexer.q_norm"], w[pa + "indexer.k_norm"], pos, qb["idx_q"],
+                                    self.raw_keys[i], self.block_keys[i], T, Hi, Di, ratio, cfg.rotary_dim, cfg.rope_theta,
+                                    cfg.rms_norm_eps)
+                    K.q4x_qsa_select(qb["idx_q"], self.block_keys[i], pos, qb["scores"], qb["sel_tokens"], qb["sel_count"], T, Hi, Di,
+                                     ratio, self.topk, min(self.nb_bound, (pos0 + T) // ratio + 1))
+                    K.q4x_qsa_attn(q, qg, self.kv[i], self.block_table, pos, qb["sel_tokens"], qb["sel_count"], w[pa + "k_descale"],
+                                   w[pa + "v_descale"], qb["acc"], qb["ml"], core, T, Hq, Hkv, D, self.sel_stride, self.qsa_splits,
+                                   gated=cfg.attn_output_gate)
+                else:
+                    K.attn_prefill(q, qg, self.kv[i], self.block_table, w[pa + "k_descale"], w[pa + "v_descale"], core, T, Hq, Hkv, D,
+                                   pos0, cfg.attn_output_gate)
+                self.lin[pa + "o"].chunk(core, cb["xh"], bout)
+            else:
+                pg = p + "gdn."
+                mixed, z, ab = cb["mixed"][:T * cfg.conv_dim].view(T, cfg.conv_dim), cb["z"][:T], cb["ab"][:T]
+                self.lin[pg + "in_proj_qkv"].chunk(x, cb["xh"], mixed)
+                self.lin[pg + "in_proj_z"].chunk(x, cb["xh"], z)
+                if self.ab_w[i].shape[0] % 4 == 0:
+                    K.linear_tc(self.ab_w[i], x, out=ab)
+                else:
+                    K.bf16_gemv(self.ab_w[i], x, out=ab)
+                core = cb["core"][:T * cfg.value_dim].view(T, cfg.value_dim)
+                K.gdn_prefill_gate(mixed, z, ab, w[pg + "conv1d_weight"], w[pg + "A_log"], w[pg + "dt_bias"], w[pg + "norm_weight"],
+                                   self.ring[i], self.gdn_state[i], cb["gdn"], core, T, Hv, Hk, Dg, pos0, cfg.rms_norm_eps,
+                                   1 if cfg.gdn_gate_act == "sigmoid" else 0)
+                self.lin[pg + "out_proj"].chunk(core, cb["xh"], bout)
+            K.q4x_hc_inject(hx, bout, inj, hc)
+            inj = self._gate_chunk(p + "hc.mlp.", T)
+            bout.zero_()                            # the chunk MoE adds into its output rows: from zero that is the block output
+            self._moe_chunk(i, x, bout, T)
+            K.q4x_hc_inject(hx, bout, inj, hc)
+        if want_logits:
+            self.hx[:1].copy_(hx[T - 1:T])
+            self._gate("text.hc_final.", 1, inject=False)
+            self.lin["lm_head"](b.x[:1], out=b.logits[:1])
+            K.argmax_rows(b.logits[:1], 0, b.next_ids[:1], b.next_vals[:1], b.argmax_scratch)
+        self.pos += T
+        self.pending_rows = 0
 
     def enable_graphs(self, rows=(1,)) -> None:
         if not self.host_ngram:
@@ -251,9 +393,6 @@ class Qwen4ExpModel(HybridModel):
         tok = int(self.buf.ids[0].item())          # host placement of the table: the ids are hashed on the host, so the step is eager
         self.feed(torch.tensor([tok], dtype=torch.int32))
         self.buf.ids[:1].copy_(self.buf.next_ids[:1])
-
-    def forward_chunk(self, T: int, want_logits: bool, skip_embed: bool = False) -> None:
-        raise NotImplementedError("no tensor-core chunk path for the qwen4_exp family: prompts take prefill_small")
 
     def verify_window(self, anchor, drafts):
         raise NotImplementedError("speculative decoding for the qwen4_exp family")

@@ -239,6 +239,11 @@ int r4dxb_trellis_gemv_grouped_pairs(const void* words, const void* suh, const v
                                      const int* offsets, const int* perm, const int* pair_ids, int pairs, int e_begin,
                                      int in_div, int pass, int tmax, int prologue, int experts, int N, int K, int kb, int ksplit,
                                      void* stream);
+/* GDN prefill with the output gate of its norm chosen by the caller (0 silu, 1 sigmoid) */
+int r4dxb_gdn_prefill_gate(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
+                           const float* dt_bias, const void* norm_w, void* ring, float* state, float* q, float* k, float* v,
+                           float* eg, float* beta, float* o, void* out, int T, int H, int Hk, int D, int pos0, float eps,
+                           float* ws, int gate_act, void* stream);
 /* GDN decode step with the output gate of its norm chosen by the caller: gate_act 0 = silu(z), 1 = sigmoid(z). */
 int r4dxb_gdn_decode_gate(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
                           const float* dt_bias, const void* norm_w, void* ring, float* state, float* log_u, float* log_k,

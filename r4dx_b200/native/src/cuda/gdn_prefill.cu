@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(128) GdnScanKernel(const float* __restrict__ q
 // one warp per (token, head)
 __global__ void GdnGatedNormKernel(const float* __restrict__ o, const __nv_bfloat16* __restrict__ z,
                                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out, long long rows,
-                                   int D, float eps) {
+                                   int D, float eps, int gate_act) {
   const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -211,7 +211,7 @@ __global__ void GdnGatedNormKernel(const float* __restrict__ o, const __nv_bfloa
   for (int i = 0; i < per; ++i) {
     const int d = lane * per + i;
     const float zv = __bfloat162float(z[item * D + d]);
-    out[item * D + d] = __float2bfloat16(v[i] * r * __bfloat162float(w[d]) * Silu(zv));
+    out[item * D + d] = __float2bfloat16(v[i] * r * __bfloat162float(w[d]) * (gate_act ? Sigmoid(zv) : Silu(zv)));
   }
 }
 
@@ -229,11 +229,25 @@ extern "C" {
 /* scratch (fp32): q [T,Hk,D], k [T,Hk,D], v [T,H,D], eg [T,H], beta [T,H], o [T,H,D];
  * ws: optional workspace of r4dxb_gdn_chunk_ws_floats(T, H) floats - with it, D = 128 and T >= 128 the
  * recurrence runs in its chunked tensor-core form, otherwise token by token */
+int r4dxb_gdn_prefill_gate(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
+                           const float* dt_bias, const void* norm_w, void* ring, float* state, float* q, float* k, float* v,
+                           float* eg, float* beta, float* o, void* out, int T, int H, int Hk, int D, int pos0, float eps,
+                           float* ws, int gate_act, void* stream);
+
 int r4dxb_gdn_prefill(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
                       const float* dt_bias, const void* norm_w, void* ring, float* state, float* q, float* k, float* v,
                       float* eg, float* beta, float* o, void* out, int T, int H, int Hk, int D, int pos0, float eps,
                       float* ws, void* stream) {
-  if (T < 1 || H % Hk || (D != 128 && D != 64)) return R4DXB_BAD_ARG;
+  return r4dxb_gdn_prefill_gate(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, q, k, v, eg, beta, o, out, T, H, Hk, D,
+                                pos0, eps, ws, 0, stream);
+}
+
+/* the same prefill with the norm's output gate chosen by the caller: 0 silu(z), 1 sigmoid(z) */
+int r4dxb_gdn_prefill_gate(const void* mixed, const void* z, const float* ab, const void* conv_w, const float* A_log,
+                           const float* dt_bias, const void* norm_w, void* ring, float* state, float* q, float* k, float* v,
+                           float* eg, float* beta, float* o, void* out, int T, int H, int Hk, int D, int pos0, float eps,
+                           float* ws, int gate_act, void* stream) {
+  if (T < 1 || H % Hk || (D != 128 && D != 64) || (gate_act != 0 && gate_act != 1)) return R4DXB_BAD_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   PrepArgs a;
   a.mixed = static_cast<const __nv_bfloat16*>(mixed);
@@ -266,7 +280,7 @@ int r4dxb_gdn_prefill(const void* mixed, const void* z, const float* ab, const v
   const long long rows = static_cast<long long>(T) * H;
   GdnGatedNormKernel<<<static_cast<unsigned>((rows + 7) / 8), 256, 0, s>>>(
       o, static_cast<const __nv_bfloat16*>(z), static_cast<const __nv_bfloat16*>(norm_w),
-      static_cast<__nv_bfloat16*>(out), rows, D, eps);
+      static_cast<__nv_bfloat16*>(out), rows, D, eps, gate_act);
   return FinishLaunch();
 }
 

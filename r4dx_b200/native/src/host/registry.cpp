@@ -62,10 +62,13 @@ const R4dxbConstraint cq1[] = {{"heads", R4DXB_C_LE, 16, nullptr}, {"heads", R4D
 const R4dxbConstraint cq2[] = {{"kernel", R4DXB_C_LE, 8, nullptr}};
 const R4dxbConstraint cq3[] = {{"Di", R4DXB_C_DIV, 32, nullptr}, {"Di", R4DXB_C_LE, 128, nullptr}, {"Hi", R4DXB_C_LE, 8, nullptr}};
 const R4dxbConstraint cq4[] = {{"D", R4DXB_C_IN, 0, "64 128 256"}, {"gqa", R4DXB_C_LE, 16, nullptr}};
+const R4dxbConstraint cq7[] = {{"D", R4DXB_C_IN, 0, "64 128"}, {"gate_act", R4DXB_C_IN, 0, "0 1"}};
 const R4dxbConstraint cq6[] = {{"T", R4DXB_C_LE, 8, nullptr}, {"hc", R4DXB_C_LE, 8, nullptr}};
 const R4dxbConstraint cq5[] = {{"T", R4DXB_C_LE, 8, nullptr}, {"D", R4DXB_C_IN, 0, "64 128"}, {"gate_act", R4DXB_C_IN, 0, "0 1"}};
 
 const R4dxbKernelInfo kKernels[] = {
+    {"gdn_prefill_gate", "gdn", "gdn_prefill", "GDN prefill (conv, gates, scan, gated norm) with the norm's output gate chosen by the caller",
+     "D 64 / 128", "bf16 rows, fp32 state", "simt", cq7, 2},
     {"gdn_decode_gate", "gdn", "gdn_decode_rows_le_8", "the GDN step with the norm's output gate chosen by the caller (silu or sigmoid)",
      "as gdn_decode_ab without the in-kernel a / b projections", "bf16 rows, fp32 state", "simt", cq5, 3},
     {"q4x_grouped_rmsnorm", "elementwise", "grouped_rmsnorm", "zero-centred RMSNorm over consecutive channel groups of a row (stream gate, n-gram layer)",

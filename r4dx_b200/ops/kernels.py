@@ -535,6 +535,22 @@ register_cuda_sig("r4dxb_gdn_chunk_ws_floats", ctypes.c_longlong, [_I, _I])
 register_cuda_sig("r4dxb_attn_prefill", _I, [_P] * 7 + [_I, _I, _I, _I, _I, _I, _P])
 
 
+register_cuda_sig("r4dxb_gdn_prefill_gate", _I, [_P] * 16 + [_I, _I, _I, _I, _I, _F, _P, _I, _P])
+
+
+def gdn_prefill_gate(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, scratch: dict, out, T: int, H: int, Hk: int,
+                     D: int, pos0: int, eps: float, gate_act: int, exact_scan: bool = True):
+    """``gdn_prefill`` with the norm's output gate chosen by the caller (1 = sigmoid).  ``exact_scan`` keeps the recurrence
+    token by token: the chunked form factors the pair decay around the chunk's midpoint, which is only safe while a chunk's
+    summed log-gates stay moderate, and this family's gates (A = exp(A_log) up to ~158 per step) exceed that by far
+    (reference: docs/qwen4exp.md "The GDN chunk-scan defect")."""
+    _check(_lib().r4dxb_gdn_prefill_gate(_p(mixed), _p(z), _p(ab), _p(conv_w), _p(A_log), _p(dt_bias), _p(norm_w), _p(ring),
+                                         _p(state), _p(scratch["q"]), _p(scratch["k"]), _p(scratch["v"]), _p(scratch["eg"]),
+                                         _p(scratch["beta"]), _p(scratch["o"]), _p(out), T, H, Hk, D, pos0, eps,
+                                         None if exact_scan else _p(scratch.get("ws")), gate_act, _stream()), "gdn_prefill_gate")
+    return out
+
+
 def gdn_prefill(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, scratch: dict, out, T: int, H: int, Hk: int,
                 D: int, pos0: int, eps: float = 1e-6):
     """scratch: dict with fp32 tensors q, k [T,Hk,D]; v, o [T,H,D]; eg, beta [T,H]; optional "ws" (see
