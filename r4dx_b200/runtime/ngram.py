@@ -331,3 +331,93 @@ class NgramTable:
         """Host ids + host rows: [n, heads * head_dim] bf16 on the host (``pinned`` and ``file`` placements, tools)."""
         ids = self.ids.generate(tokens)
         return self.rows(ids).reshape(len(tokens), self.header.heads * self.header.head_dim)
+
+
+# ---- the table file from a checkpoint's own shards ---------------------------------------------------------------------
+def repack_from_checkpoint(model_dir: str, out: str, log=None) -> NgramHeader:
+    """Streams the n-gram table of a qwen4_exp checkpoint directory into one table file.
+
+    The checkpoint stores the table as ``split_ngram_parts`` bf16 tensors
+    ``model.language_model.layers.{L}.ple.ple_embedding.ngram_embedding.shard_{i}.weight`` ([rows_i, head_dim]) spread over its
+    safetensors files and concatenated in shard order, next to three int64 buffers with the hash parameters
+    (``layer_multipliers``, ``ngram_heads_vocab_sizes``, ``ngram_heads_offsets``); L is the single entry of ``ple_layer_ids``
+    minus one.  One shard is in memory at a time.
+    (reference: tools/reference/qwen4exp/ngram_sidecar.py:1-40, 126-205 describes the same source layout.)"""
+    import json
+    from safetensors import safe_open
+    cfg = json.load(open(os.path.join(model_dir, "config.json")))
+    tc = cfg.get("text_config", cfg)
+    ple = tc.get("ple_layer_ids") or []
+    if len(ple) != 1:
+        raise NgramError(f"exactly one n-gram layer is supported, config has ple_layer_ids={ple}")
+    parts = int(tc.get("split_ngram_parts", 512))
+    prefix = f"model.language_model.layers.{int(ple[0]) - 1}.ple.ple_embedding."
+    index = json.load(open(os.path.join(model_dir, "model.safetensors.index.json")))["weight_map"]
+    want = [f"{prefix}ngram_embedding.shard_{i}.weight" for i in range(parts)]
+    have = {k for k in index if k.startswith(prefix + "ngram_embedding.shard_")}
+    if have != set(want):
+        raise NgramError(f"the index lists {len(have)} n-gram shard tensors, expected shard_0..shard_{parts - 1}")
+
+    def tensor(name: str) -> torch.Tensor:
+        if name not in index:
+            raise NgramError(f"{name} is not in model.safetensors.index.json")
+        with safe_open(os.path.join(model_dir, index[name]), "pt") as sf:
+            return sf.get_tensor(name)
+
+    mult = [int(v) for v in tensor(prefix + "layer_multipliers").reshape(-1).tolist()]
+    primes = [int(v) for v in tensor(prefix + "ngram_heads_vocab_sizes").reshape(-1).tolist()]
+    offs = [int(v) for v in tensor(prefix + "ngram_heads_offsets").reshape(-1).tolist()]
+    if len(mult) != NGRAM_SIZE or len(primes) != 16 or len(offs) != 16:
+        raise NgramError("the checkpoint's hash buffers are not 3 multipliers, 16 vocabulary sizes and 16 offsets")
+    first = tensor(want[0])
+    if first.dtype != torch.bfloat16 or first.dim() != 2:
+        raise NgramError(f"{want[0]}: {first.dtype} {tuple(first.shape)}, expected bf16 [rows, head_dim]")
+    head_dim = first.shape[1]
+    eos = int(tc.get("eos_token_id", cfg.get("eos_token_id", 248044)) or 248044)
+    rows = 0
+    shapes = []
+    for name in want:                                   # a first pass over the headers only: the row count goes into the header
+        with safe_open(os.path.join(model_dir, index[name]), "pt") as sf:
+            shp = sf.get_slice(name).get_shape()
+        if len(shp) != 2 or shp[1] != head_dim:
+            raise NgramError(f"{name}: shape {shp}, expected [rows, {head_dim}]")
+        shapes.append(shp[0])
+        rows += shp[0]
+    padded = max(o + p for o, p in zip(offs, primes))
+    if rows < padded:
+        raise NgramError(f"the shards hold {rows} rows, the head offsets reach {padded}")
+    header = NgramHeader(rows=rows, head_dim=head_dim, eos_token_id=eos, seed=int(tc.get("ngram_seed", 0)), multipliers=mult,
+                         head_offsets=offs, head_primes=primes, padded_rows=rows)
+
+    def blocks():
+        for i, name in enumerate(want):
+            t = first if i == 0 else tensor(name)
+            if log is not None:
+                log(f"shard {i + 1}/{parts}: {t.shape[0]} rows")
+            yield t
+    return write_sidecar(out, header, blocks())
+
+
+def main(argv=None) -> int:
+    import argparse
+    ap = argparse.ArgumentParser("r4dx_b200.runtime.ngram", description="n-gram table file: repack from a checkpoint, verify")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    r = sub.add_parser("repack", help="checkpoint directory -> table file")
+    r.add_argument("--model-dir", required=True)
+    r.add_argument("--out", required=True)
+    v = sub.add_parser("verify", help="check the header, the size and the body's sha256")
+    v.add_argument("--sidecar", required=True)
+    a = ap.parse_args(argv)
+    if a.cmd == "repack":
+        h = repack_from_checkpoint(a.model_dir, a.out, log=print)
+        print(f"wrote {a.out}: {h.rows} rows x {h.head_dim}, sha256 {h.body_sha256.hex()}")
+        return 0
+    t = NgramTable.open(a.sidecar, mode="file")
+    ok = t.verify_sha256()
+    print(f"{a.sidecar}: {t.header.rows} rows x {t.header.head_dim}, body sha256 {'matches' if ok else 'DOES NOT match'} the header")
+    t.close()
+    return 0 if ok else 1
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -255,3 +255,38 @@ def test_converter_writes_a_container_that_records_its_ngram_table(tmp_path):
     assert rec["path"] == "q4x.r4dx-ngram" and rec["rows"] == t.header.rows and rec["sha256"] == t.header.body_sha256.hex()
     assert t.verify_sha256()
     t.close()
+
+
+def test_table_file_from_a_checkpoints_own_shards(tmp_path, table):
+    """A checkpoint directory with the table in four shards over two files + the hash buffers -> the same table file."""
+    import json
+    from safetensors.torch import save_file
+    h = table.header
+    body = table.rows(np.arange(h.rows, dtype=np.int64))
+    cuts = [0, 1000, 5000, 9000, h.rows]
+    pre = "model.language_model.layers.1.ple.ple_embedding."
+    f1 = {pre + f"ngram_embedding.shard_{i}.weight": body[cuts[i]:cuts[i + 1]].contiguous() for i in (0, 2)}
+    f2 = {pre + f"ngram_embedding.shard_{i}.weight": body[cuts[i]:cuts[i + 1]].contiguous() for i in (1, 3)}
+    f2[pre + "layer_multipliers"] = torch.tensor(h.multipliers, dtype=torch.int64)
+    f2[pre + "ngram_heads_vocab_sizes"] = torch.tensor(h.head_primes, dtype=torch.int64)
+    f2[pre + "ngram_heads_offsets"] = torch.tensor(h.head_offsets, dtype=torch.int64)
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    save_file(f1, str(d / "model-00001.safetensors"))
+    save_file(f2, str(d / "embedding-model-00001.safetensors"))
+    wm = {k: "model-00001.safetensors" for k in f1}
+    wm.update({k: "embedding-model-00001.safetensors" for k in f2})
+    (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
+    (d / "config.json").write_text(json.dumps({"text_config": {"ple_layer_ids": [2], "split_ngram_parts": 4, "eos_token_id": h.eos_token_id}}))
+    out = str(tmp_path / "repacked.r4dx-ngram")
+    assert NG.main(["repack", "--model-dir", str(d), "--out", out]) == 0
+    t = NG.NgramTable.open(out, mode="file")
+    assert t.header.rows == h.rows and t.header.head_primes == h.head_primes and t.header.multipliers == h.multipliers
+    assert t.header.body_sha256 == h.body_sha256 and t.verify_sha256()
+    toks = [5, 6, 7, h.eos_token_id, 8]
+    assert torch.equal(t.gather_host(toks), NG.NgramTable.open(table.path, mode="file").gather_host(toks))
+    t.close()
+    assert NG.main(["verify", "--sidecar", out]) == 0
+    (d / "config.json").write_text(json.dumps({"text_config": {"ple_layer_ids": [2], "split_ngram_parts": 5}}))
+    with pytest.raises(NG.NgramError, match="expected shard_0..shard_4"):
+        NG.repack_from_checkpoint(str(d), out)
