@@ -28,7 +28,7 @@ def add_model_flags(ap: argparse.ArgumentParser) -> None:
     g.add_argument("--ngram-placement", default="device", choices=["device", "pinned", "file"],
                    help="qwen4_exp: where the n-gram table lives; device (95 GiB for the full table, no host work per token, "
                         "CUDA-graph decode), pinned host memory, or positioned reads from the file (both: host ids, eager decode)")
-    g.add_argument("--dialect", default="auto", choices=["auto", "qwen", "gemma", "lfm2", "llama"],
+    g.add_argument("--dialect", default="auto", choices=["auto", "qwen", "gemma", "lfm2", "llama", "qwen4_exp"],
                    help="reasoning markers and tool-call syntax; auto picks by model id and architecture")
     g.add_argument("--audio", default="off", choices=["off", "on"],
                    help="accept input_audio parts (the container must hold the audio projection; Gemma-style family)")

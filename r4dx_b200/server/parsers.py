@@ -441,13 +441,15 @@ class ModelDialect:
 
     TABLE = {
         # name: (reasoning open, reasoning close, architectures it is expected with)
-        "qwen": ("<think>", "</think>", ("qwen_hybrid", "qwen_hybrid_moe")),
+        "qwen": ("<think>", "</think>", ("qwen_hybrid", "qwen_hybrid_moe", "qwen4_exp")),
         "gemma": ("<|channel>thought\n", "<channel|>", ("gemma",)),
         "lfm2": ("<think>", "</think>", ("lfm2_moe",)),
         "llama": ("<think>", "</think>", ("llama",)),
     }
 
     def __init__(self, name: str):
+        if name == "qwen4_exp":
+            name = "qwen"            # the 4-stream MoE family shares the hybrid family's template, markers and tool-call syntax
         if name not in self.TABLE:
             raise ValueError(f"unknown dialect {name!r}; one of {sorted(self.TABLE)}")
         self.name = name
