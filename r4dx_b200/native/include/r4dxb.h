@@ -233,6 +233,10 @@ int r4dxb_trellis_gemv_allreduce(const void* words, const void* suh, const void*
                                  void* const* recv, void* block_seq, int* status, int world, int rank, int spin_limit,
                                  void* stream);
 
+/* router (mode 0: softmax, 1: sigmoid + selection bias) and routing plan of T <= 8 rows in one launch; the same ids, weights,
+ * offsets and perm as r4dxb_moe_router / r4dxb_moe_router_sigmoid followed by r4dxb_moe_plan */
+int r4dxb_moe_route_plan(const float* logits, const float* bias, int T, int E, int k, int renorm, int mode, float scale, int* ids,
+                         float* weights, int e_begin, int e_count, int* offsets, int* perm, void* stream);
 /* grouped expert product over a compact grid: blockIdx.z runs over the call's `pairs` routed (row, slot) pairs (pair_ids =
  * their global expert ids) instead of every local expert; results equal r4dxb_trellis_gemv_grouped */
 int r4dxb_trellis_gemv_grouped_pairs(const void* words, const void* suh, const void* svh, const void* x, void* y,

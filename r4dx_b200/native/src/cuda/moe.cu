@@ -21,32 +21,37 @@ constexpr int kMaxK = 16;
 // src/kernels/include/r4dx/kernels/lfm2_kernels.h:38-50): s[e] = sigmoid(logit[e]); the SELECTION ranks s[e] + bias[e]
 // (ties to the lower id), the weights are the unbiased s of the selected experts, divided by (their sum + 1e-6) when
 // renorm is set, then multiplied by `scale`.
-__global__ void MoeRouterKernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int k,
-                                int renorm, int mode, float scale, int* __restrict__ ids, float* __restrict__ weights) {
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (t >= T) return;
-  const float* row = logits + static_cast<size_t>(t) * E;
-  float mx = -INFINITY;
-  float z = 0.f;
+// One warp routes one row.  The row's selection values live in registers (E <= 1024: 32 per lane), so the k arg-max rounds
+// touch no memory; a lane remembers its taken entries in a bit mask.
+__device__ __forceinline__ void RouteRow(const float* __restrict__ row, const float* __restrict__ bias, int E, int k, int renorm,
+                                         int mode, float scale, int lane, int* __restrict__ ids, float* __restrict__ weights) {
+  float v[32];
+  float mx = -INFINITY, z = 0.f;
+#pragma unroll
+  for (int s = 0; s < 32; ++s) {
+    const int e = lane + 32 * s;
+    float x = -INFINITY;
+    if (e < E) x = mode == 0 ? row[e] : 1.0f / (1.0f + expf(-row[e])) + (bias ? bias[e] : 0.f);
+    v[s] = x;
+    mx = fmaxf(mx, x);
+  }
   if (mode == 0) {
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, row[e]);
     mx = WarpMax(mx);
-    for (int e = lane; e < E; e += 32) z += __expf(row[e] - mx);
+#pragma unroll
+    for (int s = 0; s < 32; ++s) z += (lane + 32 * s < E) ? __expf(v[s] - mx) : 0.f;
     z = WarpSum(z);
   }
-  // k rounds of arg-max over what is left; a lane keeps a bitmask of its taken entries (E <= 1024 -> 32 per lane)
-  uint32_t taken = 0;
   float wsum = 0.f;
-  float wv[kMaxK];
-  int wi[kMaxK];
+  uint32_t taken = 0;              // bit s: this lane's entry lane + 32 s is already picked
+  float my_p = 0.f;                // lane j keeps the j-th pick (k <= 16 <= 32)
+  int my_i = 0;
   for (int j = 0; j < k; ++j) {
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int e = lane, s = 0; e < E; e += 32, ++s) {
-      if (taken & (1u << s)) continue;
-      const float v = mode == 0 ? row[e] : 1.0f / (1.0f + expf(-row[e])) + (bias ? bias[e] : 0.f);
-      if (v > bv || (v == bv && e < bi)) { bv = v; bi = e; }
+#pragma unroll
+    for (int s = 0; s < 32; ++s) {
+      const int e = lane + 32 * s;
+      if (e < E && !((taken >> s) & 1u) && (v[s] > bv || (v[s] == bv && e < bi))) { bv = v[s]; bi = e; }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -56,15 +61,54 @@ __global__ void MoeRouterKernel(const float* __restrict__ logits, const float* _
     }
     if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
     const float p = mode == 0 ? __expf(bv - mx) / z : 1.0f / (1.0f + expf(-row[bi]));
-    wv[j] = p;
-    wi[j] = bi;
+    if (lane == j) { my_p = p; my_i = bi; }
     wsum += p;
   }
-  if (lane == 0) {
-    for (int j = 0; j < k; ++j) {
-      const float w = mode == 0 ? (renorm ? wv[j] / wsum : wv[j]) : (renorm ? wv[j] / (wsum + 1e-6f) : wv[j]) * scale;
-      ids[static_cast<size_t>(t) * k + j] = wi[j];
-      weights[static_cast<size_t>(t) * k + j] = __bfloat162float(__float2bfloat16(w));
+  if (lane < k) {
+    const float w = mode == 0 ? (renorm ? my_p / wsum : my_p) : (renorm ? my_p / (wsum + 1e-6f) : my_p) * scale;
+    ids[lane] = my_i;
+    weights[lane] = __bfloat162float(__float2bfloat16(w));
+  }
+}
+
+__global__ void MoeRouterKernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int k,
+                                int renorm, int mode, float scale, int* __restrict__ ids, float* __restrict__ weights) {
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  RouteRow(logits + static_cast<size_t>(t) * E, bias, E, k, renorm, mode, scale, threadIdx.x & 31, ids + static_cast<size_t>(t) * k,
+           weights + static_cast<size_t>(t) * k);
+}
+
+// Up to 8 rows (a decode step or a verify window): one CTA routes every row (a warp each) and then builds the plan of the
+// T * k pairs itself, so routing is one launch instead of two.  Same results as MoeRouterKernel + MoePlanKernel.
+__global__ void __launch_bounds__(256)
+MoeRoutePlanKernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int k, int renorm, int mode,
+                   float scale, int* __restrict__ ids, float* __restrict__ weights, int e_begin, int e_count,
+                   int* __restrict__ offsets, int* __restrict__ perm) {
+  extern __shared__ int cnt[];     // [e_count + 1]
+  __shared__ int s_ids[8 * kMaxK];
+  const int warp = threadIdx.x >> 5;
+  for (int e = threadIdx.x; e <= e_count; e += blockDim.x) cnt[e] = 0;
+  if (warp < T)
+    RouteRow(logits + static_cast<size_t>(warp) * E, bias, E, k, renorm, mode, scale, threadIdx.x & 31, ids + warp * k, weights + warp * k);
+  __syncthreads();                 // the ids written above are visible to the whole CTA
+  const int npairs = T * k;
+  if (threadIdx.x < npairs) {
+    const int e = ids[threadIdx.x] - e_begin;
+    s_ids[threadIdx.x] = e;
+    if (e >= 0 && e < e_count) atomicAdd(&cnt[e + 1], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int e = 0; e < e_count; ++e) cnt[e + 1] += cnt[e];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= e_count; e += blockDim.x) offsets[e] = cnt[e];
+  __syncthreads();
+  if (threadIdx.x == 0) {          // stable placement: pairs in ascending index (at most 128 pairs)
+    for (int p = 0; p < npairs; ++p) {
+      const int e = s_ids[p];
+      if (e >= 0 && e < e_count) perm[cnt[e]++] = p;
     }
   }
 }
@@ -230,6 +274,16 @@ int r4dxb_moe_router_sigmoid(const float* logits, const float* bias, int T, int 
   if (T < 1 || k < 1 || k > kMaxK || E > 1024 || E < k) return R4DXB_BAD_ARG;
   MoeRouterKernel<<<(T + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(logits, bias, T, E, k, renorm, 1, scale, ids,
                                                                               weights);
+  return FinishLaunch();
+}
+
+/* Router (mode 0 softmax, 1 sigmoid + bias) and routing plan of up to 8 rows in one launch */
+int r4dxb_moe_route_plan(const float* logits, const float* bias, int T, int E, int k, int renorm, int mode, float scale, int* ids,
+                         float* weights, int e_begin, int e_count, int* offsets, int* perm, void* stream) {
+  if (T < 1 || T > 8 || k < 1 || k > kMaxK || E > 1024 || E < k || e_count < 1 || e_count > 8192 || (mode != 0 && mode != 1))
+    return R4DXB_BAD_ARG;
+  MoeRoutePlanKernel<<<1, 256, (e_count + 1) * sizeof(int), static_cast<cudaStream_t>(stream)>>>(
+      logits, bias, T, E, k, renorm, mode, scale, ids, weights, e_begin, e_count, offsets, perm);
   return FinishLaunch();
 }
 

@@ -62,6 +62,7 @@ const R4dxbConstraint cq1[] = {{"heads", R4DXB_C_LE, 16, nullptr}, {"heads", R4D
 const R4dxbConstraint cq2[] = {{"kernel", R4DXB_C_LE, 8, nullptr}};
 const R4dxbConstraint cq3[] = {{"Di", R4DXB_C_DIV, 32, nullptr}, {"Di", R4DXB_C_LE, 128, nullptr}, {"Hi", R4DXB_C_LE, 8, nullptr}};
 const R4dxbConstraint cq4[] = {{"D", R4DXB_C_IN, 0, "64 128 256"}, {"gqa", R4DXB_C_LE, 16, nullptr}};
+const R4dxbConstraint cq8[] = {{"T", R4DXB_C_LE, 8, nullptr}, {"k", R4DXB_C_LE, 16, nullptr}, {"E", R4DXB_C_LE, 1024, nullptr}};
 const R4dxbConstraint cq7[] = {{"D", R4DXB_C_IN, 0, "64 128"}, {"gate_act", R4DXB_C_IN, 0, "0 1"}};
 const R4dxbConstraint cq6[] = {{"T", R4DXB_C_LE, 8, nullptr}, {"hc", R4DXB_C_LE, 8, nullptr}};
 const R4dxbConstraint cq5[] = {{"T", R4DXB_C_LE, 8, nullptr}, {"D", R4DXB_C_IN, 0, "64 128"}, {"gate_act", R4DXB_C_IN, 0, "0 1"}};
@@ -100,6 +101,8 @@ const R4dxbKernelInfo kKernels[] = {
      "world 2..8; hidden up to the symmetric buffer", "bf16 x, packed trellis words, bf16 y, fp32 pairs over NVLink", "simt+peer-stores", c3, 5},
     {"trellis_gemv_grouped", "gemm", "moe_experts_rows_le_16", "every local expert times its planned rows (8 rows per pass), SwiGLU prologue for the down projection",
      "experts <= 65535", "bf16 x, stacked trellis words", "simt+bulk-copy", c4, 4},
+    {"moe_route_plan", "moe", "moe_route_rows_le_8", "router (softmax or sigmoid + bias) and routing plan of up to 8 rows in one launch",
+     "T <= 8, k <= 16, E <= 1024", "fp32 logits, int32 ids / plan, fp32 weights", "simt", cq8, 3},
     {"trellis_gemv_grouped_pairs", "gemm", "moe_experts_rows_le_16", "the grouped expert product over a compact grid: only experts named by the call's routed pairs get CTAs",
      "pairs <= 65535", "bf16 x, stacked trellis words", "simt+bulk-copy", c4, 4},
     {"trellis_gemv_grouped_ep", "gemm+collective", "moe_experts_expert_parallel", "grouped experts over rows that arrive from peers; results pushed back to the owning rank",

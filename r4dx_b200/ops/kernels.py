@@ -667,6 +667,18 @@ def short_conv(bcx: torch.Tensor, w: torch.Tensor, ring: torch.Tensor, positions
     return out
 
 
+register_cuda_sig("r4dxb_moe_route_plan", _I, [_P, _P, _I, _I, _I, _I, _I, _F, _P, _P, _I, _I, _P, _P, _P])
+
+
+def moe_route_plan(logits: torch.Tensor, bias: Optional[torch.Tensor], k: int, renorm: bool, sigmoid: bool, scale: float,
+                   ids: torch.Tensor, weights: torch.Tensor, e_begin: int, e_count: int, offsets: torch.Tensor, perm: torch.Tensor):
+    """Router + routing plan of T <= 8 rows in one launch (the results of ``moe_router`` / ``moe_router_sigmoid`` + ``moe_plan``)."""
+    _req(logits, torch.float32, "logits")
+    T, E = logits.shape
+    _check(_lib().r4dxb_moe_route_plan(_p(logits), _p(bias), T, E, k, 1 if renorm else 0, 1 if sigmoid else 0, scale, _p(ids),
+                                       _p(weights), e_begin, e_count, _p(offsets), _p(perm), _stream()), "moe_route_plan")
+
+
 def moe_plan(ids: torch.Tensor, npairs: int, E: int, e_begin: int, e_count: int, offsets: torch.Tensor, perm: torch.Tensor):
     _check(_lib().r4dxb_moe_plan(_p(ids), npairs, E, e_begin, e_count, _p(offsets), _p(perm), _stream()), "moe_plan")
     return offsets, perm

@@ -570,6 +570,29 @@ def test_moe_plan_many_pairs(K, npairs, E, e_begin, e_count):
     assert off.cpu().tolist() == [0] + torch.cumsum(counts, 0).tolist()
 
 
+@pytest.mark.parametrize("T,E,k,sigmoid,e_begin,e_count", [(1, 512, 10, False, 0, 512), (8, 64, 4, True, 16, 32), (3, 1000, 16, False, 0, 1000),
+                                                             (5, 16, 4, False, 0, 16)])
+def test_route_and_plan_in_one_launch_equal_the_two_kernels(K, T, E, k, sigmoid, e_begin, e_count):
+    g = torch.Generator().manual_seed(T * 1000 + E)
+    logits = (torch.randn(T, E, generator=g) * 3).cuda()
+    logits[0, 3] = logits[0, 7] = logits[0].max() + 1.0          # a tie at the top: the lower id first
+    bias = (torch.randn(E, generator=g) * 0.3).cuda() if sigmoid else None
+    mk = lambda *s, dt=torch.int32: torch.full(s, -7, dtype=dt, device="cuda")
+    ids_a, w_a, off_a, perm_a = mk(T, k), mk(T, k, dt=torch.float32), mk(e_count + 1), mk(T * k)
+    ids_b, w_b, off_b, perm_b = mk(T, k), mk(T, k, dt=torch.float32), mk(e_count + 1), mk(T * k)
+    if sigmoid:
+        K.moe_router_sigmoid(logits, bias, k, True, 1.5, ids_a, w_a)
+    else:
+        K.moe_router(logits, k, True, ids_a, w_a)
+    K.moe_plan(ids_a, T * k, E, e_begin, e_count, off_a, perm_a)
+    K.moe_route_plan(logits, bias, k, True, sigmoid, 1.5 if sigmoid else 1.0, ids_b, w_b, e_begin, e_count, off_b, perm_b)
+    assert torch.equal(ids_a, ids_b) and torch.equal(w_a, w_b) and torch.equal(off_a, off_b)
+    n = int(off_a[-1])
+    assert torch.equal(perm_a[:n], perm_b[:n])
+    if not sigmoid:
+        assert ids_a[0, 0].item() == 3 and ids_a[0, 1].item() == 7
+
+
 def test_grouped_expert_gemv(K):
     from r4dx_b200.models.moe import ExpertStack
     from r4dx_b200.quant import trellis
