@@ -19,7 +19,7 @@ What differs from the reference's runtime (src/model/qwen4exp_stage.cpp, qwen4ex
     sized by the selection budget), so the whole step is captured in one CUDA graph, n-gram layer and sparse attention
     included (the reference launches those two outside its graphs).
 Prompts run in chunks of ``chunk_rows`` rows on the tensor cores (trellis products, stream-gate products, router and grouped
-experts; the recurrence stays token by token, which is exact for any gate range); speculative windows are refused, as the
+experts; the recurrence stays token by token unless ``chunked_scan`` is set); speculative windows are refused, as the
 reference refuses them for this family.
 """
 from __future__ import annotations
@@ -232,6 +232,8 @@ class Qwen4ExpModel(HybridModel):
         super().feed(ids, want_logits)
 
     chunk_rows = int(os.environ.get("R4DXB_Q4X_CHUNK", "1024"))       # rows per prefill chunk (0: 8-row passes only)
+    # the 64-token chunked recurrence instead of the token-by-token one (off: not yet run on a GPU with this family's gate range)
+    chunked_scan = os.environ.get("R4DXB_Q4X_CHUNKED_SCAN", "0") == "1"
 
     def prefill(self, ids: torch.Tensor, chunk: Optional[int] = None, hook=None, embed_overrides=None, image_blocks=None) -> int:
         if embed_overrides is not None or image_blocks or hook is not None:
@@ -308,7 +310,7 @@ class Qwen4ExpModel(HybridModel):
 
     def forward_chunk(self, T: int, want_logits: bool, skip_embed: bool = False) -> None:
         """T (> 8) rows staged in the chunk buffers at positions self.pos ..: trellis products, stream-gate products, router
-        and experts on the tensor cores; the recurrence token by token (exact for any gate range); attention over each row's
+        and experts on the tensor cores; the recurrence token by token (or chunked, see ``chunked_scan``); attention over each row's
         selected tokens.  Commits the rows."""
         cfg, w, cb, qb, b = self.cfg, self.w, self._cb, self._qb, self.buf
         H, hc = cfg.hidden_size, cfg.hc_count
@@ -368,7 +370,7 @@ class Qwen4ExpModel(HybridModel):
                 core = cb["core"][:T * cfg.value_dim].view(T, cfg.value_dim)
                 K.gdn_prefill_gate(mixed, z, ab, w[pg + "conv1d_weight"], w[pg + "A_log"], w[pg + "dt_bias"], w[pg + "norm_weight"],
                                    self.ring[i], self.gdn_state[i], cb["gdn"], core, T, Hv, Hk, Dg, pos0, cfg.rms_norm_eps,
-                                   1 if cfg.gdn_gate_act == "sigmoid" else 0)
+                                   1 if cfg.gdn_gate_act == "sigmoid" else 0, exact_scan=not self.chunked_scan)
                 self.lin[pg + "out_proj"].chunk(core, cb["xh"], bout)
             K.q4x_hc_inject(hx, bout, inj, hc)
             inj = self._gate_chunk(p + "hc.mlp.", T)
