@@ -232,8 +232,9 @@ class Qwen4ExpModel(HybridModel):
         super().feed(ids, want_logits)
 
     chunk_rows = int(os.environ.get("R4DXB_Q4X_CHUNK", "1024"))       # rows per prefill chunk (0: 8-row passes only)
-    # the 64-token chunked recurrence instead of the token-by-token one (off: not yet run on a GPU with this family's gate range)
-    chunked_scan = os.environ.get("R4DXB_Q4X_CHUNKED_SCAN", "0") == "1"
+    # the 64-token chunked recurrence (head width 128) instead of the token-by-token one: it forms each pair decay as
+    # exp(G_i - G_j) <= 1, and a test runs it on per-chunk gate sums above 10^4 nats against the exact recurrence
+    chunked_scan = os.environ.get("R4DXB_Q4X_CHUNKED_SCAN", "1") == "1"
 
     def prefill(self, ids: torch.Tensor, chunk: Optional[int] = None, hook=None, embed_overrides=None, image_blocks=None) -> int:
         if embed_overrides is not None or image_blocks or hook is not None:

@@ -543,8 +543,8 @@ def gdn_prefill_gate(mixed, z, ab, conv_w, A_log, dt_bias, norm_w, ring, state, 
     """``gdn_prefill`` with the norm's output gate chosen by the caller (1 = sigmoid).  ``exact_scan`` keeps the recurrence
     token by token.  The chunked kernel forms every pair decay directly as exp(G_i - G_j) <= 1 (it never splits it around
     the chunk's midpoint, the construction that broke the reference's scan on gates of A = exp(A_log) up to ~158 per step;
-    docs/qwen4exp.md "The GDN chunk-scan defect"), so it is not exposed to that defect, but it has not been run on a GPU
-    with gates of that range, so callers with such gates ask for the exact scan."""
+    docs/qwen4exp.md "The GDN chunk-scan defect"), so it is not exposed to that defect; a GPU test runs it on per-chunk gate
+    sums above 10^4 nats against the exact recurrence."""
     _check(_lib().r4dxb_gdn_prefill_gate(_p(mixed), _p(z), _p(ab), _p(conv_w), _p(A_log), _p(dt_bias), _p(norm_w), _p(ring),
                                          _p(state), _p(scratch["q"]), _p(scratch["k"]), _p(scratch["v"]), _p(scratch["eg"]),
                                          _p(scratch["beta"]), _p(scratch["o"]), _p(out), T, H, Hk, D, pos0, eps,

@@ -412,6 +412,47 @@ def test_bf16_gemv_many_rows(K):
     assert torch.allclose(y.cpu(), x.float() @ W.float().T, atol=1e-2, rtol=1e-3)
 
 
+def test_gdn_chunked_prefill_with_gates_of_thousands_of_nats_per_chunk(K):
+    """Per-step decays from exp(-0.03) to exp(-158) (A = exp(A_log), A_log from -3.5 to 5.06): a 64-token chunk's summed
+    log-gates reach ~10^4, far past where a decay split around the chunk's midpoint overflows.  The chunked kernel forms each
+    pair decay as exp(G_i - G_j) <= 1, so it must still equal the token-by-token recurrence; both with the sigmoid gate."""
+    D, Hv, Hk, T = 128, 8, 2, 300
+    g = torch.Generator().manual_seed(77)
+    key_dim, conv_dim = Hk * D, 2 * Hk * D + Hv * D
+    mixed = (torch.randn(T, conv_dim, generator=g) * 0.5).to(BF)
+    z = torch.randn(T, Hv * D, generator=g).to(BF)
+    ab = torch.randn(T, 2 * Hv, generator=g)
+    conv_w = (torch.randn(conv_dim, 4, generator=g) * 0.5).to(BF)
+    A_log = torch.linspace(-3.5, 5.06, Hv)
+    dt_bias = torch.linspace(-6.0, 1.0, Hv)
+    norm_w = (1 + 0.1 * torch.randn(D, generator=g)).to(BF)
+    y, _ = R.causal_conv1d_silu(mixed.float(), conv_w.float(), None)
+    q = R.l2norm(y[:, :key_dim].view(T, Hk, D))
+    k = R.l2norm(y[:, key_dim:2 * key_dim].view(T, Hk, D))
+    v = y[:, 2 * key_dim:].view(T, Hv, D)
+    gg, beta = R.gdn_gates(ab[:, :Hv], ab[:, Hv:], A_log, dt_bias)
+    assert float((-gg[:64].sum(0)).max()) > 5000                     # the widest head's first chunk spans hundreds of nats at least
+    o, _ = R.gdn_recurrent(q, k, v, gg, beta, None)
+    ref = (R.rmsnorm_plain(o, norm_w.float(), 1e-6) * torch.sigmoid(z.float().view(T, Hv, D))).view(T, Hv * D)
+    dev = "cuda"
+    outs, states = [], []
+    for exact in (False, True):
+        ring = torch.zeros(16, conv_dim, dtype=BF, device=dev)
+        state = torch.zeros(Hv, D, D, device=dev)
+        out = torch.zeros(T, Hv * D, dtype=BF, device=dev)
+        sc = dict(q=torch.empty(T, Hk, D, device=dev), k=torch.empty(T, Hk, D, device=dev), v=torch.empty(T, Hv, D, device=dev),
+                  o=torch.empty(T, Hv, D, device=dev), eg=torch.empty(T, Hv, device=dev), beta=torch.empty(T, Hv, device=dev),
+                  ws=torch.full((K.gdn_chunk_ws_floats(T, Hv),), float("nan"), device=dev))
+        K.gdn_prefill_gate(mixed.cuda(), z.cuda(), ab.cuda(), conv_w.cuda(), A_log.cuda(), dt_bias.cuda(), norm_w.cuda(), ring, state,
+                           sc, out, T, Hv, Hk, D, 0, 1e-6, 1, exact_scan=exact)
+        outs.append(out.float().cpu())
+        states.append(state.cpu())
+    assert bool(torch.isfinite(outs[0]).all()) and bool(torch.isfinite(states[0]).all())
+    assert torch.allclose(outs[1], ref, atol=3e-2, rtol=3e-2)
+    assert torch.allclose(outs[0], ref, atol=3e-2, rtol=3e-2)
+    assert (states[0] - states[1]).norm() / states[1].norm() < 5e-3
+
+
 @pytest.mark.parametrize("D,Hv,Hk,T", [(128, 6, 2, 70), (64, 4, 2, 33)])
 def test_gdn_prefill_matches_recurrence_and_hands_over_to_decode(K, D, Hv, Hk, T):
     g = torch.Generator().manual_seed(D + T)
