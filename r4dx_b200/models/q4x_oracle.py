@@ -199,6 +199,8 @@ class Q4xOracle(OracleModel):
         pos = torch.arange(st.pos, st.pos + T)
         q = self._r(R.rope_partial_neox(q, pos, cfg.rotary_dim, cfg.rope_theta))
         k = R.rope_partial_neox(k, pos, cfg.rotary_dim, cfg.rope_theta)
+        if self.on_kv is not None:
+            self.on_kv(li, k, v)
         if self.fp8_kv:
             k = R.fp8_e4m3_roundtrip(k, w[p + "attn.k_descale"][None, :, None])
             v = R.fp8_e4m3_roundtrip(v, w[p + "attn.v_descale"][None, :, None])
@@ -261,3 +263,26 @@ class Q4xOracle(OracleModel):
         if return_hidden:
             return logits, h, st, {}
         return logits, st
+
+
+def table_rows_fn(table):
+    """``ngram_rows`` for the oracle from an opened table (``runtime.ngram.NgramTable``): reference ids, rows read on the host."""
+    import numpy as np
+    from ..runtime import ngram as NG
+
+    def rows(tokens, history):
+        ids = np.asarray(NG.ngram_ids_reference(tokens, table.header, history), dtype=np.int64)
+        return table.rows(ids).reshape(len(tokens), -1)
+    return rows
+
+
+def make_oracle(cfg: ModelConfig, weights: Dict[str, torch.Tensor], ngram_table=None, **kw):
+    """The CPU oracle of ``cfg``'s family (calibration, KL reports, tests): ``Q4xOracle`` for the 4-stream family (its
+    n-gram layer needs the table; without one the layer sees zero rows, which only suits shape checks), ``OracleModel`` else."""
+    if not cfg.is_qwen4_exp:
+        return OracleModel(cfg, weights, **kw)
+    if ngram_table is not None:
+        rows = table_rows_fn(ngram_table)
+    else:
+        rows = lambda tokens, history: torch.zeros(len(tokens), cfg.ple_embed_dim)
+    return Q4xOracle(cfg, weights, rows, **kw)

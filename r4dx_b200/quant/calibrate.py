@@ -22,16 +22,17 @@ from ..config import ModelConfig
 from .w4a16 import W4Weight
 
 
-def _run_prompts(cfg: ModelConfig, weights: Dict[str, torch.Tensor], prompts: Sequence[torch.Tensor], on_linear=None, on_kv=None):
-    from ..models.oracle import OracleModel
-    m = OracleModel(cfg, weights)
+def _run_prompts(cfg: ModelConfig, weights: Dict[str, torch.Tensor], prompts: Sequence[torch.Tensor], on_linear=None, on_kv=None,
+                 ngram_table=None):
+    from ..models.q4x_oracle import make_oracle
+    m = make_oracle(cfg, weights, ngram_table=ngram_table)
     m.on_linear, m.on_kv = on_linear, on_kv
     for ids in prompts:
         m.forward(ids)
 
 
 def kv_descales(cfg: ModelConfig, weights: Dict[str, torch.Tensor], prompts: Sequence[torch.Tensor], margin: float = 1.0,
-                floor: float = 1e-4) -> Dict[int, Tuple[List[float], List[float]]]:
+                floor: float = 1e-4, ngram_table=None) -> Dict[int, Tuple[List[float], List[float]]]:
     """{layer: (k_descale per KV head, v_descale per KV head)} with descale = margin * amax / 448."""
     amax: Dict[int, List[torch.Tensor]] = {}
 
@@ -43,12 +44,17 @@ def kv_descales(cfg: ModelConfig, weights: Dict[str, torch.Tensor], prompts: Seq
         else:
             amax[layer] = [ka, va]
 
-    _run_prompts(cfg, weights, prompts, on_kv=on_kv)
+    _run_prompts(cfg, weights, prompts, on_kv=on_kv, ngram_table=ngram_table)
     return {int(l): ([max(floor, float(x) * margin / 448.0) for x in a[0]], [max(floor, float(x) * margin / 448.0) for x in a[1]])
             for l, a in amax.items() if isinstance(l, int)}
 
 
-def capture_hessians(cfg: ModelConfig, weights: Dict[str, torch.Tensor], prompts: Sequence[torch.Tensor]) -> Dict[str, torch.Tensor]:
+def capture_hessians(cfg: ModelConfig, weights: Dict[str, torch.Tensor], prompts: Sequence[torch.Tensor], ngram_table=None,
+                     counts: Optional[Dict[str, int]] = None) -> Dict[str, torch.Tensor]:
+    """name -> E[x x^T] over the rows each quantizable linear saw (an expert sees its routed rows only).  ``counts`` (optional
+    dict) receives the row count per linear.  A linear that saw fewer rows than it has input channels cannot have a
+    full-rank second moment: it gets the damped diagonal of what it saw instead, so the error compensation degrades to a
+    per-channel weighting (reference: docs/qwen4exp-plan.md Q12/Q16 describes the same fallback and logs the counts)."""
     H: Dict[str, torch.Tensor] = {}
     n: Dict[str, int] = {}
 
@@ -57,8 +63,17 @@ def capture_hessians(cfg: ModelConfig, weights: Dict[str, torch.Tensor], prompts
         H[name] = H.get(name, 0) + x.T @ x
         n[name] = n.get(name, 0) + x.shape[0]
 
-    _run_prompts(cfg, weights, prompts, on_linear=on_linear)
-    return {k: (v / max(1, n[k])).float() for k, v in H.items()}
+    _run_prompts(cfg, weights, prompts, on_linear=on_linear, ngram_table=ngram_table)
+    out = {}
+    for k, v in H.items():
+        h = v / max(1, n[k])
+        if n[k] < h.shape[0]:
+            d = torch.diagonal(h)
+            h = torch.diag(d + 0.01 * d.mean().clamp_min(1e-12))
+        out[k] = h.float()
+    if counts is not None:
+        counts.update(n)
+    return out
 
 
 def _group_params(w: torch.Tensor):
@@ -158,20 +173,32 @@ def main(argv=None) -> int:
     ap.add_argument("--prompts", type=int, default=4)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--out", required=True)
+    ap.add_argument("--ngram-sidecar", default=None, help="qwen4_exp: the n-gram table file the n-gram layer reads its rows from")
     a = ap.parse_args(argv)
     from ..cli.convert import load_source
     cfg, w = load_source(a.input, 0, False, a.seed)
+    table = None
+    if cfg.is_qwen4_exp and cfg.ple_layers:
+        if not a.ngram_sidecar:
+            raise SystemExit("qwen4_exp: --ngram-sidecar FILE is required (activations after the n-gram layer depend on its rows)")
+        from ..runtime import ngram as NG
+        table = NG.NgramTable.open(a.ngram_sidecar, mode="file")
     g = torch.Generator().manual_seed(a.seed)
     prompts = [torch.randint(0, cfg.vocab_size, (a.tokens,), generator=g) for _ in range(a.prompts)]
     if a.what in ("hessians", "imatrix"):
         from safetensors.torch import save_file
-        H = capture_hessians(cfg, w, prompts)
+        counts: Dict[str, int] = {}
+        H = capture_hessians(cfg, w, prompts, ngram_table=table, counts=counts)
+        thin = sorted(k for k, v in H.items() if counts.get(k, 0) < v.shape[0])
         if a.what == "imatrix":
             H = {k: torch.diagonal(v).contiguous() for k, v in H.items()}
         save_file({k: v.contiguous() for k, v in H.items()}, a.out)
         print(f"wrote {a.what} of {len(H)} linears to {a.out}")
+        if thin:
+            print(f"{len(thin)} linears saw fewer rows than input channels and got a damped diagonal (first: {thin[0]}, "
+                  f"{counts[thin[0]]} rows)")
         return 0
-    d = kv_descales(cfg, w, prompts)
+    d = kv_descales(cfg, w, prompts, ngram_table=table)
     json.dump({str(l): {"k": k, "v": v} for l, (k, v) in d.items()}, open(a.out, "w"), indent=1)
     print(f"wrote fp8 KV descales of {len(d)} attention layers to {a.out}")
     return 0

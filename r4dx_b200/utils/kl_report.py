@@ -37,17 +37,24 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--prompts", type=int, default=2)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--ngram-sidecar", default=None, help="qwen4_exp: the n-gram table file")
     a = ap.parse_args(argv)
     from ..cli.convert import _kb_rule, load_source
-    from ..models.oracle import OracleModel
+    from ..models.q4x_oracle import make_oracle
     from ..quant.weights import dequantize_weight_set, quantize_weight_set
     cfg, w = load_source(a.input, a.layers, False, a.seed)
+    table = None
+    if cfg.is_qwen4_exp and cfg.ple_layers:
+        if not a.ngram_sidecar:
+            raise SystemExit("qwen4_exp: --ngram-sidecar FILE is required")
+        from ..runtime import ngram as NG
+        table = NG.NgramTable.open(a.ngram_sidecar, mode="file")
     hess = None
     if a.hessians:
         from safetensors.torch import load_file
         hess = {k: v for k, v in load_file(a.hessians).items() if v.dim() == 2}
     q = quantize_weight_set(cfg, w, layout=a.layout, kb_rule=_kb_rule(a.kb_plan), seed=a.seed, hessians=hess)
-    src, got = OracleModel(cfg, w), OracleModel(cfg, dequantize_weight_set(q))
+    src, got = make_oracle(cfg, w, ngram_table=table), make_oracle(cfg, dequantize_weight_set(q), ngram_table=table)
     g = torch.Generator().manual_seed(a.seed + 1)
     ref_rows, got_rows = [], []
     for _ in range(a.prompts):

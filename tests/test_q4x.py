@@ -290,3 +290,38 @@ def test_table_file_from_a_checkpoints_own_shards(tmp_path, table):
     (d / "config.json").write_text(json.dumps({"text_config": {"ple_layer_ids": [2], "split_ngram_parts": 5}}))
     with pytest.raises(NG.NgramError, match="expected shard_0..shard_4"):
         NG.repack_from_checkpoint(str(d), out)
+
+
+def test_calibration_and_kl_report_run_on_the_family(tmp_path, table):
+    """Hessians of a 2-layer model (experts that saw fewer rows than input channels get a damped diagonal), KV descales
+    of its attention layer, and the KL report of a quantized set, all through the family's own oracle."""
+    import json
+    from safetensors.torch import load_file
+    from r4dx_b200.quant import calibrate
+    from r4dx_b200.quant.calibrate import capture_hessians
+    cfg = tiny_qwen4_exp_config()
+    w = init_q4x_weights(cfg, seed=2)
+    prompts = [torch.randint(0, cfg.vocab_size, (24,), generator=torch.Generator().manual_seed(s)) for s in range(2)]
+    counts = {}
+    H = capture_hessians(cfg, w, prompts, ngram_table=table, counts=counts)
+    assert counts["text.layers.0.gdn.in_proj_qkv"] == 48 and H["text.layers.0.gdn.in_proj_qkv"].shape == (256, 256)
+    ex = [k for k in H if ".experts." in k and k.endswith("gate_up")]
+    assert ex and all(counts[k] < 256 for k in ex)                # 48 rows x top-4 over 16 experts: no expert sees 256 rows
+    h = H[ex[0]]
+    assert torch.equal(h, torch.diag(torch.diagonal(h))) and float(torch.diagonal(h).min()) > 0
+    dense = H["text.layers.0.gdn.in_proj_qkv"]                    # 48 rows < 256 channels as well: diagonal, too
+    assert torch.equal(dense, torch.diag(torch.diagonal(dense)))
+    out = str(tmp_path / "kv.json")
+    with pytest.raises(SystemExit, match="ngram-sidecar"):
+        calibrate.main(["kv", "--input", "random:q4x", "--tokens", "16", "--prompts", "1", "--out", out])
+    assert calibrate.main(["kv", "--input", "random:q4x", "--tokens", "16", "--prompts", "1", "--out", out, "--ngram-sidecar", table.path]) == 0
+    kv = json.load(open(out))
+    assert list(kv) == ["3"] and len(kv["3"]["k"]) == cfg.num_key_value_heads and min(kv["3"]["k"]) > 0
+    from r4dx_b200.utils import kl_report
+    import io, contextlib
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        assert kl_report.main(["--input", "random:q4x", "--kb-plan", "kb4", "--tokens", "16", "--prompts", "1", "--layers", "2",
+                               "--ngram-sidecar", table.path]) == 0
+    rep = json.loads(buf.getvalue().strip().splitlines()[-1])
+    assert rep["positions"] == 16 and 0 <= rep["kl_mean"] < 1.0
