@@ -325,3 +325,20 @@ def test_calibration_and_kl_report_run_on_the_family(tmp_path, table):
                                "--ngram-sidecar", table.path]) == 0
     rep = json.loads(buf.getvalue().strip().splitlines()[-1])
     assert rep["positions"] == 16 and 0 <= rep["kl_mean"] < 1.0
+
+
+def test_tie_rule_noise_floor_tool(table, tiny):
+    """With exact ties forced (two equal keys blocks cannot be told apart by score) the two tie rules pick different blocks
+    on some rows and the report says so; KL of a model against itself under one rule is 0."""
+    from r4dx_b200.utils.qsa_noise_floor import noise_floor, select_blocks_oldest
+    cfg, w, _ = tiny
+    s = torch.tensor([0.0, 2.0, 0.0, 2.0, 0.0, 1.0, 0.0])
+    assert select_blocks_oldest(s, 4).tolist() == [0, 1, 3, 5] and select_blocks(s, 4).tolist() == [1, 3, 5, 6]
+    w2 = dict(w)
+    w2["text.layers.3.attn.indexer.qk"] = torch.zeros_like(w["text.layers.3.attn.indexer.qk"])    # every block scores 0: all ties
+    ids = [torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(4))]
+    rep = noise_floor(cfg, w2, table, ids)
+    assert rep["sparse_rows"] == 21 and rep["rows_where_the_rules_pick_different_blocks"] == 21
+    assert rep["kl_mean"] > 0
+    rep0 = noise_floor(cfg, w, table, ids)
+    assert rep0["rows_where_the_rules_pick_different_blocks"] <= rep["rows_where_the_rules_pick_different_blocks"]
