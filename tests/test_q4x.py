@@ -1,7 +1,6 @@
 """qwen4_exp family on the CPU: n-gram ids and table file, the oracle's stream gate, n-gram layer and block-selecting
 attention (chunking invariance, the dense limit, the tie rule)."""
 import dataclasses
-import os
 
 import numpy as np
 import pytest
@@ -296,7 +295,6 @@ def test_calibration_and_kl_report_run_on_the_family(tmp_path, table):
     """Hessians of a 2-layer model (experts that saw fewer rows than input channels get a damped diagonal), KV descales
     of its attention layer, and the KL report of a quantized set, all through the family's own oracle."""
     import json
-    from safetensors.torch import load_file
     from r4dx_b200.quant import calibrate
     from r4dx_b200.quant.calibrate import capture_hessians
     cfg = tiny_qwen4_exp_config()

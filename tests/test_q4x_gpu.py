@@ -1,7 +1,5 @@
 """qwen4_exp family on the GPU: every new kernel against the fp32 oracle's piece, then the tiny model end to end (eager,
 chunked, graph replay, checkpoint) against the oracle running the same quantized weights."""
-import dataclasses
-
 import numpy as np
 import pytest
 import torch
