@@ -118,8 +118,16 @@ def _load_qwen4_exp(args, gcfg, weights, model_arg: str, model_id: str, device):
             if not rec:
                 raise SystemExit("this container records no n-gram table; pass --ngram-sidecar FILE")
             path = rec["path"] if os.path.isabs(rec["path"]) else os.path.join(os.path.dirname(os.path.abspath(model_arg)), rec["path"])
+        placement = getattr(args, "ngram_placement", "device")
         try:
-            table = NG.NgramTable.open(path, mode=getattr(args, "ngram_placement", "device"), device=device)
+            try:
+                # rows read from the file bypass the page cache where the file system allows it (the full table is 95 GiB)
+                table = NG.NgramTable.open(path, mode=placement, device=device, direct=(placement == "file"))
+            except NG.NgramError as e:
+                if "O_DIRECT" not in str(e):
+                    raise
+                print(f"n-gram table: {e}; reading through the page cache", flush=True)
+                table = NG.NgramTable.open(path, mode=placement, device=device)
         except (OSError, NG.NgramError) as e:
             raise SystemExit(f"n-gram table {path}: {e}")
         if not getattr(args, "ngram_sidecar", None) and rec.get("sha256") and table.header.body_sha256.hex() != rec["sha256"]:

@@ -47,6 +47,11 @@ native.register_host_sig("r4dxb_ngram_read_rows", ctypes.c_int64,
                           ctypes.c_void_p, ctypes.c_int])
 
 
+native.register_host_sig("r4dxb_ngram_read_rows_direct", ctypes.c_int64,
+                         [ctypes.c_int, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int64, ctypes.c_int64,
+                          ctypes.c_void_p, ctypes.c_int])
+
+
 class NgramError(RuntimeError):
     pass
 
@@ -255,15 +260,27 @@ class NgramTable:
     """The opened table.  ``gather(tokens)`` returns the rows of the tokens, [n, heads * head_dim] bf16 on ``device``, and
     advances the history; ``device`` mode does both in one kernel on the current stream."""
 
-    def __init__(self, path: str, header: NgramHeader, mode: str, device, fd: int, body: Optional[torch.Tensor], threads: int):
+    def __init__(self, path: str, header: NgramHeader, mode: str, device, fd: int, body: Optional[torch.Tensor], threads: int,
+                 direct_fd: int = -1):
         self.path, self.header, self.mode, self.device, self._fd, self.body, self.threads = path, header, mode, device, fd, body, threads
+        self._direct_fd = direct_fd          # >= 0: row reads bypass the page cache (O_DIRECT)
         self.ids = NgramIds(header)
 
     @staticmethod
-    def open(path: str, mode: str = "device", device="cuda", threads: int = 8, allow_truncated: bool = False) -> "NgramTable":
+    def open(path: str, mode: str = "device", device="cuda", threads: int = 8, allow_truncated: bool = False,
+             direct: bool = False) -> "NgramTable":
+        """``direct`` (file placement): row reads use O_DIRECT, so the 95 GiB table neither fills nor evicts the page cache
+        (reference: docs/qwen4exp.md "Requirements": the sidecar is read with unbuffered I/O, never through the file cache)."""
         if mode not in ("device", "pinned", "file"):
             raise NgramError(f"n-gram table placement {mode!r}: device | pinned | file")
         fd = os.open(path, os.O_RDONLY)
+        direct_fd = -1
+        if direct and mode == "file":
+            try:
+                direct_fd = os.open(path, os.O_RDONLY | os.O_DIRECT)
+            except OSError as e:
+                os.close(fd)
+                raise NgramError(f"n-gram table {path}: this file system refuses O_DIRECT ({e.strerror})")
         try:
             head = NgramHeader.parse(os.pread(fd, HEADER_BYTES, 0))
             size = os.fstat(fd).st_size
@@ -283,8 +300,10 @@ class NgramTable:
                 body = host.to(device) if mode == "device" else host
         except Exception:
             os.close(fd)
+            if direct_fd >= 0:
+                os.close(direct_fd)
             raise
-        return NgramTable(path, head, mode, torch.device(device), fd, body, threads)
+        return NgramTable(path, head, mode, torch.device(device), fd, body, threads, direct_fd)
 
     @staticmethod
     def synthetic_device(header: NgramHeader, device="cuda", std: float = 0.02, seed: int = 0) -> "NgramTable":
@@ -301,6 +320,9 @@ class NgramTable:
         if self._fd >= 0:
             os.close(self._fd)
             self._fd = -1
+        if self._direct_fd >= 0:
+            os.close(self._direct_fd)
+            self._direct_fd = -1
 
     def verify_sha256(self) -> bool:
         sha, at = hashlib.sha256(), 0
@@ -321,8 +343,12 @@ class NgramTable:
                 raise NgramError("n-gram row id out of range")
             return self.body[torch.from_numpy(flat)].view(*ids.shape, h.head_dim)
         out = torch.empty(flat.shape[0], h.head_dim, dtype=torch.bfloat16)
-        rc = native.host().r4dxb_ngram_read_rows(self._fd, flat.ctypes.data, flat.shape[0], h.rows, h.row_bytes, HEADER_BYTES,
-                                                 out.data_ptr(), self.threads)
+        if self._direct_fd >= 0:
+            rc = native.host().r4dxb_ngram_read_rows_direct(self._direct_fd, flat.ctypes.data, flat.shape[0], h.rows, h.row_bytes,
+                                                            HEADER_BYTES, os.fstat(self._fd).st_size, out.data_ptr(), self.threads)
+        else:
+            rc = native.host().r4dxb_ngram_read_rows(self._fd, flat.ctypes.data, flat.shape[0], h.rows, h.row_bytes, HEADER_BYTES,
+                                                     out.data_ptr(), self.threads)
         if rc:
             raise NgramError(f"n-gram table: row {int(flat[rc - 1])} could not be read in full")
         return out.view(*ids.shape, h.head_dim)

@@ -340,3 +340,22 @@ def test_tie_rule_noise_floor_tool(table, tiny):
     assert rep["kl_mean"] > 0
     rep0 = noise_floor(cfg, w, table, ids)
     assert rep0["rows_where_the_rules_pick_different_blocks"] <= rep["rows_where_the_rules_pick_different_blocks"]
+
+
+def test_direct_row_reads_equal_buffered_reads(table, tmp_path):
+    """O_DIRECT row reads (aligned spans around each row, rows that straddle a sector boundary, the file's last rows) give
+    the same rows as buffered reads; a file system that refuses O_DIRECT says so."""
+    import shutil
+    path = str(tmp_path / "copy.r4dx-ngram")                     # (the default tmp dir may sit on a file system without O_DIRECT)
+    shutil.copyfile(table.path, path)
+    try:
+        t = NG.NgramTable.open(path, mode="file", direct=True, threads=3)
+    except NG.NgramError as e:
+        assert "O_DIRECT" in str(e)
+        pytest.skip("this file system refuses O_DIRECT")
+    h = t.header
+    ids = np.asarray([0, 1, 11, 12, 13, h.rows - 1, h.rows - 2, 4095 // h.row_bytes, 4096 // h.row_bytes, 1234, 7], dtype=np.int64)
+    assert torch.equal(t.rows(ids), table.rows(ids))
+    with pytest.raises(NG.NgramError, match="could not be read"):
+        t.rows(np.asarray([h.rows], dtype=np.int64))
+    t.close()
