@@ -343,10 +343,13 @@ class NgramTable:
                 raise NgramError("n-gram row id out of range")
             return self.body[torch.from_numpy(flat)].view(*ids.shape, h.head_dim)
         out = torch.empty(flat.shape[0], h.head_dim, dtype=torch.bfloat16)
+        rc = -1
         if self._direct_fd >= 0:
             rc = native.host().r4dxb_ngram_read_rows_direct(self._direct_fd, flat.ctypes.data, flat.shape[0], h.rows, h.row_bytes,
                                                             HEADER_BYTES, os.fstat(self._fd).st_size, out.data_ptr(), self.threads)
-        else:
+        if rc != 0:
+            # no direct descriptor, or a direct read failed (some file systems accept the flag and then refuse the reads): the
+            # buffered descriptor decides; a row it cannot deliver either is an error, never a zero row
             rc = native.host().r4dxb_ngram_read_rows(self._fd, flat.ctypes.data, flat.shape[0], h.rows, h.row_bytes, HEADER_BYTES,
                                                      out.data_ptr(), self.threads)
         if rc:
