@@ -37,7 +37,10 @@ def add_model_flags(ap: argparse.ArgumentParser) -> None:
     p.add_argument("--tp-mode", default=os.environ.get("R4DXB_TP_MODE", "fused"), choices=["fused", "nccl", "noop"])
     p.add_argument("--tp-ar-timeout-ms", type=int, default=500)
     p.add_argument("--pp", type=int, default=1, choices=[1, 2])
-    p.add_argument("--pp-split", type=int, default=0)
+    p.add_argument("--pp-split", type=int, default=0, help="first layer of the second stage (0: chosen by --pp-balance)")
+    p.add_argument("--pp-balance", default="layers", choices=["layers", "bytes"],
+                   help="how --pp-split 0 places the boundary: by layer count (equal prefill work, the head counted with the "
+                        "second stage) or by weight bytes (models that only fit when the two devices hold equal shares)")
     p.add_argument("--pp-min-rows", type=int, default=512)
     p.add_argument("--ep", type=int, default=1, choices=[1, 2, 4, 8],
                    help="expert parallelism for mixture-of-experts models: whole attention per rank, a slice of the experts each")

@@ -155,6 +155,12 @@ def _load_pipeline(args, gcfg, cfg, weights, full, model_id, device, rank, world
     from ..runtime.pp_model import HybridPpTextModel, LayerSplitTextModel
     from ..runtime.tokenizer import load_tokenizer
     split = args.pp_split or default_split(gcfg)
+    if not args.pp_split and getattr(args, "pp_balance", "layers") == "bytes":
+        from ..parallel.pp import choose_split_by_bytes, layer_bytes
+        src = full if full is not None else weights
+        nb = lambda name: 0 if name not in src else (src[name].nbytes if not isinstance(src[name], torch.Tensor)
+                                                     else src[name].numel() * src[name].element_size())
+        split = choose_split_by_bytes(layer_bytes(gcfg, src), nb("text.embed_tokens"), nb("lm_head"))
     if not 0 < split < gcfg.num_hidden_layers:
         raise SystemExit(f"--pp-split {split} must leave both stages at least one of the {gcfg.num_hidden_layers} layers")
     rng = (0, split) if rank == 0 else (split, gcfg.num_hidden_layers)

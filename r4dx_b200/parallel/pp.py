@@ -31,6 +31,40 @@ def default_split(cfg: ModelConfig) -> int:
     return max(1, (n * 29) // 64) if n >= 8 else n // 2
 
 
+def layer_bytes(cfg: ModelConfig, weights) -> List[int]:
+    """Device bytes of every layer's tensors in a weight set (quantized layouts count their packed bytes)."""
+    out = [0] * cfg.num_hidden_layers
+    for name, t in weights.items():
+        if name.startswith("text.layers."):
+            i = int(name.split(".")[2])
+            if i < len(out):
+                out[i] += t.nbytes if not isinstance(t, torch.Tensor) else t.numel() * t.element_size()
+    return out
+
+
+def choose_split_by_bytes(per_layer: List[int], first_stage_extra: int = 0, last_stage_extra: int = 0, cap: int = 0) -> int:
+    """The layer boundary k (stage A = layers [0, k), stage B = the rest) that balances the two stages' weight bytes; stage A
+    also carries ``first_stage_extra`` (embedding table), stage B ``last_stage_extra`` (head).  With ``cap`` > 0 a split
+    whose larger stage exceeds it is refused (the model does not fit two devices of that size).
+    (reference: src/model/qwen4exp_container.h:5-9 places its two stages by the same rule.)"""
+    n = len(per_layer)
+    if n < 2:
+        raise ValueError("a two-stage split needs at least two layers")
+    total = sum(per_layer)
+    best_k, best_gap, run = 1, None, 0
+    for k in range(1, n):
+        run += per_layer[k - 1]
+        a, b = run + first_stage_extra, total - run + last_stage_extra
+        gap = abs(a - b)
+        if best_gap is None or gap < best_gap:
+            best_k, best_gap = k, gap
+    a = sum(per_layer[:best_k]) + first_stage_extra
+    b = total - sum(per_layer[:best_k]) + last_stage_extra
+    if cap and max(a, b) > cap:
+        raise ValueError(f"no two-stage split fits {cap} bytes per device: the best one needs {max(a, b)}")
+    return best_k
+
+
 class PipelinePrefill:
     def __init__(self, stage: HybridModel, rank: int, split: int, chunk: int = 1024, group=None):
         self.stage, self.rank, self.split, self.chunk, self.group = stage, rank, split, chunk, group

@@ -146,3 +146,16 @@ def test_converter_writes_and_reads_the_w8a16_body_layout(tmp_path):
     assert len(body) >= 6 * cfg.num_hidden_layers and all(q[k].wq.dtype == torch.uint8 for k in body)
     dq = dequantize_weight_set(q)
     assert dq[body[0]].shape == (q[body[0]].N, q[body[0]].K)
+
+
+def test_two_stage_split_balanced_by_weight_bytes():
+    from r4dx_b200.parallel.pp import choose_split_by_bytes
+    assert choose_split_by_bytes([10] * 8) == 4
+    assert choose_split_by_bytes([10] * 8, last_stage_extra=20) == 5          # the head rides with stage B: A takes one more layer
+    assert choose_split_by_bytes([30, 10, 10, 10, 10, 10]) == 2               # a heavy first layer moves the boundary up
+    assert choose_split_by_bytes([1, 1, 1, 100]) == 3
+    with pytest.raises(ValueError, match="fits"):
+        choose_split_by_bytes([10] * 8, cap=35)
+    assert choose_split_by_bytes([10] * 8, cap=40) == 4
+    with pytest.raises(ValueError):
+        choose_split_by_bytes([5])
