@@ -135,5 +135,8 @@ def convert_parser() -> argparse.ArgumentParser:
                          "this engine's tile order) instead of encoding those linears; every imported tensor is reconstructed on "
                          "the CPU and checked against the checkpoint")
     ap.add_argument("--trellis-verify", default="full", choices=["full", "none"])
+    ap.add_argument("--plan-only", action="store_true",
+                    help="plan every tensor (layout, bit width, bytes) and print the container's tensor count and data bytes "
+                         "without quantizing anything or writing --output")
     ap.add_argument("--selftest", action="store_true", help="re-open the output and verify every tensor's reconstruction error")
     return ap

@@ -74,6 +74,42 @@ def load_source(spec: str, layers: int, mtp: bool, seed: int, raw_out=None):
     return cfg, import_hf_weights(cfg, w)
 
 
+def plan_container(cfg, w, layout: str, kb_rule, head_group: int, lm_head: str = "w4a16", keep=()) -> dict:
+    """What the converter would write, from shapes alone: per tensor the layout, the bit width and the stored bytes (the same
+    rules as ``quantize_weight_set`` + ``save_weight_set``; reference: src/convert/main.cpp --plan-only)."""
+    from ..quant.weights import F32_NAMES, is_quantized_linear
+    plan, by_layout = {}, {}
+    for name, t in w.items():
+        shape = tuple(t.shape)
+        numel = 1
+        for d in shape:
+            numel *= d
+        leaf = name.split(".")[-1]
+        kept = any(s_ in name for s_ in keep)
+        if name == "lm_head" and lm_head != "bf16" and layout != "bf16" and not kept:
+            N, K = shape
+            lay, bits, nbytes = "w4a16", 4, N * K // 2 + N * (K // head_group) * 4
+        elif not kept and is_quantized_linear(name) and layout == "trellis" and len(shape) == 2 and shape[0] % 128 == 0 and shape[1] % 128 == 0:
+            N, K = shape
+            kb = kb_rule(name)
+            lay, bits, nbytes = "trellis", kb, N * K * kb // 8 + 2 * K + 2 * N
+        elif not kept and is_quantized_linear(name) and layout == "w8a16" and len(shape) == 2 and shape[0] % 128 == 0 and shape[1] % 128 == 0:
+            N, K = shape
+            lay, bits, nbytes = "w8a16", 8, N * K + N * (K // head_group) * 2
+        elif not kept and is_quantized_linear(name) and layout == "w4a16" and len(shape) == 2:
+            N, K = shape
+            lay, bits, nbytes = "w4a16", 4, N * K // 2 + N * (K // head_group) * 4
+        elif leaf in F32_NAMES or name.startswith("rotation."):
+            lay, bits, nbytes = "f32", 32, numel * 4
+        else:
+            lay, bits, nbytes = "bf16", 16, numel * 2
+        plan[name] = {"layout": lay, "bits": bits, "shape": list(shape), "bytes": nbytes}
+        agg = by_layout.setdefault(lay, {"tensors": 0, "bytes": 0})
+        agg["tensors"] += 1
+        agg["bytes"] += nbytes
+    return {"tensors": len(plan), "data_bytes": sum(v["bytes"] for v in plan.values()), "by_layout": by_layout, "plan": plan}
+
+
 def main(argv=None) -> int:
     args = convert_parser().parse_args(argv)
     from ..quant.container import Container
@@ -92,6 +128,13 @@ def main(argv=None) -> int:
             raise SystemExit("qwen4_exp: --ngram-sidecar FILE is required (the container records the n-gram table it was built for)")
     keep = [s for s in args.keep_bf16.split(",") if s]
     layout = args.layouts.split(",")[0]
+    if args.plan_only:
+        rep = plan_container(cfg, w, layout, _kb_rule(args.kb_plan), args.lm_head_group, args.lm_head, keep)
+        plan = rep.pop("plan")
+        rep["largest"] = [[n, v["layout"], v["bytes"]] for n, v in sorted(plan.items(), key=lambda kv: -kv[1]["bytes"])[:5]]
+        rep["arch"] = cfg.arch
+        print(json.dumps(rep))
+        return 0
     src = {k: v for k, v in w.items()}
     extra_meta = {}
     if args.rotate != "none":

@@ -1,4 +1,6 @@
 """Argument parsers and the converter round trip (CPU)."""
+import os
+
 import pytest
 import torch
 
@@ -159,3 +161,20 @@ def test_two_stage_split_balanced_by_weight_bytes():
     assert choose_split_by_bytes([10] * 8, cap=40) == 4
     with pytest.raises(ValueError):
         choose_split_by_bytes([5])
+
+
+def test_plan_only_predicts_what_the_converter_writes(tmp_path, capsys):
+    """--plan-only prints tensor count and data bytes from shapes alone; they equal what a real conversion stores."""
+    import json
+    from r4dx_b200.cli.convert import main as convert_main
+    from r4dx_b200.quant.weights import load_weight_set
+    out = str(tmp_path / "m.r4dxb")
+    assert convert_main(["--input", "random:moe", "--output", out, "--layers", "2", "--kb-plan", "mix3.3", "--plan-only"]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert not os.path.exists(out) and rep["arch"] == "qwen_hybrid_moe"
+    assert convert_main(["--input", "random:moe", "--output", out, "--layers", "2", "--kb-plan", "mix3.3"]) == 0
+    cfg, w = load_weight_set(out)
+    assert rep["tensors"] == len(w)
+    stored = sum(t.nbytes if not isinstance(t, torch.Tensor) else t.numel() * t.element_size() for t in w.values())
+    assert rep["data_bytes"] == stored, (rep["data_bytes"], stored)
+    assert rep["by_layout"]["trellis"]["tensors"] == sum(type(t).__name__ == "TrellisWeight" for t in w.values())
