@@ -135,6 +135,12 @@ def convert_parser() -> argparse.ArgumentParser:
                          "this engine's tile order) instead of encoding those linears; every imported tensor is reconstructed on "
                          "the CPU and checked against the checkpoint")
     ap.add_argument("--trellis-verify", default="full", choices=["full", "none"])
+    ap.add_argument("--w4a16-group-rule", default="", metavar="REGEX=GROUP[,REGEX=GROUP...]",
+                    help="w4a16 group size per tensor name, first match wins (e.g. '^lm_head$=32'); others use --lm-head-group")
+    ap.add_argument("--w8a16-group", type=int, default=0, help="group size of the w8a16 body layout (default: --lm-head-group)")
+    ap.add_argument("--ldlq-damp", type=float, default=0.01, help="relative diagonal damping of the Hessians in the error-compensated trellis quantizer")
+    ap.add_argument("--trellis-manifest-sha256", default=None, metavar="HEX",
+                    help="with --trellis-from: refuse the directory unless its trellis_manifest.json has this sha256")
     ap.add_argument("--plan-only", action="store_true",
                     help="plan every tensor (layout, bit width, bytes) and print the container's tensor count and data bytes "
                          "without quantizing anything or writing --output")

@@ -20,6 +20,25 @@ def _kb_rule(plan: str):
     return {"mix4.5": default_kb_rule, "mix3.3": moe_kb_rule, "kb3": lambda n: 3, "kb4": lambda n: 4, "kb5": lambda n: 5}[plan]
 
 
+def parse_group_rule(text: str):
+    """'REGEX=GROUP,REGEX=GROUP' -> name -> group or None (first match wins; groups 32, 64 or 128)."""
+    import re
+    rules = []
+    for part in [p_ for p_ in text.split(",") if p_]:
+        if "=" not in part:
+            raise SystemExit(f"--w4a16-group-rule: '{part}' is not REGEX=GROUP")
+        rx, g = part.rsplit("=", 1)
+        if g not in ("32", "64", "128"):
+            raise SystemExit(f"--w4a16-group-rule: group {g} is not 32, 64 or 128")
+        try:
+            rules.append((re.compile(rx), int(g)))
+        except re.error as e:
+            raise SystemExit(f"--w4a16-group-rule: bad pattern {rx!r}: {e}")
+    if not rules:
+        return None
+    return lambda name: next((g for rx, g in rules if rx.search(name)), None)
+
+
 def load_source(spec: str, layers: int, mtp: bool, seed: int, raw_out=None):
     """(config, fp32 weights under this engine's names).  ``raw_out``: a dict that receives the checkpoint's own tensors
     when the source is a Hugging Face directory (the vision tower is imported from them)."""
@@ -161,6 +180,14 @@ def main(argv=None) -> int:
         from safetensors.torch import load_file
         imatrix = {k: v for k, v in load_file(args.imatrix).items() if v.dim() == 1}
     imported = {}
+    if args.trellis_from and args.trellis_manifest_sha256:
+        mpath = os.path.join(args.trellis_from, "trellis_manifest.json")
+        try:
+            got = hashlib.sha256(open(mpath, "rb").read()).hexdigest()
+        except OSError as e:
+            raise SystemExit(f"--trellis-from {args.trellis_from}: {e}")
+        if got != args.trellis_manifest_sha256.lower():
+            raise SystemExit(f"--trellis-manifest-sha256: {mpath} hashes to {got}")
     if args.trellis_from:
         # already-encoded body linears: taken as they are (checked against the checkpoint), everything else is quantized here
         from ..quant.weights import import_trellis_dir
@@ -177,7 +204,9 @@ def main(argv=None) -> int:
         print(f"imported {len(imported)} trellis tensors from {args.trellis_from} (worst reconstruction error {worst[1]:.4f} at {worst[0]})",
               file=sys.stderr)
     q = quantize_weight_set(cfg, src, layout=layout, kb_rule=_kb_rule(args.kb_plan), head_group=args.lm_head_group, seed=args.seed,
-                            encoder=args.encoder, hessians=hessians, imatrix=imatrix, search=args.quant == "search")
+                            encoder=args.encoder, hessians=hessians, imatrix=imatrix, search=args.quant == "search",
+                            group_rule=parse_group_rule(args.w4a16_group_rule), w8_group=args.w8a16_group or None,
+                            ldlq_damp=args.ldlq_damp)
     q.update(imported)
     if args.vision == "on":
         # the tower stays bf16 under "vision."; a random source gets a small random tower of the serving code's test geometry

@@ -50,7 +50,9 @@ def is_quantized_linear(name: str) -> bool:
 def quantize_weight_set(cfg: ModelConfig, w: Dict[str, torch.Tensor], layout: str = "trellis",
                         kb_rule: Callable[[str], int] = default_kb_rule, head_group: int = 64,
                         seed: int = 0, encoder: str = "cpu", hessians: Optional[Dict[str, torch.Tensor]] = None,
-                        imatrix: Optional[Dict[str, torch.Tensor]] = None, search: bool = False) -> Dict[str, object]:
+                        imatrix: Optional[Dict[str, torch.Tensor]] = None, search: bool = False,
+                        group_rule: Optional[Callable[[str], Optional[int]]] = None, w8_group: Optional[int] = None,
+                        ldlq_damp: float = 0.01) -> Dict[str, object]:
     """fp32 weights -> quantized set.  layout: trellis | w4a16 | bf16.  ``encoder``: where the Viterbi search of the
     trellis layout runs - "cpu" (threads) or "cuda" (one CTA per tile, ~25x the throughput of 32 host threads); the
     result lives on the CPU either way.  ``hessians``: name -> [K, K] input second moments; linears that have one are
@@ -60,20 +62,28 @@ def quantize_weight_set(cfg: ModelConfig, w: Dict[str, torch.Tensor], layout: st
     out: Dict[str, object] = {}
     hessians = hessians or {}
     imatrix = imatrix or {}
+    default_group = head_group
+
+    def group_of(name: str) -> int:
+        """w4a16 group size of ``name``: the first matching rule of ``group_rule`` (32, 64 or 128), else ``head_group``."""
+        g_ = group_rule(name) if group_rule is not None else None
+        return int(g_) if g_ else default_group
+
     for i, (name, t) in enumerate(w.items()):
         leaf = name.split(".")[-1]
+        head_group = group_of(name)
         if name == "lm_head":
             out[name] = w4a16.quantize(t, head_group) if layout != "bf16" else t.to(torch.bfloat16)
         elif is_quantized_linear(name) and layout == "trellis" and t.shape[0] % 128 == 0 and t.shape[1] % 128 == 0:
             if name in hessians:
-                out[name], _, _ = trellis.quantize_ldlq(t, hessians[name], kb_rule(name), seed=seed * 100003 + i)
+                out[name], _, _ = trellis.quantize_ldlq(t, hessians[name], kb_rule(name), seed=seed * 100003 + i, damp=ldlq_damp)
             elif encoder == "cuda":
                 tw, _ = trellis.quantize_cuda(t, kb_rule(name), seed=seed * 100003 + i)
                 out[name] = TrellisWeight(tw.words.cpu(), tw.suh.cpu(), tw.svh.cpu(), tw.N, tw.K, tw.kb)
             else:
                 out[name], _ = trellis.quantize(t, kb_rule(name), seed=seed * 100003 + i)
         elif is_quantized_linear(name) and layout == "w8a16" and t.shape[0] % 128 == 0 and t.shape[1] % 128 == 0:
-            out[name] = w4a16.quantize_w8(t, head_group)          # symmetric int8, fp16 group scales, round to nearest
+            out[name] = w4a16.quantize_w8(t, w8_group or default_group)          # symmetric int8, fp16 group scales, round to nearest
         elif is_quantized_linear(name) and layout == "w4a16":
             if name in hessians:
                 from .calibrate import gptq_w4a16

@@ -178,3 +178,30 @@ def test_plan_only_predicts_what_the_converter_writes(tmp_path, capsys):
     stored = sum(t.nbytes if not isinstance(t, torch.Tensor) else t.numel() * t.element_size() for t in w.values())
     assert rep["data_bytes"] == stored, (rep["data_bytes"], stored)
     assert rep["by_layout"]["trellis"]["tensors"] == sum(type(t).__name__ == "TrellisWeight" for t in w.values())
+
+
+def test_group_rules_and_manifest_hash_flags(tmp_path):
+    import hashlib
+    from r4dx_b200.cli.convert import main as convert_main, parse_group_rule
+    from r4dx_b200.quant.weights import export_trellis_dir, load_weight_set
+    rule = parse_group_rule("^lm_head$=32,attn=128")
+    assert rule("lm_head") == 32 and rule("text.layers.0.attn.qg") == 128 and rule("text.layers.0.mlp.down") is None
+    with pytest.raises(SystemExit, match="32, 64 or 128"):
+        parse_group_rule("x=48")
+    out = str(tmp_path / "a.r4dxb")
+    assert convert_main(["--input", "random:tiny", "--output", out, "--layers", "1", "--layouts", "w8a16", "--w4a16-group-rule", "^lm_head$=32",
+                         "--w8a16-group", "128"]) == 0
+    cfg, w = load_weight_set(out)
+    assert w["lm_head"].group == 32 and w["text.layers.0.gdn.in_proj_qkv"].group == 128
+    # the trellis import directory is pinned by the hash of its manifest
+    out2 = str(tmp_path / "b.r4dxb")
+    assert convert_main(["--input", "random:tiny", "--output", out2, "--layers", "1", "--kb-plan", "kb3"]) == 0
+    d = str(tmp_path / "enc")
+    export_trellis_dir(load_weight_set(out2)[1], d)
+    sha = hashlib.sha256(open(os.path.join(d, "trellis_manifest.json"), "rb").read()).hexdigest()
+    out3 = str(tmp_path / "c.r4dxb")
+    with pytest.raises(SystemExit, match="hashes to"):
+        convert_main(["--input", "random:tiny", "--output", out3, "--layers", "1", "--kb-plan", "kb3", "--trellis-from", d,
+                      "--trellis-manifest-sha256", "0" * 64])
+    assert convert_main(["--input", "random:tiny", "--output", out3, "--layers", "1", "--kb-plan", "kb3", "--trellis-from", d,
+                         "--trellis-manifest-sha256", sha.upper()]) == 0
