@@ -141,6 +141,9 @@ def convert_parser() -> argparse.ArgumentParser:
     ap.add_argument("--ldlq-damp", type=float, default=0.01, help="relative diagonal damping of the Hessians in the error-compensated trellis quantizer")
     ap.add_argument("--trellis-manifest-sha256", default=None, metavar="HEX",
                     help="with --trellis-from: refuse the directory unless its trellis_manifest.json has this sha256")
+    ap.add_argument("--draft-vocab-ids", default=None, metavar="FILE.json",
+                    help="with --mtp: a JSON list of token ids (or {\"ids\": [...]}); the container gets a smaller head over those "
+                         "ids (mtp.draft_head.lm_head + mtp.draft_head.vocab_ids) that the MTP drafter uses for its own drafts")
     ap.add_argument("--plan-only", action="store_true",
                     help="plan every tensor (layout, bit width, bytes) and print the container's tensor count and data bytes "
                          "without quantizing anything or writing --output")

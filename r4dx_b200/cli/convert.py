@@ -221,6 +221,23 @@ def main(argv=None) -> int:
                                                   out_hidden_size=cfg.hidden_size, num_position_embeddings=64), args.seed)
         for k, v in vw.items():
             q["vision." + k] = v.to(torch.bfloat16)
+    if args.draft_vocab_ids:
+        # reduced-vocabulary head for the MTP drafter's own drafts (the verify pass still scores the full vocabulary, so the
+        # output stays exact; reference: src/convert/main.cpp:165-169).  Ignored without --mtp, as there.
+        if args.mtp and any(k.startswith("mtp.") for k in w):
+            from ..quant import w4a16 as W4
+            raw_ids = json.load(open(args.draft_vocab_ids))
+            ids = sorted({int(i) for i in (raw_ids["ids"] if isinstance(raw_ids, dict) else raw_ids)})
+            if not ids or ids[0] < 0 or ids[-1] >= cfg.vocab_size:
+                raise SystemExit(f"--draft-vocab-ids: ids must lie in [0, {cfg.vocab_size})")
+            while len(ids) % 128:
+                ids.append(ids[-1])                  # padded with a repeat of the last id: the lowest index wins ties, same token
+            sel = torch.tensor(ids, dtype=torch.long)
+            rows = w["lm_head"].float()[sel]
+            q["mtp.draft_head.lm_head"] = rows.to(torch.bfloat16) if args.lm_head == "bf16" else W4.quantize(rows, args.lm_head_group)
+            q["mtp.draft_head.vocab_ids"] = sel.to(torch.int32)
+        else:
+            print("--draft-vocab-ids ignored: the container has no MTP head (--mtp)", file=sys.stderr)
     for k in list(q):
         if any(s in k for s in keep):
             q[k] = w[k].to(torch.bfloat16)

@@ -22,9 +22,12 @@ from .hybrid import MAX_ROWS, HybridModel, Linear
 BF = torch.bfloat16
 
 
-def mtp_config(cfg: ModelConfig) -> ModelConfig:
+def mtp_config(cfg: ModelConfig, vocab: int = 0) -> ModelConfig:
     import dataclasses
-    return dataclasses.replace(cfg, num_hidden_layers=1, layer_types=["full_attention"])
+    c = dataclasses.replace(cfg, num_hidden_layers=1, layer_types=["full_attention"])
+    if vocab:
+        c.vocab_size = vocab                 # a reduced-vocabulary draft head: the logits buffers shrink with it
+    return c
 
 
 class MtpDrafter:
@@ -33,12 +36,24 @@ class MtpDrafter:
     def __init__(self, main: HybridModel, weights: Dict[str, object]):
         self.main = main
         cfg = main.cfg
-        w: Dict[str, object] = {"text.embed_tokens": weights["text.embed_tokens"], "lm_head": weights["lm_head"],
+        # a container may carry a smaller head over a subset of the vocabulary for the drafter's own drafts
+        # (mtp.draft_head.lm_head [Vd, H] + mtp.draft_head.vocab_ids [Vd]): drafting reads Vd rows instead of the full
+        # vocabulary; the verify pass scores the full vocabulary, so what is emitted does not change
+        # (reference: src/convert/main.cpp:165-169 "reduced-vocab draft head").  Single-rank models only.
+        self.vocab_ids = None
+        head_w = weights["lm_head"]
+        vocab = 0
+        if "mtp.draft_head.lm_head" in weights and (main.comm is None or main.comm.world == 1):
+            head_w = weights["mtp.draft_head.lm_head"]
+            self.vocab_ids = weights["mtp.draft_head.vocab_ids"].to(main.device, torch.int32).contiguous()
+            vocab = int(self.vocab_ids.numel())
+        w: Dict[str, object] = {"text.embed_tokens": weights["text.embed_tokens"], "lm_head": head_w,
                                 "text.final_norm": weights["mtp.norm"]}
         for k, v in weights.items():
-            if k.startswith("mtp.") and k not in ("mtp.fc", "mtp.norm", "mtp.pre_fc_norm_embedding", "mtp.pre_fc_norm_hidden"):
+            if k.startswith("mtp.") and not k.startswith("mtp.draft_head.") and \
+                    k not in ("mtp.fc", "mtp.norm", "mtp.pre_fc_norm_embedding", "mtp.pre_fc_norm_hidden"):
                 w["text.layers.0." + k[4:]] = v
-        self.head = HybridModel(mtp_config(cfg), w, max_ctx=main.max_ctx, device=str(main.device), comm=main.comm)
+        self.head = HybridModel(mtp_config(cfg, vocab), w, max_ctx=main.max_ctx, device=str(main.device), comm=main.comm)
         self.fc = Linear(weights["mtp.fc"], "mtp.fc")
         self.norm_e, self.norm_h = weights["mtp.pre_fc_norm_embedding"], weights["mtp.pre_fc_norm_hidden"]
         H = cfg.hidden_size
@@ -127,6 +142,8 @@ class MtpDrafter:
             head.forward_rows(1, want_logits=True, skip_embed=True)
             head.pos += 1
             tok = head.buf.next_ids[:1].clone()
+            if self.vocab_ids is not None:
+                tok = self.vocab_ids[tok.long()]            # index in the reduced head -> token id
             hidden = head.buf.x[:1].clone()
             out.append(tok)
         head.pos = start + 1               # only the first pair (anchor, h_last) was a true pair

@@ -205,3 +205,29 @@ def test_group_rules_and_manifest_hash_flags(tmp_path):
                       "--trellis-manifest-sha256", "0" * 64])
     assert convert_main(["--input", "random:tiny", "--output", out3, "--layers", "1", "--kb-plan", "kb3", "--trellis-from", d,
                          "--trellis-manifest-sha256", sha.upper()]) == 0
+
+
+def test_reduced_vocabulary_draft_head_is_baked_with_mtp(tmp_path, capsys):
+    import json
+    from r4dx_b200.cli.convert import main as convert_main
+    from r4dx_b200.quant import w4a16
+    from r4dx_b200.quant.weights import load_weight_set
+    ids_file = tmp_path / "ids.json"
+    ids = sorted(set(torch.randint(0, 4096, (300,), generator=torch.Generator().manual_seed(0)).tolist()))
+    ids_file.write_text(json.dumps({"ids": ids}))
+    out = str(tmp_path / "m.r4dxb")
+    assert convert_main(["--input", "random:tiny", "--output", out, "--kb-plan", "kb3", "--mtp", "--draft-vocab-ids", str(ids_file)]) == 0
+    cfg, w = load_weight_set(out)
+    vid, dh = w["mtp.draft_head.vocab_ids"], w["mtp.draft_head.lm_head"]
+    assert vid.dtype == torch.int32 and vid.numel() % 128 == 0 and vid[:len(ids)].tolist() == ids and int(vid[-1]) == ids[-1]
+    assert dh.N == vid.numel() and dh.K == cfg.hidden_size
+    full = w4a16.dequantize(w["lm_head"])
+    part = w4a16.dequantize(dh)
+    assert (part - full[vid.long()]).abs().max().item() < 0.02 * full.abs().max().item()      # both are 4-bit roundings of the same rows
+    # without an MTP head the flag is ignored, with a note; ids outside the vocabulary are refused
+    out2 = str(tmp_path / "n.r4dxb")
+    assert convert_main(["--input", "random:tiny", "--output", out2, "--kb-plan", "kb3", "--layers", "1", "--draft-vocab-ids", str(ids_file)]) == 0
+    assert "ignored" in capsys.readouterr().err and "mtp.draft_head.lm_head" not in load_weight_set(out2)[1]
+    ids_file.write_text(json.dumps([1, 2, 5000]))
+    with pytest.raises(SystemExit, match="must lie in"):
+        convert_main(["--input", "random:tiny", "--output", out, "--kb-plan", "kb3", "--mtp", "--draft-vocab-ids", str(ids_file)])
