@@ -125,6 +125,8 @@ def convert_parser() -> argparse.ArgumentParser:
     ap.add_argument("--rotation-out", default=None, metavar="FILE.safetensors",
                     help="with --rotate and no quantization wanted: write only the rotation tensors and exit")
     ap.add_argument("--vision", default="off", choices=["on", "off"], help="keep the checkpoint's vision tower tensors (bf16)")
+    ap.add_argument("--audio", default="off", choices=["on", "off"],
+                    help="keep the checkpoint's audio embedder tensors ([model.]embed_audio.* -> audio.embed_audio.*, bf16; Gemma-style family)")
     ap.add_argument("--ngram-sidecar", default=None, metavar="FILE",
                     help="qwen4_exp: the n-gram table file the container refers to (required for that family; a random:q4x source "
                          "writes a small synthetic table there if the file does not exist)")

@@ -221,6 +221,25 @@ def main(argv=None) -> int:
                                                   out_hidden_size=cfg.hidden_size, num_position_embeddings=64), args.seed)
         for k, v in vw.items():
             q["vision." + k] = v.to(torch.bfloat16)
+    if args.audio == "on":
+        # the encoder-free audio embedder rides along in bf16 (reference: src/convert/main.cpp:184-186, --audio on copies
+        # model.embed_audio.* as audio.*); a random source gets a random projection of the serving code's shape
+        from ..models.audio import FRAME, WEIGHT_NAME
+        if cfg.arch != "gemma":
+            raise SystemExit("--audio on: the audio front end belongs to the Gemma-style family")
+        found = {}
+        for k, v in raw.items():
+            for pre in ("model.embed_audio.", "embed_audio."):
+                if k.startswith(pre):
+                    found["audio.embed_audio." + k[len(pre):]] = v.to(torch.bfloat16)
+        if not found:
+            if raw:
+                raise SystemExit("--audio on: the checkpoint has no embed_audio.* tensors")
+            gen = torch.Generator().manual_seed(args.seed + 5)
+            found[WEIGHT_NAME] = (torch.randn(cfg.hidden_size, FRAME, generator=gen) * 0.02).to(torch.bfloat16)
+        if WEIGHT_NAME not in found or tuple(found[WEIGHT_NAME].shape) != (cfg.hidden_size, FRAME):
+            raise SystemExit(f"--audio on: {WEIGHT_NAME} must be [{cfg.hidden_size}, {FRAME}]")
+        q.update(found)
     if args.draft_vocab_ids:
         # reduced-vocabulary head for the MTP drafter's own drafts (the verify pass still scores the full vocabulary, so the
         # output stays exact; reference: src/convert/main.cpp:165-169).  Ignored without --mtp, as there.

@@ -231,3 +231,17 @@ def test_reduced_vocabulary_draft_head_is_baked_with_mtp(tmp_path, capsys):
     ids_file.write_text(json.dumps([1, 2, 5000]))
     with pytest.raises(SystemExit, match="must lie in"):
         convert_main(["--input", "random:tiny", "--output", out, "--kb-plan", "kb3", "--mtp", "--draft-vocab-ids", str(ids_file)])
+
+
+def test_converter_keeps_the_audio_embedder(tmp_path):
+    from r4dx_b200.cli.convert import main as convert_main
+    from r4dx_b200.models.audio import FRAME, WEIGHT_NAME, load_audio_embedder
+    from r4dx_b200.quant.weights import load_weight_set
+    out = str(tmp_path / "g.r4dxb")
+    assert convert_main(["--input", "random:gemma", "--output", out, "--layers", "1", "--kb-plan", "kb3", "--audio", "on"]) == 0
+    cfg, w = load_weight_set(out)
+    assert w[WEIGHT_NAME].shape == (cfg.hidden_size, FRAME) and w[WEIGHT_NAME].dtype == torch.bfloat16
+    emb = load_audio_embedder(w)
+    assert emb is not None
+    with pytest.raises(SystemExit, match="Gemma-style"):
+        convert_main(["--input", "random:tiny", "--output", out, "--layers", "1", "--audio", "on"])
