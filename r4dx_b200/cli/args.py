@@ -96,8 +96,8 @@ def server_parser() -> argparse.ArgumentParser:
 
 def convert_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser("r4dxb-convert", description="checkpoint -> quantized container")
-    ap.add_argument("--input", required=True, help="safetensors file/dir with config.json, or 'random:<tiny|small>'")
-    ap.add_argument("--output", required=True)
+    ap.add_argument("--input", default=None, help="safetensors file/dir with config.json, a .gguf file, or 'random:<tiny|small|moe|llama|gemma|lfm2|q4x>'")
+    ap.add_argument("--output", default=None)
     ap.add_argument("--layouts", default="trellis", help="body layout: trellis, w4a16, w8a16 or bf16")
     ap.add_argument("--lm-head", default="w4a16", choices=["w4a16", "bf16"])
     ap.add_argument("--lm-head-group", type=int, default=64)
@@ -149,5 +149,10 @@ def convert_parser() -> argparse.ArgumentParser:
     ap.add_argument("--plan-only", action="store_true",
                     help="plan every tensor (layout, bit width, bytes) and print the container's tensor count and data bytes "
                          "without quantizing anything or writing --output")
+    ap.add_argument("--selftest-input", default=None, metavar="FILE.safetensors",
+                    help="one-tensor self test: quantize the 2-D tensor \"w\" of this file as if it were named --selftest-name, "
+                         "reconstruct it, print the error (and write the reconstruction to --selftest-output); needs no --input / --output")
+    ap.add_argument("--selftest-name", default="text.layers.0.mlp.down")
+    ap.add_argument("--selftest-output", default=None, metavar="FILE.safetensors")
     ap.add_argument("--selftest", action="store_true", help="re-open the output and verify every tensor's reconstruction error")
     return ap

@@ -129,12 +129,46 @@ def plan_container(cfg, w, layout: str, kb_rule, head_group: int, lm_head: str =
     return {"tensors": len(plan), "data_bytes": sum(v["bytes"] for v in plan.values()), "by_layout": by_layout, "plan": plan}
 
 
+def _selftest_one(args) -> int:
+    """Quantizes one tensor through the same code path a conversion takes and reports how well it reconstructs
+    (reference: src/convert/main.cpp:223-226 has the same one-tensor mode for its layouts)."""
+    from safetensors.torch import load_file, save_file
+    from ..config import tiny_hybrid_config
+    from ..quant.weights import dequantize_weight_set, quantize_weight_set
+    t = load_file(args.selftest_input).get("w")
+    if t is None or t.dim() != 2:
+        raise SystemExit("--selftest-input: the file must hold one 2-D tensor named \"w\"")
+    name = args.selftest_name
+    layout = args.layouts.split(",")[0]
+    q = quantize_weight_set(tiny_hybrid_config(), {name: t.float()}, layout=layout, kb_rule=_kb_rule(args.kb_plan),
+                            head_group=args.lm_head_group, seed=args.seed, group_rule=parse_group_rule(args.w4a16_group_rule),
+                            w8_group=args.w8a16_group or None)
+    back = dequantize_weight_set(q)[name]
+    err = float(((back - t.float()) ** 2).sum() / (t.float() ** 2).sum().clamp_min(1e-30))
+    stored = q[name]
+    rep = {"name": name, "layout": type(stored).__name__ if not isinstance(stored, torch.Tensor) else str(stored.dtype).replace("torch.", ""),
+           "shape": list(t.shape), "relative_squared_error": err,
+           "bytes": stored.nbytes if not isinstance(stored, torch.Tensor) else stored.numel() * stored.element_size()}
+    if hasattr(stored, "kb"):
+        rep["kb"] = stored.kb
+    if hasattr(stored, "group"):
+        rep["group"] = stored.group
+    if args.selftest_output:
+        save_file({"w": back.to(torch.bfloat16).contiguous()}, args.selftest_output)
+    print(json.dumps(rep))
+    return 0
+
+
 def main(argv=None) -> int:
     args = convert_parser().parse_args(argv)
     from ..quant.container import Container
     from ..quant.weights import dequantize_weight_set, load_weight_set, quantize_weight_set, save_weight_set
     if args.threads:
         torch.set_num_threads(args.threads)
+    if args.selftest_input:
+        return _selftest_one(args)
+    if not args.input or not args.output:
+        raise SystemExit("--input and --output are required")
     raw = {}
     cfg, w = load_source(args.input, args.layers, args.mtp, args.seed, raw_out=raw)
     if cfg.is_qwen4_exp:

@@ -245,3 +245,22 @@ def test_converter_keeps_the_audio_embedder(tmp_path):
     assert emb is not None
     with pytest.raises(SystemExit, match="Gemma-style"):
         convert_main(["--input", "random:tiny", "--output", out, "--layers", "1", "--audio", "on"])
+
+
+def test_one_tensor_selftest_mode(tmp_path, capsys):
+    import json
+    from safetensors.torch import load_file, save_file
+    from r4dx_b200.cli.convert import main as convert_main
+    src = str(tmp_path / "w.safetensors")
+    w = torch.randn(256, 128, generator=torch.Generator().manual_seed(1)) * 0.02
+    save_file({"w": w.to(torch.bfloat16)}, src)
+    outp = str(tmp_path / "back.safetensors")
+    assert convert_main(["--selftest-input", src, "--kb-plan", "kb4", "--selftest-output", outp]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["layout"] == "TrellisWeight" and rep["kb"] == 4 and 0 < rep["relative_squared_error"] < 6 * 4.0 ** -4
+    assert load_file(outp)["w"].shape == (256, 128)
+    assert convert_main(["--selftest-input", src, "--selftest-name", "lm_head", "--w4a16-group-rule", "^lm_head$=32"]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["layout"] == "W4Weight" and rep["group"] == 32 and rep["relative_squared_error"] < 0.02
+    with pytest.raises(SystemExit, match="--input and --output"):
+        convert_main(["--kb-plan", "kb4"])
