@@ -264,8 +264,8 @@ def _unpermute_rope(w: torch.Tensor, heads: int) -> torch.Tensor:
 def config_from_gguf(g: GgufFile) -> ModelConfig:
     md = g.metadata
     arch = str(md.get("general.architecture", "llama"))
-    if arch not in ("llama", "qwen2", "qwen3", "mistral"):
-        raise ValueError(f"GGUF architecture {arch!r} has no mapping onto this engine's dense decoder")
+    if arch not in ("llama", "qwen2", "qwen3", "mistral", "qwen2moe", "qwen3moe"):
+        raise ValueError(f"GGUF architecture {arch!r} has no mapping onto this engine's decoders")
     k = lambda name, default=None: md.get(f"{arch}.{name}", default)
     H, L, heads = int(k("embedding_length")), int(k("block_count")), int(k("attention.head_count"))
     kv = int(k("attention.head_count_kv", heads))
@@ -277,12 +277,40 @@ def config_from_gguf(g: GgufFile) -> ModelConfig:
                       rope_theta=float(k("rope.freq_base", 1.0e4)), rms_norm_eps=float(k("attention.layer_norm_rms_epsilon", 1e-6)),
                       vocab_size=vocab, tie_word_embeddings="output.weight" not in g.tensors, mtp_num_hidden_layers=0,
                       max_position_embeddings=int(k("context_length", 8192)))
+    if arch.endswith("moe"):
+        # attention in every layer, routed experts (stacked per projection in the file) and, for qwen2moe, a shared expert
+        # with a sigmoid gate: the engine's MoE family with no linear-attention layers
+        cfg.arch = "qwen_hybrid_moe"
+        cfg.num_experts = int(k("expert_count"))
+        cfg.num_experts_per_tok = int(k("expert_used_count"))
+        cfg.moe_intermediate_size = int(k("expert_feed_forward_length", cfg.intermediate_size))
+        cfg.shared_expert_intermediate_size = int(k("expert_shared_feed_forward_length", 0)) if "blk.0.ffn_gate_shexp.weight" in g.tensors else 0
+        cfg.norm_topk_prob = arch == "qwen3moe"
+        cfg.intermediate_size = 0
     cfg.validate()
     return cfg
 
 
+def _moe_tensors(g: GgufFile, cfg: ModelConfig, i: int, hf: Dict[str, torch.Tensor]) -> None:
+    """Layer i's experts: the file stacks them per projection ([experts, out, in]); the importer takes them one by one."""
+    p = f"model.layers.{i}.mlp."
+    hf[p + "gate.weight"] = g.tensor(f"blk.{i}.ffn_gate_inp.weight")
+    stacks = {n: g.tensor(f"blk.{i}.ffn_{n}_exps.weight") for n in ("gate", "up", "down")}
+    for n, t in stacks.items():
+        if t.dim() != 3 or t.shape[0] != cfg.num_experts:
+            raise ValueError(f"blk.{i}.ffn_{n}_exps.weight: shape {tuple(t.shape)} is not [experts, out, in]")
+    for e in range(cfg.num_experts):
+        for n in ("gate", "up", "down"):
+            hf[p + f"experts.{e}.{n}_proj.weight"] = stacks[n][e]
+    if cfg.shared_expert_intermediate_size:
+        for n in ("gate", "up", "down"):
+            hf[p + f"shared_expert.{n}_proj.weight"] = g.tensor(f"blk.{i}.ffn_{n}_shexp.weight")
+        hf[p + "shared_expert_gate.weight"] = g.tensor(f"blk.{i}.ffn_gate_inp_shexp.weight").reshape(1, -1)
+
+
 def import_gguf(path: str) -> Tuple[ModelConfig, Dict[str, torch.Tensor]]:
-    """GGUF checkpoint of a dense Llama-style / Qwen-style decoder -> (config, fp32 weights in this engine's names).
+    """GGUF checkpoint of a dense Llama-style / Qwen-style decoder, or of a Qwen-style MoE decoder (qwen2moe / qwen3moe:
+    experts stacked per projection, optional shared expert) -> (config, fp32 weights in this engine's names).
     Tensors are dequantised block by block; the converter then quantizes them into its own layouts."""
     from .hf_import import import_hf_weights
     g = GgufFile(path)
@@ -304,6 +332,8 @@ def import_gguf(path: str) -> Tuple[ModelConfig, Dict[str, torch.Tensor]]:
                 elif permuted and theirs == "attn_k":
                     t = _unpermute_rope(t, cfg.num_key_value_heads)
                 hf[f"model.layers.{i}.{mine}.weight"] = t
+            if cfg.is_moe:
+                _moe_tensors(g, cfg, i, hf)
         return cfg, import_hf_weights(cfg, hf)
     finally:
         g.close()

@@ -200,8 +200,9 @@ def import_hf_weights(cfg: ModelConfig, hf: Dict[str, torch.Tensor], prefix: str
         m = s + "mlp."
         if cfg.is_moe:
             out[p + "moe.router"] = get(m + "gate.weight")
-            out[p + "moe.shared_gate"] = get(m + "shared_expert_gate.weight").reshape(1, -1)
-            out[p + "moe.shared.gate_up"], out[p + "moe.shared.down"] = gate_up(m + "shared_expert."), get(m + "shared_expert.down_proj.weight")
+            if cfg.shared_expert_intermediate_size:
+                out[p + "moe.shared_gate"] = get(m + "shared_expert_gate.weight").reshape(1, -1)
+                out[p + "moe.shared.gate_up"], out[p + "moe.shared.down"] = gate_up(m + "shared_expert."), get(m + "shared_expert.down_proj.weight")
             for e in range(cfg.num_experts):
                 out[p + f"moe.experts.{e}.gate_up"] = gate_up(m + f"experts.{e}.")
                 out[p + f"moe.experts.{e}.down"] = get(m + f"experts.{e}.down_proj.weight")

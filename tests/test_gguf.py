@@ -135,3 +135,51 @@ def test_llama_gguf_imports_to_the_same_model(tmp_path):
     # the converter takes the file directly
     from r4dx_b200.cli.convert import main as convert_main
     assert convert_main(["--input", path, "--output", str(tmp_path / "m.r4dxb"), "--layers", "1"]) == 0
+
+
+def test_moe_gguf_with_stacked_experts_imports_to_the_same_model(tmp_path):
+    """An all-attention MoE decoder written the way such files are (experts stacked per projection, shared expert with its
+    gate) -> import: the same weights, the same logits."""
+    import dataclasses
+    from r4dx_b200.config import tiny_moe_config
+    from r4dx_b200.models.oracle import OracleModel, init_weights
+    cfg = dataclasses.replace(tiny_moe_config(), layer_types=["full_attention"] * 2, num_hidden_layers=2, attn_output_gate=False,
+                              norm_zero_centered=False, partial_rotary_factor=1.0, rope_theta=1.0e6, norm_topk_prob=False)
+    from r4dx_b200.quant import hf_import as HI
+    w = init_weights(cfg, 3)
+    hf = HI.export_hf_weights(cfg, w)                            # the checkpoint's conventions (plain norm scales, split gate / up)
+    E, I = cfg.num_experts, cfg.moe_intermediate_size
+    f32 = lambda t: (t.contiguous().numpy(), G.GGML_F32)
+    tensors = {"token_embd.weight": f32(hf["model.embed_tokens.weight"]), "output_norm.weight": f32(hf["model.norm.weight"]),
+               "output.weight": f32(hf["lm_head.weight"])}
+    rev = {v: k for k, v in G._LAYER_NAMES.items()}
+    for i in range(2):
+        L = f"model.layers.{i}."
+        for mine, theirs in rev.items():
+            if L + mine + ".weight" in hf:
+                tensors[f"blk.{i}.{theirs}.weight"] = f32(hf[L + mine + ".weight"])
+        m = L + "mlp."
+        tensors[f"blk.{i}.ffn_gate_inp.weight"] = f32(hf[m + "gate.weight"])
+        tensors[f"blk.{i}.ffn_gate_inp_shexp.weight"] = f32(hf[m + "shared_expert_gate.weight"].reshape(-1))
+        for n in ("gate", "up", "down"):
+            tensors[f"blk.{i}.ffn_{n}_exps.weight"] = f32(torch.stack([hf[m + f"experts.{e}.{n}_proj.weight"] for e in range(E)]))
+            tensors[f"blk.{i}.ffn_{n}_shexp.weight"] = f32(hf[m + f"shared_expert.{n}_proj.weight"])
+    a = "qwen2moe"
+    md = {"general.architecture": a, f"{a}.block_count": 2, f"{a}.embedding_length": cfg.hidden_size, f"{a}.feed_forward_length": 0,
+          f"{a}.attention.head_count": cfg.num_attention_heads, f"{a}.attention.head_count_kv": cfg.num_key_value_heads,
+          f"{a}.attention.key_length": cfg.head_dim, f"{a}.rope.freq_base": float(cfg.rope_theta),
+          f"{a}.attention.layer_norm_rms_epsilon": float(cfg.rms_norm_eps), f"{a}.expert_count": E,
+          f"{a}.expert_used_count": cfg.num_experts_per_tok, f"{a}.expert_feed_forward_length": I,
+          f"{a}.expert_shared_feed_forward_length": cfg.shared_expert_intermediate_size}
+    path = str(tmp_path / "moe.gguf")
+    G.write_gguf(path, md, tensors)
+    cfg2, back = G.import_gguf(path)
+    assert cfg2.is_moe and cfg2.num_experts == E and cfg2.shared_expert_intermediate_size == cfg.shared_expert_intermediate_size
+    assert cfg2.layer_types == ["full_attention"] * 2 and not cfg2.norm_topk_prob and not cfg2.attn_output_gate
+    assert set(back) == set(w)
+    for k_ in w:
+        assert torch.allclose(back[k_], w[k_], atol=1e-6), k_
+    ids = torch.randint(0, cfg.vocab_size, (7,), generator=torch.Generator().manual_seed(0))
+    la, _ = OracleModel(cfg, w).forward(ids)
+    lb, _ = OracleModel(cfg2, back).forward(ids)
+    assert torch.allclose(la, lb, atol=1e-4)
