@@ -23,6 +23,12 @@ def add_model_flags(ap: argparse.ArgumentParser) -> None:
     g.add_argument("--dflash-p-min", type=float, default=0.0)
     g.add_argument("--dflash-n-min", type=int, default=0)
     g.add_argument("--vision", default="off", choices=["off", "on"])
+    g.add_argument("--image-max-pixels", type=int, default=0,
+                   help="upper bound on an image's resized area in pixels (0: the vision tower's own limit); the hybrid family's tower")
+    g.add_argument("--image-soft-tokens", type=int, default=0,
+                   help="rows an image may take in the prompt (70, 140, 280, 560 or 1120; 0: 280); the Gemma-style family's embedder")
+    g.add_argument("--mtp-draft-head", default="on", choices=["on", "off"],
+                   help="use the container's reduced-vocabulary draft head for the MTP drafter's own drafts when it has one")
     g.add_argument("--ngram-sidecar", default=None, metavar="FILE",
                    help="qwen4_exp: the n-gram table file (default: the one the container records, next to it)")
     g.add_argument("--ngram-placement", default="device", choices=["device", "pinned", "file"],

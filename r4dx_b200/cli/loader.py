@@ -75,7 +75,7 @@ def load_text_model(args, device: Optional[str] = None):
     drafter = None
     if args.mtp > 0 and any(k.startswith("mtp.") for k in weights):
         from ..models.mtp import MtpDrafter
-        drafter = MtpDrafter(model, weights)
+        drafter = MtpDrafter(model, weights, use_draft_head=getattr(args, "mtp_draft_head", "on") == "on")
     if getattr(args, "ngram", 0) > 0 and drafter is None:
         from ..models.ngram import NgramDrafter
         drafter = NgramDrafter()

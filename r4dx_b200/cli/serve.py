@@ -40,6 +40,11 @@ def main(argv=None) -> int:
             from ..models.gemma_vision import GemmaVisionFront, random_embedder_weights
             vision = (GemmaVisionFront.from_container_tensors(vw, str(tm.m.device)) if vw
                       else GemmaVisionFront(random_embedder_weights(tm.config.hidden_size), str(tm.m.device)))
+            if getattr(args, "image_soft_tokens", 0):
+                from ..models.gemma_vision import SOFT_TOKEN_BUDGETS
+                if args.image_soft_tokens not in SOFT_TOKEN_BUDGETS:
+                    raise SystemExit(f"--image-soft-tokens must be one of {SOFT_TOKEN_BUDGETS}")
+                vision.max_soft_tokens = args.image_soft_tokens
             vcfg, vw = vision, None
         else:
             vcfg = VisionConfig.from_weights(vw) if vw else None
@@ -48,6 +53,8 @@ def main(argv=None) -> int:
                                 out_hidden_size=tm.config.hidden_size, num_position_embeddings=64, max_pixels=256 * 256)
             vw = init_vision_weights(vcfg, 0)
         if vision is None:
+            if getattr(args, "image_max_pixels", 0):
+                vcfg.max_pixels = max(vcfg.min_pixels, min(vcfg.max_pixels, args.image_max_pixels))
             vision = VisionTower(vcfg, vw, device=str(tm.m.device))
         image_id = getattr(tk, "image_pad_id", tm.config.vocab_size - 1)
         eng.vision = vision

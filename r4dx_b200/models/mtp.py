@@ -33,7 +33,7 @@ def mtp_config(cfg: ModelConfig, vocab: int = 0) -> ModelConfig:
 class MtpDrafter:
     kind = "mtp"
 
-    def __init__(self, main: HybridModel, weights: Dict[str, object]):
+    def __init__(self, main: HybridModel, weights: Dict[str, object], use_draft_head: bool = True):
         self.main = main
         cfg = main.cfg
         # a container may carry a smaller head over a subset of the vocabulary for the drafter's own drafts
@@ -43,7 +43,7 @@ class MtpDrafter:
         self.vocab_ids = None
         head_w = weights["lm_head"]
         vocab = 0
-        if "mtp.draft_head.lm_head" in weights and (main.comm is None or main.comm.world == 1):
+        if use_draft_head and "mtp.draft_head.lm_head" in weights and (main.comm is None or main.comm.world == 1):
             head_w = weights["mtp.draft_head.lm_head"]
             self.vocab_ids = weights["mtp.draft_head.vocab_ids"].to(main.device, torch.int32).contiguous()
             vocab = int(self.vocab_ids.numel())
