@@ -50,6 +50,8 @@ def add_model_flags(ap: argparse.ArgumentParser) -> None:
     p.add_argument("--pp-min-rows", type=int, default=512)
     p.add_argument("--ep", type=int, default=1, choices=[1, 2, 4, 8],
                    help="expert parallelism for mixture-of-experts models: whole attention per rank, a slice of the experts each")
+    p.add_argument("--hybrid-ctx", type=int, default=0,
+                   help="--hybrid: positions the two pipeline stages keep state for (0: --max-ctx); longer prompts prefill tensor-parallel")
     p.add_argument("--hybrid", action="store_true", help="pipeline-parallel prefill, then reshard to tensor-parallel decode")
     p.add_argument("--tp-fault", default=os.environ.get("R4DXB_TP_FAULT", ""), help="host-side fault injection 'rank:n:kind'")
 

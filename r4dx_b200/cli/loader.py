@@ -166,7 +166,10 @@ def _load_pipeline(args, gcfg, cfg, weights, full, model_id, device, rank, world
     rng = (0, split) if rank == 0 else (split, gcfg.num_hidden_layers)
     # the stage runs full-width layers: the unsharded weights (a synthetic set is re-created unsharded)
     stage_w = full if full is not None else weights
-    stage = HybridModel(gcfg, stage_w, max_ctx=args.max_ctx, device=device, layer_range=rng)
+    # the pipeline stages keep state for prompts only: with --hybrid-ctx they hold fewer positions than the decode model, and
+    # longer prompts take the tensor-parallel prefill (reference: docs/usage.md "--hybrid-ctx N": the stage-KV capacity)
+    stage_ctx = min(args.max_ctx, getattr(args, "hybrid_ctx", 0) or args.max_ctx) if hybrid else args.max_ctx
+    stage = HybridModel(gcfg, stage_w, max_ctx=stage_ctx, device=device, layer_range=rng)
     chunk = getattr(args, "prefill_chunk", 0) or 1024
     tk, tpl = load_tokenizer(args.tokenizer_dir, gcfg.vocab_size)
     if not hybrid:

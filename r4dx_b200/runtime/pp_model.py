@@ -108,8 +108,10 @@ class HybridPpTextModel(LocalTextModel):
 
     def prefill(self, ids: Sequence[int], embed_overrides=None) -> int:
         ids = list(ids)
-        if len(ids) < self.min_rows or self.m.pos != 0 or embed_overrides is not None or self.drafter is not None:
-            # short prompts, continuations of a cached prefix, multimodal rows and drafter hooks: the tensor-parallel model
+        if len(ids) < self.min_rows or len(ids) > self.stage.max_ctx or self.m.pos != 0 or embed_overrides is not None \
+                or self.drafter is not None:
+            # short prompts, prompts beyond the stages' capacity, continuations of a cached prefix, multimodal rows and drafter
+            # hooks: the tensor-parallel model
             return super().prefill(ids, embed_overrides)
         self._graph_active = False
         self.stage.reset()
