@@ -264,3 +264,21 @@ def test_one_tensor_selftest_mode(tmp_path, capsys):
     assert rep["layout"] == "W4Weight" and rep["group"] == 32 and rep["relative_squared_error"] < 0.02
     with pytest.raises(SystemExit, match="--input and --output"):
         convert_main(["--kb-plan", "kb4"])
+
+
+def test_draft_vocabulary_picker(tmp_path, capsys):
+    import json
+    from r4dx_b200.utils.draft_vocab import main as dv_main, pick_ids
+    rep = pick_ids([[5, 5, 5, 7, 7, 9], [5, 11]], size=3, always=[2])
+    assert rep["ids"] == [2, 5, 7] and rep["sample_tokens"] == 8 and abs(rep["coverage"] - 6 / 8) < 1e-9
+    assert pick_ids([[1, 2, 3]], size=10, vocab_size=3)["ids"] == [1, 2]           # ids outside the vocabulary are dropped
+    txt = tmp_path / "a.txt"
+    txt.write_text("hello hello world")
+    log = tmp_path / "b.jsonl"
+    log.write_text(json.dumps({"messages": [{"role": "user", "content": "hello tool"}]}) + "\n")
+    out = str(tmp_path / "ids.json")
+    assert dv_main(["--text", str(txt), str(log), "--size", "8", "--out", out]) == 0
+    ids = json.load(open(out))["ids"]
+    assert len(ids) == 8 and ids == sorted(ids) and ord("l") in ids and ord("o") in ids
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert 0 < rep["coverage"] <= 1 and rep["kept"] == 8
