@@ -418,8 +418,9 @@ def export_hf_weights(cfg: ModelConfig, w: Dict[str, torch.Tensor], prefix: str 
 
         if cfg.is_moe:
             hf[m + "gate.weight"] = w[p + "moe.router"].float()
-            hf[m + "shared_expert_gate.weight"] = w[p + "moe.shared_gate"].float()
-            split("moe.shared", m + "shared_expert.")
+            if cfg.shared_expert_intermediate_size:
+                hf[m + "shared_expert_gate.weight"] = w[p + "moe.shared_gate"].float()
+                split("moe.shared", m + "shared_expert.")
             for e in range(cfg.num_experts):
                 split(f"moe.experts.{e}", m + f"experts.{e}.")
         else:
