@@ -110,6 +110,9 @@ def convert_parser() -> argparse.ArgumentParser:
     ap.add_argument("--lm-head", default="w4a16", choices=["w4a16", "bf16"])
     ap.add_argument("--lm-head-group", type=int, default=64)
     ap.add_argument("--kb-plan", default="mix4.5", choices=["mix4.5", "mix3.3", "kb3", "kb4", "kb5"])
+    ap.add_argument("--kb-plan-file", default=None, metavar="PLAN.json",
+                    help="per-class trellis bit widths written by `python -m r4dx_b200.utils.alloc_bits` (classes it does not "
+                         "name take --kb-plan)")
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--threads", type=int, default=0)
     ap.add_argument("--encoder", default="cpu", choices=["cpu", "cuda"], help="where the trellis Viterbi search runs")

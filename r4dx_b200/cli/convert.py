@@ -15,9 +15,19 @@ import torch
 from .args import convert_parser
 
 
-def _kb_rule(plan: str):
+def _kb_rule(plan: str, plan_file: str = None):
     from ..quant.weights import default_kb_rule, moe_kb_rule
-    return {"mix4.5": default_kb_rule, "mix3.3": moe_kb_rule, "kb3": lambda n: 3, "kb4": lambda n: 4, "kb5": lambda n: 5}[plan]
+    base = {"mix4.5": default_kb_rule, "mix3.3": moe_kb_rule, "kb3": lambda n: 3, "kb4": lambda n: 4, "kb5": lambda n: 5}[plan]
+    if not plan_file:
+        return base
+    from ..utils.alloc_bits import class_of
+    doc = json.load(open(plan_file))
+    if doc.get("format") != "r4dxb-kb-plan-1" or not isinstance(doc.get("classes"), dict):
+        raise SystemExit(f"--kb-plan-file {plan_file}: not a bit-width plan")
+    classes = {k: int(v) for k, v in doc["classes"].items()}
+    if any(v not in (3, 4, 5) for v in classes.values()):
+        raise SystemExit(f"--kb-plan-file {plan_file}: widths must be 3, 4 or 5")
+    return lambda name: classes.get(class_of(name), base(name))
 
 
 def parse_group_rule(text: str):
@@ -182,7 +192,7 @@ def main(argv=None) -> int:
     keep = [s for s in args.keep_bf16.split(",") if s]
     layout = args.layouts.split(",")[0]
     if args.plan_only:
-        rep = plan_container(cfg, w, layout, _kb_rule(args.kb_plan), args.lm_head_group, args.lm_head, keep)
+        rep = plan_container(cfg, w, layout, _kb_rule(args.kb_plan, args.kb_plan_file), args.lm_head_group, args.lm_head, keep)
         plan = rep.pop("plan")
         rep["largest"] = [[n, v["layout"], v["bytes"]] for n, v in sorted(plan.items(), key=lambda kv: -kv[1]["bytes"])[:5]]
         rep["arch"] = cfg.arch
@@ -237,7 +247,7 @@ def main(argv=None) -> int:
                                                    "verify": args.trellis_verify, "worst": worst[1], "worst_tensor": worst[0]})
         print(f"imported {len(imported)} trellis tensors from {args.trellis_from} (worst reconstruction error {worst[1]:.4f} at {worst[0]})",
               file=sys.stderr)
-    q = quantize_weight_set(cfg, src, layout=layout, kb_rule=_kb_rule(args.kb_plan), head_group=args.lm_head_group, seed=args.seed,
+    q = quantize_weight_set(cfg, src, layout=layout, kb_rule=_kb_rule(args.kb_plan, args.kb_plan_file), head_group=args.lm_head_group, seed=args.seed,
                             encoder=args.encoder, hessians=hessians, imatrix=imatrix, search=args.quant == "search",
                             group_rule=parse_group_rule(args.w4a16_group_rule), w8_group=args.w8a16_group or None,
                             ldlq_damp=args.ldlq_damp)

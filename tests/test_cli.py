@@ -282,3 +282,33 @@ def test_draft_vocabulary_picker(tmp_path, capsys):
     assert len(ids) == 8 and ids == sorted(ids) and ord("l") in ids and ord("o") in ids
     rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
     assert 0 < rep["coverage"] <= 1 and rep["kept"] == 8
+
+
+def test_bit_allocation_under_a_byte_budget(tmp_path, capsys):
+    import json
+    from r4dx_b200.cli.convert import main as convert_main
+    from r4dx_b200.quant.weights import load_weight_set
+    from r4dx_b200.utils import alloc_bits as AB
+    assert AB.class_of("text.layers.7.moe.experts.12.gate_up") == "text.layers.7.moe.experts.*.gate_up"
+    err = {"a": {3: 1.0, 4: 0.2, 5: 0.05}, "b": {3: 0.5, 4: 0.4, 5: 0.39}, "c": {3: 2.0, 4: 0.5, 5: 0.1}}
+    size = {"a": 8000, "b": 8000, "c": 80000}
+    base = sum(size.values()) * 3 // 8
+    assert AB.allocate(err, size, base) == {"a": 3, "b": 3, "c": 3}
+    assert AB.allocate(err, size, base + 1000) == {"a": 4, "b": 3, "c": 3}                  # the best error drop per byte first
+    assert AB.allocate(err, size, base + 2000) == {"a": 5, "b": 3, "c": 3}
+    assert AB.allocate(err, size, base + 12100) == {"a": 5, "b": 3, "c": 4} or AB.allocate(err, size, base + 12100)["c"] == 4
+    assert AB.allocate(err, size, 10 ** 9) == {"a": 5, "b": 5, "c": 5}
+    with pytest.raises(ValueError, match="budget"):
+        AB.allocate(err, size, base - 1)
+    plan = str(tmp_path / "plan.json")
+    assert AB.main(["--input", "random:moe", "--layers", "1", "--budget-mib", "0.9", "--out", plan]) == 0
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    doc = json.load(open(plan))
+    assert rep["bytes"] <= 0.9 * 2 ** 20 and 3.0 <= rep["bits_per_weight"] <= 5.0 and doc["format"] == "r4dxb-kb-plan-1"
+    assert "text.layers.0.moe.experts.*.gate_up" in doc["classes"]
+    out = str(tmp_path / "m.r4dxb")
+    assert convert_main(["--input", "random:moe", "--layers", "1", "--output", out, "--kb-plan", "kb3", "--kb-plan-file", plan]) == 0
+    cfg, w = load_weight_set(out)
+    for name, t in w.items():
+        if type(t).__name__ == "TrellisWeight":
+            assert t.kb == doc["classes"][AB.class_of(name)], name
