@@ -77,7 +77,7 @@ def main() -> None:
                           "ms": ms, "tok_s": a.prefill / (ms / 1e3)}))
         return
     if a.single and a.family == "qwen4_exp":
-        # really prefilled context (the 8-row path is this family's prompt path), then graph decode
+        # really prefilled context (1024-row chunks on the tensor cores), then graph decode
         from r4dx_b200.models.q4x import Qwen4ExpModel
         from r4dx_b200.runtime import ngram as NG
         hd = NG.make_header(cfg.vocab_size, cfg.ngram_head_dim, cfg.eos_token_id, seed=0, first_prime_after=a.ngram_first_prime)
@@ -107,7 +107,6 @@ def main() -> None:
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / a.steps
-        from r4dx_b200 import native
         print(json.dumps({"metric": "batch-1 decode tok/s, qwen4_exp geometry", "ctx": a.ctx, "layers": cfg.num_hidden_layers,
                           "ms_per_step": ms, "tok_s": 1e3 / ms, "prefill_tok_s": a.ctx / (pre_ms / 1e3),
                           "weights_gib": m.weight_bytes() / 2**30, "ngram_table_gib": table.body.numel() * 2 / 2**30,
